@@ -1,0 +1,105 @@
+"""ctypes bindings of the in-tree native libraries.
+
+``kernels()`` returns ``libtpb200.so`` (sm_100a CUDA kernels, C ABI) with argument types set;
+``runtime()`` returns ``libtpb200rt.so`` (host runtime: store, ``.mega`` IO, symmetric memory).
+On a machine with a CUDA device the kernel library is mandatory: ops raise if it is missing
+instead of silently falling back to PyTorch.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+from pathlib import Path
+
+_LIBDIR = Path(__file__).resolve().parent / "_lib"
+_lock = threading.Lock()
+_kernels = None
+_runtime = None
+
+P = C.c_void_p
+I = C.c_int
+LL = C.c_longlong
+F = C.c_float
+U32 = C.c_uint32
+
+_KERNEL_SIGS = {
+    "tpb_gemm_bf16": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P],
+    "tpb_rmsnorm_fwd": [P, P, P, P, P, P, I, I, LL, LL, F, P],
+    "tpb_rmsnorm_bwd_grid": [I, I],
+    "tpb_rmsnorm_bwd": [P, P, P, P, P, P, P, P, P, I, I, I, LL, LL, LL, P],
+    "tpb_layernorm_fwd": [P, P, P, P, P, P, I, I, F, P],
+    "tpb_layernorm_bwd": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, P],
+    "tpb_rope": [P, P, P, P, LL, I, I, LL, LL, I, I, I, P],
+    "tpb_swiglu_fwd": [P, P, P, LL, I, LL, P],
+    "tpb_swiglu_bwd": [P, P, P, P, P, LL, I, LL, LL, P],
+    "tpb_gelu_fwd": [P, P, LL, I, P],
+    "tpb_gelu_bwd": [P, P, P, LL, I, P],
+    "tpb_cross_entropy": [P, P, P, P, P, LL, I, LL, LL, F, P],
+    "tpb_cross_entropy_bwd": [P, P, P, P, P, P, P, LL, I, LL, LL, P],
+    "tpb_adamw_flat": [P, P, P, P, I, P, I, LL, F, F, F, F, F, I, F, I, P, P, P],
+    "tpb_adamw_multi": [I, P, P, P, P, P, P, I, I, F, F, F, F, F, I, F, I, P, P, P],
+    "tpb_sumsq": [P, I, LL, F, P, P],
+    "tpb_clip_coef": [P, F, P, P, P],
+}
+
+
+class NativeUnavailable(RuntimeError):
+    pass
+
+
+def _load(name: str):
+    path = _LIBDIR / name
+    if not path.exists():
+        # Build lazily when a compiler is around (developer machines, CI); the GPU boxes
+        # receive the prebuilt objects with the tree.
+        if os.environ.get("TPB_NO_AUTOBUILD") != "1":
+            try:
+                from . import _build
+                _build.build_all()
+            except Exception as e:  # pragma: no cover - depends on toolchain
+                raise NativeUnavailable(f"{name} is not built and the in-tree build failed: {e}")
+    if not path.exists():
+        raise NativeUnavailable(f"{path} not found; run `python -m tensorplay_b200._build`")
+    return C.CDLL(str(path), mode=C.RTLD_GLOBAL)
+
+
+def register_sigs(lib, sigs) -> None:
+    for fn, args in sigs.items():
+        if hasattr(lib, fn):
+            f = getattr(lib, fn)
+            f.argtypes = args
+            f.restype = C.c_int
+
+
+def kernels():
+    global _kernels
+    if _kernels is None:
+        with _lock:
+            if _kernels is None:
+                lib = _load("libtpb200.so")
+                register_sigs(lib, _KERNEL_SIGS)
+                _kernels = lib
+    return _kernels
+
+
+def runtime():
+    global _runtime
+    if _runtime is None:
+        with _lock:
+            if _runtime is None:
+                _runtime = _load("libtpb200rt.so")
+    return _runtime
+
+
+def kernels_available() -> bool:
+    try:
+        kernels()
+        return True
+    except Exception:
+        return False
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise RuntimeError(f"{what} failed with code {code}")

@@ -1,0 +1,15 @@
+"""Hot ops of the framework. CUDA tensors run the hand-written sm_100a kernels of
+``libtpb200.so``; CPU tensors run a plain-PyTorch path that doubles as the correctness oracle."""
+from ._common import DeviceWaitTimeout, check_status, status_word
+from .activation import gelu, swiglu, swiglu_packed
+from .gemm import gemm, linear
+from .loss import cross_entropy
+from .norm import layer_norm, rms_norm
+from .optim import adamw_flat_, adamw_multi_, clip_coef_, sumsq_
+from .rope import apply_rope, rope_tables
+
+__all__ = [
+    "DeviceWaitTimeout", "check_status", "status_word", "gelu", "swiglu", "swiglu_packed", "gemm",
+    "linear", "cross_entropy", "layer_norm", "rms_norm", "adamw_flat_", "adamw_multi_",
+    "clip_coef_", "sumsq_", "apply_rope", "rope_tables",
+]

@@ -1,0 +1,105 @@
+"""bf16 GEMM on the tcgen05 kernel, and the autograd ``linear`` built on it.
+
+Replaces the cuBLASLt route of the reference (p10/src/backend/cuda/CudaBlasGemm.cpp:694-1052,
+callers p10/src/backend/cuda/LinearAlgebraKernels.cu:1304-1350).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import _native
+from ._common import lib, ptr, status_word, stream_ptr, use_native
+
+
+def _rowmajor(t: torch.Tensor) -> torch.Tensor:
+    if t.stride(-1) != 1 or (t.dim() == 2 and (t.stride(0) % 8 or t.data_ptr() % 16)):
+        t = t.contiguous()
+    return t
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+         accumulate: bool = False, out_dtype: torch.dtype = torch.bfloat16,
+         alpha: float = 1.0) -> torch.Tensor:
+    """``C[m, n] (+)= alpha * sum_k A(m, k) * B(n, k) (+ bias[n])``.
+
+    ``a`` is ``[M, K]`` (``a_mn=False``) or stored transposed ``[K, M]`` (``a_mn=True``);
+    ``b`` is ``[N, K]`` or stored ``[K, N]`` (``b_mn=True``). Operands are bf16, the
+    accumulator fp32, ``out`` bf16 or fp32.
+    """
+    if a_mn:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    if K != Kb:
+        raise ValueError(f"gemm: reduce dims differ ({K} vs {Kb})")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    if not use_native(a, b, out):
+        af = (a.t() if a_mn else a).float()
+        bf = (b if b_mn else b.t()).float()
+        r = alpha * (af @ bf)
+        if bias is not None:
+            r = r + bias.float()
+        if accumulate:
+            r = r + out.float()
+        out.copy_(r.to(out.dtype))
+        return out
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        raise TypeError("gemm: operands must be bfloat16 on CUDA")
+    a = _rowmajor(a)
+    b = _rowmajor(b)
+    if out.stride(-1) != 1:
+        raise ValueError("gemm: out must be row-major")
+    if K % 8 or a.stride(0) % 8 or b.stride(0) % 8:
+        raise ValueError("gemm: leading dimensions must be multiples of 8 elements")
+    st = status_word(a.device)
+    code = lib().tpb_gemm_bf16(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), ptr(bias), M, N, K,
+        a.stride(0), b.stride(0), out.stride(0), int(a_mn), int(b_mn),
+        int(out.dtype == torch.float32), int(bias is not None and bias.dtype == torch.float32),
+        int(accumulate), float(alpha), st.data_ptr(), stream_ptr())
+    _native.check(code, "tpb_gemm_bf16")
+    return out
+
+
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        x2 = x.reshape(-1, x.shape[-1])
+        y = gemm(x2, weight, bias=bias)
+        ctx.save_for_backward(x2, weight)
+        ctx.has_bias = bias is not None
+        ctx.x_shape = x.shape
+        return y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, weight, b_mn=True).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            dw = gemm(dy2, x2, a_mn=True, b_mn=True)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(dy.dtype)
+        return dx, dw, db
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ weight.T + bias``; on CUDA bf16 all three products run on the tcgen05 GEMM."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
+        return _LinearFn.apply(x, weight, bias)
+    if x.is_cuda:
+        # other dtypes on CUDA: cast through bf16 is not silently done; use torch's path
+        return torch.nn.functional.linear(x, weight, bias)
+    return torch.nn.functional.linear(x, weight, bias)

@@ -1,0 +1,106 @@
+"""Fused AdamW step over flat shards or tensor lists (sm_100a), plus grad-norm helpers.
+
+Reference counterpart: ``_fused_adamw_`` multi-tensor apply,
+p10/include/OptimizerMTA.cuh:560-748 and p10/src/backend/cuda/OptimizerKernels.cu.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence
+
+import torch
+
+from .. import _native
+from ._common import lib, ptr, stream_ptr, use_native
+
+
+def adamw_flat_(master: torch.Tensor, exp_avg: torch.Tensor, exp_avg_sq: torch.Tensor,
+                grad: torch.Tensor, model: Optional[torch.Tensor], *, lr: float, beta1: float,
+                beta2: float, eps: float, weight_decay: float, step: int, grad_scale: float = 1.0,
+                maximize: bool = False, clip_coef: Optional[torch.Tensor] = None,
+                found_inf: Optional[torch.Tensor] = None) -> None:
+    """One AdamW step on a flat fp32 master/moment shard; writes the bf16/fp32 model copy."""
+    n = master.numel()
+    if use_native(master, grad):
+        code = lib().tpb_adamw_flat(
+            master.data_ptr(), exp_avg.data_ptr(), exp_avg_sq.data_ptr(), grad.data_ptr(),
+            int(grad.dtype == torch.bfloat16), ptr(model),
+            int(model is not None and model.dtype == torch.bfloat16), n, lr, beta1, beta2, eps,
+            weight_decay, int(step), float(grad_scale), int(maximize), ptr(clip_coef),
+            ptr(found_inf), stream_ptr())
+        _native.check(code, "tpb_adamw_flat")
+        return
+    if found_inf is not None and float(found_inf) != 0.0:
+        return
+    g = grad.float() * grad_scale
+    if clip_coef is not None:
+        g = g * clip_coef.float()
+    if maximize:
+        g = -g
+    master.mul_(1 - lr * weight_decay)
+    exp_avg.mul_(beta1).add_(g, alpha=1 - beta1)
+    exp_avg_sq.mul_(beta2).addcmul_(g, g, value=1 - beta2)
+    bc1 = 1 - beta1 ** step
+    bc2 = 1 - beta2 ** step
+    denom = exp_avg_sq.sqrt() / (bc2 ** 0.5) + eps
+    master.addcdiv_(exp_avg, denom, value=-lr / bc1)
+    if model is not None:
+        model.copy_(master)
+
+
+def _ptr_array(ts: Sequence[Optional[torch.Tensor]]):
+    arr = (C.c_void_p * len(ts))()
+    for i, t in enumerate(ts):
+        arr[i] = None if t is None else t.data_ptr()
+    return arr
+
+
+def adamw_multi_(masters: List[torch.Tensor], exp_avgs: List[torch.Tensor],
+                 exp_avg_sqs: List[torch.Tensor], grads: List[torch.Tensor],
+                 models: Optional[List[torch.Tensor]], *, lr: float, beta1: float, beta2: float,
+                 eps: float, weight_decay: float, step: int, grad_scale: float = 1.0,
+                 maximize: bool = False, clip_coef: Optional[torch.Tensor] = None,
+                 found_inf: Optional[torch.Tensor] = None) -> None:
+    """Multi-tensor AdamW: all tensors of the list are updated by a handful of launches."""
+    if not masters:
+        return
+    if use_native(masters[0], grads[0]):
+        gb = grads[0].dtype == torch.bfloat16
+        mb = models is not None and models[0].dtype == torch.bfloat16
+        assert all((g.dtype == torch.bfloat16) == gb for g in grads)
+        numel = (C.c_longlong * len(masters))(*[t.numel() for t in masters])
+        code = lib().tpb_adamw_multi(
+            len(masters), _ptr_array(masters), _ptr_array(exp_avgs), _ptr_array(exp_avg_sqs),
+            _ptr_array(grads), _ptr_array(models) if models is not None else None, numel,
+            int(gb), int(mb), lr, beta1, beta2, eps, weight_decay, int(step), float(grad_scale),
+            int(maximize), ptr(clip_coef), ptr(found_inf), stream_ptr())
+        _native.check(code, "tpb_adamw_multi")
+        return
+    for i in range(len(masters)):
+        adamw_flat_(masters[i], exp_avgs[i], exp_avg_sqs[i], grads[i],
+                    None if models is None else models[i], lr=lr, beta1=beta1, beta2=beta2, eps=eps,
+                    weight_decay=weight_decay, step=step, grad_scale=grad_scale, maximize=maximize,
+                    clip_coef=clip_coef, found_inf=found_inf)
+
+
+def sumsq_(x: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """``out[0] += sum((x * scale)^2)`` without a host sync."""
+    if use_native(x, out):
+        code = lib().tpb_sumsq(x.data_ptr(), int(x.dtype == torch.bfloat16), x.numel(), scale,
+                               out.data_ptr(), stream_ptr())
+        _native.check(code, "tpb_sumsq")
+    else:
+        out[0] += (x.float() * scale).pow(2).sum()
+
+
+def clip_coef_(sumsq: torch.Tensor, max_norm: float, coef: torch.Tensor,
+               norm_out: Optional[torch.Tensor] = None) -> None:
+    if use_native(sumsq, coef):
+        code = lib().tpb_clip_coef(sumsq.data_ptr(), max_norm, coef.data_ptr(), ptr(norm_out),
+                                   stream_ptr())
+        _native.check(code, "tpb_clip_coef")
+    else:
+        nrm = sumsq.sqrt()
+        if norm_out is not None:
+            norm_out.copy_(nrm)
+        coef.copy_(torch.clamp(max_norm / (nrm + 1e-6), max=1.0))
