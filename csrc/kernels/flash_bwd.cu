@@ -1,0 +1,495 @@
+// Flash attention backward for sm_100a (tcgen05 / TMEM / TMA), GQA-native, causal or full.
+//
+// Two passes over the recomputed probabilities, each a warp-specialised kernel built from one
+// template:
+//   * dKV pass: a CTA owns 128 keys of one KV head, keeps K and V in shared memory and streams
+//     64-query tiles of Q and dO of every query head of the group; it accumulates
+//     dV += P^T dO and dK += dS^T Q in TMEM, so the GQA reduction over the query heads of a
+//     group happens inside the accumulator (no expanded K/V, no atomics).
+//   * dQ pass: a CTA owns 128 queries of one query head, keeps Q and dO resident and streams
+//     64-key tiles of K and V; dQ += dS K in TMEM (deterministic, no atomics).
+// Per streamed tile: S = X0 Y0^T and dP = X1 Y1^T (tcgen05.mma, TMEM double-buffered), the four
+// "softmax" warps turn them into P and dS = P (dP - delta) * scale, write them as bf16 into
+// 128-byte-swizzled tiles, and the accumulating MMAs read those tiles.
+//
+// Counterpart in the reference: FlashAttention-2 sm80 backward
+// (p10/src/backend/cuda/transformers/AttentionKernels.cu:2286-2543), which has no GQA path
+// (:2459-2461) and accumulates dQ with fp32 atomics.
+#include "sm100.cuh"
+#include "tpb_api.h"
+
+namespace tpb {
+
+int make_tmap_bthd(CUtensorMap* out, const void* base, int B, int T, int H, int D,
+                   long long tok_stride, long long head_stride, long long batch_stride, int rows);
+
+constexpr int kBwdThreads = 192;
+constexpr int kStat = 128;   // rows of the stationary tiles
+constexpr int kStream = 64;  // rows of the streamed tiles
+
+struct AttnBwdParams {
+  int B, Tq, Tk, Hq, Hkv;
+  int causal, kv_offset;
+  float scale, scale_log2e;
+  const float* lse;    // [B, Hq, lse_stride]
+  const float* delta;  // [B, Hq, lse_stride]
+  int lse_stride;
+  __nv_bfloat16* out0;  // dKV: dV ; dQ: unused
+  __nv_bfloat16* out1;  // dKV: dK ; dQ: dQ
+  long long out_tok, out_head, out_batch;
+  uint32_t* status;
+  unsigned long long wait_ns;
+};
+
+__device__ __forceinline__ float bwd_exp2(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int D>
+struct BwdSmem {
+  static constexpr int kChunks = D / 64;
+  static constexpr int kStatBytes = kStat * D * 2;      // one stationary tile
+  static constexpr int kStreamBytes = kStream * D * 2;  // one streamed tile
+  static constexpr int kPBytes = kStat * kStream * 2;   // P / dS tile (128 x 64 bf16)
+  static constexpr int kX0 = 0;
+  static constexpr int kX1 = kX0 + kStatBytes;
+  static constexpr int kY = kX1 + kStatBytes;  // 2 stages x (Y0, Y1)
+  static constexpr int kP = kY + 4 * kStreamBytes;
+  static constexpr int kDS = kP + kPBytes;
+  static constexpr int kBar = kDS + kPBytes;
+  static constexpr int kTotal = kBar + 256 + 1024;
+};
+
+// bf16 row of 64 values (fp32 in v[]) into a swizzled [128][64] tile.
+__device__ __forceinline__ void store_row64_sw128(uint8_t* tile, int row, const float (&v)[64]) {
+  uint8_t* prow = tile + row * 128;
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    uint4 u;
+    __nv_bfloat162 t0 = __floats2bfloat162_rn(v[g * 8 + 0], v[g * 8 + 1]);
+    __nv_bfloat162 t1 = __floats2bfloat162_rn(v[g * 8 + 2], v[g * 8 + 3]);
+    __nv_bfloat162 t2 = __floats2bfloat162_rn(v[g * 8 + 4], v[g * 8 + 5]);
+    __nv_bfloat162 t3 = __floats2bfloat162_rn(v[g * 8 + 6], v[g * 8 + 7]);
+    u.x = *reinterpret_cast<uint32_t*>(&t0);
+    u.y = *reinterpret_cast<uint32_t*>(&t1);
+    u.z = *reinterpret_cast<uint32_t*>(&t2);
+    u.w = *reinterpret_cast<uint32_t*>(&t3);
+    *reinterpret_cast<uint4*>(prow + ((g ^ (row & 7)) << 4)) = u;
+  }
+}
+
+// DKV = true : X = (K, V) stationary, Y = (Q, dO) streamed, rows are keys, columns queries.
+// DKV = false: X = (Q, dO) stationary, Y = (K, V) streamed, rows are queries, columns keys.
+template <int D, bool DKV>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant__ CUtensorMap tmX1,
+                 const __grid_constant__ CUtensorMap tmY0, const __grid_constant__ CUtensorMap tmY1,
+                 const AttnBwdParams p) {
+  using L = BwdSmem<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBar);
+  uint64_t* x_full = bars;           // 1
+  uint64_t* y_full = bars + 1;       // 2
+  uint64_t* y_empty = bars + 3;      // 2
+  uint64_t* sdp_full = bars + 5;     // 2
+  uint64_t* sdp_empty = bars + 7;    // 2 (128 arrivals)
+  uint64_t* pds_full = bars + 9;     // 1 (128 arrivals)
+  uint64_t* acc_done = bars + 10;    // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  volatile uint32_t* abort_w = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int G = p.Hq / p.Hkv;
+  const int b = blockIdx.z;
+  const int hx = blockIdx.y;  // DKV: kv head ; dQ: query head
+  const int xb = (DKV || !p.causal) ? blockIdx.x : (gridDim.x - 1 - blockIdx.x);
+  const int x0 = xb * kStat;  // first key (DKV) or first query (dQ) of this CTA
+
+  // iteration space over streamed tiles
+  int y_first = 0, y_count, n_it;
+  if (DKV) {
+    const int nqb = (p.Tq + kStream - 1) / kStream;
+    if (p.causal) {
+      int qmin = x0 - p.kv_offset;
+      y_first = qmin > 0 ? qmin / kStream : 0;
+    }
+    y_count = nqb - y_first;
+    if (y_count < 0) y_count = 0;
+    n_it = y_count * G;
+  } else {
+    int nkb = (p.Tk + kStream - 1) / kStream;
+    if (p.causal) {
+      int last_key = x0 + kStat - 1 + p.kv_offset;
+      int lim = last_key < 0 ? 0 : last_key / kStream + 1;
+      nkb = min(nkb, lim);
+    }
+    y_count = nkb;
+    n_it = nkb;
+  }
+
+  if (threadIdx.x == 0) {
+    *abort_w = 0;
+    mbar_init(x_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&y_full[i], 1);
+      mbar_init(&y_empty[i], 1);
+      mbar_init(&sdp_full[i], 1);
+      mbar_init(&sdp_empty[i], 128);
+    }
+    mbar_init(pds_full, 128);
+    mbar_init(acc_done, 1);
+    fence_barrier_init();
+    prefetch_tmap(&tmX0);
+    prefetch_tmap(&tmX1);
+    prefetch_tmap(&tmY0);
+    prefetch_tmap(&tmY1);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_acc0 = tmem_base + 256;
+  const uint32_t tmem_acc1 = tmem_base + 384;
+  WaitCtx wc{abort_w, p.status, p.wait_ns};
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0 && n_it > 0) {
+      mbar_arrive_expect_tx(x_full, 2 * L::kStatBytes);
+      // DKV: X tiles are K/V of kv head hx ; dQ: X tiles are Q/dO of query head hx
+#pragma unroll
+      for (int c = 0; c < L::kChunks; ++c) {
+        tma_load_4d(smem + L::kX0 + c * (kStat * 128), &tmX0, x_full, c * 64, hx, x0, b);
+        tma_load_4d(smem + L::kX1 + c * (kStat * 128), &tmX1, x_full, c * 64, hx, x0, b);
+      }
+      for (int it = 0; it < n_it; ++it) {
+        const int s = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        if (!mbar_wait(&y_empty[s], ph ^ 1, wc, 1)) break;
+        int hy, yb;
+        if (DKV) { hy = hx * G + it / y_count; yb = y_first + it % y_count; }
+        else { hy = hx / G; yb = it; }
+        uint8_t* y0 = smem + L::kY + s * 2 * L::kStreamBytes;
+        uint8_t* y1 = y0 + L::kStreamBytes;
+        mbar_arrive_expect_tx(&y_full[s], 2 * L::kStreamBytes);
+#pragma unroll
+        for (int c = 0; c < L::kChunks; ++c) {
+          tma_load_4d(y0 + c * (kStream * 128), &tmY0, &y_full[s], c * 64, hy, yb * kStream, b);
+          tma_load_4d(y1 + c * (kStream * 128), &tmY1, &y_full[s], c * 64, hy, yb * kStream, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0 && n_it > 0) {
+      constexpr uint32_t idesc_s = make_idesc_f16(kStat, kStream, 1, 0, 0);
+      constexpr uint32_t idesc_acc = make_idesc_f16(kStat, D, 1, 0, 1);
+      const uint32_t x0_s = smem_u32(smem + L::kX0);
+      const uint32_t x1_s = smem_u32(smem + L::kX1);
+      const uint32_t p_s = smem_u32(smem + L::kP);
+      const uint32_t ds_s = smem_u32(smem + L::kDS);
+      auto issue_sdp = [&](int it) -> bool {
+        const int s = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        if (!mbar_wait(&y_full[s], ph, wc, 2)) return false;
+        if (!mbar_wait(&sdp_empty[s], ph ^ 1, wc, 3)) return false;
+        tc_fence_after_sync();
+        const uint32_t y0_s = smem_u32(smem + L::kY + s * 2 * L::kStreamBytes);
+        const uint32_t y1_s = y0_s + L::kStreamBytes;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t xo = (kk / 4) * (kStat * 128) + (kk % 4) * 32;
+          const uint32_t yo = (kk / 4) * (kStream * 128) + (kk % 4) * 32;
+          umma_f16_ss(tmem_base + s * 128, make_smem_desc_sw128(x0_s + xo, 16, 1024),
+                      make_smem_desc_sw128(y0_s + yo, 16, 1024), idesc_s, kk != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t xo = (kk / 4) * (kStat * 128) + (kk % 4) * 32;
+          const uint32_t yo = (kk / 4) * (kStream * 128) + (kk % 4) * 32;
+          umma_f16_ss(tmem_base + s * 128 + 64, make_smem_desc_sw128(x1_s + xo, 16, 1024),
+                      make_smem_desc_sw128(y1_s + yo, 16, 1024), idesc_s, kk != 0);
+        }
+        umma_commit(&sdp_full[s]);
+        return true;
+      };
+      bool ok = mbar_wait(x_full, 0, wc, 4);
+      if (ok) ok = issue_sdp(0);
+      for (int it = 0; it < n_it && ok; ++it) {
+        if (it + 1 < n_it) {
+          if (!issue_sdp(it + 1)) break;
+        }
+        const int s = it & 1;
+        if (!mbar_wait(pds_full, it & 1, wc, 5)) break;
+        tc_fence_after_sync();
+        const uint32_t y0_s = smem_u32(smem + L::kY + s * 2 * L::kStreamBytes);
+        const uint32_t y1_s = y0_s + L::kStreamBytes;
+#pragma unroll
+        for (int kk = 0; kk < kStream / 16; ++kk) {
+          // acc1 += dS * Y0  (dK += dS^T Q  or  dQ += dS K)
+          umma_f16_ss(tmem_acc1, make_smem_desc_sw128(ds_s + kk * 32, 16, 1024),
+                      make_smem_desc_sw128(y0_s + kk * 2048, kStream * 128, 1024), idesc_acc,
+                      (it | kk) != 0);
+          if (DKV) {
+            // acc0 += P^T * dO
+            umma_f16_ss(tmem_acc0, make_smem_desc_sw128(p_s + kk * 32, 16, 1024),
+                        make_smem_desc_sw128(y1_s + kk * 2048, kStream * 128, 1024), idesc_acc,
+                        (it | kk) != 0);
+          }
+        }
+        umma_commit(acc_done);
+        umma_commit(&y_empty[s]);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- P / dS warps
+    const int qd = warp & 3;
+    const int row = qd * 32 + lane;
+    const int xi = x0 + row;  // key index (DKV) or query index (dQ)
+    const uint32_t t_lane = ((uint32_t)(qd * 32) << 16);
+    const float log2e = 1.4426950408889634f;
+    float lse_row = 0.f, delta_row = 0.f;
+    if (!DKV) {
+      if (xi < p.Tq) {
+        long long o = ((long long)b * p.Hq + hx) * p.lse_stride + xi;
+        lse_row = p.lse[o] * log2e;
+        delta_row = p.delta[o];
+      }
+    }
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      const int s = it & 1;
+      const uint32_t ph = (it >> 1) & 1;
+      int hy, yb;
+      if (DKV) { hy = hx * G + it / y_count; yb = y_first + it % y_count; }
+      else { hy = hx; yb = it; }
+      const int y0i = yb * kStream;  // first query (DKV) or key (dQ) of the streamed tile
+      if (!mbar_wait_warp(&sdp_full[s], ph, wc, 6)) { ok = false; break; }
+      tc_fence_after_sync();
+      uint32_t sr[2][32], dr[2][32];
+      tmem_ld_32x32b_x32(tmem_base + t_lane + s * 128, sr[0]);
+      tmem_ld_32x32b_x32(tmem_base + t_lane + s * 128 + 32, sr[1]);
+      tmem_ld_32x32b_x32(tmem_base + t_lane + s * 128 + 64, dr[0]);
+      tmem_ld_32x32b_x32(tmem_base + t_lane + s * 128 + 96, dr[1]);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&sdp_empty[s]);
+
+      float pv[64], dsv[64];
+      const float* lse_col = nullptr;
+      const float* delta_col = nullptr;
+      if (DKV) {
+        long long o = ((long long)b * p.Hq + hy) * p.lse_stride + y0i;
+        lse_col = p.lse + o;
+        delta_col = p.delta + o;
+      }
+#pragma unroll
+      for (int c = 0; c < 64; c += 4) {
+        float l4[4], d4[4];
+        if (DKV) {
+          float4 a = *reinterpret_cast<const float4*>(lse_col + c);
+          float4 d = *reinterpret_cast<const float4*>(delta_col + c);
+          l4[0] = a.x * log2e; l4[1] = a.y * log2e; l4[2] = a.z * log2e; l4[3] = a.w * log2e;
+          d4[0] = d.x; d4[1] = d.y; d4[2] = d.z; d4[3] = d.w;
+        } else {
+          l4[0] = l4[1] = l4[2] = l4[3] = lse_row;
+          d4[0] = d4[1] = d4[2] = d4[3] = delta_row;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int col = c + i;
+          const int yi = y0i + col;
+          const int key = DKV ? xi : yi;
+          const int qry = DKV ? yi : xi;
+          const bool valid = (key < p.Tk) && (qry < p.Tq) && (!p.causal || key <= qry + p.kv_offset);
+          float sv = __uint_as_float(sr[col >> 5][col & 31]);
+          float dp = __uint_as_float(dr[col >> 5][col & 31]);
+          float pr = valid ? bwd_exp2(sv * p.scale_log2e - l4[i]) : 0.f;
+          pv[col] = pr;
+          dsv[col] = valid ? pr * (dp - d4[i]) * p.scale : 0.f;
+        }
+      }
+      if (it > 0) {
+        if (!mbar_wait_warp(acc_done, (it - 1) & 1, wc, 7)) { ok = false; break; }
+      }
+      if (DKV) store_row64_sw128(smem + L::kP, row, pv);
+      store_row64_sw128(smem + L::kDS, row, dsv);
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(pds_full);
+    }
+    if (ok && n_it > 0) ok = mbar_wait_warp(acc_done, (n_it - 1) & 1, wc, 8);
+    if (ok) {
+      tc_fence_after_sync();
+      const int t_lim = DKV ? p.Tk : p.Tq;
+      const long long obase = (long long)b * p.out_batch + (long long)xi * p.out_tok +
+                              (long long)hx * p.out_head;
+#pragma unroll 1
+      for (int a = DKV ? 0 : 1; a < 2; ++a) {
+        __nv_bfloat16* orow = (a == 0 ? p.out0 : p.out1) + obase;
+        const uint32_t t_acc = (a == 0 ? tmem_acc0 : tmem_acc1) + t_lane;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          if (n_it > 0) {
+            tmem_ld_32x32b_x32(t_acc + c * 32, o);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = 0;
+          }
+          if (xi < t_lim) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 v;
+              __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(o[g * 8 + 0]),
+                                                        __uint_as_float(o[g * 8 + 1]));
+              __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(o[g * 8 + 2]),
+                                                        __uint_as_float(o[g * 8 + 3]));
+              __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(o[g * 8 + 4]),
+                                                        __uint_as_float(o[g * 8 + 5]));
+              __nv_bfloat162 t3 = __floats2bfloat162_rn(__uint_as_float(o[g * 8 + 6]),
+                                                        __uint_as_float(o[g * 8 + 7]));
+              v.x = *reinterpret_cast<uint32_t*>(&t0);
+              v.y = *reinterpret_cast<uint32_t*>(&t1);
+              v.z = *reinterpret_cast<uint32_t*>(&t2);
+              v.w = *reinterpret_cast<uint32_t*>(&t3);
+              *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = v;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_w) {
+    unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// delta[b, h, t] = sum_d O[b, t, h, d] * dO[b, t, h, d]; one warp per (b, t, h).
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o,
+                                  const __nv_bfloat16* __restrict__ dout, float* __restrict__ delta,
+                                  int B, int T, int H, int D, long long o_tok, long long o_head,
+                                  long long o_batch, long long d_tok, long long d_head,
+                                  long long d_batch, int lse_stride) {
+  long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  long long total = (long long)B * T * H;
+  if (w >= total) return;
+  int h = w % H;
+  long long bt = w / H;
+  int t = bt % T;
+  int b = bt / T;
+  const __nv_bfloat16* op = o + b * o_batch + t * o_tok + h * o_head;
+  const __nv_bfloat16* dp = dout + b * d_batch + t * d_tok + h * d_head;
+  float s = 0.f;
+  for (int i = lane * 2; i < D; i += 64) {
+    float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(op + i));
+    float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dp + i));
+    s += a.x * c.x + a.y * c.y;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (lane == 0) delta[((long long)b * H + h) * lse_stride + t] = s;
+}
+
+template <int D, bool DKV>
+static int launch_bwd(const CUtensorMap& x0, const CUtensorMap& x1, const CUtensorMap& y0,
+                      const CUtensorMap& y1, const AttnBwdParams& p, dim3 grid,
+                      cudaStream_t stream) {
+  using L = BwdSmem<D>;
+  auto kern = flash_bwd_kernel<D, DKV>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  kern<<<grid, kBwdThreads, L::kTotal, stream>>>(x0, x1, y0, y1, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace tpb
+
+using namespace tpb;
+
+// lse / delta: [B, Hq, lse_stride] fp32 with lse_stride a multiple of 64 and >= Tq rounded up
+// to 64 (the dKV pass reads whole 64-query vectors). delta is scratch written here.
+extern "C" int tpb_flash_bwd(const void* dout, const void* q, const void* k, const void* v,
+                             const void* o, const float* lse, float* delta, void* dq, void* dk,
+                             void* dv, int B, int Tq, int Tk, int Hq, int Hkv, int D,
+                             long long q_tok, long long q_head, long long q_batch, long long k_tok,
+                             long long k_head, long long k_batch, long long v_tok,
+                             long long v_head, long long v_batch, long long o_tok,
+                             long long o_head, long long o_batch, long long do_tok,
+                             long long do_head, long long do_batch, int lse_stride, int causal,
+                             float scale, uint32_t* status, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (B <= 0 || Tq <= 0 || Hq <= 0) return 0;
+  if ((D != 64 && D != 128) || Hkv <= 0 || Hq % Hkv || Tk <= 0) return -2;
+  if (lse_stride % 64 || lse_stride < (Tq + 63) / 64 * 64) return -2;
+  if ((q_tok | q_head | q_batch | k_tok | k_head | k_batch | v_tok | v_head | v_batch | do_tok |
+       do_head | do_batch) % 8)
+    return -2;
+  // delta
+  {
+    long long warps = (long long)B * Tq * Hq;
+    long long threads = warps * 32;
+    attn_delta_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(
+        (const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, B, Tq, Hq, D, o_tok, o_head,
+        o_batch, do_tok, do_head, do_batch, lse_stride);
+  }
+  AttnBwdParams p;
+  p.B = B; p.Tq = Tq; p.Tk = Tk; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal;
+  p.kv_offset = Tk - Tq; p.scale = scale; p.scale_log2e = scale * 1.4426950408889634f;
+  p.lse = lse; p.delta = delta; p.lse_stride = lse_stride; p.status = status;
+  p.wait_ns = kDefaultWaitNs;
+  int r;
+  // ---- dK / dV: outputs are contiguous [B, Tk, Hkv, D]
+  {
+    CUtensorMap tk, tv, tq, tdo;
+    if ((r = make_tmap_bthd(&tk, k, B, Tk, Hkv, D, k_tok, k_head, k_batch, kStat))) return r;
+    if ((r = make_tmap_bthd(&tv, v, B, Tk, Hkv, D, v_tok, v_head, v_batch, kStat))) return r;
+    if ((r = make_tmap_bthd(&tq, q, B, Tq, Hq, D, q_tok, q_head, q_batch, kStream))) return r;
+    if ((r = make_tmap_bthd(&tdo, dout, B, Tq, Hq, D, do_tok, do_head, do_batch, kStream))) return r;
+    p.out0 = (__nv_bfloat16*)dv; p.out1 = (__nv_bfloat16*)dk;
+    p.out_tok = (long long)Hkv * D; p.out_head = D; p.out_batch = (long long)Tk * Hkv * D;
+    dim3 grid((Tk + kStat - 1) / kStat, Hkv, B);
+    r = (D == 128) ? launch_bwd<128, true>(tk, tv, tq, tdo, p, grid, stream)
+                   : launch_bwd<64, true>(tk, tv, tq, tdo, p, grid, stream);
+    if (r) return r;
+  }
+  // ---- dQ: output contiguous [B, Tq, Hq, D]
+  {
+    CUtensorMap tq, tdo, tk, tv;
+    if ((r = make_tmap_bthd(&tq, q, B, Tq, Hq, D, q_tok, q_head, q_batch, kStat))) return r;
+    if ((r = make_tmap_bthd(&tdo, dout, B, Tq, Hq, D, do_tok, do_head, do_batch, kStat))) return r;
+    if ((r = make_tmap_bthd(&tk, k, B, Tk, Hkv, D, k_tok, k_head, k_batch, kStream))) return r;
+    if ((r = make_tmap_bthd(&tv, v, B, Tk, Hkv, D, v_tok, v_head, v_batch, kStream))) return r;
+    p.out0 = nullptr; p.out1 = (__nv_bfloat16*)dq;
+    p.out_tok = (long long)Hq * D; p.out_head = D; p.out_batch = (long long)Tq * Hq * D;
+    dim3 grid((Tq + kStat - 1) / kStat, Hq, B);
+    r = (D == 128) ? launch_bwd<128, false>(tq, tdo, tk, tv, p, grid, stream)
+                   : launch_bwd<64, false>(tq, tdo, tk, tv, p, grid, stream);
+    if (r) return r;
+  }
+  return 0;
+}

@@ -1,0 +1,439 @@
+// Flash attention forward for sm_100a: GQA-native, causal or full, head_dim 64 / 128.
+//
+// One CTA handles 128 queries of one query head. Warp 0 streams K/V tiles with TMA (two
+// stages each), warp 1 issues tcgen05.mma: S = Q K^T into a double-buffered TMEM accumulator
+// and O += P V into a second TMEM region; four softmax warps own one query row per thread:
+// they read S from TMEM, keep the running max / sum in the exp2 domain, write P (bf16) into a
+// 128-byte-swizzled shared tile for the second MMA, rescale O in TMEM only when a row max
+// moved, and finally write O / LSE. K and V of a KV head are shared by the query heads of
+// its group through L2, so GQA costs no expanded K/V traffic.
+//
+// Counterpart in the reference: vendored FlashAttention-2 sm80 leaves
+// (p10/src/backend/cuda/transformers/flash/flash_fwd_kernel.h, AttentionKernels.cu:1782-1969),
+// which expand K/V to the query head count for GQA training (nn/functional.py:3571-3586).
+#include "sm100.cuh"
+#include "tpb_api.h"
+
+#include <mutex>
+
+namespace tpb {
+
+constexpr int kAttnThreads = 192;
+constexpr int kBlockQ = 128;
+constexpr int kBlockKV = 128;
+constexpr float kNegBig = -1.0e30f;
+
+struct AttnFwdParams {
+  int B, Tq, Tk, Hq, Hkv;
+  int causal;
+  int kv_offset;  // causal: query i attends keys <= i + kv_offset (Tk - Tq)
+  float scale_log2e;
+  __nv_bfloat16* O;
+  long long o_tok_stride, o_head_stride, o_batch_stride;
+  float* lse;  // [B, Hq, lse_stride]
+  int lse_stride;
+  uint32_t* status;
+  unsigned long long wait_ns;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int D>
+struct AttnSmem {
+  static constexpr int kChunks = D / 64;
+  static constexpr int kQBytes = kBlockQ * D * 2;
+  static constexpr int kKBytes = kBlockKV * D * 2;
+  static constexpr int kPBytes = kBlockQ * kBlockKV * 2;
+  static constexpr int kQOff = 0;
+  static constexpr int kKOff = kQOff + kQBytes;
+  static constexpr int kVOff = kKOff + 2 * kKBytes;
+  static constexpr int kPOff = kVOff + 2 * kKBytes;
+  static constexpr int kBarOff = kPOff + kPBytes;
+  static constexpr int kTotal = kBarOff + 256 + 1024;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const AttnFwdParams p) {
+  using L = AttnSmem<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* q_full = bars;          // 1
+  uint64_t* k_full = bars + 1;      // 2
+  uint64_t* k_empty = bars + 3;     // 2
+  uint64_t* v_full = bars + 5;      // 2
+  uint64_t* v_empty = bars + 7;     // 2
+  uint64_t* s_full = bars + 9;      // 2
+  uint64_t* s_empty = bars + 11;    // 2 (128 arrivals)
+  uint64_t* p_full = bars + 13;     // 1 (128 arrivals)
+  uint64_t* pv_done = bars + 14;    // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  volatile uint32_t* abort_w = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int qb = p.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;  // heavy tiles first
+  const int h = blockIdx.y;
+  const int b = blockIdx.z;
+  const int hk = h / (p.Hq / p.Hkv);
+  const int q0 = qb * kBlockQ;
+  int nkv = (p.Tk + kBlockKV - 1) / kBlockKV;
+  if (p.causal) {
+    int last_key = q0 + kBlockQ - 1 + p.kv_offset;
+    int lim = last_key / kBlockKV + 1;
+    if (last_key < 0) lim = 0;
+    nkv = min(nkv, lim);
+  }
+
+  if (threadIdx.x == 0) {
+    *abort_w = 0;
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], 128);
+    }
+    mbar_init(p_full, 128);
+    mbar_init(pv_done, 1);
+    fence_barrier_init();
+    prefetch_tmap(&tmQ);
+    prefetch_tmap(&tmK);
+    prefetch_tmap(&tmV);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_o = tmem_base + 256;
+  WaitCtx wc{abort_w, p.status, p.wait_ns};
+
+  if (warp == 0) {
+    if (lane == 0 && nkv > 0) {
+      mbar_arrive_expect_tx(q_full, L::kQBytes);
+#pragma unroll
+      for (int c = 0; c < L::kChunks; ++c)
+        tma_load_4d(smem + L::kQOff + c * (kBlockQ * 128), &tmQ, q_full, c * 64, h, q0, b);
+      for (int j = 0; j < nkv; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&k_empty[s], ph ^ 1, wc, 1)) break;
+        mbar_arrive_expect_tx(&k_full[s], L::kKBytes);
+#pragma unroll
+        for (int c = 0; c < L::kChunks; ++c)
+          tma_load_4d(smem + L::kKOff + s * L::kKBytes + c * (kBlockKV * 128), &tmK, &k_full[s],
+                      c * 64, hk, j * kBlockKV, b);
+        if (!mbar_wait(&v_empty[s], ph ^ 1, wc, 2)) break;
+        mbar_arrive_expect_tx(&v_full[s], L::kKBytes);
+#pragma unroll
+        for (int c = 0; c < L::kChunks; ++c)
+          tma_load_4d(smem + L::kVOff + s * L::kKBytes + c * (kBlockKV * 128), &tmV, &v_full[s],
+                      c * 64, hk, j * kBlockKV, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && nkv > 0) {
+      constexpr uint32_t idesc_s = make_idesc_f16(kBlockQ, kBlockKV, 1, 0, 0);
+      constexpr uint32_t idesc_o = make_idesc_f16(kBlockQ, D, 1, 0, 1);
+      const uint32_t q_s = smem_u32(smem + L::kQOff);
+      const uint32_t p_s = smem_u32(smem + L::kPOff);
+      auto issue_s = [&](int j) -> bool {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&k_full[s], ph, wc, 3)) return false;
+        if (!mbar_wait(&s_empty[s], ph ^ 1, wc, 4)) return false;
+        tc_fence_after_sync();
+        const uint32_t k_s = smem_u32(smem + L::kKOff + s * L::kKBytes);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * (kBlockQ * 128) + (kk % 4) * 32;
+          umma_f16_ss(tmem_base + s * 128, make_smem_desc_sw128(q_s + off, 16, 1024),
+                      make_smem_desc_sw128(k_s + off, 16, 1024), idesc_s, kk != 0);
+        }
+        umma_commit(&s_full[s]);
+        umma_commit(&k_empty[s]);
+        return true;
+      };
+      bool ok = mbar_wait(q_full, 0, wc, 5);
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < nkv && ok; ++j) {
+        if (j + 1 < nkv) {
+          if (!issue_s(j + 1)) break;
+        }
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(p_full, j & 1, wc, 6)) break;
+        if (!mbar_wait(&v_full[s], ph, wc, 7)) break;
+        tc_fence_after_sync();
+        const uint32_t v_s = smem_u32(smem + L::kVOff + s * L::kKBytes);
+#pragma unroll
+        for (int kk = 0; kk < kBlockKV / 16; ++kk) {
+          const uint32_t poff = (kk / 4) * (kBlockQ * 128) + (kk % 4) * 32;
+          umma_f16_ss(tmem_o, make_smem_desc_sw128(p_s + poff, 16, 1024),
+                      make_smem_desc_sw128(v_s + kk * 2048, kBlockKV * 128, 1024), idesc_o,
+                      (j | kk) != 0);
+        }
+        umma_commit(pv_done);
+        umma_commit(&v_empty[s]);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax / epilogue
+    const int qd = warp & 3;
+    const int row = qd * 32 + lane;  // row inside the tile == TMEM lane
+    const int qi = q0 + row;
+    const uint32_t t_lane = ((uint32_t)(qd * 32) << 16);
+    float m = kNegBig, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nkv; ++j) {
+      const int s = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      if (!mbar_wait_warp(&s_full[s], ph, wc, 8)) { ok = false; break; }
+      tc_fence_after_sync();
+      uint32_t sr[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(tmem_base + t_lane + s * 128 + c * 32, sr[c]);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&s_empty[s]);
+
+      const int k0 = j * kBlockKV;
+      const bool need_mask = (p.causal && (k0 + kBlockKV - 1 > q0 + p.kv_offset)) ||
+                             (k0 + kBlockKV > p.Tk);
+      const int lim = p.causal ? min(qi + p.kv_offset, p.Tk - 1) : (p.Tk - 1);  // last valid key
+      float mx = m;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float v = __uint_as_float(sr[c][i]) * p.scale_log2e;
+          if (need_mask && (k0 + c * 32 + i > lim)) v = kNegBig;
+          sr[c][i] = __float_as_uint(v);
+          mx = fmaxf(mx, v);
+        }
+      const float alpha = fast_exp2(m - mx);
+      m = mx;
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float e = fast_exp2(__uint_as_float(sr[c][i]) - mx);
+          sum += e;
+          sr[c][i] = __float_as_uint(e);
+        }
+      l = l * alpha + sum;
+
+      if (j > 0) {
+        if (!mbar_wait_warp(pv_done, (j - 1) & 1, wc, 9)) { ok = false; break; }
+        tc_fence_after_sync();
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32b_x32(tmem_o + t_lane + c * 32, o);
+            tmem_ld_wait();
+            uint32_t lo[16], hi[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              lo[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              hi[i] = __float_as_uint(__uint_as_float(o[16 + i]) * alpha);
+            }
+            tmem_st_32x32b_x16(tmem_o + t_lane + c * 32, lo);
+            tmem_st_32x32b_x16(tmem_o + t_lane + c * 32 + 16, hi);
+          }
+          tmem_st_wait();
+        }
+      }
+      // P (bf16) into the swizzled tile: chunk = key / 64, 16-byte slot = (key % 64) / 8
+      uint8_t* prow = smem + L::kPOff + row * 128;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 v;
+          __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(sr[c][g * 8 + 0]),
+                                                    __uint_as_float(sr[c][g * 8 + 1]));
+          __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(sr[c][g * 8 + 2]),
+                                                    __uint_as_float(sr[c][g * 8 + 3]));
+          __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(sr[c][g * 8 + 4]),
+                                                    __uint_as_float(sr[c][g * 8 + 5]));
+          __nv_bfloat162 t3 = __floats2bfloat162_rn(__uint_as_float(sr[c][g * 8 + 6]),
+                                                    __uint_as_float(sr[c][g * 8 + 7]));
+          v.x = *reinterpret_cast<uint32_t*>(&t0);
+          v.y = *reinterpret_cast<uint32_t*>(&t1);
+          v.z = *reinterpret_cast<uint32_t*>(&t2);
+          v.w = *reinterpret_cast<uint32_t*>(&t3);
+          const int key = c * 32 + g * 8;
+          const int chunk = key >> 6;
+          const int slot = (key & 63) >> 3;
+          *reinterpret_cast<uint4*>(prow + chunk * (kBlockQ * 128) + ((slot ^ (row & 7)) << 4)) = v;
+        }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(p_full);
+    }
+    if (ok && nkv > 0) ok = mbar_wait_warp(pv_done, (nkv - 1) & 1, wc, 10);
+    if (ok) {
+      tc_fence_after_sync();
+      const float inv = (nkv > 0 && l > 0.f) ? 1.f / l : 0.f;
+      __nv_bfloat16* orow = p.O + (long long)b * p.o_batch_stride + (long long)qi * p.o_tok_stride +
+                            (long long)h * p.o_head_stride;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        if (nkv > 0) {
+          tmem_ld_32x32b_x32(tmem_o + t_lane + c * 32, o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0;
+        }
+        if (qi < p.Tq) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 v;
+            __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(o[g * 8 + 0]) * inv,
+                                                      __uint_as_float(o[g * 8 + 1]) * inv);
+            __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(o[g * 8 + 2]) * inv,
+                                                      __uint_as_float(o[g * 8 + 3]) * inv);
+            __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(o[g * 8 + 4]) * inv,
+                                                      __uint_as_float(o[g * 8 + 5]) * inv);
+            __nv_bfloat162 t3 = __floats2bfloat162_rn(__uint_as_float(o[g * 8 + 6]) * inv,
+                                                      __uint_as_float(o[g * 8 + 7]) * inv);
+            v.x = *reinterpret_cast<uint32_t*>(&t0);
+            v.y = *reinterpret_cast<uint32_t*>(&t1);
+            v.z = *reinterpret_cast<uint32_t*>(&t2);
+            v.w = *reinterpret_cast<uint32_t*>(&t3);
+            *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = v;
+          }
+        }
+      }
+      if (qi < p.Tq && p.lse) {
+        float lse = (nkv > 0 && l > 0.f) ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+        p.lse[((long long)b * p.Hq + h) * p.lse_stride + qi] = lse;
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_w) {
+    unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn2)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// General bf16 tensor map: dims/strides innermost first (strides in elements; strides[0] must
+// be 1 and is ignored), 128-byte swizzle or none.
+int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                   const uint64_t* strides_elems, const uint32_t* box, int swizzle128) {
+  static EncodeTiledFn2 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn2>(sym);
+  });
+  if (!fn) return -1;
+  cuuint64_t d[5], st[4];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; ++i) {
+    d[i] = dims[i];
+    bx[i] = box[i];
+    es[i] = 1;
+    if (i > 0) st[i - 1] = strides_elems[i] * 2;
+  }
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), d, st, bx,
+                  es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+// Tensor map over a [B, T, H, D] bf16 tensor given by strides; box = 64 (D) x 1 x rows x 1.
+int make_tmap_bthd(CUtensorMap* out, const void* base, int B, int T, int H, int D,
+                   long long tok_stride, long long head_stride, long long batch_stride, int rows) {
+  uint64_t dims[4] = {(uint64_t)D, (uint64_t)H, (uint64_t)T, (uint64_t)B};
+  uint64_t strides[4] = {1, (uint64_t)head_stride, (uint64_t)tok_stride, (uint64_t)batch_stride};
+  uint32_t box[4] = {64, 1, (uint32_t)rows, 1};
+  return make_tmap_bf16(out, base, 4, dims, strides, box, 1);
+}
+
+template <int D>
+static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                      const AttnFwdParams& p, cudaStream_t stream) {
+  using L = AttnSmem<D>;
+  auto kern = flash_fwd_kernel<D>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid((p.Tq + kBlockQ - 1) / kBlockQ, p.Hq, p.B);
+  kern<<<grid, kAttnThreads, L::kTotal, stream>>>(tq, tk, tv, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace tpb
+
+using namespace tpb;
+
+// q: [B, Tq, Hq, D], k/v: [B, Tk, Hkv, D] given by (token, head, batch) strides in elements;
+// o likewise; lse: [B, Hq, lse_stride] fp32 (lse_stride >= Tq). causal aligns the last query with the last key.
+extern "C" int tpb_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
+                             int B, int Tq, int Tk, int Hq, int Hkv, int D, long long q_tok,
+                             long long q_head, long long q_batch, long long k_tok,
+                             long long k_head, long long k_batch, long long v_tok,
+                             long long v_head, long long v_batch, long long o_tok,
+                             long long o_head, long long o_batch, int lse_stride, int causal,
+                             float scale, uint32_t* status, void* stream) {
+  if (B <= 0 || Tq <= 0 || Hq <= 0) return 0;
+  if ((D != 64 && D != 128) || Hkv <= 0 || Hq % Hkv || Tk <= 0) return -2;
+  if ((q_tok | q_head | q_batch | k_tok | k_head | k_batch | v_tok | v_head | v_batch | o_tok |
+       o_head | o_batch) % 8)
+    return -2;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
+       reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(o)) & 15)
+    return -2;
+  CUtensorMap tq, tk, tv;
+  int r;
+  if ((r = make_tmap_bthd(&tq, q, B, Tq, Hq, D, q_tok, q_head, q_batch, kBlockQ))) return r;
+  if ((r = make_tmap_bthd(&tk, k, B, Tk, Hkv, D, k_tok, k_head, k_batch, kBlockKV))) return r;
+  if ((r = make_tmap_bthd(&tv, v, B, Tk, Hkv, D, v_tok, v_head, v_batch, kBlockKV))) return r;
+  AttnFwdParams p;
+  p.B = B; p.Tq = Tq; p.Tk = Tk; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal;
+  p.kv_offset = Tk - Tq;
+  p.scale_log2e = scale * 1.4426950408889634f;
+  p.O = (__nv_bfloat16*)o; p.o_tok_stride = o_tok; p.o_head_stride = o_head;
+  p.o_batch_stride = o_batch; p.lse = lse; p.lse_stride = lse_stride > 0 ? lse_stride : Tq; p.status = status; p.wait_ns = kDefaultWaitNs;
+  if (D == 128) return launch_fwd<128>(tq, tk, tv, p, (cudaStream_t)stream);
+  return launch_fwd<64>(tq, tk, tv, p, (cudaStream_t)stream);
+}

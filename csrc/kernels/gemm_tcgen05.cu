@@ -194,7 +194,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tile_coords(tile, tiles_m, tiles_n, tm, tn);
       int as = lt & 1;
       uint32_t aph = (lt >> 1) & 1;
-      if (!mbar_wait(&tfull[as], aph, wc, 4)) break;
+      if (!mbar_wait_warp(&tfull[as], aph, wc, 4)) break;
       tc_fence_after_sync();
       const int row = tm * kBlockM + q * 32 + lane;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + as * BLOCK_N;

@@ -106,6 +106,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   }
 }
 
+// Warp-uniform form: every lane waits, and the warp proceeds only if all lanes succeeded, so
+// that .sync.aligned instructions after the wait are never executed by a partial warp.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, const WaitCtx& w,
+                                               uint32_t where) {
+  bool ok = mbar_wait(bar, parity, w, where);
+  return __all_sync(0xffffffffu, ok);
+}
+
 // Bounded wait on a 32-bit flag in global (possibly peer) memory reaching >= want.
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   uint32_t v;

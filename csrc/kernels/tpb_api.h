@@ -63,6 +63,21 @@ int tpb_cross_entropy_bwd(const void* logits, const long long* target, const flo
                           const float* g_rows, long long rows, int V, long long stride,
                           long long ignore_index, void* stream);
 
+int tpb_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Tq,
+                  int Tk, int Hq, int Hkv, int D, long long q_tok, long long q_head,
+                  long long q_batch, long long k_tok, long long k_head, long long k_batch,
+                  long long v_tok, long long v_head, long long v_batch, long long o_tok,
+                  long long o_head, long long o_batch, int lse_stride, int causal, float scale,
+                  uint32_t* status, void* stream);
+int tpb_flash_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o,
+                  const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int Tq,
+                  int Tk, int Hq, int Hkv, int D, long long q_tok, long long q_head,
+                  long long q_batch, long long k_tok, long long k_head, long long k_batch,
+                  long long v_tok, long long v_head, long long v_batch, long long o_tok,
+                  long long o_head, long long o_batch, long long do_tok, long long do_head,
+                  long long do_batch, int lse_stride, int causal, float scale, uint32_t* status,
+                  void* stream);
+
 int tpb_adamw_flat(float* master, float* m, float* v, const void* grad, int grad_bf16, void* model,
                    int model_bf16, long long n, float lr, float beta1, float beta2, float eps,
                    float wd, int step, float grad_scale, int maximize, const float* clip_coef,

@@ -76,8 +76,11 @@ def build_kernels(verbose: bool = False, ptxas_info: bool = False) -> Path:
                 log.append(out)
     lib = LIBDIR / "libtpb200.so"
     if jobs or _newer(objs, lib):
-        _run([_nvcc(), "-shared", "-o", lib, *objs, "-gencode", "arch=compute_100a,code=sm_100a",
-              "-Xcompiler", "-fPIC"], verbose)
+        # The CUDA runtime is linked dynamically so that the library shares the runtime state
+        # (per-thread current device, primary context, error state) of the process that loads
+        # it - torch's autograd threads select their device through that same runtime.
+        _run([_nvcc(), "-shared", "-cudart", "shared", "-o", lib, *objs, "-gencode",
+              "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC"], verbose)
     if ptxas_info:
         print("\n".join(log))
     return lib

@@ -37,6 +37,8 @@ _KERNEL_SIGS = {
     "tpb_gelu_bwd": [P, P, P, LL, I, P],
     "tpb_cross_entropy": [P, P, P, P, P, LL, I, LL, LL, F, P],
     "tpb_cross_entropy_bwd": [P, P, P, P, P, P, P, LL, I, LL, LL, P],
+    "tpb_flash_fwd": [P, P, P, P, P, I, I, I, I, I, I] + [LL] * 12 + [I, I, F, P, P],
+    "tpb_flash_bwd": [P] * 10 + [I, I, I, I, I, I] + [LL] * 15 + [I, I, F, P, P],
     "tpb_adamw_flat": [P, P, P, P, I, P, I, LL, F, F, F, F, F, I, F, I, P, P, P],
     "tpb_adamw_multi": [I, P, P, P, P, P, P, I, I, F, F, F, F, F, I, F, I, P, P, P],
     "tpb_sumsq": [P, I, LL, F, P, P],

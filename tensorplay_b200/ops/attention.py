@@ -1,0 +1,114 @@
+"""Flash attention (GQA-native, causal / full) on the tcgen05 kernels.
+
+Layout is token-major ``[B, T, H, D]`` with arbitrary token / head / batch strides, so q, k
+and v may be slices of one fused QKV projection buffer.
+
+Reference counterparts: FlashAttention-2 sm80 forward/backward leaves
+(p10/src/backend/cuda/transformers/AttentionKernels.cu:1782-1969, :2286-2543) behind
+``scaled_dot_product_attention`` (tensorplay/nn/functional.py:3589-3615); the reference expands
+K/V to the query head count for GQA training (:3571-3586) while these kernels take grouped
+heads natively and reduce dK/dV over the group inside the kernel.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from .. import _native
+from ._common import lib, status_word, stream_ptr, use_native
+
+
+def _strides_ok(t: torch.Tensor) -> bool:
+    return t.stride(3) == 1 and all(s % 8 == 0 for s in t.stride()[:3]) and t.data_ptr() % 16 == 0
+
+
+def attention_reference(q, k, v, causal: bool = True, scale: Optional[float] = None):
+    """Plain fp32 attention in ``[B, T, H, D]`` layout (the correctness oracle)."""
+    B, Tq, Hq, D = q.shape
+    Tk, Hkv = k.shape[1], k.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    g = Hq // Hkv
+    qf = q.float().permute(0, 2, 1, 3)
+    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
+    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    if causal:
+        i = torch.arange(Tq, device=q.device).view(-1, 1)
+        j = torch.arange(Tk, device=q.device).view(1, -1)
+        s = s.masked_fill(j > i + (Tk - Tq), float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    o = torch.matmul(p, vf)
+    return o.permute(0, 2, 1, 3).to(q.dtype)
+
+
+def flash_fwd(q, k, v, causal: bool, scale: float):
+    B, Tq, Hq, D = q.shape
+    Tk, Hkv = k.shape[1], k.shape[2]
+    o = torch.empty((B, Tq, Hq, D), dtype=q.dtype, device=q.device)
+    # rows padded to the backward kernels' 64-query vector loads
+    lse = torch.empty((B, Hq, (Tq + 127) // 128 * 128), dtype=torch.float32, device=q.device)
+    code = lib().tpb_flash_fwd(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), B, Tq, Tk, Hq, Hkv,
+        D, q.stride(1), q.stride(2), q.stride(0), k.stride(1), k.stride(2), k.stride(0),
+        v.stride(1), v.stride(2), v.stride(0), o.stride(1), o.stride(2), o.stride(0), lse.shape[2],
+        int(causal), float(scale), status_word(q.device).data_ptr(), stream_ptr())
+    _native.check(code, "tpb_flash_fwd")
+    return o, lse
+
+
+def flash_bwd(do, q, k, v, o, lse, causal: bool, scale: float):
+    B, Tq, Hq, D = q.shape
+    Tk, Hkv = k.shape[1], k.shape[2]
+    dq = torch.empty((B, Tq, Hq, D), dtype=q.dtype, device=q.device)
+    dk = torch.empty((B, Tk, Hkv, D), dtype=q.dtype, device=q.device)
+    dv = torch.empty((B, Tk, Hkv, D), dtype=q.dtype, device=q.device)
+    delta = torch.empty_like(lse)
+    if not _strides_ok(do):
+        do = do.contiguous()
+    code = lib().tpb_flash_bwd(
+        do.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+        delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, Tq, Tk, Hq, Hkv, D,
+        q.stride(1), q.stride(2), q.stride(0), k.stride(1), k.stride(2), k.stride(0),
+        v.stride(1), v.stride(2), v.stride(0), o.stride(1), o.stride(2), o.stride(0),
+        do.stride(1), do.stride(2), do.stride(0), lse.shape[2], int(causal), float(scale),
+        status_word(q.device).data_ptr(), stream_ptr())
+    _native.check(code, "tpb_flash_bwd")
+    return dq, dk, dv
+
+
+class _FlashAttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal, scale):
+        o, lse = flash_fwd(q, k, v, causal, scale)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.causal, ctx.scale = causal, scale
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = flash_bwd(do, q, k, v, o, lse, ctx.causal, ctx.scale)
+        return dq, dk, dv, None, None
+
+
+def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = True,
+                    scale: Optional[float] = None) -> torch.Tensor:
+    """``softmax(q k^T * scale [+ causal mask]) v`` for ``q [B, Tq, Hq, D]``, ``k/v [B, Tk, Hkv, D]``.
+
+    ``Hq`` must be a multiple of ``Hkv`` (grouped-query attention). With ``causal`` the last
+    query is aligned with the last key.
+    """
+    D = q.shape[-1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    native = (q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128) and use_native(q, k, v))
+    if not native:
+        return attention_reference(q, k, v, causal, scale)
+    if not _strides_ok(q):
+        q = q.contiguous()
+    if not _strides_ok(k):
+        k = k.contiguous()
+    if not _strides_ok(v):
+        v = v.contiguous()
+    return _FlashAttnFn.apply(q, k, v, causal, scale)

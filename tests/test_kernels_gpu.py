@@ -95,7 +95,7 @@ def test_rmsnorm(rows, H, with_res):
     rr = res.detach().float().requires_grad_() if with_res else None
     h = xr + rr if with_res else xr
     if with_res:
-        h = h.to(torch.bfloat16).float() + (h - h.detach())  # stream rounded to bf16, straight-through
+        h = h.detach().to(torch.bfloat16).float() + (h - h.detach())  # stream rounded to bf16, straight-through
     yr = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-5) * wr
     loss = (yr * g.float()).sum()
     if with_res:
