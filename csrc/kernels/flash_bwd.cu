@@ -440,14 +440,16 @@ extern "C" int tpb_flash_bwd(const void* dout, const void* q, const void* k, con
                              long long k_head, long long k_batch, long long v_tok,
                              long long v_head, long long v_batch, long long o_tok,
                              long long o_head, long long o_batch, long long do_tok,
-                             long long do_head, long long do_batch, int lse_stride, int causal,
+                             long long do_head, long long do_batch, long long dq_tok,
+                             long long dq_head, long long dq_batch, long long dkv_tok,
+                             long long dkv_head, long long dkv_batch, int lse_stride, int causal,
                              float scale, uint32_t* status, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   if (B <= 0 || Tq <= 0 || Hq <= 0) return 0;
   if ((D != 64 && D != 128) || Hkv <= 0 || Hq % Hkv || Tk <= 0) return -2;
   if (lse_stride % 64 || lse_stride < (Tq + 63) / 64 * 64) return -2;
   if ((q_tok | q_head | q_batch | k_tok | k_head | k_batch | v_tok | v_head | v_batch | do_tok |
-       do_head | do_batch) % 8)
+       do_head | do_batch | dq_tok | dq_head | dq_batch | dkv_tok | dkv_head | dkv_batch) % 8)
     return -2;
   // delta
   {
@@ -463,7 +465,7 @@ extern "C" int tpb_flash_bwd(const void* dout, const void* q, const void* k, con
   p.lse = lse; p.delta = delta; p.lse_stride = lse_stride; p.status = status;
   p.wait_ns = kDefaultWaitNs;
   int r;
-  // ---- dK / dV: outputs are contiguous [B, Tk, Hkv, D]
+  // ---- dK / dV: [B, Tk, Hkv, D] by the dkv strides (dk and dv share them)
   {
     CUtensorMap tk, tv, tq, tdo;
     if ((r = make_tmap_bthd(&tk, k, B, Tk, Hkv, D, k_tok, k_head, k_batch, kStat))) return r;
@@ -471,13 +473,13 @@ extern "C" int tpb_flash_bwd(const void* dout, const void* q, const void* k, con
     if ((r = make_tmap_bthd(&tq, q, B, Tq, Hq, D, q_tok, q_head, q_batch, kStream))) return r;
     if ((r = make_tmap_bthd(&tdo, dout, B, Tq, Hq, D, do_tok, do_head, do_batch, kStream))) return r;
     p.out0 = (__nv_bfloat16*)dv; p.out1 = (__nv_bfloat16*)dk;
-    p.out_tok = (long long)Hkv * D; p.out_head = D; p.out_batch = (long long)Tk * Hkv * D;
+    p.out_tok = dkv_tok; p.out_head = dkv_head; p.out_batch = dkv_batch;
     dim3 grid((Tk + kStat - 1) / kStat, Hkv, B);
     r = (D == 128) ? launch_bwd<128, true>(tk, tv, tq, tdo, p, grid, stream)
                    : launch_bwd<64, true>(tk, tv, tq, tdo, p, grid, stream);
     if (r) return r;
   }
-  // ---- dQ: output contiguous [B, Tq, Hq, D]
+  // ---- dQ: [B, Tq, Hq, D] by the dq strides
   {
     CUtensorMap tq, tdo, tk, tv;
     if ((r = make_tmap_bthd(&tq, q, B, Tq, Hq, D, q_tok, q_head, q_batch, kStat))) return r;
@@ -485,7 +487,7 @@ extern "C" int tpb_flash_bwd(const void* dout, const void* q, const void* k, con
     if ((r = make_tmap_bthd(&tk, k, B, Tk, Hkv, D, k_tok, k_head, k_batch, kStream))) return r;
     if ((r = make_tmap_bthd(&tv, v, B, Tk, Hkv, D, v_tok, v_head, v_batch, kStream))) return r;
     p.out0 = nullptr; p.out1 = (__nv_bfloat16*)dq;
-    p.out_tok = (long long)Hq * D; p.out_head = D; p.out_batch = (long long)Tq * Hq * D;
+    p.out_tok = dq_tok; p.out_head = dq_head; p.out_batch = dq_batch;
     dim3 grid((Tq + kStat - 1) / kStat, Hq, B);
     r = (D == 128) ? launch_bwd<128, false>(tq, tdo, tk, tv, p, grid, stream)
                    : launch_bwd<64, false>(tq, tdo, tk, tv, p, grid, stream);

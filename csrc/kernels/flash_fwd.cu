@@ -351,6 +351,7 @@ typedef CUresult (*EncodeTiledFn2)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
 // be 1 and is ignored), 128-byte swizzle or none.
 int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                    const uint64_t* strides_elems, const uint32_t* box, int swizzle128) {
+  ensure_thread_context();
   static EncodeTiledFn2 fn = nullptr;
   static std::once_flag once;
   std::call_once(once, [] {

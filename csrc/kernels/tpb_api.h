@@ -10,6 +10,7 @@
 #ifdef __cplusplus
 namespace tpb {
 int sm_count();
+void ensure_thread_context();
 int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t ld,
                       uint32_t box1);
 int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
@@ -75,8 +76,9 @@ int tpb_flash_bwd(const void* dout, const void* q, const void* k, const void* v,
                   long long q_batch, long long k_tok, long long k_head, long long k_batch,
                   long long v_tok, long long v_head, long long v_batch, long long o_tok,
                   long long o_head, long long o_batch, long long do_tok, long long do_head,
-                  long long do_batch, int lse_stride, int causal, float scale, uint32_t* status,
-                  void* stream);
+                  long long do_batch, long long dq_tok, long long dq_head, long long dq_batch,
+                  long long dkv_tok, long long dkv_head, long long dkv_batch, int lse_stride,
+                  int causal, float scale, uint32_t* status, void* stream);
 
 int tpb_adamw_flat(float* master, float* m, float* v, const void* grad, int grad_bf16, void* model,
                    int model_bf16, long long n, float lr, float beta1, float beta2, float eps,

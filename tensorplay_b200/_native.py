@@ -38,7 +38,7 @@ _KERNEL_SIGS = {
     "tpb_cross_entropy": [P, P, P, P, P, LL, I, LL, LL, F, P],
     "tpb_cross_entropy_bwd": [P, P, P, P, P, P, P, LL, I, LL, LL, P],
     "tpb_flash_fwd": [P, P, P, P, P, I, I, I, I, I, I] + [LL] * 12 + [I, I, F, P, P],
-    "tpb_flash_bwd": [P] * 10 + [I, I, I, I, I, I] + [LL] * 15 + [I, I, F, P, P],
+    "tpb_flash_bwd": [P] * 10 + [I, I, I, I, I, I] + [LL] * 21 + [I, I, F, P, P],
     "tpb_adamw_flat": [P, P, P, P, I, P, I, LL, F, F, F, F, F, I, F, I, P, P, P],
     "tpb_adamw_multi": [I, P, P, P, P, P, P, I, I, F, F, F, F, F, I, F, I, P, P, P],
     "tpb_sumsq": [P, I, LL, F, P, P],
@@ -66,6 +66,33 @@ def _load(name: str):
     return C.CDLL(str(path), mode=C.RTLD_GLOBAL)
 
 
+# kernel launches issued by one call of each entry point (for launch accounting)
+_LAUNCHES = {"tpb_rmsnorm_bwd": 2, "tpb_layernorm_bwd": 3, "tpb_flash_bwd": 3, "tpb_rmsnorm_bwd_grid": 0}
+launch_count = 0
+
+
+class _Counting:
+    """Proxy over the ctypes library that counts kernel launches per entry point."""
+
+    def __init__(self, lib):
+        self._lib = lib
+        self._cache = {}
+
+    def __getattr__(self, name):
+        fn = self._cache.get(name)
+        if fn is None:
+            raw = getattr(self._lib, name)
+            n = _LAUNCHES.get(name, 1)
+
+            def fn(*a, _raw=raw, _n=n):
+                global launch_count
+                launch_count += _n
+                return _raw(*a)
+
+            self._cache[name] = fn
+        return fn
+
+
 def register_sigs(lib, sigs) -> None:
     for fn, args in sigs.items():
         if hasattr(lib, fn):
@@ -81,7 +108,7 @@ def kernels():
             if _kernels is None:
                 lib = _load("libtpb200.so")
                 register_sigs(lib, _KERNEL_SIGS)
-                _kernels = lib
+                _kernels = _Counting(lib)
     return _kernels
 
 

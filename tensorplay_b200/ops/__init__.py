@@ -2,6 +2,7 @@
 ``libtpb200.so``; CPU tensors run a plain-PyTorch path that doubles as the correctness oracle."""
 from ._common import DeviceWaitTimeout, check_status, status_word
 from .activation import gelu, swiglu, swiglu_packed
+from .attention import attention_reference, flash_attention, qkv_attention
 from .gemm import gemm, linear
 from .loss import cross_entropy
 from .norm import layer_norm, rms_norm
@@ -11,5 +12,6 @@ from .rope import apply_rope, rope_tables
 __all__ = [
     "DeviceWaitTimeout", "check_status", "status_word", "gelu", "swiglu", "swiglu_packed", "gemm",
     "linear", "cross_entropy", "layer_norm", "rms_norm", "adamw_flat_", "adamw_multi_",
-    "clip_coef_", "sumsq_", "apply_rope", "rope_tables",
+    "clip_coef_", "sumsq_", "apply_rope", "rope_tables", "attention_reference", "flash_attention",
+    "qkv_attention",
 ]

@@ -58,12 +58,18 @@ def flash_fwd(q, k, v, causal: bool, scale: float):
     return o, lse
 
 
-def flash_bwd(do, q, k, v, o, lse, causal: bool, scale: float):
+def flash_bwd(do, q, k, v, o, lse, causal: bool, scale: float, dq=None, dk=None, dv=None):
+    """Backward of ``flash_fwd``. ``dq``/``dk``/``dv`` may be preallocated (strided) views, e.g.
+    slices of one fused dQKV buffer; ``dk`` and ``dv`` must share their strides."""
     B, Tq, Hq, D = q.shape
     Tk, Hkv = k.shape[1], k.shape[2]
-    dq = torch.empty((B, Tq, Hq, D), dtype=q.dtype, device=q.device)
-    dk = torch.empty((B, Tk, Hkv, D), dtype=q.dtype, device=q.device)
-    dv = torch.empty((B, Tk, Hkv, D), dtype=q.dtype, device=q.device)
+    if dq is None:
+        dq = torch.empty((B, Tq, Hq, D), dtype=q.dtype, device=q.device)
+    if dk is None:
+        dk = torch.empty((B, Tk, Hkv, D), dtype=q.dtype, device=q.device)
+    if dv is None:
+        dv = torch.empty((B, Tk, Hkv, D), dtype=q.dtype, device=q.device)
+    assert dk.stride() == dv.stride()
     delta = torch.empty_like(lse)
     if not _strides_ok(do):
         do = do.contiguous()
@@ -72,7 +78,8 @@ def flash_bwd(do, q, k, v, o, lse, causal: bool, scale: float):
         delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, Tq, Tk, Hq, Hkv, D,
         q.stride(1), q.stride(2), q.stride(0), k.stride(1), k.stride(2), k.stride(0),
         v.stride(1), v.stride(2), v.stride(0), o.stride(1), o.stride(2), o.stride(0),
-        do.stride(1), do.stride(2), do.stride(0), lse.shape[2], int(causal), float(scale),
+        do.stride(1), do.stride(2), do.stride(0), dq.stride(1), dq.stride(2), dq.stride(0),
+        dk.stride(1), dk.stride(2), dk.stride(0), lse.shape[2], int(causal), float(scale),
         status_word(q.device).data_ptr(), stream_ptr())
     _native.check(code, "tpb_flash_bwd")
     return dq, dk, dv
@@ -112,3 +119,68 @@ def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: b
     if not _strides_ok(v):
         v = v.contiguous()
     return _FlashAttnFn.apply(q, k, v, causal, scale)
+
+
+class _QKVAttnFn(torch.autograd.Function):
+    """RoPE + flash attention on a packed QKV projection ``[B, T, (Hq + 2 Hkv) * D]``.
+
+    Forward rotates q and k into a fresh ``[B, T, Hq + Hkv, D]`` buffer with one launch and
+    attends with v read in place from the packed buffer. Backward has the flash kernels
+    write dq, dk and dv straight into the slices of one packed gradient buffer and un-rotates
+    its q/k part in place, so that no concatenation or copy is needed around the projection.
+    """
+
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, pos, Hq, Hkv, D, causal, scale, interleaved):
+        from .rope import _rope_native_
+        B, T, _ = qkv.shape
+        tot = Hq + 2 * Hkv
+        packed = qkv.view(B, T, tot, D)
+        qk = packed[:, :, : Hq + Hkv].contiguous()
+        _rope_native_(qk, cos, sin, pos, interleaved, False)
+        q, k, v = qk[:, :, :Hq], qk[:, :, Hq:], packed[:, :, Hq + Hkv:]
+        o, lse = flash_fwd(q, k, v, causal, scale)
+        ctx.save_for_backward(qk, qkv, o, lse, cos, sin, pos if pos is not None else torch.empty(0))
+        ctx.cfg = (Hq, Hkv, D, causal, scale, interleaved, pos is not None)
+        return o.view(B, T, Hq * D)
+
+    @staticmethod
+    def backward(ctx, do):
+        from .rope import _rope_native_
+        qk, qkv, o, lse, cos, sin, pos = ctx.saved_tensors
+        Hq, Hkv, D, causal, scale, interleaved, has_pos = ctx.cfg
+        B, T, _ = qkv.shape
+        tot = Hq + 2 * Hkv
+        packed = qkv.view(B, T, tot, D)
+        dqkv = torch.empty_like(qkv)
+        dp = dqkv.view(B, T, tot, D)
+        do4 = do.reshape(B, T, Hq, D)
+        if not _strides_ok(do4):
+            do4 = do4.contiguous()
+        flash_bwd(do4, qk[:, :, :Hq], qk[:, :, Hq:], packed[:, :, Hq + Hkv:], o, lse, causal, scale,
+                  dq=dp[:, :, :Hq], dk=dp[:, :, Hq:Hq + Hkv], dv=dp[:, :, Hq + Hkv:])
+        _rope_native_(dp[:, :, : Hq + Hkv], cos, sin, pos if has_pos else None, interleaved, True)
+        return dqkv, None, None, None, None, None, None, None, None, None
+
+
+def qkv_attention(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                  position_ids: Optional[torch.Tensor], num_heads: int, num_kv_heads: int,
+                  head_dim: int, causal: bool = True, scale: Optional[float] = None,
+                  interleaved: bool = False) -> torch.Tensor:
+    """Attention over a packed QKV projection; returns ``[B, T, num_heads * head_dim]``."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
+    B, T, _ = qkv.shape
+    native = (qkv.is_cuda and qkv.dtype == torch.bfloat16 and head_dim in (64, 128)
+              and use_native(qkv))
+    pos = None if position_ids is None else position_ids.reshape(-1).to(torch.int64).contiguous()
+    if native:
+        if not qkv.is_contiguous():
+            qkv = qkv.contiguous()
+        return _QKVAttnFn.apply(qkv, cos, sin, pos, num_heads, num_kv_heads, head_dim, causal, scale,
+                                interleaved)
+    from .rope import _rope_ref
+    packed = qkv.view(B, T, num_heads + 2 * num_kv_heads, head_dim)
+    qk = _rope_ref(packed[:, :, : num_heads + num_kv_heads], cos, sin, position_ids, interleaved, 1.0)
+    o = attention_reference(qk[:, :, :num_heads], qk[:, :, num_heads:],
+                            packed[:, :, num_heads + num_kv_heads:], causal, scale)
+    return o.reshape(B, T, num_heads * head_dim)

@@ -77,6 +77,9 @@ class _LinearFn(torch.autograd.Function):
         ctx.save_for_backward(x2, weight)
         ctx.has_bias = bias is not None
         ctx.x_shape = x.shape
+        # A training engine may own the gradient storage (a view into a flat per-unit buffer):
+        # the weight-gradient GEMM then writes / accumulates there and autograd sees no grad.
+        ctx.w_ref = weight if hasattr(weight, "_tpb_grad_view") else None
         return y.view(*x.shape[:-1], weight.shape[0])
 
     @staticmethod
@@ -89,7 +92,13 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, weight, b_mn=True).view(ctx.x_shape)
         if ctx.needs_input_grad[1]:
-            dw = gemm(dy2, x2, a_mn=True, b_mn=True)
+            w_ref = ctx.w_ref
+            if w_ref is not None and w_ref._tpb_grad_view is not None:
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=w_ref._tpb_grad_view,
+                     accumulate=getattr(w_ref, "_tpb_grad_written", False))
+                w_ref._tpb_grad_written = True
+            else:
+                dw = gemm(dy2, x2, a_mn=True, b_mn=True)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy2.float().sum(0).to(dy.dtype)
         return dx, dw, db

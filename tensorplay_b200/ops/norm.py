@@ -44,6 +44,7 @@ class _RMSNormFn(torch.autograd.Function):
         ctx.save_for_backward(xin, weight, rstd)
         ctx.shape = x.shape
         ctx.has_res = residual is not None
+        ctx.w_ref = weight if hasattr(weight, "_tpb_grad_view") else None
         if residual is not None:
             return y.view(x.shape), res_out.view(x.shape)
         return y.view(x.shape), None
@@ -61,12 +62,22 @@ class _RMSNormFn(torch.autograd.Function):
         dx = torch.empty((rows, H), dtype=xin.dtype, device=xin.device)
         grid = lib().tpb_rmsnorm_bwd_grid(rows, H)
         part = torch.empty((grid, H), dtype=torch.float32, device=xin.device)
-        dw = torch.empty(H, dtype=weight.dtype, device=xin.device)
+        w_ref = ctx.w_ref
+        owned = w_ref is not None and w_ref._tpb_grad_view is not None
+        acc = 0
+        if owned:
+            dw = w_ref._tpb_grad_view
+            acc = int(getattr(w_ref, "_tpb_grad_written", False))
+            w_ref._tpb_grad_written = True
+        else:
+            dw = torch.empty(H, dtype=weight.dtype, device=xin.device)
         code = lib().tpb_rmsnorm_bwd(dy2.data_ptr(), xin.data_ptr(), weight.data_ptr(),
                                      rstd.data_ptr(), ptr(dres2), dx.data_ptr(), part.data_ptr(),
-                                     None, dw.data_ptr(), 0, rows, H, xin.stride(0), dy2.stride(0),
+                                     None, dw.data_ptr(), acc, rows, H, xin.stride(0), dy2.stride(0),
                                      dx.stride(0), stream_ptr())
         _native.check(code, "tpb_rmsnorm_bwd")
+        if owned:
+            dw = None
         dxv = dx.view(ctx.shape)
         return dxv, dw, None, (dxv if ctx.has_res else None)
 

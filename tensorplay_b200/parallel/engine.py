@@ -1,0 +1,416 @@
+"""Flat-buffer fully-sharded training engine (ZeRO-3 style) with the optimizer fused into backward.
+
+Design (one process per GPU):
+
+* The model is cut into *units* (embedding, each transformer block, head). Every unit owns one
+  flat bf16 parameter buffer; the module's parameters are views into it, so a unit is
+  all-gathered as a single contiguous range and its GEMMs read the gathered buffer directly -
+  there is no copy-in / copy-out as in the reference's ``foreach_all_gather`` +
+  ``foreach_all_gather_copy_out`` (tensorplay/distributed/fsdp/_fully_shard/_fsdp_collectives.py:337-470).
+* Each rank keeps only its 1/N shard of the fp32 master weights and Adam moments.
+* Backward of a unit writes weight gradients straight into a flat bf16 gradient buffer (the
+  GEMM / norm kernels take the destination view), then ONE fused step reduces the unit's
+  gradients across ranks, scales, applies AdamW on the owned shard and emits the new bf16
+  parameters - the reference runs cast + chunk_cat + ncclReduceScatter + divide + views
+  (:473-690) and later a separate multi-tensor AdamW (p10/include/OptimizerMTA.cuh:627).
+* Activation checkpointing per unit: forward keeps only the unit input; backward re-gathers
+  the parameters (prefetching the next unit on the communication stream) and recomputes.
+
+Communication backends: ``single`` (one rank), ``torch`` (torch.distributed all-gather /
+reduce-scatter, gloo or NCCL: the baseline and the CPU test path) and ``symm`` (the fused
+peer-memory kernels of ``tensorplay_b200.parallel.symm``).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+from torch import Tensor, nn
+
+from .. import ops
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+@dataclass
+class AdamWConfig:
+    lr: float = 3e-4
+    betas: Tuple[float, float] = (0.9, 0.95)
+    eps: float = 1e-8
+    weight_decay: float = 0.1
+
+
+class ParamUnit:
+    """One shardable group of parameters living in a flat buffer."""
+
+    def __init__(self, index: int, name: str, params: List[Tuple[str, nn.Parameter]], world: int,
+                 rank: int, device, param_dtype: torch.dtype):
+        self.index, self.name, self.params = index, name, params
+        self.world, self.rank = world, rank
+        self.offsets: List[int] = []
+        off = 0
+        for _, p in params:
+            self.offsets.append(off)
+            off += _round_up(p.numel(), 8)  # keep every view 16-byte aligned
+        self.numel = off
+        self.padded = _round_up(max(off, 8), world * 128)
+        self.shard_numel = self.padded // world
+        self.device, self.param_dtype = device, param_dtype
+        # state filled in by the engine
+        self.full: Optional[Tensor] = None
+        self.grad: Optional[Tensor] = None
+        self.shard: Optional[Tensor] = None
+        self.master: Optional[Tensor] = None
+        self.exp_avg: Optional[Tensor] = None
+        self.exp_avg_sq: Optional[Tensor] = None
+        self.gather_event = None
+        self.update_event = None
+
+    def bind_params(self, full: Tensor) -> None:
+        self.full = full
+        for (_, p), off in zip(self.params, self.offsets):
+            p.data = full[off: off + p.numel()].view(p.shape)
+
+    def bind_grads(self, grad: Optional[Tensor]) -> None:
+        self.grad = grad
+        for (_, p), off in zip(self.params, self.offsets):
+            p._tpb_grad_view = None if grad is None else grad[off: off + p.numel()].view(p.shape)
+            p._tpb_grad_written = False
+
+    def collect_autograd_grads(self) -> None:
+        """Fold ``.grad`` tensors produced by plain autograd paths into the flat buffer."""
+        for _, p in self.params:
+            if p.grad is not None:
+                v = p._tpb_grad_view
+                if getattr(p, "_tpb_grad_written", False):
+                    v.add_(p.grad.to(v.dtype))
+                else:
+                    v.copy_(p.grad)
+                    p._tpb_grad_written = True
+                p.grad = None
+
+    def shard_range(self, rank: Optional[int] = None) -> Tuple[int, int]:
+        r = self.rank if rank is None else rank
+        return r * self.shard_numel, (r + 1) * self.shard_numel
+
+
+class _UnitFn(torch.autograd.Function):
+    """Runs one unit; with checkpointing only the inputs are kept and forward is recomputed."""
+
+    @staticmethod
+    def forward(ctx, engine, unit_idx, fn, checkpoint, n_tensor, *args):
+        tensors, extra = args[:n_tensor], args[n_tensor:]
+        ctx.engine, ctx.unit_idx, ctx.fn, ctx.checkpoint, ctx.extra = engine, unit_idx, fn, checkpoint, extra
+        engine._pre_forward(unit_idx)
+        if checkpoint:
+            with torch.no_grad():
+                out = fn(*tensors, *extra)
+            ctx.save_for_backward(*tensors)
+        else:
+            detached = [t.detach().requires_grad_(t.requires_grad) if t.is_floating_point() else t
+                        for t in tensors]
+            with torch.enable_grad():
+                out = fn(*detached, *extra)
+            ctx.detached, ctx.out = detached, out
+            out = out.detach()
+        engine._post_forward(unit_idx)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        engine, u = ctx.engine, ctx.unit_idx
+        engine._pre_backward(u)
+        if ctx.checkpoint:
+            tensors = [t.detach().requires_grad_(t.requires_grad) if t.is_floating_point() else t
+                       for t in ctx.saved_tensors]
+            with torch.enable_grad():
+                out = ctx.fn(*tensors, *ctx.extra)
+        else:
+            tensors, out = ctx.detached, ctx.out
+            ctx.detached = ctx.out = None
+        torch.autograd.backward(out, dout)
+        grads = tuple(t.grad if (t.is_floating_point() and t.requires_grad) else None for t in tensors)
+        engine._post_backward(u)
+        return (None, None, None, None, None) + grads + (None,) * len(ctx.extra)
+
+
+class FSDPEngine:
+    """Sharded trainer for models with ``embed_tokens(tokens)``, ``layers`` and ``head(x, targets)``.
+
+    ``step(tokens, targets)`` runs forward, backward and the AdamW update and returns the loss
+    tensor (on device).
+    """
+
+    def __init__(self, model: nn.Module, optim: AdamWConfig = AdamWConfig(),
+                 group: Optional[dist.ProcessGroup] = None, comm: str = "auto",
+                 activation_checkpointing: bool = True, max_grad_norm: Optional[float] = None,
+                 unit_modules: Optional[Sequence[Sequence[nn.Module]]] = None,
+                 layer_args: Callable[[nn.Module, Tensor], tuple] = None):
+        self.model = model
+        self.cfg = optim
+        self.group = group
+        self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        first = next(model.parameters())
+        self.device = first.device
+        self.param_dtype = first.dtype
+        self.checkpoint = activation_checkpointing
+        self.max_grad_norm = max_grad_norm
+        self.step_count = 0
+        self.cuda = self.device.type == "cuda"
+        if comm == "auto":
+            comm = "single" if self.world == 1 else ("symm" if self.cuda else "torch")
+        self.comm_kind = comm
+        self._build_units()
+        self._alloc()
+        self._dummy = torch.zeros(1, device=self.device, requires_grad=True)
+        self.kernel_launch_estimate = 0
+
+    # ------------------------------------------------------------------ construction
+    def _build_units(self) -> None:
+        m = self.model
+        seen = set()
+
+        def plist(named):
+            out = []
+            for n, p in named:
+                if id(p) not in seen:
+                    seen.add(id(p))
+                    out.append((n, p))
+            return out
+
+        layer_params = [plist(layer.named_parameters(prefix=f"layers.{i}")) for i, layer in enumerate(m.layers)]
+        layer_ids = {id(p) for lp in layer_params for _, p in lp}
+        rest = [(n, p) for n, p in m.named_parameters() if id(p) not in layer_ids]
+        embed_names = getattr(m, "embed_param_names", ("embed", "wte", "wpe", "tok_emb", "pos_emb"))
+        emb = [(n, p) for n, p in rest if n.split(".")[0] in embed_names]
+        head = [(n, p) for n, p in rest if n.split(".")[0] not in embed_names]
+        groups = [("embed", emb)] + [(f"layer{i}", lp) for i, lp in enumerate(layer_params)] + [("head", head)]
+        self.units: List[ParamUnit] = []
+        for name, ps in groups:
+            self.units.append(ParamUnit(len(self.units), name, ps, self.world, self.rank, self.device,
+                                        self.param_dtype))
+        self.n_layers = len(m.layers)
+
+    def _alloc(self) -> None:
+        dev, dt = self.device, self.param_dtype
+        self.max_padded = max(u.padded for u in self.units)
+        single = self.world == 1
+        if self.comm_kind == "symm":
+            from .symm import SymmComm
+            self.comm = SymmComm(self)
+        else:
+            self.comm = None
+        for u in self.units:
+            init = torch.zeros(u.padded, dtype=dt, device=dev)
+            for (_, p), off in zip(u.params, u.offsets):
+                init[off: off + p.numel()].copy_(p.data.reshape(-1))
+            lo, hi = u.shard_range()
+            u.master = init[lo:hi].float()
+            u.exp_avg = torch.zeros(u.shard_numel, dtype=torch.float32, device=dev)
+            u.exp_avg_sq = torch.zeros(u.shard_numel, dtype=torch.float32, device=dev)
+            if single:
+                u.bind_params(init)
+                u.shard = init
+            else:
+                u.shard = self.comm.alloc_shard(u) if self.comm is not None else init[lo:hi].clone()
+                if self.comm is not None:
+                    u.shard.copy_(init[lo:hi])
+                # until gathered, parameters point at an empty placeholder
+                for _, p in u.params:
+                    p.data = torch.empty(0, dtype=dt, device=dev)
+            del init
+        # rotating full-parameter and gradient buffers
+        # without checkpointing autograd keeps views of the gathered buffers until backward,
+        # so every unit needs a buffer of its own for the whole step
+        self.keep_gathered = not self.checkpoint
+        n_full = 0 if single else (len(self.units) if self.keep_gathered else 3)
+        n_grad = 2 if self.cuda else 2
+        if self.comm is not None:
+            self.full_pool = [self.comm.alloc_full(self.max_padded) for _ in range(n_full)]
+            self.grad_pool = [self.comm.alloc_full(self.max_padded) for _ in range(n_grad)]
+        else:
+            self.full_pool = [torch.empty(self.max_padded, dtype=dt, device=dev) for _ in range(n_full)]
+            self.grad_pool = [torch.empty(self.max_padded, dtype=dt, device=dev) for _ in range(n_grad)]
+        self.grad_pool_events = [None] * n_grad
+        self.full_owner = [None] * n_full
+        if self.cuda:
+            self.comm_stream = torch.cuda.Stream(device=dev)
+            self.opt_stream = torch.cuda.Stream(device=dev)
+        else:
+            self.comm_stream = self.opt_stream = None
+        self.sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.clip_coef = torch.ones(1, dtype=torch.float32, device=dev)
+        self._grad_slot = 0
+
+    # ------------------------------------------------------------------ gather / release
+    def _gather(self, u: ParamUnit, slot: int) -> None:
+        """Launch the all-gather of unit ``u`` into full-buffer ``slot`` on the comm stream."""
+        buf = self.full_pool[slot][: u.padded]
+        self.full_owner[slot] = u.index
+        if self.cuda:
+            self.comm_stream.wait_stream(torch.cuda.current_stream())
+            if u.update_event is not None:
+                self.comm_stream.wait_event(u.update_event)
+            with torch.cuda.stream(self.comm_stream):
+                self._gather_impl(u, buf)
+                u.gather_event = torch.cuda.Event()
+                u.gather_event.record(self.comm_stream)
+        else:
+            self._gather_impl(u, buf)
+        u._slot = slot
+        u._pending_full = buf
+
+    def _gather_impl(self, u: ParamUnit, buf: Tensor) -> None:
+        if self.comm is not None:
+            self.comm.all_gather(u, buf)
+        else:
+            dist.all_gather_into_tensor(buf, u.shard, group=self.group)
+
+    def _slot_for(self, u: ParamUnit) -> int:
+        for i, owner in enumerate(self.full_owner):
+            if owner == u.index:
+                return i
+        for i, owner in enumerate(self.full_owner):
+            if owner is None:
+                return i
+        raise RuntimeError("no free full-parameter buffer")
+
+    def _ensure_gathered(self, u: ParamUnit, prefetch: Optional[ParamUnit]) -> None:
+        if self.world == 1:
+            return
+        if getattr(u, "_pending_full", None) is None:
+            self._gather(u, self._slot_for(u))
+        if self.cuda and u.gather_event is not None:
+            torch.cuda.current_stream().wait_event(u.gather_event)
+        u.bind_params(u._pending_full)
+        if prefetch is not None and getattr(prefetch, "_pending_full", None) is None:
+            try:
+                self._gather(prefetch, self._slot_for(prefetch))
+            except RuntimeError:
+                pass  # all buffers busy; the gather happens when the unit is reached
+
+    def _release(self, u: ParamUnit) -> None:
+        if self.world == 1:
+            return
+        if self.cuda:
+            # the buffer may be re-filled by the comm stream only after this unit's kernels ran
+            u._release_event = torch.cuda.Event()
+            u._release_event.record(torch.cuda.current_stream())
+            self.comm_stream.wait_event(u._release_event)
+        self.full_owner[u._slot] = None
+        u._pending_full = None
+        u.full = None
+
+    # ------------------------------------------------------------------ unit hooks
+    def _pre_forward(self, idx: int) -> None:
+        u = self.units[idx]
+        nxt = self.units[idx + 1] if idx + 1 < len(self.units) else None
+        self._ensure_gathered(u, nxt)
+
+    def _post_forward(self, idx: int) -> None:
+        u = self.units[idx]
+        # the head's backward follows its forward immediately: keep it gathered
+        if idx != len(self.units) - 1 and not self.keep_gathered:
+            self._release(u)
+
+    def _pre_backward(self, idx: int) -> None:
+        u = self.units[idx]
+        prv = self.units[idx - 1] if idx > 0 else None
+        self._ensure_gathered(u, prv)
+        slot = self._grad_slot
+        self._grad_slot = (slot + 1) % len(self.grad_pool)
+        ev = self.grad_pool_events[slot]
+        if ev is not None and self.cuda:
+            torch.cuda.current_stream().wait_event(ev)
+        g = self.grad_pool[slot][: u.padded]
+        g.zero_()
+        u.bind_grads(g)
+        u._grad_slot = slot
+
+    def _post_backward(self, idx: int) -> None:
+        u = self.units[idx]
+        u.collect_autograd_grads()
+        self._release(u)
+        self._reduce_and_update(u)
+
+    # ------------------------------------------------------------------ reduce + AdamW
+    def _adam_kwargs(self):
+        c = self.cfg
+        return dict(lr=c.lr, beta1=c.betas[0], beta2=c.betas[1], eps=c.eps, weight_decay=c.weight_decay,
+                    step=self.step_count)
+
+    def _reduce_and_update(self, u: ParamUnit) -> None:
+        g = u.grad
+        stream = self.opt_stream if self.world == 1 else self.comm_stream
+        if self.cuda:
+            stream.wait_stream(torch.cuda.current_stream())
+            ctx = torch.cuda.stream(stream)
+        else:
+            import contextlib
+            ctx = contextlib.nullcontext()
+        with ctx:
+            if self.world == 1:
+                ops.adamw_flat_(u.master, u.exp_avg, u.exp_avg_sq, g, u.shard, **self._adam_kwargs())
+            elif self.comm is not None:
+                self.comm.reduce_scatter_adamw(u, g, self._adam_kwargs())
+            else:
+                gs = torch.empty(u.shard_numel, dtype=g.dtype, device=g.device)
+                if g.device.type == "cpu" or dist.get_backend(self.group) == "gloo":
+                    tmp = g.float()
+                    dist.all_reduce(tmp, group=self.group)
+                    lo, hi = u.shard_range()
+                    gs = tmp[lo:hi].div_(self.world).to(g.dtype)
+                else:
+                    dist.reduce_scatter_tensor(gs, g, op=dist.ReduceOp.AVG, group=self.group)
+                ops.adamw_flat_(u.master, u.exp_avg, u.exp_avg_sq, gs, u.shard, **self._adam_kwargs())
+            if self.cuda:
+                ev = torch.cuda.Event()
+                ev.record(stream)
+                self.grad_pool_events[u._grad_slot] = ev
+                u.update_event = ev
+        u.bind_grads(None)
+
+    # ------------------------------------------------------------------ public API
+    def forward_backward(self, tokens: Tensor, targets: Tensor) -> Tensor:
+        m = self.model
+        self.step_count += 1
+        if self.cuda:
+            # parameters updated by the previous step's in-backward AdamW
+            for u in self.units:
+                if u.update_event is not None and self.world == 1:
+                    torch.cuda.current_stream().wait_event(u.update_event)
+        x = _UnitFn.apply(self, 0, lambda d, t: m.embed_tokens(t), False, 1, self._dummy, tokens)
+        extra = m.layer_extra_args(tokens) if hasattr(m, "layer_extra_args") else ()
+        for i, layer in enumerate(m.layers):
+            x = _UnitFn.apply(self, 1 + i, layer, self.checkpoint, 1, x, *extra)
+        loss = _UnitFn.apply(self, len(self.units) - 1, lambda h, t: m.head(h, t), False, 1, x, targets)
+        loss.backward()
+        return loss.detach()
+
+    def step(self, tokens: Tensor, targets: Tensor) -> Tensor:
+        return self.forward_backward(tokens, targets)
+
+    def synchronize(self) -> None:
+        if self.cuda:
+            torch.cuda.synchronize(self.device)
+
+    def gather_full_state(self) -> dict:
+        """Full (unsharded) parameters as a name -> tensor dict on every rank (for checkpoints/tests)."""
+        out = {}
+        for u in self.units:
+            if self.world == 1:
+                full = u.master
+            else:
+                full = torch.empty(u.padded, dtype=torch.float32, device=self.device)
+                if self.cuda:
+                    torch.cuda.synchronize()
+                dist.all_gather_into_tensor(full, u.master.contiguous(), group=self.group)
+            for (n, p), off in zip(u.params, u.offsets):
+                out[n] = full[off: off + p.numel()].view(p.shape).clone()
+        return out
