@@ -1,0 +1,383 @@
+// Symmetric (peer-mapped) memory and the collectives built on it, for one process per GPU on an
+// NVLink / NVSwitch box.
+//
+//  * Arena: every rank cudaMalloc's one arena and exports it with CUDA IPC; ranks open each
+//    other's arenas, so a buffer at offset X of the local arena is reachable on rank r at
+//    peer_base[r] + X. Allocation is a bump pointer that all ranks advance identically.
+//  * Signal pads: a block of 32-bit flags inside the arena. A rank publishes progress by writing
+//    (st.release.sys) into the pads of its peers; waiting is always a bounded poll of LOCAL memory.
+//  * Kernels: all-gather by peer pulls, reduce-scatter fused with scale + AdamW + bf16 parameter
+//    emit (the FSDP gradient path), all-reduce fused the same way plus parameter broadcast (the
+//    DDP path), and a barrier.
+//
+// The reference has no peer-memory path at all: tensorplay/distributed/_symmetric_memory is a
+// facade over NCCL collectives (__init__.py:228-432) and the NCCL wrapper is
+// p10/src/backend/cuda/NCCLContext.cpp:231-458.
+#include "sm100.cuh"
+#include "tpb_api.h"
+
+#include <string.h>
+
+namespace tpb {
+
+constexpr int kMaxRanks = 16;
+
+struct SymmState {
+  int world = 0, rank = 0;
+  char* base = nullptr;           // local arena
+  char* peer[kMaxRanks] = {};     // mapped arenas (peer[rank] == base)
+  size_t bytes = 0, used = 0;
+  bool opened = false;
+};
+static SymmState g_symm;
+
+struct PeerPtrs {
+  const char* p[kMaxRanks];
+};
+
+// ---------------------------------------------------------------- device helpers
+__device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+// Cross-rank rendezvous at kernel start. Thread 0 of block 0 publishes `epoch` into slot
+// [slot_base + my_rank] of every peer's pad; every block then waits (bounded) until all local
+// slots reached `epoch`. Returns false if the wait ran out of time.
+struct SyncArgs {
+  uint32_t* pad_local;         // local pad (flags written by peers)
+  uint32_t* pad_peer[kMaxRanks];  // the same pad on every rank
+  int world, rank;
+  uint32_t epoch;
+  unsigned long long wait_ns;
+  uint32_t* status;
+};
+
+__device__ __forceinline__ bool rendezvous(const SyncArgs& s, int slot_base, uint32_t where) {
+  if (blockIdx.x == 0 && threadIdx.x < s.world) {
+    __threadfence_system();
+    st_release_sys(s.pad_peer[threadIdx.x] + slot_base + s.rank, s.epoch);
+  }
+  __shared__ int ok_sh;
+  if (threadIdx.x == 0) ok_sh = 1;
+  __syncthreads();
+  if (threadIdx.x < s.world) {
+    if (!flag_wait_ge(s.pad_local + slot_base + threadIdx.x, s.epoch, true, s.status, s.wait_ns, where))
+      ok_sh = 0;
+  }
+  __syncthreads();
+  return ok_sh != 0;
+}
+
+// ---------------------------------------------------------------- all-gather (pull)
+// out[r * shard_bytes ...] = shard of rank r. Chunks are visited starting at rank+1 so that at
+// any moment the ranks pull from different peers.
+__global__ void __launch_bounds__(512)
+allgather_pull_kernel(PeerPtrs shards, char* __restrict__ out, size_t shard_bytes, SyncArgs s,
+                      int slot_base) {
+  if (!rendezvous(s, slot_base, 20)) return;
+  const size_t nvec = shard_bytes / 16;
+  const size_t per_rank_blocks = gridDim.x / s.world;
+  const int pr = blockIdx.x / per_rank_blocks;          // which peer (offset from own rank)
+  const int r = (s.rank + 1 + pr) % s.world;
+  if (pr >= s.world) return;
+  const size_t bid = blockIdx.x % per_rank_blocks;
+  const uint4* src = reinterpret_cast<const uint4*>(shards.p[r]);
+  uint4* dst = reinterpret_cast<uint4*>(out + (size_t)r * shard_bytes);
+  for (size_t i = bid * blockDim.x + threadIdx.x; i < nvec; i += per_rank_blocks * blockDim.x) {
+    dst[i] = ld_relaxed_sys_v4(src + i);
+  }
+}
+
+// ---------------------------------------------------------------- reduce-scatter + AdamW
+struct AdamArgs {
+  float lr, beta1, beta2, eps, weight_decay, bias_c1, bias_c2, grad_scale;
+};
+
+__device__ __forceinline__ void adamw_elem(float& p, float& m, float& v, float g, const AdamArgs& h) {
+  p *= (1.f - h.lr * h.weight_decay);
+  m = h.beta1 * m + (1.f - h.beta1) * g;
+  v = h.beta2 * v + (1.f - h.beta2) * g * g;
+  float denom = sqrtf(v) / sqrtf(h.bias_c2) + h.eps;
+  p -= (h.lr / h.bias_c1) * (m / denom);
+}
+
+// grads.p[r] points at rank r's full bf16 gradient buffer (same offset in every arena). This
+// rank owns elements [lo, lo + n) of it: it sums the N copies in fp32 in rank order, scales,
+// and either applies AdamW (mode 0) writing fp32 master / moments and the bf16 parameter shard
+// (+ optionally the same bf16 values into every peer's full parameter buffer: the all-reduce /
+// DDP form), or (mode 1) stores the reduced fp32 gradient and its sum of squares.
+// done_slot: after all blocks finished reading, the peers are told (slot done_slot + rank).
+__global__ void __launch_bounds__(512)
+rs_adamw_kernel(PeerPtrs grads, size_t lo, size_t n, float* __restrict__ master,
+                float* __restrict__ m, float* __restrict__ v, __nv_bfloat16* __restrict__ shard_out,
+                PeerPtrs bcast_out, size_t bcast_off, int do_bcast, float* __restrict__ red_out,
+                float* __restrict__ sumsq, int mode, AdamArgs h, const float* clip_coef, SyncArgs s,
+                int ready_slot, int done_slot, uint32_t* block_counter) {
+  if (!rendezvous(s, ready_slot, 21)) return;
+  const float gs = h.grad_scale * (clip_coef ? *clip_coef : 1.f);
+  const size_t nvec = n / 8;
+  float local_sq = 0.f;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+       i += (size_t)gridDim.x * blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int r = 0; r < s.world; ++r) {
+      const uint4* src = reinterpret_cast<const uint4*>(grads.p[r]) + lo / 8 + i;
+      uint4 raw = (r == s.rank) ? *src : ld_relaxed_sys_v4(src);
+      const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __bfloat1622float2(hb[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] *= gs;
+    if (mode == 1) {
+      float4* ro = reinterpret_cast<float4*>(red_out) + 2 * i;
+      ro[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      ro[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) local_sq += acc[j] * acc[j];
+      continue;
+    }
+    float4* mp = reinterpret_cast<float4*>(master) + 2 * i;
+    float4* mm = reinterpret_cast<float4*>(m) + 2 * i;
+    float4* vv = reinterpret_cast<float4*>(v) + 2 * i;
+    float pw[8], mw[8], vw[8];
+    *reinterpret_cast<float4*>(pw) = mp[0];
+    *reinterpret_cast<float4*>(pw + 4) = mp[1];
+    *reinterpret_cast<float4*>(mw) = mm[0];
+    *reinterpret_cast<float4*>(mw + 4) = mm[1];
+    *reinterpret_cast<float4*>(vw) = vv[0];
+    *reinterpret_cast<float4*>(vw + 4) = vv[1];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) adamw_elem(pw[j], mw[j], vw[j], acc[j], h);
+    mp[0] = *reinterpret_cast<float4*>(pw);
+    mp[1] = *reinterpret_cast<float4*>(pw + 4);
+    mm[0] = *reinterpret_cast<float4*>(mw);
+    mm[1] = *reinterpret_cast<float4*>(mw + 4);
+    vv[0] = *reinterpret_cast<float4*>(vw);
+    vv[1] = *reinterpret_cast<float4*>(vw + 4);
+    uint4 o;
+    __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) ob[j] = __floats2bfloat162_rn(pw[2 * j], pw[2 * j + 1]);
+    if (shard_out) reinterpret_cast<uint4*>(shard_out)[i] = o;
+    if (do_bcast) {
+      for (int r = 0; r < s.world; ++r) {
+        int rr = (s.rank + r) % s.world;
+        uint4* dst = reinterpret_cast<uint4*>(const_cast<char*>(bcast_out.p[rr]) + bcast_off) + lo / 8 + i;
+        *dst = o;
+      }
+    }
+  }
+  if (mode == 1 && sumsq) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) local_sq += __shfl_xor_sync(0xffffffffu, local_sq, o);
+    if ((threadIdx.x & 31) == 0) atomicAdd(sumsq, local_sq);
+  }
+  // tell the peers that this rank no longer reads their gradient buffers (and, for the
+  // broadcast form, that its slice of their parameters has landed)
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned prev = atomicAdd(block_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *block_counter = 0;
+      __threadfence_system();
+      for (int r = 0; r < s.world; ++r) st_release_sys(s.pad_peer[r] + done_slot + s.rank, s.epoch);
+    }
+  }
+}
+
+// Bounded wait until all `world` slots starting at slot_base reached `epoch` (local pad).
+__global__ void wait_slots_kernel(SyncArgs s, int slot_base, uint32_t where) {
+  if (threadIdx.x < s.world)
+    flag_wait_ge(s.pad_local + slot_base + threadIdx.x, s.epoch, true, s.status, s.wait_ns, where);
+}
+
+__global__ void barrier_kernel(SyncArgs s, int slot_base) { rendezvous(s, slot_base, 22); }
+
+// Generic peer copy: dst (local) <- src on rank r (no rendezvous; caller orders it).
+__global__ void __launch_bounds__(512)
+peer_copy_kernel(const char* __restrict__ src, char* __restrict__ dst, size_t bytes) {
+  const size_t nvec = bytes / 16;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+       i += (size_t)gridDim.x * blockDim.x)
+    reinterpret_cast<uint4*>(dst)[i] = ld_relaxed_sys_v4(reinterpret_cast<const uint4*>(src) + i);
+}
+
+static SyncArgs make_sync(size_t pad_off, uint32_t epoch, uint32_t* status, double wait_s) {
+  SyncArgs s;
+  memset(&s, 0, sizeof(s));
+  s.world = g_symm.world;
+  s.rank = g_symm.rank;
+  s.pad_local = reinterpret_cast<uint32_t*>(g_symm.base + pad_off);
+  for (int r = 0; r < g_symm.world; ++r)
+    s.pad_peer[r] = reinterpret_cast<uint32_t*>(g_symm.peer[r] + pad_off);
+  s.epoch = epoch;
+  s.wait_ns = wait_s > 0 ? (unsigned long long)(wait_s * 1e9) : kDefaultWaitNs;
+  s.status = status;
+  return s;
+}
+
+}  // namespace tpb
+
+using namespace tpb;
+
+// ------------------------------------------------------------------ arena management (host)
+// Returns 0 and fills handle_out (64 bytes) with the IPC handle of the new arena.
+extern "C" int tpb_symm_create(int world, int rank, size_t bytes, void* handle_out) {
+  if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world) return -2;
+  if (g_symm.base) return -4;  // already created
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaMemset(p, 0, bytes);
+  if (e != cudaSuccess) return (int)e;
+  g_symm.world = world;
+  g_symm.rank = rank;
+  g_symm.base = static_cast<char*>(p);
+  g_symm.bytes = bytes;
+  g_symm.used = 0;
+  g_symm.peer[rank] = g_symm.base;
+  if (world > 1) {
+    cudaIpcMemHandle_t h;
+    e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) return (int)e;
+    memcpy(handle_out, &h, sizeof(h));
+  } else {
+    memset(handle_out, 0, 64);
+  }
+  return 0;
+}
+
+// handles: world * 64 bytes, rank-major (as gathered from tpb_symm_create on every rank).
+extern "C" int tpb_symm_open(const void* handles) {
+  if (!g_symm.base) return -4;
+  for (int r = 0; r < g_symm.world; ++r) {
+    if (r == g_symm.rank) continue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, static_cast<const char*>(handles) + 64 * r, sizeof(h));
+    void* p = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return (int)e;
+    g_symm.peer[r] = static_cast<char*>(p);
+  }
+  g_symm.opened = true;
+  return 0;
+}
+
+extern "C" int tpb_symm_destroy() {
+  if (!g_symm.base) return 0;
+  for (int r = 0; r < g_symm.world; ++r)
+    if (r != g_symm.rank && g_symm.peer[r]) cudaIpcCloseMemHandle(g_symm.peer[r]);
+  cudaFree(g_symm.base);
+  g_symm = SymmState();
+  return 0;
+}
+
+// Bump allocation (256-byte aligned). Returns the offset, or (size_t)-1 when the arena is full.
+extern "C" size_t tpb_symm_alloc(size_t bytes) {
+  size_t off = (g_symm.used + 255) & ~size_t(255);
+  if (!g_symm.base || off + bytes > g_symm.bytes) return (size_t)-1;
+  g_symm.used = off + bytes;
+  return off;
+}
+extern "C" void* tpb_symm_ptr(int rank, size_t off) {
+  if (!g_symm.base || rank < 0 || rank >= g_symm.world) return nullptr;
+  return g_symm.peer[rank] + off;
+}
+extern "C" size_t tpb_symm_used() { return g_symm.used; }
+
+// ------------------------------------------------------------------ collectives
+static PeerPtrs peers_at(size_t off) {
+  PeerPtrs pp;
+  memset(&pp, 0, sizeof(pp));
+  for (int r = 0; r < g_symm.world; ++r) pp.p[r] = g_symm.peer[r] + off;
+  return pp;
+}
+
+// out (any local device pointer) <- concatenation over ranks of the shard at arena offset
+// shard_off. pad_off/slot_base: `world` consecutive flag slots used as the "shards are valid
+// at epoch" rendezvous.
+extern "C" int tpb_symm_allgather(size_t shard_off, size_t shard_bytes, void* out, size_t pad_off,
+                                  int slot_base, uint32_t epoch, int ctas, double wait_s,
+                                  uint32_t* status, void* stream) {
+  if (!g_symm.opened && g_symm.world > 1) return -4;
+  if (shard_bytes % 16 || (reinterpret_cast<uintptr_t>(out) & 15)) return -2;
+  int per_rank = ctas > 0 ? ctas : 8;
+  int grid = per_rank * g_symm.world;
+  SyncArgs s = make_sync(pad_off, epoch, status, wait_s);
+  allgather_pull_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(
+      peers_at(shard_off), static_cast<char*>(out), shard_bytes, s, slot_base);
+  return (int)cudaGetLastError();
+}
+
+// Fused reduce-scatter + AdamW over the bf16 gradient buffer at arena offset grad_off.
+//   mode 0: update master/m/v (local fp32 pointers, n elements), write bf16 shard to shard_out
+//           (local pointer, may be null); if bcast_off != (size_t)-1 also write the bf16 values
+//           into every rank's buffer at arena offset bcast_off (+ lo): all-reduce/DDP form.
+//   mode 1: write the reduced, scaled fp32 gradient to red_out and add its squares to sumsq.
+// ready_slot / done_slot: `world` flag slots each.
+extern "C" int tpb_symm_rs_adamw(size_t grad_off, size_t lo, size_t n, float* master, float* m,
+                                 float* v, void* shard_out, size_t bcast_off, float* red_out,
+                                 float* sumsq, int mode, float lr, float beta1, float beta2,
+                                 float eps, float wd, int step, float grad_scale,
+                                 const float* clip_coef, size_t pad_off, int ready_slot,
+                                 int done_slot, uint32_t epoch, uint32_t* block_counter, int ctas,
+                                 double wait_s, uint32_t* status, void* stream) {
+  if (!g_symm.opened && g_symm.world > 1) return -4;
+  if (n % 8 || lo % 8) return -2;
+  AdamArgs h;
+  h.lr = lr; h.beta1 = beta1; h.beta2 = beta2; h.eps = eps; h.weight_decay = wd;
+  h.bias_c1 = 1.f - powf(beta1, (float)step);
+  h.bias_c2 = 1.f - powf(beta2, (float)step);
+  h.grad_scale = grad_scale;
+  SyncArgs s = make_sync(pad_off, epoch, status, wait_s);
+  int grid = ctas > 0 ? ctas : 64;
+  int do_bcast = bcast_off != (size_t)-1;
+  rs_adamw_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(
+      peers_at(grad_off), lo, n, master, m, v, (__nv_bfloat16*)shard_out,
+      do_bcast ? peers_at(0) : peers_at(0), do_bcast ? bcast_off : 0, do_bcast, red_out, sumsq, mode,
+      h, clip_coef, s, ready_slot, done_slot, block_counter);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int tpb_symm_wait_slots(size_t pad_off, int slot_base, uint32_t epoch, double wait_s,
+                                   uint32_t* status, void* stream) {
+  SyncArgs s = make_sync(pad_off, epoch, status, wait_s);
+  wait_slots_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(s, slot_base, 23);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int tpb_symm_barrier(size_t pad_off, int slot_base, uint32_t epoch, double wait_s,
+                                uint32_t* status, void* stream) {
+  SyncArgs s = make_sync(pad_off, epoch, status, wait_s);
+  barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(s, slot_base);
+  return (int)cudaGetLastError();
+}
+
+// dst (local) <- [src_off, src_off + bytes) of rank src_rank's arena.
+extern "C" int tpb_symm_peer_copy(int src_rank, size_t src_off, void* dst, size_t bytes, int ctas,
+                                  void* stream) {
+  if (bytes % 16) return -2;
+  peer_copy_kernel<<<ctas > 0 ? ctas : 32, 512, 0, (cudaStream_t)stream>>>(
+      g_symm.peer[src_rank] + src_off, static_cast<char*>(dst), bytes);
+  return (int)cudaGetLastError();
+}

@@ -328,6 +328,8 @@ class FSDPEngine:
         ev = self.grad_pool_events[slot]
         if ev is not None and self.cuda:
             torch.cuda.current_stream().wait_event(ev)
+        if self.comm is not None:
+            self.comm.before_grad_reuse(slot)
         g = self.grad_pool[slot][: u.padded]
         g.zero_()
         u.bind_grads(g)

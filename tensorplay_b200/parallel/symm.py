@@ -1,0 +1,184 @@
+"""Symmetric memory over NVLink: arena allocation, handle exchange and the fused collectives.
+
+Every rank allocates one device arena, exports it with CUDA IPC and maps the arenas of its
+peers; buffers are carved from the arena at identical offsets on every rank, so that a kernel can
+address the same buffer on any peer. This is the real counterpart of the reference's facade
+``tensorplay/distributed/_symmetric_memory`` (``get_buffer(peer)`` there returns the local tensor,
+__init__.py:118-130; ``rendezvous`` only all-gathers metadata, :456-467).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import _native
+from ..ops._common import status_word, stream_ptr
+
+_SIGS = {
+    "tpb_symm_create": [C.c_int, C.c_int, C.c_size_t, C.c_void_p],
+    "tpb_symm_open": [C.c_void_p],
+    "tpb_symm_destroy": [],
+    "tpb_symm_allgather": [C.c_size_t, C.c_size_t, C.c_void_p, C.c_size_t, C.c_int, C.c_uint32,
+                           C.c_int, C.c_double, C.c_void_p, C.c_void_p],
+    "tpb_symm_rs_adamw": [C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p,
+                          C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_int, C.c_float,
+                          C.c_float, C.c_float, C.c_float, C.c_float, C.c_int, C.c_float, C.c_void_p,
+                          C.c_size_t, C.c_int, C.c_int, C.c_uint32, C.c_void_p, C.c_int, C.c_double,
+                          C.c_void_p, C.c_void_p],
+    "tpb_symm_wait_slots": [C.c_size_t, C.c_int, C.c_uint32, C.c_double, C.c_void_p, C.c_void_p],
+    "tpb_symm_barrier": [C.c_size_t, C.c_int, C.c_uint32, C.c_double, C.c_void_p, C.c_void_p],
+    "tpb_symm_peer_copy": [C.c_int, C.c_size_t, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p],
+}
+NO_OFFSET = C.c_size_t(-1).value
+
+
+class _DevMem:
+    """Exposes a raw device range through ``__cuda_array_interface__``."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False),
+                                         "version": 2, "strides": None}
+
+
+class SymmArena:
+    """Process-wide symmetric arena (one per process; collective to create)."""
+
+    _instance: Optional["SymmArena"] = None
+
+    def __init__(self, nbytes: int, group=None, pad_slots: int = 16384):
+        lib = _native.kernels()
+        raw = lib._lib
+        _native.register_sigs(raw, _SIGS)
+        raw.tpb_symm_alloc.argtypes = [C.c_size_t]
+        raw.tpb_symm_alloc.restype = C.c_size_t
+        raw.tpb_symm_ptr.argtypes = [C.c_int, C.c_size_t]
+        raw.tpb_symm_ptr.restype = C.c_void_p
+        self.lib = lib
+        self.raw = raw
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        handle = (C.c_char * 64)()
+        _native.check(raw.tpb_symm_create(self.world, self.rank, nbytes, handle), "tpb_symm_create")
+        if self.world > 1:
+            gathered = [None] * self.world
+            dist.all_gather_object(gathered, bytes(handle.raw), group=group)
+            blob = b"".join(gathered)
+            buf = (C.c_char * len(blob)).from_buffer_copy(blob)
+            _native.check(raw.tpb_symm_open(buf), "tpb_symm_open")
+        self.nbytes = nbytes
+        self._offsets: Dict[int, int] = {}
+        self.pad_slots = pad_slots
+        self.pad_off = self._alloc_bytes(pad_slots * 4)
+        self._next_slot = 0
+        self.counter = torch.zeros(64, dtype=torch.int32, device=self.device)
+        if self.world > 1:
+            dist.barrier(group=group)
+        SymmArena._instance = self
+
+    def _alloc_bytes(self, nbytes: int) -> int:
+        off = self.raw.tpb_symm_alloc(nbytes)
+        if off == NO_OFFSET:
+            raise MemoryError(f"symmetric arena exhausted (asked {nbytes} bytes of {self.nbytes})")
+        return off
+
+    def alloc(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        """Tensor backed by the arena at the same offset on every rank (call collectively)."""
+        nbytes = numel * torch.empty(0, dtype=dtype).element_size()
+        off = self._alloc_bytes(max(nbytes, 16))
+        ptr = self.raw.tpb_symm_ptr(self.rank, off)
+        t = torch.as_tensor(_DevMem(ptr, max(nbytes, 16)), device=self.device)[:nbytes].view(dtype)
+        self._offsets[t.data_ptr()] = off
+        return t
+
+    def offset_of(self, t: torch.Tensor) -> int:
+        """Arena offset of a tensor returned by ``alloc`` (or of a slice of one)."""
+        base = self.raw.tpb_symm_ptr(self.rank, 0)
+        off = t.data_ptr() - base
+        if off < 0 or off >= self.nbytes:
+            raise ValueError("tensor is not in the symmetric arena")
+        return off
+
+    def slots(self, n: int) -> int:
+        s = self._next_slot
+        if s + n > self.pad_slots:
+            raise MemoryError("out of signal slots")
+        self._next_slot += n
+        return s
+
+    def close(self) -> None:
+        self.raw.tpb_symm_destroy()
+        SymmArena._instance = None
+
+
+class SymmComm:
+    """The engine's communication backend on peer memory: all-gather by pulls and the fused
+    reduce-scatter + AdamW + bf16 parameter emit."""
+
+    def __init__(self, engine, wait_s: float = 30.0, gather_ctas: int = 4, reduce_ctas: int = 48):
+        self.engine = engine
+        self.world, self.rank = engine.world, engine.rank
+        units = engine.units
+        esz = torch.empty(0, dtype=engine.param_dtype).element_size()
+        max_padded = max(u.padded for u in units)
+        n_pool = (len(units) if not engine.checkpoint else 3) + 2
+        total = sum(u.shard_numel for u in units) * esz + n_pool * max_padded * esz
+        total += (len(units) + n_pool + 8) * 512 + (1 << 20)
+        self.arena = SymmArena(total, group=engine.group)
+        self.wait_s = wait_s
+        self.gather_ctas, self.reduce_ctas = gather_ctas, reduce_ctas
+        w = self.world
+        self.slot_gather = {u.index: self.arena.slots(w) for u in units}
+        self.slot_ready = {u.index: self.arena.slots(w) for u in units}
+        self.slot_done = {u.index: self.arena.slots(w) for u in units}
+        self.epoch_gather = {u.index: 0 for u in units}
+        self.epoch_reduce = {u.index: 0 for u in units}
+        self.grad_slot_last = {}  # grad pool slot -> (unit index, epoch) whose readers must finish
+        self.status = status_word(engine.device)
+
+    def alloc_shard(self, u) -> torch.Tensor:
+        t = self.arena.alloc(u.shard_numel, self.engine.param_dtype)
+        u._shard_off = self.arena.offset_of(t)
+        return t
+
+    def alloc_full(self, numel: int) -> torch.Tensor:
+        return self.arena.alloc(numel, self.engine.param_dtype)
+
+    def all_gather(self, u, buf: torch.Tensor) -> None:
+        self.epoch_gather[u.index] += 1
+        code = self.arena.raw.tpb_symm_allgather(
+            u._shard_off, u.shard_numel * buf.element_size(), buf.data_ptr(), self.arena.pad_off,
+            self.slot_gather[u.index], self.epoch_gather[u.index], self.gather_ctas, self.wait_s,
+            self.status.data_ptr(), stream_ptr())
+        _native.launch_count += 1
+        _native.check(code, "tpb_symm_allgather")
+
+    def reduce_scatter_adamw(self, u, g: torch.Tensor, adam: dict) -> None:
+        self.epoch_reduce[u.index] += 1
+        ep = self.epoch_reduce[u.index]
+        lo, hi = u.shard_range()
+        code = self.arena.raw.tpb_symm_rs_adamw(
+            self.arena.offset_of(g), lo, hi - lo, u.master.data_ptr(), u.exp_avg.data_ptr(),
+            u.exp_avg_sq.data_ptr(), u.shard.data_ptr(), NO_OFFSET, None, None, 0, adam["lr"],
+            adam["beta1"], adam["beta2"], adam["eps"], adam["weight_decay"], int(adam["step"]),
+            1.0 / self.world, None, self.arena.pad_off, self.slot_ready[u.index],
+            self.slot_done[u.index], ep, self.arena.counter[u.index % 64:].data_ptr(),
+            self.reduce_ctas, self.wait_s, self.status.data_ptr(), stream_ptr())
+        _native.launch_count += 1
+        _native.check(code, "tpb_symm_rs_adamw")
+        self.grad_slot_last[u._grad_slot] = (u.index, ep)
+
+    def before_grad_reuse(self, slot: int) -> None:
+        """Order the current stream after every peer's reads of gradient buffer ``slot``."""
+        last = self.grad_slot_last.get(slot)
+        if last is None:
+            return
+        uidx, ep = last
+        code = self.arena.raw.tpb_symm_wait_slots(self.arena.pad_off, self.slot_done[uidx], ep,
+                                                  self.wait_s, self.status.data_ptr(), stream_ptr())
+        _native.launch_count += 1
+        _native.check(code, "tpb_symm_wait_slots")
