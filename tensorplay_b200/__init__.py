@@ -1,0 +1,81 @@
+"""tensorplay_b200: a Blackwell-native deep-learning framework with the public API of TensorPlay.
+
+The framework layer is PyTorch (``Tensor`` is ``torch.Tensor``, autograd is torch's); the hot
+ops are hand-written sm_100a kernels (``tensorplay_b200.ops``), the parallel runtime
+(``tensorplay_b200.parallel`` and ``tensorplay_b200.distributed``) is built on NVLink peer memory
+with NCCL kept for point-to-point and as the baseline, and a plain-PyTorch CPU path is the
+correctness oracle. Top-level names follow tensorplay/__init__.py:270-760 of the reference: what
+coincides with torch semantics is re-exported, what the reference adds lives in this package.
+
+``import tensorplay_b200 as tp`` (or ``tensorplay_b200.compat.install_alias()`` to make
+``import tensorplay`` resolve here).
+"""
+from __future__ import annotations
+
+import importlib as _importlib
+import sys as _sys
+
+import torch as _torch
+
+__version__ = "0.1.0"
+
+# ---- everything torch exposes at top level (functions, dtypes, grad modes, ...)
+for _n in dir(_torch):
+    if _n.startswith("_"):
+        continue
+    globals()[_n] = getattr(_torch, _n)
+del _n
+
+Tensor = _torch.Tensor
+DType = _torch.dtype
+Device = _torch.device
+dtype = _torch.dtype
+device = _torch.device
+
+# ---- own subpackages (imported eagerly: they are light) and torch-backed ones (lazy)
+from . import ops  # noqa: E402
+from . import nn  # noqa: E402
+from . import optim  # noqa: E402
+from . import amp  # noqa: E402
+from . import serialization  # noqa: E402
+from .serialization import inspect_checkpoint, load, save  # noqa: E402
+from .nn.generation import sample  # noqa: E402
+
+_LAZY_OWN = {"distributed", "utils", "models", "parallel", "cuda", "profiler", "autograd", "compat",
+             "multiprocessing", "testing", "quantization", "metrics", "snn", "library"}
+_LAZY_TORCH = {"linalg", "fft", "special", "sparse", "distributions", "func", "futures", "hub", "onnx",
+               "masked", "nested", "monitor", "backends", "accelerator", "export", "fx", "random",
+               "signal", "overrides", "package", "storage", "types", "jit"}
+
+
+def __getattr__(name):
+    if name in _LAZY_OWN:
+        mod = _importlib.import_module(f"{__name__}.{name}")
+        globals()[name] = mod
+        return mod
+    if name in _LAZY_TORCH:
+        mod = _importlib.import_module(f"torch.{name}")
+        globals()[name] = mod
+        return mod
+    if name == "graph":
+        return _importlib.import_module("torch.fx")
+    return getattr(_torch, name)
+
+
+def compile(model=None, *, backend: str = "cuda_graph", **kwargs):
+    """``tensorplay.compile`` counterpart. There is no tracing compiler here by design: the hot
+    path is hand-written kernels. ``backend="cuda_graph"`` returns a callable that captures the
+    module's forward into a CUDA graph for static shapes (launch-bound inner loops);
+    ``backend="eager"`` returns the module unchanged."""
+    def wrap(m):
+        if backend == "eager" or not _torch.cuda.is_available():
+            return m
+        from .cuda.graphs import make_graphed_callable
+        return make_graphed_callable(m)
+    return wrap if model is None else wrap(model)
+
+
+def is_native_available() -> bool:
+    """True when the sm_100a kernel library is built and loadable."""
+    from . import _native
+    return _native.kernels_available()

@@ -53,10 +53,12 @@ class ParamUnit:
         self.index, self.name, self.params = index, name, params
         self.world, self.rank = world, rank
         self.offsets: List[int] = []
+        self.shapes = [tuple(p.shape) for _, p in params]
+        self.numels = [p.numel() for _, p in params]
         off = 0
-        for _, p in params:
+        for n in self.numels:
             self.offsets.append(off)
-            off += _round_up(p.numel(), 8)  # keep every view 16-byte aligned
+            off += _round_up(n, 8)  # keep every view 16-byte aligned
         self.numel = off
         self.padded = _round_up(max(off, 8), world * 128)
         self.shard_numel = self.padded // world
@@ -73,13 +75,13 @@ class ParamUnit:
 
     def bind_params(self, full: Tensor) -> None:
         self.full = full
-        for (_, p), off in zip(self.params, self.offsets):
-            p.data = full[off: off + p.numel()].view(p.shape)
+        for (_, p), off, n, shape in zip(self.params, self.offsets, self.numels, self.shapes):
+            p.data = full[off: off + n].view(shape)
 
     def bind_grads(self, grad: Optional[Tensor]) -> None:
         self.grad = grad
-        for (_, p), off in zip(self.params, self.offsets):
-            p._tpb_grad_view = None if grad is None else grad[off: off + p.numel()].view(p.shape)
+        for (_, p), off, n, shape in zip(self.params, self.offsets, self.numels, self.shapes):
+            p._tpb_grad_view = None if grad is None else grad[off: off + n].view(shape)
             p._tpb_grad_written = False
 
     def collect_autograd_grads(self) -> None:
@@ -208,8 +210,8 @@ class FSDPEngine:
             self.comm = None
         for u in self.units:
             init = torch.zeros(u.padded, dtype=dt, device=dev)
-            for (_, p), off in zip(u.params, u.offsets):
-                init[off: off + p.numel()].copy_(p.data.reshape(-1))
+            for (_, p), off, n in zip(u.params, u.offsets, u.numels):
+                init[off: off + n].copy_(p.data.reshape(-1))
             lo, hi = u.shard_range()
             u.master = init[lo:hi].float()
             u.exp_avg = torch.zeros(u.shard_numel, dtype=torch.float32, device=dev)
@@ -413,6 +415,6 @@ class FSDPEngine:
                 if self.cuda:
                     torch.cuda.synchronize()
                 dist.all_gather_into_tensor(full, u.master.contiguous(), group=self.group)
-            for (n, p), off in zip(u.params, u.offsets):
-                out[n] = full[off: off + p.numel()].view(p.shape).clone()
+            for (n, p), off, cnt, shape in zip(u.params, u.offsets, u.numels, u.shapes):
+                out[n] = full[off: off + cnt].view(shape).clone()
         return out
