@@ -95,9 +95,18 @@ allgather_pull_kernel(PeerPtrs shards, char* __restrict__ out, size_t shard_byte
   const size_t bid = blockIdx.x % per_rank_blocks;
   const uint4* src = reinterpret_cast<const uint4*>(shards.p[r]);
   uint4* dst = reinterpret_cast<uint4*>(out + (size_t)r * shard_bytes);
-  for (size_t i = bid * blockDim.x + threadIdx.x; i < nvec; i += per_rank_blocks * blockDim.x) {
-    dst[i] = ld_relaxed_sys_v4(src + i);
+  // NVLink latency is microseconds: keep kUnroll independent 16-byte loads in flight per thread
+  constexpr int kUnroll = 8;
+  const size_t stride = per_rank_blocks * blockDim.x;
+  size_t i = bid * blockDim.x + threadIdx.x;
+  for (; i + (kUnroll - 1) * stride < nvec; i += kUnroll * stride) {
+    uint4 v[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) v[u] = ld_relaxed_sys_v4(src + i + u * stride);
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) dst[i + u * stride] = v[u];
   }
+  for (; i < nvec; i += stride) dst[i] = ld_relaxed_sys_v4(src + i);
 }
 
 // ---------------------------------------------------------------- reduce-scatter + AdamW
@@ -134,15 +143,28 @@ rs_adamw_kernel(PeerPtrs grads, size_t lo, size_t n, float* __restrict__ master,
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    for (int r = 0; r < s.world; ++r) {
-      const uint4* src = reinterpret_cast<const uint4*>(grads.p[r]) + lo / 8 + i;
-      uint4 raw = (r == s.rank) ? *src : ld_relaxed_sys_v4(src);
-      const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    // loads of up to four ranks are issued together, then summed in rank order (deterministic)
+    for (int r0 = 0; r0 < s.world; r0 += 4) {
+      uint4 raw[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float2 f = __bfloat1622float2(hb[j]);
-        acc[2 * j] += f.x;
-        acc[2 * j + 1] += f.y;
+      for (int u = 0; u < 4; ++u) {
+        const int r = r0 + u;
+        if (r < s.world) {
+          const uint4* src = reinterpret_cast<const uint4*>(grads.p[r]) + lo / 8 + i;
+          raw[u] = (r == s.rank) ? *src : ld_relaxed_sys_v4(src);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (r0 + u < s.world) {
+          const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float2 f = __bfloat1622float2(hb[j]);
+            acc[2 * j] += f.x;
+            acc[2 * j + 1] += f.y;
+          }
+        }
       }
     }
 #pragma unroll

@@ -119,7 +119,7 @@ class SymmComm:
     """The engine's communication backend on peer memory: all-gather by pulls and the fused
     reduce-scatter + AdamW + bf16 parameter emit."""
 
-    def __init__(self, engine, wait_s: float = 30.0, gather_ctas: int = 4, reduce_ctas: int = 48):
+    def __init__(self, engine, wait_s: float = 30.0, gather_ctas: int = 24, reduce_ctas: int = 148):
         self.engine = engine
         self.world, self.rank = engine.world, engine.rank
         units = engine.units
