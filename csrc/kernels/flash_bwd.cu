@@ -26,6 +26,7 @@ int make_tmap_bthd(CUtensorMap* out, const void* base, int B, int T, int H, int 
 constexpr int kBwdThreads = 192;
 constexpr int kStat = 128;   // rows of the stationary tiles
 constexpr int kStream = 64;  // rows of the streamed tiles
+constexpr int kYStages = 3;  // streamed-tile ring: loads run two tiles ahead of the MMAs
 
 struct AttnBwdParams {
   int B, Tq, Tk, Hq, Hkv;
@@ -55,8 +56,8 @@ struct BwdSmem {
   static constexpr int kPBytes = kStat * kStream * 2;   // P / dS tile (128 x 64 bf16)
   static constexpr int kX0 = 0;
   static constexpr int kX1 = kX0 + kStatBytes;
-  static constexpr int kY = kX1 + kStatBytes;  // 2 stages x (Y0, Y1)
-  static constexpr int kP = kY + 4 * kStreamBytes;
+  static constexpr int kY = kX1 + kStatBytes;  // kYStages x (Y0, Y1)
+  static constexpr int kP = kY + 2 * kYStages * kStreamBytes;
   static constexpr int kDS = kP + kPBytes;
   static constexpr int kBar = kDS + kPBytes;
   static constexpr int kTotal = kBar + 256 + 1024;
@@ -92,14 +93,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBar);
-  uint64_t* x_full = bars;           // 1
-  uint64_t* y_full = bars + 1;       // 2
-  uint64_t* y_empty = bars + 3;      // 2
-  uint64_t* sdp_full = bars + 5;     // 2
-  uint64_t* sdp_empty = bars + 7;    // 2 (128 arrivals)
-  uint64_t* pds_full = bars + 9;     // 1 (128 arrivals)
-  uint64_t* acc_done = bars + 10;    // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* x_full = bars;                        // 1
+  uint64_t* y_full = bars + 1;                    // kYStages
+  uint64_t* y_empty = y_full + kYStages;          // kYStages
+  uint64_t* sdp_full = y_empty + kYStages;        // 2
+  uint64_t* sdp_empty = sdp_full + 2;             // 2 (128 arrivals)
+  uint64_t* pds_full = sdp_empty + 2;             // 1 (128 arrivals)
+  uint64_t* acc_done = pds_full + 1;              // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
   volatile uint32_t* abort_w = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -135,9 +136,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
   if (threadIdx.x == 0) {
     *abort_w = 0;
     mbar_init(x_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kYStages; ++i) {
       mbar_init(&y_full[i], 1);
       mbar_init(&y_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&sdp_full[i], 1);
       mbar_init(&sdp_empty[i], 128);
     }
@@ -172,8 +175,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
         tma_load_4d(smem + L::kX1 + c * (kStat * 128), &tmX1, x_full, c * 64, hx, x0, b);
       }
       for (int it = 0; it < n_it; ++it) {
-        const int s = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
+        const int s = it % kYStages;
+        const uint32_t ph = (it / kYStages) & 1;
         if (!mbar_wait(&y_empty[s], ph ^ 1, wc, 1)) break;
         int hy, yb;
         if (DKV) { hy = hx * G + it / y_count; yb = y_first + it % y_count; }
@@ -198,12 +201,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
       const uint32_t p_s = smem_u32(smem + L::kP);
       const uint32_t ds_s = smem_u32(smem + L::kDS);
       auto issue_sdp = [&](int it) -> bool {
+        const int ys = it % kYStages;
+        const uint32_t yph = (it / kYStages) & 1;
         const int s = it & 1;
         const uint32_t ph = (it >> 1) & 1;
-        if (!mbar_wait(&y_full[s], ph, wc, 2)) return false;
+        if (!mbar_wait(&y_full[ys], yph, wc, 2)) return false;
         if (!mbar_wait(&sdp_empty[s], ph ^ 1, wc, 3)) return false;
         tc_fence_after_sync();
-        const uint32_t y0_s = smem_u32(smem + L::kY + s * 2 * L::kStreamBytes);
+        const uint32_t y0_s = smem_u32(smem + L::kY + ys * 2 * L::kStreamBytes);
         const uint32_t y1_s = y0_s + L::kStreamBytes;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
@@ -228,7 +233,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
         if (it + 1 < n_it) {
           if (!issue_sdp(it + 1)) break;
         }
-        const int s = it & 1;
+        const int s = it % kYStages;
         if (!mbar_wait(pds_full, it & 1, wc, 5)) break;
         tc_fence_after_sync();
         const uint32_t y0_s = smem_u32(smem + L::kY + s * 2 * L::kStreamBytes);

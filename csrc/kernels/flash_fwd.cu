@@ -49,9 +49,10 @@ struct AttnSmem {
   static constexpr int kKBytes = kBlockKV * D * 2;
   static constexpr int kPBytes = kBlockQ * kBlockKV * 2;
   static constexpr int kQOff = 0;
+  // K and V tiles share one ring (K0 V0 K1 V1 ...): the loads run up to kRing tiles ahead
+  static constexpr int kRing = D == 128 ? 5 : 6;
   static constexpr int kKOff = kQOff + kQBytes;
-  static constexpr int kVOff = kKOff + 2 * kKBytes;
-  static constexpr int kPOff = kVOff + 2 * kKBytes;
+  static constexpr int kPOff = kKOff + kRing * kKBytes;
   static constexpr int kBarOff = kPOff + kPBytes;
   static constexpr int kTotal = kBarOff + 256 + 1024;
 };
@@ -65,16 +66,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
-  uint64_t* q_full = bars;          // 1
-  uint64_t* k_full = bars + 1;      // 2
-  uint64_t* k_empty = bars + 3;     // 2
-  uint64_t* v_full = bars + 5;      // 2
-  uint64_t* v_empty = bars + 7;     // 2
-  uint64_t* s_full = bars + 9;      // 2
-  uint64_t* s_empty = bars + 11;    // 2 (128 arrivals)
-  uint64_t* p_full = bars + 13;     // 1 (128 arrivals)
-  uint64_t* pv_done = bars + 14;    // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  constexpr int R = L::kRing;
+  uint64_t* q_full = bars;              // 1
+  uint64_t* kv_full = bars + 1;         // R
+  uint64_t* kv_empty = kv_full + R;     // R
+  uint64_t* s_full = kv_empty + R;      // 2
+  uint64_t* s_empty = s_full + 2;       // 2 (128 arrivals)
+  uint64_t* p_full = s_empty + 2;       // 1 (128 arrivals)
+  uint64_t* pv_done = p_full + 1;       // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
   volatile uint32_t* abort_w = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -95,11 +95,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (threadIdx.x == 0) {
     *abort_w = 0;
     mbar_init(q_full, 1);
+    for (int i = 0; i < R; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+    }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&k_full[i], 1);
-      mbar_init(&k_empty[i], 1);
-      mbar_init(&v_full[i], 1);
-      mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&s_empty[i], 128);
     }
@@ -127,20 +127,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
       for (int c = 0; c < L::kChunks; ++c)
         tma_load_4d(smem + L::kQOff + c * (kBlockQ * 128), &tmQ, q_full, c * 64, h, q0, b);
-      for (int j = 0; j < nkv; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&k_empty[s], ph ^ 1, wc, 1)) break;
-        mbar_arrive_expect_tx(&k_full[s], L::kKBytes);
+      for (int t = 0; t < 2 * nkv; ++t) {
+        const int j = t >> 1;
+        const int slot = t % R;
+        const uint32_t ph = (t / R) & 1;
+        if (!mbar_wait(&kv_empty[slot], ph ^ 1, wc, 1)) break;
+        mbar_arrive_expect_tx(&kv_full[slot], L::kKBytes);
+        const CUtensorMap* tm = (t & 1) ? &tmV : &tmK;
 #pragma unroll
         for (int c = 0; c < L::kChunks; ++c)
-          tma_load_4d(smem + L::kKOff + s * L::kKBytes + c * (kBlockKV * 128), &tmK, &k_full[s],
-                      c * 64, hk, j * kBlockKV, b);
-        if (!mbar_wait(&v_empty[s], ph ^ 1, wc, 2)) break;
-        mbar_arrive_expect_tx(&v_full[s], L::kKBytes);
-#pragma unroll
-        for (int c = 0; c < L::kChunks; ++c)
-          tma_load_4d(smem + L::kVOff + s * L::kKBytes + c * (kBlockKV * 128), &tmV, &v_full[s],
+          tma_load_4d(smem + L::kKOff + slot * L::kKBytes + c * (kBlockKV * 128), tm, &kv_full[slot],
                       c * 64, hk, j * kBlockKV, b);
       }
     }
@@ -153,10 +149,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       auto issue_s = [&](int j) -> bool {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&k_full[s], ph, wc, 3)) return false;
+        const int slot = (2 * j) % R;
+        const uint32_t kph = ((2 * j) / R) & 1;
+        if (!mbar_wait(&kv_full[slot], kph, wc, 3)) return false;
         if (!mbar_wait(&s_empty[s], ph ^ 1, wc, 4)) return false;
         tc_fence_after_sync();
-        const uint32_t k_s = smem_u32(smem + L::kKOff + s * L::kKBytes);
+        const uint32_t k_s = smem_u32(smem + L::kKOff + slot * L::kKBytes);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * (kBlockQ * 128) + (kk % 4) * 32;
@@ -164,7 +162,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                       make_smem_desc_sw128(k_s + off, 16, 1024), idesc_s, kk != 0);
         }
         umma_commit(&s_full[s]);
-        umma_commit(&k_empty[s]);
+        umma_commit(&kv_empty[slot]);
         return true;
       };
       bool ok = mbar_wait(q_full, 0, wc, 5);
@@ -173,12 +171,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (j + 1 < nkv) {
           if (!issue_s(j + 1)) break;
         }
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
+        const int slot = (2 * j + 1) % R;
+        const uint32_t vph = ((2 * j + 1) / R) & 1;
         if (!mbar_wait(p_full, j & 1, wc, 6)) break;
-        if (!mbar_wait(&v_full[s], ph, wc, 7)) break;
+        if (!mbar_wait(&kv_full[slot], vph, wc, 7)) break;
         tc_fence_after_sync();
-        const uint32_t v_s = smem_u32(smem + L::kVOff + s * L::kKBytes);
+        const uint32_t v_s = smem_u32(smem + L::kKOff + slot * L::kKBytes);
 #pragma unroll
         for (int kk = 0; kk < kBlockKV / 16; ++kk) {
           const uint32_t poff = (kk / 4) * (kBlockQ * 128) + (kk % 4) * 32;
@@ -187,7 +185,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                       (j | kk) != 0);
         }
         umma_commit(pv_done);
-        umma_commit(&v_empty[s]);
+        umma_commit(&kv_empty[slot]);
       }
     }
   } else {

@@ -169,6 +169,19 @@ rs_adamw_kernel(PeerPtrs grads, size_t lo, size_t n, float* __restrict__ master,
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] *= gs;
+    if (mode == 2) {
+      // plain all-reduce: the averaged bf16 slice goes into every rank's buffer at bcast_off
+      uint4 o2;
+      __nv_bfloat162* ob2 = reinterpret_cast<__nv_bfloat162*>(&o2);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) ob2[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+      for (int r = 0; r < s.world; ++r) {
+        int rr = (s.rank + r) % s.world;
+        uint4* dst = reinterpret_cast<uint4*>(const_cast<char*>(bcast_out.p[rr]) + bcast_off) + lo / 8 + i;
+        *dst = o2;
+      }
+      continue;
+    }
     if (mode == 1) {
       float4* ro = reinterpret_cast<float4*>(red_out) + 2 * i;
       ro[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
@@ -356,6 +369,8 @@ extern "C" int tpb_symm_allgather(size_t shard_off, size_t shard_bytes, void* ou
 //           (local pointer, may be null); if bcast_off != (size_t)-1 also write the bf16 values
 //           into every rank's buffer at arena offset bcast_off (+ lo): all-reduce/DDP form.
 //   mode 1: write the reduced, scaled fp32 gradient to red_out and add its squares to sumsq.
+//   mode 2: all-reduce: write the reduced, scaled bf16 values into every rank's buffer at
+//           arena offset bcast_off (may equal grad_off: in place).
 // ready_slot / done_slot: `world` flag slots each.
 extern "C" int tpb_symm_rs_adamw(size_t grad_off, size_t lo, size_t n, float* master, float* m,
                                  float* v, void* shard_out, size_t bcast_off, float* red_out,

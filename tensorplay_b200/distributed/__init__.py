@@ -1,0 +1,40 @@
+"""``distributed``: process groups and collectives (torch.distributed over gloo / NCCL for the
+plumbing), stores, device meshes, DDP, FSDP, pipeline and tensor parallelism, expert parallelism,
+distributed checkpointing, the elastic launcher and observability - the surface of
+tensorplay/distributed (distributed_core.py:24-104 lists the collective API; names coincide).
+
+The fused compute+collective kernels live in ``tensorplay_b200.parallel``; the wrappers here
+route to them on CUDA and to plain collectives on CPU ranks.
+"""
+from __future__ import annotations
+
+import torch.distributed as _td
+from torch.distributed import *  # noqa: F401,F403
+from torch.distributed import (Backend, GroupMember, P2POp, ProcessGroup, ReduceOp, Work, all_gather,  # noqa: F401
+                               all_gather_into_tensor, all_gather_object, all_reduce, all_to_all,
+                               all_to_all_single, barrier, batch_isend_irecv, broadcast,
+                               broadcast_object_list, destroy_process_group, gather, get_backend,
+                               get_rank, get_world_size, init_process_group, irecv, is_available,
+                               is_initialized, isend, monitored_barrier, new_group, recv, reduce,
+                               reduce_scatter, reduce_scatter_tensor, scatter, send)
+
+from . import store  # noqa: F401
+from .store import FileStore, HashStore, PrefixStore, StoreTimeoutError, TCPStore  # noqa: F401
+
+# reference spellings of the single-tensor collectives
+all_gather_single = all_gather_into_tensor
+reduce_scatter_single = reduce_scatter_tensor
+
+_LAZY = {"ddp", "fsdp", "device_mesh", "pipelining", "tensor", "checkpoint", "elastic", "run", "launcher",
+         "flight_recorder", "watchdog", "_symmetric_memory", "_token_switch", "algorithms", "optim",
+         "rendezvous", "debug"}
+
+
+def __getattr__(name):
+    import importlib
+    if name in _LAZY:
+        return importlib.import_module(f"{__name__}.{name}")
+    if name in ("DeviceMesh", "init_device_mesh"):
+        from . import device_mesh
+        return getattr(device_mesh, name)
+    return getattr(_td, name)

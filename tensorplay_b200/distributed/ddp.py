@@ -1,0 +1,267 @@
+"""DistributedDataParallel with a bucketed reducer overlapped with backward.
+
+Gradients live as views of flat 25 MiB buckets (built in reverse parameter order, the order
+backward produces them); a post-accumulate hook counts a bucket's parameters down and launches
+its reduction on a communication stream as soon as the bucket is complete. Three reduction paths:
+
+* ``torch`` collectives (gloo / NCCL all-reduce) - the baseline and the CPU path;
+* ``symm``: in-place all-reduce over peer memory (each rank reduces its slice of the bucket in
+  fp32 and stores the bf16 result into every peer's bucket);
+* ``symm`` + ``fused_adamw``: the same kernel also applies AdamW to the slice it owns and
+  broadcasts the new bf16 parameters into every rank's parameter bucket, so that
+  ``optimizer.step()`` disappears (ZeRO-1 style sharded optimizer state).
+
+Replaces the reference's C++ ``DDPReducer`` (src/bindings/python/Distributed.cpp:33-247:
+eager copy-in, in-order flush, ncclAllReduce on a pooled stream) and its Python wrapper
+(tensorplay/nn/parallel/distributed.py:265-400, ``no_sync`` :824-836).
+"""
+from __future__ import annotations
+
+import contextlib
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from ..parallel.engine import AdamWConfig
+from .. import ops
+
+
+class _Bucket:
+    def __init__(self, index: int, params: List[nn.Parameter], flat_grad: torch.Tensor,
+                 flat_param: Optional[torch.Tensor]):
+        self.index, self.params = index, params
+        self.flat_grad, self.flat_param = flat_grad, flat_param
+        self.pending = len(params)
+        self.event = None
+
+
+class GradBucket:
+    """What a communication hook receives (tensorplay/distributed/distributed_core.py:3325-3358)."""
+
+    def __init__(self, b: _Bucket, last: bool):
+        self._b, self._last = b, last
+
+    def index(self): return self._b.index
+    def buffer(self): return self._b.flat_grad
+    def set_buffer(self, t): self._b.flat_grad.copy_(t)
+    def gradients(self): return [p.grad for p in self._b.params]
+    def parameters(self): return self._b.params
+    def is_last(self): return self._last
+
+
+class DistributedDataParallel(nn.Module):
+    def __init__(self, module: nn.Module, device_ids=None, output_device=None, dim: int = 0,
+                 broadcast_buffers: bool = True, process_group=None, bucket_cap_mb: float = 25.0,
+                 find_unused_parameters: bool = False, gradient_as_bucket_view: bool = True,
+                 static_graph: bool = False, comm: str = "auto",
+                 fused_adamw: Optional[AdamWConfig] = None):
+        super().__init__()
+        self.module = module
+        self.process_group = process_group
+        self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(process_group) if dist.is_initialized() else 0
+        self.broadcast_buffers = broadcast_buffers
+        self.find_unused_parameters = find_unused_parameters
+        self.require_backward_grad_sync = True
+        self._hook = None
+        self._hook_state = None
+        params = [p for p in module.parameters() if p.requires_grad]
+        self.device = params[0].device
+        self.cuda = self.device.type == "cuda"
+        if comm == "auto":
+            comm = "symm" if (self.cuda and self.world > 1 and params[0].dtype == torch.bfloat16) else "torch"
+        self.comm_kind = comm
+        self.fused = fused_adamw
+        if self.fused is not None and comm != "symm" and self.world > 1:
+            raise ValueError("fused_adamw needs the symmetric-memory path (bf16 parameters on CUDA)")
+        self._sync_module_states()
+        self._build_buckets(params, int(bucket_cap_mb * 1024 * 1024))
+        self.comm_stream = torch.cuda.Stream(device=self.device) if self.cuda else None
+        self.step_count = 0
+        self._accum = False
+        for p in params:
+            p.register_post_accumulate_grad_hook(self._make_hook(p))
+
+    # ---------------------------------------------------------------- construction
+    def _sync_module_states(self) -> None:
+        if self.world == 1:
+            return
+        with torch.no_grad():
+            for t in list(self.module.parameters()) + list(self.module.buffers()):
+                dist.broadcast(t.data, src=dist.get_global_rank(self.process_group, 0) if self.process_group else 0,
+                               group=self.process_group)
+
+    def _build_buckets(self, params, cap_bytes) -> None:
+        groups, cur, size = [], [], 0
+        for p in reversed(params):
+            nb = p.numel() * p.element_size()
+            if cur and (size + nb > cap_bytes or p.dtype != cur[0].dtype):
+                groups.append(cur)
+                cur, size = [], 0
+            cur.append(p)
+            size += nb
+        if cur:
+            groups.append(cur)
+        arena = None
+        if self.comm_kind == "symm":
+            from ..parallel.symm import SymmArena
+            esz = params[0].element_size()
+            total = sum(((sum((p.numel() + 7) // 8 * 8 for p in g) + self.world * 128 - 1) // (self.world * 128)) * self.world * 128
+                        for g in groups) * esz * 2 + (1 << 22)
+            arena = SymmArena._instance or SymmArena(total + (8 << 20), group=self.process_group)
+        self.arena = arena
+        self.buckets: List[_Bucket] = []
+        self._bucket_of = {}
+        for gi, g in enumerate(groups):
+            offs, off = [], 0
+            for p in g:
+                offs.append(off)
+                off += (p.numel() + 7) // 8 * 8
+            padded = (off + self.world * 128 - 1) // (self.world * 128) * (self.world * 128)
+            if arena is not None:
+                fg = arena.alloc(padded, g[0].dtype)
+                fp = arena.alloc(padded, g[0].dtype)
+                fg.zero_()
+            else:
+                fg = torch.zeros(padded, dtype=g[0].dtype, device=self.device)
+                fp = None
+            b = _Bucket(gi, g, fg, fp)
+            b.offsets, b.padded = offs, padded
+            b.offset_of = {id(p): o for p, o in zip(g, offs)}
+            for p, o in zip(g, offs):
+                if fp is not None:
+                    fp[o: o + p.numel()].copy_(p.data.reshape(-1))
+                    p.data = fp[o: o + p.numel()].view(p.shape)
+                p.grad = fg[o: o + p.numel()].view(p.shape)
+                self._bucket_of[id(p)] = b
+            if arena is not None:
+                w = self.world
+                b.slot_ready, b.slot_done = arena.slots(w), arena.slots(w)
+                b.epoch = 0
+                if self.fused is not None:
+                    shard = padded // w
+                    lo = self.rank * shard
+                    b.master = fp[lo: lo + shard].float()
+                    b.exp_avg = torch.zeros(shard, dtype=torch.float32, device=self.device)
+                    b.exp_avg_sq = torch.zeros(shard, dtype=torch.float32, device=self.device)
+            self.buckets.append(b)
+
+    # ---------------------------------------------------------------- reduction
+    def _make_hook(self, p):
+        def hook(param):
+            if not self.require_backward_grad_sync or self.world == 1 and self.fused is None:
+                return
+            b = self._bucket_of[id(param)]
+            o = b.offset_of[id(param)]
+            v = b.flat_grad[o: o + param.numel()]
+            if param.grad.data_ptr() != v.data_ptr():
+                v.copy_(param.grad.reshape(-1))
+                param.grad = v.view(param.shape)
+            b.pending -= 1
+            if b.pending == 0:
+                self._reduce(b)
+        return hook
+
+    def _reduce(self, b: _Bucket) -> None:
+        last = b.index == len(self.buckets) - 1
+        if self._hook is not None:
+            fut = self._hook(self._hook_state, GradBucket(b, last))
+            out = fut.wait() if hasattr(fut, "wait") else fut
+            out = out[0] if isinstance(out, (list, tuple)) else out
+            if out is not None and out.data_ptr() != b.flat_grad.data_ptr():
+                b.flat_grad.copy_(out)
+            b.pending = len(b.params)
+            return
+        if self.cuda:
+            self.comm_stream.wait_stream(torch.cuda.current_stream())
+            ctx = torch.cuda.stream(self.comm_stream)
+        else:
+            ctx = contextlib.nullcontext()
+        with ctx:
+            if self.comm_kind == "symm" and self.world >= 1 and self.arena is not None:
+                self._reduce_symm(b)
+            elif self.world > 1:
+                if b.flat_grad.dtype == torch.float32 or dist.get_backend(self.process_group) == "gloo":
+                    dist.all_reduce(b.flat_grad, group=self.process_group)
+                    b.flat_grad.div_(self.world)
+                else:
+                    dist.all_reduce(b.flat_grad, op=dist.ReduceOp.AVG, group=self.process_group)
+            if self.cuda:
+                b.event = torch.cuda.Event()
+                b.event.record(self.comm_stream)
+        b.pending = len(b.params)
+
+    def _reduce_symm(self, b: _Bucket) -> None:
+        from .. import _native
+        from ..ops._common import status_word, stream_ptr
+        from ..parallel.symm import NO_OFFSET
+        a = self.arena
+        b.epoch += 1
+        shard = b.padded // self.world
+        lo = self.rank * shard
+        goff = a.offset_of(b.flat_grad)
+        st = status_word(self.device)
+        if self.fused is not None:
+            c = self.fused
+            code = a.raw.tpb_symm_rs_adamw(
+                goff, lo, shard, b.master.data_ptr(), b.exp_avg.data_ptr(), b.exp_avg_sq.data_ptr(), None,
+                a.offset_of(b.flat_param), None, None, 0, c.lr, c.betas[0], c.betas[1], c.eps, c.weight_decay,
+                self.step_count + 1, 1.0 / self.world, None, a.pad_off, b.slot_ready, b.slot_done, b.epoch,
+                a.counter[b.index % 64:].data_ptr(), 64, 30.0, st.data_ptr(), stream_ptr())
+        else:
+            code = a.raw.tpb_symm_rs_adamw(
+                goff, lo, shard, None, None, None, None, goff, None, None, 2, 0.0, 0.0, 0.0, 0.0, 0.0, 1,
+                1.0 / self.world, None, a.pad_off, b.slot_ready, b.slot_done, b.epoch,
+                a.counter[b.index % 64:].data_ptr(), 64, 30.0, st.data_ptr(), stream_ptr())
+        _native.launch_count += 1
+        _native.check(code, "tpb_symm_rs_adamw")
+        # every rank's slice must have landed before this rank reads the bucket again
+        code = a.raw.tpb_symm_wait_slots(a.pad_off, b.slot_done, b.epoch, 30.0, st.data_ptr(), stream_ptr())
+        _native.launch_count += 1
+        _native.check(code, "tpb_symm_wait_slots")
+
+    # ---------------------------------------------------------------- module API
+    def forward(self, *args, **kwargs):
+        if self.cuda:
+            for b in self.buckets:
+                if b.event is not None:
+                    torch.cuda.current_stream().wait_event(b.event)
+        if self.broadcast_buffers and self.world > 1 and self.require_backward_grad_sync:
+            for buf in self.module.buffers():
+                dist.broadcast(buf, src=0, group=self.process_group)
+        return self.module(*args, **kwargs)
+
+    def finish_step(self) -> None:
+        """With ``fused_adamw``: call after ``backward`` instead of ``optimizer.step()`` +
+        ``zero_grad()``. Orders the main stream after the reductions and clears the buckets."""
+        if self.cuda:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+        self.step_count += 1
+        for b in self.buckets:
+            b.flat_grad.zero_()
+
+    def synchronize(self) -> None:
+        """Order the current stream after all outstanding bucket reductions."""
+        if self.cuda:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+
+    @contextlib.contextmanager
+    def no_sync(self):
+        old = self.require_backward_grad_sync
+        self.require_backward_grad_sync = False
+        try:
+            yield
+        finally:
+            self.require_backward_grad_sync = old
+
+    def register_comm_hook(self, state, hook) -> None:
+        """``hook(state, bucket: GradBucket) -> Future[Tensor] | Tensor``."""
+        self._hook_state, self._hook = state, hook
+
+    def state_dict(self, *a, **kw):
+        return self.module.state_dict(*a, **kw)
+
+    def load_state_dict(self, *a, **kw):
+        return self.module.load_state_dict(*a, **kw)
