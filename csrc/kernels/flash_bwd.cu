@@ -59,7 +59,8 @@ struct BwdSmem {
   static constexpr int kY = kX1 + kStatBytes;  // kYStages x (Y0, Y1)
   static constexpr int kP = kY + 2 * kYStages * kStreamBytes;
   static constexpr int kDS = kP + kPBytes;
-  static constexpr int kBar = kDS + kPBytes;
+  static constexpr int kStats = kDS + kPBytes;  // per Y stage: lse[64] then delta[64] (fp32)
+  static constexpr int kBar = kStats + kYStages * 2 * kStream * 4;
   static constexpr int kTotal = kBar + 256 + 1024;
 };
 
@@ -183,7 +184,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
         else { hy = hx / G; yb = it; }
         uint8_t* y0 = smem + L::kY + s * 2 * L::kStreamBytes;
         uint8_t* y1 = y0 + L::kStreamBytes;
-        mbar_arrive_expect_tx(&y_full[s], 2 * L::kStreamBytes);
+        mbar_arrive_expect_tx(&y_full[s], 2 * L::kStreamBytes + (DKV ? 2 * kStream * 4 : 0));
+        if (DKV) {
+          // the per-query statistics of the streamed tile ride along with it
+          const long long so = ((long long)b * p.Hq + hy) * p.lse_stride + (long long)yb * kStream;
+          float* st = reinterpret_cast<float*>(smem + L::kStats) + s * 2 * kStream;
+          bulk_load_1d(st, p.lse + so, kStream * 4, &y_full[s]);
+          bulk_load_1d(st + kStream, p.delta + so, kStream * 4, &y_full[s]);
+        }
 #pragma unroll
         for (int c = 0; c < L::kChunks; ++c) {
           tma_load_4d(y0 + c * (kStream * 128), &tmY0, &y_full[s], c * 64, hy, yb * kStream, b);
@@ -293,9 +301,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
       const float* lse_col = nullptr;
       const float* delta_col = nullptr;
       if (DKV) {
-        long long o = ((long long)b * p.Hq + hy) * p.lse_stride + y0i;
-        lse_col = p.lse + o;
-        delta_col = p.delta + o;
+        // statistics landed with the tile (the wait below returns at once and orders the read)
+        const int ys = it % kYStages;
+        if (!mbar_wait_warp(&y_full[ys], (it / kYStages) & 1, wc, 9)) { ok = false; break; }
+        lse_col = reinterpret_cast<const float*>(smem + L::kStats) + ys * 2 * kStream;
+        delta_col = lse_col + kStream;
       }
 #pragma unroll
       for (int c = 0; c < 64; c += 4) {

@@ -14,6 +14,7 @@
 #include "tpb_api.h"
 
 #include <mutex>
+#include <string.h>
 
 namespace tpb {
 
@@ -49,6 +50,31 @@ struct GemmParams {
   const uint32_t* b_flags;
   int rows_per_flag;
   uint32_t flag_want;
+  // ---- fused all-gather of one operand (ag_operand: 0 none, 1 = A rows, 2 = B rows). The
+  // first n_copy blocks of the grid are copy CTAs: they pull the peers' row shards into the
+  // local gathered buffer chunk by chunk and publish one flag per chunk; the GEMM producer
+  // waits for the flags of the rows a tile needs (own-rank rows need no wait).
+  int n_copy, ag_operand;
+  int world, rank;
+  const char* ag_src[16];   // ag_src[r]: rank r's shard inside rank r's gathered buffer
+  char* ag_dst;             // local gathered buffer
+  unsigned long long ag_shard_bytes, ag_chunk_bytes;
+  int ag_rows_per_rank, ag_rows_per_flag;
+  uint32_t* ag_flags;       // local, one per chunk of every rank's shard
+  uint32_t* pad_local;      // signal pad: [ready_slot + r] = rank r's shard is valid at epoch
+  uint32_t* pad_peer[16];
+  int ready_slot, done_slot;
+  uint32_t epoch;
+  int tile_m_shift;         // rotate M tiles so that locally available rows are computed first
+  // ---- fused reduce-scatter epilogue (rs_mode = 1): row block d of the product belongs to
+  // rank d; tiles are stored (bf16) into rank d's staging slice [rank][rows_per_rank, N] and a
+  // per-source counter on rank d is bumped; after its tiles every CTA helps reducing the slices
+  // that arrived for this rank into rs_out.
+  int rs_mode, rs_rows_per_rank;
+  char* rs_stage[16];       // staging buffer base on every rank
+  uint32_t* rs_cnt[16];     // counters on every rank ([src] = tile-quarters received from src)
+  uint32_t rs_expect;       // counter value that means "all tiles of this launch arrived"
+  __nv_bfloat16* rs_out;    // local [rows_per_rank, N]
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
@@ -59,6 +85,121 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   int r = tile - g * per_group;
   tm = first_m + (r % gsize);
   tn = r / gsize;
+}
+
+
+__device__ __forceinline__ uint4 ld_peer_v4(const void* ptr) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(ptr)
+               : "memory");
+  return v;
+}
+
+// Copy CTAs of the fused all-gather: chunk c of peer (rank + 1 + c / chunks_per_rank).
+__device__ void ag_copy_role(const GemmParams& p) {
+  // publish "my shard is valid" to every peer, once
+  if (blockIdx.x == 0 && threadIdx.x < p.world) {
+    __threadfence_system();
+    st_release_sys(p.pad_peer[threadIdx.x] + p.ready_slot + p.rank, p.epoch);
+  }
+  const int cpr = (int)((p.ag_shard_bytes + p.ag_chunk_bytes - 1) / p.ag_chunk_bytes);
+  const int total = cpr * (p.world - 1);
+  __shared__ int ok_sh;
+  for (int c = blockIdx.x; c < total; c += p.n_copy) {
+    const int pr = c / cpr, ci = c % cpr;
+    const int r = (p.rank + 1 + pr) % p.world;
+    if (threadIdx.x == 0)
+      ok_sh = flag_wait_ge(p.pad_local + p.ready_slot + r, p.epoch, true, p.status, p.wait_ns, 11) ? 1 : 0;
+    __syncthreads();
+    if (!ok_sh) return;
+    const unsigned long long off = (unsigned long long)ci * p.ag_chunk_bytes;
+    const unsigned long long nbytes = min(p.ag_chunk_bytes, p.ag_shard_bytes - off);
+    const uint4* src = reinterpret_cast<const uint4*>(p.ag_src[r] + off);
+    uint4* dst = reinterpret_cast<uint4*>(p.ag_dst + (unsigned long long)r * p.ag_shard_bytes + off);
+    const unsigned long long nvec = nbytes / 16;
+    constexpr int U = 8;
+    unsigned long long i = threadIdx.x;
+    for (; i + (U - 1) * blockDim.x < nvec; i += U * blockDim.x) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) v[u] = ld_peer_v4(src + i + u * blockDim.x);
+#pragma unroll
+      for (int u = 0; u < U; ++u) dst[i + u * blockDim.x] = v[u];
+    }
+    for (; i < nvec; i += blockDim.x) dst[i] = ld_peer_v4(src + i);
+    // generic-proxy stores -> later read by TMA (async proxy) of other CTAs
+    asm volatile("fence.proxy.async.global;" ::: "memory");
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) st_release_gpu(p.ag_flags + (size_t)r * cpr + ci, p.epoch);
+  }
+  // the sources may overwrite their shards once every reader is done
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    unsigned prev = atomicAdd(p.ag_flags + (size_t)p.world * cpr, 1u);
+    if (prev == (unsigned)p.n_copy - 1) {
+      p.ag_flags[(size_t)p.world * cpr] = 0;
+      for (int r = 0; r < p.world; ++r) st_release_sys(p.pad_peer[r] + p.done_slot + p.rank, p.epoch);
+    }
+  }
+}
+
+// Wait until rows [r0, r1) of the gathered operand are in local memory.
+__device__ __forceinline__ bool ag_wait_rows(const GemmParams& p, int r0, int r1) {
+  const int cpr = (int)((p.ag_shard_bytes + p.ag_chunk_bytes - 1) / p.ag_chunk_bytes);
+  bool waited = false;
+  for (int row = r0; row < r1;) {
+    const int owner = row / p.ag_rows_per_rank;
+    const int in_shard = row - owner * p.ag_rows_per_rank;
+    const int ci = in_shard / p.ag_rows_per_flag;
+    const int next = owner * p.ag_rows_per_rank + min((ci + 1) * p.ag_rows_per_flag, p.ag_rows_per_rank);
+    if (owner != p.rank && owner < p.world) {
+      if (!flag_wait_ge(p.ag_flags + (size_t)owner * cpr + ci, p.epoch, false, p.status, p.wait_ns, 12))
+        return false;
+      waited = true;
+    }
+    row = next;
+  }
+  if (waited) asm volatile("fence.proxy.async.global;" ::: "memory");
+  return true;
+}
+
+// After its tiles, every GEMM CTA helps summing the staged partials that arrived for this
+// rank: out[i] = sum_src stage[src][i] (fp32 accumulate, rank order).
+__device__ void rs_reduce_role(const GemmParams& p, int bid, int nctas, int t, const WaitCtx& wc) {
+  // wait for every source's tiles (each tile bumps the counter once per epilogue warp)
+  if (t < p.world &&
+      !flag_wait_ge(p.rs_cnt[p.rank] + t, p.rs_expect, true, p.status, p.wait_ns, 13))
+    *wc.abort_smem = 1;
+  // named barrier over the 128 epilogue threads (each of the four warps gets here exactly once)
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  if (*wc.abort_smem) return;
+  const size_t per_src = (size_t)p.rs_rows_per_rank * p.N;
+  const size_t nvec = per_src / 8;
+  const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(p.rs_stage[p.rank]);
+  for (size_t i = (size_t)bid * 128 + t; i < nvec; i += (size_t)nctas * 128) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int r = 0; r < p.world; ++r) {
+      uint4 raw = ld_peer_v4(reinterpret_cast<const uint4*>(stage + r * per_src) + i);
+      const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __bfloat1622float2(hb[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) ob[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    reinterpret_cast<uint4*>(p.rs_out)[i] = o;
+  }
 }
 
 template <int BLOCK_N, bool A_MN, bool B_MN>
@@ -79,6 +220,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  if ((int)blockIdx.x < p.n_copy) {
+    ag_copy_role(p);
+    return;
+  }
+  const int bid = blockIdx.x - p.n_copy;
+  const int nctas = gridDim.x - p.n_copy;
   const int tiles_m = (p.M + kBlockM - 1) / kBlockM;
   const int tiles_n = (p.N + BLOCK_N - 1) / BLOCK_N;
   const int n_tiles = tiles_m * tiles_n;
@@ -113,9 +260,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      for (int tile = bid; tile < n_tiles && ok; tile += nctas) {
         int tm, tn;
         tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        tm = (tm + p.tile_m_shift) % tiles_m;
+        if (p.ag_operand) {
+          ok = ag_wait_rows(p, p.ag_operand == 1 ? tm * kBlockM : tn * BLOCK_N,
+                            p.ag_operand == 1 ? min(tm * kBlockM + kBlockM, p.M) : min(tn * BLOCK_N + BLOCK_N, p.N));
+          if (!ok) { *abort_w = 1; break; }
+        }
         if (p.b_flags) {
           int r0 = tn * BLOCK_N;
           int r1 = min(r0 + BLOCK_N, p.N) - 1;
@@ -159,7 +312,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       constexpr uint32_t idesc = make_idesc_f16(kBlockM, BLOCK_N, 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
       uint32_t it = 0, lt = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++lt) {
+      for (int tile = bid; tile < n_tiles && ok; tile += nctas, ++lt) {
         int as = lt & 1;
         uint32_t aph = (lt >> 1) & 1;
         if (!mbar_wait(&tempty[as], aph ^ 1, wc, 2)) break;
@@ -189,9 +342,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------------------------------------ epilogue (4 warps)
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     uint32_t lt = 0;
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++lt) {
+    for (int tile = bid; tile < n_tiles; tile += nctas, ++lt) {
       int tm, tn;
       tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      tm = (tm + p.tile_m_shift) % tiles_m;
       int as = lt & 1;
       uint32_t aph = (lt >> 1) & 1;
       if (!mbar_wait_warp(&tfull[as], aph, wc, 4)) break;
@@ -222,7 +376,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               }
             }
           }
-          if (p.out_f32) {
+          if (p.rs_mode) {
+            // row block -> owning rank; bf16 partial straight into that rank's staging slice
+            const int d = row / p.rs_rows_per_rank;
+            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.rs_stage[d]) +
+                                  ((size_t)p.rank * p.rs_rows_per_rank + (row - d * p.rs_rows_per_rank)) * p.N + col0;
+            if (full_chunk) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                uint4 o;
+                __nv_bfloat162* ob2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  ob2[j] = __floats2bfloat162_rn(v[i + 2 * j], v[i + 2 * j + 1]);
+                *reinterpret_cast<uint4*>(crow + i) = o;
+              }
+            } else {
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < p.N) crow[i] = __float2bfloat16(v[i]);
+            }
+          } else if (p.out_f32) {
             float* crow = reinterpret_cast<float*>(p.C) + (size_t)row * p.ldc + col0;
             if (full_chunk && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
 #pragma unroll
@@ -274,7 +447,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[as]);
+      if (p.rs_mode) {
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          const int d = (tm * kBlockM) / p.rs_rows_per_rank;
+          red_release_sys_add(p.rs_cnt[d] + p.rank, 1u);
+        }
+      }
     }
+    if (p.rs_mode) rs_reduce_role(p, bid, nctas, (warp & 3) * 32 + lane, wc);
   }
 
   // ---------------------------------------------------------------- teardown
@@ -363,7 +545,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
     configured = true;
   }
   int tiles = ((p.M + kBlockM - 1) / kBlockM) * ((p.N + BLOCK_N - 1) / BLOCK_N);
-  int grid = tiles < max_ctas ? tiles : max_ctas;
+  int grid = (tiles < max_ctas ? tiles : max_ctas) + p.n_copy;
   if (grid <= 0) return 0;
   kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
   return (int)cudaGetLastError();
@@ -373,7 +555,7 @@ int gemm_bf16_dispatch(const void* A, const void* B, void* C, const void* bias, 
                        int K, int lda, int ldb, int ldc, int a_mn, int b_mn, int out_f32,
                        int bias_f32, int accumulate, float alpha, const uint32_t* b_flags,
                        int rows_per_flag, uint32_t flag_want, int max_ctas, uint32_t* status,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, const GemmFused* fused) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) ||
       (reinterpret_cast<uintptr_t>(B) & 15))
@@ -393,7 +575,25 @@ int gemm_bf16_dispatch(const void* A, const void* B, void* C, const void* bias, 
   p.wait_ns = kDefaultWaitNs;
   p.b_flags = b_flags; p.rows_per_flag = rows_per_flag > 0 ? rows_per_flag : 1;
   p.flag_want = flag_want;
+  p.n_copy = 0; p.ag_operand = 0; p.rs_mode = 0; p.tile_m_shift = 0; p.world = 1; p.rank = 0;
+  if (fused) {
+    p.n_copy = fused->n_copy; p.ag_operand = fused->ag_operand; p.world = fused->world;
+    p.rank = fused->rank; p.ag_dst = fused->ag_dst; p.ag_shard_bytes = fused->ag_shard_bytes;
+    p.ag_chunk_bytes = fused->ag_chunk_bytes; p.ag_rows_per_rank = fused->ag_rows_per_rank;
+    p.ag_rows_per_flag = fused->ag_rows_per_flag; p.ag_flags = fused->ag_flags;
+    p.pad_local = fused->pad_local; p.ready_slot = fused->ready_slot; p.done_slot = fused->done_slot;
+    p.epoch = fused->epoch; p.tile_m_shift = fused->tile_m_shift; p.rs_mode = fused->rs_mode;
+    p.rs_rows_per_rank = fused->rs_rows_per_rank; p.rs_expect = fused->rs_expect;
+    p.rs_out = fused->rs_out;
+    for (int r = 0; r < 16; ++r) {
+      p.ag_src[r] = fused->ag_src[r]; p.pad_peer[r] = fused->pad_peer[r];
+      p.rs_stage[r] = fused->rs_stage[r]; p.rs_cnt[r] = fused->rs_cnt[r];
+    }
+    if (fused->wait_ns) p.wait_ns = fused->wait_ns;
+  }
   if (max_ctas <= 0) max_ctas = sm_count();
+  max_ctas -= p.n_copy;
+  if (max_ctas < 1) return -2;
 #define TPB_GEMM_CASE(BN, AM, BM) \
   if (block_n == BN && (bool)a_mn == AM && (bool)b_mn == BM) \
     return launch_gemm<BN, AM, BM>(ta, tb, p, max_ctas, stream);
@@ -417,5 +617,76 @@ extern "C" int tpb_gemm_bf16(const void* A, const void* B, void* C, const void* 
                              void* stream) {
   return tpb::gemm_bf16_dispatch(A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_f32,
                                  bias_f32, accumulate, alpha, nullptr, 0, 0, 0, status,
-                                 static_cast<cudaStream_t>(stream));
+                                 static_cast<cudaStream_t>(stream), nullptr);
+}
+
+// ------------------------------------------------------------------ fused collectives (host)
+// C[M, N] = gather_rows(A)[M, K] * B[N, K]^T where A is row-sharded over the ranks: rank r's
+// rows [r * M/world, (r+1) * M/world) live in rank r's copy of the symmetric buffer at arena
+// offset a_off (shape [M, K], ld = K); after the call the local copy holds all rows.
+//   flags: local device array of at least world * ceil(shard_rows / rows_per_flag) + 1 words.
+//   ready_slot / done_slot: `world` signal slots each; epoch must grow by one per call.
+extern "C" int tpb_ag_gemm(size_t a_off, const void* B, void* C, const void* bias, int M, int N,
+                           int K, int ldb, int ldc, int b_mn, int out_f32, uint32_t* flags,
+                           int rows_per_flag, size_t pad_off, int ready_slot, int done_slot,
+                           uint32_t epoch, int n_copy, double wait_s, uint32_t* status,
+                           void* stream) {
+  const tpb::SymmView* sv = tpb::symm_view();
+  if (!sv || sv->world < 1 || M % sv->world) return -2;
+  const int world = sv->world, rank = sv->rank;
+  const int rows_per_rank = M / world;
+  if (rows_per_rank % rows_per_flag) return -2;
+  tpb::GemmFused f;
+  memset(&f, 0, sizeof(f));
+  f.world = world; f.rank = rank;
+  f.n_copy = world > 1 ? (n_copy > 0 ? n_copy : 16) : 0;
+  f.ag_operand = world > 1 ? 1 : 0;
+  f.ag_shard_bytes = (unsigned long long)rows_per_rank * K * 2;
+  f.ag_chunk_bytes = (unsigned long long)rows_per_flag * K * 2;
+  f.ag_rows_per_rank = rows_per_rank; f.ag_rows_per_flag = rows_per_flag;
+  f.ag_flags = flags;
+  f.ag_dst = sv->peer[rank] + a_off;
+  for (int r = 0; r < world; ++r) {
+    f.ag_src[r] = sv->peer[r] + a_off + (size_t)r * f.ag_shard_bytes;
+    f.pad_peer[r] = reinterpret_cast<uint32_t*>(sv->peer[r] + pad_off);
+  }
+  f.pad_local = reinterpret_cast<uint32_t*>(sv->peer[rank] + pad_off);
+  f.ready_slot = ready_slot; f.done_slot = done_slot; f.epoch = epoch;
+  const int tiles_m = (M + 127) / 128;
+  f.tile_m_shift = (int)(((long long)rank * rows_per_rank / 128) % tiles_m);
+  f.wait_ns = wait_s > 0 ? (unsigned long long)(wait_s * 1e9) : 0;
+  return tpb::gemm_bf16_dispatch(sv->peer[rank] + a_off, B, C, bias, M, N, K, K, ldb, ldc, 0, b_mn,
+                                 out_f32, 0, 0, 1.f, nullptr, 0, 0, 0, status,
+                                 static_cast<cudaStream_t>(stream), &f);
+}
+
+// out[M/world, N] (local) = sum over ranks of (A_r[M, K] * B_r[N, K]^T)[rows of this rank].
+// stage_off: arena offset of a [world, M/world, N] bf16 staging buffer; cnt_slot: `world`
+// signal slots used as tile counters (monotonic; `expect` = value meaning "all arrived").
+extern "C" int tpb_gemm_rs(const void* A, const void* B, void* out, int M, int N, int K, int lda,
+                           int ldb, int a_mn, int b_mn, size_t stage_off, size_t pad_off,
+                           int cnt_slot, uint32_t epoch, double wait_s, uint32_t* status,
+                           void* stream) {
+  const tpb::SymmView* sv = tpb::symm_view();
+  if (!sv || sv->world < 1 || M % (sv->world * 128) || N % 8) return -2;
+  const int world = sv->world, rank = sv->rank;
+  tpb::GemmFused f;
+  memset(&f, 0, sizeof(f));
+  f.world = world; f.rank = rank;
+  f.rs_mode = 1;
+  f.rs_rows_per_rank = M / world;
+  for (int r = 0; r < world; ++r) {
+    f.rs_stage[r] = sv->peer[r] + stage_off;
+    f.rs_cnt[r] = reinterpret_cast<uint32_t*>(sv->peer[r] + pad_off) + cnt_slot;
+  }
+  const int block_n = N > 128 ? 256 : 128;
+  const int tiles_per_rank = (f.rs_rows_per_rank / 128) * ((N + block_n - 1) / block_n);
+  f.rs_expect = epoch * (uint32_t)tiles_per_rank * 4u;
+  f.rs_out = static_cast<__nv_bfloat16*>(out);
+  const int tiles_m = M / 128;
+  f.tile_m_shift = (int)(((long long)((rank + 1) % world) * f.rs_rows_per_rank / 128) % tiles_m);
+  f.wait_ns = wait_s > 0 ? (unsigned long long)(wait_s * 1e9) : 0;
+  return tpb::gemm_bf16_dispatch(A, B, nullptr, nullptr, M, N, K, lda, ldb, N, a_mn, b_mn, 0, 0, 0,
+                                 1.f, nullptr, 0, 0, 0, status, static_cast<cudaStream_t>(stream),
+                                 &f);
 }

@@ -31,6 +31,15 @@ struct SymmState {
 };
 static SymmState g_symm;
 
+const SymmView* symm_view() {
+  static SymmView v;
+  if (!g_symm.base) return nullptr;
+  v.world = g_symm.world;
+  v.rank = g_symm.rank;
+  for (int r = 0; r < kMaxRanks; ++r) v.peer[r] = g_symm.peer[r];
+  return &v;
+}
+
 struct PeerPtrs {
   const char* p[kMaxRanks];
 };

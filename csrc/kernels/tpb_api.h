@@ -4,6 +4,7 @@
 // device memory; scratch buffers are passed in by the caller.
 #pragma once
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -15,11 +16,37 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t d0, uint64_t 
                       uint32_t box1);
 int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                    const uint64_t* strides_elems, const uint32_t* box, int swizzle128);
+// Mapped symmetric arenas of this process (see symm_comm.cu); null before tpb_symm_create.
+struct SymmView {
+  int world, rank;
+  char* peer[16];
+};
+const SymmView* symm_view();
+// Optional fused-collective description handed to the GEMM (see GemmParams in gemm_tcgen05.cu).
+struct GemmFused {
+  int n_copy, ag_operand, world, rank;
+  const char* ag_src[16];
+  char* ag_dst;
+  unsigned long long ag_shard_bytes, ag_chunk_bytes;
+  int ag_rows_per_rank, ag_rows_per_flag;
+  uint32_t* ag_flags;
+  uint32_t* pad_local;
+  uint32_t* pad_peer[16];
+  int ready_slot, done_slot;
+  uint32_t epoch;
+  int tile_m_shift;
+  int rs_mode, rs_rows_per_rank;
+  char* rs_stage[16];
+  uint32_t* rs_cnt[16];
+  uint32_t rs_expect;
+  __nv_bfloat16* rs_out;
+  unsigned long long wait_ns;
+};
 int gemm_bf16_dispatch(const void* A, const void* B, void* C, const void* bias, int M, int N,
                        int K, int lda, int ldb, int ldc, int a_mn, int b_mn, int out_f32,
                        int bias_f32, int accumulate, float alpha, const uint32_t* b_flags,
                        int rows_per_flag, uint32_t flag_want, int max_ctas, uint32_t* status,
-                       cudaStream_t stream);
+                       cudaStream_t stream, const GemmFused* fused);
 }  // namespace tpb
 extern "C" {
 #endif

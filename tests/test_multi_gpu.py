@@ -37,3 +37,11 @@ def test_fsdp_symm_matches_nccl_and_dense():
     r = _run_workers("fsdp_symm_worker.py", n)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "RESULT" in r.stdout
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_tp_fused_ag_gemm_and_gemm_rs():
+    n = 2 if _ngpu() < 4 else 4
+    r = _run_workers("tp_fused_worker.py", n)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "RESULT" in r.stdout
