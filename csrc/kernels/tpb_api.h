@@ -107,6 +107,11 @@ int tpb_flash_bwd(const void* dout, const void* q, const void* k, const void* v,
                   long long dkv_tok, long long dkv_head, long long dkv_batch, int lse_stride,
                   int causal, float scale, uint32_t* status, void* stream);
 
+int tpb_grouped_workspace_ints(int max_rows, int G);
+int tpb_grouped_gemm(const void* A, const void* B, void* C, const int* offs, int G, int max_rows,
+                     int N, int K, int mode, int b_mn, int out_f32, int accumulate, int* workspace,
+                     uint32_t* status, void* stream);
+
 int tpb_adamw_flat(float* master, float* m, float* v, const void* grad, int grad_bf16, void* model,
                    int model_bf16, long long n, float lr, float beta1, float beta2, float eps,
                    float wd, int step, float grad_scale, int maximize, const float* clip_coef,

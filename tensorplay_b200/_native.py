@@ -39,6 +39,8 @@ _KERNEL_SIGS = {
     "tpb_cross_entropy_bwd": [P, P, P, P, P, P, P, LL, I, LL, LL, P],
     "tpb_flash_fwd": [P, P, P, P, P, I, I, I, I, I, I] + [LL] * 12 + [I, I, F, P, P],
     "tpb_flash_bwd": [P] * 10 + [I, I, I, I, I, I] + [LL] * 21 + [I, I, F, P, P],
+    "tpb_grouped_workspace_ints": [I, I],
+    "tpb_grouped_gemm": [P, P, P, P, I, I, I, I, I, I, I, I, P, P, P],
     "tpb_adamw_flat": [P, P, P, P, I, P, I, LL, F, F, F, F, F, I, F, I, P, P, P],
     "tpb_adamw_multi": [I, P, P, P, P, P, P, I, I, F, F, F, F, F, I, F, I, P, P, P],
     "tpb_sumsq": [P, I, LL, F, P, P],
@@ -67,7 +69,8 @@ def _load(name: str):
 
 
 # kernel launches issued by one call of each entry point (for launch accounting)
-_LAUNCHES = {"tpb_rmsnorm_bwd": 2, "tpb_layernorm_bwd": 3, "tpb_flash_bwd": 3, "tpb_rmsnorm_bwd_grid": 0}
+_LAUNCHES = {"tpb_rmsnorm_bwd": 2, "tpb_layernorm_bwd": 3, "tpb_flash_bwd": 3, "tpb_rmsnorm_bwd_grid": 0,
+             "tpb_grouped_workspace_ints": 0, "tpb_grouped_gemm": 2}
 launch_count = 0
 
 
