@@ -45,3 +45,11 @@ def test_tp_fused_ag_gemm_and_gemm_rs():
     r = _run_workers("tp_fused_worker.py", n)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "RESULT" in r.stdout
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_moe_expert_parallel_dispatch_combine():
+    n = 2 if _ngpu() < 4 else 4
+    r = _run_workers("moe_ep_worker.py", n)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "RESULT" in r.stdout
