@@ -72,6 +72,7 @@ class ParamUnit:
         self.exp_avg_sq: Optional[Tensor] = None
         self.gather_event = None
         self.update_event = None
+        self.local: Optional["ParamUnit"] = None
 
     def bind_params(self, full: Tensor) -> None:
         self.full = full
@@ -195,8 +196,12 @@ class FSDPEngine:
         groups = [("embed", emb)] + [(f"layer{i}", lp) for i, lp in enumerate(layer_params)] + [("head", head)]
         self.units: List[ParamUnit] = []
         for name, ps in groups:
-            self.units.append(ParamUnit(len(self.units), name, ps, self.world, self.rank, self.device,
-                                        self.param_dtype))
+            # expert-parallel parameters are owned by this rank alone: never gathered or reduced
+            shared = [(n, p) for n, p in ps if not getattr(p, "_tpb_expert_parallel", False)]
+            local = [(n, p) for n, p in ps if getattr(p, "_tpb_expert_parallel", False)]
+            u = ParamUnit(len(self.units), name, shared, self.world, self.rank, self.device, self.param_dtype)
+            u.local = ParamUnit(u.index, name + ".experts", local, 1, 0, self.device, self.param_dtype) if local else None
+            self.units.append(u)
         self.n_layers = len(m.layers)
 
     def _alloc(self) -> None:
@@ -227,6 +232,20 @@ class FSDPEngine:
                 for _, p in u.params:
                     p.data = torch.empty(0, dtype=dt, device=dev)
             del init
+            if u.local is not None:
+                lu = u.local
+                full = torch.zeros(lu.padded, dtype=dt, device=dev)
+                for (_, p), off, n in zip(lu.params, lu.offsets, lu.numels):
+                    full[off: off + n].copy_(p.data.reshape(-1))
+                lu.bind_params(full)
+                lu.shard = full
+                lu.master = full.float()
+                lu.exp_avg = torch.zeros(lu.padded, dtype=torch.float32, device=dev)
+                lu.exp_avg_sq = torch.zeros(lu.padded, dtype=torch.float32, device=dev)
+        max_local = max([u.local.padded for u in self.units if u.local is not None] or [0])
+        self.local_grad_pool = [torch.empty(max_local, dtype=dt, device=dev) for _ in range(2)] if max_local else []
+        self.local_grad_events = [None, None]
+        self._local_slot = 0
         # rotating full-parameter and gradient buffers
         # without checkpointing autograd keeps views of the gathered buffers until backward,
         # so every unit needs a buffer of its own for the whole step
@@ -336,10 +355,22 @@ class FSDPEngine:
         g.zero_()
         u.bind_grads(g)
         u._grad_slot = slot
+        if u.local is not None:
+            ls = self._local_slot
+            self._local_slot = (ls + 1) % 2
+            ev = self.local_grad_events[ls]
+            if ev is not None and self.cuda:
+                torch.cuda.current_stream().wait_event(ev)
+            lg = self.local_grad_pool[ls][: u.local.padded]
+            lg.zero_()
+            u.local.bind_grads(lg)
+            u.local._grad_slot = ls
 
     def _post_backward(self, idx: int) -> None:
         u = self.units[idx]
         u.collect_autograd_grads()
+        if u.local is not None:
+            u.local.collect_autograd_grads()
         self._release(u)
         self._reduce_and_update(u)
 
@@ -373,6 +404,16 @@ class FSDPEngine:
                 else:
                     dist.reduce_scatter_tensor(gs, g, op=dist.ReduceOp.AVG, group=self.group)
                 ops.adamw_flat_(u.master, u.exp_avg, u.exp_avg_sq, gs, u.shard, **self._adam_kwargs())
+            if u.local is not None:
+                lu = u.local
+                ops.adamw_flat_(lu.master, lu.exp_avg, lu.exp_avg_sq, lu.grad, lu.shard,
+                                grad_scale=1.0 / self.world, **self._adam_kwargs())
+                if self.cuda:
+                    lev = torch.cuda.Event()
+                    lev.record(stream)
+                    self.local_grad_events[lu._grad_slot] = lev
+                    lu.update_event = lev
+                lu.bind_grads(None)
             if self.cuda:
                 ev = torch.cuda.Event()
                 ev.record(stream)
@@ -389,6 +430,8 @@ class FSDPEngine:
             for u in self.units:
                 if u.update_event is not None and self.world == 1:
                     torch.cuda.current_stream().wait_event(u.update_event)
+                if u.local is not None and u.local.update_event is not None:
+                    torch.cuda.current_stream().wait_event(u.local.update_event)
         x = _UnitFn.apply(self, 0, lambda d, t: m.embed_tokens(t), False, 1, self._dummy, tokens)
         extra = m.layer_extra_args(tokens) if hasattr(m, "layer_extra_args") else ()
         for i, layer in enumerate(m.layers):
@@ -417,4 +460,8 @@ class FSDPEngine:
                 dist.all_gather_into_tensor(full, u.master.contiguous(), group=self.group)
             for (n, p), off, cnt, shape in zip(u.params, u.offsets, u.numels, u.shapes):
                 out[n] = full[off: off + cnt].view(shape).clone()
+            if u.local is not None:
+                lu = u.local
+                for (n, p), off, cnt, shape in zip(lu.params, lu.offsets, lu.numels, lu.shapes):
+                    out[n] = lu.master[off: off + cnt].view(shape).clone()
         return out
