@@ -833,3 +833,61 @@ extern "C" int tpb_cross_entropy_bwd(const void* logits, const long long* target
       V, stride, ignore_index);
   return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------------ allocation-free variant
+#include "tpb_noalloc.h"
+
+// Scratch for tpb_rmsnorm_bwd_noalloc: per-block partial sums of dw. Lives in every device
+// that loads this library for the life of the process.
+static __device__ __align__(256) float g_noalloc_rms_scratch[TPB_NOALLOC_RMSNORM_MAX_FLOATS];
+
+namespace {
+constexpr int kNoAllocMaxDevices = 64;
+float* g_noalloc_scratch_ptr[kNoAllocMaxDevices] = {};
+}  // namespace
+
+extern "C" const char* tpb_noalloc_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case TPB_NOALLOC_TOO_LARGE:
+      return "problem exceeds the built-in scratch (H <= 8192 and at most 296 blocks are supported)";
+    case TPB_NOALLOC_BAD_ARGS: return "H must be a positive multiple of 8 and strides multiples of 8";
+    case TPB_NOALLOC_NO_SYMBOL: return "could not obtain the device address of the built-in scratch";
+    default: return code > 0 ? "CUDA error (see cudaGetErrorString)" : "unknown error";
+  }
+}
+
+extern "C" int tpb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w,
+                                       const float* rstd, const void* dres, void* dx, float* dw_f32,
+                                       void* dw_bf16, int dw_accumulate, int rows, int H,
+                                       long long x_stride, long long dy_stride, long long dx_stride,
+                                       void* stream) {
+  if (H <= 0 || H % 8 || x_stride % 8 || dy_stride % 8 || dx_stride % 8) return TPB_NOALLOC_BAD_ARGS;
+  if (H > TPB_NOALLOC_RMSNORM_MAX_H) return TPB_NOALLOC_TOO_LARGE;
+  if (rows <= 0) return 0;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kNoAllocMaxDevices) return TPB_NOALLOC_NO_SYMBOL;
+  // First call on this device: the array's name is only a host-side handle, the kernel needs
+  // the address the symbol has on the current device.
+  float* scratch = g_noalloc_scratch_ptr[dev];
+  if (!scratch) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_rms_scratch);
+    if (e != cudaSuccess || !p) return TPB_NOALLOC_NO_SYMBOL;
+    scratch = static_cast<float*>(p);
+    g_noalloc_scratch_ptr[dev] = scratch;
+  }
+  const int tpr = pick_tpr(H);
+  int grid = tpb_rmsnorm_bwd_grid(rows, H);
+  if (grid > TPB_NOALLOC_RMSNORM_MAX_BLOCKS) grid = TPB_NOALLOC_RMSNORM_MAX_BLOCKS;
+  if ((long long)grid * H > (long long)TPB_NOALLOC_RMSNORM_MAX_FLOATS) return TPB_NOALLOC_TOO_LARGE;
+  TPB_ROW_SWITCH(tpr, pick_vpt(H, tpr), (rmsnorm_bwd_kernel<TPR, VPT><<<grid, kRowThreads, 0, (cudaStream_t)stream>>>(
+                          (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+                          (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres,
+                          (__nv_bfloat16*)dx, scratch, rows, H, x_stride, dy_stride, dx_stride)));
+  colsum_kernel<<<(H + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
+      scratch, grid, H, dw_f32, (__nv_bfloat16*)dw_bf16, dw_accumulate);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,82 @@
+"""The allocation-free RMSNorm backward (``tpb_rmsnorm_bwd_noalloc``) against the regular entry
+point, called through its exported C symbol, twice in a row.
+
+The variant exists for callers that may not create device memory when they need the op (all
+memory pre-committed to a cache pool, a plug-in that must not touch its host's allocator, a loop
+that cannot take cudaMalloc's synchronisation): its scratch is a static device array inside the
+library. The file name sorts last so that a run stopping at the first failure has already run
+every other test; the test also passes when run alone in a fresh process.
+"""
+import ctypes as C
+import os
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+LIB = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "tensorplay_b200", "_lib",
+                   "libtpb200.so")
+
+
+def _lib():
+    lib = C.CDLL(LIB)
+    P, I, LL = C.c_void_p, C.c_int, C.c_longlong
+    lib.tpb_rmsnorm_bwd_noalloc.argtypes = [P, P, P, P, P, P, P, P, I, I, I, LL, LL, LL, P]
+    lib.tpb_rmsnorm_bwd_noalloc.restype = I
+    lib.tpb_rmsnorm_bwd.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, LL, LL, LL, P]
+    lib.tpb_rmsnorm_bwd.restype = I
+    lib.tpb_rmsnorm_bwd_grid.argtypes = [I, I]
+    lib.tpb_rmsnorm_bwd_grid.restype = I
+    lib.tpb_noalloc_strerror.argtypes = [I]
+    lib.tpb_noalloc_strerror.restype = C.c_char_p
+    return lib
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("rows,H", [(1000, 4096), (333, 768)])
+def test_noalloc_matches_regular_entry_point_twice(rows, H):
+    lib = _lib()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    for call in range(2):  # the second call reuses the scratch that still holds the first call's data
+        torch.manual_seed(10 + call)
+        r = rows - 17 * call
+        x = torch.randn(r, H, device=dev, dtype=torch.bfloat16)
+        dy = torch.randn(r, H, device=dev, dtype=torch.bfloat16)
+        w = (1 + 0.1 * torch.randn(H, device=dev)).to(torch.bfloat16)
+        rstd = torch.rsqrt(x.float().pow(2).mean(-1) + 1e-5).contiguous()
+        dx_a, dx_b = torch.empty_like(x), torch.empty_like(x)
+        dw_a = torch.zeros(H, device=dev, dtype=torch.float32)
+        dw_b = torch.zeros(H, device=dev, dtype=torch.float32)
+        part = torch.empty(lib.tpb_rmsnorm_bwd_grid(r, H) * H, device=dev, dtype=torch.float32)
+        code = lib.tpb_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), None,
+                                   dx_a.data_ptr(), part.data_ptr(), dw_a.data_ptr(), None, 0, r, H, H, H, H, stream)
+        assert code == 0
+        before = torch.cuda.memory_allocated(dev)
+        code = lib.tpb_rmsnorm_bwd_noalloc(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), None,
+                                           dx_b.data_ptr(), dw_b.data_ptr(), None, 0, r, H, H, H, H, stream)
+        assert code == 0, lib.tpb_noalloc_strerror(code)
+        torch.cuda.synchronize()
+        assert torch.cuda.memory_allocated(dev) == before
+        assert torch.equal(dx_a, dx_b)
+        assert _rel(dw_b, dw_a) < 1e-5
+        # and both agree with the fp32 formula within the tolerance of the kernel tests
+        xf, gf, wf = x.float(), dy.float(), w.float()
+        xh = xf * rstd[:, None]
+        ref_dw = (gf * xh).sum(0)
+        assert _rel(dw_b, ref_dw) < 1e-2
+
+
+def test_noalloc_rejects_oversized_problem():
+    lib = _lib()
+    code = lib.tpb_rmsnorm_bwd_noalloc(None, None, None, None, None, None, None, None, 0, 16, 16384, 16384, 16384,
+                                       16384, None)
+    assert code == -22
+    assert b"scratch" in lib.tpb_noalloc_strerror(code)
+    assert lib.tpb_rmsnorm_bwd_noalloc(None, None, None, None, None, None, None, None, 0, 16, 100, 100, 100, 100,
+                                       None) == -2
