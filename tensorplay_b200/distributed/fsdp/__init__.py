@@ -1,0 +1,23 @@
+"""FSDP: ``fully_shard`` (FSDP2-style, per-module sharding with forward/backward hooks) and the
+``FullyShardedDataParallel`` wrapper facade.
+
+Two implementations live in this package:
+
+* ``fully_shard`` below is the general, API-compatible path for arbitrary modules: parameters are
+  sharded on dim 0 (ceil chunks, padded to the first chunk like the reference,
+  tensorplay/distributed/fsdp/_fully_shard/_fsdp_param.py:284-374), a forward pre-hook all-gathers
+  a unit's parameters, a post-hook frees them, and a backward hook re-gathers, then
+  reduce-scatters gradients into ``param.grad`` shards. It runs on gloo and NCCL through
+  torch.distributed and is what the CPU oracle configuration uses.
+* ``tensorplay_b200.parallel.FSDPEngine`` is the performance path for transformer stacks (flat
+  per-layer buffers, peer-memory kernels, optimizer fused into backward).
+
+Knobs follow tensorplay/distributed/fsdp/_fully_shard/_fully_shard.py:66-455 and _fsdp_api.py:20-75.
+"""
+from __future__ import annotations
+
+from .api import (BackwardPrefetch, CPUOffload, CPUOffloadPolicy, FSDPModule, FullyShardedDataParallel,
+                  MixedPrecision, MixedPrecisionPolicy, OffloadPolicy, ShardingStrategy, fully_shard)
+
+__all__ = ["fully_shard", "FSDPModule", "MixedPrecisionPolicy", "CPUOffloadPolicy", "OffloadPolicy",
+           "FullyShardedDataParallel", "ShardingStrategy", "MixedPrecision", "CPUOffload", "BackwardPrefetch"]

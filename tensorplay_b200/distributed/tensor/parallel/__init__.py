@@ -1,0 +1,201 @@
+"""Tensor / sequence parallel styles and ``parallelize_module``.
+
+``ColwiseParallel`` / ``RowwiseParallel`` shard ``nn.Linear`` weights across the TP group and
+replace the module's forward with the fused kernels of ``tensorplay_b200.parallel.tp``
+(all-gather->GEMM for column-parallel layers fed by sequence-sharded activations,
+GEMM->reduce-scatter for row-parallel layers); on CPU ranks the same styles run plain collectives.
+``SequenceParallel`` marks norm-like modules as operating on sequence shards (their parameters
+stay replicated and their gradients are all-reduced). Names follow
+tensorplay/distributed/tensor/parallel/api.py:16-55 and style.py:67-218.
+"""
+from __future__ import annotations
+
+import fnmatch
+from typing import Dict, Optional, Union
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from ....parallel.tp import TPContext, _AllGatherRows, _ReduceScatterRows
+
+__all__ = ["ParallelStyle", "ColwiseParallel", "RowwiseParallel", "SequenceParallel", "parallelize_module",
+           "loss_parallel"]
+
+
+class ParallelStyle:
+    def apply(self, module: nn.Module, ctx: TPContext) -> nn.Module:
+        raise NotImplementedError
+
+
+def _shard_rows(w: torch.Tensor, world: int, rank: int) -> torch.Tensor:
+    assert w.shape[0] % world == 0, "dimension not divisible by the TP degree"
+    n = w.shape[0] // world
+    return w[rank * n: (rank + 1) * n].clone()
+
+
+class ColwiseParallel(ParallelStyle):
+    """Weight ``[out, in]`` sharded on ``out``. ``input_sharded=True``: the input arrives
+    sequence-sharded ``[rows/world, in]`` and is all-gathered inside the GEMM kernel; otherwise the
+    input is replicated and the layer is a local GEMM. Output: ``[rows, out/world]``."""
+
+    def __init__(self, *, input_sharded: bool = True):
+        self.input_sharded = input_sharded
+
+    def apply(self, module: nn.Linear, ctx: TPContext) -> nn.Module:
+        w, r = ctx.world, ctx.rank
+        module.weight = nn.Parameter(_shard_rows(module.weight.data, w, r))
+        if module.bias is not None:
+            module.bias = nn.Parameter(_shard_rows(module.bias.data, w, r))
+        sharded = self.input_sharded
+
+        def forward(x):
+            shape = x.shape
+            x2 = x.reshape(-1, shape[-1])
+            if sharded and w > 1:
+                y = ctx.all_gather_linear(x2, module.weight)
+            else:
+                y = torch.nn.functional.linear(x2, module.weight) if not x2.is_cuda else _local_linear(x2, module.weight)
+            if module.bias is not None:
+                y = y + module.bias
+            return y
+        module.forward = forward
+        return module
+
+
+class RowwiseParallel(ParallelStyle):
+    """Weight ``[out, in]`` sharded on ``in``; the input is ``[rows, in/world]``. With
+    ``output_sharded=True`` the partial products are reduce-scattered over rows inside the GEMM
+    kernel (sequence parallel output ``[rows/world, out]``), otherwise all-reduced."""
+
+    def __init__(self, *, output_sharded: bool = True):
+        self.output_sharded = output_sharded
+
+    def apply(self, module: nn.Linear, ctx: TPContext) -> nn.Module:
+        w, r = ctx.world, ctx.rank
+        module.weight = nn.Parameter(_shard_rows(module.weight.data.t().contiguous(), w, r).t().contiguous())
+        scattered = self.output_sharded
+
+        def forward(x):
+            x2 = x.reshape(-1, x.shape[-1])
+            if w == 1:
+                y = torch.nn.functional.linear(x2, module.weight)
+            elif scattered:
+                y = ctx.linear_reduce_scatter(x2, module.weight)
+            else:
+                y = _AllReduce.apply(torch.nn.functional.linear(x2, module.weight), ctx.group)
+            if module.bias is not None:
+                y = y + module.bias
+            return y
+        module.forward = forward
+        return module
+
+
+class SequenceParallel(ParallelStyle):
+    """Norm / dropout style: runs unchanged on the local sequence shard; parameter gradients are
+    summed over the TP group after backward (``sync_grads``)."""
+
+    def apply(self, module: nn.Module, ctx: TPContext) -> nn.Module:
+        for p in module.parameters():
+            p._tp_replicated = True
+        return module
+
+
+def _local_linear(x, w):
+    from .... import ops
+    return ops.linear(x, w)
+
+
+class _AllReduce(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        y = x.clone()
+        dist.all_reduce(y, group=group)
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+def parallelize_module(module: nn.Module, device_mesh=None, parallelize_plan: Union[ParallelStyle, Dict[str, ParallelStyle], None] = None,
+                       *, tp_context: Optional[TPContext] = None) -> nn.Module:
+    """Apply styles to sub-modules selected by fnmatch-style dotted paths."""
+    group = None
+    if device_mesh is not None:
+        group = device_mesh.get_group() if device_mesh.ndim == 1 else device_mesh.get_group(device_mesh.ndim - 1)
+    ctx = tp_context or TPContext(group=group)
+    module._tp_context = ctx
+    if parallelize_plan is None:
+        return module
+    if isinstance(parallelize_plan, ParallelStyle):
+        return parallelize_plan.apply(module, ctx)
+    names = dict(module.named_modules())
+    for pattern, style in parallelize_plan.items():
+        matched = [n for n in names if fnmatch.fnmatch(n, pattern)]
+        if not matched:
+            raise ValueError(f"parallelize_plan key {pattern!r} matches no sub-module")
+        for n in matched:
+            style.apply(names[n], ctx)
+    return module
+
+
+def sync_replicated_grads(module: nn.Module) -> None:
+    """Sum the gradients of parameters that are replicated across the TP group but saw only a
+    sequence shard of the activations (``SequenceParallel`` modules)."""
+    ctx = getattr(module, "_tp_context", None)
+    if ctx is None or ctx.world == 1:
+        return
+    for p in module.parameters():
+        if getattr(p, "_tp_replicated", False) and p.grad is not None:
+            dist.all_reduce(p.grad, group=ctx.group)
+
+
+class loss_parallel:
+    """Context manager: cross-entropy over vocabulary-sharded logits ``[rows, V/world]``
+    (column-parallel LM head) without gathering them: max and sum-exp are all-reduced."""
+
+    def __init__(self, group=None):
+        self.group = group
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+    def cross_entropy(self, logits_shard: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
+        return _VocabParallelCE.apply(logits_shard, target, self.group)
+
+
+class _VocabParallelCE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, target, group):
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        rank = dist.get_rank(group) if dist.is_initialized() else 0
+        lf = logits.float()
+        vs = lf.shape[-1]
+        m = lf.max(dim=-1).values
+        if world > 1:
+            dist.all_reduce(m, op=dist.ReduceOp.MAX, group=group)
+        e = torch.exp(lf - m[:, None])
+        s = e.sum(-1)
+        lo = rank * vs
+        mine = (target >= lo) & (target < lo + vs)
+        tl = torch.zeros_like(m)
+        idx = (target - lo).clamp(0, vs - 1)
+        tl[mine] = lf.gather(1, idx[:, None]).squeeze(1)[mine]
+        if world > 1:
+            dist.all_reduce(s, group=group)
+            dist.all_reduce(tl, group=group)
+        lse = m + s.log()
+        ctx.save_for_backward(e / s[:, None], mine, idx)
+        return (lse - tl).mean()
+
+    @staticmethod
+    def backward(ctx, g):
+        p, mine, idx = ctx.saved_tensors
+        grad = p.clone()
+        rows = torch.arange(p.shape[0], device=p.device)[mine]
+        grad[rows, idx[mine]] -= 1.0
+        return (grad * (g / p.shape[0])).to(p.dtype), None, None

@@ -1,0 +1,5 @@
+"""``utils``: activation checkpointing, data loading (``DistributedSampler``), pytree, hooks."""
+from torch.utils import *  # noqa: F401,F403
+from torch.utils import _pytree, hooks  # noqa: F401
+
+from . import checkpoint, data  # noqa: F401

@@ -1,0 +1,80 @@
+"""tprun restart-on-failure with a flaky worker, ChildFailedError, watchdog and flight recorder
+(host-side fault injection only, as in the reference's test_distributed_elastic.py:208-219)."""
+import json
+import os
+import sys
+import textwrap
+import time
+
+import pytest
+
+from tensorplay_b200.distributed import flight_recorder as fr
+from tensorplay_b200.distributed.run import ChildFailedError, LaunchConfig, elastic_launch
+from tensorplay_b200.distributed.watchdog import PeerHeartbeat, Watchdog, WatchdogTimeout
+
+
+def _script(tmp_path, body):
+    p = tmp_path / "worker.py"
+    p.write_text(textwrap.dedent(body))
+    return str(p)
+
+
+def test_tprun_restarts_flaky_worker(tmp_path):
+    marker = tmp_path / "done"
+    s = _script(tmp_path, f"""
+        import os, sys
+        rank = int(os.environ["RANK"]); attempt = int(os.environ["TP_RESTART_COUNT"])
+        assert os.environ["WORLD_SIZE"] == "2" and "MASTER_PORT" in os.environ
+        if attempt == 0 and rank == 1:
+            sys.exit(3)          # first generation: rank 1 fails
+        open(r"{marker}" + str(rank), "w").write(str(attempt))
+    """)
+    rc = elastic_launch(LaunchConfig(nproc_per_node=2, max_restarts=2, log_dir=str(tmp_path / "logs")),
+                        [sys.executable, s])
+    assert rc == 0
+    assert (tmp_path / "done0").read_text() == "1" and (tmp_path / "done1").read_text() == "1"
+    assert os.path.exists(tmp_path / "logs" / "attempt0_rank1.log")
+
+
+def test_tprun_raises_when_restarts_exhausted(tmp_path):
+    s = _script(tmp_path, "import sys; sys.exit(5)")
+    with pytest.raises(ChildFailedError) as ei:
+        elastic_launch(LaunchConfig(nproc_per_node=2, max_restarts=1), [sys.executable, s])
+    assert 5 in ei.value.failures.values()
+
+
+def test_watchdog_trips_and_raises():
+    wd = Watchdog(cpu_timeout=0.15, action="raise", poll_interval=0.02)
+    try:
+        wd.heartbeat()
+        time.sleep(0.4)
+        with pytest.raises(WatchdogTimeout):
+            wd.heartbeat()
+        wd.heartbeat()  # recovered
+    finally:
+        wd.close()
+
+
+def test_peer_heartbeat_detects_silent_rank():
+    from tensorplay_b200.distributed.store import HashStore
+    st = HashStore()
+    a, b = PeerHeartbeat(st, 0, 2, timeout=0.1), PeerHeartbeat(st, 1, 2, timeout=0.1)
+    a.beat(); b.beat()
+    assert a.missing() == []
+    time.sleep(0.25)
+    a.beat()
+    assert a.missing() == [1]   # rank 1 stopped beating
+    b.beat()
+    assert a.missing() == []
+
+
+def test_flight_recorder_dump_and_analyze(tmp_path):
+    paths = []
+    for rank, ops in enumerate([["all_gather", "reduce_scatter", "all_gather"], ["all_gather", "all_reduce"]]):
+        fr.clear()
+        for o in ops:
+            fr.record(o, numel=8, group="dp")
+        paths.append(fr.dump(str(tmp_path / f"fr{rank}.json"), rank=rank))
+    rep = fr.analyze(paths)
+    assert rep["mismatch"]["index"] == 1 and rep["behind"] == [1]
+    assert json.load(open(paths[0]))["entries"][0]["op"] == "all_gather"
