@@ -26,8 +26,11 @@ def timeit(fn, iters=20, warmup=5):
 def main():
     shapes = [(4096, 6144, 4096), (4096, 4096, 4096), (4096, 28672, 4096), (4096, 4096, 14336),
               (4096, 128256, 4096), (8192, 8192, 8192)]
-    if len(sys.argv) > 1 and sys.argv[1] == "--small":
+    if "--small" in sys.argv:
         shapes = [(4096, 4096, 4096)]
+    if "--splitk" in sys.argv:
+        from tensorplay_b200.ops.gemm import enable_splitk
+        enable_splitk()
     for M, N, K in shapes:
         a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
         b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)

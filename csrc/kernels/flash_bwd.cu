@@ -40,7 +40,22 @@ struct AttnBwdParams {
   long long out_tok, out_head, out_batch;
   uint32_t* status;
   unsigned long long wait_ns;
+  unsigned long long* trace;  // optional: timestamps of CTA (0,0,0), see tpb_flash_bwd_set_trace
+  int trace_cap;
 };
+
+// Debug aid: records (role, iteration, phase, globaltimer) tuples of block (0,0,0).
+__device__ __forceinline__ void trace_pt(const AttnBwdParams& p, int role, int it, int phase) {
+  if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+    unsigned long long idx = atomicAdd(p.trace, 1ull);
+    if ((int)idx < p.trace_cap) {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+      p.trace[1 + idx * 2] = ((unsigned long long)role << 48) | ((unsigned long long)(it & 0xffffff) << 16) | (unsigned)phase;
+      p.trace[2 + idx * 2] = t;
+    }
+  }
+}
 
 __device__ __forceinline__ float bwd_exp2(float x) {
   float y;
@@ -179,6 +194,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
         const int s = it % kYStages;
         const uint32_t ph = (it / kYStages) & 1;
         if (!mbar_wait(&y_empty[s], ph ^ 1, wc, 1)) break;
+        trace_pt(p, 0, it, 1);
         int hy, yb;
         if (DKV) { hy = hx * G + it / y_count; yb = y_first + it % y_count; }
         else { hy = hx / G; yb = it; }
@@ -214,7 +230,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
         const int s = it & 1;
         const uint32_t ph = (it >> 1) & 1;
         if (!mbar_wait(&y_full[ys], yph, wc, 2)) return false;
+        trace_pt(p, 1, it, 1);
         if (!mbar_wait(&sdp_empty[s], ph ^ 1, wc, 3)) return false;
+        trace_pt(p, 1, it, 2);
         tc_fence_after_sync();
         const uint32_t y0_s = smem_u32(smem + L::kY + ys * 2 * L::kStreamBytes);
         const uint32_t y1_s = y0_s + L::kStreamBytes;
@@ -243,6 +261,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
         }
         const int s = it % kYStages;
         if (!mbar_wait(pds_full, it & 1, wc, 5)) break;
+        trace_pt(p, 1, it, 3);
         tc_fence_after_sync();
         const uint32_t y0_s = smem_u32(smem + L::kY + s * 2 * L::kStreamBytes);
         const uint32_t y1_s = y0_s + L::kStreamBytes;
@@ -261,6 +280,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
         }
         umma_commit(acc_done);
         umma_commit(&y_empty[s]);
+        trace_pt(p, 1, it, 4);
       }
     }
   } else {
@@ -287,6 +307,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
       else { hy = hx; yb = it; }
       const int y0i = yb * kStream;  // first query (DKV) or key (dQ) of the streamed tile
       if (!mbar_wait_warp(&sdp_full[s], ph, wc, 6)) { ok = false; break; }
+      if (threadIdx.x == 64) trace_pt(p, 2, it, 1);
       tc_fence_after_sync();
       uint32_t sr[2][32], dr[2][32];
       tmem_ld_32x32b_x32(tmem_base + t_lane + s * 128, sr[0]);
@@ -296,6 +317,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
       tmem_ld_wait();
       tc_fence_before_sync();
       mbar_arrive(&sdp_empty[s]);
+      if (threadIdx.x == 64) trace_pt(p, 2, it, 2);
 
       float pv[64], dsv[64];
       const float* lse_col = nullptr;
@@ -333,14 +355,17 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
           dsv[col] = valid ? pr * (dp - d4[i]) * p.scale : 0.f;
         }
       }
+      if (threadIdx.x == 64) trace_pt(p, 2, it, 3);
       if (it > 0) {
         if (!mbar_wait_warp(acc_done, (it - 1) & 1, wc, 7)) { ok = false; break; }
       }
+      if (threadIdx.x == 64) trace_pt(p, 2, it, 4);
       if (DKV) store_row64_sw128(smem + L::kP, row, pv);
       store_row64_sw128(smem + L::kDS, row, dsv);
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(pds_full);
+      if (threadIdx.x == 64) trace_pt(p, 2, it, 5);
     }
     if (ok && n_it > 0) ok = mbar_wait_warp(acc_done, (n_it - 1) & 1, wc, 8);
     if (ok) {
@@ -426,6 +451,9 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o,
   if (lane == 0) delta[((long long)b * H + h) * lse_stride + t] = s;
 }
 
+static unsigned long long* g_bwd_trace = nullptr;
+static int g_bwd_trace_cap = 0;
+
 template <int D, bool DKV>
 static int launch_bwd(const CUtensorMap& x0, const CUtensorMap& x1, const CUtensorMap& y0,
                       const CUtensorMap& y1, const AttnBwdParams& p, dim3 grid,
@@ -479,6 +507,7 @@ extern "C" int tpb_flash_bwd(const void* dout, const void* q, const void* k, con
   p.kv_offset = Tk - Tq; p.scale = scale; p.scale_log2e = scale * 1.4426950408889634f;
   p.lse = lse; p.delta = delta; p.lse_stride = lse_stride; p.status = status;
   p.wait_ns = kDefaultWaitNs;
+  p.trace = g_bwd_trace; p.trace_cap = g_bwd_trace_cap;
   int r;
   // ---- dK / dV: [B, Tk, Hkv, D] by the dkv strides (dk and dv share them)
   {
@@ -508,5 +537,14 @@ extern "C" int tpb_flash_bwd(const void* dout, const void* q, const void* k, con
                    : launch_bwd<64, false>(tq, tdo, tk, tv, p, grid, stream);
     if (r) return r;
   }
+  return 0;
+}
+
+// Debug aid: buf = device array of 1 + 2 * cap uint64 (buf[0] = record count, zero it first). The
+// next backward launches record role / iteration / phase timestamps of block (0,0,0) of BOTH
+// passes into it. Pass null to switch tracing off.
+extern "C" int tpb_flash_bwd_set_trace(unsigned long long* buf, int cap) {
+  tpb::g_bwd_trace = buf;
+  tpb::g_bwd_trace_cap = cap;
   return 0;
 }

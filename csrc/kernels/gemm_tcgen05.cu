@@ -24,6 +24,11 @@ constexpr int kUmmaK = 16;
 constexpr int kGemmThreads = 192;  // warp0 TMA, warp1 MMA, warps 2..5 epilogue
 constexpr int kGroupM = 16;        // rasterisation: 16 M-tiles share a column sweep for L2 reuse
 
+// One unit of work of a CTA: a whole tile, or one K range of a tile of the split last wave.
+struct WorkItem {
+  int tile, kb0, kb1, split, nsplit, tail_idx;
+};
+
 template <int BLOCK_N>
 struct GemmCfg {
   static constexpr int kStages = BLOCK_N == 256 ? 4 : 6;
@@ -50,6 +55,12 @@ struct GemmParams {
   const uint32_t* b_flags;
   int rows_per_flag;
   uint32_t flag_want;
+  // ---- split-K of the last, partially filled wave: when the tiles left over after the full
+  // waves would occupy only a fraction of the CTAs, each of them is computed by `nsplit` CTAs over
+  // disjoint K ranges; the helpers store fp32 partials to `sk_ws` and bump `sk_flags[tail tile]`,
+  // the owner adds them in its epilogue (and resets the flag). Null sk_ws disables it.
+  float* sk_ws;
+  uint32_t* sk_flags;
   // ---- fused all-gather of one operand (ag_operand: 0 none, 1 = A rows, 2 = B rows). The
   // first n_copy blocks of the grid are copy CTAs: they pull the peers' row shards into the
   // local gathered buffer chunk by chunk and publish one flag per chunk; the GEMM producer
@@ -230,6 +241,34 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int tiles_n = (p.N + BLOCK_N - 1) / BLOCK_N;
   const int n_tiles = tiles_m * tiles_n;
   const int k_blocks = (p.K + kBlockK - 1) / kBlockK;
+  // schedule: full waves of whole tiles, then the tail tiles split along K over the idle CTAs
+  const int full_per_cta = n_tiles / nctas;
+  const int tail = n_tiles - full_per_cta * nctas;
+  int nsplit = 1;
+  if (p.sk_ws && tail > 0) {
+    nsplit = min(nctas / tail, k_blocks / 4);
+    if (nsplit > 8) nsplit = 8;
+    if (nsplit < 1) nsplit = 1;
+  }
+  const int n_units = tail * nsplit;
+  const int n_items = full_per_cta + ((nsplit > 1 ? bid < n_units : bid < tail) ? 1 : 0);
+  auto get_work = [&](int i) {
+    WorkItem w;
+    if (i < full_per_cta) {
+      w.tile = bid + i * nctas; w.kb0 = 0; w.kb1 = k_blocks; w.split = 0; w.nsplit = 1; w.tail_idx = 0;
+    } else if (nsplit > 1) {
+      w.tail_idx = bid / nsplit;
+      w.split = bid % nsplit;
+      w.nsplit = nsplit;
+      w.tile = full_per_cta * nctas + w.tail_idx;
+      const int qk = k_blocks / nsplit, rk = k_blocks % nsplit;  // every range is non-empty
+      w.kb0 = w.split * qk + min(w.split, rk);
+      w.kb1 = w.kb0 + qk + (w.split < rk ? 1 : 0);
+    } else {
+      w.tile = full_per_cta * nctas + bid; w.kb0 = 0; w.kb1 = k_blocks; w.split = 0; w.nsplit = 1; w.tail_idx = 0;
+    }
+    return w;
+  };
 
   if (threadIdx.x == 0) {
     *abort_w = 0;
@@ -260,7 +299,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = bid; tile < n_tiles && ok; tile += nctas) {
+      for (int wi = 0; wi < n_items && ok; ++wi) {
+        const WorkItem w = get_work(wi);
+        const int tile = w.tile;
         int tm, tn;
         tile_coords(tile, tiles_m, tiles_n, tm, tn);
         tm = (tm + p.tile_m_shift) % tiles_m;
@@ -280,7 +321,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           // rows were written with generic-proxy stores by other CTAs; order them before TMA reads
           asm volatile("fence.proxy.async.global;" ::: "memory");
         }
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
           int s = it % Cfg::kStages;
           uint32_t ph = (it / Cfg::kStages) & 1;
           if (!mbar_wait(&empty[s], ph ^ 1, wc, 1)) { ok = false; break; }
@@ -312,13 +353,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       constexpr uint32_t idesc = make_idesc_f16(kBlockM, BLOCK_N, 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
       uint32_t it = 0, lt = 0;
       bool ok = true;
-      for (int tile = bid; tile < n_tiles && ok; tile += nctas, ++lt) {
+      for (int wi = 0; wi < n_items && ok; ++wi, ++lt) {
+        const WorkItem w = get_work(wi);
         int as = lt & 1;
         uint32_t aph = (lt >> 1) & 1;
         if (!mbar_wait(&tempty[as], aph ^ 1, wc, 2)) break;
         tc_fence_after_sync();
         uint32_t d_tmem = tmem_base + as * BLOCK_N;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
           int s = it % Cfg::kStages;
           uint32_t ph = (it / Cfg::kStages) & 1;
           if (!mbar_wait(&full[s], ph, wc, 3)) { ok = false; break; }
@@ -331,7 +373,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                : make_smem_desc_sw128(sa + j * 32, 16, 1024);
             uint64_t db = B_MN ? make_smem_desc_sw128(sb + j * 2048, kBlockK * 128, 1024)
                                : make_smem_desc_sw128(sb + j * 32, 16, 1024);
-            umma_f16_ss(d_tmem, da, db, idesc, (kb | j) != 0);
+            umma_f16_ss(d_tmem, da, db, idesc, (kb != w.kb0) || (j != 0));
           }
           umma_commit(&empty[s]);
         }
@@ -342,7 +384,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------------------------------------ epilogue (4 warps)
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     uint32_t lt = 0;
-    for (int tile = bid; tile < n_tiles; tile += nctas, ++lt) {
+    for (int wi = 0; wi < n_items; ++wi, ++lt) {
+      const WorkItem w = get_work(wi);
+      const int tile = w.tile;
       int tm, tn;
       tile_coords(tile, tiles_m, tiles_n, tm, tn);
       tm = (tm + p.tile_m_shift) % tiles_m;
@@ -352,6 +396,40 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after_sync();
       const int row = tm * kBlockM + q * 32 + lane;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + as * BLOCK_N;
+      // split last wave: helpers park their fp32 partial tile in the workspace; the owner waits
+      // for them and folds them in below
+      float* sk_tile = nullptr;
+      if (w.nsplit > 1) {
+        sk_tile = p.sk_ws + ((size_t)w.tail_idx * (w.nsplit - 1)) * (size_t)(kBlockM * BLOCK_N);
+        if (w.split > 0) {
+          float* dst = sk_tile + (size_t)(w.split - 1) * (kBlockM * BLOCK_N) + (size_t)(q * 32 + lane) * BLOCK_N;
+#pragma unroll 1
+          for (int c = 0; c < BLOCK_N; c += 32) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(t_row + c, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              *reinterpret_cast<float4*>(dst + c + i) =
+                  make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
+                              __uint_as_float(r[i + 3]));
+          }
+          tc_fence_before_sync();
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(&tempty[as]);
+            red_release_gpu_add(p.sk_flags + w.tail_idx, 1u);
+          }
+          continue;
+        }
+        // owner: all helpers (4 warps each) must have stored their partials
+        bool got = true;
+        if (lane == 0)
+          got = flag_wait_ge(p.sk_flags + w.tail_idx, 4u * (w.nsplit - 1), false, p.status, p.wait_ns, 14);
+        got = __all_sync(0xffffffffu, got);
+        if (!got) { *abort_w = 1; break; }
+      }
 #pragma unroll 1
       for (int c = 0; c < BLOCK_N; c += 32) {
         const int col0 = tn * BLOCK_N + c;
@@ -362,7 +440,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (row < p.M) {
           float v[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          if (sk_tile) {
+            for (int h = 0; h < w.nsplit - 1; ++h) {
+              const float* src = sk_tile + (size_t)h * (kBlockM * BLOCK_N) + (size_t)(q * 32 + lane) * BLOCK_N + c;
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                float4 t4 = __ldcg(reinterpret_cast<const float4*>(src + i));
+                v[i] += t4.x; v[i + 1] += t4.y; v[i + 2] += t4.z; v[i + 3] += t4.w;
+              }
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] *= p.alpha;
           const bool full_chunk = (col0 + 32 <= p.N);
           if (p.bias) {
 #pragma unroll
@@ -447,6 +537,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[as]);
+      if (sk_tile && lane == 0) {
+        // each owner warp checks out after consuming the partials; the last one re-arms the flag
+        // (no warp can still be waiting: checking out happens after passing the wait)
+        const unsigned old = atomicAdd(p.sk_flags + w.tail_idx, 1u);
+        if (old == 4u * (w.nsplit - 1) + 3u) p.sk_flags[w.tail_idx] = 0;
+      }
       if (p.rs_mode) {
         __threadfence_system();
         __syncwarp();
@@ -532,6 +628,11 @@ int sm_count() {
   return n;
 }
 
+// Split-K workspace (fp32 partial tiles + one flag per tail tile), registered by the caller once
+// per device; GEMMs that use it must be stream-ordered with respect to each other.
+static float* g_sk_ws = nullptr;
+static uint32_t* g_sk_flags = nullptr;
+
 template <int BLOCK_N, bool A_MN, bool B_MN>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
                        int max_ctas, cudaStream_t stream) {
@@ -545,7 +646,10 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
     configured = true;
   }
   int tiles = ((p.M + kBlockM - 1) / kBlockM) * ((p.N + BLOCK_N - 1) / BLOCK_N);
-  int grid = (tiles < max_ctas ? tiles : max_ctas) + p.n_copy;
+  int grid = tiles < max_ctas ? tiles : max_ctas;
+  // few tiles and a deep reduction: launch every SM and let the tail split along K
+  if (p.sk_ws && tiles * 2 <= max_ctas && (p.K + kBlockK - 1) / kBlockK >= 8) grid = max_ctas;
+  grid += p.n_copy;
   if (grid <= 0) return 0;
   kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
   return (int)cudaGetLastError();
@@ -576,6 +680,7 @@ int gemm_bf16_dispatch(const void* A, const void* B, void* C, const void* bias, 
   p.b_flags = b_flags; p.rows_per_flag = rows_per_flag > 0 ? rows_per_flag : 1;
   p.flag_want = flag_want;
   p.n_copy = 0; p.ag_operand = 0; p.rs_mode = 0; p.tile_m_shift = 0; p.world = 1; p.rank = 0;
+  p.sk_ws = fused ? nullptr : g_sk_ws; p.sk_flags = g_sk_flags;
   if (fused) {
     p.n_copy = fused->n_copy; p.ag_operand = fused->ag_operand; p.world = fused->world;
     p.rank = fused->rank; p.ag_dst = fused->ag_dst; p.ag_shard_bytes = fused->ag_shard_bytes;
@@ -689,4 +794,16 @@ extern "C" int tpb_gemm_rs(const void* A, const void* B, void* out, int M, int N
   return tpb::gemm_bf16_dispatch(A, B, nullptr, nullptr, M, N, K, lda, ldb, N, a_mn, b_mn, 0, 0, 0,
                                  1.f, nullptr, 0, 0, 0, status, static_cast<cudaStream_t>(stream),
                                  &f);
+}
+
+// Bytes of fp32 workspace and number of flag words that tpb_gemm_set_splitk_workspace expects.
+extern "C" long long tpb_gemm_splitk_workspace_bytes() {
+  return (long long)tpb::sm_count() * 128 * 256 * 4;
+}
+// ws: tpb_gemm_splitk_workspace_bytes() bytes; flags: sm_count() zero-initialised uint32 words.
+// Passing null disables the split of the last wave.
+extern "C" int tpb_gemm_set_splitk_workspace(void* ws, uint32_t* flags) {
+  tpb::g_sk_ws = static_cast<float*>(ws);
+  tpb::g_sk_flags = flags;
+  return 0;
 }

@@ -59,6 +59,9 @@ int tpb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M
                   int lda, int ldb, int ldc, int a_mn, int b_mn, int out_f32, int bias_f32,
                   int accumulate, float alpha, uint32_t* status, void* stream);
 
+long long tpb_gemm_splitk_workspace_bytes();
+int tpb_gemm_set_splitk_workspace(void* ws, uint32_t* flags);
+
 int tpb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* res_out,
                     float* rstd, int rows, int H, long long x_stride, long long y_stride,
                     float eps, void* stream);

@@ -25,6 +25,7 @@ U32 = C.c_uint32
 
 _KERNEL_SIGS = {
     "tpb_gemm_bf16": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P],
+    "tpb_gemm_set_splitk_workspace": [P, P],
     "tpb_rmsnorm_fwd": [P, P, P, P, P, P, I, I, LL, LL, F, P],
     "tpb_rmsnorm_bwd_grid": [I, I],
     "tpb_rmsnorm_bwd": [P, P, P, P, P, P, P, P, P, I, I, I, LL, LL, LL, P],
@@ -70,7 +71,7 @@ def _load(name: str):
 
 # kernel launches issued by one call of each entry point (for launch accounting)
 _LAUNCHES = {"tpb_rmsnorm_bwd": 2, "tpb_layernorm_bwd": 3, "tpb_flash_bwd": 3, "tpb_rmsnorm_bwd_grid": 0,
-             "tpb_grouped_workspace_ints": 0, "tpb_grouped_gemm": 2}
+             "tpb_grouped_workspace_ints": 0, "tpb_gemm_set_splitk_workspace": 0, "tpb_grouped_gemm": 2}
 launch_count = 0
 
 

@@ -13,6 +13,31 @@ from .. import _native
 from ._common import lib, ptr, status_word, stream_ptr, use_native
 
 
+_splitk = {}
+
+
+def enable_splitk(device=None, enable: bool = True) -> None:
+    """Register (once per device) the fp32 workspace that lets the GEMM split the tiles of its
+    last, partially filled wave along K over the idle SMs. GEMMs sharing it must run on one
+    stream (they do: every op here launches on the current stream of the training loop)."""
+    import ctypes as C
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    L = lib()
+    raw = L._lib
+    raw.tpb_gemm_splitk_workspace_bytes.restype = C.c_longlong
+    if not enable:
+        _splitk.pop(dev.index, None)
+        L.tpb_gemm_set_splitk_workspace(None, None)
+        return
+    if dev.index not in _splitk:
+        nbytes = raw.tpb_gemm_splitk_workspace_bytes()
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        flags = torch.zeros(1024, dtype=torch.int32, device=dev)
+        _splitk[dev.index] = (ws, flags)
+    ws, flags = _splitk[dev.index]
+    L.tpb_gemm_set_splitk_workspace(ws.data_ptr(), flags.data_ptr())
+
+
 def _rowmajor(t: torch.Tensor) -> torch.Tensor:
     if t.stride(-1) != 1 or (t.dim() == 2 and (t.stride(0) % 8 or t.data_ptr() % 16)):
         t = t.contiguous()

@@ -60,6 +60,30 @@ def test_gemm_many_tiles_persistent():
     assert _rel(out, ref) < 5e-3
 
 
+@pytest.mark.parametrize("M,N,K", [(4096, 4096, 4096), (512, 1024, 8192), (4096, 6144, 2048), (1152, 2304, 1024)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (True, True)])
+def test_gemm_splitk_tail(M, N, K, a_mn, b_mn):
+    """The last partial wave is split along K over idle SMs; results must match the unsplit run."""
+    from tensorplay_b200.ops.gemm import enable_splitk
+    torch.manual_seed(5)
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
+    A = a.t().contiguous() if a_mn else a
+    B = b.t().contiguous() if b_mn else b
+    enable_splitk(enable=False)
+    base = O.gemm(A, B, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+    enable_splitk()
+    try:
+        for _ in range(3):  # flags must re-arm between calls
+            out = O.gemm(A, B, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+            O.check_status()
+            assert _rel(out, base) < 2e-6
+        outb = O.gemm(A, B, a_mn=a_mn, b_mn=b_mn)
+        assert _rel(outb, a.float() @ b.float().t()) < 5e-3
+    finally:
+        enable_splitk(enable=False)
+
+
 def test_linear_autograd():
     torch.manual_seed(3)
     x = torch.randn(4, 96, 256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
