@@ -59,7 +59,7 @@ __device__ __forceinline__ void trace_pt(const AttnBwdParams& p, int role, int i
 
 __device__ __forceinline__ float bwd_exp2(float x) {
   float y;
-  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));  // pure: let the compiler schedule it
   return y;
 }
 
@@ -319,6 +319,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
       mbar_arrive(&sdp_empty[s]);
       if (threadIdx.x == 64) trace_pt(p, 2, it, 2);
 
+      // tiles entirely inside the causal / length limits skip the per-element predicate
+      const int key_hi = DKV ? x0 + kStat - 1 : y0i + kStream - 1;
+      const int qry_lo = DKV ? y0i : x0;
+      const int qry_hi = DKV ? y0i + kStream - 1 : x0 + kStat - 1;
+      const bool need_mask = (key_hi >= p.Tk) || (qry_hi >= p.Tq) || (p.causal && key_hi > qry_lo + p.kv_offset);
       float pv[64], dsv[64];
       const float* lse_col = nullptr;
       const float* delta_col = nullptr;
@@ -347,7 +352,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
           const int yi = y0i + col;
           const int key = DKV ? xi : yi;
           const int qry = DKV ? yi : xi;
-          const bool valid = (key < p.Tk) && (qry < p.Tq) && (!p.causal || key <= qry + p.kv_offset);
+          const bool valid = !need_mask ||
+                             ((key < p.Tk) && (qry < p.Tq) && (!p.causal || key <= qry + p.kv_offset));
           float sv = __uint_as_float(sr[col >> 5][col & 31]);
           float dp = __uint_as_float(dr[col >> 5][col & 31]);
           float pr = valid ? bwd_exp2(sv * p.scale_log2e - l4[i]) : 0.f;

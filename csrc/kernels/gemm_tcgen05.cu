@@ -247,7 +247,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   int nsplit = 1;
   if (p.sk_ws && tail > 0) {
     nsplit = min(nctas / tail, k_blocks / 4);
-    if (nsplit > 8) nsplit = 8;
+    if (nsplit > 16) nsplit = 16;
     if (nsplit < 1) nsplit = 1;
   }
   const int n_units = tail * nsplit;
@@ -547,8 +547,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         __threadfence_system();
         __syncwarp();
         if (lane == 0) {
-          const int d = (tm * kBlockM) / p.rs_rows_per_rank;
-          red_release_sys_add(p.rs_cnt[d] + p.rank, 1u);
+          // one arrival per destination rank whose rows this warp's 32-row block touched
+          const int r0 = tm * kBlockM + q * 32;
+          const int r1 = min(r0 + 32, p.M) - 1;
+          if (r1 >= r0)
+            for (int d = r0 / p.rs_rows_per_rank; d <= r1 / p.rs_rows_per_rank; ++d)
+              red_release_sys_add(p.rs_cnt[d] + p.rank, 1u);
         }
       }
     }
@@ -680,7 +684,7 @@ int gemm_bf16_dispatch(const void* A, const void* B, void* C, const void* bias, 
   p.b_flags = b_flags; p.rows_per_flag = rows_per_flag > 0 ? rows_per_flag : 1;
   p.flag_want = flag_want;
   p.n_copy = 0; p.ag_operand = 0; p.rs_mode = 0; p.tile_m_shift = 0; p.world = 1; p.rank = 0;
-  p.sk_ws = fused ? nullptr : g_sk_ws; p.sk_flags = g_sk_flags;
+  p.sk_ws = g_sk_ws; p.sk_flags = g_sk_flags;
   if (fused) {
     p.n_copy = fused->n_copy; p.ag_operand = fused->ag_operand; p.world = fused->world;
     p.rank = fused->rank; p.ag_dst = fused->ag_dst; p.ag_shard_bytes = fused->ag_shard_bytes;
@@ -758,7 +762,7 @@ extern "C" int tpb_ag_gemm(size_t a_off, const void* B, void* C, const void* bia
   f.pad_local = reinterpret_cast<uint32_t*>(sv->peer[rank] + pad_off);
   f.ready_slot = ready_slot; f.done_slot = done_slot; f.epoch = epoch;
   const int tiles_m = (M + 127) / 128;
-  f.tile_m_shift = (int)(((long long)rank * rows_per_rank / 128) % tiles_m);
+  f.tile_m_shift = (rows_per_rank % 128 == 0) ? (int)(((long long)rank * rows_per_rank / 128) % tiles_m) : 0;
   f.wait_ns = wait_s > 0 ? (unsigned long long)(wait_s * 1e9) : 0;
   return tpb::gemm_bf16_dispatch(sv->peer[rank] + a_off, B, C, bias, M, N, K, K, ldb, ldc, 0, b_mn,
                                  out_f32, 0, 0, 1.f, nullptr, 0, 0, 0, status,
@@ -773,7 +777,7 @@ extern "C" int tpb_gemm_rs(const void* A, const void* B, void* out, int M, int N
                            int cnt_slot, uint32_t epoch, double wait_s, uint32_t* status,
                            void* stream) {
   const tpb::SymmView* sv = tpb::symm_view();
-  if (!sv || sv->world < 1 || M % (sv->world * 128) || N % 8) return -2;
+  if (!sv || sv->world < 1 || M % sv->world || N % 8) return -2;
   const int world = sv->world, rank = sv->rank;
   tpb::GemmFused f;
   memset(&f, 0, sizeof(f));
@@ -785,11 +789,17 @@ extern "C" int tpb_gemm_rs(const void* A, const void* B, void* out, int M, int N
     f.rs_cnt[r] = reinterpret_cast<uint32_t*>(sv->peer[r] + pad_off) + cnt_slot;
   }
   const int block_n = N > 128 ? 256 : 128;
-  const int tiles_per_rank = (f.rs_rows_per_rank / 128) * ((N + block_n - 1) / block_n);
-  f.rs_expect = epoch * (uint32_t)tiles_per_rank * 4u;
+  // arrivals this rank expects from each source per call: one per (N tile, 32-row block that
+  // overlaps this rank's rows)
+  const int my0 = rank * f.rs_rows_per_rank, my1 = my0 + f.rs_rows_per_rank - 1;
+  const int row_blocks = my1 / 32 - my0 / 32 + 1;
+  const int per_call = row_blocks * ((N + block_n - 1) / block_n);
+  f.rs_expect = epoch * (uint32_t)per_call;
   f.rs_out = static_cast<__nv_bfloat16*>(out);
-  const int tiles_m = M / 128;
-  f.tile_m_shift = (int)(((long long)((rank + 1) % world) * f.rs_rows_per_rank / 128) % tiles_m);
+  const int tiles_m = (M + 127) / 128;
+  f.tile_m_shift = (f.rs_rows_per_rank % 128 == 0)
+                       ? (int)(((long long)((rank + 1) % world) * f.rs_rows_per_rank / 128) % tiles_m)
+                       : 0;
   f.wait_ns = wait_s > 0 ? (unsigned long long)(wait_s * 1e9) : 0;
   return tpb::gemm_bf16_dispatch(A, B, nullptr, nullptr, M, N, K, lda, ldb, N, a_mn, b_mn, 0, 0, 0,
                                  1.f, nullptr, 0, 0, 0, status, static_cast<cudaStream_t>(stream),

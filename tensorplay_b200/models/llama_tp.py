@@ -1,0 +1,169 @@
+"""Tensor-parallel Llama (Megatron-style TP with a sequence-parallel residual stream) for
+inference and training on the fused kernels:
+
+    x_local [rows/tp, H] --rmsnorm--> all-gather->GEMM (QKV shard) --> RoPE + flash attention over
+    the local heads --> GEMM->reduce-scatter (o_proj shard) --> residual
+    --rmsnorm--> all-gather->GEMM (gate/up shard) --> SwiGLU --> GEMM->reduce-scatter (down shard)
+
+Every rank builds only its own weight shards (no rank ever holds the full model), keeps a KV
+cache for its local KV heads in the token-major layout the attention kernel reads, and the LM
+head is vocabulary-parallel (greedy decoding merges per-shard maxima).
+The reference has no TP inference runner: users apply ``parallelize_module`` to a model and call
+``generate`` on every rank (tensorplay/nn/generation.py:73-164).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+from torch import Tensor, nn
+
+from .. import ops
+from ..ops.attention import flash_attention
+from ..parallel.tp import TPContext
+from .llama import LlamaConfig
+
+
+class LlamaTPBlock(nn.Module):
+    def __init__(self, cfg: LlamaConfig, tp: TPContext, layer_idx: int, device=None, dtype=None):
+        super().__init__()
+        kw = {"device": device, "dtype": dtype}
+        w = tp.world
+        assert cfg.num_heads % w == 0 and cfg.num_kv_heads % w == 0 and cfg.ffn_size % w == 0
+        self.cfg, self.tp, self.layer_idx = cfg, tp, layer_idx
+        self.hq, self.hkv, self.ff = cfg.num_heads // w, cfg.num_kv_heads // w, cfg.ffn_size // w
+        H, D = cfg.hidden_size, cfg.head_dim
+        self.attn_norm = nn.Parameter(torch.ones(H, **kw))
+        self.wqkv = nn.Parameter(torch.empty((self.hq + 2 * self.hkv) * D, H, **kw))
+        self.wo = nn.Parameter(torch.empty(H, self.hq * D, **kw))
+        self.ffn_norm = nn.Parameter(torch.ones(H, **kw))
+        self.w_gate_up = nn.Parameter(torch.empty(2 * self.ff, H, **kw))
+        self.w_down = nn.Parameter(torch.empty(H, self.ff, **kw))
+        self.k_cache: Optional[Tensor] = None
+        self.v_cache: Optional[Tensor] = None
+
+    def reset_parameters(self, gen=None):
+        for p in (self.wqkv, self.wo, self.w_gate_up, self.w_down):
+            nn.init.normal_(p, std=self.cfg.init_std, generator=gen)
+
+    def forward(self, x_local: Tensor, B: int, T: int, cos: Tensor, sin: Tensor, pos0: int = 0,
+                use_cache: bool = False) -> Tensor:
+        cfg, tp = self.cfg, self.tp
+        D = cfg.head_dim
+        h = ops.rms_norm(x_local, self.attn_norm, cfg.rms_eps)
+        qkv = tp.all_gather_linear(h, self.wqkv).view(B, T, self.hq + 2 * self.hkv, D)
+        pos = None
+        if pos0:
+            pos = torch.arange(pos0, pos0 + T, device=qkv.device).expand(B, T)
+        qk = ops.apply_rope(qkv[:, :, : self.hq + self.hkv], cos, sin, pos)
+        q, k, v = qk[:, :, : self.hq], qk[:, :, self.hq:], qkv[:, :, self.hq + self.hkv:]
+        if use_cache:
+            self.k_cache[:B, pos0: pos0 + T] = k
+            self.v_cache[:B, pos0: pos0 + T] = v
+            k, v = self.k_cache[:B, : pos0 + T], self.v_cache[:B, : pos0 + T]
+        if T == 1 and use_cache and self.hq % self.hkv == 0:
+            # decode: the query heads of a KV group become the rows of one attention tile
+            G = self.hq // self.hkv
+            o = flash_attention(q.reshape(B, self.hkv, G, D).transpose(1, 2), k, v, causal=False)
+            o = o.transpose(1, 2).reshape(B * T, self.hq * D)
+        else:
+            o = flash_attention(q, k, v, causal=True).reshape(B * T, self.hq * D)
+        x_local = x_local + tp.linear_reduce_scatter(o, self.wo)
+        h = ops.rms_norm(x_local, self.ffn_norm, cfg.rms_eps)
+        gu = tp.all_gather_linear(h, self.w_gate_up)
+        a = ops.swiglu_packed(gu)
+        return x_local + tp.linear_reduce_scatter(a, self.w_down)
+
+
+class LlamaTP(nn.Module):
+    def __init__(self, cfg: LlamaConfig, tp: TPContext, device=None, dtype=None):
+        super().__init__()
+        kw = {"device": device, "dtype": dtype}
+        self.cfg, self.tp = cfg, tp
+        w = tp.world
+        self.vshard = (cfg.vocab_size + w - 1) // w
+        self.embed = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, **kw))  # replicated
+        self.layers = nn.ModuleList([LlamaTPBlock(cfg, tp, i, **kw) for i in range(cfg.num_layers)])
+        self.final_norm = nn.Parameter(torch.ones(cfg.hidden_size, **kw))
+        self.lm_head = nn.Parameter(torch.empty(self.vshard, cfg.hidden_size, **kw))  # vocabulary shard
+        self._rope = None
+
+    def reset_parameters(self, seed: int = 0) -> None:
+        dev = self.embed.device
+        g_rep = torch.Generator(device=dev).manual_seed(seed)          # same on every rank
+        g_loc = torch.Generator(device=dev).manual_seed(seed + 1 + self.tp.rank)  # per-rank shards
+        nn.init.normal_(self.embed, std=self.cfg.init_std, generator=g_rep)
+        nn.init.normal_(self.lm_head, std=self.cfg.init_std, generator=g_loc)
+        for l in self.layers:
+            l.reset_parameters(g_loc)
+
+    def allocate_cache(self, batch: int, max_len: int) -> None:
+        for l in self.layers:
+            shape = (batch, max_len, l.hkv, self.cfg.head_dim)
+            l.k_cache = torch.zeros(shape, dtype=self.embed.dtype, device=self.embed.device)
+            l.v_cache = torch.zeros(shape, dtype=self.embed.dtype, device=self.embed.device)
+
+    def rope_tables(self, n: int, device):
+        if self._rope is None or self._rope[0].shape[0] < n:
+            self._rope = ops.rope_tables(n, self.cfg.head_dim, self.cfg.rope_theta, device=device)
+        return self._rope
+
+    def _local_rows(self, tokens: Tensor) -> Tensor:
+        """Embedding rows of this rank's slice of the flattened (batch, time) token list."""
+        w, r = self.tp.world, self.tp.rank
+        flat = tokens.reshape(-1)
+        n = flat.numel() // w
+        return self.embed.index_select(0, flat[r * n: (r + 1) * n])
+
+    def hidden(self, tokens: Tensor, pos0: int = 0, use_cache: bool = False) -> Tensor:
+        B, T = tokens.shape
+        assert (B * T) % self.tp.world == 0
+        cos, sin = self.rope_tables(max(pos0 + T, self.cfg.max_seq_len), tokens.device)
+        x = self._local_rows(tokens)
+        for l in self.layers:
+            x = l(x, B, T, cos, sin, pos0, use_cache)
+        return x  # [B*T / tp, H], rows of this rank
+
+    def last_token_hidden(self, x_local: Tensor, B: int, T: int) -> Tensor:
+        """``[B, H]`` hidden state of each sequence's last position, on every rank."""
+        w, r = self.tp.world, self.tp.rank
+        n = (B * T) // w
+        rows = torch.arange(B, device=x_local.device) * T + (T - 1)
+        mine = (rows >= r * n) & (rows < (r + 1) * n)
+        out = torch.zeros(B, x_local.shape[1], dtype=torch.float32, device=x_local.device)
+        out[mine] = x_local[(rows[mine] - r * n)].float()
+        if w > 1:
+            dist.all_reduce(out, group=self.tp.group)
+        return out.to(x_local.dtype)
+
+    def greedy_next(self, h_last: Tensor) -> Tensor:
+        """Argmax over the vocabulary-parallel logits of ``h_last [B, H]``."""
+        h = ops.rms_norm(h_last, self.final_norm, self.cfg.rms_eps)
+        logits = ops.linear(h, self.lm_head).float()  # [B, V/tp]
+        w, r = self.tp.world, self.tp.rank
+        valid = min(self.vshard, self.cfg.vocab_size - r * self.vshard)
+        if valid < self.vshard:
+            logits[:, valid:] = float("-inf")
+        m, idx = logits.max(dim=-1)
+        idx = idx + r * self.vshard
+        if w == 1:
+            return idx
+        pair = torch.stack((m, idx.float()), dim=-1)  # [B, 2]
+        allp = [torch.empty_like(pair) for _ in range(w)]
+        dist.all_gather(allp, pair, group=self.tp.group)
+        allp = torch.stack(allp)  # [w, B, 2]
+        best = allp[..., 0].argmax(dim=0)
+        return allp[best, torch.arange(pair.shape[0], device=pair.device), 1].long()
+
+    @torch.no_grad()
+    def prefill(self, tokens: Tensor) -> Tensor:
+        B, T = tokens.shape
+        x = self.hidden(tokens, 0, use_cache=True)
+        return self.greedy_next(self.last_token_hidden(x, B, T))
+
+    @torch.no_grad()
+    def decode_step(self, last_tokens: Tensor, pos: int) -> Tensor:
+        B = last_tokens.shape[0]
+        x = self.hidden(last_tokens.view(B, 1), pos, use_cache=True)
+        return self.greedy_next(self.last_token_hidden(x, B, 1))

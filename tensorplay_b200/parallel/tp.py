@@ -96,7 +96,7 @@ class GemmRSPlan:
 
     def __init__(self, arena: SymmArena, m_total: int, n: int, wait_s: float = 30.0):
         w = arena.world
-        assert m_total % (w * 128) == 0 and n % 8 == 0
+        assert m_total % w == 0 and n % 8 == 0
         self.arena, self.m, self.n, self.world, self.rank = arena, m_total, n, w, arena.rank
         self.rows = m_total // w
         self.stage = [arena.alloc(m_total * n, torch.bfloat16) for _ in range(2)]
@@ -210,7 +210,7 @@ class TPContext:
         """``all_gather_rows(x_local) @ weight.T`` -> ``[rows * world, N_shard]``."""
         rows, k = x_local.reshape(-1, x_local.shape[-1]).shape
         m = rows * self.world
-        if self.arena is not None and x_local.is_cuda and x_local.dtype == torch.bfloat16 and m % (self.world * 128) == 0:
+        if self.arena is not None and x_local.is_cuda and x_local.dtype == torch.bfloat16:
             return _AGLinearFn.apply(x_local, weight, self.ag_plan(m, k), self.rs_plan(m, k))
         return _ag_linear_ref(x_local.reshape(rows, k), weight, self.group)
 
@@ -218,7 +218,7 @@ class TPContext:
         """``reduce_scatter_rows(x @ weight.T)`` -> ``[rows / world, N]``."""
         x2 = x.reshape(-1, x.shape[-1])
         m, n = x2.shape[0], weight.shape[0]
-        if self.arena is not None and x.is_cuda and x.dtype == torch.bfloat16 and m % (self.world * 128) == 0:
+        if self.arena is not None and x.is_cuda and x.dtype == torch.bfloat16 and m % self.world == 0:
             return _LinearRSFn.apply(x2, weight, self.rs_plan(m, n), self.ag_plan(m, n))
         return _linear_rs_ref(x2, weight, self.group)
 

@@ -53,3 +53,11 @@ def test_moe_expert_parallel_dispatch_combine():
     r = _run_workers("moe_ep_worker.py", n)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "RESULT" in r.stdout
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_tp_llama_prefill_and_decode():
+    n = 2 if _ngpu() < 4 else 4
+    r = _run_workers("tp_llama_worker.py", n)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "RESULT" in r.stdout
