@@ -42,6 +42,7 @@ struct AttnBwdParams {
   unsigned long long wait_ns;
   unsigned long long* trace;  // optional: timestamps of CTA (0,0,0), see tpb_flash_bwd_set_trace
   int trace_cap;
+  int debug;  // probe switches (results are wrong when set): 1 = no exp2, 2 = no P/dS math at all
 };
 
 // Debug aid: records (role, iteration, phase, globaltimer) tuples of block (0,0,0).
@@ -327,19 +328,27 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
       float pv[64], dsv[64];
       const float* lse_col = nullptr;
       const float* delta_col = nullptr;
+      uint32_t lse_sa = 0;
+      (void)delta_col;
       if (DKV) {
         // statistics landed with the tile (the wait below returns at once and orders the read)
         const int ys = it % kYStages;
         if (!mbar_wait_warp(&y_full[ys], (it / kYStages) & 1, wc, 9)) { ok = false; break; }
         lse_col = reinterpret_cast<const float*>(smem + L::kStats) + ys * 2 * kStream;
         delta_col = lse_col + kStream;
+        lse_sa = smem_u32(lse_col);
       }
+      if (p.debug & 2) {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) { pv[c] = __uint_as_float(sr[c >> 5][c & 31]); dsv[c] = __uint_as_float(dr[c >> 5][c & 31]); }
+      } else
 #pragma unroll
       for (int c = 0; c < 64; c += 4) {
         float l4[4], d4[4];
         if (DKV) {
-          float4 a = *reinterpret_cast<const float4*>(lse_col + c);
-          float4 d = *reinterpret_cast<const float4*>(delta_col + c);
+          float4 a, d;
+          asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w) : "r"(lse_sa + c * 4));
+          asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(d.x), "=f"(d.y), "=f"(d.z), "=f"(d.w) : "r"(lse_sa + (kStream + c) * 4));
           l4[0] = a.x * log2e; l4[1] = a.y * log2e; l4[2] = a.z * log2e; l4[3] = a.w * log2e;
           d4[0] = d.x; d4[1] = d.y; d4[2] = d.z; d4[3] = d.w;
         } else {
@@ -356,7 +365,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
                              ((key < p.Tk) && (qry < p.Tq) && (!p.causal || key <= qry + p.kv_offset));
           float sv = __uint_as_float(sr[col >> 5][col & 31]);
           float dp = __uint_as_float(dr[col >> 5][col & 31]);
-          float pr = valid ? bwd_exp2(sv * p.scale_log2e - l4[i]) : 0.f;
+          float pr = valid ? ((p.debug & 1) ? (sv * p.scale_log2e - l4[i]) : bwd_exp2(sv * p.scale_log2e - l4[i])) : 0.f;
           pv[col] = pr;
           dsv[col] = valid ? pr * (dp - d4[i]) * p.scale : 0.f;
         }
@@ -459,6 +468,7 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o,
 
 static unsigned long long* g_bwd_trace = nullptr;
 static int g_bwd_trace_cap = 0;
+static int g_bwd_debug = 0;
 
 template <int D, bool DKV>
 static int launch_bwd(const CUtensorMap& x0, const CUtensorMap& x1, const CUtensorMap& y0,
@@ -513,7 +523,7 @@ extern "C" int tpb_flash_bwd(const void* dout, const void* q, const void* k, con
   p.kv_offset = Tk - Tq; p.scale = scale; p.scale_log2e = scale * 1.4426950408889634f;
   p.lse = lse; p.delta = delta; p.lse_stride = lse_stride; p.status = status;
   p.wait_ns = kDefaultWaitNs;
-  p.trace = g_bwd_trace; p.trace_cap = g_bwd_trace_cap;
+  p.trace = g_bwd_trace; p.trace_cap = g_bwd_trace_cap; p.debug = g_bwd_debug;
   int r;
   // ---- dK / dV: [B, Tk, Hkv, D] by the dkv strides (dk and dv share them)
   {
@@ -549,6 +559,10 @@ extern "C" int tpb_flash_bwd(const void* dout, const void* q, const void* k, con
 // Debug aid: buf = device array of 1 + 2 * cap uint64 (buf[0] = record count, zero it first). The
 // next backward launches record role / iteration / phase timestamps of block (0,0,0) of BOTH
 // passes into it. Pass null to switch tracing off.
+extern "C" int tpb_flash_bwd_set_debug(int flags) {
+  tpb::g_bwd_debug = flags;
+  return 0;
+}
 extern "C" int tpb_flash_bwd_set_trace(unsigned long long* buf, int cap) {
   tpb::g_bwd_trace = buf;
   tpb::g_bwd_trace_cap = cap;

@@ -77,7 +77,7 @@ def test_gemm_splitk_tail(M, N, K, a_mn, b_mn):
         for _ in range(3):  # flags must re-arm between calls
             out = O.gemm(A, B, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
             O.check_status()
-            assert _rel(out, base) < 2e-6
+            assert _rel(out, base) < 2e-5
         outb = O.gemm(A, B, a_mn=a_mn, b_mn=b_mn)
         assert _rel(outb, a.float() @ b.float().t()) < 5e-3
     finally:
