@@ -224,14 +224,21 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       const float alpha = fast_exp2(m - mx);
       m = mx;
+      // p = exp2(s - max) evaluated two at a time in bf16 (ex2.approx.bf16x2): P is consumed as bf16
+      // by the second MMA anyway, the packed form halves the MUFU work, and the row sum adds
+      // exactly the rounded values that the MMA multiplies with V.
       float sum = 0.f;
+      uint32_t pw[64];
 #pragma unroll
       for (int c = 0; c < 4; ++c)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float e = fast_exp2(__uint_as_float(sr[c][i]) - mx);
-          sum += e;
-          sr[c][i] = __float_as_uint(e);
+        for (int i = 0; i < 32; i += 2) {
+          __nv_bfloat162 d = __floats2bfloat162_rn(__uint_as_float(sr[c][i]) - mx,
+                                                   __uint_as_float(sr[c][i + 1]) - mx);
+          uint32_t e;
+          asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(e) : "r"(*reinterpret_cast<uint32_t*>(&d)));
+          sum += __uint_as_float(e << 16) + __uint_as_float(e & 0xffff0000u);
+          pw[c * 16 + i / 2] = e;
         }
       l = l * alpha + sum;
 
@@ -259,27 +266,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       // P (bf16) into the swizzled tile: chunk = key / 64, 16-byte slot = (key % 64) / 8
       uint8_t* prow = smem + L::kPOff + row * 128;
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint4 v;
-          __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(sr[c][g * 8 + 0]),
-                                                    __uint_as_float(sr[c][g * 8 + 1]));
-          __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(sr[c][g * 8 + 2]),
-                                                    __uint_as_float(sr[c][g * 8 + 3]));
-          __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(sr[c][g * 8 + 4]),
-                                                    __uint_as_float(sr[c][g * 8 + 5]));
-          __nv_bfloat162 t3 = __floats2bfloat162_rn(__uint_as_float(sr[c][g * 8 + 6]),
-                                                    __uint_as_float(sr[c][g * 8 + 7]));
-          v.x = *reinterpret_cast<uint32_t*>(&t0);
-          v.y = *reinterpret_cast<uint32_t*>(&t1);
-          v.z = *reinterpret_cast<uint32_t*>(&t2);
-          v.w = *reinterpret_cast<uint32_t*>(&t3);
-          const int key = c * 32 + g * 8;
-          const int chunk = key >> 6;
-          const int slot = (key & 63) >> 3;
-          *reinterpret_cast<uint4*>(prow + chunk * (kBlockQ * 128) + ((slot ^ (row & 7)) << 4)) = v;
-        }
+      for (int g = 0; g < 16; ++g) {  // 16 groups of 8 keys
+        uint4 v = make_uint4(pw[g * 4 + 0], pw[g * 4 + 1], pw[g * 4 + 2], pw[g * 4 + 3]);
+        const int key = g * 8;
+        const int chunk = key >> 6;
+        const int slot = (key & 63) >> 3;
+        *reinterpret_cast<uint4*>(prow + chunk * (kBlockQ * 128) + ((slot ^ (row & 7)) << 4)) = v;
+      }
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(p_full);

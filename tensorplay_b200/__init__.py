@@ -20,11 +20,16 @@ import torch as _torch
 __version__ = "0.1.0"
 
 # ---- everything torch exposes at top level (functions, dtypes, grad modes, ...)
+import types as _types
+
 for _n in dir(_torch):
     if _n.startswith("_"):
         continue
-    globals()[_n] = getattr(_torch, _n)
-del _n
+    _v = getattr(_torch, _n)
+    if isinstance(_v, _types.ModuleType):
+        continue  # sub-packages are resolved below (ours first, torch's lazily)
+    globals()[_n] = _v
+del _n, _v
 
 Tensor = _torch.Tensor
 DType = _torch.dtype
@@ -33,11 +38,11 @@ dtype = _torch.dtype
 device = _torch.device
 
 # ---- own subpackages (imported eagerly: they are light) and torch-backed ones (lazy)
-from . import ops  # noqa: E402
-from . import nn  # noqa: E402
-from . import optim  # noqa: E402
-from . import amp  # noqa: E402
-from . import serialization  # noqa: E402
+ops = _importlib.import_module(__name__ + ".ops")
+nn = _importlib.import_module(__name__ + ".nn")
+optim = _importlib.import_module(__name__ + ".optim")
+amp = _importlib.import_module(__name__ + ".amp")
+serialization = _importlib.import_module(__name__ + ".serialization")
 from .serialization import inspect_checkpoint, load, save  # noqa: E402
 from .nn.generation import sample  # noqa: E402
 
