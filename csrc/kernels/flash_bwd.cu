@@ -23,7 +23,8 @@ namespace tpb {
 int make_tmap_bthd(CUtensorMap* out, const void* base, int B, int T, int H, int D,
                    long long tok_stride, long long head_stride, long long batch_stride, int rows);
 
-constexpr int kBwdThreads = 192;
+constexpr int kBwdThreads = 320;  // TMA warp, MMA warp, 8 P/dS warps (two per TMEM lane quarter)
+constexpr int kSoftThreads = 256;
 constexpr int kStat = 128;   // rows of the stationary tiles
 constexpr int kStream = 64;  // rows of the streamed tiles
 constexpr int kYStages = 3;  // streamed-tile ring: loads run two tiles ahead of the MMAs
@@ -79,6 +80,26 @@ struct BwdSmem {
   static constexpr int kBar = kStats + kYStages * 2 * kStream * 4;
   static constexpr int kTotal = kBar + 256 + 1024;
 };
+
+// 32 consecutive bf16 values (fp32 in v[]) of a row, starting at column 32 * half, into a
+// swizzled [128][64] tile.
+__device__ __forceinline__ void store_row32_sw128(uint8_t* tile, int row, int half, const float (&v)[32]) {
+  uint8_t* prow = tile + row * 128;
+#pragma unroll
+  for (int gg = 0; gg < 4; ++gg) {
+    const int g = half * 4 + gg;
+    uint4 u;
+    __nv_bfloat162 t0 = __floats2bfloat162_rn(v[gg * 8 + 0], v[gg * 8 + 1]);
+    __nv_bfloat162 t1 = __floats2bfloat162_rn(v[gg * 8 + 2], v[gg * 8 + 3]);
+    __nv_bfloat162 t2 = __floats2bfloat162_rn(v[gg * 8 + 4], v[gg * 8 + 5]);
+    __nv_bfloat162 t3 = __floats2bfloat162_rn(v[gg * 8 + 6], v[gg * 8 + 7]);
+    u.x = *reinterpret_cast<uint32_t*>(&t0);
+    u.y = *reinterpret_cast<uint32_t*>(&t1);
+    u.z = *reinterpret_cast<uint32_t*>(&t2);
+    u.w = *reinterpret_cast<uint32_t*>(&t3);
+    *reinterpret_cast<uint4*>(prow + ((g ^ (row & 7)) << 4)) = u;
+  }
+}
 
 // bf16 row of 64 values (fp32 in v[]) into a swizzled [128][64] tile.
 __device__ __forceinline__ void store_row64_sw128(uint8_t* tile, int row, const float (&v)[64]) {
@@ -159,9 +180,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sdp_full[i], 1);
-      mbar_init(&sdp_empty[i], 128);
+      mbar_init(&sdp_empty[i], kSoftThreads);
     }
-    mbar_init(pds_full, 128);
+    mbar_init(pds_full, kSoftThreads);
     mbar_init(acc_done, 1);
     fence_barrier_init();
     prefetch_tmap(&tmX0);
@@ -287,6 +308,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
   } else {
     // ---------------------------------------------------------------- P / dS warps
     const int qd = warp & 3;
+    const int half = (warp - 2) >> 2;  // which 32 of the tile's 64 columns this warp handles
     const int row = qd * 32 + lane;
     const int xi = x0 + row;  // key index (DKV) or query index (dQ)
     const uint32_t t_lane = ((uint32_t)(qd * 32) << 16);
@@ -303,47 +325,40 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
     for (int it = 0; it < n_it; ++it) {
       const int s = it & 1;
       const uint32_t ph = (it >> 1) & 1;
-      int hy, yb;
-      if (DKV) { hy = hx * G + it / y_count; yb = y_first + it % y_count; }
-      else { hy = hx; yb = it; }
-      const int y0i = yb * kStream;  // first query (DKV) or key (dQ) of the streamed tile
+      int yb;
+      if (DKV) yb = y_first + it % y_count;
+      else yb = it;
+      const int y0i = yb * kStream + half * 32;  // first query (DKV) or key (dQ) of this warp's columns
       if (!mbar_wait_warp(&sdp_full[s], ph, wc, 6)) { ok = false; break; }
       if (threadIdx.x == 64) trace_pt(p, 2, it, 1);
       tc_fence_after_sync();
-      uint32_t sr[2][32], dr[2][32];
-      tmem_ld_32x32b_x32(tmem_base + t_lane + s * 128, sr[0]);
-      tmem_ld_32x32b_x32(tmem_base + t_lane + s * 128 + 32, sr[1]);
-      tmem_ld_32x32b_x32(tmem_base + t_lane + s * 128 + 64, dr[0]);
-      tmem_ld_32x32b_x32(tmem_base + t_lane + s * 128 + 96, dr[1]);
+      uint32_t sr[32], dr[32];
+      tmem_ld_32x32b_x32(tmem_base + t_lane + s * 128 + half * 32, sr);
+      tmem_ld_32x32b_x32(tmem_base + t_lane + s * 128 + 64 + half * 32, dr);
       tmem_ld_wait();
       tc_fence_before_sync();
       mbar_arrive(&sdp_empty[s]);
       if (threadIdx.x == 64) trace_pt(p, 2, it, 2);
 
       // tiles entirely inside the causal / length limits skip the per-element predicate
-      const int key_hi = DKV ? x0 + kStat - 1 : y0i + kStream - 1;
+      const int key_hi = DKV ? x0 + kStat - 1 : y0i + 31;
       const int qry_lo = DKV ? y0i : x0;
-      const int qry_hi = DKV ? y0i + kStream - 1 : x0 + kStat - 1;
+      const int qry_hi = DKV ? y0i + 31 : x0 + kStat - 1;
       const bool need_mask = (key_hi >= p.Tk) || (qry_hi >= p.Tq) || (p.causal && key_hi > qry_lo + p.kv_offset);
-      float pv[64], dsv[64];
-      const float* lse_col = nullptr;
-      const float* delta_col = nullptr;
+      float pv[32], dsv[32];
       uint32_t lse_sa = 0;
-      (void)delta_col;
       if (DKV) {
         // statistics landed with the tile (the wait below returns at once and orders the read)
         const int ys = it % kYStages;
         if (!mbar_wait_warp(&y_full[ys], (it / kYStages) & 1, wc, 9)) { ok = false; break; }
-        lse_col = reinterpret_cast<const float*>(smem + L::kStats) + ys * 2 * kStream;
-        delta_col = lse_col + kStream;
-        lse_sa = smem_u32(lse_col);
+        lse_sa = smem_u32(smem + L::kStats) + (ys * 2 * kStream + half * 32) * 4;
       }
       if (p.debug & 2) {
 #pragma unroll
-        for (int c = 0; c < 64; ++c) { pv[c] = __uint_as_float(sr[c >> 5][c & 31]); dsv[c] = __uint_as_float(dr[c >> 5][c & 31]); }
+        for (int c = 0; c < 32; ++c) { pv[c] = __uint_as_float(sr[c]); dsv[c] = __uint_as_float(dr[c]); }
       } else
 #pragma unroll
-      for (int c = 0; c < 64; c += 4) {
+      for (int c = 0; c < 32; c += 4) {
         float l4[4], d4[4];
         if (DKV) {
           float4 a, d;
@@ -363,8 +378,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
           const int qry = DKV ? yi : xi;
           const bool valid = !need_mask ||
                              ((key < p.Tk) && (qry < p.Tq) && (!p.causal || key <= qry + p.kv_offset));
-          float sv = __uint_as_float(sr[col >> 5][col & 31]);
-          float dp = __uint_as_float(dr[col >> 5][col & 31]);
+          float sv = __uint_as_float(sr[col]);
+          float dp = __uint_as_float(dr[col]);
           float pr = valid ? ((p.debug & 1) ? (sv * p.scale_log2e - l4[i]) : bwd_exp2(sv * p.scale_log2e - l4[i])) : 0.f;
           pv[col] = pr;
           dsv[col] = valid ? pr * (dp - d4[i]) * p.scale : 0.f;
@@ -375,8 +390,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
         if (!mbar_wait_warp(acc_done, (it - 1) & 1, wc, 7)) { ok = false; break; }
       }
       if (threadIdx.x == 64) trace_pt(p, 2, it, 4);
-      if (DKV) store_row64_sw128(smem + L::kP, row, pv);
-      store_row64_sw128(smem + L::kDS, row, dsv);
+      if (DKV) store_row32_sw128(smem + L::kP, row, half, pv);
+      store_row32_sw128(smem + L::kDS, row, half, dsv);
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(pds_full);
@@ -393,7 +408,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
         __nv_bfloat16* orow = (a == 0 ? p.out0 : p.out1) + obase;
         const uint32_t t_acc = (a == 0 ? tmem_acc0 : tmem_acc1) + t_lane;
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
           uint32_t o[32];
           if (n_it > 0) {
             tmem_ld_32x32b_x32(t_acc + c * 32, o);

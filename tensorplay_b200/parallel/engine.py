@@ -153,7 +153,7 @@ class FSDPEngine:
                  group: Optional[dist.ProcessGroup] = None, comm: str = "auto",
                  activation_checkpointing: bool = True, max_grad_norm: Optional[float] = None,
                  unit_modules: Optional[Sequence[Sequence[nn.Module]]] = None,
-                 layer_args: Callable[[nn.Module, Tensor], tuple] = None):
+                 layer_args: Callable[[nn.Module, Tensor], tuple] = None, symm_extra_bytes: int = 1 << 30):
         self.model = model
         self.cfg = optim
         self.group = group
@@ -169,6 +169,7 @@ class FSDPEngine:
         if comm == "auto":
             comm = "single" if self.world == 1 else ("symm" if self.cuda else "torch")
         self.comm_kind = comm
+        self.symm_extra_bytes = symm_extra_bytes
         self._build_units()
         self._alloc()
         self._dummy = torch.zeros(1, device=self.device, requires_grad=True)
@@ -210,7 +211,7 @@ class FSDPEngine:
         single = self.world == 1
         if self.comm_kind == "symm":
             from .symm import SymmComm
-            self.comm = SymmComm(self)
+            self.comm = SymmComm(self, extra_bytes=self.symm_extra_bytes)
         else:
             self.comm = None
         for u in self.units:

@@ -119,7 +119,8 @@ class SymmComm:
     """The engine's communication backend on peer memory: all-gather by pulls and the fused
     reduce-scatter + AdamW + bf16 parameter emit."""
 
-    def __init__(self, engine, wait_s: float = 30.0, gather_ctas: int = 24, reduce_ctas: int = 148):
+    def __init__(self, engine, wait_s: float = 30.0, gather_ctas: int = 24, reduce_ctas: int = 148,
+                 extra_bytes: int = 1 << 30):
         self.engine = engine
         self.world, self.rank = engine.world, engine.rank
         units = engine.units
@@ -128,6 +129,7 @@ class SymmComm:
         n_pool = (len(units) if not engine.checkpoint else 3) + 2
         total = sum(u.shard_numel for u in units) * esz + n_pool * max_padded * esz
         total += (len(units) + n_pool + 8) * 512 + (1 << 20)
+        total += extra_bytes  # head-room for other users of the arena (TP plans, MoE workspaces)
         self.arena = SymmArena(total, group=engine.group)
         self.wait_s = wait_s
         self.gather_ctas, self.reduce_ctas = gather_ctas, reduce_ctas
