@@ -18,7 +18,7 @@
 
 namespace tpb {
 
-constexpr int kAttnThreads = 192;
+constexpr int kAttnThreads = 320;  // TMA warp, MMA warp, 8 softmax warps (two per TMEM lane quarter)
 constexpr int kBlockQ = 128;
 constexpr int kBlockKV = 128;
 constexpr float kNegBig = -1.0e30f;
@@ -53,8 +53,12 @@ struct AttnSmem {
   static constexpr int kRing = D == 128 ? 5 : 6;
   static constexpr int kKOff = kQOff + kQBytes;
   static constexpr int kPOff = kKOff + kRing * kKBytes;
-  static constexpr int kBarOff = kPOff + kPBytes;
+  // row-max exchange between the two halves: bf16 [2 buffers][2 halves][128 rows], then the
+  // fp32 row sums [2 halves][128 rows] exchanged once at the end
+  static constexpr int kXOff = kPOff + kPBytes;
+  static constexpr int kBarOff = kXOff + 2 * 2 * 128 * 2;
   static constexpr int kTotal = kBarOff + 256 + 1024;
+  static_assert(kTotal <= 227 * 1024, "attention forward exceeds the shared memory of one CTA");
 };
 
 template <int D>
@@ -74,7 +78,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* s_empty = s_full + 2;       // 2 (128 arrivals)
   uint64_t* p_full = s_empty + 2;       // 1 (128 arrivals)
   uint64_t* pv_done = p_full + 1;       // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
+  uint64_t* pair_bar = pv_done + 1;     // 4 (64 arrivals: the two warps sharing a lane quarter)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pair_bar + 4);
   volatile uint32_t* abort_w = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -101,9 +106,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 128);
+      mbar_init(&s_empty[i], 256);
     }
-    mbar_init(p_full, 128);
+    for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 64);
+    mbar_init(p_full, 256);
     mbar_init(pv_done, 1);
     fence_barrier_init();
     prefetch_tmap(&tmQ);
@@ -191,30 +197,32 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   } else {
     // ---------------------------------------------------------------- softmax / epilogue
     const int qd = warp & 3;
-    const int row = qd * 32 + lane;  // row inside the tile == TMEM lane
+    const int half = (warp - 2) >> 2;  // which 64 of the block's 128 keys this warp handles
+    const int row = qd * 32 + lane;    // row inside the tile == TMEM lane
     const int qi = q0 + row;
     const uint32_t t_lane = ((uint32_t)(qd * 32) << 16);
+    __nv_bfloat16* xch = reinterpret_cast<__nv_bfloat16*>(smem + L::kXOff);
     float m = kNegBig, l = 0.f;
     bool ok = true;
+    uint32_t xph = 0;  // phase of the pair barrier
     for (int j = 0; j < nkv; ++j) {
       const int s = j & 1;
       const uint32_t ph = (j >> 1) & 1;
       if (!mbar_wait_warp(&s_full[s], ph, wc, 8)) { ok = false; break; }
       tc_fence_after_sync();
-      uint32_t sr[4][32];
+      uint32_t sr[2][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(tmem_base + t_lane + s * 128 + c * 32, sr[c]);
+      for (int c = 0; c < 2; ++c) tmem_ld_32x32b_x32(tmem_base + t_lane + s * 128 + half * 64 + c * 32, sr[c]);
       tmem_ld_wait();
       tc_fence_before_sync();
       mbar_arrive(&s_empty[s]);
 
-      const int k0 = j * kBlockKV;
-      const bool need_mask = (p.causal && (k0 + kBlockKV - 1 > q0 + p.kv_offset)) ||
-                             (k0 + kBlockKV > p.Tk);
+      const int k0 = j * kBlockKV + half * 64;
+      const bool need_mask = (p.causal && (k0 + 63 > q0 + p.kv_offset)) || (k0 + 64 > p.Tk);
       const int lim = p.causal ? min(qi + p.kv_offset, p.Tk - 1) : (p.Tk - 1);  // last valid key
       float mx = m;
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           float v = __uint_as_float(sr[c][i]) * p.scale_log2e;
@@ -222,15 +230,27 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           sr[c][i] = __float_as_uint(v);
           mx = fmaxf(mx, v);
         }
+      // Row maximum over both halves. The halves exchange it rounded UP to bf16 (two buffers of
+      // 16-bit slots fit the shared memory left over): any common reference >= the true maximum
+      // serves the softmax, and both halves use exactly the same value.
+      {
+        const __nv_bfloat16 mine = __float2bfloat16_ru(mx);
+        xch[((j & 1) * 2 + half) * 128 + row] = mine;
+        mbar_arrive(&pair_bar[qd]);
+        if (!mbar_wait_warp(&pair_bar[qd], xph, wc, 11)) { ok = false; break; }
+        xph ^= 1;
+        mx = fmaxf(__bfloat162float(mine),
+                   __bfloat162float(xch[((j & 1) * 2 + (half ^ 1)) * 128 + row]));
+      }
       const float alpha = fast_exp2(m - mx);
       m = mx;
-      // p = exp2(s - max) evaluated two at a time in bf16 (ex2.approx.bf16x2): P is consumed as bf16
-      // by the second MMA anyway, the packed form halves the MUFU work, and the row sum adds
-      // exactly the rounded values that the MMA multiplies with V.
+      // p = exp2(s - max) two at a time in bf16 (ex2.approx.bf16x2): P is consumed as bf16 by the
+      // second MMA anyway, the packed form halves the MUFU work, and the row sum adds exactly the
+      // rounded values that the MMA multiplies with V.
       float sum = 0.f;
-      uint32_t pw[64];
+      uint32_t pw[32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           __nv_bfloat162 d = __floats2bfloat162_rn(__uint_as_float(sr[c][i]) - mx,
@@ -246,8 +266,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (!mbar_wait_warp(pv_done, (j - 1) & 1, wc, 9)) { ok = false; break; }
         tc_fence_after_sync();
         if (__any_sync(0xffffffffu, alpha != 1.f)) {
+          // each half rescales its half of the head dimension
 #pragma unroll 1
-          for (int c = 0; c < D / 32; ++c) {
+          for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
             uint32_t o[32];
             tmem_ld_32x32b_x32(tmem_o + t_lane + c * 32, o);
             tmem_ld_wait();
@@ -263,15 +284,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tmem_st_wait();
         }
       }
-      // P (bf16) into the swizzled tile: chunk = key / 64, 16-byte slot = (key % 64) / 8
-      uint8_t* prow = smem + L::kPOff + row * 128;
+      // P (bf16) into the swizzled tile: chunk = key / 64 = half, 16-byte slot = (key % 64) / 8
+      uint8_t* prow = smem + L::kPOff + half * (kBlockQ * 128) + row * 128;
 #pragma unroll
-      for (int g = 0; g < 16; ++g) {  // 16 groups of 8 keys
+      for (int g = 0; g < 8; ++g) {
         uint4 v = make_uint4(pw[g * 4 + 0], pw[g * 4 + 1], pw[g * 4 + 2], pw[g * 4 + 3]);
-        const int key = g * 8;
-        const int chunk = key >> 6;
-        const int slot = (key & 63) >> 3;
-        *reinterpret_cast<uint4*>(prow + chunk * (kBlockQ * 128) + ((slot ^ (row & 7)) << 4)) = v;
+        *reinterpret_cast<uint4*>(prow + ((g ^ (row & 7)) << 4)) = v;
       }
       fence_proxy_async_smem();
       tc_fence_before_sync();
@@ -279,12 +297,21 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     if (ok && nkv > 0) ok = mbar_wait_warp(pv_done, (nkv - 1) & 1, wc, 10);
     if (ok) {
+      // total row sum = sum of the two halves, exchanged through the P tile, which is idle once
+      // the last PV MMA has completed
+      float* xl = reinterpret_cast<float*>(smem + L::kPOff);
+      xl[half * 128 + row] = l;
+      mbar_arrive(&pair_bar[qd]);
+      ok = mbar_wait_warp(&pair_bar[qd], xph, wc, 12);
+      l += xl[(half ^ 1) * 128 + row];
+    }
+    if (ok) {
       tc_fence_after_sync();
       const float inv = (nkv > 0 && l > 0.f) ? 1.f / l : 0.f;
       __nv_bfloat16* orow = p.O + (long long)b * p.o_batch_stride + (long long)qi * p.o_tok_stride +
                             (long long)h * p.o_head_stride;
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
         uint32_t o[32];
         if (nkv > 0) {
           tmem_ld_32x32b_x32(tmem_o + t_lane + c * 32, o);
@@ -313,7 +340,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         }
       }
-      if (qi < p.Tq && p.lse) {
+      if (half == 0 && qi < p.Tq && p.lse) {
         float lse = (nkv > 0 && l > 0.f) ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
         p.lse[((long long)b * p.Hq + h) * p.lse_stride + qi] = lse;
       }

@@ -622,6 +622,21 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t d0, uint64_t 
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
+// 2-D int8 tensor map with 128-byte swizzle: inner dim `d0` contiguous (bytes), box = {128, box1}.
+int make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t ld,
+                    uint32_t box1) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {d0, d1};
+  cuuint64_t strides[1] = {ld};
+  cuuint32_t box[2] = {128, box1};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
 int sm_count() {
   static int n = 0;
   if (n == 0) {

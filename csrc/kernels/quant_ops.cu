@@ -1,0 +1,492 @@
+// Quantized linear algebra for inference on sm_100a.
+//
+//   * int8 x int8 -> int32 GEMM on the tcgen05 tensor cores (kind::i8) with a fused
+//     row-scale x column-scale (+ bias) epilogue that emits bf16 (A8W8, rowwise scales);
+//   * weight-only GEMV for decode (W8A16 per-channel, W4A16 group-wise): weights are read
+//     once at their packed width, activations stay in bf16, accumulation in fp32;
+//   * quantise / dequantise kernels (rowwise int8, int8/int4 weights -> bf16, fp8 e4m3 / e5m2).
+//
+// Capability reference: p10/src/backend/cuda/QuantGemmKernels.cu:92-1611 (weight-only and A8W8
+// GEMMs), IntMM.cu:62 (int8 matmul), AffineQuantKernels.cu:1302 (fp8 quantise / dequantise).
+#include <cuda_fp8.h>
+
+#include "sm100.cuh"
+#include "tpb_api.h"
+
+namespace tpb {
+namespace {
+
+constexpr int kQThreads = 192;
+constexpr int kQBlockM = 128;
+constexpr int kQBlockN = 256;
+constexpr int kQBlockK = 128;  // int8 elements = one 128-byte swizzle row
+constexpr int kQStages = 4;
+constexpr int kQABytes = kQBlockM * kQBlockK;
+constexpr int kQBBytes = kQBlockN * kQBlockK;
+constexpr int kQStageBytes = kQABytes + kQBBytes;
+constexpr int kQSmem = kQStages * kQStageBytes + 256 + 1024;
+
+struct I8Params {
+  int M, N, K, ldc;
+  __nv_bfloat16* C;
+  const float* a_scale;  // [M] or null
+  const float* b_scale;  // [N] or null
+  const __nv_bfloat16* bias;  // [N] or null
+  uint32_t* status;
+  unsigned long long wait_ns;
+};
+
+// Persistent kernel: warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..5 = epilogue.
+__global__ void __launch_bounds__(kQThreads, 1)
+gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const I8Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kQStages * kQStageBytes);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + kQStages;
+  uint64_t* tfull = empty + kQStages;   // 2
+  uint64_t* tempty = tfull + 2;         // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile uint32_t* abort_w = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + kQBlockM - 1) / kQBlockM;
+  const int tiles_n = (p.N + kQBlockN - 1) / kQBlockN;
+  const int n_tiles = tiles_m * tiles_n;
+  const int k_blocks = (p.K + kQBlockK - 1) / kQBlockK;
+
+  if (threadIdx.x == 0) {
+    *abort_w = 0;
+    for (int i = 0; i < kQStages; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    mbar_init(&tfull[0], 1);
+    mbar_init(&tfull[1], 1);
+    mbar_init(&tempty[0], 4);
+    mbar_init(&tempty[1], 4);
+    fence_barrier_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  WaitCtx wc{abort_w, p.status, p.wait_ns};
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        // column-major over tiles: consecutive CTAs share the B (weight) tile row in L2
+        const int tm = tile % tiles_m, tn = tile / tiles_m;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % kQStages;
+          const uint32_t ph = (it / kQStages) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, wc, 1)) { ok = false; break; }
+          uint8_t* sa = smem + s * kQStageBytes;
+          mbar_arrive_expect_tx(&full[s], kQStageBytes);
+          tma_load_2d(sa, &tmA, &full[s], kb * kQBlockK, tm * kQBlockM);
+          tma_load_2d(sa + kQABytes, &tmB, &full[s], kb * kQBlockK, tn * kQBlockN);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_i8(kQBlockM, kQBlockN);
+      uint32_t it = 0, lt = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++lt) {
+        const int as = lt & 1;
+        const uint32_t aph = (lt >> 1) & 1;
+        if (!mbar_wait(&tempty[as], aph ^ 1, wc, 2)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + as * kQBlockN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % kQStages;
+          const uint32_t ph = (it / kQStages) & 1;
+          if (!mbar_wait(&full[s], ph, wc, 3)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + s * kQStageBytes);
+          const uint32_t sb = sa + kQABytes;
+#pragma unroll
+          for (int j = 0; j < kQBlockK / 32; ++j)  // one kind::i8 instruction covers K = 32
+            umma_i8_ss(d_tmem, make_smem_desc_sw128(sa + j * 32, 16, 1024),
+                       make_smem_desc_sw128(sb + j * 32, 16, 1024), idesc, (kb | j) != 0);
+          umma_commit(&empty[s]);
+        }
+        if (ok) umma_commit(&tfull[as]);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    uint32_t lt = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++lt) {
+      const int tm = tile % tiles_m, tn = tile / tiles_m;
+      const int as = lt & 1;
+      const uint32_t aph = (lt >> 1) & 1;
+      if (!mbar_wait_warp(&tfull[as], aph, wc, 4)) break;
+      tc_fence_after_sync();
+      const int row = tm * kQBlockM + q * 32 + lane;
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + as * kQBlockN;
+      const float sa = (p.a_scale && row < p.M) ? p.a_scale[row] : 1.f;
+#pragma unroll 1
+      for (int c = 0; c < kQBlockN; c += 32) {
+        const int col0 = tn * kQBlockN + c;
+        if (col0 >= p.N) break;
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c, r);
+        tmem_ld_wait();
+        if (row < p.M) {
+          __nv_bfloat16* dst = p.C + (size_t)row * p.ldc + col0;
+          const bool full_chunk = (col0 + 32 <= p.N) && ((p.ldc & 7) == 0);
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = min(col0 + i, p.N - 1);
+            float x = (float)(int)r[i] * sa * (p.b_scale ? __ldg(p.b_scale + col) : 1.f);
+            if (p.bias) x += __bfloat162float(p.bias[col]);
+            v[i] = x;
+          }
+          if (full_chunk) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 o;
+              __nv_bfloat162 t0 = __floats2bfloat162_rn(v[g * 8 + 0], v[g * 8 + 1]);
+              __nv_bfloat162 t1 = __floats2bfloat162_rn(v[g * 8 + 2], v[g * 8 + 3]);
+              __nv_bfloat162 t2 = __floats2bfloat162_rn(v[g * 8 + 4], v[g * 8 + 5]);
+              __nv_bfloat162 t3 = __floats2bfloat162_rn(v[g * 8 + 6], v[g * 8 + 7]);
+              o.x = *reinterpret_cast<uint32_t*>(&t0);
+              o.y = *reinterpret_cast<uint32_t*>(&t1);
+              o.z = *reinterpret_cast<uint32_t*>(&t2);
+              o.w = *reinterpret_cast<uint32_t*>(&t3);
+              *reinterpret_cast<uint4*>(dst + g * 8) = o;
+            }
+          } else {
+            for (int i = 0; i < 32 && col0 + i < p.N; ++i) dst[i] = __float2bfloat16(v[i]);
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[as]);
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------ weight-only GEMV (decode)
+// y[m, n] = sum_k x[m, k] * dq(W[n, k]); one warp per output column, up to 8 rows of x held
+// per pass; weights stream through once at packed width.
+template <int BITS>
+__global__ void __launch_bounds__(256)
+wq_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ w,
+               const __nv_bfloat16* __restrict__ scale, const __nv_bfloat16* __restrict__ zero,
+               const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ y, int M, int N,
+               int K, int group, long long ldx, long long ldy) {
+  constexpr int kRows = 8;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * 8 + warp;
+  if (n >= N) return;
+  const int groups_per_row = (group > 0) ? K / group : 1;
+  const size_t wrow = (size_t)n * (BITS == 8 ? K : K / 2);
+  for (int m0 = 0; m0 < M; m0 += kRows) {
+    float acc[kRows];
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) acc[r] = 0.f;
+    // 16 packed bytes per lane per step: 16 (int8) or 32 (int4) weights
+    constexpr int kPerLane = (BITS == 8) ? 16 : 32;
+    for (int k0 = lane * kPerLane; k0 < K; k0 += 32 * kPerLane) {
+      const uint4 pk = __ldg(reinterpret_cast<const uint4*>(w + wrow + (BITS == 8 ? k0 : k0 / 2)));
+      const uint32_t words[4] = {pk.x, pk.y, pk.z, pk.w};
+      float wv[kPerLane];
+      if (BITS == 8) {
+        const float s = __bfloat162float(scale[(size_t)n * groups_per_row + (group > 0 ? k0 / group : 0)]);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) wv[i] = (float)(int8_t)((words[i >> 2] >> ((i & 3) * 8)) & 0xff) * s;
+      } else {
+        // unsigned 4-bit codes, low nibble first; dq = (code - zero) * scale, zero defaults to 8
+        const int g = group > 0 ? k0 / group : 0;  // 32 consecutive weights never straddle a group (group % 32 == 0)
+        const float s = __bfloat162float(scale[(size_t)n * groups_per_row + g]);
+        const float z = zero ? __bfloat162float(zero[(size_t)n * groups_per_row + g]) : 8.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) wv[i] = ((float)((words[i >> 3] >> ((i & 7) * 4)) & 0xf) - z) * s;
+      }
+#pragma unroll
+      for (int r = 0; r < kRows; ++r) {
+        if (m0 + r < M) {
+          const __nv_bfloat16* xr = x + (size_t)(m0 + r) * ldx + k0;
+#pragma unroll
+          for (int i = 0; i < kPerLane; i += 8) {
+            const uint4 xv = *reinterpret_cast<const uint4*>(xr + i);
+            const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = __bfloat1622float2(xp[j]);
+              acc[r] += f.x * wv[i + 2 * j] + f.y * wv[i + 2 * j + 1];
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+      float a = acc[r];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+      if (lane == 0 && m0 + r < M) {
+        if (bias) a += __bfloat162float(bias[n]);
+        y[(size_t)(m0 + r) * ldy + n] = __float2bfloat16(a);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ quantise / dequantise
+// Rowwise symmetric int8: scale = absmax / 127 per row; one CTA per row.
+__global__ void __launch_bounds__(256)
+quant_i8_rowwise_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__ q,
+                        float* __restrict__ scale, int K, long long ldx) {
+  __shared__ float red[8];
+  const int row = blockIdx.x;
+  const __nv_bfloat16* xr = x + (size_t)row * ldx;
+  float mx = 0.f;
+  for (int k = threadIdx.x * 8; k < K; k += 256 * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(xr + k);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(h[j]);
+      mx = fmaxf(mx, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  mx = red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) mx = fmaxf(mx, red[i]);
+  const float s = mx > 0.f ? mx / 127.f : 1.f;
+  const float inv = 1.f / s;
+  if (threadIdx.x == 0) scale[row] = s;
+  for (int k = threadIdx.x * 8; k < K; k += 256 * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(xr + k);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+    uint32_t o[2] = {0, 0};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(h[j]);
+      const int a = max(-127, min(127, __float2int_rn(f.x * inv)));
+      const int b = max(-127, min(127, __float2int_rn(f.y * inv)));
+      o[j >> 1] |= ((uint32_t)(a & 0xff) << ((j & 1) * 16)) | ((uint32_t)(b & 0xff) << ((j & 1) * 16 + 8));
+    }
+    *reinterpret_cast<uint2*>(q + (size_t)row * K + k) = make_uint2(o[0], o[1]);
+  }
+}
+
+// Packed weights -> bf16 (prefill path: dequantise once, then the bf16 tensor-core GEMM).
+template <int BITS>
+__global__ void __launch_bounds__(256)
+dequant_w_kernel(const uint8_t* __restrict__ w, const __nv_bfloat16* __restrict__ scale,
+                 const __nv_bfloat16* __restrict__ zero, __nv_bfloat16* __restrict__ out, int N,
+                 int K, int group) {
+  const long long idx = ((long long)blockIdx.x * 256 + threadIdx.x) * 8;  // 8 weights per thread
+  if (idx >= (long long)N * K) return;
+  const int n = (int)(idx / K), k = (int)(idx % K);
+  const int gpr = group > 0 ? K / group : 1;
+  const int g = group > 0 ? k / group : 0;
+  const float s = __bfloat162float(scale[(size_t)n * gpr + g]);
+  float v[8];
+  if (BITS == 8) {
+    const uint2 pk = *reinterpret_cast<const uint2*>(w + idx);
+    const uint32_t words[2] = {pk.x, pk.y};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = (float)(int8_t)((words[i >> 2] >> ((i & 3) * 8)) & 0xff) * s;
+  } else {
+    const uint32_t pk = *reinterpret_cast<const uint32_t*>(w + idx / 2);
+    const float z = zero ? __bfloat162float(zero[(size_t)n * gpr + g]) : 8.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = ((float)((pk >> (i * 4)) & 0xf) - z) * s;
+  }
+  uint4 o;
+  __nv_bfloat162 t0 = __floats2bfloat162_rn(v[0], v[1]), t1 = __floats2bfloat162_rn(v[2], v[3]);
+  __nv_bfloat162 t2 = __floats2bfloat162_rn(v[4], v[5]), t3 = __floats2bfloat162_rn(v[6], v[7]);
+  o.x = *reinterpret_cast<uint32_t*>(&t0); o.y = *reinterpret_cast<uint32_t*>(&t1);
+  o.z = *reinterpret_cast<uint32_t*>(&t2); o.w = *reinterpret_cast<uint32_t*>(&t3);
+  *reinterpret_cast<uint4*>(out + idx) = o;
+}
+
+// fp8 quantise: q = saturate(x / scale); scale is per tensor (rows_per_scale = 0) or per row.
+template <typename F8>
+__global__ void __launch_bounds__(256)
+fp8_quant_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ scale,
+                 uint8_t* __restrict__ q, long long n, int row_len, int per_row) {
+  const long long idx = ((long long)blockIdx.x * 256 + threadIdx.x) * 8;
+  if (idx >= n) return;
+  const float inv = 1.f / scale[per_row ? idx / row_len : 0];
+  const uint4 v = *reinterpret_cast<const uint4*>(x + idx);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+  uint8_t o[8];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __bfloat1622float2(h[j]);
+    F8 a(f.x * inv), b(f.y * inv);  // the constructor saturates to the finite range
+    o[2 * j] = *reinterpret_cast<uint8_t*>(&a);
+    o[2 * j + 1] = *reinterpret_cast<uint8_t*>(&b);
+  }
+  *reinterpret_cast<uint2*>(q + idx) = *reinterpret_cast<uint2*>(o);
+}
+
+template <typename F8>
+__global__ void __launch_bounds__(256)
+fp8_dequant_kernel(const uint8_t* __restrict__ q, const float* __restrict__ scale,
+                   __nv_bfloat16* __restrict__ out, long long n, int row_len, int per_row) {
+  const long long idx = ((long long)blockIdx.x * 256 + threadIdx.x) * 8;
+  if (idx >= n) return;
+  const float s = scale[per_row ? idx / row_len : 0];
+  const uint2 pk = *reinterpret_cast<const uint2*>(q + idx);
+  const uint8_t* b = reinterpret_cast<const uint8_t*>(&pk);
+  float v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    F8 t;
+    *reinterpret_cast<uint8_t*>(&t) = b[i];
+    v[i] = (float)t * s;
+  }
+  uint4 o;
+  __nv_bfloat162 t0 = __floats2bfloat162_rn(v[0], v[1]), t1 = __floats2bfloat162_rn(v[2], v[3]);
+  __nv_bfloat162 t2 = __floats2bfloat162_rn(v[4], v[5]), t3 = __floats2bfloat162_rn(v[6], v[7]);
+  o.x = *reinterpret_cast<uint32_t*>(&t0); o.y = *reinterpret_cast<uint32_t*>(&t1);
+  o.z = *reinterpret_cast<uint32_t*>(&t2); o.w = *reinterpret_cast<uint32_t*>(&t3);
+  *reinterpret_cast<uint4*>(out + idx) = o;
+}
+
+}  // namespace
+}  // namespace tpb
+
+using namespace tpb;
+
+extern "C" {
+
+// C[M, N] (bf16) = (A_q[M, K] . B_q[N, K]^T) * a_scale[m] * b_scale[n] (+ bias[n]); int8 operands,
+// K a multiple of 16 and both row pitches multiples of 16 bytes (TMA).
+int tpb_gemm_i8(const void* A, const void* B, void* C, const float* a_scale, const float* b_scale,
+                const void* bias, int M, int N, int K, int lda, int ldb, int ldc, uint32_t* status,
+                void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return -1;
+  if ((K & 15) || (lda & 15) || (ldb & 15)) return -2;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) return -3;
+  CUtensorMap ta, tb;
+  int r = make_tmap_2d_u8(&ta, A, K, M, lda, kQBlockM);
+  if (r) return r;
+  r = make_tmap_2d_u8(&tb, B, K, N, ldb, kQBlockN);
+  if (r) return r;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kQSmem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  I8Params p;
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc;
+  p.C = static_cast<__nv_bfloat16*>(C);
+  p.a_scale = a_scale; p.b_scale = b_scale;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.status = status; p.wait_ns = kDefaultWaitNs;
+  const int tiles = ((M + kQBlockM - 1) / kQBlockM) * ((N + kQBlockN - 1) / kQBlockN);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  gemm_i8_kernel<<<grid, kQThreads, kQSmem, static_cast<cudaStream_t>(stream)>>>(ta, tb, p);
+  return (int)cudaGetLastError();
+}
+
+// bits = 8: W int8 [N, K], scale bf16 [N, K/group] (group = 0: one scale per row).
+// bits = 4: W uint8 [N, K/2] (two codes per byte, low nibble first), group % 32 == 0.
+int tpb_wq_gemv(const void* x, const void* w, const void* scale, const void* zero, const void* bias,
+                void* y, int M, int N, int K, int bits, int group, long long ldx, long long ldy,
+                void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return -1;
+  const int per_lane = bits == 8 ? 16 : 32;
+  if (bits != 8 && bits != 4) return -2;
+  if (K % (per_lane) || (ldx & 7)) return -3;
+  if (group > 0 && (K % group || group % per_lane)) return -4;
+  const int grid = (N + 7) / 8;
+  auto st = static_cast<cudaStream_t>(stream);
+  if (bits == 8)
+    wq_gemv_kernel<8><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (const uint8_t*)w,
+                                            (const __nv_bfloat16*)scale, (const __nv_bfloat16*)zero,
+                                            (const __nv_bfloat16*)bias, (__nv_bfloat16*)y, M, N, K,
+                                            group, ldx, ldy);
+  else
+    wq_gemv_kernel<4><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (const uint8_t*)w,
+                                            (const __nv_bfloat16*)scale, (const __nv_bfloat16*)zero,
+                                            (const __nv_bfloat16*)bias, (__nv_bfloat16*)y, M, N, K,
+                                            group, ldx, ldy);
+  return (int)cudaGetLastError();
+}
+
+int tpb_quant_i8_rowwise(const void* x, void* q, float* scale, int M, int K, long long ldx,
+                         void* stream) {
+  if (M <= 0 || K <= 0 || (K & 7) || (ldx & 7)) return -1;
+  quant_i8_rowwise_kernel<<<M, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      (const __nv_bfloat16*)x, (int8_t*)q, scale, K, ldx);
+  return (int)cudaGetLastError();
+}
+
+int tpb_dequant_weight(const void* w, const void* scale, const void* zero, void* out, int N, int K,
+                       int bits, int group, void* stream) {
+  if (N <= 0 || K <= 0 || (K & 7)) return -1;
+  if (group > 0 && (K % group || (group & 7))) return -2;
+  const long long n = (long long)N * K;
+  const int grid = (int)((n / 8 + 255) / 256);
+  auto st = static_cast<cudaStream_t>(stream);
+  if (bits == 8)
+    dequant_w_kernel<8><<<grid, 256, 0, st>>>((const uint8_t*)w, (const __nv_bfloat16*)scale,
+                                              (const __nv_bfloat16*)zero, (__nv_bfloat16*)out, N, K, group);
+  else if (bits == 4)
+    dequant_w_kernel<4><<<grid, 256, 0, st>>>((const uint8_t*)w, (const __nv_bfloat16*)scale,
+                                              (const __nv_bfloat16*)zero, (__nv_bfloat16*)out, N, K, group);
+  else
+    return -3;
+  return (int)cudaGetLastError();
+}
+
+// fmt 0 = e4m3, 1 = e5m2; n a multiple of 8; per_row: one scale per `row_len` elements.
+int tpb_fp8_quant(const void* x, const float* scale, void* q, long long n, int row_len, int per_row,
+                  int fmt, void* stream) {
+  if (n <= 0 || (n & 7) || (per_row && (row_len <= 0 || (row_len & 7)))) return -1;
+  const int grid = (int)((n / 8 + 255) / 256);
+  auto st = static_cast<cudaStream_t>(stream);
+  if (fmt == 0)
+    fp8_quant_kernel<__nv_fp8_e4m3><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, scale, (uint8_t*)q, n, row_len, per_row);
+  else
+    fp8_quant_kernel<__nv_fp8_e5m2><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, scale, (uint8_t*)q, n, row_len, per_row);
+  return (int)cudaGetLastError();
+}
+
+int tpb_fp8_dequant(const void* q, const float* scale, void* out, long long n, int row_len,
+                    int per_row, int fmt, void* stream) {
+  if (n <= 0 || (n & 7) || (per_row && (row_len <= 0 || (row_len & 7)))) return -1;
+  const int grid = (int)((n / 8 + 255) / 256);
+  auto st = static_cast<cudaStream_t>(stream);
+  if (fmt == 0)
+    fp8_dequant_kernel<__nv_fp8_e4m3><<<grid, 256, 0, st>>>((const uint8_t*)q, scale, (__nv_bfloat16*)out, n, row_len, per_row);
+  else
+    fp8_dequant_kernel<__nv_fp8_e5m2><<<grid, 256, 0, st>>>((const uint8_t*)q, scale, (__nv_bfloat16*)out, n, row_len, per_row);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -14,6 +14,8 @@ int sm_count();
 void ensure_thread_context();
 int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t ld,
                       uint32_t box1);
+int make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t ld,
+                    uint32_t box1);
 int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                    const uint64_t* strides_elems, const uint32_t* box, int swizzle128);
 // Mapped symmetric arenas of this process (see symm_comm.cu); null before tpb_symm_create.

@@ -46,6 +46,16 @@ _KERNEL_SIGS = {
     "tpb_adamw_multi": [I, P, P, P, P, P, P, I, I, F, F, F, F, F, I, F, I, P, P, P],
     "tpb_sumsq": [P, I, LL, F, P, P],
     "tpb_clip_coef": [P, F, P, P, P],
+    "tpb_gemm_i8": [P, P, P, P, P, P, I, I, I, I, I, I, P, P],
+    "tpb_wq_gemv": [P, P, P, P, P, P, I, I, I, I, I, LL, LL, P],
+    "tpb_quant_i8_rowwise": [P, P, P, I, I, LL, P],
+    "tpb_dequant_weight": [P, P, P, P, I, I, I, I, P],
+    "tpb_fp8_quant": [P, P, P, LL, I, I, I, P],
+    "tpb_fp8_dequant": [P, P, P, LL, I, I, I, P],
+    "tpb_embedding_fwd": [P, P, P, LL, I, LL, P],
+    "tpb_embedding_bwd": [P, P, P, LL, I, LL, I, P],
+    "tpb_kv_append": [P, P, P, P, I, I, I, I, I, I, I, LL, LL, LL, LL, LL, LL, P],
+    "tpb_sample": [P, P, P, P, I, I, LL, I, F, I, F, P],
 }
 
 

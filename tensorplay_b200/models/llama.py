@@ -181,27 +181,6 @@ class Llama(nn.Module):
         return self.head(x, targets)
 
 
-class _EmbeddingFn(torch.autograd.Function):
-    """Row gather whose backward scatter-adds straight into the weight's gradient buffer."""
-
-    @staticmethod
-    def forward(ctx, tokens, weight):
-        ctx.save_for_backward(tokens)
-        ctx.wshape = weight.shape
-        ctx.grad_view = getattr(weight, "_tpb_grad_view", None)
-        return weight.index_select(0, tokens.reshape(-1)).view(*tokens.shape, weight.shape[1])
-
-    @staticmethod
-    def backward(ctx, dy):
-        (tokens,) = ctx.saved_tensors
-        dst = ctx.grad_view
-        if dst is not None:
-            dst.index_add_(0, tokens.reshape(-1), dy.reshape(-1, dy.shape[-1]).to(dst.dtype))
-            return None, None
-        dw = torch.zeros(ctx.wshape, dtype=dy.dtype, device=dy.device)
-        dw.index_add_(0, tokens.reshape(-1), dy.reshape(-1, dy.shape[-1]))
-        return None, dw
-
-
 def _embedding(tokens: Tensor, weight: Tensor) -> Tensor:
-    return _EmbeddingFn.apply(tokens, weight)
+    """Row gather; the backward scatter-adds straight into the weight's gradient buffer."""
+    return ops.embedding(tokens, weight)

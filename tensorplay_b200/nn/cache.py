@@ -39,8 +39,13 @@ class DynamicCache(Cache):
                 nk[:, :, :n] = buf[:, :, :n]
                 nv[:, :, :n] = self._v[layer_idx][:, :, :n]
             self._k[layer_idx], self._v[layer_idx] = nk, nv
-        self._k[layer_idx][:, :, n:n + t] = key
-        self._v[layer_idx][:, :, n:n + t] = value
+        if key.is_cuda and key.dtype == torch.bfloat16:
+            from ..ops import kv_append
+            kv_append(self._k[layer_idx], key, n)
+            kv_append(self._v[layer_idx], value, n)
+        else:
+            self._k[layer_idx][:, :, n:n + t] = key
+            self._v[layer_idx][:, :, n:n + t] = value
         self._len[layer_idx] = n + t
         return self._k[layer_idx][:, :, :n + t], self._v[layer_idx][:, :, :n + t]
 
@@ -66,8 +71,13 @@ class StaticCache(Cache):
             shape = (key.shape[0], key.shape[1], self.max_seq_len, key.shape[3])
             self._k[layer_idx] = key.new_zeros(shape)
             self._v[layer_idx] = value.new_zeros(shape)
-        self._k[layer_idx][:, :, n:n + t] = key
-        self._v[layer_idx][:, :, n:n + t] = value
+        if key.is_cuda and key.dtype == torch.bfloat16:
+            from ..ops import kv_append
+            kv_append(self._k[layer_idx], key, n)
+            kv_append(self._v[layer_idx], value, n)
+        else:
+            self._k[layer_idx][:, :, n:n + t] = key
+            self._v[layer_idx][:, :, n:n + t] = value
         self._len[layer_idx] = n + t
         return self._k[layer_idx][:, :, :n + t], self._v[layer_idx][:, :, :n + t]
 
@@ -152,8 +162,13 @@ class PagedCache(Cache):
         tbl = torch.tensor(tables, device=key.device, dtype=torch.long)  # [B, need]
         blk = tbl[:, pos // bs]  # [B, t]
         off = (pos % bs).expand(B, t)
-        pk[blk, :, off] = key.transpose(1, 2)
-        pv[blk, :, off] = value.transpose(1, 2)
+        if key.is_cuda and key.dtype == torch.bfloat16:
+            from ..ops import kv_append
+            kv_append(pk, key, n, block_table=tbl, block_size=bs)
+            kv_append(pv, value, n, block_table=tbl, block_size=bs)
+        else:
+            pk[blk, :, off] = key.transpose(1, 2)
+            pv[blk, :, off] = value.transpose(1, 2)
         self._len[layer_idx] = n + t
         kk = pk[tbl].permute(0, 2, 1, 3, 4).reshape(B, H, need * bs, D)[:, :, :n + t]
         vv = pv[tbl].permute(0, 2, 1, 3, 4).reshape(B, H, need * bs, D)[:, :, :n + t]

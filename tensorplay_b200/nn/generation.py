@@ -37,6 +37,10 @@ def _apply_repetition_penalty(logits: Tensor, sequences: Tensor, penalty: float)
 
 def sample(logits: Tensor, temperature: float = 1.0, top_k: int = 0, top_p: float = 1.0) -> Tensor:
     """One token id per row from the filtered, tempered distribution."""
+    if logits.is_cuda and logits.dim() == 2:
+        # one kernel: sort-free top-k / nucleus support + inverse-CDF draw
+        from .. import ops
+        return ops.sample(logits, temperature, top_k, top_p)
     scaled = logits.float() / max(temperature, 1e-6)
     filtered = top_k_top_p_filtering(scaled, top_k, top_p)
     return torch.multinomial(torch.softmax(filtered, dim=-1), num_samples=1).squeeze(-1)
