@@ -27,7 +27,7 @@ constexpr int kBwdThreads = 320;  // TMA warp, MMA warp, 8 P/dS warps (two per T
 constexpr int kSoftThreads = 256;
 constexpr int kStat = 128;   // rows of the stationary tiles
 constexpr int kStream = 64;  // rows of the streamed tiles
-constexpr int kYStages = 3;  // streamed-tile ring: loads run two tiles ahead of the MMAs
+constexpr int kYStages = 4;  // streamed-tile ring: loads run three tiles ahead of the MMAs
 
 struct AttnBwdParams {
   int B, Tq, Tk, Hq, Hkv;
@@ -43,7 +43,6 @@ struct AttnBwdParams {
   unsigned long long wait_ns;
   unsigned long long* trace;  // optional: timestamps of CTA (0,0,0), see tpb_flash_bwd_set_trace
   int trace_cap;
-  int debug;  // probe switches (results are wrong when set): 1 = no exp2, 2 = no P/dS math at all
 };
 
 // Debug aid: records (role, iteration, phase, globaltimer) tuples of block (0,0,0).
@@ -70,52 +69,59 @@ struct BwdSmem {
   static constexpr int kChunks = D / 64;
   static constexpr int kStatBytes = kStat * D * 2;      // one stationary tile
   static constexpr int kStreamBytes = kStream * D * 2;  // one streamed tile
-  static constexpr int kPBytes = kStat * kStream * 2;   // P / dS tile (128 x 64 bf16)
   static constexpr int kX0 = 0;
   static constexpr int kX1 = kX0 + kStatBytes;
   static constexpr int kY = kX1 + kStatBytes;  // kYStages x (Y0, Y1)
-  static constexpr int kP = kY + 2 * kYStages * kStreamBytes;
-  static constexpr int kDS = kP + kPBytes;
-  static constexpr int kStats = kDS + kPBytes;  // per Y stage: lse[64] then delta[64] (fp32)
+  static constexpr int kStats = kY + 2 * kYStages * kStreamBytes;  // per Y stage: lse[64] then delta[64] (fp32)
   static constexpr int kBar = kStats + kYStages * 2 * kStream * 4;
   static constexpr int kTotal = kBar + 256 + 1024;
+  static_assert(kTotal <= 227 * 1024, "attention backward exceeds the shared memory of one CTA");
 };
 
-// 32 consecutive bf16 values (fp32 in v[]) of a row, starting at column 32 * half, into a
-// swizzled [128][64] tile.
-__device__ __forceinline__ void store_row32_sw128(uint8_t* tile, int row, int half, const float (&v)[32]) {
-  uint8_t* prow = tile + row * 128;
+// P = exp2(S * scale_log2e - lse2) and dS = P * (dP * scale - delta * scale) for 32 columns of
+// one row, packed to bf16 pairs. Straight-line code: the masked variant selects, it never branches.
+//   DKV: per-column statistics (lse, delta of the streamed queries) come from shared memory;
+//   dQ : the row's own statistics (already scaled) are in registers.
+template <bool DKV, bool MASKED>
+__device__ __forceinline__ void pds_math(const uint32_t (&sr)[32], const uint32_t (&dr)[32],
+                                         uint32_t stats_sa, float lse2_row, float dsc_row, int y0i,
+                                         int y_lo, int y_hi, float scale_log2e, float scale,
+                                         uint32_t (&pw)[16], uint32_t (&dw)[16]) {
+  constexpr float kLog2e = 1.4426950408889634f;
 #pragma unroll
-  for (int gg = 0; gg < 4; ++gg) {
-    const int g = half * 4 + gg;
-    uint4 u;
-    __nv_bfloat162 t0 = __floats2bfloat162_rn(v[gg * 8 + 0], v[gg * 8 + 1]);
-    __nv_bfloat162 t1 = __floats2bfloat162_rn(v[gg * 8 + 2], v[gg * 8 + 3]);
-    __nv_bfloat162 t2 = __floats2bfloat162_rn(v[gg * 8 + 4], v[gg * 8 + 5]);
-    __nv_bfloat162 t3 = __floats2bfloat162_rn(v[gg * 8 + 6], v[gg * 8 + 7]);
-    u.x = *reinterpret_cast<uint32_t*>(&t0);
-    u.y = *reinterpret_cast<uint32_t*>(&t1);
-    u.z = *reinterpret_cast<uint32_t*>(&t2);
-    u.w = *reinterpret_cast<uint32_t*>(&t3);
-    *reinterpret_cast<uint4*>(prow + ((g ^ (row & 7)) << 4)) = u;
-  }
-}
-
-// bf16 row of 64 values (fp32 in v[]) into a swizzled [128][64] tile.
-__device__ __forceinline__ void store_row64_sw128(uint8_t* tile, int row, const float (&v)[64]) {
-  uint8_t* prow = tile + row * 128;
+  for (int c = 0; c < 32; c += 4) {
+    float l4[4], d4[4];
+    if (DKV) {
+      float4 a, d;
+      asm("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w) : "r"(stats_sa + c * 4));
+      asm("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(d.x), "=f"(d.y), "=f"(d.z), "=f"(d.w) : "r"(stats_sa + (kStream + c) * 4));
+      l4[0] = a.x * kLog2e; l4[1] = a.y * kLog2e; l4[2] = a.z * kLog2e; l4[3] = a.w * kLog2e;
+      d4[0] = d.x * scale; d4[1] = d.y * scale; d4[2] = d.z * scale; d4[3] = d.w * scale;
+    } else {
+      l4[0] = l4[1] = l4[2] = l4[3] = lse2_row;
+      d4[0] = d4[1] = d4[2] = d4[3] = dsc_row;
+    }
+    float pr[4], ds[4];
 #pragma unroll
-  for (int g = 0; g < 8; ++g) {
-    uint4 u;
-    __nv_bfloat162 t0 = __floats2bfloat162_rn(v[g * 8 + 0], v[g * 8 + 1]);
-    __nv_bfloat162 t1 = __floats2bfloat162_rn(v[g * 8 + 2], v[g * 8 + 3]);
-    __nv_bfloat162 t2 = __floats2bfloat162_rn(v[g * 8 + 4], v[g * 8 + 5]);
-    __nv_bfloat162 t3 = __floats2bfloat162_rn(v[g * 8 + 6], v[g * 8 + 7]);
-    u.x = *reinterpret_cast<uint32_t*>(&t0);
-    u.y = *reinterpret_cast<uint32_t*>(&t1);
-    u.z = *reinterpret_cast<uint32_t*>(&t2);
-    u.w = *reinterpret_cast<uint32_t*>(&t3);
-    *reinterpret_cast<uint4*>(prow + ((g ^ (row & 7)) << 4)) = u;
+    for (int i = 0; i < 4; ++i) {
+      const float e = bwd_exp2(fmaf(__uint_as_float(sr[c + i]), scale_log2e, -l4[i]));
+      const float t = fmaf(__uint_as_float(dr[c + i]), scale, -d4[i]);
+      if (MASKED) {
+        const int yi = y0i + c + i;
+        const bool valid = (yi >= y_lo) & (yi < y_hi);
+        pr[i] = valid ? e : 0.f;
+        ds[i] = valid ? e * t : 0.f;
+      } else {
+        pr[i] = e;
+        ds[i] = e * t;
+      }
+    }
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(pr[0], pr[1]), p1 = __floats2bfloat162_rn(pr[2], pr[3]);
+    __nv_bfloat162 s0 = __floats2bfloat162_rn(ds[0], ds[1]), s1 = __floats2bfloat162_rn(ds[2], ds[3]);
+    pw[c / 2] = *reinterpret_cast<uint32_t*>(&p0);
+    pw[c / 2 + 1] = *reinterpret_cast<uint32_t*>(&p1);
+    dw[c / 2] = *reinterpret_cast<uint32_t*>(&s0);
+    dw[c / 2 + 1] = *reinterpret_cast<uint32_t*>(&s1);
   }
 }
 
@@ -135,8 +141,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
   uint64_t* y_full = bars + 1;                    // kYStages
   uint64_t* y_empty = y_full + kYStages;          // kYStages
   uint64_t* sdp_full = y_empty + kYStages;        // 2
-  uint64_t* sdp_empty = sdp_full + 2;             // 2 (128 arrivals)
-  uint64_t* pds_full = sdp_empty + 2;             // 1 (128 arrivals)
+  uint64_t* pds_full = sdp_full + 2;              // 1 (256 arrivals)
   uint64_t* acc_done = pds_full + 1;              // 1
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
   volatile uint32_t* abort_w = tmem_slot + 1;
@@ -180,7 +185,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sdp_full[i], 1);
-      mbar_init(&sdp_empty[i], kSoftThreads);
     }
     mbar_init(pds_full, kSoftThreads);
     mbar_init(acc_done, 1);
@@ -244,17 +248,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
       constexpr uint32_t idesc_acc = make_idesc_f16(kStat, D, 1, 0, 1);
       const uint32_t x0_s = smem_u32(smem + L::kX0);
       const uint32_t x1_s = smem_u32(smem + L::kX1);
-      const uint32_t p_s = smem_u32(smem + L::kP);
-      const uint32_t ds_s = smem_u32(smem + L::kDS);
       auto issue_sdp = [&](int it) -> bool {
         const int ys = it % kYStages;
         const uint32_t yph = (it / kYStages) & 1;
         const int s = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
         if (!mbar_wait(&y_full[ys], yph, wc, 2)) return false;
         trace_pt(p, 1, it, 1);
-        if (!mbar_wait(&sdp_empty[s], ph ^ 1, wc, 3)) return false;
-        trace_pt(p, 1, it, 2);
+        // Slot s last held iteration it - 2: its S / dP were read by the P/dS warps before they
+        // arrived on pds_full(it - 2), and its P / dS (same columns) are consumed by MMAs issued
+        // earlier by this thread, which the tensor pipe executes in order before these.
         tc_fence_after_sync();
         const uint32_t y0_s = smem_u32(smem + L::kY + ys * 2 * L::kStreamBytes);
         const uint32_t y1_s = y0_s + L::kStreamBytes;
@@ -287,21 +289,25 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
         tc_fence_after_sync();
         const uint32_t y0_s = smem_u32(smem + L::kY + s * 2 * L::kStreamBytes);
         const uint32_t y1_s = y0_s + L::kStreamBytes;
+        // P and dS are the A operands straight from TMEM: bf16 pairs written over the S / dP
+        // columns; k-step kk (16 streamed rows) sits at column (kk / 2) * 32 + (kk % 2) * 8
+        const uint32_t t_p = tmem_base + (it & 1) * 128;
 #pragma unroll
         for (int kk = 0; kk < kStream / 16; ++kk) {
+          const uint32_t a_col = (kk >> 1) * 32 + (kk & 1) * 8;
           // acc1 += dS * Y0  (dK += dS^T Q  or  dQ += dS K)
-          umma_f16_ss(tmem_acc1, make_smem_desc_sw128(ds_s + kk * 32, 16, 1024),
+          umma_f16_ts(tmem_acc1, t_p + 64 + a_col,
                       make_smem_desc_sw128(y0_s + kk * 2048, kStream * 128, 1024), idesc_acc,
                       (it | kk) != 0);
           if (DKV) {
             // acc0 += P^T * dO
-            umma_f16_ss(tmem_acc0, make_smem_desc_sw128(p_s + kk * 32, 16, 1024),
+            umma_f16_ts(tmem_acc0, t_p + a_col,
                         make_smem_desc_sw128(y1_s + kk * 2048, kStream * 128, 1024), idesc_acc,
                         (it | kk) != 0);
           }
         }
-        umma_commit(acc_done);
         umma_commit(&y_empty[s]);
+        if (it == n_it - 1) umma_commit(acc_done);
         trace_pt(p, 1, it, 4);
       }
     }
@@ -317,10 +323,21 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
     if (!DKV) {
       if (xi < p.Tq) {
         long long o = ((long long)b * p.Hq + hx) * p.lse_stride + xi;
-        lse_row = p.lse[o] * log2e;
+        lse_row = p.lse[o];
         delta_row = p.delta[o];
       }
     }
+    // streamed indices (queries for dKV, keys for dQ) that this row may pair with
+    int y_lo, y_hi;
+    if (DKV) {
+      y_lo = (xi < p.Tk) ? (p.causal ? max(xi - p.kv_offset, 0) : 0) : 0x3fffffff;
+      y_hi = p.Tq;
+    } else {
+      y_lo = 0;
+      y_hi = (xi < p.Tq) ? (p.causal ? min(p.Tk, xi + p.kv_offset + 1) : p.Tk) : 0;
+    }
+    lse_row *= log2e;
+    delta_row *= p.scale;
     bool ok = true;
     for (int it = 0; it < n_it; ++it) {
       const int s = it & 1;
@@ -336,16 +353,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
       tmem_ld_32x32b_x32(tmem_base + t_lane + s * 128 + half * 32, sr);
       tmem_ld_32x32b_x32(tmem_base + t_lane + s * 128 + 64 + half * 32, dr);
       tmem_ld_wait();
-      tc_fence_before_sync();
-      mbar_arrive(&sdp_empty[s]);
       if (threadIdx.x == 64) trace_pt(p, 2, it, 2);
 
-      // tiles entirely inside the causal / length limits skip the per-element predicate
-      const int key_hi = DKV ? x0 + kStat - 1 : y0i + 31;
-      const int qry_lo = DKV ? y0i : x0;
-      const int qry_hi = DKV ? y0i + 31 : x0 + kStat - 1;
-      const bool need_mask = (key_hi >= p.Tk) || (qry_hi >= p.Tq) || (p.causal && key_hi > qry_lo + p.kv_offset);
-      float pv[32], dsv[32];
+      // Valid streamed indices of this thread's row form one interval [lo, hi): tiles that lie
+      // entirely inside it take the predicate-free path (warp-uniform choice).
+      const bool need_mask = __any_sync(0xffffffffu, (y0i < y_lo) || (y0i + 32 > y_hi));
       uint32_t lse_sa = 0;
       if (DKV) {
         // statistics landed with the tile (the wait below returns at once and orders the read)
@@ -353,51 +365,19 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
         if (!mbar_wait_warp(&y_full[ys], (it / kYStages) & 1, wc, 9)) { ok = false; break; }
         lse_sa = smem_u32(smem + L::kStats) + (ys * 2 * kStream + half * 32) * 4;
       }
-      if (p.debug & 2) {
-#pragma unroll
-        for (int c = 0; c < 32; ++c) { pv[c] = __uint_as_float(sr[c]); dsv[c] = __uint_as_float(dr[c]); }
-      } else
-#pragma unroll
-      for (int c = 0; c < 32; c += 4) {
-        float l4[4], d4[4];
-        if (DKV) {
-          float4 a, d;
-          asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w) : "r"(lse_sa + c * 4));
-          asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(d.x), "=f"(d.y), "=f"(d.z), "=f"(d.w) : "r"(lse_sa + (kStream + c) * 4));
-          l4[0] = a.x * log2e; l4[1] = a.y * log2e; l4[2] = a.z * log2e; l4[3] = a.w * log2e;
-          d4[0] = d.x; d4[1] = d.y; d4[2] = d.z; d4[3] = d.w;
-        } else {
-          l4[0] = l4[1] = l4[2] = l4[3] = lse_row;
-          d4[0] = d4[1] = d4[2] = d4[3] = delta_row;
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int col = c + i;
-          const int yi = y0i + col;
-          const int key = DKV ? xi : yi;
-          const int qry = DKV ? yi : xi;
-          const bool valid = !need_mask ||
-                             ((key < p.Tk) && (qry < p.Tq) && (!p.causal || key <= qry + p.kv_offset));
-          float sv = __uint_as_float(sr[col]);
-          float dp = __uint_as_float(dr[col]);
-          float pr = valid ? ((p.debug & 1) ? (sv * p.scale_log2e - l4[i]) : bwd_exp2(sv * p.scale_log2e - l4[i])) : 0.f;
-          pv[col] = pr;
-          dsv[col] = valid ? pr * (dp - d4[i]) * p.scale : 0.f;
-        }
-      }
+      uint32_t pw[16], dw[16];
+      if (need_mask) pds_math<DKV, true>(sr, dr, lse_sa, lse_row, delta_row, y0i, y_lo, y_hi, p.scale_log2e, p.scale, pw, dw);
+      else pds_math<DKV, false>(sr, dr, lse_sa, lse_row, delta_row, y0i, y_lo, y_hi, p.scale_log2e, p.scale, pw, dw);
       if (threadIdx.x == 64) trace_pt(p, 2, it, 3);
-      if (it > 0) {
-        if (!mbar_wait_warp(acc_done, (it - 1) & 1, wc, 7)) { ok = false; break; }
-      }
-      if (threadIdx.x == 64) trace_pt(p, 2, it, 4);
-      if (DKV) store_row32_sw128(smem + L::kP, row, half, pv);
-      store_row32_sw128(smem + L::kDS, row, half, dsv);
-      fence_proxy_async_smem();
+      // P / dS (bf16 pairs) go back into this warp's own S / dP columns
+      if (DKV) tmem_st_32x32b_x16(tmem_base + t_lane + s * 128 + half * 32, pw);
+      tmem_st_32x32b_x16(tmem_base + t_lane + s * 128 + 64 + half * 32, dw);
+      tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(pds_full);
       if (threadIdx.x == 64) trace_pt(p, 2, it, 5);
     }
-    if (ok && n_it > 0) ok = mbar_wait_warp(acc_done, (n_it - 1) & 1, wc, 8);
+    if (ok && n_it > 0) ok = mbar_wait_warp(acc_done, 0, wc, 8);
     if (ok) {
       tc_fence_after_sync();
       const int t_lim = DKV ? p.Tk : p.Tq;
@@ -483,7 +463,6 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o,
 
 static unsigned long long* g_bwd_trace = nullptr;
 static int g_bwd_trace_cap = 0;
-static int g_bwd_debug = 0;
 
 template <int D, bool DKV>
 static int launch_bwd(const CUtensorMap& x0, const CUtensorMap& x1, const CUtensorMap& y0,
@@ -538,7 +517,7 @@ extern "C" int tpb_flash_bwd(const void* dout, const void* q, const void* k, con
   p.kv_offset = Tk - Tq; p.scale = scale; p.scale_log2e = scale * 1.4426950408889634f;
   p.lse = lse; p.delta = delta; p.lse_stride = lse_stride; p.status = status;
   p.wait_ns = kDefaultWaitNs;
-  p.trace = g_bwd_trace; p.trace_cap = g_bwd_trace_cap; p.debug = g_bwd_debug;
+  p.trace = g_bwd_trace; p.trace_cap = g_bwd_trace_cap;
   int r;
   // ---- dK / dV: [B, Tk, Hkv, D] by the dkv strides (dk and dv share them)
   {
@@ -574,10 +553,6 @@ extern "C" int tpb_flash_bwd(const void* dout, const void* q, const void* k, con
 // Debug aid: buf = device array of 1 + 2 * cap uint64 (buf[0] = record count, zero it first). The
 // next backward launches record role / iteration / phase timestamps of block (0,0,0) of BOTH
 // passes into it. Pass null to switch tracing off.
-extern "C" int tpb_flash_bwd_set_debug(int flags) {
-  tpb::g_bwd_debug = flags;
-  return 0;
-}
 extern "C" int tpb_flash_bwd_set_trace(unsigned long long* buf, int cap) {
   tpb::g_bwd_trace = buf;
   tpb::g_bwd_trace_cap = cap;

@@ -1,12 +1,14 @@
 // Flash attention forward for sm_100a: GQA-native, causal or full, head_dim 64 / 128.
 //
-// One CTA handles 128 queries of one query head. Warp 0 streams K/V tiles with TMA (two
-// stages each), warp 1 issues tcgen05.mma: S = Q K^T into a double-buffered TMEM accumulator
-// and O += P V into a second TMEM region; four softmax warps own one query row per thread:
-// they read S from TMEM, keep the running max / sum in the exp2 domain, write P (bf16) into a
-// 128-byte-swizzled shared tile for the second MMA, rescale O in TMEM only when a row max
-// moved, and finally write O / LSE. K and V of a KV head are shared by the query heads of
-// its group through L2, so GQA costs no expanded K/V traffic.
+// One CTA handles two tiles of 128 queries of one query head in ping-pong. Warp 0 streams K/V
+// tiles with TMA through one ring, warp 1 issues tcgen05.mma: S_g = Q_g K^T into the TMEM region
+// of tile g and O_g += P_g V into a second region; each tile has four softmax warps with one
+// query row per thread: they read S from TMEM, keep the running max / sum in the exp2 domain,
+// write P (bf16 pairs) back over the S columns - the second MMA takes P as its A operand
+// straight from TMEM - rescale O in TMEM only when a row maximum grew by more than a factor of two, and
+// finally write O / LSE. While one tile is in its softmax the tensor pipe runs the other tile's
+// MMAs. K and V of a KV head are shared by the query heads of its group through L2, so GQA costs
+// no expanded K/V traffic.
 //
 // Counterpart in the reference: vendored FlashAttention-2 sm80 leaves
 // (p10/src/backend/cuda/transformers/flash/flash_fwd_kernel.h, AttentionKernels.cu:1782-1969),
@@ -18,8 +20,9 @@
 
 namespace tpb {
 
-constexpr int kAttnThreads = 320;  // TMA warp, MMA warp, 8 softmax warps (two per TMEM lane quarter)
+constexpr int kAttnThreads = 320;  // TMA warp, MMA warp, 2 x 4 softmax warps (one group per query tile)
 constexpr int kBlockQ = 128;
+constexpr int kTilesQ = 2;  // query tiles per CTA, processed in ping-pong
 constexpr int kBlockKV = 128;
 constexpr float kNegBig = -1.0e30f;
 
@@ -45,18 +48,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
 template <int D>
 struct AttnSmem {
   static constexpr int kChunks = D / 64;
-  static constexpr int kQBytes = kBlockQ * D * 2;
-  static constexpr int kKBytes = kBlockKV * D * 2;
-  static constexpr int kPBytes = kBlockQ * kBlockKV * 2;
-  static constexpr int kQOff = 0;
-  // K and V tiles share one ring (K0 V0 K1 V1 ...): the loads run up to kRing tiles ahead
-  static constexpr int kRing = D == 128 ? 5 : 6;
-  static constexpr int kKOff = kQOff + kQBytes;
-  static constexpr int kPOff = kKOff + kRing * kKBytes;
-  // row-max exchange between the two halves: bf16 [2 buffers][2 halves][128 rows], then the
-  // fp32 row sums [2 halves][128 rows] exchanged once at the end
-  static constexpr int kXOff = kPOff + kPBytes;
-  static constexpr int kBarOff = kXOff + 2 * 2 * 128 * 2;
+  static constexpr int kQBytes = kBlockQ * D * 2;   // one Q tile
+  static constexpr int kKBytes = kBlockKV * D * 2;  // one K or V tile
+  static constexpr int kQOff = 0;                   // two Q tiles
+  // K and V tiles share one ring (K0 V0 K1 V1 ...)
+  static constexpr int kRing = D == 128 ? 4 : 6;
+  static constexpr int kKOff = kQOff + kTilesQ * kQBytes;
+  static constexpr int kBarOff = kKOff + kRing * kKBytes;
   static constexpr int kTotal = kBarOff + 256 + 1024;
   static_assert(kTotal <= 227 * 1024, "attention forward exceeds the shared memory of one CTA");
 };
@@ -74,12 +72,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* q_full = bars;              // 1
   uint64_t* kv_full = bars + 1;         // R
   uint64_t* kv_empty = kv_full + R;     // R
-  uint64_t* s_full = kv_empty + R;      // 2
-  uint64_t* s_empty = s_full + 2;       // 2 (128 arrivals)
-  uint64_t* p_full = s_empty + 2;       // 1 (128 arrivals)
-  uint64_t* pv_done = p_full + 1;       // 1
-  uint64_t* pair_bar = pv_done + 1;     // 4 (64 arrivals: the two warps sharing a lane quarter)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pair_bar + 4);
+  uint64_t* s_full = kv_empty + R;      // 2: S of tile g is complete (and so is every earlier MMA)
+  uint64_t* p_full = s_full + 2;        // 2 (128 arrivals): P of tile g is in TMEM
+  uint64_t* o_done = p_full + 2;        // 2: last PV of tile g is complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
   volatile uint32_t* abort_w = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -88,13 +84,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int h = blockIdx.y;
   const int b = blockIdx.z;
   const int hk = h / (p.Hq / p.Hkv);
-  const int q0 = qb * kBlockQ;
-  int nkv = (p.Tk + kBlockKV - 1) / kBlockKV;
-  if (p.causal) {
-    int last_key = q0 + kBlockQ - 1 + p.kv_offset;
-    int lim = last_key / kBlockKV + 1;
-    if (last_key < 0) lim = 0;
-    nkv = min(nkv, lim);
+  const int q0 = qb * (kTilesQ * kBlockQ);
+  // KV blocks needed by each of the two query tiles
+  int nkv_t[kTilesQ];
+  int nkv = 0;
+#pragma unroll
+  for (int g = 0; g < kTilesQ; ++g) {
+    int n = (p.Tk + kBlockKV - 1) / kBlockKV;
+    if (p.causal) {
+      const int last_key = q0 + g * kBlockQ + kBlockQ - 1 + p.kv_offset;
+      n = last_key < 0 ? 0 : min(n, last_key / kBlockKV + 1);
+    }
+    if (q0 + g * kBlockQ >= p.Tq) n = 0;  // tile past the end of the sequence
+    nkv_t[g] = n;
+    nkv = max(nkv, n);
   }
 
   if (threadIdx.x == 0) {
@@ -104,13 +107,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
     }
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kTilesQ; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 256);
+      mbar_init(&p_full[i], 128);
+      mbar_init(&o_done[i], 1);
     }
-    for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 64);
-    mbar_init(p_full, 256);
-    mbar_init(pv_done, 1);
     fence_barrier_init();
     prefetch_tmap(&tmQ);
     prefetch_tmap(&tmK);
@@ -124,15 +125,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_o = tmem_base + 256;
   WaitCtx wc{abort_w, p.status, p.wait_ns};
 
   if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
     if (lane == 0 && nkv > 0) {
-      mbar_arrive_expect_tx(q_full, L::kQBytes);
+      mbar_arrive_expect_tx(q_full, kTilesQ * L::kQBytes);
 #pragma unroll
-      for (int c = 0; c < L::kChunks; ++c)
-        tma_load_4d(smem + L::kQOff + c * (kBlockQ * 128), &tmQ, q_full, c * 64, h, q0, b);
+      for (int g = 0; g < kTilesQ; ++g)
+#pragma unroll
+        for (int c = 0; c < L::kChunks; ++c)
+          tma_load_4d(smem + L::kQOff + g * L::kQBytes + c * (kBlockQ * 128), &tmQ, q_full, c * 64, h,
+                      q0 + g * kBlockQ, b);
       for (int t = 0; t < 2 * nkv; ++t) {
         const int j = t >> 1;
         const int slot = t % R;
@@ -147,174 +151,177 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
   } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    // Order on the tensor pipe: S0(0) S1(0) | PV0(0) S0(1) PV1(0) S1(1) | PV0(1) S0(2) ...
+    // While the softmax warps of one tile work, the pipe runs the other tile's MMAs. P(j) lives
+    // in the columns of S(j); S(j+1) is issued after PV(j) and the pipe executes in issue order,
+    // so the overwrite needs no barrier.
     if (lane == 0 && nkv > 0) {
       constexpr uint32_t idesc_s = make_idesc_f16(kBlockQ, kBlockKV, 1, 0, 0);
       constexpr uint32_t idesc_o = make_idesc_f16(kBlockQ, D, 1, 0, 1);
       const uint32_t q_s = smem_u32(smem + L::kQOff);
-      const uint32_t p_s = smem_u32(smem + L::kPOff);
-      auto issue_s = [&](int j) -> bool {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
+      auto issue_s = [&](int g, int j) {
         const int slot = (2 * j) % R;
-        const uint32_t kph = ((2 * j) / R) & 1;
-        if (!mbar_wait(&kv_full[slot], kph, wc, 3)) return false;
-        if (!mbar_wait(&s_empty[s], ph ^ 1, wc, 4)) return false;
-        tc_fence_after_sync();
         const uint32_t k_s = smem_u32(smem + L::kKOff + slot * L::kKBytes);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * (kBlockQ * 128) + (kk % 4) * 32;
-          umma_f16_ss(tmem_base + s * 128, make_smem_desc_sw128(q_s + off, 16, 1024),
+          umma_f16_ss(tmem_base + g * 128, make_smem_desc_sw128(q_s + g * L::kQBytes + off, 16, 1024),
                       make_smem_desc_sw128(k_s + off, 16, 1024), idesc_s, kk != 0);
         }
-        umma_commit(&s_full[s]);
-        umma_commit(&kv_empty[slot]);
-        return true;
+        umma_commit(&s_full[g]);
       };
       bool ok = mbar_wait(q_full, 0, wc, 5);
-      if (ok) ok = issue_s(0);
-      for (int j = 0; j < nkv && ok; ++j) {
-        if (j + 1 < nkv) {
-          if (!issue_s(j + 1)) break;
-        }
-        const int slot = (2 * j + 1) % R;
-        const uint32_t vph = ((2 * j + 1) / R) & 1;
-        if (!mbar_wait(p_full, j & 1, wc, 6)) break;
-        if (!mbar_wait(&kv_full[slot], vph, wc, 7)) break;
+      if (ok) ok = mbar_wait(&kv_full[0], 0, wc, 3);
+      if (ok) {
         tc_fence_after_sync();
-        const uint32_t v_s = smem_u32(smem + L::kKOff + slot * L::kKBytes);
 #pragma unroll
-        for (int kk = 0; kk < kBlockKV / 16; ++kk) {
-          const uint32_t poff = (kk / 4) * (kBlockQ * 128) + (kk % 4) * 32;
-          umma_f16_ss(tmem_o, make_smem_desc_sw128(p_s + poff, 16, 1024),
-                      make_smem_desc_sw128(v_s + kk * 2048, kBlockKV * 128, 1024), idesc_o,
-                      (j | kk) != 0);
+        for (int g = 0; g < kTilesQ; ++g)
+          if (nkv_t[g] > 0) issue_s(g, 0);
+        umma_commit(&kv_empty[0]);
+      }
+      for (int j = 0; j < nkv && ok; ++j) {
+        const int vslot = (2 * j + 1) % R;
+        const uint32_t vph = ((2 * j + 1) / R) & 1;
+        const int kslot = (2 * j + 2) % R;
+        const uint32_t kph = ((2 * j + 2) / R) & 1;
+        const uint32_t v_s = smem_u32(smem + L::kKOff + vslot * L::kKBytes);
+        bool have_v = false, have_k = false;
+#pragma unroll
+        for (int g = 0; g < kTilesQ; ++g) {
+          if (j >= nkv_t[g]) continue;
+          if (!mbar_wait(&p_full[g], j & 1, wc, 6)) { ok = false; break; }
+          if (!have_v) {
+            if (!mbar_wait(&kv_full[vslot], vph, wc, 7)) { ok = false; break; }
+            have_v = true;
+          }
+          tc_fence_after_sync();
+#pragma unroll
+          for (int kk = 0; kk < kBlockKV / 16; ++kk)
+            umma_f16_ts(tmem_base + 256 + g * 128, tmem_base + g * 128 + kk * 8,
+                        make_smem_desc_sw128(v_s + kk * 2048, kBlockKV * 128, 1024), idesc_o,
+                        (j | kk) != 0);
+          if (j + 1 < nkv_t[g]) {
+            if (!have_k) {
+              if (!mbar_wait(&kv_full[kslot], kph, wc, 3)) { ok = false; break; }
+              have_k = true;
+              tc_fence_after_sync();
+            }
+            issue_s(g, j + 1);
+          } else {
+            umma_commit(&o_done[g]);
+          }
         }
-        umma_commit(pv_done);
-        umma_commit(&kv_empty[slot]);
+        if (!ok) break;
+        umma_commit(&kv_empty[vslot]);
+        if (have_k) umma_commit(&kv_empty[kslot]);
       }
     }
   } else {
     // ---------------------------------------------------------------- softmax / epilogue
+    // warps 2..5 own query tile 0, warps 6..9 tile 1; one query row per thread
+    const int g = (warp - 2) >> 2;
     const int qd = warp & 3;
-    const int half = (warp - 2) >> 2;  // which 64 of the block's 128 keys this warp handles
-    const int row = qd * 32 + lane;    // row inside the tile == TMEM lane
-    const int qi = q0 + row;
-    const uint32_t t_lane = ((uint32_t)(qd * 32) << 16);
-    __nv_bfloat16* xch = reinterpret_cast<__nv_bfloat16*>(smem + L::kXOff);
+    const int row = qd * 32 + lane;  // row inside the tile == TMEM lane
+    const int qi = q0 + g * kBlockQ + row;
+    const uint32_t t_s = tmem_base + ((uint32_t)(qd * 32) << 16) + g * 128;
+    const uint32_t t_o = tmem_base + ((uint32_t)(qd * 32) << 16) + 256 + g * 128;
+    const int my_nkv = nkv_t[g];
+    const int lim = p.causal ? min(qi + p.kv_offset, p.Tk - 1) : (p.Tk - 1);  // last valid key
     float m = kNegBig, l = 0.f;
     bool ok = true;
-    uint32_t xph = 0;  // phase of the pair barrier
-    for (int j = 0; j < nkv; ++j) {
-      const int s = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      if (!mbar_wait_warp(&s_full[s], ph, wc, 8)) { ok = false; break; }
+    for (int j = 0; j < my_nkv; ++j) {
+      if (!mbar_wait_warp(&s_full[g], j & 1, wc, 8)) { ok = false; break; }
       tc_fence_after_sync();
-      uint32_t sr[2][32];
+      const int k0 = j * kBlockKV;
+      const bool need_mask = (p.causal && (k0 + kBlockKV - 1 > q0 + g * kBlockQ + p.kv_offset)) ||
+                             (k0 + kBlockKV > p.Tk);
+      // pass 1: row maximum
+      float mx = kNegBig;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sr[32];
+        tmem_ld_32x32b_x32(t_s + c * 32, sr);
+        tmem_ld_wait();
+        if (need_mask) {
 #pragma unroll
-      for (int c = 0; c < 2; ++c) tmem_ld_32x32b_x32(tmem_base + t_lane + s * 128 + half * 64 + c * 32, sr[c]);
-      tmem_ld_wait();
-      tc_fence_before_sync();
-      mbar_arrive(&s_empty[s]);
-
-      const int k0 = j * kBlockKV + half * 64;
-      const bool need_mask = (p.causal && (k0 + 63 > q0 + p.kv_offset)) || (k0 + 64 > p.Tk);
-      const int lim = p.causal ? min(qi + p.kv_offset, p.Tk - 1) : (p.Tk - 1);  // last valid key
-      float mx = m;
+          for (int i = 0; i < 32; ++i)
+            if (k0 + c * 32 + i <= lim) mx = fmaxf(mx, __uint_as_float(sr[i]));
+        } else {
 #pragma unroll
-      for (int c = 0; c < 2; ++c)
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(sr[c][i]) * p.scale_log2e;
-          if (need_mask && (k0 + c * 32 + i > lim)) v = kNegBig;
-          sr[c][i] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
+          for (int i = 0; i < 32; i += 2)
+            mx = fmaxf(mx, fmaxf(__uint_as_float(sr[i]), __uint_as_float(sr[i + 1])));
         }
-      // Row maximum over both halves. The halves exchange it rounded UP to bf16 (two buffers of
-      // 16-bit slots fit the shared memory left over): any common reference >= the true maximum
-      // serves the softmax, and both halves use exactly the same value.
-      {
-        const __nv_bfloat16 mine = __float2bfloat16_ru(mx);
-        xch[((j & 1) * 2 + half) * 128 + row] = mine;
-        mbar_arrive(&pair_bar[qd]);
-        if (!mbar_wait_warp(&pair_bar[qd], xph, wc, 11)) { ok = false; break; }
-        xph ^= 1;
-        mx = fmaxf(__bfloat162float(mine),
-                   __bfloat162float(xch[((j & 1) * 2 + (half ^ 1)) * 128 + row]));
       }
-      const float alpha = fast_exp2(m - mx);
-      m = mx;
-      // p = exp2(s - max) two at a time in bf16 (ex2.approx.bf16x2): P is consumed as bf16 by the
-      // second MMA anyway, the packed form halves the MUFU work, and the row sum adds exactly the
-      // rounded values that the MMA multiplies with V.
-      float sum = 0.f;
-      uint32_t pw[32];
+      mx = fmaxf(m, mx * p.scale_log2e);
+      // The reference maximum only moves when the row maximum grew by more than a factor of two:
+      // until then P stays below 2 and O needs no rescale. (A larger slack would cost accuracy:
+      // the exponent is rounded to bf16 before ex2, which is only harmless near zero.)
+      float alpha = 1.f;
+      if (mx - m > 1.f) {
+        alpha = fast_exp2(m - mx);
+        m = mx;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        // every MMA issued before S(j), PV(j-1) included, completed before s_full fired
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(t_o + c * 32, o);
+          tmem_ld_wait();
+          uint32_t lo[16], hi[16];
 #pragma unroll
-      for (int c = 0; c < 2; ++c)
+          for (int i = 0; i < 16; ++i) {
+            lo[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            hi[i] = __float_as_uint(__uint_as_float(o[16 + i]) * alpha);
+          }
+          tmem_st_32x32b_x16(t_o + c * 32, lo);
+          tmem_st_32x32b_x16(t_o + c * 32 + 16, hi);
+        }
+      }
+      // pass 2: P = exp2(S * scale - m) as bf16 pairs (ex2.approx.bf16x2 halves the MUFU work; the
+      // row sum adds exactly the rounded values that the MMA multiplies with V), written over the
+      // first 64 columns of S: chunk c (32 keys) lands on columns 16c..16c+15, which belong to S
+      // chunks already consumed.
+      float sum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sr[32];
+        tmem_ld_32x32b_x32(t_s + c * 32, sr);
+        tmem_ld_wait();
+        uint32_t pw[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          __nv_bfloat162 d = __floats2bfloat162_rn(__uint_as_float(sr[c][i]) - mx,
-                                                   __uint_as_float(sr[c][i + 1]) - mx);
+          float x0 = __uint_as_float(sr[i]) * p.scale_log2e - m;
+          float x1 = __uint_as_float(sr[i + 1]) * p.scale_log2e - m;
+          if (need_mask) {
+            if (k0 + c * 32 + i > lim) x0 = kNegBig;
+            if (k0 + c * 32 + i + 1 > lim) x1 = kNegBig;
+          }
+          __nv_bfloat162 d = __floats2bfloat162_rn(x0, x1);
           uint32_t e;
           asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(e) : "r"(*reinterpret_cast<uint32_t*>(&d)));
           sum += __uint_as_float(e << 16) + __uint_as_float(e & 0xffff0000u);
-          pw[c * 16 + i / 2] = e;
+          pw[i / 2] = e;
         }
+        tmem_st_32x32b_x16(t_s + c * 16, pw);
+      }
       l = l * alpha + sum;
-
-      if (j > 0) {
-        if (!mbar_wait_warp(pv_done, (j - 1) & 1, wc, 9)) { ok = false; break; }
-        tc_fence_after_sync();
-        if (__any_sync(0xffffffffu, alpha != 1.f)) {
-          // each half rescales its half of the head dimension
-#pragma unroll 1
-          for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
-            uint32_t o[32];
-            tmem_ld_32x32b_x32(tmem_o + t_lane + c * 32, o);
-            tmem_ld_wait();
-            uint32_t lo[16], hi[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              lo[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-              hi[i] = __float_as_uint(__uint_as_float(o[16 + i]) * alpha);
-            }
-            tmem_st_32x32b_x16(tmem_o + t_lane + c * 32, lo);
-            tmem_st_32x32b_x16(tmem_o + t_lane + c * 32 + 16, hi);
-          }
-          tmem_st_wait();
-        }
-      }
-      // P (bf16) into the swizzled tile: chunk = key / 64 = half, 16-byte slot = (key % 64) / 8
-      uint8_t* prow = smem + L::kPOff + half * (kBlockQ * 128) + row * 128;
-#pragma unroll
-      for (int g = 0; g < 8; ++g) {
-        uint4 v = make_uint4(pw[g * 4 + 0], pw[g * 4 + 1], pw[g * 4 + 2], pw[g * 4 + 3]);
-        *reinterpret_cast<uint4*>(prow + ((g ^ (row & 7)) << 4)) = v;
-      }
-      fence_proxy_async_smem();
+      tmem_st_wait();
       tc_fence_before_sync();
-      mbar_arrive(p_full);
+      mbar_arrive(&p_full[g]);
     }
-    if (ok && nkv > 0) ok = mbar_wait_warp(pv_done, (nkv - 1) & 1, wc, 10);
-    if (ok) {
-      // total row sum = sum of the two halves, exchanged through the P tile, which is idle once
-      // the last PV MMA has completed
-      float* xl = reinterpret_cast<float*>(smem + L::kPOff);
-      xl[half * 128 + row] = l;
-      mbar_arrive(&pair_bar[qd]);
-      ok = mbar_wait_warp(&pair_bar[qd], xph, wc, 12);
-      l += xl[(half ^ 1) * 128 + row];
-    }
+    if (ok && my_nkv > 0) ok = mbar_wait_warp(&o_done[g], 0, wc, 10);
     if (ok) {
       tc_fence_after_sync();
-      const float inv = (nkv > 0 && l > 0.f) ? 1.f / l : 0.f;
+      const float inv = (my_nkv > 0 && l > 0.f) ? 1.f / l : 0.f;
       __nv_bfloat16* orow = p.O + (long long)b * p.o_batch_stride + (long long)qi * p.o_tok_stride +
                             (long long)h * p.o_head_stride;
 #pragma unroll 1
-      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
+      for (int c = 0; c < D / 32; ++c) {
         uint32_t o[32];
-        if (nkv > 0) {
-          tmem_ld_32x32b_x32(tmem_o + t_lane + c * 32, o);
+        if (my_nkv > 0) {
+          tmem_ld_32x32b_x32(t_o + c * 32, o);
           tmem_ld_wait();
         } else {
 #pragma unroll
@@ -322,26 +329,26 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         if (qi < p.Tq) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
+          for (int gg = 0; gg < 4; ++gg) {
             uint4 v;
-            __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(o[g * 8 + 0]) * inv,
-                                                      __uint_as_float(o[g * 8 + 1]) * inv);
-            __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(o[g * 8 + 2]) * inv,
-                                                      __uint_as_float(o[g * 8 + 3]) * inv);
-            __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(o[g * 8 + 4]) * inv,
-                                                      __uint_as_float(o[g * 8 + 5]) * inv);
-            __nv_bfloat162 t3 = __floats2bfloat162_rn(__uint_as_float(o[g * 8 + 6]) * inv,
-                                                      __uint_as_float(o[g * 8 + 7]) * inv);
+            __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(o[gg * 8 + 0]) * inv,
+                                                      __uint_as_float(o[gg * 8 + 1]) * inv);
+            __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(o[gg * 8 + 2]) * inv,
+                                                      __uint_as_float(o[gg * 8 + 3]) * inv);
+            __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(o[gg * 8 + 4]) * inv,
+                                                      __uint_as_float(o[gg * 8 + 5]) * inv);
+            __nv_bfloat162 t3 = __floats2bfloat162_rn(__uint_as_float(o[gg * 8 + 6]) * inv,
+                                                      __uint_as_float(o[gg * 8 + 7]) * inv);
             v.x = *reinterpret_cast<uint32_t*>(&t0);
             v.y = *reinterpret_cast<uint32_t*>(&t1);
             v.z = *reinterpret_cast<uint32_t*>(&t2);
             v.w = *reinterpret_cast<uint32_t*>(&t3);
-            *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = v;
+            *reinterpret_cast<uint4*>(orow + c * 32 + gg * 8) = v;
           }
         }
       }
-      if (half == 0 && qi < p.Tq && p.lse) {
-        float lse = (nkv > 0 && l > 0.f) ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+      if (qi < p.Tq && p.lse) {
+        float lse = (my_nkv > 0 && l > 0.f) ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
         p.lse[((long long)b * p.Hq + h) * p.lse_stride + qi] = lse;
       }
     }
@@ -416,7 +423,7 @@ static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid((p.Tq + kBlockQ - 1) / kBlockQ, p.Hq, p.B);
+  dim3 grid((p.Tq + kTilesQ * kBlockQ - 1) / (kTilesQ * kBlockQ), p.Hq, p.B);
   kern<<<grid, kAttnThreads, L::kTotal, stream>>>(tq, tk, tv, p);
   return (int)cudaGetLastError();
 }
