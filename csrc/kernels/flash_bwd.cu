@@ -339,20 +339,38 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
     lse_row *= log2e;
     delta_row *= p.scale;
     bool ok = true;
-    for (int it = 0; it < n_it; ++it) {
+    // S / dP of iteration `it` are held in registers; the TMEM loads of iteration it + 1 are
+    // issued before the math of `it` whenever its MMAs have already completed, so that the load
+    // latency hides behind the math.
+    uint32_t sr[32], dr[32];
+    if (n_it > 0) {
+      ok = mbar_wait_warp(&sdp_full[0], 0, wc, 6);
+      if (ok) {
+        tc_fence_after_sync();
+        tmem_ld_32x32b_x32(tmem_base + t_lane + half * 32, sr);
+        tmem_ld_32x32b_x32(tmem_base + t_lane + 64 + half * 32, dr);
+        tmem_ld_wait();
+      }
+    }
+    for (int it = 0; it < n_it && ok; ++it) {
       const int s = it & 1;
-      const uint32_t ph = (it >> 1) & 1;
       int yb;
       if (DKV) yb = y_first + it % y_count;
       else yb = it;
       const int y0i = yb * kStream + half * 32;  // first query (DKV) or key (dQ) of this warp's columns
-      if (!mbar_wait_warp(&sdp_full[s], ph, wc, 6)) { ok = false; break; }
       if (threadIdx.x == 64) trace_pt(p, 2, it, 1);
-      tc_fence_after_sync();
-      uint32_t sr[32], dr[32];
-      tmem_ld_32x32b_x32(tmem_base + t_lane + s * 128 + half * 32, sr);
-      tmem_ld_32x32b_x32(tmem_base + t_lane + s * 128 + 64 + half * 32, dr);
-      tmem_ld_wait();
+      uint32_t sn[32], dn[32];
+      const int s1 = (it + 1) & 1;
+      const uint32_t ph1 = ((it + 1) >> 1) & 1;
+      bool pre = false;
+      if (it + 1 < n_it) {
+        pre = __all_sync(0xffffffffu, mbar_test(&sdp_full[s1], ph1));
+        if (pre) {
+          tc_fence_after_sync();
+          tmem_ld_32x32b_x32(tmem_base + t_lane + s1 * 128 + half * 32, sn);
+          tmem_ld_32x32b_x32(tmem_base + t_lane + s1 * 128 + 64 + half * 32, dn);
+        }
+      }
       if (threadIdx.x == 64) trace_pt(p, 2, it, 2);
 
       // Valid streamed indices of this thread's row form one interval [lo, hi): tiles that lie
@@ -376,6 +394,17 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
       tc_fence_before_sync();
       mbar_arrive(pds_full);
       if (threadIdx.x == 64) trace_pt(p, 2, it, 5);
+      if (it + 1 < n_it) {
+        if (!pre) {
+          if (!mbar_wait_warp(&sdp_full[s1], ph1, wc, 6)) { ok = false; break; }
+          tc_fence_after_sync();
+          tmem_ld_32x32b_x32(tmem_base + t_lane + s1 * 128 + half * 32, sn);
+          tmem_ld_32x32b_x32(tmem_base + t_lane + s1 * 128 + 64 + half * 32, dn);
+        }
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { sr[i] = sn[i]; dr[i] = dn[i]; }
+      }
     }
     if (ok && n_it > 0) ok = mbar_wait_warp(acc_done, 0, wc, 8);
     if (ok) {

@@ -45,6 +45,45 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// Maximum of one S row (raw scores); keys beyond `lim` are excluded in the masked variant.
+template <bool MASKED>
+__device__ __forceinline__ float row_max(const uint32_t (&sr)[128], int k0, int lim) {
+  float mx = kNegBig;
+#pragma unroll
+  for (int i = 0; i < 128; i += 2) {
+    float a = __uint_as_float(sr[i]), b = __uint_as_float(sr[i + 1]);
+    if (MASKED) {
+      a = (k0 + i <= lim) ? a : kNegBig;
+      b = (k0 + i + 1 <= lim) ? b : kNegBig;
+    }
+    mx = fmaxf(mx, fmaxf(a, b));
+  }
+  return mx;
+}
+
+// sr[i / 2] <- bf16 pair exp2(S[i] * scale - m), exp2(S[i+1] * scale - m) in place; returns the
+// sum of the rounded values.
+template <bool MASKED>
+__device__ __forceinline__ float row_exp(uint32_t (&sr)[128], int k0, int lim, float scale_log2e, float m) {
+  float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+  for (int i = 0; i < 128; i += 2) {
+    float x0 = fmaf(__uint_as_float(sr[i]), scale_log2e, -m);
+    float x1 = fmaf(__uint_as_float(sr[i + 1]), scale_log2e, -m);
+    if (MASKED) {
+      x0 = (k0 + i <= lim) ? x0 : kNegBig;
+      x1 = (k0 + i + 1 <= lim) ? x1 : kNegBig;
+    }
+    __nv_bfloat162 d = __floats2bfloat162_rn(x0, x1);
+    uint32_t e;
+    asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(e) : "r"(*reinterpret_cast<uint32_t*>(&d)));
+    s0 += __uint_as_float(e << 16);
+    s1 += __uint_as_float(e & 0xffff0000u);
+    sr[i / 2] = e;
+  }
+  return s0 + s1;
+}
+
 template <int D>
 struct AttnSmem {
   static constexpr int kChunks = D / 64;
@@ -236,23 +275,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int k0 = j * kBlockKV;
       const bool need_mask = (p.causal && (k0 + kBlockKV - 1 > q0 + g * kBlockQ + p.kv_offset)) ||
                              (k0 + kBlockKV > p.Tk);
-      // pass 1: row maximum
-      float mx = kNegBig;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sr[32];
-        tmem_ld_32x32b_x32(t_s + c * 32, sr);
-        tmem_ld_wait();
-        if (need_mask) {
+      // the whole S row (128 fp32) in one TMEM round trip
+      uint32_t sr[128];
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (k0 + c * 32 + i <= lim) mx = fmaxf(mx, __uint_as_float(sr[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2)
-            mx = fmaxf(mx, fmaxf(__uint_as_float(sr[i]), __uint_as_float(sr[i + 1])));
-        }
-      }
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(t_s + c * 32, &sr[c * 32]);
+      tmem_ld_wait();
+      float mx;
+      if (need_mask) mx = row_max<true>(sr, k0, lim);
+      else mx = row_max<false>(sr, k0, lim);
       mx = fmaxf(m, mx * p.scale_log2e);
       // The reference maximum only moves when the row maximum grew by more than a factor of two:
       // until then P stays below 2 and O needs no rescale. (A larger slack would cost accuracy:
@@ -262,6 +292,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         alpha = fast_exp2(m - mx);
         m = mx;
       }
+      // P = exp2(S * scale - m) as bf16 pairs (ex2.approx.bf16x2 halves the MUFU work; the row sum
+      // adds exactly the rounded values that the MMA multiplies with V), written over the first
+      // 64 columns of S
+      float sum;
+      if (need_mask) sum = row_exp<true>(sr, k0, lim, p.scale_log2e, m);
+      else sum = row_exp<false>(sr, k0, lim, p.scale_log2e, m);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_st_32x32b_x16(t_s + c * 16, &sr[c * 16]);
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
         // every MMA issued before S(j), PV(j-1) included, completed before s_full fired
 #pragma unroll 1
@@ -269,42 +307,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           uint32_t o[32];
           tmem_ld_32x32b_x32(t_o + c * 32, o);
           tmem_ld_wait();
-          uint32_t lo[16], hi[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            lo[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            hi[i] = __float_as_uint(__uint_as_float(o[16 + i]) * alpha);
-          }
-          tmem_st_32x32b_x16(t_o + c * 32, lo);
-          tmem_st_32x32b_x16(t_o + c * 32 + 16, hi);
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_32x32b_x16(t_o + c * 32, &o[0]);
+          tmem_st_32x32b_x16(t_o + c * 32 + 16, &o[16]);
         }
-      }
-      // pass 2: P = exp2(S * scale - m) as bf16 pairs (ex2.approx.bf16x2 halves the MUFU work; the
-      // row sum adds exactly the rounded values that the MMA multiplies with V), written over the
-      // first 64 columns of S: chunk c (32 keys) lands on columns 16c..16c+15, which belong to S
-      // chunks already consumed.
-      float sum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sr[32];
-        tmem_ld_32x32b_x32(t_s + c * 32, sr);
-        tmem_ld_wait();
-        uint32_t pw[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float x0 = __uint_as_float(sr[i]) * p.scale_log2e - m;
-          float x1 = __uint_as_float(sr[i + 1]) * p.scale_log2e - m;
-          if (need_mask) {
-            if (k0 + c * 32 + i > lim) x0 = kNegBig;
-            if (k0 + c * 32 + i + 1 > lim) x1 = kNegBig;
-          }
-          __nv_bfloat162 d = __floats2bfloat162_rn(x0, x1);
-          uint32_t e;
-          asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(e) : "r"(*reinterpret_cast<uint32_t*>(&d)));
-          sum += __uint_as_float(e << 16) + __uint_as_float(e & 0xffff0000u);
-          pw[i / 2] = e;
-        }
-        tmem_st_32x32b_x16(t_s + c * 16, pw);
       }
       l = l * alpha + sum;
       tmem_st_wait();

@@ -73,6 +73,7 @@ class ParamUnit:
         self.gather_event = None
         self.update_event = None
         self.local: Optional["ParamUnit"] = None
+        self.red: Optional[Tensor] = None  # reduced gradient shard kept for a clipped (two-phase) step
 
     def bind_params(self, full: Tensor) -> None:
         self.full = full
@@ -268,6 +269,7 @@ class FSDPEngine:
             self.comm_stream = self.opt_stream = None
         self.sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
         self.clip_coef = torch.ones(1, dtype=torch.float32, device=dev)
+        self.grad_norm = torch.zeros(1, dtype=torch.float32, device=dev)  # last step's global norm
         self._grad_slot = 0
 
     # ------------------------------------------------------------------ gather / release
@@ -391,7 +393,9 @@ class FSDPEngine:
             import contextlib
             ctx = contextlib.nullcontext()
         with ctx:
-            if self.world == 1:
+            if self.max_grad_norm is not None:
+                self._reduce_only(u, g)
+            elif self.world == 1:
                 ops.adamw_flat_(u.master, u.exp_avg, u.exp_avg_sq, g, u.shard, **self._adam_kwargs())
             elif self.comm is not None:
                 self.comm.reduce_scatter_adamw(u, g, self._adam_kwargs())
@@ -405,7 +409,18 @@ class FSDPEngine:
                 else:
                     dist.reduce_scatter_tensor(gs, g, op=dist.ReduceOp.AVG, group=self.group)
                 ops.adamw_flat_(u.master, u.exp_avg, u.exp_avg_sq, gs, u.shard, **self._adam_kwargs())
-            if u.local is not None:
+            if u.local is not None and self.max_grad_norm is not None:
+                lu = u.local
+                if lu.red is None:
+                    lu.red = torch.empty(lu.padded, dtype=torch.float32, device=self.device)
+                lu.red.copy_(lu.grad[: lu.padded]).mul_(1.0 / self.world)
+                ops.sumsq_(lu.red, self.sumsq)
+                if self.cuda:
+                    lev = torch.cuda.Event()
+                    lev.record(stream)
+                    self.local_grad_events[lu._grad_slot] = lev
+                lu.bind_grads(None)
+            elif u.local is not None:
                 lu = u.local
                 ops.adamw_flat_(lu.master, lu.exp_avg, lu.exp_avg_sq, lu.grad, lu.shard,
                                 grad_scale=1.0 / self.world, **self._adam_kwargs())
@@ -421,6 +436,55 @@ class FSDPEngine:
                 self.grad_pool_events[u._grad_slot] = ev
                 u.update_event = ev
         u.bind_grads(None)
+
+    # ------------------------------------------------------------------ gradient clipping (two phases)
+    def _reduce_only(self, u: ParamUnit, g: Tensor) -> None:
+        """Phase 1 of a clipped step: reduce this unit's gradient into its persistent shard-sized
+        buffer and add its squared norm to the running total; the update waits for the global norm."""
+        if u.red is None:
+            dt = self.param_dtype if self.world == 1 else torch.float32
+            u.red = torch.empty(u.shard_numel, dtype=dt, device=self.device)
+        if self.world == 1:
+            u.red.copy_(g[: u.shard_numel])
+            ops.sumsq_(u.red, self.sumsq)
+        elif self.comm is not None:
+            self.comm.reduce_scatter_only(u, g, u.red, self.sumsq)
+        else:
+            if g.device.type == "cpu" or dist.get_backend(self.group) == "gloo":
+                tmp = g.float()
+                dist.all_reduce(tmp, group=self.group)
+                lo, hi = u.shard_range()
+                u.red.copy_(tmp[lo:hi]).div_(self.world)
+            else:
+                gs = torch.empty(u.shard_numel, dtype=g.dtype, device=g.device)
+                dist.reduce_scatter_tensor(gs, g, op=dist.ReduceOp.AVG, group=self.group)
+                u.red.copy_(gs)
+            ops.sumsq_(u.red, self.sumsq)
+
+    def _clipped_update(self) -> None:
+        """Phase 2: global norm -> clip coefficient on the device -> AdamW on every shard."""
+        stream = self.opt_stream if self.world == 1 else self.comm_stream
+        if self.cuda:
+            stream.wait_stream(torch.cuda.current_stream())
+            ctx = torch.cuda.stream(stream)
+        else:
+            import contextlib
+            ctx = contextlib.nullcontext()
+        with ctx:
+            if self.world > 1:
+                dist.all_reduce(self.sumsq, group=self.group)
+            ops.clip_coef_(self.sumsq, float(self.max_grad_norm), self.clip_coef, self.grad_norm)
+            kw = self._adam_kwargs()
+            for u in self.units:
+                for t in (u, u.local):
+                    if t is None or t.red is None:
+                        continue
+                    ops.adamw_flat_(t.master, t.exp_avg, t.exp_avg_sq, t.red, t.shard, clip_coef=self.clip_coef, **kw)
+                    if self.cuda:
+                        ev = torch.cuda.Event()
+                        ev.record(stream)
+                        t.update_event = ev
+            self.sumsq.zero_()
 
     # ------------------------------------------------------------------ public API
     def forward_backward(self, tokens: Tensor, targets: Tensor) -> Tensor:
@@ -439,6 +503,8 @@ class FSDPEngine:
             x = _UnitFn.apply(self, 1 + i, layer, self.checkpoint, 1, x, *extra)
         loss = _UnitFn.apply(self, len(self.units) - 1, lambda h, t: m.head(h, t), False, 1, x, targets)
         loss.backward()
+        if self.max_grad_norm is not None:
+            self._clipped_update()
         return loss.detach()
 
     def step(self, tokens: Tensor, targets: Tensor) -> Tensor:

@@ -174,6 +174,22 @@ class SymmComm:
         _native.check(code, "tpb_symm_rs_adamw")
         self.grad_slot_last[u._grad_slot] = (u.index, ep)
 
+    def reduce_scatter_only(self, u, g: torch.Tensor, red_out: torch.Tensor, sumsq: torch.Tensor) -> None:
+        """Reduce-scatter (mean) of the bf16 gradient into ``red_out`` (fp32 shard) and add its squared
+        norm to ``sumsq``: phase 1 of a clipped step."""
+        self.epoch_reduce[u.index] += 1
+        ep = self.epoch_reduce[u.index]
+        lo, hi = u.shard_range()
+        code = self.arena.raw.tpb_symm_rs_adamw(
+            self.arena.offset_of(g), lo, hi - lo, None, None, None, None, NO_OFFSET, red_out.data_ptr(),
+            sumsq.data_ptr(), 1, 0.0, 0.9, 0.999, 1e-8, 0.0, 1, 1.0 / self.world, None, self.arena.pad_off,
+            self.slot_ready[u.index], self.slot_done[u.index], ep,
+            self.arena.counter[u.index % 64:].data_ptr(), self.reduce_ctas, self.wait_s,
+            self.status.data_ptr(), stream_ptr())
+        _native.launch_count += 1
+        _native.check(code, "tpb_symm_rs_adamw")
+        self.grad_slot_last[u._grad_slot] = (u.index, ep)
+
     def before_grad_reuse(self, slot: int) -> None:
         """Order the current stream after every peer's reads of gradient buffer ``slot``."""
         last = self.grad_slot_last.get(slot)

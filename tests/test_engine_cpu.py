@@ -39,3 +39,30 @@ def test_engine_matches_autograd_single_rank():
         state = eng.gather_full_state()
         for n, p in ref.named_parameters():
             assert torch.allclose(state[n], p.detach(), atol=2e-5), n
+
+
+def test_engine_gradient_clipping_matches_clip_grad_norm():
+    torch.manual_seed(0)
+    cfg = LlamaConfig.tiny(num_layers=2)
+    model = Llama(cfg)
+    model.reset_parameters(0)
+    ref = copy.deepcopy(model)
+    tokens = torch.randint(0, cfg.vocab_size, (2, 24))
+    targets = torch.randint(0, cfg.vocab_size, (2, 24))
+    ocfg = AdamWConfig(lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    max_norm = 0.05  # well below the actual norm, so the clip is active
+    opt = torch.optim.AdamW(ref.parameters(), lr=ocfg.lr, betas=ocfg.betas, eps=ocfg.eps, weight_decay=ocfg.weight_decay)
+    norms = []
+    for _ in range(3):
+        opt.zero_grad()
+        ref(tokens, targets).backward()
+        norms.append(float(torch.nn.utils.clip_grad_norm_(ref.parameters(), max_norm)))
+        opt.step()
+    eng = FSDPEngine(copy.deepcopy(model), ocfg, max_grad_norm=max_norm)
+    for i in range(3):
+        eng.step(tokens, targets)
+        assert abs(float(eng.grad_norm) - norms[i]) < 1e-4 * max(1.0, norms[i]), (i, float(eng.grad_norm), norms[i])
+    assert norms[0] > max_norm
+    state = eng.gather_full_state()
+    for n, p in ref.named_parameters():
+        assert torch.allclose(state[n], p.detach(), atol=3e-5), n

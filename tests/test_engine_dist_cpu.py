@@ -50,3 +50,42 @@ def _worker(rank, world):
 
 def test_engine_two_ranks_gloo_matches_dense():
     assert all(run_ranks(_worker, 2))
+
+
+def _clip_worker(rank, world):
+    import torch.distributed as dist
+    from tensorplay_b200.models.llama import Llama, LlamaConfig
+    from tensorplay_b200.parallel import AdamWConfig, FSDPEngine
+
+    torch.manual_seed(0)
+    cfg = LlamaConfig.tiny(hidden_size=64, num_heads=4, num_kv_heads=2, head_dim=16, ffn_size=128,
+                           vocab_size=128, num_layers=2)
+    base = Llama(cfg)
+    base.reset_parameters(0)
+    g = torch.Generator().manual_seed(5)
+    toks = torch.randint(0, cfg.vocab_size, (world, 2, 16), generator=g)
+    tgts = torch.randint(0, cfg.vocab_size, (world, 2, 16), generator=g)
+    ocfg = AdamWConfig(lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    eng = FSDPEngine(copy.deepcopy(base), ocfg, comm="torch", max_grad_norm=0.05)
+    norms = []
+    for _ in range(3):
+        eng.step(toks[rank], tgts[rank])
+        norms.append(float(eng.grad_norm))
+    state = eng.gather_full_state()
+    ref = copy.deepcopy(base)
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    for i in range(3):
+        opt.zero_grad()
+        ref(toks.flatten(0, 1), tgts.flatten(0, 1)).backward()
+        n = float(torch.nn.utils.clip_grad_norm_(ref.parameters(), 0.05))
+        assert abs(n - norms[i]) < 1e-4 * max(1.0, n), (i, n, norms[i])
+        opt.step()
+    for n, p in ref.named_parameters():
+        d = (state[n] - p.detach()).abs().max().item()
+        assert d < 2e-4, (n, d)
+    dist.barrier()
+    return True
+
+
+def test_engine_two_ranks_clipped_step():
+    assert all(run_ranks(_clip_worker, 2))
