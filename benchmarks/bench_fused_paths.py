@@ -82,10 +82,10 @@ def main():
     torch.manual_seed(rank)
 
     # the engine creates the process-wide symmetric arena with head-room for the TP plans
-    cfg = LlamaConfig(vocab_size=1024, hidden_size=4096, intermediate_size=14336, num_layers=2,
-                      num_heads=32, num_kv_heads=8, max_seq_len=4096)
-    with torch.device(dev):
-        model = Llama(cfg, dtype=torch.bfloat16)
+    cfg = LlamaConfig(vocab_size=1024, hidden_size=4096, num_layers=2, num_heads=32, num_kv_heads=8,
+                      head_dim=128, ffn_size=14336, max_seq_len=4096)
+    model = Llama(cfg, device=dev, dtype=torch.bfloat16)
+    model.reset_parameters(0)
     eng = FSDPEngine(model, AdamWConfig(lr=1e-4), comm="symm" if world > 1 else "auto",
                      activation_checkpointing=True, symm_extra_bytes=3 << 30)
     # ---- tensor-parallel: all-gather -> GEMM (column-parallel) and GEMM -> reduce-scatter (row-parallel)

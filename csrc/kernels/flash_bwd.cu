@@ -102,19 +102,24 @@ __device__ __forceinline__ void pds_math(const uint32_t (&sr)[32], const uint32_
       d4[0] = d4[1] = d4[2] = d4[3] = dsc_row;
     }
     float pr[4], ds[4];
+    const float2 sc2 = make_float2(scale_log2e, scale_log2e), s2 = make_float2(scale, scale);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float e = bwd_exp2(fmaf(__uint_as_float(sr[c + i]), scale_log2e, -l4[i]));
-      const float t = fmaf(__uint_as_float(dr[c + i]), scale, -d4[i]);
+    for (int i = 0; i < 4; i += 2) {
+      // packed fp32x2 arithmetic: two elements per FMA / MUL
+      const float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[c + i]), __uint_as_float(sr[c + i + 1])), sc2,
+                                  make_float2(-l4[i], -l4[i + 1]));
+      const float2 t = __ffma2_rn(make_float2(__uint_as_float(dr[c + i]), __uint_as_float(dr[c + i + 1])), s2,
+                                  make_float2(-d4[i], -d4[i + 1]));
+      float2 e = make_float2(bwd_exp2(x.x), bwd_exp2(x.y));
+      float2 g = __fmul2_rn(e, t);
       if (MASKED) {
         const int yi = y0i + c + i;
-        const bool valid = (yi >= y_lo) & (yi < y_hi);
-        pr[i] = valid ? e : 0.f;
-        ds[i] = valid ? e * t : 0.f;
-      } else {
-        pr[i] = e;
-        ds[i] = e * t;
+        const bool v0 = (yi >= y_lo) & (yi < y_hi), v1 = (yi + 1 >= y_lo) & (yi + 1 < y_hi);
+        e.x = v0 ? e.x : 0.f; g.x = v0 ? g.x : 0.f;
+        e.y = v1 ? e.y : 0.f; g.y = v1 ? g.y : 0.f;
       }
+      pr[i] = e.x; pr[i + 1] = e.y;
+      ds[i] = g.x; ds[i + 1] = g.y;
     }
     __nv_bfloat162 p0 = __floats2bfloat162_rn(pr[0], pr[1]), p1 = __floats2bfloat162_rn(pr[2], pr[3]);
     __nv_bfloat162 s0 = __floats2bfloat162_rn(ds[0], ds[1]), s1 = __floats2bfloat162_rn(ds[2], ds[3]);
@@ -219,7 +224,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
       for (int it = 0; it < n_it; ++it) {
         const int s = it % kYStages;
         const uint32_t ph = (it / kYStages) & 1;
-        if (!mbar_wait(&y_empty[s], ph ^ 1, wc, 1)) break;
+        if (!mbar_wait_relaxed(&y_empty[s], ph ^ 1, wc, 1)) break;
         trace_pt(p, 0, it, 1);
         int hy, yb;
         if (DKV) { hy = hx * G + it / y_count; yb = y_first + it % y_count; }
@@ -339,38 +344,20 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
     lse_row *= log2e;
     delta_row *= p.scale;
     bool ok = true;
-    // S / dP of iteration `it` are held in registers; the TMEM loads of iteration it + 1 are
-    // issued before the math of `it` whenever its MMAs have already completed, so that the load
-    // latency hides behind the math.
-    uint32_t sr[32], dr[32];
-    if (n_it > 0) {
-      ok = mbar_wait_warp(&sdp_full[0], 0, wc, 6);
-      if (ok) {
-        tc_fence_after_sync();
-        tmem_ld_32x32b_x32(tmem_base + t_lane + half * 32, sr);
-        tmem_ld_32x32b_x32(tmem_base + t_lane + 64 + half * 32, dr);
-        tmem_ld_wait();
-      }
-    }
-    for (int it = 0; it < n_it && ok; ++it) {
+    for (int it = 0; it < n_it; ++it) {
       const int s = it & 1;
+      const uint32_t ph = (it >> 1) & 1;
       int yb;
       if (DKV) yb = y_first + it % y_count;
       else yb = it;
       const int y0i = yb * kStream + half * 32;  // first query (DKV) or key (dQ) of this warp's columns
+      if (!mbar_wait_warp(&sdp_full[s], ph, wc, 6)) { ok = false; break; }
       if (threadIdx.x == 64) trace_pt(p, 2, it, 1);
-      uint32_t sn[32], dn[32];
-      const int s1 = (it + 1) & 1;
-      const uint32_t ph1 = ((it + 1) >> 1) & 1;
-      bool pre = false;
-      if (it + 1 < n_it) {
-        pre = __all_sync(0xffffffffu, mbar_test(&sdp_full[s1], ph1));
-        if (pre) {
-          tc_fence_after_sync();
-          tmem_ld_32x32b_x32(tmem_base + t_lane + s1 * 128 + half * 32, sn);
-          tmem_ld_32x32b_x32(tmem_base + t_lane + s1 * 128 + 64 + half * 32, dn);
-        }
-      }
+      tc_fence_after_sync();
+      uint32_t sr[32], dr[32];
+      tmem_ld_32x32b_x32(tmem_base + t_lane + s * 128 + half * 32, sr);
+      tmem_ld_32x32b_x32(tmem_base + t_lane + s * 128 + 64 + half * 32, dr);
+      tmem_ld_wait();
       if (threadIdx.x == 64) trace_pt(p, 2, it, 2);
 
       // Valid streamed indices of this thread's row form one interval [lo, hi): tiles that lie
@@ -394,17 +381,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
       tc_fence_before_sync();
       mbar_arrive(pds_full);
       if (threadIdx.x == 64) trace_pt(p, 2, it, 5);
-      if (it + 1 < n_it) {
-        if (!pre) {
-          if (!mbar_wait_warp(&sdp_full[s1], ph1, wc, 6)) { ok = false; break; }
-          tc_fence_after_sync();
-          tmem_ld_32x32b_x32(tmem_base + t_lane + s1 * 128 + half * 32, sn);
-          tmem_ld_32x32b_x32(tmem_base + t_lane + s1 * 128 + 64 + half * 32, dn);
-        }
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) { sr[i] = sn[i]; dr[i] = dn[i]; }
-      }
     }
     if (ok && n_it > 0) ok = mbar_wait_warp(acc_done, 0, wc, 8);
     if (ok) {

@@ -48,40 +48,52 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // Maximum of one S row (raw scores); keys beyond `lim` are excluded in the masked variant.
 template <bool MASKED>
 __device__ __forceinline__ float row_max(const uint32_t (&sr)[128], int k0, int lim) {
-  float mx = kNegBig;
+  float m0 = kNegBig, m1 = kNegBig;  // two chains for instruction-level parallelism
 #pragma unroll
-  for (int i = 0; i < 128; i += 2) {
+  for (int i = 0; i < 128; i += 4) {
     float a = __uint_as_float(sr[i]), b = __uint_as_float(sr[i + 1]);
+    float c = __uint_as_float(sr[i + 2]), d = __uint_as_float(sr[i + 3]);
     if (MASKED) {
       a = (k0 + i <= lim) ? a : kNegBig;
       b = (k0 + i + 1 <= lim) ? b : kNegBig;
+      c = (k0 + i + 2 <= lim) ? c : kNegBig;
+      d = (k0 + i + 3 <= lim) ? d : kNegBig;
     }
-    mx = fmaxf(mx, fmaxf(a, b));
+    m0 = fmaxf(m0, fmaxf(a, b));
+    m1 = fmaxf(m1, fmaxf(c, d));
   }
-  return mx;
+  return fmaxf(m0, m1);
 }
 
 // sr[i / 2] <- bf16 pair exp2(S[i] * scale - m), exp2(S[i+1] * scale - m) in place; returns the
-// sum of the rounded values.
+// row sum. Packed fp32x2 FMA / ADD and a bf16x2 pre-add of neighbouring pairs keep the count at
+// about three instructions per element (the pre-add rounds the sum of two values <= 2 to bf16:
+// a relative error of 2^-9 on a 64th of the row sum).
 template <bool MASKED>
 __device__ __forceinline__ float row_exp(uint32_t (&sr)[128], int k0, int lim, float scale_log2e, float m) {
-  float s0 = 0.f, s1 = 0.f;
+  const float2 sc = make_float2(scale_log2e, scale_log2e);
+  const float2 nm = make_float2(-m, -m);
+  float2 acc = make_float2(0.f, 0.f);
 #pragma unroll
-  for (int i = 0; i < 128; i += 2) {
-    float x0 = fmaf(__uint_as_float(sr[i]), scale_log2e, -m);
-    float x1 = fmaf(__uint_as_float(sr[i + 1]), scale_log2e, -m);
-    if (MASKED) {
-      x0 = (k0 + i <= lim) ? x0 : kNegBig;
-      x1 = (k0 + i + 1 <= lim) ? x1 : kNegBig;
+  for (int i = 0; i < 128; i += 4) {
+    uint32_t e[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[i + 2 * h]), __uint_as_float(sr[i + 2 * h + 1])), sc, nm);
+      if (MASKED) {
+        x.x = (k0 + i + 2 * h <= lim) ? x.x : kNegBig;
+        x.y = (k0 + i + 2 * h + 1 <= lim) ? x.y : kNegBig;
+      }
+      __nv_bfloat162 d = __floats2bfloat162_rn(x.x, x.y);
+      asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(e[h]) : "r"(*reinterpret_cast<uint32_t*>(&d)));
     }
-    __nv_bfloat162 d = __floats2bfloat162_rn(x0, x1);
-    uint32_t e;
-    asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(e) : "r"(*reinterpret_cast<uint32_t*>(&d)));
-    s0 += __uint_as_float(e << 16);
-    s1 += __uint_as_float(e & 0xffff0000u);
-    sr[i / 2] = e;
+    uint32_t pair;
+    asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(pair) : "r"(e[0]), "r"(e[1]));
+    acc = __fadd2_rn(acc, make_float2(__uint_as_float(pair << 16), __uint_as_float(pair & 0xffff0000u)));
+    sr[i / 2] = e[0];
+    sr[i / 2 + 1] = e[1];
   }
-  return s0 + s1;
+  return acc.x + acc.y;
 }
 
 template <int D>
@@ -180,7 +192,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int j = t >> 1;
         const int slot = t % R;
         const uint32_t ph = (t / R) & 1;
-        if (!mbar_wait(&kv_empty[slot], ph ^ 1, wc, 1)) break;
+        if (!mbar_wait_relaxed(&kv_empty[slot], ph ^ 1, wc, 1)) break;
         mbar_arrive_expect_tx(&kv_full[slot], L::kKBytes);
         const CUtensorMap* tm = (t & 1) ? &tmV : &tmK;
 #pragma unroll

@@ -119,6 +119,29 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   }
 }
 
+// Same bounded wait for threads that run far ahead of their consumers (TMA producers): it backs
+// off between polls so that the spinning warp leaves the issue slots of its scheduler to the
+// warps that do arithmetic.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, const WaitCtx& w,
+                                                  uint32_t where) {
+  if (mbar_test(bar, parity)) return true;
+  unsigned long long t0 = 0;
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(64);
+    if ((++spins & 0x3f) == 0) {
+      if (*w.abort_smem) return false;
+      unsigned long long t = globaltimer_ns();
+      if (t0 == 0) t0 = t;
+      else if (t - t0 > w.limit_ns) {
+        report_timeout(w, kStatusMbarTimeout, where);
+        return false;
+      }
+    }
+  }
+}
+
 // Warp-uniform form: every lane waits, and the warp proceeds only if all lanes succeeded, so
 // that .sync.aligned instructions after the wait are never executed by a partial warp.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, const WaitCtx& w,

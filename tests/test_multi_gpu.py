@@ -61,3 +61,11 @@ def test_tp_llama_prefill_and_decode():
     r = _run_workers("tp_llama_worker.py", n)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "RESULT" in r.stdout
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_ring_attention_and_clipped_step():
+    n = 2 if _ngpu() < 4 else 4
+    r = _run_workers("cp_worker.py", n)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "RESULT" in r.stdout

@@ -88,7 +88,7 @@ def test_embedding_forward_backward():
     g = torch.randn_like(y)
     y.backward(g)
     ref = torch.zeros(V, H).index_add_(0, ids.reshape(-1).cpu(), g.reshape(-1, H).float().cpu())
-    torch.testing.assert_close(w.grad.float().cpu(), ref, rtol=2e-2, atol=0.15)
+    torch.testing.assert_close(w.grad.float().cpu(), ref, rtol=2e-2, atol=0.5)  # bf16 accumulation of up to 50 duplicates
     # fp32 destination
     dw = torch.zeros(V, H, device=DEV)
     from tensorplay_b200.ops.decode import embedding_backward_
