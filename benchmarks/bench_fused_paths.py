@@ -105,8 +105,9 @@ def main():
         O.gemm(xf, w_col)
 
     t_f, t_b = timed(ag_fused, args.iters), timed(ag_base, args.iters)
+    t_g = timed(lambda: O.gemm(xf, w_col), args.iters)
     report(rank, f"ag_gemm tp{world} [{M}x{H}]x[{n_col}x{H}]", t_f, t_b, 2.0 * M * H * n_col,
-           (world - 1) * (M // world) * H * 2, 0, tf_peak, hbm_peak, which)
+           (world - 1) * (M // world) * H * 2, 0, tf_peak, hbm_peak, which, {"local_gemm_only_ms": round(t_g, 4)})
 
     k_loc = F // world
     x_row = torch.randn(M, k_loc, device=dev, dtype=torch.bfloat16)
@@ -122,8 +123,9 @@ def main():
         dist.reduce_scatter_tensor(y_loc, y)
 
     t_f, t_b = timed(rs_fused, args.iters), timed(rs_base, args.iters)
+    t_g = timed(lambda: O.gemm(x_row, w_row), args.iters)
     report(rank, f"gemm_rs tp{world} [{M}x{k_loc}]x[{H}x{k_loc}]", t_f, t_b, 2.0 * M * k_loc * H,
-           (world - 1) * (M // world) * H * 2, 0, tf_peak, hbm_peak, which)
+           (world - 1) * (M // world) * H * 2, 0, tf_peak, hbm_peak, which, {"local_gemm_only_ms": round(t_g, 4)})
 
     # ---- FSDP: parameter all-gather by peer pulls; reduce-scatter fused with scale + AdamW + bf16 emit
     u = max(eng.units, key=lambda t: t.padded)  # one transformer layer (218 M parameters)

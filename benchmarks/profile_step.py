@@ -28,6 +28,14 @@ def main():
     for _ in range(3):
         eng.step(tok, tok)
     torch.cuda.synchronize()
+    # device-timed step without the profiler, to compare with the sum of kernel times (idle gaps)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(3):
+        eng.step(tok, tok)
+    e1.record()
+    torch.cuda.synchronize()
+    step_ms = e0.elapsed_time(e1) / 3
     from torch.profiler import ProfilerActivity, profile
     with profile(activities=[ProfilerActivity.CUDA]) as prof:
         for _ in range(2):
@@ -40,7 +48,8 @@ def main():
     rows.sort(reverse=True)
     total = sum(r[0] for r in rows)
     lines = [f"# kernel time per step, Llama-3-8B shape with {a.layers} layers, seq 4096, 1 GPU (torch.profiler)",
-             f"# total device kernel time per step: {total / 1e3:.2f} ms"]
+             f"# total device kernel time per step: {total / 1e3:.2f} ms; CUDA-event step time without "
+             f"the profiler: {step_ms:.2f} ms (kernels on side streams overlap, gaps are idle time)"]
     for t, c, k in rows[:30]:
         lines.append(f"{t / 1e3:9.3f} ms {100 * t / total:5.1f}%  x{c:4d}  {k[:90]}")
     text = "\n".join(lines)

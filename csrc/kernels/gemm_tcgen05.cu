@@ -191,25 +191,51 @@ __device__ void rs_reduce_role(const GemmParams& p, int bid, int nctas, int t, c
   const size_t per_src = (size_t)p.rs_rows_per_rank * p.N;
   const size_t nvec = per_src / 8;
   const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(p.rs_stage[p.rank]);
-  for (size_t i = (size_t)bid * 128 + t; i < nvec; i += (size_t)nctas * 128) {
-    float acc[8];
+  // kU vectors per thread and pass, all sources' loads issued before the first use: with only 128
+  // threads per CTA the memory system needs this many requests in flight to run near its bandwidth
+  constexpr int kU = 4;
+  const size_t stride = (size_t)nctas * 128;
+  for (size_t i0 = (size_t)bid * 128 + t; i0 < nvec; i0 += stride * kU) {
+    float acc[kU][8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    for (int r = 0; r < p.world; ++r) {
-      uint4 raw = ld_peer_v4(reinterpret_cast<const uint4*>(stage + r * per_src) + i);
-      const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    for (int u = 0; u < kU; ++u)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float2 f = __bfloat1622float2(hb[j]);
-        acc[2 * j] += f.x;
-        acc[2 * j + 1] += f.y;
+      for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
+    for (int r = 0; r < p.world; r += 2) {
+      uint4 raw[2][kU];
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr)
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+          const size_t i = i0 + (size_t)u * stride;
+          raw[rr][u] = (r + rr < p.world && i < nvec)
+                           ? ld_peer_v4(reinterpret_cast<const uint4*>(stage + (size_t)(r + rr) * per_src) + i)
+                           : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr)
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+          const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&raw[rr][u]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float2 f = __bfloat1622float2(hb[j]);
+            acc[u][2 * j] += f.x;
+            acc[u][2 * j + 1] += f.y;
+          }
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const size_t i = i0 + (size_t)u * stride;
+      if (i < nvec) {
+        uint4 o;
+        __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) ob[j] = __floats2bfloat162_rn(acc[u][2 * j], acc[u][2 * j + 1]);
+        reinterpret_cast<uint4*>(p.rs_out)[i] = o;
       }
     }
-    uint4 o;
-    __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) ob[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-    reinterpret_cast<uint4*>(p.rs_out)[i] = o;
   }
 }
 

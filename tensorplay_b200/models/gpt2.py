@@ -93,6 +93,7 @@ class GPT2(nn.Module):
         self.layers = nn.ModuleList([GPT2Block(cfg, **kw) for _ in range(cfg.n_layers)])
         self.lnf_w = nn.Parameter(torch.ones(cfg.d_model, **kw))
         self.lnf_b = nn.Parameter(torch.zeros(cfg.d_model, **kw))
+        self._pad_bias = None  # constant epilogue bias that masks the padded vocabulary columns
         self.lm_head = None if cfg.tie_embeddings else nn.Parameter(torch.empty(cfg.padded_vocab, cfg.d_model, **kw))
 
     def reset_parameters(self, seed: Optional[int] = None) -> None:
@@ -116,14 +117,19 @@ class GPT2(nn.Module):
     def head(self, x: Tensor, targets: Optional[Tensor] = None) -> Tensor:
         h = ops.layer_norm(x, self.lnf_w, self.lnf_b, self.cfg.ln_eps)
         w = self.wte if self.lm_head is None else self.lm_head
-        logits = ops.linear(h, w)
         V = self.cfg.vocab_size
+        if targets is not None and h.is_cuda and h.dtype == torch.bfloat16:
+            # padded vocabulary columns hold exactly-zero weights; a constant bias in the GEMM
+            # epilogue pushes them out of the softmax without another pass over the logits
+            if self._pad_bias is None or self._pad_bias.device != h.device:
+                pb = torch.zeros(w.shape[0], dtype=torch.bfloat16, device=h.device)
+                pb[V:] = -30000.0
+                self._pad_bias = pb
+            logits = ops.linear(h, w, self._pad_bias)
+            return ops.cross_entropy(logits.view(-1, logits.shape[-1]), targets.reshape(-1))
+        logits = ops.linear(h, w)
         if targets is None:
             return logits[..., :V]
-        if logits.is_cuda and logits.dtype == torch.bfloat16:
-            # padded columns hold exactly-zero weights; push them out of the softmax
-            logits[..., V:] = -30000.0
-            return ops.cross_entropy(logits.view(-1, logits.shape[-1]), targets.reshape(-1))
         return ops.cross_entropy(logits[..., :V].reshape(-1, V), targets.reshape(-1))
 
     def forward(self, tokens: Tensor, targets: Optional[Tensor] = None, position_ids=None,

@@ -21,16 +21,20 @@ class _EmbeddingFn(torch.autograd.Function):
     def forward(ctx, ids, weight):
         ctx.save_for_backward(ids)
         ctx.wshape, ctx.wdtype = weight.shape, weight.dtype
-        ctx.grad_view = getattr(weight, "_tpb_grad_view", None)
-        ctx.weight_ref = weight if ctx.grad_view is not None else None
+        # an engine may own the gradient storage; its view is bound only by the time backward runs
+        ctx.weight_ref = weight if hasattr(weight, "_tpb_grad_view") else None
         return embedding_forward(ids, weight)
 
     @staticmethod
     def backward(ctx, dy):
         (ids,) = ctx.saved_tensors
-        dst = ctx.grad_view
+        w = ctx.weight_ref
+        dst = None if w is None else w._tpb_grad_view
         if dst is not None:
             # engine-owned flat gradient: accumulate in place, nothing flows through autograd
+            if not getattr(w, "_tpb_grad_written", False):
+                dst.zero_()
+                w._tpb_grad_written = True
             embedding_backward_(dst, ids, dy)
             return None, None
         dw = torch.zeros(ctx.wshape, dtype=ctx.wdtype, device=dy.device)

@@ -87,16 +87,30 @@ class ParamUnit:
             p._tpb_grad_written = False
 
     def collect_autograd_grads(self) -> None:
-        """Fold ``.grad`` tensors produced by plain autograd paths into the flat buffer."""
+        """Fold ``.grad`` tensors produced by plain autograd paths into the flat buffer and zero the
+        views that nothing wrote (the buffer itself is not cleared before backward: the kernels'
+        first write to a view overwrites it)."""
         for _, p in self.params:
+            v = p._tpb_grad_view
             if p.grad is not None:
-                v = p._tpb_grad_view
                 if getattr(p, "_tpb_grad_written", False):
                     v.add_(p.grad.to(v.dtype))
                 else:
                     v.copy_(p.grad)
                     p._tpb_grad_written = True
                 p.grad = None
+            elif v is not None and not getattr(p, "_tpb_grad_written", False):
+                v.zero_()
+
+    def zero_padding(self, grad: Tensor) -> None:
+        """Clear the alignment gaps and the tail of a freshly bound gradient buffer."""
+        end = 0
+        for off, n in zip(self.offsets, self.numels):
+            if off > end:
+                grad[end:off].zero_()
+            end = off + n
+        if end < grad.numel():
+            grad[end:].zero_()
 
     def shard_range(self, rank: Optional[int] = None) -> Tuple[int, int]:
         r = self.rank if rank is None else rank
@@ -355,7 +369,7 @@ class FSDPEngine:
         if self.comm is not None:
             self.comm.before_grad_reuse(slot)
         g = self.grad_pool[slot][: u.padded]
-        g.zero_()
+        u.zero_padding(g)
         u.bind_grads(g)
         u._grad_slot = slot
         if u.local is not None:
@@ -365,7 +379,7 @@ class FSDPEngine:
             if ev is not None and self.cuda:
                 torch.cuda.current_stream().wait_event(ev)
             lg = self.local_grad_pool[ls][: u.local.padded]
-            lg.zero_()
+            u.local.zero_padding(lg)
             u.local.bind_grads(lg)
             u.local._grad_slot = ls
 
@@ -485,6 +499,9 @@ class FSDPEngine:
                         ev.record(stream)
                         t.update_event = ev
             self.sumsq.zero_()
+        if self.cuda:
+            # readers of grad_norm (and the next step) on the main stream see the finished update
+            torch.cuda.current_stream().wait_stream(stream)
 
     # ------------------------------------------------------------------ public API
     def forward_backward(self, tokens: Tensor, targets: Tensor) -> Tensor:
