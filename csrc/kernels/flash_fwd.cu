@@ -35,6 +35,7 @@ struct AttnFwdParams {
   long long o_tok_stride, o_head_stride, o_batch_stride;
   float* lse;  // [B, Hq, lse_stride]
   int lse_stride;
+  const int* kv_len;  // optional device word: number of valid keys (<= Tk), for graph-replayed decode
   uint32_t* status;
   unsigned long long wait_ns;
 };
@@ -136,12 +137,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int b = blockIdx.z;
   const int hk = h / (p.Hq / p.Hkv);
   const int q0 = qb * (kTilesQ * kBlockQ);
+  const int Tk = p.kv_len ? min(p.Tk, *p.kv_len) : p.Tk;
   // KV blocks needed by each of the two query tiles
   int nkv_t[kTilesQ];
   int nkv = 0;
 #pragma unroll
   for (int g = 0; g < kTilesQ; ++g) {
-    int n = (p.Tk + kBlockKV - 1) / kBlockKV;
+    int n = (Tk + kBlockKV - 1) / kBlockKV;
     if (p.causal) {
       const int last_key = q0 + g * kBlockQ + kBlockQ - 1 + p.kv_offset;
       n = last_key < 0 ? 0 : min(n, last_key / kBlockKV + 1);
@@ -278,7 +280,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t t_s = tmem_base + ((uint32_t)(qd * 32) << 16) + g * 128;
     const uint32_t t_o = tmem_base + ((uint32_t)(qd * 32) << 16) + 256 + g * 128;
     const int my_nkv = nkv_t[g];
-    const int lim = p.causal ? min(qi + p.kv_offset, p.Tk - 1) : (p.Tk - 1);  // last valid key
+    const int lim = p.causal ? min(qi + p.kv_offset, Tk - 1) : (Tk - 1);  // last valid key
     float m = kNegBig, l = 0.f;
     bool ok = true;
     for (int j = 0; j < my_nkv; ++j) {
@@ -286,7 +288,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_after_sync();
       const int k0 = j * kBlockKV;
       const bool need_mask = (p.causal && (k0 + kBlockKV - 1 > q0 + g * kBlockQ + p.kv_offset)) ||
-                             (k0 + kBlockKV > p.Tk);
+                             (k0 + kBlockKV > Tk);
       // the whole S row (128 fp32) in one TMEM round trip
       uint32_t sr[128];
 #pragma unroll
@@ -459,7 +461,7 @@ extern "C" int tpb_flash_fwd(const void* q, const void* k, const void* v, void* 
                              long long k_head, long long k_batch, long long v_tok,
                              long long v_head, long long v_batch, long long o_tok,
                              long long o_head, long long o_batch, int lse_stride, int causal,
-                             float scale, uint32_t* status, void* stream) {
+                             float scale, uint32_t* status, void* stream, const int* kv_len) {
   if (B <= 0 || Tq <= 0 || Hq <= 0) return 0;
   if ((D != 64 && D != 128) || Hkv <= 0 || Hq % Hkv || Tk <= 0) return -2;
   if ((q_tok | q_head | q_batch | k_tok | k_head | k_batch | v_tok | v_head | v_batch | o_tok |
@@ -478,7 +480,7 @@ extern "C" int tpb_flash_fwd(const void* q, const void* k, const void* v, void* 
   p.kv_offset = Tk - Tq;
   p.scale_log2e = scale * 1.4426950408889634f;
   p.O = (__nv_bfloat16*)o; p.o_tok_stride = o_tok; p.o_head_stride = o_head;
-  p.o_batch_stride = o_batch; p.lse = lse; p.lse_stride = lse_stride > 0 ? lse_stride : Tq; p.status = status; p.wait_ns = kDefaultWaitNs;
+  p.o_batch_stride = o_batch; p.lse = lse; p.lse_stride = lse_stride > 0 ? lse_stride : Tq; p.status = status; p.wait_ns = kDefaultWaitNs; p.kv_len = kv_len;
   if (D == 128) return launch_fwd<128>(tq, tk, tv, p, (cudaStream_t)stream);
   return launch_fwd<64>(tq, tk, tv, p, (cudaStream_t)stream);
 }

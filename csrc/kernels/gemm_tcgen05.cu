@@ -76,6 +76,11 @@ struct GemmParams {
   uint32_t* pad_peer[16];
   int ready_slot, done_slot;
   uint32_t epoch;
+  // When set, the epoch of this launch is *epoch_dev + 1, read on the device: the launch then
+  // carries no host-side counter and can be replayed from a CUDA graph (a one-thread kernel bumps
+  // the word after the launch).
+  const uint32_t* epoch_dev;
+  uint32_t rs_per_call;     // arrivals per launch and source (rs_expect = epoch * rs_per_call)
   int tile_m_shift;         // rotate M tiles so that locally available rows are computed first
   // ---- fused reduce-scatter epilogue (rs_mode = 1): row block d of the product belongs to
   // rank d; tiles are stored (bf16) into rank d's staging slice [rank][rows_per_rank, N] and a
@@ -108,12 +113,19 @@ __device__ __forceinline__ uint4 ld_peer_v4(const void* ptr) {
   return v;
 }
 
+__device__ __forceinline__ uint32_t fused_epoch(const GemmParams& p) {
+  return p.epoch_dev ? *reinterpret_cast<const volatile uint32_t*>(p.epoch_dev) + 1u : p.epoch;
+}
+__device__ __forceinline__ uint32_t fused_rs_expect(const GemmParams& p) {
+  return p.epoch_dev ? fused_epoch(p) * p.rs_per_call : p.rs_expect;
+}
+
 // Copy CTAs of the fused all-gather: chunk c of peer (rank + 1 + c / chunks_per_rank).
 __device__ void ag_copy_role(const GemmParams& p) {
   // publish "my shard is valid" to every peer, once
   if (blockIdx.x == 0 && threadIdx.x < p.world) {
     __threadfence_system();
-    st_release_sys(p.pad_peer[threadIdx.x] + p.ready_slot + p.rank, p.epoch);
+    st_release_sys(p.pad_peer[threadIdx.x] + p.ready_slot + p.rank, fused_epoch(p));
   }
   const int cpr = (int)((p.ag_shard_bytes + p.ag_chunk_bytes - 1) / p.ag_chunk_bytes);
   const int total = cpr * (p.world - 1);
@@ -122,7 +134,7 @@ __device__ void ag_copy_role(const GemmParams& p) {
     const int pr = c / cpr, ci = c % cpr;
     const int r = (p.rank + 1 + pr) % p.world;
     if (threadIdx.x == 0)
-      ok_sh = flag_wait_ge(p.pad_local + p.ready_slot + r, p.epoch, true, p.status, p.wait_ns, 11) ? 1 : 0;
+      ok_sh = flag_wait_ge(p.pad_local + p.ready_slot + r, fused_epoch(p), true, p.status, p.wait_ns, 11) ? 1 : 0;
     __syncthreads();
     if (!ok_sh) return;
     const unsigned long long off = (unsigned long long)ci * p.ag_chunk_bytes;
@@ -144,7 +156,7 @@ __device__ void ag_copy_role(const GemmParams& p) {
     asm volatile("fence.proxy.async.global;" ::: "memory");
     __threadfence();
     __syncthreads();
-    if (threadIdx.x == 0) st_release_gpu(p.ag_flags + (size_t)r * cpr + ci, p.epoch);
+    if (threadIdx.x == 0) st_release_gpu(p.ag_flags + (size_t)r * cpr + ci, fused_epoch(p));
   }
   // the sources may overwrite their shards once every reader is done
   __syncthreads();
@@ -153,7 +165,7 @@ __device__ void ag_copy_role(const GemmParams& p) {
     unsigned prev = atomicAdd(p.ag_flags + (size_t)p.world * cpr, 1u);
     if (prev == (unsigned)p.n_copy - 1) {
       p.ag_flags[(size_t)p.world * cpr] = 0;
-      for (int r = 0; r < p.world; ++r) st_release_sys(p.pad_peer[r] + p.done_slot + p.rank, p.epoch);
+      for (int r = 0; r < p.world; ++r) st_release_sys(p.pad_peer[r] + p.done_slot + p.rank, fused_epoch(p));
     }
   }
 }
@@ -168,7 +180,7 @@ __device__ __forceinline__ bool ag_wait_rows(const GemmParams& p, int r0, int r1
     const int ci = in_shard / p.ag_rows_per_flag;
     const int next = owner * p.ag_rows_per_rank + min((ci + 1) * p.ag_rows_per_flag, p.ag_rows_per_rank);
     if (owner != p.rank && owner < p.world) {
-      if (!flag_wait_ge(p.ag_flags + (size_t)owner * cpr + ci, p.epoch, false, p.status, p.wait_ns, 12))
+      if (!flag_wait_ge(p.ag_flags + (size_t)owner * cpr + ci, fused_epoch(p), false, p.status, p.wait_ns, 12))
         return false;
       waited = true;
     }
@@ -183,7 +195,7 @@ __device__ __forceinline__ bool ag_wait_rows(const GemmParams& p, int r0, int r1
 __device__ void rs_reduce_role(const GemmParams& p, int bid, int nctas, int t, const WaitCtx& wc) {
   // wait for every source's tiles (each tile bumps the counter once per epilogue warp)
   if (t < p.world &&
-      !flag_wait_ge(p.rs_cnt[p.rank] + t, p.rs_expect, true, p.status, p.wait_ns, 13))
+      !flag_wait_ge(p.rs_cnt[p.rank] + t, fused_rs_expect(p), true, p.status, p.wait_ns, 13))
     *wc.abort_smem = 1;
   // named barrier over the 128 epilogue threads (each of the four warps gets here exactly once)
   asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -724,6 +736,7 @@ int gemm_bf16_dispatch(const void* A, const void* B, void* C, const void* bias, 
   p.wait_ns = kDefaultWaitNs;
   p.b_flags = b_flags; p.rows_per_flag = rows_per_flag > 0 ? rows_per_flag : 1;
   p.flag_want = flag_want;
+  p.epoch_dev = nullptr; p.rs_per_call = 0;
   p.n_copy = 0; p.ag_operand = 0; p.rs_mode = 0; p.tile_m_shift = 0; p.world = 1; p.rank = 0;
   p.sk_ws = g_sk_ws; p.sk_flags = g_sk_flags;
   if (fused) {
@@ -732,7 +745,7 @@ int gemm_bf16_dispatch(const void* A, const void* B, void* C, const void* bias, 
     p.ag_chunk_bytes = fused->ag_chunk_bytes; p.ag_rows_per_rank = fused->ag_rows_per_rank;
     p.ag_rows_per_flag = fused->ag_rows_per_flag; p.ag_flags = fused->ag_flags;
     p.pad_local = fused->pad_local; p.ready_slot = fused->ready_slot; p.done_slot = fused->done_slot;
-    p.epoch = fused->epoch; p.tile_m_shift = fused->tile_m_shift; p.rs_mode = fused->rs_mode;
+    p.epoch = fused->epoch; p.epoch_dev = fused->epoch_dev; p.rs_per_call = fused->rs_per_call; p.tile_m_shift = fused->tile_m_shift; p.rs_mode = fused->rs_mode;
     p.rs_rows_per_rank = fused->rs_rows_per_rank; p.rs_expect = fused->rs_expect;
     p.rs_out = fused->rs_out;
     for (int r = 0; r < 16; ++r) {
@@ -780,7 +793,7 @@ extern "C" int tpb_ag_gemm(size_t a_off, const void* B, void* C, const void* bia
                            int K, int ldb, int ldc, int b_mn, int out_f32, uint32_t* flags,
                            int rows_per_flag, size_t pad_off, int ready_slot, int done_slot,
                            uint32_t epoch, int n_copy, double wait_s, uint32_t* status,
-                           void* stream) {
+                           void* stream, const uint32_t* epoch_dev) {
   const tpb::SymmView* sv = tpb::symm_view();
   if (!sv || sv->world < 1 || M % sv->world) return -2;
   const int world = sv->world, rank = sv->rank;
@@ -801,7 +814,7 @@ extern "C" int tpb_ag_gemm(size_t a_off, const void* B, void* C, const void* bia
     f.pad_peer[r] = reinterpret_cast<uint32_t*>(sv->peer[r] + pad_off);
   }
   f.pad_local = reinterpret_cast<uint32_t*>(sv->peer[rank] + pad_off);
-  f.ready_slot = ready_slot; f.done_slot = done_slot; f.epoch = epoch;
+  f.ready_slot = ready_slot; f.done_slot = done_slot; f.epoch = epoch; f.epoch_dev = epoch_dev;
   const int tiles_m = (M + 127) / 128;
   f.tile_m_shift = (rows_per_rank % 128 == 0) ? (int)(((long long)rank * rows_per_rank / 128) % tiles_m) : 0;
   f.wait_ns = wait_s > 0 ? (unsigned long long)(wait_s * 1e9) : 0;
@@ -816,7 +829,7 @@ extern "C" int tpb_ag_gemm(size_t a_off, const void* B, void* C, const void* bia
 extern "C" int tpb_gemm_rs(const void* A, const void* B, void* out, int M, int N, int K, int lda,
                            int ldb, int a_mn, int b_mn, size_t stage_off, size_t pad_off,
                            int cnt_slot, uint32_t epoch, double wait_s, uint32_t* status,
-                           void* stream) {
+                           void* stream, const uint32_t* epoch_dev) {
   const tpb::SymmView* sv = tpb::symm_view();
   if (!sv || sv->world < 1 || M % sv->world || N % 8) return -2;
   const int world = sv->world, rank = sv->rank;
@@ -836,6 +849,7 @@ extern "C" int tpb_gemm_rs(const void* A, const void* B, void* out, int M, int N
   const int row_blocks = my1 / 32 - my0 / 32 + 1;
   const int per_call = row_blocks * ((N + block_n - 1) / block_n);
   f.rs_expect = epoch * (uint32_t)per_call;
+  f.epoch = epoch; f.epoch_dev = epoch_dev; f.rs_per_call = (uint32_t)per_call;
   f.rs_out = static_cast<__nv_bfloat16*>(out);
   const int tiles_m = (M + 127) / 128;
   f.tile_m_shift = (f.rs_rows_per_rank % 128 == 0)

@@ -255,6 +255,13 @@ __global__ void wait_slots_kernel(SyncArgs s, int slot_base, uint32_t where) {
     flag_wait_ge(s.pad_local + slot_base + threadIdx.x, s.epoch, true, s.status, s.wait_ns, where);
 }
 
+// Same wait with the target read from a device word (graph-replayable callers).
+__global__ void wait_slots_dev_kernel(SyncArgs s, int slot_base, const uint32_t* epoch_dev, uint32_t where) {
+  if (threadIdx.x < s.world)
+    flag_wait_ge(s.pad_local + slot_base + threadIdx.x, *epoch_dev, true, s.status, s.wait_ns, where);
+}
+__global__ void bump_kernel(uint32_t* ctr) { *ctr += 1u; }
+
 __global__ void barrier_kernel(SyncArgs s, int slot_base) { rendezvous(s, slot_base, 22); }
 
 // Generic peer copy: dst (local) <- src on rank r (no rendezvous; caller orders it).
@@ -409,6 +416,19 @@ extern "C" int tpb_symm_wait_slots(size_t pad_off, int slot_base, uint32_t epoch
                                    uint32_t* status, void* stream) {
   SyncArgs s = make_sync(pad_off, epoch, status, wait_s);
   wait_slots_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(s, slot_base, 23);
+  return (int)cudaGetLastError();
+}
+
+// Wait until all `world` slots reached the value stored at epoch_dev (device memory).
+extern "C" int tpb_symm_wait_slots_dev(size_t pad_off, int slot_base, const uint32_t* epoch_dev, double wait_s,
+                                       uint32_t* status, void* stream) {
+  SyncArgs s = make_sync(pad_off, 0, status, wait_s);
+  wait_slots_dev_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(s, slot_base, epoch_dev, 24);
+  return (int)cudaGetLastError();
+}
+// *ctr += 1 in stream order (advances a device-side epoch after the launch that used it).
+extern "C" int tpb_symm_bump(uint32_t* ctr, void* stream) {
+  bump_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(ctr);
   return (int)cudaGetLastError();
 }
 

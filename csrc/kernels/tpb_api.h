@@ -36,6 +36,8 @@ struct GemmFused {
   uint32_t* pad_peer[16];
   int ready_slot, done_slot;
   uint32_t epoch;
+  const uint32_t* epoch_dev;  // device-side epoch word (epoch = *epoch_dev + 1) or null
+  uint32_t rs_per_call;
   int tile_m_shift;
   int rs_mode, rs_rows_per_rank;
   char* rs_stage[16];
@@ -101,7 +103,7 @@ int tpb_flash_fwd(const void* q, const void* k, const void* v, void* o, float* l
                   long long q_batch, long long k_tok, long long k_head, long long k_batch,
                   long long v_tok, long long v_head, long long v_batch, long long o_tok,
                   long long o_head, long long o_batch, int lse_stride, int causal, float scale,
-                  uint32_t* status, void* stream);
+                  uint32_t* status, void* stream, const int* kv_len);
 int tpb_flash_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o,
                   const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int Tq,
                   int Tk, int Hq, int Hkv, int D, long long q_tok, long long q_head,

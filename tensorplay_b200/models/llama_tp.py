@@ -13,6 +13,7 @@ The reference has no TP inference runner: users apply ``parallelize_module`` to 
 """
 from __future__ import annotations
 
+import math
 from typing import Optional
 
 import torch
@@ -20,7 +21,7 @@ import torch.distributed as dist
 from torch import Tensor, nn
 
 from .. import ops
-from ..ops.attention import flash_attention
+from ..ops.attention import flash_attention, flash_fwd
 from ..parallel.tp import TPContext
 from .llama import LlamaConfig
 
@@ -76,6 +77,30 @@ class LlamaTPBlock(nn.Module):
         return x_local + tp.linear_reduce_scatter(a, self.w_down)
 
 
+    def decode(self, x_local: Tensor, B: int, cos: Tensor, sin: Tensor, pos64: Tensor, pos32: Tensor,
+               kv_len: Tensor) -> Tensor:
+        """One-token step with every position-dependent quantity read from device memory (``pos64``
+        / ``pos32``: ``[B]`` write positions, ``kv_len``: int32 scalar = position + 1), so that the
+        launch sequence is identical at every step and can be replayed from a CUDA graph."""
+        cfg, tp = self.cfg, self.tp
+        D = cfg.head_dim
+        h = ops.rms_norm(x_local, self.attn_norm, cfg.rms_eps)
+        qkv = tp.all_gather_linear(h, self.wqkv).view(B, 1, self.hq + 2 * self.hkv, D)
+        qk = ops.apply_rope(qkv[:, :, : self.hq + self.hkv], cos, sin, pos64.view(B, 1))
+        q, k, v = qk[:, :, : self.hq], qk[:, :, self.hq:], qkv[:, :, self.hq + self.hkv:]
+        # caches are token-major [B, S, hkv, D]; the append kernel takes them head-major by strides
+        ops.kv_append(self.k_cache[:B].permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), pos32)
+        ops.kv_append(self.v_cache[:B].permute(0, 2, 1, 3), v.permute(0, 2, 1, 3), pos32)
+        G = self.hq // self.hkv
+        o, _ = flash_fwd(q.reshape(B, self.hkv, G, D).transpose(1, 2), self.k_cache[:B], self.v_cache[:B],
+                         False, 1.0 / math.sqrt(D), kv_len=kv_len)
+        o = o.transpose(1, 2).reshape(B, self.hq * D)
+        x_local = x_local + tp.linear_reduce_scatter(o, self.wo)
+        h = ops.rms_norm(x_local, self.ffn_norm, cfg.rms_eps)
+        a = ops.swiglu_packed(tp.all_gather_linear(h, self.w_gate_up))
+        return x_local + tp.linear_reduce_scatter(a, self.w_down)
+
+
 class LlamaTP(nn.Module):
     def __init__(self, cfg: LlamaConfig, tp: TPContext, device=None, dtype=None):
         super().__init__()
@@ -88,6 +113,7 @@ class LlamaTP(nn.Module):
         self.final_norm = nn.Parameter(torch.ones(cfg.hidden_size, **kw))
         self.lm_head = nn.Parameter(torch.empty(self.vshard, cfg.hidden_size, **kw))  # vocabulary shard
         self._rope = None
+        self._graph = None  # captured decode step (see decode_step)
 
     def reset_parameters(self, seed: int = 0) -> None:
         dev = self.embed.device
@@ -163,7 +189,53 @@ class LlamaTP(nn.Module):
         return self.greedy_next(self.last_token_hidden(x, B, T))
 
     @torch.no_grad()
-    def decode_step(self, last_tokens: Tensor, pos: int) -> Tensor:
+    def decode_step(self, last_tokens: Tensor, pos: int, use_graph: bool = True) -> Tensor:
+        """Greedy next token for ``last_tokens [B]`` written at cache position ``pos``.
+
+        On CUDA the transformer body of the step is captured once into a CUDA graph and replayed:
+        positions and the key length live in device memory and advance inside the graph, the fused
+        collectives keep their epochs on the device, so a replay needs no host-side argument. The
+        vocabulary-parallel head (an NCCL exchange of per-shard maxima) runs eagerly after it."""
         B = last_tokens.shape[0]
-        x = self.hidden(last_tokens.view(B, 1), pos, use_cache=True)
-        return self.greedy_next(self.last_token_hidden(x, B, 1))
+        if not (use_graph and last_tokens.is_cuda and self.cfg.num_heads % self.cfg.num_kv_heads == 0):
+            x = self.hidden(last_tokens.view(B, 1), pos, use_cache=True)
+            return self.greedy_next(self.last_token_hidden(x, B, 1))
+        g = self._graph
+        if g is None or g["B"] != B:
+            # First step at this batch size: run the body eagerly (it is the real step, so every
+            # kernel is configured and every plan buffer exists), then capture it for the next ones.
+            assert B % self.tp.world == 0
+            dev = last_tokens.device
+            g = self._graph = {"B": B, "pos": pos + 1,
+                               "tok": last_tokens.view(B, 1).clone(),
+                               "pos64": torch.full((B,), pos, dtype=torch.long, device=dev),
+                               "pos32": torch.full((B,), pos, dtype=torch.int32, device=dev),
+                               "kv_len": torch.full((1,), pos + 1, dtype=torch.int32, device=dev)}
+            out = self._decode_body(g)
+            nxt = self.greedy_next(self.last_token_hidden(out, B, 1))
+            torch.cuda.synchronize(dev)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                g["out"] = self._decode_body(g)
+            g["graph"] = graph
+            return nxt
+        if g["pos"] != pos:  # (re)position: plain copies outside the graph
+            g["pos64"].fill_(pos)
+            g["pos32"].fill_(pos)
+            g["kv_len"].fill_(pos + 1)
+        g["tok"].copy_(last_tokens.view(B, 1))
+        g["graph"].replay()
+        g["pos"] = pos + 1  # the graph advanced the device-side positions itself
+        return self.greedy_next(self.last_token_hidden(g["out"], B, 1))
+
+    def _decode_body(self, g) -> Tensor:
+        B = g["B"]
+        cap = max(self.cfg.max_seq_len, self.layers[0].k_cache.shape[1])  # every cache position has a row
+        cos, sin = self.rope_tables(cap, g["tok"].device)
+        x = self._local_rows(g["tok"])
+        for l in self.layers:
+            x = l.decode(x, B, cos, sin, g["pos64"], g["pos32"], g["kv_len"])
+        g["pos64"] += 1
+        g["pos32"] += 1
+        g["kv_len"] += 1
+        return x

@@ -43,7 +43,10 @@ def attention_reference(q, k, v, causal: bool = True, scale: Optional[float] = N
     return o.permute(0, 2, 1, 3).to(q.dtype)
 
 
-def flash_fwd(q, k, v, causal: bool, scale: float):
+def flash_fwd(q, k, v, causal: bool, scale: float, kv_len: Optional[torch.Tensor] = None):
+    """Forward kernel. ``kv_len`` (int32 device scalar) limits the keys to the first ``kv_len`` of
+    ``k``/``v`` without a host-side shape change, so that a decode step over a preallocated cache
+    can be captured in a CUDA graph."""
     B, Tq, Hq, D = q.shape
     Tk, Hkv = k.shape[1], k.shape[2]
     o = torch.empty((B, Tq, Hq, D), dtype=q.dtype, device=q.device)
@@ -53,7 +56,8 @@ def flash_fwd(q, k, v, causal: bool, scale: float):
         q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), B, Tq, Tk, Hq, Hkv,
         D, q.stride(1), q.stride(2), q.stride(0), k.stride(1), k.stride(2), k.stride(0),
         v.stride(1), v.stride(2), v.stride(0), o.stride(1), o.stride(2), o.stride(0), lse.shape[2],
-        int(causal), float(scale), status_word(q.device).data_ptr(), stream_ptr())
+        int(causal), float(scale), status_word(q.device).data_ptr(), stream_ptr(),
+        None if kv_len is None else kv_len.data_ptr())
     _native.check(code, "tpb_flash_fwd")
     return o, lse
 

@@ -531,6 +531,80 @@ class FSDPEngine:
         if self.cuda:
             torch.cuda.synchronize(self.device)
 
+    # ------------------------------------------------------------------ checkpoint / resume
+    def save_checkpoint(self, directory: str) -> None:
+        """Sharded checkpoint: every rank writes its fp32 master / moment shards of every unit to
+        ``rank{r}.mega`` (one collective-free file per rank); rank 0 adds ``engine.json`` with the
+        layout. Expert-parallel (rank-local) parameters are stored whole in their owner's file."""
+        import json
+        import os
+        from ..serialization import save
+        os.makedirs(directory, exist_ok=True)
+        self.synchronize()
+        blob = {}
+        for u in self.units:
+            for tag, t in (("master", u.master), ("exp_avg", u.exp_avg), ("exp_avg_sq", u.exp_avg_sq)):
+                blob[f"{u.name}.{tag}"] = t.detach().cpu()
+            if u.local is not None:
+                for tag, t in (("master", u.local.master), ("exp_avg", u.local.exp_avg), ("exp_avg_sq", u.local.exp_avg_sq)):
+                    blob[f"{u.name}.local.{tag}"] = t.detach().cpu()
+        save(blob, os.path.join(directory, f"rank{self.rank}.mega"))
+        if self.rank == 0:
+            meta = {"world": self.world, "step": self.step_count,
+                    "units": [{"name": u.name, "numel": u.numel, "padded": u.padded,
+                               "params": [n for n, _ in u.params]} for u in self.units]}
+            with open(os.path.join(directory, "engine.json"), "w") as f:
+                json.dump(meta, f)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+
+    def load_checkpoint(self, directory: str) -> None:
+        """Resume from :meth:`save_checkpoint`. The saving job may have had a different number of
+        ranks: a unit's state is one flat vector cut into equal shards, so this rank's slice is
+        assembled from the overlapping slices of the old shards."""
+        import json
+        import os
+        from ..serialization import load
+        with open(os.path.join(directory, "engine.json")) as f:
+            meta = json.load(f)
+        old_world = int(meta["world"])
+        by_name = {m["name"]: m for m in meta["units"]}
+        files = {}
+
+        def old_file(r):
+            if r not in files:
+                files[r] = load(os.path.join(directory, f"rank{r}.mega"))
+            return files[r]
+
+        for u in self.units:
+            m = by_name[u.name]
+            if m["numel"] != u.numel or m["params"] != [n for n, _ in u.params]:
+                raise ValueError(f"checkpoint unit {u.name} does not match the model")
+            old_shard = int(m["padded"]) // old_world
+            lo, hi = u.shard_range()
+            for tag, dst in (("master", u.master), ("exp_avg", u.exp_avg), ("exp_avg_sq", u.exp_avg_sq)):
+                out = torch.zeros(hi - lo, dtype=torch.float32)
+                pos = lo
+                while pos < min(hi, u.numel):
+                    r = pos // old_shard
+                    src = old_file(r)[f"{u.name}.{tag}"]
+                    a = pos - r * old_shard
+                    n = min(old_shard - a, min(hi, u.numel) - pos)
+                    out[pos - lo: pos - lo + n] = src[a: a + n]
+                    pos += n
+                dst.copy_(out)
+            u.shard.copy_(u.master[: u.shard.numel()] if self.world == 1 else u.master)
+            if u.local is not None:
+                if old_world != self.world:
+                    raise ValueError("expert-parallel state cannot be resharded to another world size")
+                src = old_file(self.rank)
+                for tag, dst in (("master", u.local.master), ("exp_avg", u.local.exp_avg), ("exp_avg_sq", u.local.exp_avg_sq)):
+                    dst.copy_(src[f"{u.name}.local.{tag}"])
+                u.local.shard.copy_(u.local.master)
+        self.step_count = int(meta["step"])
+        if self.world > 1:
+            dist.barrier(group=self.group)
+
     def gather_full_state(self) -> dict:
         """Full (unsharded) parameters as a name -> tensor dict on every rank (for checkpoints/tests)."""
         out = {}

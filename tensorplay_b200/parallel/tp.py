@@ -28,10 +28,12 @@ from .symm import SymmArena
 _SIGS = {
     "tpb_ag_gemm": [C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                     C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_size_t, C.c_int, C.c_int,
-                    C.c_uint32, C.c_int, C.c_double, C.c_void_p, C.c_void_p],
+                    C.c_uint32, C.c_int, C.c_double, C.c_void_p, C.c_void_p, C.c_void_p],
     "tpb_gemm_rs": [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                     C.c_int, C.c_int, C.c_size_t, C.c_size_t, C.c_int, C.c_uint32, C.c_double,
-                    C.c_void_p, C.c_void_p],
+                    C.c_void_p, C.c_void_p, C.c_void_p],
+    "tpb_symm_wait_slots_dev": [C.c_size_t, C.c_int, C.c_void_p, C.c_double, C.c_void_p, C.c_void_p],
+    "tpb_symm_bump": [C.c_void_p, C.c_void_p],
 }
 
 
@@ -58,7 +60,9 @@ class AGGemmPlan:
                       for _ in range(2)]
         self.ready = [arena.slots(w) for _ in range(2)]
         self.done = [arena.slots(w) for _ in range(2)]
-        self.epoch = [0, 0]
+        # Epochs live on the device (one word per buffer, bumped in stream order after each launch):
+        # no host-side counter enters a launch, so a sequence of calls can be replayed from a CUDA graph.
+        self.epoch_dev = torch.zeros(2, dtype=torch.int32, device=arena.device)
         self.calls = 0
         self.status = status_word(arena.device)
 
@@ -66,17 +70,18 @@ class AGGemmPlan:
         """Where this rank's rows of the next call go (write here, then call ``run``)."""
         i = self.calls & 1
         raw = _raw(self.arena)
-        if self.epoch[i] > 0 and self.world > 1:
+        if self.world > 1:
             # peers must have finished pulling the previous contents of this buffer
-            _native.check(raw.tpb_symm_wait_slots(self.arena.pad_off, self.done[i], self.epoch[i], self.wait_s,
-                                                  self.status.data_ptr(), stream_ptr()), "tpb_symm_wait_slots")
+            _native.check(raw.tpb_symm_wait_slots_dev(self.arena.pad_off, self.done[i], self.epoch_dev[i:].data_ptr(),
+                                                      self.wait_s, self.status.data_ptr(), stream_ptr()),
+                          "tpb_symm_wait_slots_dev")
+            _native.launch_count += 1
         return self.full[i][self.rank * self.rows: (self.rank + 1) * self.rows]
 
     def run(self, weight: torch.Tensor, bias=None, b_mn: bool = False, out=None):
         """C[M_total, N] = gathered_rows @ weight^T; returns (C, gathered rows)."""
         i = self.calls & 1
         self.calls += 1
-        self.epoch[i] += 1
         n = weight.shape[1] if b_mn else weight.shape[0]
         if out is None:
             out = torch.empty(self.m, n, dtype=torch.bfloat16, device=weight.device)
@@ -84,10 +89,11 @@ class AGGemmPlan:
         code = raw.tpb_ag_gemm(self.arena.offset_of(self.full[i]), weight.data_ptr(), out.data_ptr(),
                                None if bias is None else bias.data_ptr(), self.m, n, self.k, weight.stride(0),
                                out.stride(0), int(b_mn), 0, self.flags[i].data_ptr(), self.rpf,
-                               self.arena.pad_off, self.ready[i], self.done[i], self.epoch[i], self.n_copy,
-                               self.wait_s, self.status.data_ptr(), stream_ptr())
-        _native.launch_count += 1
+                               self.arena.pad_off, self.ready[i], self.done[i], 0, self.n_copy,
+                               self.wait_s, self.status.data_ptr(), stream_ptr(), self.epoch_dev[i:].data_ptr())
         _native.check(code, "tpb_ag_gemm")
+        _native.check(raw.tpb_symm_bump(self.epoch_dev[i:].data_ptr(), stream_ptr()), "tpb_symm_bump")
+        _native.launch_count += 2
         return out, self.full[i]
 
 
@@ -101,7 +107,7 @@ class GemmRSPlan:
         self.rows = m_total // w
         self.stage = [arena.alloc(m_total * n, torch.bfloat16) for _ in range(2)]
         self.cnt = [arena.slots(w) for _ in range(2)]
-        self.epoch = [0, 0]
+        self.epoch_dev = torch.zeros(2, dtype=torch.int32, device=arena.device)  # see AGGemmPlan
         self.calls = 0
         self.wait_s = wait_s
         self.status = status_word(arena.device)
@@ -110,17 +116,17 @@ class GemmRSPlan:
         """out[M_total / world, N] = rows of this rank of sum_r (A_r @ W_r^T)."""
         i = self.calls & 1
         self.calls += 1
-        self.epoch[i] += 1
         k = a.shape[0] if a_mn else a.shape[1]
         if out is None:
             out = torch.empty(self.rows, self.n, dtype=torch.bfloat16, device=a.device)
         raw = _raw(self.arena)
         code = raw.tpb_gemm_rs(a.data_ptr(), weight.data_ptr(), out.data_ptr(), self.m, self.n, k, a.stride(0),
                                weight.stride(0), int(a_mn), int(b_mn), self.arena.offset_of(self.stage[i]),
-                               self.arena.pad_off, self.cnt[i], self.epoch[i], self.wait_s,
-                               self.status.data_ptr(), stream_ptr())
-        _native.launch_count += 1
+                               self.arena.pad_off, self.cnt[i], 0, self.wait_s,
+                               self.status.data_ptr(), stream_ptr(), self.epoch_dev[i:].data_ptr())
         _native.check(code, "tpb_gemm_rs")
+        _native.check(raw.tpb_symm_bump(self.epoch_dev[i:].data_ptr(), stream_ptr()), "tpb_symm_bump")
+        _native.launch_count += 2
         return out
 
 
