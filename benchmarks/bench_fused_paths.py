@@ -142,7 +142,8 @@ def main():
 
         t_f, t_b = timed(gather_fused, args.iters), timed(gather_base, args.iters)
         report(rank, f"fsdp_all_gather {u.padded * 2 / 1e6:.0f} MB / {world} ranks", t_f, t_b, 0.0,
-               (world - 1) * u.shard_numel * 2, u.padded * 2, tf_peak, hbm_peak, which)
+               (world - 1) * u.shard_numel * 2, u.padded * 2, tf_peak, hbm_peak, which,
+               {"transport": eng.comm.transport})
 
         g = eng.grad_pool[0][: u.padded]
         g.normal_()
@@ -161,7 +162,8 @@ def main():
         t_f, t_b = timed(rs_adamw_fused, args.iters), timed(rs_adamw_base, args.iters)
         # per rank: pulls (world-1) peer slices of its shard; AdamW streams 28 B per owned parameter
         report(rank, f"fsdp_rs_adamw {u.padded * 2 / 1e6:.0f} MB / {world} ranks", t_f, t_b, 0.0,
-               (world - 1) * u.shard_numel * 2, u.shard_numel * (2 + 28), tf_peak, hbm_peak, which)
+               (world - 1) * u.shard_numel * 2, u.shard_numel * (2 + 28), tf_peak, hbm_peak, which,
+               {"transport": eng.comm.transport})
     torch.cuda.synchronize()
     O.check_status()
     dist.barrier()

@@ -40,7 +40,9 @@ def main():
     model.reset_parameters(seed=0)
     eng = FSDPEngine(model, AdamWConfig(lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1),
                      activation_checkpointing=True)
-    model.attach_workspace(a.seq, capacity_factor=2.0)
+    # drop-less for any routing: one rank may receive every token of the box (a random-init router
+    # over 48 layers concentrates tokens on few experts, which shows up as load imbalance below)
+    ws = model.attach_workspace(a.seq, capacity_factor=float(world))
     g = torch.Generator().manual_seed(rank)
     tok = torch.randint(0, cfg.vocab_size, (1, a.seq), generator=g).to(dev)
     tgt = torch.randint(0, cfg.vocab_size, (1, a.seq), generator=g).to(dev)
@@ -60,13 +62,19 @@ def main():
     torch.cuda.synchronize()
     O.check_status()
     t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    rows = ws.last_recv_rows.double().reshape(1) if getattr(ws, "last_recv_rows", None) is not None else t.new_zeros(1)
+    rows_max = rows.clone()
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(rows_max, op=dist.ReduceOp.MAX)
+        dist.all_reduce(rows)
     if rank == 0:
         ms = float(t[0]) / a.steps
         print(json.dumps({"config": f"Qwen3-30B-A3B-shape MoE ({a.layers} layers, {a.experts} experts, top-8), EP={world}, seq {a.seq}, bf16",
                           "n_gpus": world, "tokens_per_s": round(world * a.seq / (ms / 1e3), 1),
-                          "ms_per_step": round(ms, 3), "loss": round(float(loss), 4), "data": "synthetic"}), flush=True)
+                          "ms_per_step": round(ms, 3), "loss": round(float(loss), 4), "data": "synthetic",
+                          "expert_load_max_over_mean_last_layer": round(float(rows_max) * world / max(float(rows), 1.0), 2)}),
+              flush=True)
     if world > 1:
         dist.destroy_process_group()
 

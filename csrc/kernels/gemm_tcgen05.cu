@@ -35,7 +35,11 @@ struct GemmCfg {
   static constexpr int kABytes = kBlockM * kBlockK * 2;
   static constexpr int kBBytes = BLOCK_N * kBlockK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  // staging of the reduce-scatter epilogue: per epilogue warp 32 rows x 64 bf16 columns, rows padded
+  // to 144 bytes (conflict-free 16-byte accesses both ways)
+  static constexpr int kOutStageOff = kStages * kStageBytes + 256;
+  static constexpr int kOutStageBytes = 4 * 32 * 144;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/ + kOutStageBytes;
   static constexpr int kTmemCols = 2 * BLOCK_N;  // double-buffered accumulator (256 or 512)
 };
 
@@ -421,6 +425,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else {
     // ------------------------------------------------------------ epilogue (4 warps)
     const int q = warp & 3;  // TMEM lane quarter this warp may read
+    uint8_t* out_stage = smem + Cfg::kOutStageOff + q * (32 * 144);
+    const bool rs_coalesce = p.rs_mode && (p.N % 64 == 0);
     uint32_t lt = 0;
     for (int wi = 0; wi < n_items; ++wi, ++lt) {
       const WorkItem w = get_work(wi);
@@ -504,7 +510,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               }
             }
           }
-          if (p.rs_mode) {
+          if (p.rs_mode && rs_coalesce) {
+            // bf16 partial into the warp's staging rows; flushed below in 128-byte row segments
+            uint8_t* srow = out_stage + lane * 144 + (c & 32) * 2;
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 o;
+              __nv_bfloat162* ob2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                ob2[j] = __floats2bfloat162_rn(v[i + 2 * j], v[i + 2 * j + 1]);
+              *reinterpret_cast<uint4*>(srow + i * 2) = o;
+            }
+          } else if (p.rs_mode) {
             // row block -> owning rank; bf16 partial straight into that rank's staging slice
             const int d = row / p.rs_rows_per_rank;
             __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.rs_stage[d]) +
@@ -570,6 +588,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 }
             }
           }
+        }
+        if (p.rs_mode && rs_coalesce && (c & 32)) {
+          // two 32-column chunks are staged: each store instruction now writes 4 rows x 128
+          // contiguous bytes (peer stores of whole cache lines instead of 16-byte fragments)
+          __syncwarp();
+          const int col64 = tn * BLOCK_N + (c - 32);
+#pragma unroll
+          for (int it4 = 0; it4 < 8; ++it4) {
+            const int rr = it4 * 4 + (lane >> 3);
+            const int grow = tm * kBlockM + q * 32 + rr;
+            if (grow < p.M) {
+              const uint4 val = *reinterpret_cast<const uint4*>(out_stage + rr * 144 + (lane & 7) * 16);
+              const int d = grow / p.rs_rows_per_rank;
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.rs_stage[d]) +
+                                   ((size_t)p.rank * p.rs_rows_per_rank + (grow - d * p.rs_rows_per_rank)) * p.N +
+                                   col64 + (lane & 7) * 8;
+              *reinterpret_cast<uint4*>(dst) = val;
+            }
+          }
+          __syncwarp();
         }
       }
       tc_fence_before_sync();

@@ -179,6 +179,22 @@ static AdamHyper make_hyper(float lr, float b1, float b2, float eps, float wd, i
   return h;
 }
 
+// Overlap mode of the flat AdamW (see tpb_adamw_set_overlap).
+static int g_adamw_ctas_per_sm = 0;
+static bool g_adamw_max_shared = false;
+static bool g_adamw_carveout_dirty = false;
+
+// ctas_per_sm > 0 limits the grid of tpb_adamw_flat to that many CTAs per SM and max_shared != 0 lets
+// them share an SM with the persistent GEMM: a memory-bound update launched on a side stream then
+// trickles along under the compute-bound GEMMs of the next layer instead of holding their SMs.
+// (0, 0) restores the stand-alone configuration (full grid, default carveout).
+extern "C" int tpb_adamw_set_overlap(int ctas_per_sm, int max_shared) {
+  g_adamw_ctas_per_sm = ctas_per_sm;
+  g_adamw_max_shared = max_shared != 0;
+  g_adamw_carveout_dirty = true;
+  return 0;
+}
+
 extern "C" int tpb_adamw_flat(float* master, float* m, float* v, const void* grad, int grad_bf16,
                               void* model, int model_bf16, long long n, float lr, float beta1,
                               float beta2, float eps, float wd, int step, float grad_scale,
@@ -193,10 +209,21 @@ extern "C" int tpb_adamw_flat(float* master, float* m, float* v, const void* gra
     return -2;
   AdamHyper h = make_hyper(lr, beta1, beta2, eps, wd, step, grad_scale, maximize);
   long long blocks = (n / 4 + 255) / 256;
-  long long cap = (long long)sm_count() * 16;
+  long long cap = (long long)sm_count() * (g_adamw_ctas_per_sm > 0 ? g_adamw_ctas_per_sm : 16);
   int grid = (int)(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
   // the tail loop needs at least ceil(3/256) = 1 block; grid >= 1 always holds
   cudaStream_t s = (cudaStream_t)stream;
+  if (g_adamw_carveout_dirty) {
+    // In overlap mode the kernel accepts the persistent GEMM's shared-memory carveout, so that its
+    // CTAs can be placed on an SM beside a GEMM CTA (an SM keeps its L1 / shared split while any CTA
+    // is resident; with the default preference the next GEMM would wait for this kernel to drain).
+    const int pref = g_adamw_max_shared ? (int)cudaSharedmemCarveoutMaxShared : (int)cudaSharedmemCarveoutDefault;
+    cudaFuncSetAttribute(adamw_flat_kernel<__nv_bfloat16, __nv_bfloat16>, cudaFuncAttributePreferredSharedMemoryCarveout, pref);
+    cudaFuncSetAttribute(adamw_flat_kernel<__nv_bfloat16, float>, cudaFuncAttributePreferredSharedMemoryCarveout, pref);
+    cudaFuncSetAttribute(adamw_flat_kernel<float, __nv_bfloat16>, cudaFuncAttributePreferredSharedMemoryCarveout, pref);
+    cudaFuncSetAttribute(adamw_flat_kernel<float, float>, cudaFuncAttributePreferredSharedMemoryCarveout, pref);
+    g_adamw_carveout_dirty = false;
+  }
 #define LAUNCH(GT, MT)                                                                     \
   adamw_flat_kernel<GT, MT><<<grid, 256, 0, s>>>(master, m, v, (const GT*)grad, (MT*)model, n, h, \
                                                  clip_coef, found_inf)

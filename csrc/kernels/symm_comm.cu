@@ -142,8 +142,10 @@ rs_adamw_kernel(PeerPtrs grads, size_t lo, size_t n, float* __restrict__ master,
                 float* __restrict__ m, float* __restrict__ v, __nv_bfloat16* __restrict__ shard_out,
                 PeerPtrs bcast_out, size_t bcast_off, int do_bcast, float* __restrict__ red_out,
                 float* __restrict__ sumsq, int mode, AdamArgs h, const float* clip_coef, SyncArgs s,
-                int ready_slot, int done_slot, uint32_t* block_counter) {
-  if (!rendezvous(s, ready_slot, 21)) return;
+                int ready_slot, int done_slot, uint32_t* block_counter, int local_only) {
+  // local_only: every gradient copy already sits in this GPU's memory (the copy engines pulled the
+  // peers' slices and the hand-shakes ran as separate one-CTA kernels): no flags are touched here
+  if (!local_only && !rendezvous(s, ready_slot, 21)) return;
   const float gs = h.grad_scale * (clip_coef ? *clip_coef : 1.f);
   const size_t nvec = n / 8;
   float local_sq = 0.f;
@@ -152,11 +154,11 @@ rs_adamw_kernel(PeerPtrs grads, size_t lo, size_t n, float* __restrict__ master,
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    // loads of up to four ranks are issued together, then summed in rank order (deterministic)
-    for (int r0 = 0; r0 < s.world; r0 += 4) {
-      uint4 raw[4];
+    // loads of up to eight ranks are issued together, then summed in rank order (deterministic)
+    for (int r0 = 0; r0 < s.world; r0 += 8) {
+      uint4 raw[8];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < 8; ++u) {
         const int r = r0 + u;
         if (r < s.world) {
           const uint4* src = reinterpret_cast<const uint4*>(grads.p[r]) + lo / 8 + i;
@@ -164,7 +166,7 @@ rs_adamw_kernel(PeerPtrs grads, size_t lo, size_t n, float* __restrict__ master,
         }
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < 8; ++u) {
         if (r0 + u < s.world) {
           const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
 #pragma unroll
@@ -235,6 +237,7 @@ rs_adamw_kernel(PeerPtrs grads, size_t lo, size_t n, float* __restrict__ master,
     for (int o = 16; o > 0; o >>= 1) local_sq += __shfl_xor_sync(0xffffffffu, local_sq, o);
     if ((threadIdx.x & 31) == 0) atomicAdd(sumsq, local_sq);
   }
+  if (local_only) return;
   // tell the peers that this rank no longer reads their gradient buffers (and, for the
   // broadcast form, that its slice of their parameters has landed)
   __threadfence_system();
@@ -263,6 +266,15 @@ __global__ void wait_slots_dev_kernel(SyncArgs s, int slot_base, const uint32_t*
 __global__ void bump_kernel(uint32_t* ctr) { *ctr += 1u; }
 
 __global__ void barrier_kernel(SyncArgs s, int slot_base) { rendezvous(s, slot_base, 22); }
+
+// One-way signal: slot (slot_base + rank) on every rank's pad <- epoch (everything this stream did
+// before, copies by the copy engines included, is complete and visible).
+__global__ void signal_kernel(SyncArgs s, int slot_base) {
+  if (threadIdx.x < s.world) {
+    __threadfence_system();
+    st_release_sys(s.pad_peer[threadIdx.x] + slot_base + s.rank, s.epoch);
+  }
+}
 
 // Generic peer copy: dst (local) <- src on rank r (no rendezvous; caller orders it).
 __global__ void __launch_bounds__(512)
@@ -408,7 +420,7 @@ extern "C" int tpb_symm_rs_adamw(size_t grad_off, size_t lo, size_t n, float* ma
   rs_adamw_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(
       peers_at(grad_off), lo, n, master, m, v, (__nv_bfloat16*)shard_out,
       do_bcast ? peers_at(0) : peers_at(0), do_bcast ? bcast_off : 0, do_bcast, red_out, sumsq, mode,
-      h, clip_coef, s, ready_slot, done_slot, block_counter);
+      h, clip_coef, s, ready_slot, done_slot, block_counter, 0);
   return (int)cudaGetLastError();
 }
 
@@ -445,5 +457,91 @@ extern "C" int tpb_symm_peer_copy(int src_rank, size_t src_off, void* dst, size_
   if (bytes % 16) return -2;
   peer_copy_kernel<<<ctas > 0 ? ctas : 32, 512, 0, (cudaStream_t)stream>>>(
       g_symm.peer[src_rank] + src_off, static_cast<char*>(dst), bytes);
+  return (int)cudaGetLastError();
+}
+
+// Overlap mode of the reduce + AdamW kernel (both transports): `threads` per CTA (256 leaves room
+// beside a persistent GEMM CTA in the register file) and whether it accepts the GEMM's shared-memory
+// carveout, i.e. may share an SM with it instead of waiting for the GEMM's CTAs to leave.
+static int g_rs_threads = 512;
+static bool g_rs_cfg_dirty = false;
+static bool g_rs_max_shared = false;
+extern "C" int tpb_symm_set_overlap(int threads, int max_shared) {
+  if (threads != 128 && threads != 256 && threads != 512) return -1;
+  g_rs_threads = threads;
+  g_rs_max_shared = max_shared != 0;
+  g_rs_cfg_dirty = true;
+  return 0;
+}
+static int rs_threads() {
+  if (g_rs_cfg_dirty) {
+    cudaFuncSetAttribute(rs_adamw_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         g_rs_max_shared ? (int)cudaSharedmemCarveoutMaxShared : (int)cudaSharedmemCarveoutDefault);
+    g_rs_cfg_dirty = false;
+  }
+  return g_rs_threads;
+}
+
+// ---------------------------------------------------------------- copy-engine variants
+// Bulk transfers by the GPU's copy engines instead of SM kernels: the NVLink traffic then costs no
+// SM time and never competes with the persistent GEMMs for their SMs. The hand-shakes stay on the
+// device (one-CTA kernels in the same stream); the arithmetic stays fused in one kernel that reads
+// only local memory.
+
+// All-gather: out[r * shard_bytes ...] = shard of rank r (peers are visited starting at rank + 1).
+extern "C" int tpb_symm_allgather_ce(size_t shard_off, size_t shard_bytes, void* out, size_t pad_off,
+                                     int slot_base, uint32_t epoch, double wait_s, uint32_t* status,
+                                     void* stream) {
+  if (!g_symm.opened && g_symm.world > 1) return -4;
+  cudaStream_t st = (cudaStream_t)stream;
+  SyncArgs s = make_sync(pad_off, epoch, status, wait_s);
+  barrier_kernel<<<1, 32, 0, st>>>(s, slot_base);  // every rank's shard is valid at this epoch
+  for (int k = 1; k <= g_symm.world; ++k) {
+    const int r = (g_symm.rank + k) % g_symm.world;
+    cudaError_t e = cudaMemcpyAsync(static_cast<char*>(out) + (size_t)r * shard_bytes,
+                                    g_symm.peer[r] + shard_off, shard_bytes, cudaMemcpyDeviceToDevice, st);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return (int)cudaGetLastError();
+}
+
+// Reduce-scatter + AdamW: the peers' slices [lo, lo + n) of the bf16 gradient buffer at grad_off are
+// pulled into `staging` ([world][n] bf16, local), the peers are told that their buffers are free, and
+// the fused reduce + scale + AdamW kernel runs on local memory only. Modes as in tpb_symm_rs_adamw
+// (0 and 1; the broadcast forms need peer stores and stay with the SM kernel).
+extern "C" int tpb_symm_rs_adamw_ce(size_t grad_off, size_t lo, size_t n, void* staging, float* master,
+                                    float* m, float* v, void* shard_out, float* red_out, float* sumsq,
+                                    int mode, float lr, float beta1, float beta2, float eps, float wd,
+                                    int step, float grad_scale, const float* clip_coef, size_t pad_off,
+                                    int ready_slot, int done_slot, uint32_t epoch, int ctas,
+                                    double wait_s, uint32_t* status, void* stream) {
+  if (!g_symm.opened && g_symm.world > 1) return -4;
+  if (n % 8 || lo % 8 || (mode != 0 && mode != 1)) return -2;
+  cudaStream_t st = (cudaStream_t)stream;
+  SyncArgs s = make_sync(pad_off, epoch, status, wait_s);
+  barrier_kernel<<<1, 32, 0, st>>>(s, ready_slot);  // every rank's gradients are complete
+  PeerPtrs local;
+  memset(&local, 0, sizeof(local));
+  for (int k = 0; k < g_symm.world; ++k) {
+    const int r = (g_symm.rank + k) % g_symm.world;
+    if (r == g_symm.rank) {
+      local.p[r] = g_symm.base + grad_off;  // own copy is read in place
+      continue;
+    }
+    char* dst = static_cast<char*>(staging) + (size_t)r * n * 2;
+    cudaError_t e = cudaMemcpyAsync(dst, g_symm.peer[r] + grad_off + lo * 2, n * 2, cudaMemcpyDeviceToDevice, st);
+    if (e != cudaSuccess) return (int)e;
+    local.p[r] = dst - lo * 2;  // the kernel indexes every copy at element lo + i
+  }
+  signal_kernel<<<1, 32, 0, st>>>(s, done_slot);  // the peers' gradient buffers may be reused
+  AdamArgs h;
+  h.lr = lr; h.beta1 = beta1; h.beta2 = beta2; h.eps = eps; h.weight_decay = wd;
+  h.bias_c1 = 1.f - powf(beta1, (float)step);
+  h.bias_c2 = 1.f - powf(beta2, (float)step);
+  h.grad_scale = grad_scale;
+  const int grid = ctas > 0 ? ctas : 148;
+  rs_adamw_kernel<<<grid, rs_threads(), 0, st>>>(local, lo, n, master, m, v, (__nv_bfloat16*)shard_out, local, 0, 0,
+                                        red_out, sumsq, mode, h, clip_coef, s, ready_slot, done_slot,
+                                        nullptr, 1);
   return (int)cudaGetLastError();
 }

@@ -43,6 +43,7 @@ _KERNEL_SIGS = {
     "tpb_grouped_workspace_ints": [I, I],
     "tpb_grouped_gemm": [P, P, P, P, I, I, I, I, I, I, I, I, P, P, P],
     "tpb_adamw_flat": [P, P, P, P, I, P, I, LL, F, F, F, F, F, I, F, I, P, P, P],
+    "tpb_adamw_set_overlap": [I, I],
     "tpb_adamw_multi": [I, P, P, P, P, P, P, I, I, F, F, F, F, F, I, F, I, P, P, P],
     "tpb_sumsq": [P, I, LL, F, P, P],
     "tpb_clip_coef": [P, F, P, P, P],
@@ -81,7 +82,7 @@ def _load(name: str):
 
 # kernel launches issued by one call of each entry point (for launch accounting)
 _LAUNCHES = {"tpb_rmsnorm_bwd": 2, "tpb_layernorm_bwd": 3, "tpb_flash_bwd": 3, "tpb_rmsnorm_bwd_grid": 0,
-             "tpb_grouped_workspace_ints": 0, "tpb_gemm_set_splitk_workspace": 0, "tpb_grouped_gemm": 2}
+             "tpb_grouped_workspace_ints": 0, "tpb_adamw_set_overlap": 0, "tpb_gemm_set_splitk_workspace": 0, "tpb_grouped_gemm": 2}
 launch_count = 0
 
 

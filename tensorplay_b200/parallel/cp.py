@@ -168,13 +168,15 @@ class _RingAttnFn(torch.autograd.Function):
             ring.prefetch(order[1], 1)
         for i, c in enumerate(order):
             kc, vc = ring.get(c)
-            if i + 2 < len(order):
-                ring.prefetch(order[i + 2], i & 1)
             if q.is_cuda:
                 o_s, lse_s = flash_fwd(q, kc, vc, causal and c == rank, scale)
             else:
                 o_s, lse_s, _ = _ref_attn_lse(q, kc, vc, causal and c == rank, scale)
             acc, lse = merge_partials(acc, lse, o_s, lse_s)
+            # staging buffer i & 1 is free once the kernels just enqueued have read it: the pull of
+            # chunk i + 2 is ordered after them and overlaps with the attention over chunk i + 1
+            if i + 2 < len(order):
+                ring.prefetch(order[i + 2], i & 1)
         ring.close()
         out = acc.to(q.dtype)
         ctx.save_for_backward(q, k, v, out, lse)
@@ -194,8 +196,6 @@ class _RingAttnFn(torch.autograd.Function):
             ring.prefetch(order[1], 1)
         for i, c in enumerate(order):
             kc, vc = ring.get(c)
-            if i + 2 < len(order):
-                ring.prefetch(order[i + 2], i & 1)
             if q.is_cuda:
                 dq_s, dk_s, dv_s = flash_bwd(do, q, kc, vc, out, lse, causal and c == rank, scale)
             else:
@@ -203,6 +203,8 @@ class _RingAttnFn(torch.autograd.Function):
             dq += dq_s.float()
             dkv[c, 0] = dk_s.float()
             dkv[c, 1] = dv_s.float()
+            if i + 2 < len(order):
+                ring.prefetch(order[i + 2], i & 1)
         ring.close()
         # partials for chunk c go back to rank c, summed over the ranks that attended it
         mine = torch.empty((2,) + tuple(k.shape), dtype=torch.float32, device=k.device)

@@ -188,6 +188,15 @@ class FSDPEngine:
         self._build_units()
         self._alloc()
         self._dummy = torch.zeros(1, device=self.device, requires_grad=True)
+        if self.cuda and self.world == 1:
+            # the per-unit AdamW runs on a side stream under the next unit's backward: a small grid
+            # that may share SMs with the persistent GEMM (TPB_ADAMW_OVERLAP="ctas_per_sm,max_shared")
+            import os
+            spec = os.environ.get("TPB_ADAMW_OVERLAP", "")
+            if spec:
+                c, m_ = (int(x) for x in spec.split(","))
+                from .. import _native
+                _native.kernels().tpb_adamw_set_overlap(c, m_)
         self.kernel_launch_estimate = 0
 
     # ------------------------------------------------------------------ construction

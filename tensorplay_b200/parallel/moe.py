@@ -136,6 +136,7 @@ class MoEWorkspace:
                                       self.slot_route, self.epoch, self.wait_s, self.status.data_ptr(), stream_ptr())
         _native.launch_count += 1
         _native.check(code, "tpb_moe_route")
+        self.last_recv_rows = rows  # device scalar: padded rows this rank received (load statistic)
         return dst_rank, dst_row, offs
 
     def dispatch(self, x: torch.Tensor, dst_rank, dst_row, buf: torch.Tensor, scale=None) -> None:

@@ -9,6 +9,7 @@ __init__.py:118-130; ``rendezvous`` only all-gathers metadata, :456-467).
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Dict, Optional
 
 import torch
@@ -28,6 +29,13 @@ _SIGS = {
                           C.c_float, C.c_float, C.c_float, C.c_float, C.c_int, C.c_float, C.c_void_p,
                           C.c_size_t, C.c_int, C.c_int, C.c_uint32, C.c_void_p, C.c_int, C.c_double,
                           C.c_void_p, C.c_void_p],
+    "tpb_symm_allgather_ce": [C.c_size_t, C.c_size_t, C.c_void_p, C.c_size_t, C.c_int, C.c_uint32, C.c_double,
+                              C.c_void_p, C.c_void_p],
+    "tpb_symm_rs_adamw_ce": [C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                             C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_float, C.c_float, C.c_float,
+                             C.c_float, C.c_float, C.c_int, C.c_float, C.c_void_p, C.c_size_t, C.c_int, C.c_int,
+                             C.c_uint32, C.c_int, C.c_double, C.c_void_p, C.c_void_p],
+    "tpb_symm_set_overlap": [C.c_int, C.c_int],
     "tpb_symm_wait_slots": [C.c_size_t, C.c_int, C.c_uint32, C.c_double, C.c_void_p, C.c_void_p],
     "tpb_symm_barrier": [C.c_size_t, C.c_int, C.c_uint32, C.c_double, C.c_void_p, C.c_void_p],
     "tpb_symm_peer_copy": [C.c_int, C.c_size_t, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p],
@@ -132,7 +140,10 @@ class SymmComm:
         total += extra_bytes  # head-room for other users of the arena (TP plans, MoE workspaces)
         self.arena = SymmArena(total, group=engine.group)
         self.wait_s = wait_s
-        self.gather_ctas, self.reduce_ctas = gather_ctas, reduce_ctas
+        # CTAs of the communication kernels: enough to keep NVLink busy, few enough to leave the SMs
+        # to the GEMMs they overlap with (TPB_GATHER_CTAS / TPB_REDUCE_CTAS override for tuning)
+        self.gather_ctas = int(os.environ.get("TPB_GATHER_CTAS", gather_ctas))
+        self.reduce_ctas = int(os.environ.get("TPB_REDUCE_CTAS", reduce_ctas))
         w = self.world
         self.slot_gather = {u.index: self.arena.slots(w) for u in units}
         self.slot_ready = {u.index: self.arena.slots(w) for u in units}
@@ -141,6 +152,17 @@ class SymmComm:
         self.epoch_reduce = {u.index: 0 for u in units}
         self.grad_slot_last = {}  # grad pool slot -> (unit index, epoch) whose readers must finish
         self.status = status_word(engine.device)
+        # "ce": bulk transfers by the copy engines (no SM time; the fused reduce + AdamW kernel then
+        # reads local memory only); "sm": pull kernels that load from peer memory themselves.
+        spec = os.environ.get("TPB_REDUCE_OVERLAP", "")  # "threads,max_shared" for the reduce + AdamW kernel
+        if spec:
+            th, ms = (int(x) for x in spec.split(","))
+            _native.check(self.arena.raw.tpb_symm_set_overlap(th, ms), "tpb_symm_set_overlap")
+        self.transport = os.environ.get("TPB_COMM_TRANSPORT", "ce")
+        self.staging = None
+        if self.transport == "ce":
+            shard_max = max(u.shard_numel for u in units)
+            self.staging = torch.empty(self.world * shard_max, dtype=engine.param_dtype, device=engine.device)
 
     def alloc_shard(self, u) -> torch.Tensor:
         t = self.arena.alloc(u.shard_numel, self.engine.param_dtype)
@@ -152,6 +174,14 @@ class SymmComm:
 
     def all_gather(self, u, buf: torch.Tensor) -> None:
         self.epoch_gather[u.index] += 1
+        if self.transport == "ce":
+            code = self.arena.raw.tpb_symm_allgather_ce(
+                u._shard_off, u.shard_numel * buf.element_size(), buf.data_ptr(), self.arena.pad_off,
+                self.slot_gather[u.index], self.epoch_gather[u.index], self.wait_s, self.status.data_ptr(),
+                stream_ptr())
+            _native.launch_count += 1
+            _native.check(code, "tpb_symm_allgather_ce")
+            return
         code = self.arena.raw.tpb_symm_allgather(
             u._shard_off, u.shard_numel * buf.element_size(), buf.data_ptr(), self.arena.pad_off,
             self.slot_gather[u.index], self.epoch_gather[u.index], self.gather_ctas, self.wait_s,
@@ -163,6 +193,17 @@ class SymmComm:
         self.epoch_reduce[u.index] += 1
         ep = self.epoch_reduce[u.index]
         lo, hi = u.shard_range()
+        if self.transport == "ce":
+            code = self.arena.raw.tpb_symm_rs_adamw_ce(
+                self.arena.offset_of(g), lo, hi - lo, self.staging.data_ptr(), u.master.data_ptr(),
+                u.exp_avg.data_ptr(), u.exp_avg_sq.data_ptr(), u.shard.data_ptr(), None, None, 0, adam["lr"],
+                adam["beta1"], adam["beta2"], adam["eps"], adam["weight_decay"], int(adam["step"]),
+                1.0 / self.world, None, self.arena.pad_off, self.slot_ready[u.index], self.slot_done[u.index],
+                ep, self.reduce_ctas, self.wait_s, self.status.data_ptr(), stream_ptr())
+            _native.launch_count += 3
+            _native.check(code, "tpb_symm_rs_adamw_ce")
+            self.grad_slot_last[u._grad_slot] = (u.index, ep)
+            return
         code = self.arena.raw.tpb_symm_rs_adamw(
             self.arena.offset_of(g), lo, hi - lo, u.master.data_ptr(), u.exp_avg.data_ptr(),
             u.exp_avg_sq.data_ptr(), u.shard.data_ptr(), NO_OFFSET, None, None, 0, adam["lr"],
@@ -180,6 +221,16 @@ class SymmComm:
         self.epoch_reduce[u.index] += 1
         ep = self.epoch_reduce[u.index]
         lo, hi = u.shard_range()
+        if self.transport == "ce":
+            code = self.arena.raw.tpb_symm_rs_adamw_ce(
+                self.arena.offset_of(g), lo, hi - lo, self.staging.data_ptr(), None, None, None, None,
+                red_out.data_ptr(), sumsq.data_ptr(), 1, 0.0, 0.9, 0.999, 1e-8, 0.0, 1, 1.0 / self.world, None,
+                self.arena.pad_off, self.slot_ready[u.index], self.slot_done[u.index], ep, self.reduce_ctas,
+                self.wait_s, self.status.data_ptr(), stream_ptr())
+            _native.launch_count += 3
+            _native.check(code, "tpb_symm_rs_adamw_ce")
+            self.grad_slot_last[u._grad_slot] = (u.index, ep)
+            return
         code = self.arena.raw.tpb_symm_rs_adamw(
             self.arena.offset_of(g), lo, hi - lo, None, None, None, None, NO_OFFSET, red_out.data_ptr(),
             sumsq.data_ptr(), 1, 0.0, 0.9, 0.999, 1e-8, 0.0, 1, 1.0 / self.world, None, self.arena.pad_off,
