@@ -1,0 +1,75 @@
+"""Quantised kernels on one B200: int8 tensor-core GEMM (A8W8) against the bf16 GEMM of the same
+shape, and the weight-only GEMV (W8A16 / W4A16) against its weight-streaming roofline.
+
+    python benchmarks/bench_quant.py
+CUDA events, 3 warm-ups; every operand set is larger than the 126 MB L2 or rotated so that weights
+come from HBM.
+"""
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import tensorplay_b200.ops as O  # noqa: E402
+
+
+def timeit(fn, iters=10, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def main():
+    dev = "cuda"
+    try:
+        with open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")) as f:
+            hbm = float(json.load(f).get("hbm_gbs", 6650.0))
+    except Exception:
+        hbm = 6650.0
+    out = []
+    for M, N, K in ((8192, 8192, 8192), (4096, 28672, 4096)):
+        a = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev)
+        w = torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev)
+        sa, sw = torch.rand(M, device=dev), torch.rand(N, device=dev)
+        ab, wb = torch.randn(M, K, device=dev).bfloat16(), torch.randn(N, K, device=dev).bfloat16()
+        t8 = timeit(lambda: O.int8_gemm(a, w, sa, sw))
+        t16 = timeit(lambda: O.gemm(ab, wb))
+        out.append({"kernel": "int8_gemm (tcgen05 kind::i8, scaled bf16 out)", "shape": [M, N, K], "ms": round(t8, 4),
+                    "tops": round(2.0 * M * N * K / t8 / 1e9, 1), "bf16_gemm_ms": round(t16, 4),
+                    "bf16_tflops": round(2.0 * M * N * K / t16 / 1e9, 1)})
+    # decode GEMV: 8 rotating weight matrices (1.9 GB of int8) so that every call streams from HBM
+    N, K, M = 28672, 8192, 8
+    x = torch.randn(M, K, device=dev).bfloat16()
+    for bits, group in ((8, 0), (4, 128)):
+        ws = []
+        for _ in range(8):
+            w = torch.randn(N, K, device=dev)
+            ws.append(O.quantize_weight_int8(w) + (None,) if bits == 8 else O.quantize_weight_int4(w, group))
+            del w
+        i = [0]
+
+        def run():
+            q, s, z = ws[i[0] % 8]
+            i[0] += 1
+            O.weight_only_linear(x, q, s, z, None, bits, group)
+
+        t = timeit(run, iters=16)
+        wbytes = N * K * bits // 8
+        out.append({"kernel": f"W{bits}A16 GEMV", "shape": [M, N, K], "group": group, "ms": round(t, 4),
+                    "weight_gbs": round(wbytes / t / 1e6, 1), "fraction_of_measured_hbm": round(wbytes / t / 1e6 / hbm, 3)})
+    O.check_status()
+    for o in out:
+        print(json.dumps(o), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -38,8 +38,10 @@ def main():
     cfg.num_layers = a.layers
     model = Qwen3MoE(cfg, device=dev, dtype=torch.bfloat16)
     model.reset_parameters(seed=0)
+    # arena head-room for the expert-parallel workspace (3 row buffers of `world` x the mean load)
+    ws_bytes = 3 * (a.seq * cfg.top_k * world + 4096) * cfg.hidden_size * 2 + (256 << 20)
     eng = FSDPEngine(model, AdamWConfig(lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1),
-                     activation_checkpointing=True)
+                     activation_checkpointing=True, symm_extra_bytes=ws_bytes)
     # drop-less for any routing: one rank may receive every token of the box (a random-init router
     # over 48 layers concentrates tokens on few experts, which shows up as load imbalance below)
     ws = model.attach_workspace(a.seq, capacity_factor=float(world))

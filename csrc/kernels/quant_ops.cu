@@ -189,8 +189,19 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 }
 
 // ------------------------------------------------------------------ weight-only GEMV (decode)
-// y[m, n] = sum_k x[m, k] * dq(W[n, k]); one warp per output column, up to 8 rows of x held
-// per pass; weights stream through once at packed width.
+// y[m, n] = sum_k x[m, k] * dq(W[n, k]) for up to 8 rows of x. A warp owns kCols output columns at a
+// time; every lane owns 16 consecutive k per step: it unpacks the 8 x 16 activations of its slice to
+// fp32 registers once and reuses them for all kCols columns, so the kernel streams the packed weights
+// once and the activations (L2-resident) only 1/kCols times per column. Integer codes become fp32
+// by placing them in the mantissa of 2^23 (one permute + one add, no conversion instruction) and
+// the inner products use packed fp32x2 FMAs.
+constexpr int kGemvCols = 4;
+
+__device__ __forceinline__ float code_to_f32(uint32_t byte_in_low_bits) {
+  // 0x4B000000 = 2^23; the code sits in the low mantissa bits
+  return __uint_as_float(0x4B000000u | byte_in_low_bits) - 8388608.f;
+}
+
 template <int BITS>
 __global__ void __launch_bounds__(256)
 wq_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ w,
@@ -199,57 +210,90 @@ wq_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ 
                int K, int group, long long ldx, long long ldy) {
   constexpr int kRows = 8;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n = blockIdx.x * 8 + warp;
-  if (n >= N) return;
   const int groups_per_row = (group > 0) ? K / group : 1;
-  const size_t wrow = (size_t)n * (BITS == 8 ? K : K / 2);
-  for (int m0 = 0; m0 < M; m0 += kRows) {
-    float acc[kRows];
+  const int n_groups = (N + kGemvCols - 1) / kGemvCols;
+  for (int ng = blockIdx.x * 8 + warp; ng < n_groups; ng += gridDim.x * 8) {
+    const int n0 = ng * kGemvCols;
+    float2 acc[kGemvCols][kRows / 2];  // acc[c][r / 2].{x, y} = rows r, r + 1
 #pragma unroll
-    for (int r = 0; r < kRows; ++r) acc[r] = 0.f;
-    // 16 packed bytes per lane per step: 16 (int8) or 32 (int4) weights
-    constexpr int kPerLane = (BITS == 8) ? 16 : 32;
-    for (int k0 = lane * kPerLane; k0 < K; k0 += 32 * kPerLane) {
-      const uint4 pk = __ldg(reinterpret_cast<const uint4*>(w + wrow + (BITS == 8 ? k0 : k0 / 2)));
-      const uint32_t words[4] = {pk.x, pk.y, pk.z, pk.w};
-      float wv[kPerLane];
-      if (BITS == 8) {
-        const float s = __bfloat162float(scale[(size_t)n * groups_per_row + (group > 0 ? k0 / group : 0)]);
+    for (int c = 0; c < kGemvCols; ++c)
 #pragma unroll
-        for (int i = 0; i < 16; ++i) wv[i] = (float)(int8_t)((words[i >> 2] >> ((i & 3) * 8)) & 0xff) * s;
-      } else {
-        // unsigned 4-bit codes, low nibble first; dq = (code - zero) * scale, zero defaults to 8
-        const int g = group > 0 ? k0 / group : 0;  // 32 consecutive weights never straddle a group (group % 32 == 0)
-        const float s = __bfloat162float(scale[(size_t)n * groups_per_row + g]);
-        const float z = zero ? __bfloat162float(zero[(size_t)n * groups_per_row + g]) : 8.f;
+      for (int r = 0; r < kRows / 2; ++r) acc[c][r] = make_float2(0.f, 0.f);
+    for (int k0 = lane * 16; k0 < K; k0 += 32 * 16) {
+      // packed weights of the kCols columns first (independent global loads in flight)
+      uint32_t wq[kGemvCols][4];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) wv[i] = ((float)((words[i >> 3] >> ((i & 7) * 4)) & 0xf) - z) * s;
+      for (int c = 0; c < kGemvCols; ++c) {
+        const int n = min(n0 + c, N - 1);
+        if (BITS == 8) {
+          const uint4 v = __ldg(reinterpret_cast<const uint4*>(w + (size_t)n * K + k0));
+          wq[c][0] = v.x; wq[c][1] = v.y; wq[c][2] = v.z; wq[c][3] = v.w;
+        } else {
+          const uint2 v = __ldg(reinterpret_cast<const uint2*>(w + (size_t)n * (K / 2) + k0 / 2));
+          wq[c][0] = v.x; wq[c][1] = v.y; wq[c][2] = 0; wq[c][3] = 0;
+        }
       }
+      // activations of this k slice: xr[j][r / 2] = (x[r][k0 + j], x[r + 1][k0 + j])
+      float2 xr[16][kRows / 2];
 #pragma unroll
       for (int r = 0; r < kRows; ++r) {
-        if (m0 + r < M) {
-          const __nv_bfloat16* xr = x + (size_t)(m0 + r) * ldx + k0;
+        uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+        if (r < M) {
+          const uint4* xp = reinterpret_cast<const uint4*>(x + (size_t)r * ldx + k0);
+          lo = __ldg(xp);
+          hi = __ldg(xp + 1);
+        }
+        const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
 #pragma unroll
-          for (int i = 0; i < kPerLane; i += 8) {
-            const uint4 xv = *reinterpret_cast<const uint4*>(xr + i);
-            const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+        for (int j = 0; j < 16; ++j) {
+          const uint32_t u = words[j >> 1];
+          const float f = __uint_as_float((j & 1) ? (u & 0xffff0000u) : (u << 16));
+          if (r & 1) xr[j][r >> 1].y = f; else xr[j][r >> 1].x = f;
+        }
+      }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 f = __bfloat1622float2(xp[j]);
-              acc[r] += f.x * wv[i + 2 * j] + f.y * wv[i + 2 * j + 1];
-            }
+      for (int c = 0; c < kGemvCols; ++c) {
+        float sc = 1.f, zp = 0.f;
+        if (group > 0 || BITS == 4) {
+          // group-wise: the slice of 16 k lies inside one group (group % 16 == 0)
+          const int n = min(n0 + c, N - 1);
+          const int g = group > 0 ? k0 / group : 0;
+          sc = __bfloat162float(scale[(size_t)n * groups_per_row + g]);
+          if (BITS == 4) zp = zero ? __bfloat162float(zero[(size_t)n * groups_per_row + g]) : 8.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          float wv;
+          if (BITS == 8) {
+            // signed byte -> biased code (b ^ 0x80) in [0, 255], value = code - 128
+            const uint32_t code = ((wq[c][j >> 2] >> ((j & 3) * 8)) & 0xffu) ^ 0x80u;
+            wv = code_to_f32(code) - 128.f;
+          } else {
+            const uint32_t code = (wq[c][j >> 3] >> ((j & 7) * 4)) & 0xfu;
+            wv = code_to_f32(code) - zp;
           }
+          if (group > 0 || BITS == 4) wv *= sc;
+          const float2 w2 = make_float2(wv, wv);
+#pragma unroll
+          for (int r = 0; r < kRows / 2; ++r) acc[c][r] = __ffma2_rn(xr[j][r], w2, acc[c][r]);
         }
       }
     }
 #pragma unroll
-    for (int r = 0; r < kRows; ++r) {
-      float a = acc[r];
+    for (int c = 0; c < kGemvCols; ++c) {
+      const int n = n0 + c;
+      float sc = 1.f;
+      if (group <= 0 && BITS == 8 && n < N) sc = __bfloat162float(scale[n]);  // per-channel scale applied once
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-      if (lane == 0 && m0 + r < M) {
-        if (bias) a += __bfloat162float(bias[n]);
-        y[(size_t)(m0 + r) * ldy + n] = __float2bfloat16(a);
+      for (int r = 0; r < kRows; ++r) {
+        float a = (r & 1) ? acc[c][r >> 1].y : acc[c][r >> 1].x;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+        if (lane == 0 && r < M && n < N) {
+          a *= sc;
+          if (bias) a += __bfloat162float(bias[n]);
+          y[(size_t)r * ldy + n] = __float2bfloat16(a);
+        }
       }
     }
   }
@@ -414,27 +458,33 @@ int tpb_gemm_i8(const void* A, const void* B, void* C, const float* a_scale, con
 }
 
 // bits = 8: W int8 [N, K], scale bf16 [N, K/group] (group = 0: one scale per row).
-// bits = 4: W uint8 [N, K/2] (two codes per byte, low nibble first), group % 32 == 0.
+// bits = 4: W uint8 [N, K/2] (two codes per byte, low nibble first), group-wise (group % 16 == 0).
 int tpb_wq_gemv(const void* x, const void* w, const void* scale, const void* zero, const void* bias,
                 void* y, int M, int N, int K, int bits, int group, long long ldx, long long ldy,
                 void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return -1;
-  const int per_lane = bits == 8 ? 16 : 32;
   if (bits != 8 && bits != 4) return -2;
-  if (K % (per_lane) || (ldx & 7)) return -3;
-  if (group > 0 && (K % group || group % per_lane)) return -4;
-  const int grid = (N + 7) / 8;
+  if (K % 16 || (ldx & 7)) return -3;
+  if (group > 0 && (K % group || group % 16)) return -4;
+  if (bits == 4 && group <= 0) return -4;
   auto st = static_cast<cudaStream_t>(stream);
-  if (bits == 8)
-    wq_gemv_kernel<8><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (const uint8_t*)w,
-                                            (const __nv_bfloat16*)scale, (const __nv_bfloat16*)zero,
-                                            (const __nv_bfloat16*)bias, (__nv_bfloat16*)y, M, N, K,
-                                            group, ldx, ldy);
-  else
-    wq_gemv_kernel<4><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (const uint8_t*)w,
-                                            (const __nv_bfloat16*)scale, (const __nv_bfloat16*)zero,
-                                            (const __nv_bfloat16*)bias, (__nv_bfloat16*)y, M, N, K,
-                                            group, ldx, ldy);
+  const int n_groups = (N + kGemvCols - 1) / kGemvCols;
+  int grid = (n_groups + 7) / 8;
+  const int cap = sm_count() * 4;
+  if (grid > cap) grid = cap;
+  for (int m0 = 0; m0 < M; m0 += 8) {  // 8 rows of x per launch
+    const __nv_bfloat16* xs = (const __nv_bfloat16*)x + (size_t)m0 * ldx;
+    __nv_bfloat16* ys = (__nv_bfloat16*)y + (size_t)m0 * ldy;
+    const int rows = M - m0 < 8 ? M - m0 : 8;
+    if (bits == 8)
+      wq_gemv_kernel<8><<<grid, 256, 0, st>>>(xs, (const uint8_t*)w, (const __nv_bfloat16*)scale,
+                                              (const __nv_bfloat16*)zero, (const __nv_bfloat16*)bias, ys, rows, N,
+                                              K, group, ldx, ldy);
+    else
+      wq_gemv_kernel<4><<<grid, 256, 0, st>>>(xs, (const uint8_t*)w, (const __nv_bfloat16*)scale,
+                                              (const __nv_bfloat16*)zero, (const __nv_bfloat16*)bias, ys, rows, N,
+                                              K, group, ldx, ldy);
+  }
   return (int)cudaGetLastError();
 }
 

@@ -116,9 +116,8 @@ def weight_only_linear(x: Tensor, q: Tensor, scale: Tensor, zero: Optional[Tenso
     K = x.shape[-1]
     x2 = x.reshape(-1, K)
     M, N = x2.shape[0], q.shape[0]
-    per_lane = 16 if bits == 8 else 32
-    if (use_native(x2, q) and x2.dtype == torch.bfloat16 and M <= 16 and K % per_lane == 0
-            and (group_size <= 0 or group_size % per_lane == 0)):
+    if (use_native(x2, q) and x2.dtype == torch.bfloat16 and M <= 16 and K % 16 == 0
+            and (group_size % 16 == 0 if group_size > 0 else bits == 8)):
         if x2.stride(1) != 1 or x2.stride(0) % 8:
             x2 = x2.contiguous()
         y = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
