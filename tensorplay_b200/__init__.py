@@ -50,7 +50,7 @@ _LAZY_OWN = {"distributed", "utils", "models", "parallel", "cuda", "profiler", "
              "multiprocessing", "testing", "quantization", "metrics", "snn", "library"}
 _LAZY_TORCH = {"linalg", "fft", "special", "sparse", "distributions", "func", "futures", "hub", "onnx",
                "masked", "nested", "monitor", "backends", "accelerator", "export", "fx", "random",
-               "signal", "overrides", "package", "storage", "types", "jit"}
+               "signal", "overrides", "package", "storage", "types", "jit", "_numpy"}
 
 
 def __getattr__(name):

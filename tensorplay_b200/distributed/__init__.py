@@ -27,7 +27,11 @@ reduce_scatter_single = reduce_scatter_tensor
 
 _LAZY = {"ddp", "fsdp", "device_mesh", "pipelining", "tensor", "checkpoint", "elastic", "run", "launcher",
          "flight_recorder", "watchdog", "_symmetric_memory", "_token_switch", "algorithms", "optim",
-         "rendezvous", "debug"}
+         "rendezvous", "debug", "_tools"}
+# the star import above also copied torch's sub-modules of these names; ours must win
+for _n in _LAZY:
+    globals().pop(_n, None)
+del _n
 
 
 def __getattr__(name):

@@ -78,3 +78,23 @@ def test_flight_recorder_dump_and_analyze(tmp_path):
     rep = fr.analyze(paths)
     assert rep["mismatch"]["index"] == 1 and rep["behind"] == [1]
     assert json.load(open(paths[0]))["entries"][0]["op"] == "all_gather"
+
+
+def test_debug_server_and_package_surface():
+    import json
+    import urllib.request
+
+    import tensorplay_b200 as tp
+    d = tp.distributed
+    # own sub-packages win over torch's modules of the same name
+    assert d.algorithms.__name__.startswith("tensorplay_b200") and d.optim.__name__.startswith("tensorplay_b200")
+    assert d.elastic.LocalElasticAgent is d.launcher.LocalElasticAgent
+    port = d.debug.start_debug_server(0)
+    try:
+        root = json.loads(urllib.request.urlopen(f"http://127.0.0.1:{port}/", timeout=5).read())
+        assert "/stacks" in root["endpoints"]
+        stacks = urllib.request.urlopen(f"http://127.0.0.1:{port}/stacks", timeout=5).read().decode()
+        assert "MainThread" in stacks and "test_debug_server_and_package_surface" in stacks
+        json.loads(urllib.request.urlopen(f"http://127.0.0.1:{port}/flight", timeout=5).read())
+    finally:
+        d.debug.stop_debug_server()
