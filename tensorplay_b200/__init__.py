@@ -62,6 +62,11 @@ def __getattr__(name):
         mod = _importlib.import_module(f"torch.{name}")
         globals()[name] = mod
         return mod
+    if name in ("vision", "audio"):
+        # the domain packs resolve to torchvision / torchaudio when they are installed
+        mod = _importlib.import_module("torchvision" if name == "vision" else "torchaudio")
+        globals()[name] = mod
+        return mod
     if name == "graph":
         return _importlib.import_module("torch.fx")
     return getattr(_torch, name)

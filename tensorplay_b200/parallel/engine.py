@@ -168,7 +168,8 @@ class FSDPEngine:
                  group: Optional[dist.ProcessGroup] = None, comm: str = "auto",
                  activation_checkpointing: bool = True, max_grad_norm: Optional[float] = None,
                  unit_modules: Optional[Sequence[Sequence[nn.Module]]] = None,
-                 layer_args: Callable[[nn.Module, Tensor], tuple] = None, symm_extra_bytes: int = 1 << 30):
+                 layer_args: Callable[[nn.Module, Tensor], tuple] = None, symm_extra_bytes: int = 1 << 30,
+                 replicate_group: Optional[dist.ProcessGroup] = None):
         self.model = model
         self.cfg = optim
         self.group = group
@@ -179,6 +180,10 @@ class FSDPEngine:
         self.param_dtype = first.dtype
         self.checkpoint = activation_checkpointing
         self.max_grad_norm = max_grad_norm
+        # hybrid sharding (HSDP): parameters are sharded over `group` and replicated over
+        # `replicate_group`; the reduced gradient shards are averaged over the replicas before the update
+        self.replicate_group = replicate_group
+        self.two_phase = max_grad_norm is not None or replicate_group is not None
         self.step_count = 0
         self.cuda = self.device.type == "cuda"
         if comm == "auto":
@@ -416,7 +421,7 @@ class FSDPEngine:
             import contextlib
             ctx = contextlib.nullcontext()
         with ctx:
-            if self.max_grad_norm is not None:
+            if self.two_phase:
                 self._reduce_only(u, g)
             elif self.world == 1:
                 ops.adamw_flat_(u.master, u.exp_avg, u.exp_avg_sq, g, u.shard, **self._adam_kwargs())
@@ -432,7 +437,7 @@ class FSDPEngine:
                 else:
                     dist.reduce_scatter_tensor(gs, g, op=dist.ReduceOp.AVG, group=self.group)
                 ops.adamw_flat_(u.master, u.exp_avg, u.exp_avg_sq, gs, u.shard, **self._adam_kwargs())
-            if u.local is not None and self.max_grad_norm is not None:
+            if u.local is not None and self.two_phase:
                 lu = u.local
                 if lu.red is None:
                     lu.red = torch.empty(lu.padded, dtype=torch.float32, device=self.device)
@@ -494,15 +499,33 @@ class FSDPEngine:
             import contextlib
             ctx = contextlib.nullcontext()
         with ctx:
-            if self.world > 1:
-                dist.all_reduce(self.sumsq, group=self.group)
-            ops.clip_coef_(self.sumsq, float(self.max_grad_norm), self.clip_coef, self.grad_norm)
+            if self.replicate_group is not None:
+                # average the reduced shards over the replicas, then take the norm of the result
+                r = dist.get_world_size(self.replicate_group)
+                self.sumsq.zero_()
+                for u in self.units:
+                    if u.local is not None:
+                        raise NotImplementedError("expert-parallel parameters are not supported with a replicate group")
+                    if u.red.dtype == torch.float32 or u.red.device.type == "cuda":
+                        dist.all_reduce(u.red, group=self.replicate_group)
+                        u.red.div_(r)
+                    else:
+                        tmp = u.red.float()
+                        dist.all_reduce(tmp, group=self.replicate_group)
+                        u.red.copy_(tmp.div_(r))
+                    ops.sumsq_(u.red, self.sumsq)
+            clip = None
+            if self.max_grad_norm is not None:
+                if self.world > 1:
+                    dist.all_reduce(self.sumsq, group=self.group)
+                ops.clip_coef_(self.sumsq, float(self.max_grad_norm), self.clip_coef, self.grad_norm)
+                clip = self.clip_coef
             kw = self._adam_kwargs()
             for u in self.units:
                 for t in (u, u.local):
                     if t is None or t.red is None:
                         continue
-                    ops.adamw_flat_(t.master, t.exp_avg, t.exp_avg_sq, t.red, t.shard, clip_coef=self.clip_coef, **kw)
+                    ops.adamw_flat_(t.master, t.exp_avg, t.exp_avg_sq, t.red, t.shard, clip_coef=clip, **kw)
                     if self.cuda:
                         ev = torch.cuda.Event()
                         ev.record(stream)
@@ -529,7 +552,7 @@ class FSDPEngine:
             x = _UnitFn.apply(self, 1 + i, layer, self.checkpoint, 1, x, *extra)
         loss = _UnitFn.apply(self, len(self.units) - 1, lambda h, t: m.head(h, t), False, 1, x, targets)
         loss.backward()
-        if self.max_grad_norm is not None:
+        if self.two_phase:
             self._clipped_update()
         return loss.detach()
 

@@ -151,3 +151,41 @@ def test_engine_checkpoint_resume_and_reshard(tmp_path):
         for got in (resumed2, resumed1):
             d_ = (torch.from_numpy(got[n]) - p.detach()).abs().max().item()
             assert d_ < 3e-4, (n, d_)
+
+
+def _hsdp_worker(rank, world):
+    """2 x 2 hybrid sharding: shard over pairs {0,1}, {2,3}; replicate over {0,2}, {1,3}."""
+    import torch.distributed as dist
+    from tensorplay_b200.models.llama import Llama, LlamaConfig
+    from tensorplay_b200.parallel import AdamWConfig, FSDPEngine
+
+    shard_groups = [dist.new_group([0, 1]), dist.new_group([2, 3])]
+    rep_groups = [dist.new_group([0, 2]), dist.new_group([1, 3])]
+    shard_g, rep_g = shard_groups[rank // 2], rep_groups[rank % 2]
+    torch.manual_seed(0)
+    cfg = LlamaConfig.tiny(hidden_size=64, num_heads=4, num_kv_heads=2, head_dim=16, ffn_size=128,
+                           vocab_size=128, num_layers=2)
+    base = Llama(cfg)
+    base.reset_parameters(0)
+    g = torch.Generator().manual_seed(5)
+    toks = torch.randint(0, cfg.vocab_size, (world, 2, 16), generator=g)
+    ocfg = AdamWConfig(lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    eng = FSDPEngine(copy.deepcopy(base), ocfg, group=shard_g, comm="torch", replicate_group=rep_g)
+    for _ in range(3):
+        eng.step(toks[rank], toks[rank])
+    state = eng.gather_full_state()
+    ref = copy.deepcopy(base)
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    for _ in range(3):
+        opt.zero_grad()
+        ref(toks.flatten(0, 1), toks.flatten(0, 1)).backward()
+        opt.step()
+    for n, p in ref.named_parameters():
+        d = (state[n] - p.detach()).abs().max().item()
+        assert d < 2e-4, (n, d)
+    dist.barrier()
+    return True
+
+
+def test_engine_hybrid_sharding_2x2():
+    assert all(run_ranks(_hsdp_worker, 4))
