@@ -750,6 +750,14 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
   return (int)cudaGetLastError();
 }
 
+// Tile width: 256 columns, except when that leaves more than half of the SMs without a tile
+// (small-M decode shapes): then 128-column tiles double the number of CTAs that stream weights.
+static int pick_block_n(int M, int N) {
+  if (N <= 128) return 128;
+  const long long tiles256 = (long long)((M + kBlockM - 1) / kBlockM) * ((N + 255) / 256);
+  return tiles256 * 2 <= sm_count() ? 128 : 256;
+}
+
 int gemm_bf16_dispatch(const void* A, const void* B, void* C, const void* bias, int M, int N,
                        int K, int lda, int ldb, int ldc, int a_mn, int b_mn, int out_f32,
                        int bias_f32, int accumulate, float alpha, const uint32_t* b_flags,
@@ -759,7 +767,7 @@ int gemm_bf16_dispatch(const void* A, const void* B, void* C, const void* bias, 
   if (K <= 0 || (lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) ||
       (reinterpret_cast<uintptr_t>(B) & 15))
     return -2;
-  const int block_n = (N > 128) ? 256 : 128;
+  const int block_n = pick_block_n(M, N);
   CUtensorMap ta, tb;
   int r;
   if (!a_mn) r = make_tmap_2d_bf16(&ta, A, K, M, lda, kBlockM);
@@ -880,7 +888,7 @@ extern "C" int tpb_gemm_rs(const void* A, const void* B, void* out, int M, int N
     f.rs_stage[r] = sv->peer[r] + stage_off;
     f.rs_cnt[r] = reinterpret_cast<uint32_t*>(sv->peer[r] + pad_off) + cnt_slot;
   }
-  const int block_n = N > 128 ? 256 : 128;
+  const int block_n = tpb::pick_block_n(M, N);
   // arrivals this rank expects from each source per call: one per (N tile, 32-row block that
   // overlaps this rank's rows)
   const int my0 = rank * f.rs_rows_per_rank, my1 = my0 + f.rs_rows_per_rank - 1;
