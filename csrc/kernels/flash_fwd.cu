@@ -36,6 +36,10 @@ struct AttnFwdParams {
   float* lse;  // [B, Hq, lse_stride]
   int lse_stride;
   const int* kv_len;  // optional device word: number of valid keys (<= Tk), for graph-replayed decode
+  // split-KV (decode): CTA (x = tile * n_splits + split) handles KV blocks [split * blocks_per_split, ...)
+  // and writes a partial O / LSE at split * o_split_stride / lse_split_stride (merged by a second kernel)
+  int n_splits, blocks_per_split;
+  long long o_split_stride, lse_split_stride;
   uint32_t* status;
   unsigned long long wait_ns;
 };
@@ -132,7 +136,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int qb = p.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;  // heavy tiles first
+  const int n_splits = p.n_splits > 1 ? p.n_splits : 1;
+  const int split = blockIdx.x % n_splits;
+  const int q_tiles = gridDim.x / n_splits;
+  const int qt = blockIdx.x / n_splits;
+  const int qb = p.causal ? (q_tiles - 1 - qt) : qt;  // heavy tiles first
+  const int j0 = split * p.blocks_per_split;  // first KV block of this CTA (0 without splitting)
   const int h = blockIdx.y;
   const int b = blockIdx.z;
   const int hk = h / (p.Hq / p.Hkv);
@@ -149,6 +158,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       n = last_key < 0 ? 0 : min(n, last_key / kBlockKV + 1);
     }
     if (q0 + g * kBlockQ >= p.Tq) n = 0;  // tile past the end of the sequence
+    if (n_splits > 1) n = max(0, min(n - j0, p.blocks_per_split));  // this split's share
     nkv_t[g] = n;
     nkv = max(nkv, n);
   }
@@ -200,7 +210,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
         for (int c = 0; c < L::kChunks; ++c)
           tma_load_4d(smem + L::kKOff + slot * L::kKBytes + c * (kBlockKV * 128), tm, &kv_full[slot],
-                      c * 64, hk, j * kBlockKV, b);
+                      c * 64, hk, (j0 + j) * kBlockKV, b);
       }
     }
   } else if (warp == 1) {
@@ -286,7 +296,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int j = 0; j < my_nkv; ++j) {
       if (!mbar_wait_warp(&s_full[g], j & 1, wc, 8)) { ok = false; break; }
       tc_fence_after_sync();
-      const int k0 = j * kBlockKV;
+      const int k0 = (j0 + j) * kBlockKV;
       const bool need_mask = (p.causal && (k0 + kBlockKV - 1 > q0 + g * kBlockQ + p.kv_offset)) ||
                              (k0 + kBlockKV > Tk);
       // the whole S row (128 fp32) in one TMEM round trip
@@ -336,7 +346,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (ok) {
       tc_fence_after_sync();
       const float inv = (my_nkv > 0 && l > 0.f) ? 1.f / l : 0.f;
-      __nv_bfloat16* orow = p.O + (long long)b * p.o_batch_stride + (long long)qi * p.o_tok_stride +
+      __nv_bfloat16* orow = p.O + split * p.o_split_stride + (long long)b * p.o_batch_stride + (long long)qi * p.o_tok_stride +
                             (long long)h * p.o_head_stride;
 #pragma unroll 1
       for (int c = 0; c < D / 32; ++c) {
@@ -370,7 +380,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       if (qi < p.Tq && p.lse) {
         float lse = (my_nkv > 0 && l > 0.f) ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
-        p.lse[((long long)b * p.Hq + h) * p.lse_stride + qi] = lse;
+        p.lse[split * p.lse_split_stride + ((long long)b * p.Hq + h) * p.lse_stride + qi] = lse;
       }
     }
   }
@@ -444,9 +454,47 @@ static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid((p.Tq + kTilesQ * kBlockQ - 1) / (kTilesQ * kBlockQ), p.Hq, p.B);
+  dim3 grid(((p.Tq + kTilesQ * kBlockQ - 1) / (kTilesQ * kBlockQ)) * (p.n_splits > 1 ? p.n_splits : 1), p.Hq, p.B);
   kern<<<grid, kAttnThreads, L::kTotal, stream>>>(tq, tk, tv, p);
   return (int)cudaGetLastError();
+}
+
+// Merge of split-KV partials: out[b, t, h, :] = sum_s w_s * part[s][b, t, h, :] with
+// w_s = exp(lse_s - lse), lse = log sum_s exp(lse_s). One warp per (b, t, h).
+__global__ void __launch_bounds__(256)
+attn_split_merge_kernel(const __nv_bfloat16* __restrict__ part, const float* __restrict__ lse_part,
+                        __nv_bfloat16* __restrict__ out, float* __restrict__ lse_out, int n_splits, int B,
+                        int T, int H, int D, long long part_split_stride, long long lse_split_stride,
+                        int lse_stride, long long o_tok, long long o_head, long long o_batch) {
+  const long long w = ((long long)blockIdx.x * 256 + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= (long long)B * T * H) return;
+  const int h = (int)(w % H);
+  const long long bt = w / H;
+  const int t = (int)(bt % T);
+  const int b = (int)(bt / T);
+  const long long li = ((long long)b * H + h) * lse_stride + t;
+  float mx = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, lse_part[s * lse_split_stride + li]);
+  float den = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float l = lse_part[s * lse_split_stride + li];
+    den += (l == -INFINITY) ? 0.f : __expf(l - mx);
+  }
+  const long long row = ((long long)(b * (long long)T + t) * H + h) * D;  // partials are contiguous [B, T, H, D]
+  for (int d = lane * 2; d < D; d += 64) {
+    float2 acc = make_float2(0.f, 0.f);
+    for (int s = 0; s < n_splits; ++s) {
+      const float l = lse_part[s * lse_split_stride + li];
+      if (l == -INFINITY) continue;
+      const float wgt = __expf(l - mx) / den;
+      const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(part + s * part_split_stride + row + d));
+      acc.x += wgt * v.x;
+      acc.y += wgt * v.y;
+    }
+    *reinterpret_cast<__nv_bfloat162*>(out + b * o_batch + t * o_tok + h * o_head + d) = __floats2bfloat162_rn(acc.x, acc.y);
+  }
+  if (lane == 0 && lse_out) lse_out[li] = (den > 0.f) ? mx + __logf(den) : -INFINITY;
 }
 
 }  // namespace tpb
@@ -461,7 +509,8 @@ extern "C" int tpb_flash_fwd(const void* q, const void* k, const void* v, void* 
                              long long k_head, long long k_batch, long long v_tok,
                              long long v_head, long long v_batch, long long o_tok,
                              long long o_head, long long o_batch, int lse_stride, int causal,
-                             float scale, uint32_t* status, void* stream, const int* kv_len) {
+                             float scale, uint32_t* status, void* stream, const int* kv_len, int n_splits,
+                             long long o_split_stride, long long lse_split_stride) {
   if (B <= 0 || Tq <= 0 || Hq <= 0) return 0;
   if ((D != 64 && D != 128) || Hkv <= 0 || Hq % Hkv || Tk <= 0) return -2;
   if ((q_tok | q_head | q_batch | k_tok | k_head | k_batch | v_tok | v_head | v_batch | o_tok |
@@ -481,6 +530,29 @@ extern "C" int tpb_flash_fwd(const void* q, const void* k, const void* v, void* 
   p.scale_log2e = scale * 1.4426950408889634f;
   p.O = (__nv_bfloat16*)o; p.o_tok_stride = o_tok; p.o_head_stride = o_head;
   p.o_batch_stride = o_batch; p.lse = lse; p.lse_stride = lse_stride > 0 ? lse_stride : Tq; p.status = status; p.wait_ns = kDefaultWaitNs; p.kv_len = kv_len;
+  p.n_splits = n_splits > 1 ? n_splits : 1;
+  {
+    const int blocks = (Tk + kBlockKV - 1) / kBlockKV;
+    p.blocks_per_split = (blocks + p.n_splits - 1) / p.n_splits;
+  }
+  p.o_split_stride = o_split_stride; p.lse_split_stride = lse_split_stride;
+  if (p.n_splits > 1 && causal) return -3;  // splitting is for decode (one query tile, no causal mask)
   if (D == 128) return launch_fwd<128>(tq, tk, tv, p, (cudaStream_t)stream);
   return launch_fwd<64>(tq, tk, tv, p, (cudaStream_t)stream);
+}
+
+// Merge the partials of a split-KV forward (see tpb_flash_fwd): part [n_splits][B, T, H, D] bf16
+// contiguous, lse_part [n_splits][B, H, lse_stride]; out by strides, lse_out [B, H, lse_stride] or null.
+extern "C" int tpb_attn_split_merge(const void* part, const float* lse_part, void* out, float* lse_out,
+                                    int n_splits, int B, int T, int H, int D, long long part_split_stride,
+                                    long long lse_split_stride, int lse_stride, long long o_tok,
+                                    long long o_head, long long o_batch, void* stream) {
+  if (B <= 0 || T <= 0 || H <= 0 || n_splits <= 0) return 0;
+  if (D & 1) return -1;
+  const long long warps = (long long)B * T * H;
+  const int grid = (int)((warps * 32 + 255) / 256);
+  attn_split_merge_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(part), lse_part, static_cast<__nv_bfloat16*>(out), lse_out, n_splits, B, T,
+      H, D, part_split_stride, lse_split_stride, lse_stride, o_tok, o_head, o_batch);
+  return (int)cudaGetLastError();
 }

@@ -103,7 +103,8 @@ int tpb_flash_fwd(const void* q, const void* k, const void* v, void* o, float* l
                   long long q_batch, long long k_tok, long long k_head, long long k_batch,
                   long long v_tok, long long v_head, long long v_batch, long long o_tok,
                   long long o_head, long long o_batch, int lse_stride, int causal, float scale,
-                  uint32_t* status, void* stream, const int* kv_len);
+                  uint32_t* status, void* stream, const int* kv_len, int n_splits,
+                  long long o_split_stride, long long lse_split_stride);
 int tpb_flash_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o,
                   const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int Tq,
                   int Tk, int Hq, int Hkv, int D, long long q_tok, long long q_head,

@@ -38,7 +38,8 @@ _KERNEL_SIGS = {
     "tpb_gelu_bwd": [P, P, P, LL, I, P],
     "tpb_cross_entropy": [P, P, P, P, P, LL, I, LL, LL, F, P],
     "tpb_cross_entropy_bwd": [P, P, P, P, P, P, P, LL, I, LL, LL, P],
-    "tpb_flash_fwd": [P, P, P, P, P, I, I, I, I, I, I] + [LL] * 12 + [I, I, F, P, P, P],
+    "tpb_flash_fwd": [P, P, P, P, P, I, I, I, I, I, I] + [LL] * 12 + [I, I, F, P, P, P, I, LL, LL],
+    "tpb_attn_split_merge": [P, P, P, P, I, I, I, I, I, LL, LL, I, LL, LL, LL, P],
     "tpb_flash_bwd": [P] * 10 + [I, I, I, I, I, I] + [LL] * 21 + [I, I, F, P, P],
     "tpb_grouped_workspace_ints": [I, I],
     "tpb_grouped_gemm": [P, P, P, P, I, I, I, I, I, I, I, I, P, P, P],

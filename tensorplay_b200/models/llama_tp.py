@@ -92,8 +92,11 @@ class LlamaTPBlock(nn.Module):
         ops.kv_append(self.k_cache[:B].permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), pos32)
         ops.kv_append(self.v_cache[:B].permute(0, 2, 1, 3), v.permute(0, 2, 1, 3), pos32)
         G = self.hq // self.hkv
+        # few CTAs per (sequence, kv head) would walk the whole cache serially: split the keys
+        cap_blocks = (self.k_cache.shape[1] + 127) // 128
+        n_splits = max(1, min(8, cap_blocks // 4, (2 * 148) // max(1, B * self.hkv)))
         o, _ = flash_fwd(q.reshape(B, self.hkv, G, D).transpose(1, 2), self.k_cache[:B], self.v_cache[:B],
-                         False, 1.0 / math.sqrt(D), kv_len=kv_len)
+                         False, 1.0 / math.sqrt(D), kv_len=kv_len, n_splits=n_splits)
         o = o.transpose(1, 2).reshape(B, self.hq * D)
         x_local = x_local + tp.linear_reduce_scatter(o, self.wo)
         h = ops.rms_norm(x_local, self.ffn_norm, cfg.rms_eps)

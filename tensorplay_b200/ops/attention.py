@@ -43,22 +43,37 @@ def attention_reference(q, k, v, causal: bool = True, scale: Optional[float] = N
     return o.permute(0, 2, 1, 3).to(q.dtype)
 
 
-def flash_fwd(q, k, v, causal: bool, scale: float, kv_len: Optional[torch.Tensor] = None):
+def flash_fwd(q, k, v, causal: bool, scale: float, kv_len: Optional[torch.Tensor] = None, n_splits: int = 1):
     """Forward kernel. ``kv_len`` (int32 device scalar) limits the keys to the first ``kv_len`` of
     ``k``/``v`` without a host-side shape change, so that a decode step over a preallocated cache
-    can be captured in a CUDA graph."""
+    can be captured in a CUDA graph. ``n_splits > 1`` (non-causal, i.e. decode) spreads the keys of
+    every (batch, head) over that many CTAs and merges the partial outputs by their LSE."""
     B, Tq, Hq, D = q.shape
     Tk, Hkv = k.shape[1], k.shape[2]
     o = torch.empty((B, Tq, Hq, D), dtype=q.dtype, device=q.device)
     # rows padded to the backward kernels' 64-query vector loads
-    lse = torch.empty((B, Hq, (Tq + 127) // 128 * 128), dtype=torch.float32, device=q.device)
+    lse_stride = (Tq + 127) // 128 * 128
+    lse = torch.empty((B, Hq, lse_stride), dtype=torch.float32, device=q.device)
+    n_splits = max(1, min(int(n_splits), (Tk + 127) // 128)) if not causal else 1
+    if n_splits > 1:
+        part = torch.empty((n_splits, B, Tq, Hq, D), dtype=q.dtype, device=q.device)
+        lse_part = torch.empty((n_splits, B, Hq, lse_stride), dtype=torch.float32, device=q.device)
+        dst, dst_lse = part[0], lse_part
+        o_split, lse_split = part.stride(0), lse_part.stride(0)
+    else:
+        dst, dst_lse, o_split, lse_split = o, lse, 0, 0
     code = lib().tpb_flash_fwd(
-        q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), B, Tq, Tk, Hq, Hkv,
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), dst.data_ptr(), dst_lse.data_ptr(), B, Tq, Tk, Hq, Hkv,
         D, q.stride(1), q.stride(2), q.stride(0), k.stride(1), k.stride(2), k.stride(0),
-        v.stride(1), v.stride(2), v.stride(0), o.stride(1), o.stride(2), o.stride(0), lse.shape[2],
+        v.stride(1), v.stride(2), v.stride(0), dst.stride(1), dst.stride(2), dst.stride(0), lse_stride,
         int(causal), float(scale), status_word(q.device).data_ptr(), stream_ptr(),
-        None if kv_len is None else kv_len.data_ptr())
+        None if kv_len is None else kv_len.data_ptr(), n_splits, o_split, lse_split)
     _native.check(code, "tpb_flash_fwd")
+    if n_splits > 1:
+        code = lib().tpb_attn_split_merge(part.data_ptr(), lse_part.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                                          n_splits, B, Tq, Hq, D, o_split, lse_split, lse_stride, o.stride(1),
+                                          o.stride(2), o.stride(0), stream_ptr())
+        _native.check(code, "tpb_attn_split_merge")
     return o, lse
 
 

@@ -69,3 +69,22 @@ def test_flash_fused_qkv_strides():
     O.check_status()
     ref = attention_reference(q.float(), k.float(), v.float(), True)
     assert _rel(o, ref) < 1e-2
+
+
+@pytest.mark.parametrize("n_splits", [1, 3, 8])
+def test_decode_attention_device_length_and_split_kv(n_splits):
+    """Decode form: few query rows per (batch, kv head), keys limited by a device-side length,
+    optionally split over several CTAs and merged by LSE."""
+    from tensorplay_b200.ops.attention import flash_fwd
+    torch.manual_seed(5)
+    B, G, Hkv, D, cap, used = 3, 4, 2, 128, 1024, 700
+    q = torch.randn(B, G, Hkv, D, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(B, cap, Hkv, D, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(B, cap, Hkv, D, device=DEV, dtype=torch.bfloat16)
+    kv_len = torch.tensor([used], device=DEV, dtype=torch.int32)
+    o, lse = flash_fwd(q, k, v, False, 1.0 / D ** 0.5, kv_len=kv_len, n_splits=n_splits)
+    O.check_status()
+    ref = attention_reference(q.float(), k[:, :used].float(), v[:, :used].float(), False)
+    assert _rel(o, ref) < 1e-2
+    s = torch.einsum("bghd,bthd->bhgt", q.float(), k[:, :used].float()) / D ** 0.5
+    torch.testing.assert_close(lse[:, :, :G], torch.logsumexp(s, -1), rtol=1e-2, atol=2e-2)

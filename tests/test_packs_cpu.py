@@ -60,3 +60,30 @@ def test_dtensor_and_cp_surface():
     q = torch.randn(1, 8, 2, 16)
     out = ring_attention(q, q, q, causal=True)  # single process: plain attention
     assert out.shape == q.shape
+
+
+def test_hot_ops_registered_as_custom_operators():
+    import tensorplay_b200.ops.registry  # noqa: F401  (registers torch.ops.tpb.*)
+    x = torch.randn(4, 32, requires_grad=True)
+    w = torch.rand(32, requires_grad=True)
+    wl = torch.randn(16, 32, requires_grad=True)
+    # eager results and gradients equal the plain expressions
+    y = torch.ops.tpb.rms_norm(x, w, 1e-6)
+    ref = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6) * w
+    torch.testing.assert_close(y, ref)
+    gx, gw = torch.autograd.grad(y.sum(), (x, w))
+    rx, rw = torch.autograd.grad(ref.sum(), (x, w))
+    torch.testing.assert_close(gx, rx)
+    torch.testing.assert_close(gw, rw)
+    z = torch.ops.tpb.linear(x, wl, None)
+    torch.testing.assert_close(z, x @ wl.t())
+    # the dispatcher's own checks: schema, fake-tensor shapes, autograd registration
+    torch.library.opcheck(torch.ops.tpb.rms_norm.default, (x.detach(), w.detach(), 1e-6))
+    torch.library.opcheck(torch.ops.tpb.swiglu.default, (torch.randn(3, 8), torch.randn(3, 8)))
+    q = torch.randn(1, 8, 2, 16)
+    torch.library.opcheck(torch.ops.tpb.attention.default, (q, q, q, True, 0.25))
+    # shape propagation without running a kernel
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    with FakeTensorMode():
+        out = torch.ops.tpb.linear(torch.empty(5, 7, 32), torch.empty(16, 32), None)
+        assert tuple(out.shape) == (5, 7, 16)
