@@ -7,8 +7,8 @@ from . import cache, functional, generation  # noqa: F401
 from .cache import (Cache, DynamicCache, LinearStateCache, PagedCache, QuantizedCache,
                     SlidingWindowCache, StaticCache)
 from .generation import generate, sample, top_k_top_p_filtering
-from .modules import (GroupedQueryAttention, LayerNorm, Linear, RMSNorm, RotaryEmbedding, SwiGLUMLP,
-                      TransformerBlock, apply_rotary_emb)
+from .modules import (GatedDeltaNet, GroupedQueryAttention, LayerNorm, Linear, MultiheadLatentAttention, RMSNorm,
+                      RotaryEmbedding, SwiGLUMLP, TransformerBlock, apply_rotary_emb, gated_delta_rule)
 from . import parallel  # noqa: F401,E402
 
 

@@ -1,5 +1,7 @@
 from .llm import (GroupedQueryAttention, LayerNorm, Linear, RMSNorm, RotaryEmbedding, SwiGLUMLP,
                   TransformerBlock, apply_rotary_emb)
 
+from .mixers import GatedDeltaNet, MultiheadLatentAttention, gated_delta_rule
+
 __all__ = ["GroupedQueryAttention", "LayerNorm", "Linear", "RMSNorm", "RotaryEmbedding", "SwiGLUMLP",
-           "TransformerBlock", "apply_rotary_emb"]
+           "TransformerBlock", "apply_rotary_emb", "MultiheadLatentAttention", "GatedDeltaNet", "gated_delta_rule"]

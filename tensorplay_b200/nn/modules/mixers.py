@@ -1,0 +1,184 @@
+"""Sequence mixers beyond grouped-query attention: multi-head latent attention (compressed KV
+cache) and the gated delta rule (linear-time recurrent mixer).
+
+API after tensorplay/nn/modules/latent_attention.py:30-224 (``MultiheadLatentAttention``) and
+tensorplay/nn/modules/gated_delta.py (``GatedDeltaNet``); the math follows the published
+formulations (DeepSeek-V2 MLA; gated DeltaNet), written for this package's ops: attention runs on
+the flash kernels whenever the head width allows, everything else is plain tensor algebra.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+from torch import Tensor
+from torch.nn import Module
+
+from ... import ops as _ops
+from .llm import Linear, RMSNorm, RotaryEmbedding
+
+
+class MultiheadLatentAttention(Module):
+    """Causal attention whose cache holds one compressed latent (``kv_lora_rank`` wide) plus one
+    rotary key (``qk_rope_head_dim`` wide) per token instead of per-head keys and values.
+
+    Queries and keys have a content part (``qk_nope_head_dim``, no position) and a rotary part
+    (``qk_rope_head_dim``; the rotary key is shared by all heads). Keys and values are
+    up-projected from the cached latent on every call.
+    """
+
+    def __init__(self, embed_dim: int, num_heads: int, kv_lora_rank: int, qk_nope_head_dim: int,
+                 qk_rope_head_dim: int, v_head_dim: Optional[int] = None, q_lora_rank: Optional[int] = None,
+                 dropout: float = 0.0, bias: bool = False, rope_base: float = 10000.0,
+                 rope_interleaved: bool = False, layer_idx: int = 0, device=None, dtype=None) -> None:
+        kw = {"device": device, "dtype": dtype}
+        super().__init__()
+        if embed_dim % num_heads:
+            raise ValueError(f"embed_dim ({embed_dim}) must be divisible by num_heads ({num_heads})")
+        if qk_rope_head_dim % 2:
+            raise ValueError(f"qk_rope_head_dim must be even for rotary embedding, got {qk_rope_head_dim}")
+        v_head_dim = qk_nope_head_dim if v_head_dim is None else v_head_dim
+        self.embed_dim, self.num_heads, self.kv_lora_rank = embed_dim, num_heads, kv_lora_rank
+        self.qk_nope_head_dim, self.qk_rope_head_dim = qk_nope_head_dim, qk_rope_head_dim
+        self.qk_head_dim = qk_nope_head_dim + qk_rope_head_dim
+        self.v_head_dim, self.q_lora_rank = v_head_dim, q_lora_rank
+        self.dropout, self.layer_idx = dropout, layer_idx
+        self.scaling = self.qk_head_dim ** -0.5
+        if q_lora_rank is None:
+            self.q_proj = Linear(embed_dim, num_heads * self.qk_head_dim, bias=bias, **kw)
+            self.q_a_proj = self.q_a_layernorm = self.q_b_proj = None
+        else:
+            self.q_proj = None
+            self.q_a_proj = Linear(embed_dim, q_lora_rank, bias=bias, **kw)
+            self.q_a_layernorm = RMSNorm(q_lora_rank, **kw)
+            self.q_b_proj = Linear(q_lora_rank, num_heads * self.qk_head_dim, bias=False, **kw)
+        self.kv_a_proj_with_mqa = Linear(embed_dim, kv_lora_rank + qk_rope_head_dim, bias=bias, **kw)
+        self.kv_a_layernorm = RMSNorm(kv_lora_rank, **kw)
+        self.kv_b_proj = Linear(kv_lora_rank, num_heads * (qk_nope_head_dim + v_head_dim), bias=False, **kw)
+        self.o_proj = Linear(num_heads * v_head_dim, embed_dim, bias=bias, **kw)
+        self.rope = RotaryEmbedding(qk_rope_head_dim, base=rope_base, interleaved=rope_interleaved, device=device)
+
+    def forward(self, hidden_states: Tensor, position_ids: Optional[Tensor] = None, past_key_values=None) -> Tensor:
+        B, T, _ = hidden_states.shape
+        H, dn, dr, dv = self.num_heads, self.qk_nope_head_dim, self.qk_rope_head_dim, self.v_head_dim
+        offset = past_key_values.get_seq_length(self.layer_idx) if past_key_values is not None else 0
+        pos = position_ids
+        if pos is None:
+            pos = torch.arange(offset, offset + T, device=hidden_states.device).expand(B, T)
+        if self.q_proj is not None:
+            q = self.q_proj(hidden_states)
+        else:
+            q = self.q_b_proj(self.q_a_layernorm(self.q_a_proj(hidden_states)))
+        q = q.view(B, T, H, dn + dr)
+        q_nope, q_rot = q[..., :dn], q[..., dn:]
+        ckv = self.kv_a_proj_with_mqa(hidden_states)
+        latent, k_rot = self.kv_a_layernorm(ckv[..., : self.kv_lora_rank]), ckv[..., self.kv_lora_rank:]
+        cos, sin = self.rope.tables(int(pos.max().item()) + 1, hidden_states.device)
+        q_rot = _ops.apply_rope(q_rot.contiguous(), cos, sin, pos, self.rope.interleaved)
+        k_rot = _ops.apply_rope(k_rot.reshape(B, T, 1, dr).contiguous(), cos, sin, pos, self.rope.interleaved)
+        if past_key_values is not None:
+            # the cache keeps [B, 1, S, width] entries: latent as "key", rotary key as "value"
+            lat_c, rot_c = past_key_values.update(latent.unsqueeze(1), k_rot.transpose(1, 2), self.layer_idx)
+            latent, k_rot = lat_c.squeeze(1), rot_c.transpose(1, 2)
+        S = latent.shape[1]
+        kv = self.kv_b_proj(latent).view(B, S, H, dn + dv)
+        k = torch.cat((kv[..., :dn], k_rot.expand(B, S, H, dr)), dim=-1)
+        v = kv[..., dn:]
+        qf = torch.cat((q_nope, q_rot), dim=-1)
+        drop = self.dropout if self.training else 0.0
+        if drop == 0.0 and k.shape[-1] == v.shape[-1] and k.shape[-1] in (64, 128):
+            o = _ops.flash_attention(qf, k, v, causal=True, scale=self.scaling)
+        else:
+            # widths the flash kernels do not cover (q/k wider than v): SDPA with a bottom-right mask
+            i = torch.arange(T, device=qf.device).view(-1, 1) + (S - T)
+            mask = torch.arange(S, device=qf.device).view(1, -1) <= i
+            o = F.scaled_dot_product_attention(qf.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                               attn_mask=mask, dropout_p=drop, scale=self.scaling).transpose(1, 2)
+        return self.o_proj(o.reshape(B, T, H * dv))
+
+    def extra_repr(self) -> str:
+        return (f"embed_dim={self.embed_dim}, num_heads={self.num_heads}, kv_lora_rank={self.kv_lora_rank}, "
+                f"qk_nope_head_dim={self.qk_nope_head_dim}, qk_rope_head_dim={self.qk_rope_head_dim}, "
+                f"v_head_dim={self.v_head_dim}, q_lora_rank={self.q_lora_rank}")
+
+
+def gated_delta_rule(q: Tensor, k: Tensor, v: Tensor, g: Tensor, beta: Tensor,
+                     state: Optional[Tensor] = None) -> Tuple[Tensor, Tensor]:
+    """Gated delta rule, one step per token.
+
+    ``q, k``: [B, T, H, Dk] (keys L2-normalised by the caller), ``v``: [B, T, H, Dv], ``g``: [B, T, H]
+    log-decay (<= 0), ``beta``: [B, T, H] write strength in (0, 1); ``state``: [B, H, Dk, Dv].
+    Per token: ``S <- exp(g) * S``; ``S <- S + beta * k (v - S^T k)^T``; ``o = S^T q``.
+    Returns (o [B, T, H, Dv], final state).
+    """
+    B, T, H, Dk = k.shape
+    Dv = v.shape[-1]
+    S = torch.zeros(B, H, Dk, Dv, dtype=torch.float32, device=k.device) if state is None else state.float()
+    qf, kf, vf = q.float(), k.float(), v.float()
+    out = []
+    for t in range(T):
+        S = S * torch.exp(g[:, t].float())[..., None, None]
+        kt, vt = kf[:, t], vf[:, t]
+        pred = torch.einsum("bhkv,bhk->bhv", S, kt)
+        S = S + torch.einsum("bhk,bhv->bhkv", kt, (vt - pred) * beta[:, t].float()[..., None])
+        out.append(torch.einsum("bhkv,bhk->bhv", S, qf[:, t]))
+    return torch.stack(out, dim=1).to(v.dtype), S
+
+
+class GatedDeltaNet(Module):
+    """Linear-time token mixer: short causal depthwise convolutions on q / k / v, a decaying
+    matrix-valued state updated by the delta rule with a learned write strength, and a gated,
+    normalised read-out. ``past_key_values`` is a ``LinearStateCache`` (conv window + state)."""
+
+    def __init__(self, embed_dim: int, num_heads: int, head_dim: Optional[int] = None, expand_v: float = 2.0,
+                 conv_size: int = 4, layer_idx: int = 0, norm_eps: float = 1e-6, device=None, dtype=None) -> None:
+        kw = {"device": device, "dtype": dtype}
+        super().__init__()
+        head_dim = embed_dim // num_heads if head_dim is None else head_dim
+        self.embed_dim, self.num_heads, self.head_k_dim = embed_dim, num_heads, head_dim
+        self.head_v_dim = int(head_dim * expand_v)
+        self.conv_size, self.layer_idx = conv_size, layer_idx
+        kd, vd = num_heads * self.head_k_dim, num_heads * self.head_v_dim
+        self.q_proj = Linear(embed_dim, kd, bias=False, **kw)
+        self.k_proj = Linear(embed_dim, kd, bias=False, **kw)
+        self.v_proj = Linear(embed_dim, vd, bias=False, **kw)
+        self.a_proj = Linear(embed_dim, num_heads, bias=False, **kw)   # decay input
+        self.b_proj = Linear(embed_dim, num_heads, bias=False, **kw)   # write strength
+        self.g_proj = Linear(embed_dim, vd, bias=False, **kw)          # output gate
+        self.o_proj = Linear(vd, embed_dim, bias=False, **kw)
+        self.conv_weight = torch.nn.Parameter(torch.empty(2 * kd + vd, conv_size, **kw))
+        torch.nn.init.normal_(self.conv_weight, std=conv_size ** -0.5)
+        self.A_log = torch.nn.Parameter(torch.log(torch.empty(num_heads, **kw).uniform_(1.0, 16.0)))
+        self.dt_bias = torch.nn.Parameter(torch.zeros(num_heads, **kw))
+        self.o_norm = RMSNorm(self.head_v_dim, eps=norm_eps, **kw)
+
+    def _conv(self, x: Tensor, cache) -> Tensor:
+        """Causal depthwise convolution over time of ``x [B, T, C]`` followed by SiLU."""
+        xt = x.transpose(1, 2)  # [B, C, T]
+        if cache is not None:
+            full = cache.update_conv_state(self.layer_idx, xt, self.conv_size)
+            pad = self.conv_size - 1 - (full.shape[-1] - xt.shape[-1])
+        else:
+            full, pad = xt, self.conv_size - 1
+        full = F.pad(full, (max(pad, 0), 0))
+        y = F.conv1d(full, self.conv_weight.unsqueeze(1).to(full.dtype), groups=full.shape[1])
+        return F.silu(y[..., -xt.shape[-1]:]).transpose(1, 2)
+
+    def forward(self, hidden_states: Tensor, position_ids: Optional[Tensor] = None, past_key_values=None) -> Tensor:
+        B, T, _ = hidden_states.shape
+        H, dk, dv = self.num_heads, self.head_k_dim, self.head_v_dim
+        qkv = torch.cat((self.q_proj(hidden_states), self.k_proj(hidden_states), self.v_proj(hidden_states)), dim=-1)
+        qkv = self._conv(qkv, past_key_values)
+        q, k, v = qkv.split((H * dk, H * dk, H * dv), dim=-1)
+        q = F.normalize(q.view(B, T, H, dk).float(), dim=-1) * dk ** -0.5
+        k = F.normalize(k.view(B, T, H, dk).float(), dim=-1)
+        v = v.reshape(B, T, H, dv)
+        beta = torch.sigmoid(self.b_proj(hidden_states).float())
+        g = -torch.exp(self.A_log.float()) * F.softplus(self.a_proj(hidden_states).float() + self.dt_bias.float())
+        state = past_key_values.recurrent_states.get(self.layer_idx) if past_key_values is not None else None
+        o, state = gated_delta_rule(q, k, v, g, beta, state)
+        if past_key_values is not None:
+            past_key_values.update_recurrent_state(self.layer_idx, state)
+        o = self.o_norm(o) * F.silu(self.g_proj(hidden_states).view(B, T, H, dv))
+        return self.o_proj(o.reshape(B, T, H * dv).to(hidden_states.dtype))
