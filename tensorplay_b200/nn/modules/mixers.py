@@ -107,23 +107,60 @@ def gated_delta_rule(q: Tensor, k: Tensor, v: Tensor, g: Tensor, beta: Tensor,
                      state: Optional[Tensor] = None) -> Tuple[Tensor, Tensor]:
     """Gated delta rule, one step per token.
 
-    ``q, k``: [B, T, H, Dk] (keys L2-normalised by the caller), ``v``: [B, T, H, Dv], ``g``: [B, T, H]
-    log-decay (<= 0), ``beta``: [B, T, H] write strength in (0, 1); ``state``: [B, H, Dk, Dv].
-    Per token: ``S <- exp(g) * S``; ``S <- S + beta * k (v - S^T k)^T``; ``o = S^T q``.
-    Returns (o [B, T, H, Dv], final state).
+    ``q, k``: [B, T, H, Dk] (keys L2-normalised by the caller), ``v``: [B, T, H, Dv], ``beta``:
+    [B, T, H] write strength in (0, 1), ``g``: log-decay (<= 0), either one value per head
+    ([B, T, H]) or one per key channel ([B, T, H, Dk]: the fine-grained variant); ``state``:
+    [B, H, Dk, Dv]. Per token: ``S <- diag(exp(g)) S``; ``S <- S + beta * k (v - S^T k)^T``;
+    ``o = S^T q``. Returns (o [B, T, H, Dv], final state).
     """
     B, T, H, Dk = k.shape
     Dv = v.shape[-1]
     S = torch.zeros(B, H, Dk, Dv, dtype=torch.float32, device=k.device) if state is None else state.float()
     qf, kf, vf = q.float(), k.float(), v.float()
+    per_channel = g.dim() == 4
     out = []
     for t in range(T):
-        S = S * torch.exp(g[:, t].float())[..., None, None]
+        decay = torch.exp(g[:, t].float())
+        S = S * (decay[..., None] if per_channel else decay[..., None, None])
         kt, vt = kf[:, t], vf[:, t]
         pred = torch.einsum("bhkv,bhk->bhv", S, kt)
         S = S + torch.einsum("bhk,bhv->bhkv", kt, (vt - pred) * beta[:, t].float()[..., None])
         out.append(torch.einsum("bhkv,bhk->bhv", S, qf[:, t]))
     return torch.stack(out, dim=1).to(v.dtype), S
+
+
+def chunk_gated_delta_rule(q: Tensor, k: Tensor, v: Tensor, g: Tensor, beta: Tensor, state: Optional[Tensor] = None,
+                           chunk: int = 64) -> Tuple[Tensor, Tensor]:
+    """Same result as :func:`gated_delta_rule` (head-scalar decay) with matrix algebra per chunk of
+    ``chunk`` tokens: inside a chunk the delta-rule writes form a unit lower-triangular system
+    ``(I + tril(beta * decay * K K^T, -1)) U = beta * (V - decay_in * K S)`` solved in closed form,
+    so the sequential depth is T / chunk instead of T (the GEMM-shaped form used for training)."""
+    B, T, H, Dk = k.shape
+    Dv = v.shape[-1]
+    S = torch.zeros(B, H, Dk, Dv, dtype=torch.float32, device=k.device) if state is None else state.float()
+    qf, kf, vf = (t.float().transpose(1, 2) for t in (q, k, v))      # [B, H, T, D]
+    gf, bf = g.float().transpose(1, 2), beta.float().transpose(1, 2)  # [B, H, T]
+    outs = []
+    for c0 in range(0, T, chunk):
+        c1 = min(c0 + chunk, T)
+        n = c1 - c0
+        qc, kc, vc, bc = qf[:, :, c0:c1], kf[:, :, c0:c1], vf[:, :, c0:c1], bf[:, :, c0:c1]
+        gc = torch.cumsum(gf[:, :, c0:c1], dim=-1)                    # log-decay from chunk start to token i (incl.)
+        # decay between tokens: D[i, j] = exp(gc[i] - gc[j]) for j <= i
+        diff = gc.unsqueeze(-1) - gc.unsqueeze(-2)
+        tri = torch.tril(torch.ones(n, n, dtype=torch.bool, device=k.device))
+        Dm = torch.where(tri, torch.exp(diff.masked_fill(~tri, 0.0)), torch.zeros_like(diff))
+        kk = torch.einsum("bhik,bhjk->bhij", kc, kc) * Dm
+        A = torch.tril(kk * bc.unsqueeze(-1), diagonal=-1)            # strictly lower part: earlier writes seen by token i
+        rhs = bc.unsqueeze(-1) * (vc - torch.exp(gc).unsqueeze(-1) * torch.einsum("bhik,bhkv->bhiv", kc, S))
+        eye = torch.eye(n, device=k.device).expand(B, H, n, n)
+        U = torch.linalg.solve_triangular(eye + A, rhs, upper=False)  # the per-token write vectors
+        qk = torch.einsum("bhik,bhjk->bhij", qc, kc) * Dm
+        o = torch.exp(gc).unsqueeze(-1) * torch.einsum("bhik,bhkv->bhiv", qc, S) + torch.einsum("bhij,bhjv->bhiv", qk, U)
+        outs.append(o)
+        tail = torch.exp(gc[..., -1:] - gc)                           # decay from token j to the chunk end
+        S = torch.exp(gc[..., -1])[..., None, None] * S + torch.einsum("bhjk,bhjv->bhkv", kc * tail.unsqueeze(-1), U)
+    return torch.cat(outs, dim=2).transpose(1, 2).to(v.dtype), S
 
 
 class GatedDeltaNet(Module):
@@ -176,6 +213,44 @@ class GatedDeltaNet(Module):
         v = v.reshape(B, T, H, dv)
         beta = torch.sigmoid(self.b_proj(hidden_states).float())
         g = -torch.exp(self.A_log.float()) * F.softplus(self.a_proj(hidden_states).float() + self.dt_bias.float())
+        state = past_key_values.recurrent_states.get(self.layer_idx) if past_key_values is not None else None
+        rule = chunk_gated_delta_rule if T > 16 else gated_delta_rule
+        o, state = rule(q, k, v, g, beta, state)
+        if past_key_values is not None:
+            past_key_values.update_recurrent_state(self.layer_idx, state)
+        o = self.o_norm(o) * F.silu(self.g_proj(hidden_states).view(B, T, H, dv))
+        return self.o_proj(o.reshape(B, T, H * dv).to(hidden_states.dtype))
+
+
+class KimiDeltaAttention(GatedDeltaNet):
+    """Gated delta rule with the decay resolved per key channel: the forget gate comes from a
+    low-rank projection and has shape ``[B, T, H, Dk]``, so that different key coordinates keep
+    their associations for different time spans; the write rule is unchanged
+    (tensorplay/nn/modules/kimi_delta.py)."""
+
+    def __init__(self, embed_dim: int, num_heads: int, head_dim: Optional[int] = None, expand_v: float = 1.0,
+                 conv_size: int = 4, gate_rank: Optional[int] = None, layer_idx: int = 0, norm_eps: float = 1e-6,
+                 device=None, dtype=None) -> None:
+        super().__init__(embed_dim, num_heads, head_dim, expand_v, conv_size, layer_idx, norm_eps, device, dtype)
+        kw = {"device": device, "dtype": dtype}
+        rank = gate_rank if gate_rank is not None else self.head_k_dim
+        self.f_a_proj = Linear(embed_dim, rank, bias=False, **kw)
+        self.f_b_proj = Linear(rank, num_heads * self.head_k_dim, bias=False, **kw)
+        self.a_proj = None  # the head-scalar decay input is replaced by the low-rank channel gate
+        self.dt_bias = torch.nn.Parameter(torch.zeros(num_heads * self.head_k_dim, **kw))
+
+    def forward(self, hidden_states: Tensor, position_ids: Optional[Tensor] = None, past_key_values=None) -> Tensor:
+        B, T, _ = hidden_states.shape
+        H, dk, dv = self.num_heads, self.head_k_dim, self.head_v_dim
+        qkv = torch.cat((self.q_proj(hidden_states), self.k_proj(hidden_states), self.v_proj(hidden_states)), dim=-1)
+        qkv = self._conv(qkv, past_key_values)
+        q, k, v = qkv.split((H * dk, H * dk, H * dv), dim=-1)
+        q = F.normalize(q.view(B, T, H, dk).float(), dim=-1) * dk ** -0.5
+        k = F.normalize(k.view(B, T, H, dk).float(), dim=-1)
+        v = v.reshape(B, T, H, dv)
+        beta = torch.sigmoid(self.b_proj(hidden_states).float())
+        gate_in = self.f_b_proj(self.f_a_proj(hidden_states)).float() + self.dt_bias.float()
+        g = (-torch.exp(self.A_log.float()).view(1, 1, H, 1) * F.softplus(gate_in.view(B, T, H, dk)))
         state = past_key_values.recurrent_states.get(self.layer_idx) if past_key_values is not None else None
         o, state = gated_delta_rule(q, k, v, g, beta, state)
         if past_key_values is not None:

@@ -60,3 +60,35 @@ def test_gated_delta_net_streaming_equals_full_sequence_and_trains():
     full.pow(2).mean().backward()
     assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in m.parameters())
     assert tp.nn.GatedDeltaNet is GatedDeltaNet
+
+
+def test_chunked_delta_rule_equals_token_recurrence():
+    from tensorplay_b200.nn import chunk_gated_delta_rule
+    torch.manual_seed(3)
+    B, T, H, Dk, Dv = 2, 37, 2, 8, 5
+    q, k = torch.randn(B, T, H, Dk), torch.nn.functional.normalize(torch.randn(B, T, H, Dk), dim=-1)
+    v, g, beta = torch.randn(B, T, H, Dv), -0.3 * torch.rand(B, T, H), torch.rand(B, T, H)
+    s0 = torch.randn(B, H, Dk, Dv)
+    o_ref, s_ref = gated_delta_rule(q, k, v, g, beta, s0)
+    for chunk in (8, 16, 64):
+        o, s = chunk_gated_delta_rule(q, k, v, g, beta, s0, chunk=chunk)
+        torch.testing.assert_close(o, o_ref, rtol=1e-4, atol=1e-4)
+        torch.testing.assert_close(s, s_ref, rtol=1e-4, atol=1e-4)
+
+
+def test_kimi_delta_attention_streaming_and_per_channel_decay():
+    from tensorplay_b200.nn import KimiDeltaAttention
+    torch.manual_seed(4)
+    m = KimiDeltaAttention(embed_dim=32, num_heads=2, head_dim=8, gate_rank=4)
+    x = torch.randn(2, 7, 32)
+    full = m(x)
+    cache = LinearStateCache()
+    parts = [m(x[:, :3], past_key_values=cache)] + [m(x[:, t:t + 1], past_key_values=cache) for t in range(3, 7)]
+    torch.testing.assert_close(torch.cat(parts, 1), full, rtol=1e-4, atol=1e-5)
+    # with a decay that is constant over the channels the fine-grained rule equals the head-scalar one
+    B, T, H, Dk, Dv = 1, 6, 2, 4, 3
+    q, k = torch.randn(B, T, H, Dk), torch.nn.functional.normalize(torch.randn(B, T, H, Dk), dim=-1)
+    v, g, beta = torch.randn(B, T, H, Dv), -torch.rand(B, T, H), torch.rand(B, T, H)
+    o1, _ = gated_delta_rule(q, k, v, g, beta)
+    o2, _ = gated_delta_rule(q, k, v, g.unsqueeze(-1).expand(B, T, H, Dk), beta)
+    torch.testing.assert_close(o1, o2)
