@@ -257,3 +257,68 @@ class KimiDeltaAttention(GatedDeltaNet):
             past_key_values.update_recurrent_state(self.layer_idx, state)
         o = self.o_norm(o) * F.silu(self.g_proj(hidden_states).view(B, T, H, dv))
         return self.o_proj(o.reshape(B, T, H * dv).to(hidden_states.dtype))
+
+
+class CrossAttention(Module):
+    """Pre-norm multi-head attention from a decoder stream onto an encoder memory (no mask: every
+    decoder position may read the whole memory), added to the stream as a residual."""
+
+    def __init__(self, hidden_size: int, num_heads: int, rms_norm_eps: float = 1e-6, device=None, dtype=None) -> None:
+        kw = {"device": device, "dtype": dtype}
+        super().__init__()
+        if hidden_size % num_heads:
+            raise ValueError(f"hidden_size ({hidden_size}) must be divisible by num_heads ({num_heads})")
+        self.num_heads, self.head_dim = num_heads, hidden_size // num_heads
+        self.norm = RMSNorm(hidden_size, eps=rms_norm_eps, **kw)
+        self.q_proj = Linear(hidden_size, hidden_size, bias=False, **kw)
+        self.kv_proj = Linear(hidden_size, 2 * hidden_size, bias=False, **kw)
+        self.o_proj = Linear(hidden_size, hidden_size, bias=False, **kw)
+
+    def forward(self, x: Tensor, memory: Tensor) -> Tensor:
+        B, T, C = x.shape
+        S = memory.shape[1]
+        q = self.q_proj(self.norm(x)).view(B, T, self.num_heads, self.head_dim)
+        kv = self.kv_proj(memory).view(B, S, 2, self.num_heads, self.head_dim)
+        o = _ops.flash_attention(q, kv[:, :, 0], kv[:, :, 1], causal=False, scale=self.head_dim ** -0.5)
+        return x + self.o_proj(o.reshape(B, T, C))
+
+
+class CausalEncoderDecoder(Module):
+    """Two causal stacks of :class:`TransformerBlock`: the encoder digests the sequence into a
+    memory (final norm + projection), the decoder processes the same sequence and reads that
+    memory through a :class:`CrossAttention` after each of its blocks. ``mixer_factory(hidden_size,
+    layer_idx)`` chooses the token mixer per layer (default: grouped-query attention), so linear
+    and latent-attention mixers can be swapped in (tensorplay/nn/modules/causal_encoder_decoder.py:80-163).
+    """
+
+    def __init__(self, hidden_size: int, num_heads: int, n_encoder_layers: int = 2, n_decoder_layers: int = 2,
+                 mixer_factory=None, num_kv_heads: Optional[int] = None, mlp_intermediate_size: Optional[int] = None,
+                 rms_norm_eps: float = 1e-6, device=None, dtype=None) -> None:
+        from .llm import GroupedQueryAttention, TransformerBlock
+        kw = {"device": device, "dtype": dtype}
+        super().__init__()
+        if mixer_factory is None:
+            def mixer_factory(width, layer_idx):
+                return GroupedQueryAttention(width, num_heads, num_kv_heads=num_kv_heads, layer_idx=layer_idx, **kw)
+        self.hidden_size = hidden_size
+
+        def stack(n):
+            return torch.nn.ModuleList(
+                TransformerBlock(hidden_size, mixer_factory(hidden_size, i), mlp_intermediate_size=mlp_intermediate_size,
+                                 rms_norm_eps=rms_norm_eps, **kw) for i in range(n))
+
+        self.encoder, self.decoder = stack(n_encoder_layers), stack(n_decoder_layers)
+        self.cross_attention = torch.nn.ModuleList(
+            CrossAttention(hidden_size, num_heads, rms_norm_eps=rms_norm_eps, **kw) for _ in range(n_decoder_layers))
+        self.memory_proj = Linear(hidden_size, hidden_size, bias=False, **kw)
+        self.encoder_final_norm = RMSNorm(hidden_size, eps=rms_norm_eps, **kw)
+
+    def forward(self, hidden_states: Tensor) -> Tensor:
+        memory = hidden_states
+        for block in self.encoder:
+            memory = block(memory)
+        memory = self.memory_proj(self.encoder_final_norm(memory))
+        x = hidden_states
+        for block, cross in zip(self.decoder, self.cross_attention):
+            x = cross(block(x), memory)
+        return x

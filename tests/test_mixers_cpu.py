@@ -92,3 +92,17 @@ def test_kimi_delta_attention_streaming_and_per_channel_decay():
     o1, _ = gated_delta_rule(q, k, v, g, beta)
     o2, _ = gated_delta_rule(q, k, v, g.unsqueeze(-1).expand(B, T, H, Dk), beta)
     torch.testing.assert_close(o1, o2)
+
+
+def test_causal_encoder_decoder_shapes_mixers_and_gradients():
+    from tensorplay_b200.nn import CausalEncoderDecoder
+    torch.manual_seed(6)
+    m = CausalEncoderDecoder(hidden_size=32, num_heads=4, n_encoder_layers=2, n_decoder_layers=2, num_kv_heads=2)
+    x = torch.randn(2, 6, 32)
+    y = m(x)
+    assert y.shape == x.shape
+    y.pow(2).mean().backward()
+    assert all(p.grad is not None for p in m.parameters())
+    # the mixer is swappable per layer: a linear-time mixer in both stacks
+    m2 = CausalEncoderDecoder(32, 4, 1, 1, mixer_factory=lambda w, i: GatedDeltaNet(w, 2, head_dim=8, layer_idx=i))
+    assert m2(x).shape == x.shape
