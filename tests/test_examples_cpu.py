@@ -1,0 +1,29 @@
+"""The user-facing examples run end to end on CPU with tiny settings."""
+import os
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(args, timeout=600):
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    r = subprocess.run([sys.executable] + args, capture_output=True, text=True, timeout=timeout, env=env, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    return r.stdout
+
+
+def test_train_example_saves_and_resumes(tmp_path):
+    d = str(tmp_path / "ck")
+    out = _run(["examples/train_llama_fsdp.py", "--preset", "tiny", "--steps", "6", "--seq", "32", "--log-every", "3",
+                "--save", d])
+    assert "step 6: loss" in out and os.path.exists(os.path.join(d, "engine.json"))
+    out = _run(["examples/train_llama_fsdp.py", "--preset", "tiny", "--steps", "3", "--seq", "32", "--log-every", "3",
+                "--resume", d])
+    assert "step 9: loss" in out
+
+
+def test_generate_example_cache_kinds():
+    for kind in ("dynamic", "static", "paged"):
+        out = _run(["examples/generate.py", "--new-tokens", "6", "--cache", kind])
+        assert "greedy with and without cache agree: True" in out, out
