@@ -33,7 +33,6 @@ class _Bucket:
                  flat_param: Optional[torch.Tensor]):
         self.index, self.params = index, params
         self.flat_grad, self.flat_param = flat_grad, flat_param
-        self.pending = len(params)
         self.event = None
 
 
@@ -94,16 +93,35 @@ class DistributedDataParallel(nn.Module):
                                group=self.process_group)
 
     def _build_buckets(self, params, cap_bytes) -> None:
-        groups, cur, size = [], [], 0
-        for p in reversed(params):
-            nb = p.numel() * p.element_size()
-            if cur and (size + nb > cap_bytes or p.dtype != cur[0].dtype):
-                groups.append(cur)
-                cur, size = [], 0
-            cur.append(p)
-            size += nb
-        if cur:
-            groups.append(cur)
+        # bucket assignment and ready counting live in the native reducer (csrc/runtime/reducer.cpp)
+        import ctypes as C
+        from .. import _native
+        rt = _native.runtime()
+        rt.tpb_reducer_create.restype = C.c_void_p
+        rt.tpb_reducer_create.argtypes = [C.POINTER(C.c_longlong), C.POINTER(C.c_int), C.c_int, C.c_longlong,
+                                          C.c_longlong]
+        for fn, res, args in (("tpb_reducer_num_buckets", C.c_int, [C.c_void_p]),
+                              ("tpb_reducer_bucket_size", C.c_int, [C.c_void_p, C.c_int]),
+                              ("tpb_reducer_bucket_numel", C.c_longlong, [C.c_void_p, C.c_int]),
+                              ("tpb_reducer_offset_of", C.c_longlong, [C.c_void_p, C.c_int]),
+                              ("tpb_reducer_bucket_members", None, [C.c_void_p, C.c_int, C.POINTER(C.c_int)]),
+                              ("tpb_reducer_mark_ready", C.c_int, [C.c_void_p, C.c_int]),
+                              ("tpb_reducer_rearm", None, [C.c_void_p, C.c_int]),
+                              ("tpb_reducer_reset", None, [C.c_void_p]),
+                              ("tpb_reducer_destroy", None, [C.c_void_p])):
+            f = getattr(rt, fn)
+            f.restype, f.argtypes = res, args
+        n = len(params)
+        self._rt = rt
+        self._reducer = rt.tpb_reducer_create((C.c_longlong * n)(*[p.numel() for p in params]),
+                                              (C.c_int * n)(*[p.element_size() for p in params]), n,
+                                              int(cap_bytes), self.world * 128)
+        self._param_index = {id(p): i for i, p in enumerate(params)}
+        groups = []
+        for b in range(rt.tpb_reducer_num_buckets(self._reducer)):
+            m = (C.c_int * rt.tpb_reducer_bucket_size(self._reducer, b))()
+            rt.tpb_reducer_bucket_members(self._reducer, b, m)
+            groups.append([params[i] for i in m])
         arena = None
         if self.comm_kind == "symm":
             from ..parallel.symm import SymmArena
@@ -115,11 +133,8 @@ class DistributedDataParallel(nn.Module):
         self.buckets: List[_Bucket] = []
         self._bucket_of = {}
         for gi, g in enumerate(groups):
-            offs, off = [], 0
-            for p in g:
-                offs.append(off)
-                off += (p.numel() + 7) // 8 * 8
-            padded = (off + self.world * 128 - 1) // (self.world * 128) * (self.world * 128)
+            offs = [int(self._rt.tpb_reducer_offset_of(self._reducer, self._param_index[id(p)])) for p in g]
+            padded = int(self._rt.tpb_reducer_bucket_numel(self._reducer, gi))
             if arena is not None:
                 fg = arena.alloc(padded, g[0].dtype)
                 fp = arena.alloc(padded, g[0].dtype)
@@ -159,9 +174,9 @@ class DistributedDataParallel(nn.Module):
             if param.grad.data_ptr() != v.data_ptr():
                 v.copy_(param.grad.reshape(-1))
                 param.grad = v.view(param.shape)
-            b.pending -= 1
-            if b.pending == 0:
-                self._reduce(b)
+            done = self._rt.tpb_reducer_mark_ready(self._reducer, self._param_index[id(param)])
+            if done >= 0:
+                self._reduce(self.buckets[done])
         return hook
 
     def _reduce(self, b: _Bucket) -> None:
@@ -172,7 +187,7 @@ class DistributedDataParallel(nn.Module):
             out = out[0] if isinstance(out, (list, tuple)) else out
             if out is not None and out.data_ptr() != b.flat_grad.data_ptr():
                 b.flat_grad.copy_(out)
-            b.pending = len(b.params)
+            self._rt.tpb_reducer_rearm(self._reducer, b.index)
             return
         if self.cuda:
             self.comm_stream.wait_stream(torch.cuda.current_stream())
@@ -191,7 +206,7 @@ class DistributedDataParallel(nn.Module):
             if self.cuda:
                 b.event = torch.cuda.Event()
                 b.event.record(self.comm_stream)
-        b.pending = len(b.params)
+        self._rt.tpb_reducer_rearm(self._reducer, b.index)
 
     def _reduce_symm(self, b: _Bucket) -> None:
         from .. import _native

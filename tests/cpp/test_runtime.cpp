@@ -29,6 +29,15 @@ uint32_t tpb_crc32(const void* data, size_t n, uint32_t seed);
 int tpb_mega_write(const char* path, const void* header, uint64_t header_len, uint64_t alignment,
                    int n, const void* const* ptrs, const uint64_t* sizes, int nthreads);
 int tpb_file_read(const char* path, uint64_t offset, void* dst, uint64_t nbytes, int nthreads);
+void* tpb_reducer_create(const long long* numels, const int* elem_bytes, int n, long long cap_bytes, long long align);
+void tpb_reducer_destroy(void* h);
+int tpb_reducer_num_buckets(void* h);
+int tpb_reducer_bucket_of(void* h, int param);
+long long tpb_reducer_offset_of(void* h, int param);
+long long tpb_reducer_bucket_numel(void* h, int bucket);
+int tpb_reducer_mark_ready(void* h, int param);
+void tpb_reducer_rearm(void* h, int bucket);
+void tpb_reducer_reset(void* h);
 }
 
 static int failures = 0;
@@ -124,8 +133,31 @@ static void test_file_io(const char* dir) {
   std::remove(path.c_str());
 }
 
+static void test_reducer() {
+  // 4 parameters, model order; gradients arrive last-first: buckets are filled from the end
+  const long long numels[4] = {100, 200, 50, 1000};
+  const int elem[4] = {2, 2, 4, 2};
+  void* r = tpb_reducer_create(numels, elem, 4, /*cap_bytes=*/1000, /*align=*/256);
+  CHECK(tpb_reducer_num_buckets(r) == 3);
+  CHECK(tpb_reducer_bucket_of(r, 3) == 0);   // larger than the cap: alone
+  CHECK(tpb_reducer_bucket_of(r, 2) == 1);   // other element size: own bucket
+  CHECK(tpb_reducer_bucket_of(r, 1) == 2 && tpb_reducer_bucket_of(r, 0) == 2);
+  CHECK(tpb_reducer_offset_of(r, 1) == 0 && tpb_reducer_offset_of(r, 0) == 200);  // 8-element aligned
+  CHECK(tpb_reducer_bucket_numel(r, 0) == 1024 && tpb_reducer_bucket_numel(r, 2) == 512);
+  CHECK(tpb_reducer_mark_ready(r, 3) == 0);
+  CHECK(tpb_reducer_mark_ready(r, 1) == -1);
+  CHECK(tpb_reducer_mark_ready(r, 1) == -2);  // double mark in one iteration
+  CHECK(tpb_reducer_mark_ready(r, 0) == 2);
+  tpb_reducer_rearm(r, 2);
+  CHECK(tpb_reducer_mark_ready(r, 0) == -1);  // counts again after re-arming
+  tpb_reducer_reset(r);
+  CHECK(tpb_reducer_mark_ready(r, 2) == 1);
+  tpb_reducer_destroy(r);
+}
+
 int main(int argc, char** argv) {
   test_store();
+  test_reducer();
   test_file_io(argc > 1 ? argv[1] : "/tmp");
   if (failures) {
     std::fprintf(stderr, "%d check(s) failed\n", failures);
