@@ -1,9 +1,9 @@
 from .llm import (GroupedQueryAttention, LayerNorm, Linear, RMSNorm, RotaryEmbedding, SwiGLUMLP,
                   TransformerBlock, apply_rotary_emb)
 
-from .mixers import (CausalEncoderDecoder, CrossAttention, GatedDeltaNet, KimiDeltaAttention, MultiheadLatentAttention, chunk_gated_delta_rule,
+from .mixers import (CausalEncoderDecoder, CompressedSparseAttention, CrossAttention, GatedDeltaNet, KimiDeltaAttention, MultiheadLatentAttention, chunk_gated_delta_rule,
                      gated_delta_rule)
 
 __all__ = ["GroupedQueryAttention", "LayerNorm", "Linear", "RMSNorm", "RotaryEmbedding", "SwiGLUMLP",
            "TransformerBlock", "apply_rotary_emb", "MultiheadLatentAttention", "GatedDeltaNet", "gated_delta_rule",
-           "chunk_gated_delta_rule", "KimiDeltaAttention", "CrossAttention", "CausalEncoderDecoder"]
+           "chunk_gated_delta_rule", "KimiDeltaAttention", "CrossAttention", "CausalEncoderDecoder", "CompressedSparseAttention"]

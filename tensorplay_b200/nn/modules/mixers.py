@@ -322,3 +322,103 @@ class CausalEncoderDecoder(Module):
         for block, cross in zip(self.decoder, self.cross_attention):
             x = cross(block(x), memory)
         return x
+
+
+class CompressedSparseAttention(Module):
+    """Long-context mixer with two key/value tiers (tensorplay/nn/modules/compressed_attention.py):
+
+    * a sliding window of the last ``window_size`` tokens, attended at full resolution through one
+      shared key/value head with ``k == v``;
+    * one compressed entry per ``compress_rate`` source tokens (a softmax-gated reduction of the
+      window's key/value vectors), of which every query sees at most ``index_topk``: a small
+      indexer scores the entries per query, ``sum_h w[t, h] * relu(q_idx[t, h] . k_idx[s])``, and
+      only entries that lie completely in the query's past are eligible.
+
+    Each head also has a learned sink logit that takes part in the softmax without contributing a
+    value. This implementation processes whole sequences (training / prefill); it keeps no
+    incremental state between calls.
+    """
+
+    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, q_lora_rank: int, compress_rate: int = 4,
+                 window_size: int = 128, rope_head_dim: Optional[int] = None, index_n_heads: int = 4,
+                 index_head_dim: int = 32, index_topk: int = 16, rope_base: float = 10000.0,
+                 rms_norm_eps: float = 1e-6, layer_idx: int = 0, device=None, dtype=None) -> None:
+        kw = {"device": device, "dtype": dtype}
+        super().__init__()
+        if hidden_size % num_heads:
+            raise ValueError(f"hidden_size ({hidden_size}) must be divisible by num_heads ({num_heads})")
+        self.hidden_size, self.num_heads, self.head_dim = hidden_size, num_heads, head_dim
+        self.sliding_window, self.compress_rate, self.index_topk = window_size, compress_rate, index_topk
+        self.index_n_heads, self.index_head_dim, self.layer_idx = index_n_heads, index_head_dim, layer_idx
+        self.scaling = head_dim ** -0.5
+        self.q_a_proj = Linear(hidden_size, q_lora_rank, bias=False, **kw)
+        self.q_a_norm = RMSNorm(q_lora_rank, eps=rms_norm_eps, **kw)
+        self.q_b_proj = Linear(q_lora_rank, num_heads * head_dim, bias=False, **kw)
+        self.kv_proj = Linear(hidden_size, head_dim, bias=False, **kw)
+        self.kv_norm = RMSNorm(head_dim, eps=rms_norm_eps, **kw)
+        self.o_proj = Linear(num_heads * head_dim, hidden_size, bias=False, **kw)
+        self.sinks = torch.nn.Parameter(torch.zeros(num_heads, **kw))
+        self.rope_dim = rope_head_dim if rope_head_dim is not None else head_dim
+        self.rope = RotaryEmbedding(self.rope_dim, base=rope_base, device=device)
+        # compressor: per-token gate logit; entries are gate-softmax-weighted means of the window's kv
+        self.compress_gate = Linear(hidden_size, 1, bias=False, **kw)
+        self.compress_norm = RMSNorm(head_dim, eps=rms_norm_eps, **kw)
+        # indexer: its own small keys per entry, queries and head weights per token
+        self.idx_k_proj = Linear(hidden_size, index_head_dim, bias=False, **kw)
+        self.idx_q_proj = Linear(q_lora_rank, index_n_heads * index_head_dim, bias=False, **kw)
+        self.idx_w_proj = Linear(hidden_size, index_n_heads, bias=False, **kw)
+
+    def _compress(self, x: Tensor, feats: Tensor) -> Tensor:
+        """[B, T, C] features -> [B, T // rate, C] gate-weighted window means (incomplete tail dropped)."""
+        B, T, C = feats.shape
+        r = self.compress_rate
+        n = T // r
+        if n == 0:
+            return feats.new_zeros(B, 0, C)
+        gate = torch.softmax(self.compress_gate(x[:, : n * r]).float().view(B, n, r), dim=-1)
+        return (feats[:, : n * r].float().view(B, n, r, C) * gate.unsqueeze(-1)).sum(2).to(feats.dtype)
+
+    def forward(self, hidden_states: Tensor, position_ids: Optional[Tensor] = None, past_key_values=None) -> Tensor:
+        if past_key_values is not None:
+            raise NotImplementedError("CompressedSparseAttention keeps no incremental state in this build")
+        B, T, _ = hidden_states.shape
+        H, D, r = self.num_heads, self.head_dim, self.compress_rate
+        dev = hidden_states.device
+        pos = position_ids if position_ids is not None else torch.arange(T, device=dev).expand(B, T)
+        q_lat = self.q_a_norm(self.q_a_proj(hidden_states))
+        q = self.q_b_proj(q_lat).view(B, T, H, D)
+        kv = self.kv_norm(self.kv_proj(hidden_states)).view(B, T, 1, D)
+        cos, sin = self.rope.tables(int(pos.max().item()) + 1, dev)
+        rd = self.rope_dim
+        q = torch.cat((_ops.apply_rope(q[..., :rd].contiguous(), cos, sin, pos), q[..., rd:]), dim=-1)
+        k_win = torch.cat((_ops.apply_rope(kv[..., :rd].contiguous(), cos, sin, pos), kv[..., rd:]), dim=-1)
+        # ---- tier 1: sliding window (shared head, k == v up to the rotation of k)
+        i = torch.arange(T, device=dev).view(T, 1)
+        j = torch.arange(T, device=dev).view(1, T)
+        win_ok = (j <= i) & (j > i - self.sliding_window)
+        s_win = torch.einsum("bthd,bsd->bhts", q.float(), k_win[:, :, 0].float()) * self.scaling
+        s_win = s_win.masked_fill(~win_ok, float("-inf"))
+        # ---- tier 2: compressed entries selected by the indexer
+        ent = self.compress_norm(self._compress(hidden_states, kv[:, :, 0]))        # [B, n, D]
+        n = ent.shape[1]
+        if n > 0:
+            ent_end = (torch.arange(n, device=dev) + 1) * r - 1                     # last source position of an entry
+            eligible = ent_end.view(1, 1, n) <= pos.unsqueeze(-1)                   # completely in the query's past
+            k_idx = self._compress(hidden_states, self.idx_k_proj(hidden_states))   # [B, n, Di]
+            q_idx = self.idx_q_proj(q_lat).view(B, T, self.index_n_heads, self.index_head_dim)
+            w_idx = self.idx_w_proj(hidden_states).float()
+            score = (torch.relu(torch.einsum("bthd,bnd->bthn", q_idx.float(), k_idx.float())) * w_idx.unsqueeze(-1)).sum(2)
+            score = score.masked_fill(~eligible, float("-inf"))
+            k_sel = min(self.index_topk, n)
+            top = score.topk(k_sel, dim=-1).indices
+            chosen = torch.zeros(B, T, n, dtype=torch.bool, device=dev).scatter_(-1, top, True) & eligible
+            s_ent = torch.einsum("bthd,bnd->bhtn", q.float(), ent.float()) * self.scaling
+            s_ent = s_ent.masked_fill(~chosen.unsqueeze(1), float("-inf"))
+        else:
+            s_ent = s_win.new_zeros(B, H, T, 0)
+        sink = self.sinks.float().view(1, H, 1, 1).expand(B, H, T, 1)
+        p = torch.softmax(torch.cat((s_win, s_ent, sink), dim=-1), dim=-1)
+        o = torch.einsum("bhts,bsd->bthd", p[..., :T], kv[:, :, 0].float())
+        if n > 0:
+            o = o + torch.einsum("bhtn,bnd->bthd", p[..., T: T + n], ent.float())
+        return self.o_proj(o.reshape(B, T, H * D).to(hidden_states.dtype))

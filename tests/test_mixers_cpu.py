@@ -106,3 +106,24 @@ def test_causal_encoder_decoder_shapes_mixers_and_gradients():
     # the mixer is swappable per layer: a linear-time mixer in both stacks
     m2 = CausalEncoderDecoder(32, 4, 1, 1, mixer_factory=lambda w, i: GatedDeltaNet(w, 2, head_dim=8, layer_idx=i))
     assert m2(x).shape == x.shape
+
+
+def test_compressed_sparse_attention_causality_and_tiers():
+    from tensorplay_b200.nn import CompressedSparseAttention
+    torch.manual_seed(7)
+    m = CompressedSparseAttention(hidden_size=32, num_heads=4, head_dim=8, q_lora_rank=16, compress_rate=4,
+                                  window_size=6, index_n_heads=2, index_head_dim=8, index_topk=2).eval()
+    x = torch.randn(2, 24, 32)
+    y = m(x)
+    assert y.shape == x.shape
+    # causal: outputs before position 13 do not depend on tokens from 13 on (also through the
+    # compressed entries: an entry is visible only when all of its source tokens are in the past)
+    x2 = x.clone()
+    x2[:, 13:] += 1.0
+    torch.testing.assert_close(m(x2)[:, :13], y[:, :13], rtol=1e-4, atol=1e-5)
+    # the compressed tier matters: beyond the window, distant tokens still influence the output
+    x3 = x.clone()
+    x3[:, 0:4] += 1.0           # far outside the 6-token window of position 23, inside entry 0
+    assert (m(x3)[:, 23] - y[:, 23]).abs().max() > 1e-6
+    y.pow(2).mean().backward()
+    assert m.sinks.grad is not None and m.compress_gate.weight.grad is not None
