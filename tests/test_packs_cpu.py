@@ -87,3 +87,24 @@ def test_hot_ops_registered_as_custom_operators():
     with FakeTensorMode():
         out = torch.ops.tpb.linear(torch.empty(5, 7, 32), torch.empty(16, 32), None)
         assert tuple(out.shape) == (5, 7, 16)
+
+
+def _metric_sync_worker(rank, world):
+    import torch.distributed as dist
+    import tensorplay_b200 as tp
+    torch.manual_seed(0)
+    logits = torch.randn(40, 3)
+    target = torch.randint(0, 3, (40,))
+    acc = tp.metrics.Accuracy(3)
+    half = slice(rank * 20, (rank + 1) * 20)
+    acc.update(logits[half], target[half])
+    acc.sync()
+    expected = (logits.argmax(-1) == target).float().mean()
+    assert abs(float(acc.compute()) - float(expected)) < 1e-6
+    dist.barrier()
+    return True
+
+
+def test_metrics_sync_over_process_group():
+    from tests.distutil import run_ranks
+    assert all(run_ranks(_metric_sync_worker, 2))
