@@ -69,3 +69,12 @@ def test_ring_attention_and_clipped_step():
     r = _run_workers("cp_worker.py", n)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "RESULT" in r.stdout
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_fsdp_symm_pull_kernel_transport():
+    """Same check with the SM pull kernels instead of the copy engines."""
+    n = 2 if _ngpu() < 4 else 4
+    r = _run_workers("fsdp_symm_worker.py", n, extra_env={"TPB_COMM_TRANSPORT": "sm"})
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "RESULT" in r.stdout
