@@ -36,6 +36,9 @@ def parse_args():
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--micro-batch", type=int, default=1)
     ap.add_argument("--comm", default="auto", choices=["auto", "symm", "torch"])
+    ap.add_argument("--ac", default="full", choices=["full", "selective"],
+                    help="activation checkpointing per transformer block: recompute the whole block in backward, "
+                         "or keep the GEMM / attention outputs and recompute only norms, RoPE and SwiGLU")
     ap.add_argument("--layers", type=int, default=None,
                     help="debug only: fewer layers (the JSON then names the reduced model)")
     return ap.parse_args()
@@ -142,7 +145,7 @@ def main():
     model = Llama(cfg, device=dev, dtype=torch.bfloat16)
     model.reset_parameters(seed=1234)
     engine = FSDPEngine(model, AdamWConfig(lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1),
-                        comm=args.comm, activation_checkpointing=True)
+                        comm=args.comm, activation_checkpointing=True if args.ac == "full" else "selective")
     B, T = args.micro_batch, args.seq
     gen = torch.Generator(device="cpu")
     gen.manual_seed(100 + rank)
@@ -211,7 +214,7 @@ def main():
             "data": "synthetic (uniform random token ids, random-init N(0, 0.02) weights)",
             "config": {"model": name, "global_batch": world * B, "seq_len": T,
                        "parallelism": f"fsdp{world}" if world > 1 else "single-gpu (fsdp1)",
-                       "activation_checkpointing": True, "optimizer": "AdamW fp32 state + fp32 master",
+                       "activation_checkpointing": ("per block, full recompute" if args.ac == "full" else "per block, selective: GEMM and attention outputs kept, norms / RoPE / SwiGLU recomputed"), "optimizer": "AdamW fp32 state + fp32 master",
                        "comm": engine.comm_kind,
                        "l2": "per-step working set (parameters + optimizer state, >100 GB/box) "
                              "exceeds the 126 MB L2; no explicit flush"},

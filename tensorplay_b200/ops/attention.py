@@ -17,6 +17,7 @@ from typing import Optional
 import torch
 
 from .. import _native
+from . import _ckpt
 from ._common import lib, status_word, stream_ptr, use_native
 
 
@@ -158,7 +159,12 @@ class _QKVAttnFn(torch.autograd.Function):
         qk = packed[:, :, : Hq + Hkv].contiguous()
         _rope_native_(qk, cos, sin, pos, interleaved, False)
         q, k, v = qk[:, :, :Hq], qk[:, :, Hq:], packed[:, :, Hq + Hkv:]
-        o, lse = flash_fwd(q, k, v, causal, scale)
+        kept = _ckpt.take()  # selective checkpointing: output and LSE of the first forward pass
+        if kept is not None:
+            o, lse = kept
+        else:
+            o, lse = flash_fwd(q, k, v, causal, scale)
+            _ckpt.stash(o, lse)
         ctx.save_for_backward(qk, qkv, o, lse, cos, sin, pos if pos is not None else torch.empty(0))
         ctx.cfg = (Hq, Hkv, D, causal, scale, interleaved, pos is not None)
         return o.view(B, T, Hq * D)

@@ -10,6 +10,7 @@ from typing import Optional
 import torch
 
 from .. import _native
+from . import _ckpt
 from ._common import lib, ptr, status_word, stream_ptr, use_native
 
 
@@ -98,7 +99,12 @@ class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias):
         x2 = x.reshape(-1, x.shape[-1])
-        y = gemm(x2, weight, bias=bias)
+        kept = _ckpt.take()  # selective checkpointing: reuse the output of the first forward pass
+        if kept is not None:
+            y = kept[0]
+        else:
+            y = gemm(x2, weight, bias=bias, out_dtype=x2.dtype)
+            _ckpt.stash(y)
         ctx.save_for_backward(x2, weight)
         ctx.has_bias = bias is not None
         ctx.x_shape = x.shape
@@ -115,7 +121,7 @@ class _LinearFn(torch.autograd.Function):
             dy2 = dy2.contiguous()
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
-            dx = gemm(dy2, weight, b_mn=True).view(ctx.x_shape)
+            dx = gemm(dy2, weight, b_mn=True, out_dtype=dy2.dtype).view(ctx.x_shape)
         if ctx.needs_input_grad[1]:
             w_ref = ctx.w_ref
             if w_ref is not None and w_ref._tpb_grad_view is not None:
@@ -123,7 +129,7 @@ class _LinearFn(torch.autograd.Function):
                      accumulate=getattr(w_ref, "_tpb_grad_written", False))
                 w_ref._tpb_grad_written = True
             else:
-                dw = gemm(dy2, x2, a_mn=True, b_mn=True)
+                dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=weight.dtype)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy2.float().sum(0).to(dy.dtype)
         return dx, dw, db
@@ -131,7 +137,7 @@ class _LinearFn(torch.autograd.Function):
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``x @ weight.T + bias``; on CUDA bf16 all three products run on the tcgen05 GEMM."""
-    if x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
+    if (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16) or _ckpt.active():
         return _LinearFn.apply(x, weight, bias)
     if x.is_cuda:
         # other dtypes on CUDA: cast through bf16 is not silently done; use torch's path

@@ -22,6 +22,7 @@ peer-memory kernels of ``tensorplay_b200.parallel.symm``).
 """
 from __future__ import annotations
 
+import contextlib
 import math
 from dataclasses import dataclass, field
 from typing import Callable, List, Optional, Sequence, Tuple
@@ -31,6 +32,7 @@ import torch.distributed as dist
 from torch import Tensor, nn
 
 from .. import ops
+from ..ops import _ckpt
 
 
 def _round_up(x: int, m: int) -> int:
@@ -125,7 +127,14 @@ class _UnitFn(torch.autograd.Function):
         tensors, extra = args[:n_tensor], args[n_tensor:]
         ctx.engine, ctx.unit_idx, ctx.fn, ctx.checkpoint, ctx.extra = engine, unit_idx, fn, checkpoint, extra
         engine._pre_forward(unit_idx)
-        if checkpoint:
+        ctx.kept = None
+        if checkpoint == "selective":
+            # GEMM and attention outputs are kept, the cheap ops in between are recomputed
+            with torch.no_grad(), _ckpt.record() as kept:
+                out = fn(*tensors, *extra)
+            ctx.kept = kept
+            ctx.save_for_backward(*tensors)
+        elif checkpoint:
             with torch.no_grad():
                 out = fn(*tensors, *extra)
             ctx.save_for_backward(*tensors)
@@ -146,8 +155,9 @@ class _UnitFn(torch.autograd.Function):
         if ctx.checkpoint:
             tensors = [t.detach().requires_grad_(t.requires_grad) if t.is_floating_point() else t
                        for t in ctx.saved_tensors]
-            with torch.enable_grad():
+            with torch.enable_grad(), (_ckpt.replay(ctx.kept) if ctx.kept is not None else contextlib.nullcontext()):
                 out = ctx.fn(*tensors, *ctx.extra)
+            ctx.kept = None
         else:
             tensors, out = ctx.detached, ctx.out
             ctx.detached = ctx.out = None
