@@ -46,6 +46,19 @@ class Block(nn.Module):
         return x + self.down(F.silu(g) * u)
 
 
+def _selective_contexts():
+    from torch.utils.checkpoint import CheckpointPolicy, create_selective_checkpoint_contexts
+    keep = {torch.ops.aten.mm.default, torch.ops.aten.addmm.default, torch.ops.aten.bmm.default,
+            torch.ops.aten._scaled_dot_product_flash_attention.default,
+            torch.ops.aten._scaled_dot_product_cudnn_attention.default,
+            torch.ops.aten._scaled_dot_product_efficient_attention.default}
+
+    def policy(ctx, op, *args, **kwargs):
+        return CheckpointPolicy.MUST_SAVE if op in keep else CheckpointPolicy.PREFER_RECOMPUTE
+
+    return create_selective_checkpoint_contexts(policy)
+
+
 class Model(nn.Module):
     def __init__(self, V=128256, H=4096, L=32, Hq=32, Hkv=8, D=128, FF=14336, eps=1e-5, theta=5e5, T=4096):
         super().__init__()
@@ -58,10 +71,15 @@ class Model(nn.Module):
         self.register_buffer("cos", ang.cos()[None, :, None, :], persistent=False)
         self.register_buffer("sin", ang.sin()[None, :, None, :], persistent=False)
 
+    ac = "full"  # "selective": keep matmul and attention outputs, recompute the rest (torch's policy API)
+
     def forward(self, tok, tgt):
         x = self.emb(tok)
         for l in self.layers:
-            x = checkpoint(l, x, self.cos, self.sin, use_reentrant=False)
+            if self.ac == "selective":
+                x = checkpoint(l, x, self.cos, self.sin, use_reentrant=False, context_fn=_selective_contexts)
+            else:
+                x = checkpoint(l, x, self.cos, self.sin, use_reentrant=False)
         logits = self.head(self.norm(x))
         return F.cross_entropy(logits.view(-1, logits.shape[-1]).float(), tgt.reshape(-1))
 
@@ -72,6 +90,7 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--ac", default="full", choices=["full", "selective"])
     a = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -83,6 +102,7 @@ def main():
     torch.manual_seed(0)
     with torch.device(dev):
         model = Model(L=a.layers).to(torch.bfloat16)
+        model.ac = a.ac
     for p in model.parameters():
         if p.dim() > 1:
             nn.init.normal_(p, std=0.02)
@@ -124,7 +144,7 @@ def main():
                           "note": "bf16 parameters and bf16 AdamW state (torch fused AdamW on bf16 params); no fp32 master",
                           "value": round(world * T * a.steps / (ms / 1e3), 1), "unit": "tokens/s", "n_gpus": world,
                           "ms_per_step": round(ms / a.steps, 3), "loss": round(float(loss), 4),
-                          "layers": a.layers}), flush=True)
+                          "layers": a.layers, "activation_checkpointing": a.ac}), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
