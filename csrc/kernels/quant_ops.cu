@@ -219,20 +219,27 @@ wq_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ 
     for (int c = 0; c < kGemvCols; ++c)
 #pragma unroll
       for (int r = 0; r < kRows / 2; ++r) acc[c][r] = make_float2(0.f, 0.f);
-    for (int k0 = lane * 16; k0 < K; k0 += 32 * 16) {
-      // packed weights of the kCols columns first (independent global loads in flight)
-      uint32_t wq[kGemvCols][4];
+    // the packed weights of step i + 1 are requested before the arithmetic of step i: the HBM
+    // latency of the only stream that comes from DRAM hides behind the FMAs
+    auto load_w = [&](int k0, uint32_t (&dst)[kGemvCols][4]) {
 #pragma unroll
       for (int c = 0; c < kGemvCols; ++c) {
         const int n = min(n0 + c, N - 1);
-        if (BITS == 8) {
+        if (k0 >= K) {
+          dst[c][0] = dst[c][1] = dst[c][2] = dst[c][3] = 0;
+        } else if (BITS == 8) {
           const uint4 v = __ldg(reinterpret_cast<const uint4*>(w + (size_t)n * K + k0));
-          wq[c][0] = v.x; wq[c][1] = v.y; wq[c][2] = v.z; wq[c][3] = v.w;
+          dst[c][0] = v.x; dst[c][1] = v.y; dst[c][2] = v.z; dst[c][3] = v.w;
         } else {
           const uint2 v = __ldg(reinterpret_cast<const uint2*>(w + (size_t)n * (K / 2) + k0 / 2));
-          wq[c][0] = v.x; wq[c][1] = v.y; wq[c][2] = 0; wq[c][3] = 0;
+          dst[c][0] = v.x; dst[c][1] = v.y; dst[c][2] = 0; dst[c][3] = 0;
         }
       }
+    };
+    uint32_t wq[kGemvCols][4], wn[kGemvCols][4];
+    load_w(lane * 16, wq);
+    for (int k0 = lane * 16; k0 < K; k0 += 32 * 16) {
+      load_w(k0 + 32 * 16, wn);
       // activations of this k slice: xr[j][r / 2] = (x[r][k0 + j], x[r + 1][k0 + j])
       float2 xr[16][kRows / 2];
 #pragma unroll
@@ -278,6 +285,10 @@ wq_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ 
           for (int r = 0; r < kRows / 2; ++r) acc[c][r] = __ffma2_rn(xr[j][r], w2, acc[c][r]);
         }
       }
+#pragma unroll
+      for (int c = 0; c < kGemvCols; ++c)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) wq[c][i] = wn[c][i];
     }
 #pragma unroll
     for (int c = 0; c < kGemvCols; ++c) {
