@@ -151,69 +151,95 @@ class _Ring:
             self._barrier()  # peers are done reading this rank's chunk before it is overwritten
 
 
-def _chunks(rank: int, world: int, causal: bool) -> List[int]:
-    """Ring order of the K/V chunks that rank attends to (own chunk first)."""
-    order = [(rank - s) % world for s in range(world)]
-    return [c for c in order if not causal or c <= rank]
+def _gids(rank: int, world: int, zigzag: bool) -> List[int]:
+    """Global chunk ids of the parts a rank holds: one contiguous chunk, or (load-balanced for causal
+    masks) chunk ``rank`` from the head and chunk ``2 * world - 1 - rank`` from the tail."""
+    return [rank, 2 * world - 1 - rank] if zigzag else [rank]
+
+
+def _plan(rank: int, world: int, causal: bool, zigzag: bool):
+    """Ring order of the peers this rank needs and, per peer, the (q part, kv part, causal) pairs."""
+    mine = _gids(rank, world, zigzag)
+    steps = []
+    for s in range(world):
+        c = (rank - s) % world
+        pairs = []
+        for p, gi in enumerate(mine):
+            for pp, gj in enumerate(_gids(c, world, zigzag)):
+                if causal and gj > gi:
+                    continue  # that chunk lies entirely in this part's future
+                pairs.append((p, pp, causal and gi == gj))
+        if pairs:
+            steps.append((c, pairs))
+    return steps
 
 
 class _RingAttnFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, causal, scale, group):
+    def forward(ctx, q, k, v, causal, scale, group, zigzag):
         ring = _Ring(k, v, group)
         rank, world = ring.rank, ring.world
-        order = _chunks(rank, world, causal)
-        acc = lse = None
-        if len(order) > 1:
-            ring.prefetch(order[1], 1)
-        for i, c in enumerate(order):
+        steps = _plan(rank, world, causal, zigzag)
+        P = 2 if zigzag else 1
+        Tc = q.shape[1] // P
+        acc, lse = [None] * P, [None] * P
+        if len(steps) > 1:
+            ring.prefetch(steps[1][0], 1)
+        for i, (c, pairs) in enumerate(steps):
             kc, vc = ring.get(c)
-            if q.is_cuda:
-                o_s, lse_s = flash_fwd(q, kc, vc, causal and c == rank, scale)
-            else:
-                o_s, lse_s, _ = _ref_attn_lse(q, kc, vc, causal and c == rank, scale)
-            acc, lse = merge_partials(acc, lse, o_s, lse_s)
+            for p, pp, cz in pairs:
+                qp = q[:, p * Tc: (p + 1) * Tc]
+                kp, vp = kc[:, pp * Tc: (pp + 1) * Tc], vc[:, pp * Tc: (pp + 1) * Tc]
+                if q.is_cuda:
+                    o_s, lse_s = flash_fwd(qp, kp, vp, cz, scale)
+                else:
+                    o_s, lse_s, _ = _ref_attn_lse(qp, kp, vp, cz, scale)
+                acc[p], lse[p] = merge_partials(acc[p], lse[p], o_s, lse_s)
             # staging buffer i & 1 is free once the kernels just enqueued have read it: the pull of
-            # chunk i + 2 is ordered after them and overlaps with the attention over chunk i + 1
-            if i + 2 < len(order):
-                ring.prefetch(order[i + 2], i & 1)
+            # the next-but-one peer is ordered after them and overlaps with the next step's attention
+            if i + 2 < len(steps):
+                ring.prefetch(steps[i + 2][0], i & 1)
         ring.close()
-        out = acc.to(q.dtype)
-        ctx.save_for_backward(q, k, v, out, lse)
-        ctx.causal, ctx.scale, ctx.group = causal, scale, group
+        out = torch.cat([a.to(q.dtype) for a in acc], dim=1)
+        ctx.save_for_backward(q, k, v, out, *lse)
+        ctx.causal, ctx.scale, ctx.group, ctx.zigzag = causal, scale, group, zigzag
         return out
 
     @staticmethod
     def backward(ctx, do):
-        q, k, v, out, lse = ctx.saved_tensors
-        causal, scale, group = ctx.causal, ctx.scale, ctx.group
+        q, k, v, out = ctx.saved_tensors[:4]
+        lse = ctx.saved_tensors[4:]
+        causal, scale, group, zigzag = ctx.causal, ctx.scale, ctx.group, ctx.zigzag
         ring = _Ring(k, v, group)
         rank, world = ring.rank, ring.world
-        order = _chunks(rank, world, causal)
+        steps = _plan(rank, world, causal, zigzag)
+        P = 2 if zigzag else 1
+        Tc = q.shape[1] // P
+        do = do.contiguous()
         dq = torch.zeros_like(q, dtype=torch.float32)
         dkv = torch.zeros((world, 2) + tuple(k.shape), dtype=torch.float32, device=k.device)
-        if len(order) > 1:
-            ring.prefetch(order[1], 1)
-        for i, c in enumerate(order):
+        if len(steps) > 1:
+            ring.prefetch(steps[1][0], 1)
+        for i, (c, pairs) in enumerate(steps):
             kc, vc = ring.get(c)
-            if q.is_cuda:
-                dq_s, dk_s, dv_s = flash_bwd(do, q, kc, vc, out, lse, causal and c == rank, scale)
-            else:
-                dq_s, dk_s, dv_s = _ref_bwd(do, q, kc, vc, out, lse, causal and c == rank, scale)
-            dq += dq_s.float()
-            dkv[c, 0] = dk_s.float()
-            dkv[c, 1] = dv_s.float()
-            if i + 2 < len(order):
-                ring.prefetch(order[i + 2], i & 1)
+            for p, pp, cz in pairs:
+                sl, sk = slice(p * Tc, (p + 1) * Tc), slice(pp * Tc, (pp + 1) * Tc)
+                args = (do[:, sl], q[:, sl], kc[:, sk], vc[:, sk], out[:, sl], lse[p], cz, scale)
+                dq_s, dk_s, dv_s = flash_bwd(*args) if q.is_cuda else _ref_bwd(*args)
+                dq[:, sl] += dq_s.float()
+                dkv[c, 0, :, sk] += dk_s.float()
+                dkv[c, 1, :, sk] += dv_s.float()
+            if i + 2 < len(steps):
+                ring.prefetch(steps[i + 2][0], i & 1)
         ring.close()
-        # partials for chunk c go back to rank c, summed over the ranks that attended it
+        # partials for the chunks of rank c go back to rank c, summed over the ranks that attended them
         mine = torch.empty((2,) + tuple(k.shape), dtype=torch.float32, device=k.device)
         if k.is_cuda:
             dist.reduce_scatter_tensor(mine, dkv, group=group)
         else:
             dist.all_reduce(dkv, group=group)
             mine = dkv[rank]
-        return dq.to(q.dtype), mine[0].to(k.dtype), mine[1].to(v.dtype), None, None, None
+        return dq.to(q.dtype), mine[0].to(k.dtype), mine[1].to(v.dtype), None, None, None, None
 
 
 def _ref_bwd(do, q, k, v, out, lse, causal, scale):
@@ -243,35 +269,49 @@ def _ref_bwd(do, q, k, v, out, lse, causal, scale):
 
 
 def ring_attention(q: Tensor, k: Tensor, v: Tensor, causal: bool = True, scale: Optional[float] = None,
-                   group=None) -> Tensor:
-    """Attention over a sequence sharded contiguously across ``group``; inputs and output are this
-    rank's chunk, ``[B, T_local, H, D]``."""
+                   group=None, load_balance: bool = False) -> Tensor:
+    """Attention over a sequence sharded across ``group``; inputs and output are this rank's share,
+    ``[B, T_local, H, D]``. ``load_balance=False``: rank r holds the r-th contiguous chunk.
+    ``load_balance=True`` (for causal masks): the sequence is cut into ``2 * world`` chunks and rank r
+    holds chunks ``r`` and ``2 * world - 1 - r`` (see :func:`context_parallel_shard`), so that every
+    rank attends the same number of chunk pairs."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     if not dist.is_initialized() or dist.get_world_size(group) == 1:
         from ..ops.attention import flash_attention
         return flash_attention(q, k, v, causal, scale)
-    return _RingAttnFn.apply(q.contiguous(), k.contiguous(), v.contiguous(), causal, scale, group)
+    if load_balance and q.shape[1] % 2:
+        raise ValueError("load-balanced context parallelism needs an even local sequence length")
+    return _RingAttnFn.apply(q.contiguous(), k.contiguous(), v.contiguous(), causal, scale, group, bool(load_balance))
 
 
 # ---------------------------------------------------------------------------- sharding helpers
-def context_parallel_shard(buffers: Sequence[Tensor], seq_dims: Sequence[int], group=None) -> List[Tensor]:
-    """This rank's contiguous chunk of every buffer along its sequence dim (length divisible by world)."""
+def context_parallel_shard(buffers: Sequence[Tensor], seq_dims: Sequence[int], group=None,
+                           load_balance: bool = False) -> List[Tensor]:
+    """This rank's share of every buffer along its sequence dim: the rank-th contiguous chunk, or with
+    ``load_balance`` the head chunk ``rank`` and the tail chunk ``2 * world - 1 - rank`` of ``2 * world``
+    chunks, concatenated (tensorplay/distributed/tensor/experimental/_context_parallel/_load_balancer.py:26-47)."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
+    n = 2 * world if load_balance else world
     out = []
     for b, d in zip(buffers, seq_dims):
-        if b.shape[d] % world:
-            raise ValueError(f"sequence length {b.shape[d]} is not divisible by the context-parallel size {world}")
-        out.append(b.chunk(world, dim=d)[rank].contiguous())
+        if b.shape[d] % n:
+            raise ValueError(f"sequence length {b.shape[d]} is not divisible by {n}")
+        ch = b.chunk(n, dim=d)
+        out.append(torch.cat((ch[rank], ch[n - 1 - rank]), dim=d).contiguous() if load_balance else ch[rank].contiguous())
     return out
 
 
-def context_parallel_unshard(buffers: Sequence[Tensor], seq_dims: Sequence[int], group=None) -> List[Tensor]:
-    """All-gather the chunks back into full sequences."""
+def context_parallel_unshard(buffers: Sequence[Tensor], seq_dims: Sequence[int], group=None,
+                             load_balance: bool = False) -> List[Tensor]:
+    """All-gather the shares back into full sequences (undoing the head-tail interleave if used)."""
     world = dist.get_world_size(group)
     out = []
     for b, d in zip(buffers, seq_dims):
         parts = [torch.empty_like(b) for _ in range(world)]
         dist.all_gather(parts, b.contiguous(), group=group)
+        if load_balance:
+            halves = [p.chunk(2, dim=d) for p in parts]
+            parts = [h[0] for h in halves] + [h[1] for h in reversed(halves)]
         out.append(torch.cat(parts, dim=d))
     return out
 

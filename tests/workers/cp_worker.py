@@ -85,6 +85,26 @@ def main():
             if not e < 2e-2:
                 res["ok"] = False
                 res["msgs"].append(f"ring causal={causal} {name} rel {e}")
+    # ---- load-balanced (head-tail) sharding for the causal mask
+    torch.manual_seed(2)
+    B, T, Hq, Hkv, D = 1, 256 * 2 * world, 8, 2, 128
+    q = torch.randn(B, T, Hq, D, device=dev, dtype=torch.bfloat16)
+    k = torch.randn(B, T, Hkv, D, device=dev, dtype=torch.bfloat16)
+    v = torch.randn(B, T, Hkv, D, device=dev, dtype=torch.bfloat16)
+    go = torch.randn(B, T, Hq, D, device=dev, dtype=torch.bfloat16)
+    qr, kr, vr = (t.float().requires_grad_() for t in (q, k, v))
+    ref = attention_reference(qr, kr, vr, True)
+    ref.backward(go.float())
+    ql, kl, vl, gl = (t.detach().requires_grad_() for t in
+                      context_parallel_shard([q, k, v, go], [1, 1, 1, 1], load_balance=True))
+    out = ring_attention(ql, kl, vl, True, load_balance=True)
+    out.backward(gl.detach())
+    wants = context_parallel_shard([ref.detach(), qr.grad, kr.grad, vr.grad], [1, 1, 1, 1], load_balance=True)
+    for name, a, b in zip(("o", "dq", "dk", "dv"), (out, ql.grad, kl.grad, vl.grad), wants):
+        e = rel(a, b)
+        if not e < 2e-2:
+            res["ok"] = False
+            res["msgs"].append(f"ring zigzag {name} rel {e}")
     torch.cuda.synchronize()
     try:
         O.check_status()
