@@ -106,8 +106,11 @@ class _ShardedParam:
         self.module._parameters[self.name] = self.sharded
         self.unsharded = None
 
-    def reduce_scatter_grad(self, divide: float, reduce_grads: bool = True) -> None:
-        g = self.unsharded.grad if self.unsharded is not None else None
+    def reduce_scatter_grad(self, divide: float, reduce_grads: bool = True, full: Optional[torch.Tensor] = None) -> None:
+        """Reduce the gradient held by ``full`` (the gathered tensor one forward computed with; the
+        currently gathered one by default) into the shard's ``.grad``, accumulating."""
+        full = full if full is not None else self.unsharded
+        g = full.grad if full is not None else None
         if g is None:
             return
         rd = self.mp.reduce_dtype or g.dtype
@@ -130,7 +133,7 @@ class _ShardedParam:
             self.sharded.grad = shard_grad.reshape(self.sharded.shape).clone()
         else:
             self.sharded.grad.add_(shard_grad.reshape(self.sharded.shape))
-        self.unsharded.grad = None
+        full.grad = None
 
 
 def setattr_param(module: nn.Module, name: str, p: nn.Parameter) -> None:
@@ -238,16 +241,18 @@ class _FSDPState:
             self.is_unsharded = False
         return output
 
-    def post_backward(self) -> None:
-        for p in self.params:
-            full = p.unsharded if p.unsharded is not None else getattr(p, "kept", None)
+    def post_backward(self, fulls: Optional[list] = None) -> None:
+        """``fulls``: the gathered tensors of the forward whose backward just finished. Several
+        forwards may precede the first backward (pipeline micro-batches), each with its own gathered
+        copies, so the gradients are read from the copies that forward used."""
+        for i, p in enumerate(self.params):
+            full = fulls[i] if fulls is not None else (
+                p.unsharded if p.unsharded is not None else getattr(p, "kept", None))
             if full is None:
                 continue
-            p.unsharded = full
-            p.reduce_scatter_grad(self.divide, self.reduce_grads)
-            p.kept = None
-            if self.reshard_after_backward or not self.is_unsharded:
-                p.unsharded = None
+            p.reduce_scatter_grad(self.divide, self.reduce_grads, full)
+            if getattr(p, "kept", None) is full:
+                p.kept = None
         if self.reshard_after_backward:
             self.reshard()
 
@@ -271,21 +276,21 @@ class _PostBackward(torch.autograd.Function):
 def _register_post_backward(state: _FSDPState, output):
     # Hook a callback on the module's parameters' accumulation: run post_backward once all of the
     # unit's unsharded tensors have received their gradient.
-    pending = {"n": sum(1 for p in state.params if p.sharded.requires_grad)}
+    fulls = [p.unsharded for p in state.params]
+    pending = {"n": sum(1 for t in fulls if t is not None and t.requires_grad)}
     total = pending["n"]
 
-    def make(p):
-        def hook(_):
-            pending["n"] -= 1
-            if pending["n"] == 0:
-                pending["n"] = total
-                state.post_backward()
-        return hook
+    def hook(_):
+        pending["n"] -= 1
+        if pending["n"] == 0:
+            pending["n"] = total
+            state.post_backward(fulls)
 
-    for p in state.params:
-        t = p.unsharded
-        if t is not None and t.requires_grad:
-            t.register_post_accumulate_grad_hook(make(p))
+    for t in fulls:
+        # a unit kept gathered across forwards reuses its tensors: one set of hooks serves them all
+        if t is not None and t.requires_grad and not getattr(t, "_tpb_hooked", False):
+            t.register_post_accumulate_grad_hook(hook)
+            t._tpb_hooked = True
     return output
 
 
