@@ -13,6 +13,7 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import tensorplay_b200.ops as O  # noqa: E402
+from tensorplay_b200.ops.quant import gemv_config  # noqa: E402
 
 
 def timeit(fn, iters=10, warmup=3):
@@ -62,10 +63,15 @@ def main():
             i[0] += 1
             O.weight_only_linear(x, q, s, z, None, bits, group)
 
-        t = timeit(run, iters=16)
         wbytes = N * K * bits // 8
-        out.append({"kernel": f"W{bits}A16 GEMV", "shape": [M, N, K], "group": group, "ms": round(t, 4),
-                    "weight_gbs": round(wbytes / t / 1e6, 1), "fraction_of_measured_hbm": round(wbytes / t / 1e6 / hbm, 3)})
+        for label, tiles, simt in (("warp-MMA, chosen tiles", 0, False), ("warp-MMA, 1 tile per CTA", 1, False),
+                                   ("warp-MMA, 2 tiles per CTA", 2, False), ("CUDA-core FMA kernel", 0, True)):
+            gemv_config(tiles, simt)
+            t = timeit(run, iters=16)
+            out.append({"kernel": f"W{bits}A16 GEMV ({label})", "shape": [M, N, K], "group": group,
+                        "ms": round(t, 4), "weight_gbs": round(wbytes / t / 1e6, 1),
+                        "fraction_of_measured_hbm": round(wbytes / t / 1e6 / hbm, 3)})
+        gemv_config(0, False)
     O.check_status()
     for o in out:
         print(json.dumps(o), flush=True)

@@ -310,6 +310,160 @@ wq_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ 
   }
 }
 
+// ------------------------------------------------------------------ weight-only GEMV on the warp MMA
+// Same contract as wq_gemv_kernel, for K that is a multiple of the chunk (64 k for 8-bit, 128 k
+// for 4-bit). With at most 8 rows of x the op is bound by streaming the packed weights, and the
+// CUDA-core version spends 8 FMAs per weight; here the weights of 16 output columns form the
+// 16 x 16 A tile of mma.sync.m16n8k16 and the (up to) 8 rows of x its 16 x 8 B tile, so a weight
+// costs only its dequantisation (3-5 instructions). tcgen05 needs the operands in shared memory
+// and a 64/128-row accumulator in TMEM: for an 8-row product the warp-level MMA, fed straight from
+// the registers the weights were loaded into, is the shorter path. The sum over k is order-free, so
+// lane (g, t) takes 16 consecutive bytes of weight rows g and g + 8 (16 or 32 k) and the matching
+// k of x row g: every global load is a full 16-byte vector and no shuffles are needed.
+// A CTA owns TILES x 16 output columns; its 8 warps split K and reduce through shared memory.
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                               uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+template <int BITS, int TILES>
+__global__ void __launch_bounds__(256)
+wq_gemv_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ w,
+                   const __nv_bfloat16* __restrict__ scale, const __nv_bfloat16* __restrict__ zero,
+                   const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ y, int M, int N,
+                   int K, int group, long long ldx, long long ldy) {
+  constexpr int KL = BITS == 8 ? 16 : 32;  // k per lane per chunk = 16 bytes of packed weights
+  constexpr int CH = 4 * KL;
+  __shared__ float red[8][TILES * 128];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int n_base = blockIdx.x * TILES * 16;
+  const int n_chunks = K / CH;
+  const int gpr = group > 0 ? K / group : 1;
+  const size_t row_bytes = BITS == 8 ? (size_t)K : (size_t)K / 2;
+  int rown[TILES][2];
+#pragma unroll
+  for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) rown[tl][h] = min(n_base + tl * 16 + g + 8 * h, N - 1);
+  float acc[TILES][4];
+#pragma unroll
+  for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[tl][i] = 0.f;
+
+  auto load_w = [&](int c, uint4 (&dst)[TILES][2]) {
+    const size_t off = (size_t)(c * CH + t * KL) * BITS / 8;
+#pragma unroll
+    for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+        dst[tl][h] = __ldg(reinterpret_cast<const uint4*>(w + (size_t)rown[tl][h] * row_bytes + off));
+  };
+  uint4 cur[TILES][2], nxt[TILES][2];
+  int c = warp;
+  if (c < n_chunks) load_w(c, cur);
+  for (; c < n_chunks; c += 8) {
+    if (c + 8 < n_chunks) load_w(c + 8, nxt);
+    const int k = c * CH + t * KL;
+    uint32_t xw[KL / 2];
+    if (g < M) {
+      const uint4* xp = reinterpret_cast<const uint4*>(x + (size_t)g * ldx + k);
+#pragma unroll
+      for (int i = 0; i < KL / 8; ++i) {
+        const uint4 v = __ldg(xp + i);
+        xw[4 * i + 0] = v.x; xw[4 * i + 1] = v.y; xw[4 * i + 2] = v.z; xw[4 * i + 3] = v.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < KL / 2; ++i) xw[i] = 0u;
+    }
+#pragma unroll
+    for (int tl = 0; tl < TILES; ++tl) {
+      float sc[2] = {1.f, 1.f}, zs[2] = {0.f, 0.f};
+      if (group > 0 || BITS == 4) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const size_t idx = (size_t)rown[tl][h] * gpr + (group > 0 ? k / group : 0);
+          sc[h] = __bfloat162float(scale[idx]);
+          if (BITS == 4) zs[h] = -(zero ? __bfloat162float(zero[idx]) : 8.f) * sc[h];
+        }
+      }
+      const uint32_t wv[2][4] = {{cur[tl][0].x, cur[tl][0].y, cur[tl][0].z, cur[tl][0].w},
+                                 {cur[tl][1].x, cur[tl][1].y, cur[tl][1].z, cur[tl][1].w}};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (BITS == 8) {
+          uint32_t a[2][2];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint32_t q = wv[h][i] ^ 0x80808080u;  // signed byte -> biased code, value = code - 128
+            float f[4];
+            f[0] = __uint_as_float(__byte_perm(q, 0x4B000000u, 0x7440)) - 8388736.f;
+            f[1] = __uint_as_float(__byte_perm(q, 0x4B000000u, 0x7441)) - 8388736.f;
+            f[2] = __uint_as_float(__byte_perm(q, 0x4B000000u, 0x7442)) - 8388736.f;
+            f[3] = __uint_as_float(__byte_perm(q, 0x4B000000u, 0x7443)) - 8388736.f;
+            if (group > 0) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) f[j] *= sc[h];
+            }
+            a[h][0] = pack_bf16x2(f[0], f[1]);
+            a[h][1] = pack_bf16x2(f[2], f[3]);
+          }
+          mma_bf16_16816(acc[tl], a[0][0], a[1][0], a[0][1], a[1][1], xw[2 * i], xw[2 * i + 1]);
+        } else {
+          uint32_t a[2][4];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint32_t q = wv[h][i];
+            float f[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float code = __uint_as_float(((q >> (4 * j)) & 0xfu) | 0x4B000000u) - 8388608.f;
+              f[j] = fmaf(code, sc[h], zs[h]);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) a[h][j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
+          }
+          mma_bf16_16816(acc[tl], a[0][0], a[1][0], a[0][1], a[1][1], xw[4 * i], xw[4 * i + 1]);
+          mma_bf16_16816(acc[tl], a[0][2], a[1][2], a[0][3], a[1][3], xw[4 * i + 2], xw[4 * i + 3]);
+        }
+      }
+    }
+#pragma unroll
+    for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) cur[tl][h] = nxt[tl][h];
+  }
+#pragma unroll
+  for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) red[warp][tl * 128 + lane * 4 + i] = acc[tl][i];
+  __syncthreads();
+  for (int o = threadIdx.x; o < TILES * 128; o += 256) {
+    float a = 0.f;
+#pragma unroll
+    for (int wi = 0; wi < 8; ++wi) a += red[wi][o];
+    // accumulator element (lane l, register ci) = (column g + 8 * (ci / 2), row 2 t + (ci & 1))
+    const int tl = o >> 7, l = (o >> 2) & 31, ci = o & 3;
+    const int n = n_base + tl * 16 + (l >> 2) + ((ci & 2) ? 8 : 0);
+    const int r = 2 * (l & 3) + (ci & 1);
+    if (n < N && r < M) {
+      if (group <= 0 && BITS == 8) a *= __bfloat162float(scale[n]);  // per-channel scale applied once
+      if (bias) a += __bfloat162float(bias[n]);
+      y[(size_t)r * ldy + n] = __float2bfloat16(a);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ quantise / dequantise
 // Rowwise symmetric int8: scale = absmax / 127 per row; one CTA per row.
 __global__ void __launch_bounds__(256)
@@ -468,6 +622,15 @@ int tpb_gemm_i8(const void* A, const void* B, void* C, const float* a_scale, con
   return (int)cudaGetLastError();
 }
 
+static int g_gemv_tiles = 0;       // 0: pick by N; 1 / 2: 16-column tiles per CTA of the MMA kernel
+static int g_gemv_force_simt = 0;  // 1: always the CUDA-core kernel (for comparison runs)
+// Tuning / comparison knobs of the weight-only GEMV (process-wide).
+int tpb_wq_gemv_config(int tiles, int force_simt) {
+  g_gemv_tiles = (tiles == 1 || tiles == 2) ? tiles : 0;
+  g_gemv_force_simt = force_simt ? 1 : 0;
+  return 0;
+}
+
 // bits = 8: W int8 [N, K], scale bf16 [N, K/group] (group = 0: one scale per row).
 // bits = 4: W uint8 [N, K/2] (two codes per byte, low nibble first), group-wise (group % 16 == 0).
 int tpb_wq_gemv(const void* x, const void* w, const void* scale, const void* zero, const void* bias,
@@ -479,6 +642,13 @@ int tpb_wq_gemv(const void* x, const void* w, const void* scale, const void* zer
   if (group > 0 && (K % group || group % 16)) return -4;
   if (bits == 4 && group <= 0) return -4;
   auto st = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16 *sc = (const __nv_bfloat16*)scale, *zp = (const __nv_bfloat16*)zero,
+                      *bs = (const __nv_bfloat16*)bias;
+  const int chunk = bits == 8 ? 64 : 128;
+  const bool mma_ok = !g_gemv_force_simt && K % chunk == 0 && (group <= 0 || group % (chunk / 4) == 0) &&
+                      (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+  // two 16-column tiles per CTA halve the reads of x; one keeps more CTAs in flight when N is short
+  const int tiles = g_gemv_tiles ? g_gemv_tiles : ((N + 31) / 32 >= sm_count() * 8 ? 2 : 1);
   const int n_groups = (N + kGemvCols - 1) / kGemvCols;
   int grid = (n_groups + 7) / 8;
   const int cap = sm_count() * 4;
@@ -487,14 +657,22 @@ int tpb_wq_gemv(const void* x, const void* w, const void* scale, const void* zer
     const __nv_bfloat16* xs = (const __nv_bfloat16*)x + (size_t)m0 * ldx;
     __nv_bfloat16* ys = (__nv_bfloat16*)y + (size_t)m0 * ldy;
     const int rows = M - m0 < 8 ? M - m0 : 8;
-    if (bits == 8)
-      wq_gemv_kernel<8><<<grid, 256, 0, st>>>(xs, (const uint8_t*)w, (const __nv_bfloat16*)scale,
-                                              (const __nv_bfloat16*)zero, (const __nv_bfloat16*)bias, ys, rows, N,
-                                              K, group, ldx, ldy);
-    else
-      wq_gemv_kernel<4><<<grid, 256, 0, st>>>(xs, (const uint8_t*)w, (const __nv_bfloat16*)scale,
-                                              (const __nv_bfloat16*)zero, (const __nv_bfloat16*)bias, ys, rows, N,
-                                              K, group, ldx, ldy);
+    const uint8_t* wp = (const uint8_t*)w;
+    if (mma_ok) {
+      const int g2 = (N + 16 * tiles - 1) / (16 * tiles);
+      if (bits == 8 && tiles == 2)
+        wq_gemv_mma_kernel<8, 2><<<g2, 256, 0, st>>>(xs, wp, sc, zp, bs, ys, rows, N, K, group, ldx, ldy);
+      else if (bits == 8)
+        wq_gemv_mma_kernel<8, 1><<<g2, 256, 0, st>>>(xs, wp, sc, zp, bs, ys, rows, N, K, group, ldx, ldy);
+      else if (tiles == 2)
+        wq_gemv_mma_kernel<4, 2><<<g2, 256, 0, st>>>(xs, wp, sc, zp, bs, ys, rows, N, K, group, ldx, ldy);
+      else
+        wq_gemv_mma_kernel<4, 1><<<g2, 256, 0, st>>>(xs, wp, sc, zp, bs, ys, rows, N, K, group, ldx, ldy);
+    } else if (bits == 8) {
+      wq_gemv_kernel<8><<<grid, 256, 0, st>>>(xs, wp, sc, zp, bs, ys, rows, N, K, group, ldx, ldy);
+    } else {
+      wq_gemv_kernel<4><<<grid, 256, 0, st>>>(xs, wp, sc, zp, bs, ys, rows, N, K, group, ldx, ldy);
+    }
   }
   return (int)cudaGetLastError();
 }

@@ -50,6 +50,7 @@ _KERNEL_SIGS = {
     "tpb_clip_coef": [P, F, P, P, P],
     "tpb_gemm_i8": [P, P, P, P, P, P, I, I, I, I, I, I, P, P],
     "tpb_wq_gemv": [P, P, P, P, P, P, I, I, I, I, I, LL, LL, P],
+    "tpb_wq_gemv_config": [I, I],
     "tpb_quant_i8_rowwise": [P, P, P, I, I, LL, P],
     "tpb_dequant_weight": [P, P, P, P, I, I, I, I, P],
     "tpb_fp8_quant": [P, P, P, LL, I, I, I, P],

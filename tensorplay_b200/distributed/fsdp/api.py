@@ -113,12 +113,25 @@ class _ShardedParam:
         g = full.grad if full is not None else None
         if g is None:
             return
+        full.grad = None
+        acc = getattr(self, "unreduced", None)
+        if not reduce_grads:
+            # gradient synchronisation is off (accumulation steps): keep the full-size sum locally
+            # until a backward with synchronisation on reduces it
+            self.unreduced = g if acc is None else acc.add_(g)
+            return
+        if acc is not None:
+            g = acc.add_(g)
+            self.unreduced = None
         rd = self.mp.reduce_dtype or g.dtype
         n0 = self.full_shape[0] if len(self.full_shape) else 1
         g2 = g.reshape((n0,) + tuple(g.shape[1:]) if g.dim() else (1,)).to(rd)
-        padded = torch.zeros((self.world * self.chunk,) + tuple(g2.shape[1:]), dtype=rd, device=g.device)
-        padded[:n0].copy_(g2)
-        if self.world > 1 and reduce_grads:
+        if self.world * self.chunk == n0:
+            padded = g2.contiguous()
+        else:
+            padded = torch.zeros((self.world * self.chunk,) + tuple(g2.shape[1:]), dtype=rd, device=g.device)
+            padded[:n0].copy_(g2)
+        if self.world > 1:
             out = torch.empty((self.chunk,) + tuple(g2.shape[1:]), dtype=rd, device=g.device)
             if dist.get_backend(self.group) == "gloo":
                 dist.all_reduce(padded, group=self.group)
@@ -133,7 +146,6 @@ class _ShardedParam:
             self.sharded.grad = shard_grad.reshape(self.sharded.shape).clone()
         else:
             self.sharded.grad.add_(shard_grad.reshape(self.sharded.shape))
-        full.grad = None
 
 
 def setattr_param(module: nn.Module, name: str, p: nn.Parameter) -> None:

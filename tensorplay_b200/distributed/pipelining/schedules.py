@@ -32,19 +32,30 @@ class PipelineScheduleSingle:
         self._wrapped = None
 
     def _sync_wrappers(self, enable: bool) -> None:
-        """DDP-wrapped stages reduce only on the last micro-batch's backward."""
+        """DDP- and FSDP-wrapped stages reduce only on the last micro-batch's backward (the earlier
+        micro-batches accumulate locally)."""
         m = self.stage.submod
         if hasattr(m, "require_backward_grad_sync"):
             m.require_backward_grad_sync = enable
+        elif hasattr(m, "set_requires_gradient_sync"):
+            m.set_requires_gradient_sync(enable)
+            if not m._fsdp_state.reshard_after_forward:
+                # parameters kept gathered across the step's micro-batches: shard them again only
+                # after the last backward
+                m.set_reshard_after_backward(enable)
 
-    def step(self, *args, target=None, losses: Optional[List] = None, **kwargs):
+    def step(self, *args, target=None, losses: Optional[List] = None, return_outputs: bool = True, **kwargs):
+        """``return_outputs=False``: the last stage drops each micro-batch's output once its loss
+        exists (no merged copy of, say, the logits of the whole batch)."""
         st = self.stage
+        st.keep_outputs = return_outputs
         a_chunks, k_chunks = split_args_kwargs_into_chunks(args, kwargs, self.n) if st.is_first else ([()] * self.n, [{}] * self.n)
         t_chunks = list(torch.chunk(target, self.n)) if (st.is_last and target is not None) else [None] * self.n
         self._step_microbatches(a_chunks, k_chunks, t_chunks)
         out = None
         if st.is_last:
-            out = merge_chunks([st.outputs[i].detach() for i in range(self.n)])
+            if return_outputs:
+                out = merge_chunks([st.outputs[i].detach() for i in range(self.n)])
             if losses is not None:
                 losses.extend(st.losses[i] for i in range(self.n))
         st.outputs.clear()

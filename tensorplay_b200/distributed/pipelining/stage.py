@@ -26,13 +26,22 @@ class PipelineStage:
         self.prev_rank = (stage_index - 1) % self.group_size
         self.next_rank = (stage_index + 1) % self.group_size
         self.fwd_cache: Dict[int, tuple] = {}
-        self.in_meta: Optional[tuple] = None
-        self.out_meta: Optional[tuple] = None
+        # example tensors given up front fix the activation shapes and skip the first-step hand-shake
+        self.in_meta: Optional[tuple] = self._meta_of(input_args)
+        self.out_meta: Optional[tuple] = self._meta_of(output_args)
         self.grad_scale = 1.0
+        self.keep_outputs = True
         self.outputs: Dict[int, torch.Tensor] = {}
         self.losses: Dict[int, torch.Tensor] = {}
         self.recv_fwd: Dict[int, torch.Tensor] = {}
         self.recv_bwd: Dict[int, torch.Tensor] = {}
+
+    @staticmethod
+    def _meta_of(example) -> Optional[tuple]:
+        if example is None:
+            return None
+        t = example[0] if isinstance(example, (tuple, list)) else example
+        return tuple(t.shape), t.dtype
 
     def _g(self, r: int) -> int:
         return dist.get_global_rank(self.group, r) if self.group is not None else r
@@ -103,7 +112,8 @@ class PipelineStage:
                 x.requires_grad_()
             inputs = (x,)
         out = self.submod(*inputs, **kwargs)
-        self.outputs[mb] = out
+        if self.keep_outputs or not self.is_last:
+            self.outputs[mb] = out
         loss = None
         if self.is_last and loss_fn is not None:
             loss = loss_fn(out, target)

@@ -53,7 +53,12 @@ class LlamaTPBlock(nn.Module):
         cfg, tp = self.cfg, self.tp
         D = cfg.head_dim
         h = ops.rms_norm(x_local, self.attn_norm, cfg.rms_eps)
-        qkv = tp.all_gather_linear(h, self.wqkv).view(B, T, self.hq + 2 * self.hkv, D)
+        qkv = tp.all_gather_linear(h, self.wqkv)
+        if not use_cache and pos0 == 0:
+            # training: RoPE + attention on the packed projection, gradients written back packed
+            o = ops.qkv_attention(qkv.view(B, T, -1), cos, sin, None, self.hq, self.hkv, D, causal=True)
+            return self._after_attention(x_local, o.reshape(B * T, self.hq * D))
+        qkv = qkv.view(B, T, self.hq + 2 * self.hkv, D)
         pos = None
         if pos0:
             pos = torch.arange(pos0, pos0 + T, device=qkv.device).expand(B, T)
@@ -70,12 +75,15 @@ class LlamaTPBlock(nn.Module):
             o = o.transpose(1, 2).reshape(B * T, self.hq * D)
         else:
             o = flash_attention(q, k, v, causal=True).reshape(B * T, self.hq * D)
+        return self._after_attention(x_local, o)
+
+    def _after_attention(self, x_local: Tensor, o: Tensor) -> Tensor:
+        cfg, tp = self.cfg, self.tp
         x_local = x_local + tp.linear_reduce_scatter(o, self.wo)
         h = ops.rms_norm(x_local, self.ffn_norm, cfg.rms_eps)
         gu = tp.all_gather_linear(h, self.w_gate_up)
         a = ops.swiglu_packed(gu)
         return x_local + tp.linear_reduce_scatter(a, self.w_down)
-
 
     def decode(self, x_local: Tensor, B: int, cos: Tensor, sin: Tensor, pos64: Tensor, pos32: Tensor,
                kv_len: Tensor) -> Tensor:
@@ -242,3 +250,82 @@ class LlamaTP(nn.Module):
         g["pos32"] += 1
         g["kv_len"] += 1
         return x
+
+
+class LlamaTPStage(nn.Module):
+    """One pipeline stage of the tensor-parallel Llama for training: ``num_layers / num_stages``
+    blocks, plus the embedding on the first stage and the final norm and LM head on the last.
+
+    Activations between stages are this rank's rows ``[b * T / tp, H]`` of the sequence-parallel
+    residual stream, so a stage talks only to the same tensor-parallel rank of the neighbouring
+    stage. Embedding, norms and LM head are replicated over the tensor-parallel group and see only
+    the local rows: their gradients are summed over that group by ``sync_replicated_grads`` after
+    the backward passes. The last stage returns the logits of its local rows.
+    """
+
+    def __init__(self, cfg: LlamaConfig, tp: TPContext, stage_index: int, num_stages: int, micro_batch: int,
+                 seq_len: int, device=None, dtype=None):
+        super().__init__()
+        kw = {"device": device, "dtype": dtype}
+        assert cfg.num_layers % num_stages == 0 and (micro_batch * seq_len) % tp.world == 0
+        self.cfg, self.tp = cfg, tp
+        self.first, self.last = stage_index == 0, stage_index == num_stages - 1
+        self.b, self.T = micro_batch, seq_len
+        per = cfg.num_layers // num_stages
+        self.embed = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, **kw)) if self.first else None
+        self.layers = nn.ModuleList([LlamaTPBlock(cfg, tp, stage_index * per + i, **kw) for i in range(per)])
+        if self.last:
+            self.final_norm = nn.Parameter(torch.ones(cfg.hidden_size, **kw))
+            self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, **kw))
+        self._rope = None
+
+    def reset_parameters(self, seed: int = 0) -> None:
+        dev = self.layers[0].wqkv.device
+        g_rep = torch.Generator(device=dev).manual_seed(seed)
+        g_loc = torch.Generator(device=dev).manual_seed(seed + 1 + self.tp.rank + 64 * self.layers[0].layer_idx)
+        if self.first:
+            nn.init.normal_(self.embed, std=self.cfg.init_std, generator=g_rep)
+        if self.last:
+            nn.init.normal_(self.lm_head, std=self.cfg.init_std, generator=g_rep)
+        for l in self.layers:
+            l.reset_parameters(g_loc)
+
+    def local_rows(self, t: Tensor) -> Tensor:
+        """This rank's slice of a ``[b, T, ...]`` tensor flattened over (batch, time)."""
+        flat = t.reshape(self.b * self.T, *t.shape[2:])
+        n = flat.shape[0] // self.tp.world
+        return flat[self.tp.rank * n: (self.tp.rank + 1) * n]
+
+    def replicated_parameters(self):
+        """Parameters that every tensor-parallel rank holds in full (by name)."""
+        return [n for n, _ in self.named_parameters()
+                if n.endswith("norm") or n in ("embed", "lm_head")]
+
+    def forward(self, x: Tensor) -> Tensor:
+        if self._rope is None:
+            self._rope = ops.rope_tables(max(self.T, self.cfg.max_seq_len), self.cfg.head_dim, self.cfg.rope_theta,
+                                         device=x.device)
+        cos, sin = self._rope
+        if self.first:
+            x = ops.embedding(self.local_rows(x), self.embed)
+        for l in self.layers:
+            x = l(x, self.b, self.T, cos, sin)
+        if self.last:
+            x = ops.linear(ops.rms_norm(x, self.final_norm, self.cfg.rms_eps), self.lm_head)
+        return x
+
+
+def sync_replicated_grads(module: nn.Module, names, group) -> None:
+    """Sum over the tensor-parallel group the gradients of the parameters ``names`` (those every
+    rank of the group holds in full while seeing only its rows of the sequence): one flat
+    all-reduce."""
+    params = dict(module.named_parameters())
+    grads = [params[n].grad for n in names if n in params and params[n].grad is not None]
+    if not grads or dist.get_world_size(group) == 1:
+        return
+    flat = torch.cat([g.reshape(-1).float() for g in grads])
+    dist.all_reduce(flat, group=group)
+    off = 0
+    for g in grads:
+        g.copy_(flat[off: off + g.numel()].view_as(g))
+        off += g.numel()

@@ -131,6 +131,12 @@ def weight_only_linear(x: Tensor, q: Tensor, scale: Tensor, zero: Optional[Tenso
     return linear(x, w.to(x.dtype), bias)
 
 
+def gemv_config(tiles: int = 0, force_simt: bool = False) -> None:
+    """Knobs of the weight-only GEMV for comparison runs: 16-column tiles per CTA of the warp-MMA
+    kernel (0 = chosen from N) and whether to force the CUDA-core kernel."""
+    lib()._lib.tpb_wq_gemv_config(int(tiles), int(bool(force_simt)))
+
+
 def fp8_quantize(x: Tensor, scale: Tensor, dtype=torch.float8_e4m3fn) -> Tensor:
     """``saturate(x / scale)`` in fp8; ``scale`` is one value or one per row (last dim = row)."""
     per_row = scale.numel() > 1

@@ -27,3 +27,15 @@ def test_generate_example_cache_kinds():
     for kind in ("dynamic", "static", "paged"):
         out = _run(["examples/generate.py", "--new-tokens", "6", "--cache", kind])
         assert "greedy with and without cache agree: True" in out, out
+
+
+def test_composed_layout_benchmark_runs_on_gloo_ranks():
+    """TP2 x PP2 x FSDP1 of the composed-layout benchmark script on four CPU ranks."""
+    import json
+    from tests.distutil import free_port
+    out = _run(["-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "4", "--master-addr", "127.0.0.1",
+                "--master-port", str(free_port()), "benchmarks/bench_llama_3d.py", "--cpu", "--layers", "2",
+                "--seq", "16", "--microbatches", "4", "--steps", "2", "--warmup", "1"])
+    line = json.loads([l for l in out.splitlines() if l.startswith("{")][-1])
+    assert line["config"]["parallelism"].startswith("tp2 x pp2") and line["n_gpus"] == 4
+    assert 3.0 < line["loss"] < 6.0   # ln(128) = 4.85 at random init

@@ -78,3 +78,17 @@ def test_fsdp_symm_pull_kernel_transport():
     r = _run_workers("fsdp_symm_worker.py", n, extra_env={"TPB_COMM_TRANSPORT": "sm"})
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "RESULT" in r.stdout
+
+
+@pytest.mark.skipif(_ngpu() < 4, reason="needs 4 GPUs")
+def test_composed_tp_pp_layout_trains():
+    """TP2 x PP2 of the composed-layout benchmark on a short Llama-shaped model: runs, loss near ln(V)."""
+    import json
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+           os.path.join(ROOT, "benchmarks", "bench_llama_3d.py"), "--layers", "4", "--microbatches", "4",
+           "--seq", "1024", "--steps", "2", "--warmup", "2"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    line = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
+    assert 10.0 < line["loss"] < 13.5, line   # ln(128256) = 11.76

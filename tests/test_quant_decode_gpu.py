@@ -37,11 +37,13 @@ def test_int8_rowwise_quantise():
     assert (q.cpu() != qr).float().mean() < 1e-3
 
 
-@pytest.mark.parametrize("bits,group", [(8, 0), (8, 128), (4, 128), (4, 64)])
+@pytest.mark.parametrize("bits,group,K", [(8, 0, 2048), (8, 128, 2048), (4, 128, 2048), (4, 64, 2048),
+                                          (8, 16, 2048),   # one group per lane slice of the MMA kernel
+                                          (8, 0, 2064), (4, 16, 2064)])  # K off the MMA chunk: CUDA-core kernel
 @pytest.mark.parametrize("M", [1, 3, 16])
-def test_weight_only_gemv(bits, group, M):
+def test_weight_only_gemv(bits, group, K, M):
     torch.manual_seed(1)
-    N, K = 1000, 2048
+    N = 1000
     w = torch.randn(N, K, device=DEV)
     x = torch.randn(M, K, device=DEV).bfloat16()
     bias = torch.randn(N, device=DEV).bfloat16()
