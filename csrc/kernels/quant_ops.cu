@@ -368,24 +368,34 @@ wq_gemv_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restric
       for (int h = 0; h < 2; ++h)
         dst[tl][h] = __ldg(reinterpret_cast<const uint4*>(w + (size_t)rown[tl][h] * row_bytes + off));
   };
-  uint4 cur[TILES][2], nxt[TILES][2];
-  int c = warp;
-  if (c < n_chunks) load_w(c, cur);
-  for (; c < n_chunks; c += 8) {
-    if (c + 8 < n_chunks) load_w(c + 8, nxt);
-    const int k = c * CH + t * KL;
-    uint32_t xw[KL / 2];
+  // x rows of a chunk: KL bf16 of row g (zeros past M); requested one chunk ahead like the weights,
+  // so that neither stream's latency sits on the loop's critical path
+  auto load_x = [&](int c, uint32_t (&dst)[KL / 2]) {
     if (g < M) {
-      const uint4* xp = reinterpret_cast<const uint4*>(x + (size_t)g * ldx + k);
+      const uint4* xp = reinterpret_cast<const uint4*>(x + (size_t)g * ldx + c * CH + t * KL);
 #pragma unroll
       for (int i = 0; i < KL / 8; ++i) {
         const uint4 v = __ldg(xp + i);
-        xw[4 * i + 0] = v.x; xw[4 * i + 1] = v.y; xw[4 * i + 2] = v.z; xw[4 * i + 3] = v.w;
+        dst[4 * i + 0] = v.x; dst[4 * i + 1] = v.y; dst[4 * i + 2] = v.z; dst[4 * i + 3] = v.w;
       }
     } else {
 #pragma unroll
-      for (int i = 0; i < KL / 2; ++i) xw[i] = 0u;
+      for (int i = 0; i < KL / 2; ++i) dst[i] = 0u;
     }
+  };
+  uint4 cur[TILES][2], nxt[TILES][2];
+  uint32_t xw[KL / 2], xn[KL / 2];
+  int c = warp;
+  if (c < n_chunks) {
+    load_w(c, cur);
+    load_x(c, xw);
+  }
+  for (; c < n_chunks; c += 8) {
+    if (c + 8 < n_chunks) {
+      load_w(c + 8, nxt);
+      load_x(c + 8, xn);
+    }
+    const int k = c * CH + t * KL;
 #pragma unroll
     for (int tl = 0; tl < TILES; ++tl) {
       float sc[2] = {1.f, 1.f}, zs[2] = {0.f, 0.f};
@@ -394,7 +404,12 @@ wq_gemv_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restric
         for (int h = 0; h < 2; ++h) {
           const size_t idx = (size_t)rown[tl][h] * gpr + (group > 0 ? k / group : 0);
           sc[h] = __bfloat162float(scale[idx]);
-          if (BITS == 4) zs[h] = -(zero ? __bfloat162float(zero[idx]) : 8.f) * sc[h];
+          if (BITS == 4) {
+            // the nibble goes to the top mantissa bits of 1.0: v = 1 + code / 16, and one FMA gives
+            // (code - zp) * sc = v * (16 sc) - (16 + zp) * sc, the constant exact to 2^-24 of 16 sc
+            zs[h] = -(16.f + (zero ? __bfloat162float(zero[idx]) : 8.f)) * sc[h];
+            sc[h] *= 16.f;
+          }
         }
       }
       const uint32_t wv[2][4] = {{cur[tl][0].x, cur[tl][0].y, cur[tl][0].z, cur[tl][0].w},
@@ -427,8 +442,8 @@ wq_gemv_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restric
             float f[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              const float code = __uint_as_float(((q >> (4 * j)) & 0xfu) | 0x4B000000u) - 8388608.f;
-              f[j] = fmaf(code, sc[h], zs[h]);
+              const uint32_t sh = (4 * j <= 19) ? (q << (19 - 4 * j)) : (q >> (4 * j - 19));
+              f[j] = fmaf(__uint_as_float((sh & 0x00780000u) | 0x3F800000u), sc[h], zs[h]);
             }
 #pragma unroll
             for (int j = 0; j < 4; ++j) a[h][j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
@@ -442,6 +457,8 @@ wq_gemv_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restric
     for (int tl = 0; tl < TILES; ++tl)
 #pragma unroll
       for (int h = 0; h < 2; ++h) cur[tl][h] = nxt[tl][h];
+#pragma unroll
+    for (int i = 0; i < KL / 2; ++i) xw[i] = xn[i];
   }
 #pragma unroll
   for (int tl = 0; tl < TILES; ++tl)

@@ -1,0 +1,24 @@
+"""lumen: model interpretability and attribution (the ``tensorplay.lumen`` pack).
+
+Gradient methods (:class:`Saliency`, :class:`InputXGradient`, :class:`IntegratedGradients`,
+:class:`GradientShap`, :class:`DeepLift`, :class:`GuidedBackprop`, :class:`Deconvolution`,
+:class:`NoiseTunnel`), perturbation and surrogate methods (:class:`FeatureAblation`,
+:class:`Occlusion`, :class:`FeaturePermutation`, :class:`ShapleyValues`,
+:class:`ShapleyValueSampling`, :class:`Lime`, :class:`KernelShap`), layer methods
+(:class:`LayerActivation`, :class:`LayerGradientXActivation`, :class:`LayerGradCam`,
+:class:`LayerIntegratedGradients`, :class:`LayerConductance`, :class:`InternalInfluence`,
+:class:`NeuronConductance`) and language-model tools (``lumen.llm``: logit lens, activation
+patching, attention rollout, gradient attribution of a continuation).
+
+Every algorithm wraps a forward function and exposes ``attribute(inputs, ..., target=...)``; all
+of them run on whatever device the model lives on, through autograd and batched forwards.
+"""
+from . import llm
+from ._common import Attribution
+from .gradient import (Deconvolution, DeepLift, GradientShap, GuidedBackprop, InputXGradient, IntegratedGradients,
+                       NoiseTunnel, Saliency)
+from .layer import (InternalInfluence, LayerActivation, LayerAttribution, LayerConductance, LayerGradCam,
+                    LayerGradientXActivation, LayerIntegratedGradients, NeuronConductance)
+from .llm import LLMGradientAttribution, activation_patching, attention_rollout, logit_lens
+from .perturbation import (FeatureAblation, FeaturePermutation, KernelShap, Lime, Occlusion, ShapleyValues,
+                           ShapleyValueSampling)

@@ -1,0 +1,24 @@
+"""State-vector quantum simulation on the tensor primitives (the ``tensorplay.quantum`` pack).
+
+States are ``[batch, 2, ..., 2]`` complex tensors with qubit 0 leading; density matrices are
+``[batch, 2^n, 2^n]``. Gates stay differentiable in their angles; on a B200 one-qubit and
+controlled one-qubit gates on complex64 states run in a streaming CUDA kernel when no gradient
+is required.
+
+    >>> from tensorplay_b200 import quantum as tq
+    >>> bell = tq.Circuit(2); bell.h(0); bell.cx(0, 1)
+    >>> tq.probs(bell())            # tensor([[0.5, 0.0, 0.0, 0.5]])
+    >>> tq.expectation(bell(), "ZZ")   # tensor([1.])
+"""
+from .circuit import (GATE_TABLE, Circuit, efficient_su2, entanglement_pairs, expand_to_register, nlocal_circuit,
+                      qft_circuit, real_amplitudes)
+from .gates import *  # noqa: F401,F403
+from .gates import apply_controlled, apply_gate, n_qubits_of, zero_state
+from .measure import (apply_measurement_basis, apply_pauli_word, apply_readout_error, commuting_groups,
+                      counts_from_indices, density_probs, expectation, expectation_from_counts,
+                      expectation_from_density, gen_bitstrings, joint_expectation, marginal_probs, measure, probs,
+                      readout_error_matrix, sample_indices)
+from .physics import (Hamiltonian, amplitude_damping_kraus, apply_amplitude_damping, apply_bit_flip, apply_channel,
+                      apply_depolarizing, apply_phase_flip, bit_flip_kraus, density_matrix, depolarizing_kraus,
+                      dissipator, energy, energy_from_density, lindbladian, matrix_exp_evolve, mesolve, param_shift,
+                      pauli_kraus, phase_flip_kraus, sesolve, trotter_evolve)

@@ -1,0 +1,144 @@
+"""Attribution algorithms on models whose attributions are known in closed form."""
+import torch
+from torch import nn
+
+from tensorplay_b200 import lumen
+
+
+def _linear():
+    torch.manual_seed(0)
+    m = nn.Linear(6, 3)
+    return m, torch.randn(4, 6)
+
+
+def test_gradient_methods_on_a_linear_model():
+    m, x = _linear()
+    w = m.weight[1]
+    torch.testing.assert_close(lumen.Saliency(m).attribute(x, target=1), w.abs().expand(4, 6))
+    torch.testing.assert_close(lumen.InputXGradient(m).attribute(x, target=1), (x * w).detach())
+    ig, delta = lumen.IntegratedGradients(m).attribute(x, target=1, n_steps=8, return_convergence_delta=True)
+    torch.testing.assert_close(ig, (x * w).detach(), atol=1e-5, rtol=1e-5)
+    assert delta.abs().max() < 1e-5
+    # per-example targets
+    t = torch.tensor([0, 1, 2, 1])
+    ig = lumen.IntegratedGradients(m).attribute(x, target=t, n_steps=4)
+    torch.testing.assert_close(ig, (x * m.weight[t]).detach(), atol=1e-5, rtol=1e-5)
+
+
+def test_integrated_gradients_completeness_on_a_nonlinear_model():
+    torch.manual_seed(1)
+    m = nn.Sequential(nn.Linear(5, 16), nn.Tanh(), nn.Linear(16, 2))
+    x, b = torch.randn(3, 5), torch.randn(1, 5)
+    attr, delta = lumen.IntegratedGradients(m).attribute(x, baselines=b, target=0, n_steps=64,
+                                                         return_convergence_delta=True)
+    assert delta.abs().max() < 1e-4
+    with torch.no_grad():
+        torch.testing.assert_close(attr.sum(1), m(x)[:, 0] - m(b)[:, 0].expand(3), atol=1e-4, rtol=1e-4)
+
+
+def test_deeplift_sums_to_output_difference_on_relu_net():
+    torch.manual_seed(2)
+    m = nn.Sequential(nn.Linear(5, 12), nn.ReLU(), nn.Linear(12, 12), nn.ReLU(), nn.Linear(12, 1))
+    x = torch.randn(4, 5)
+    attr, delta = lumen.DeepLift(m).attribute(x, return_convergence_delta=True)
+    assert delta.abs().max() < 1e-5
+    gb = lumen.GuidedBackprop(m).attribute(x)
+    dc = lumen.Deconvolution(m).attribute(x)
+    assert gb.shape == x.shape and dc.shape == x.shape and not torch.equal(gb, dc)
+
+
+def test_perturbation_methods_on_an_additive_model():
+    m, x = _linear()
+    w = m.weight[2]
+    exact = (x * w).detach()
+    torch.testing.assert_close(lumen.FeatureAblation(m).attribute(x, target=2, perturbations_per_eval=3), exact,
+                               atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(lumen.Occlusion(m).attribute(x, (1,), target=2), exact, atol=1e-5, rtol=1e-5)
+    g = torch.Generator().manual_seed(0)
+    torch.testing.assert_close(lumen.ShapleyValueSampling(m).attribute(x, target=2, n_samples=3, generator=g), exact,
+                               atol=1e-5, rtol=1e-5)
+    mask = torch.tensor([[0, 0, 1, 1, 2, 2]])
+    sv = lumen.ShapleyValues(m).attribute(x, target=2, feature_mask=mask)
+    torch.testing.assert_close(sv[:, 0], exact[:, 0] + exact[:, 1], atol=1e-5, rtol=1e-5)
+    ks = lumen.KernelShap(m).attribute(x[:1], target=2, n_samples=200, generator=g)
+    torch.testing.assert_close(ks, exact[:1], atol=1e-3, rtol=1e-3)
+    li = lumen.Lime(m).attribute(x[:1], target=2, n_samples=200, generator=g)
+    torch.testing.assert_close(li, exact[:1], atol=1e-3, rtol=1e-3)
+    fp = lumen.FeaturePermutation(m).attribute(x, target=2, generator=g)
+    assert fp.shape == x.shape
+
+
+def test_shapley_values_exact_on_an_interaction():
+    # f = x0 * x1 + x2: the product's value is shared equally by x0 and x1
+    f = lambda x: x[:, 0] * x[:, 1] + x[:, 2]   # noqa: E731
+    x = torch.tensor([[2.0, 3.0, 5.0]])
+    sv = lumen.ShapleyValues(f).attribute(x)
+    torch.testing.assert_close(sv, torch.tensor([[3.0, 3.0, 5.0]]))
+
+
+def test_noise_tunnel_and_gradient_shap():
+    m, x = _linear()
+    g = torch.Generator().manual_seed(0)
+    sg = lumen.NoiseTunnel(lumen.Saliency(m)).attribute(x, nt_samples=3, stdevs=0.1, generator=g, target=0, abs=False)
+    torch.testing.assert_close(sg, m.weight[0].expand(4, 6).detach())          # constant gradient
+    vg = lumen.NoiseTunnel(lumen.Saliency(m)).attribute(x, nt_type="vargrad", nt_samples=3, generator=g, target=0)
+    assert vg.abs().max() < 1e-6
+    gs = lumen.GradientShap(m).attribute(x, torch.zeros(2, 6), target=0, n_samples=4, generator=g)
+    torch.testing.assert_close(gs, (x * m.weight[0]).detach(), atol=1e-5, rtol=1e-5)
+
+
+def test_layer_methods():
+    torch.manual_seed(3)
+    conv = nn.Conv2d(2, 4, 3, padding=1)
+    m = nn.Sequential(conv, nn.ReLU(), nn.AdaptiveAvgPool2d(1), nn.Flatten(), nn.Linear(4, 3))
+    x = torch.randn(2, 2, 5, 5)
+    act = lumen.LayerActivation(m, conv).attribute(x)
+    torch.testing.assert_close(act, conv(x).detach())
+    cam = lumen.LayerGradCam(m, conv).attribute(x, target=1)
+    assert cam.shape == (2, 1, 5, 5)
+    ga = lumen.LayerGradientXActivation(m, conv).attribute(x, target=1)
+    assert ga.shape == act.shape
+    # conductance of a layer sums to the output difference (completeness through the layer)
+    mlp = nn.Sequential(nn.Linear(4, 8), nn.Tanh(), nn.Linear(8, 1))
+    xi = torch.randn(3, 4)
+    cond = lumen.LayerConductance(mlp, mlp[1]).attribute(xi, n_steps=200)
+    with torch.no_grad():
+        torch.testing.assert_close(cond.sum(1), (mlp(xi) - mlp(torch.zeros(3, 4)))[:, 0], atol=1e-3, rtol=1e-3)
+    lig, delta = lumen.LayerIntegratedGradients(mlp, mlp[0]).attribute(xi, n_steps=32, return_convergence_delta=True)
+    assert lig.shape == (3, 8) and delta.abs().max() < 1e-4
+    assert lumen.InternalInfluence(mlp, mlp[1]).attribute(xi, n_steps=8).shape == (3, 8)
+    assert lumen.NeuronConductance(mlp, mlp[1]).attribute(xi, 2, n_steps=8).shape == (3,)
+
+
+def test_llm_tools_on_the_tiny_llama():
+    from tensorplay_b200.models.llama import Llama, LlamaConfig
+    cfg = LlamaConfig.tiny(hidden_size=32, num_heads=4, num_kv_heads=2, head_dim=8, ffn_size=48, vocab_size=50,
+                           num_layers=3, max_seq_len=16)
+    m = Llama(cfg)
+    m.reset_parameters(0)
+    toks = torch.randint(0, 50, (2, 7), generator=torch.Generator().manual_seed(0))
+    lens = lumen.logit_lens(m, toks)
+    assert lens.shape == (3, 2, 7, 50)
+    with torch.no_grad():
+        torch.testing.assert_close(lens[-1], m(toks))       # the last block's lens is the model's output
+    other = toks.clone()
+    other[:, 6] = (other[:, 6] + 1) % 50      # last position: under the causal mask only it differs
+    metric = lambda logits: logits[0, -1, 3]   # noqa: E731
+    patch = lumen.activation_patching(m, toks, other, metric)
+    assert patch.shape == (3, 7)
+    with torch.no_grad():
+        clean_val = float(metric(m(toks)))
+    # restoring the corrupted position after the first block restores the clean run exactly
+    assert abs(float(patch[0, 6]) - clean_val) < 1e-5 and abs(float(patch[0, 2]) - clean_val) > 1e-6
+    att = [torch.softmax(torch.randn(2, 4, 7, 7), -1) for _ in range(3)]
+    roll = lumen.attention_rollout(att)
+    torch.testing.assert_close(roll.sum(-1), torch.ones(2, 7))
+
+    def fwd_embeds(e):
+        cos, sin = m.rope_tables(e.shape[1], e.device)
+        x = e
+        for l in m.layers:
+            x = l(x, cos, sin)
+        return m.head(x)
+    res = lumen.LLMGradientAttribution(m, m.embed_tokens, fwd_embeds).attribute(toks[:, :5], toks[:, 5:])
+    assert res["token_attr"].shape == (2, 7) and res["log_prob"].shape == (2, 2)

@@ -146,3 +146,20 @@ def test_sampling_distribution():
     got = O.sample(logits, 1.0, 0, 0.7)  # nucleus keeps {0.5, 0.25}
     freq = torch.bincount(got, minlength=4).float() / got.numel()
     torch.testing.assert_close(freq, torch.tensor([2 / 3, 1 / 3, 0, 0], device=DEV), atol=0.02, rtol=0)
+
+
+@pytest.mark.parametrize("n,target,controls", [(10, 0, ()), (10, 9, ()), (12, 5, (2,)), (12, 11, (0, 7)), (3, 1, (2,))])
+def test_quantum_gate_kernel_matches_tensor_path(n, target, controls):
+    """One-qubit and controlled gates of the quantum pack: streaming kernel against the matmul path."""
+    from tensorplay_b200 import quantum as tq
+    g = torch.Generator().manual_seed(n + target)
+    s = torch.randn(3, 2 ** n, 2, generator=g)
+    s = torch.view_as_complex(s / s.norm(dim=(1, 2), keepdim=True)).reshape([3] + [2] * n)
+    u = tq.random_unitary(1, generator=g)
+    ref = tq.apply_controlled(s, u, list(controls), target) if controls else tq.apply_gate(s, u, target)
+    with torch.no_grad():
+        sd, ud = s.to(DEV), u.to(DEV)
+        out = tq.apply_controlled(sd, ud, list(controls), target) if controls else tq.apply_gate(sd, ud, target)
+    torch.testing.assert_close(out.cpu(), ref, atol=1e-6, rtol=1e-5)
+    from tensorplay_b200.quantum._native import apply_1q_native
+    assert apply_1q_native(sd, ud, target, tuple(controls)) is not None   # the kernel is what ran
