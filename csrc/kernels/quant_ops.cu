@@ -335,6 +335,28 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return r;
 }
 
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+// Stages of the per-warp weight ring. The kernel is bound by bytes in flight, not by arithmetic:
+// at ~2 us of loaded HBM latency an SM needs ~90 KB outstanding to draw its share of the
+// bandwidth, far more than a register double buffer holds, so the packed weights go through
+// cp.async into a shared-memory ring that is STAGES - 1 chunks ahead of the arithmetic. Every lane
+// reads back exactly the 16-byte pieces it requested itself, so the ring needs no barrier.
+template <int TILES>
+struct GemvRing {
+  static constexpr int kStages = TILES == 1 ? 6 : 4;
+  static constexpr int kStageVecs = 2 * TILES * 32;  // uint4 per stage per warp
+  static constexpr int kBytes = 8 * kStages * kStageVecs * 16;
+};
+
 template <int BITS, int TILES>
 __global__ void __launch_bounds__(256)
 wq_gemv_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ w,
@@ -343,11 +365,16 @@ wq_gemv_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restric
                    int K, int group, long long ldx, long long ldy) {
   constexpr int KL = BITS == 8 ? 16 : 32;  // k per lane per chunk = 16 bytes of packed weights
   constexpr int CH = 4 * KL;
-  __shared__ float red[8][TILES * 128];
+  constexpr int S = GemvRing<TILES>::kStages;
+  constexpr int SV = GemvRing<TILES>::kStageVecs;
+  constexpr bool kScaled = BITS == 4;      // 8-bit: grouped scales are a run-time property
+  extern __shared__ uint4 gemv_ring[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  uint4* my_ring = gemv_ring + (size_t)warp * S * SV;
   const int n_base = blockIdx.x * TILES * 16;
   const int n_chunks = K / CH;
   const int gpr = group > 0 ? K / group : 1;
+  const bool grouped = kScaled || group > 0;
   const size_t row_bytes = BITS == 8 ? (size_t)K : (size_t)K / 2;
   int rown[TILES][2];
 #pragma unroll
@@ -360,18 +387,23 @@ wq_gemv_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restric
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[tl][i] = 0.f;
 
-  auto load_w = [&](int c, uint4 (&dst)[TILES][2]) {
-    const size_t off = (size_t)(c * CH + t * KL) * BITS / 8;
+  // one commit group per chunk, also when the chunk does not exist: the group count stays uniform
+  auto issue_w = [&](int c, int stage) {
+    if (c < n_chunks) {
+      const size_t off = (size_t)(c * CH + t * KL) * BITS / 8;
 #pragma unroll
-    for (int tl = 0; tl < TILES; ++tl)
+      for (int tl = 0; tl < TILES; ++tl)
 #pragma unroll
-      for (int h = 0; h < 2; ++h)
-        dst[tl][h] = __ldg(reinterpret_cast<const uint4*>(w + (size_t)rown[tl][h] * row_bytes + off));
+        for (int h = 0; h < 2; ++h)
+          cp_async_16(my_ring + (size_t)stage * SV + (tl * 2 + h) * 32 + lane,
+                      w + (size_t)rown[tl][h] * row_bytes + off);
+    }
+    cp_async_commit();
   };
-  // x rows of a chunk: KL bf16 of row g (zeros past M); requested one chunk ahead like the weights,
-  // so that neither stream's latency sits on the loop's critical path
+  // x rows of a chunk (KL bf16 of row g, zeros past M) and the chunk's group scales are requested
+  // one chunk ahead in registers: they come from L1 / L2
   auto load_x = [&](int c, uint32_t (&dst)[KL / 2]) {
-    if (g < M) {
+    if (g < M && c < n_chunks) {
       const uint4* xp = reinterpret_cast<const uint4*>(x + (size_t)g * ldx + c * CH + t * KL);
 #pragma unroll
       for (int i = 0; i < KL / 8; ++i) {
@@ -383,37 +415,46 @@ wq_gemv_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restric
       for (int i = 0; i < KL / 2; ++i) dst[i] = 0u;
     }
   };
-  uint4 cur[TILES][2], nxt[TILES][2];
-  uint32_t xw[KL / 2], xn[KL / 2];
-  int c = warp;
-  if (c < n_chunks) {
-    load_w(c, cur);
-    load_x(c, xw);
-  }
-  for (; c < n_chunks; c += 8) {
-    if (c + 8 < n_chunks) {
-      load_w(c + 8, nxt);
-      load_x(c + 8, xn);
-    }
-    const int k = c * CH + t * KL;
+  auto load_s = [&](int c, float (&sc)[TILES][2], float (&zp)[TILES][2]) {
 #pragma unroll
-    for (int tl = 0; tl < TILES; ++tl) {
-      float sc[2] = {1.f, 1.f}, zs[2] = {0.f, 0.f};
-      if (group > 0 || BITS == 4) {
+    for (int tl = 0; tl < TILES; ++tl)
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const size_t idx = (size_t)rown[tl][h] * gpr + (group > 0 ? k / group : 0);
-          sc[h] = __bfloat162float(scale[idx]);
-          if (BITS == 4) {
-            // the nibble goes to the top mantissa bits of 1.0: v = 1 + code / 16, and one FMA gives
-            // (code - zp) * sc = v * (16 sc) - (16 + zp) * sc, the constant exact to 2^-24 of 16 sc
-            zs[h] = -(16.f + (zero ? __bfloat162float(zero[idx]) : 8.f)) * sc[h];
-            sc[h] *= 16.f;
-          }
+      for (int h = 0; h < 2; ++h) {
+        sc[tl][h] = 1.f;
+        zp[tl][h] = 8.f;
+        if (grouped && c < n_chunks) {
+          const size_t idx = (size_t)rown[tl][h] * gpr + (group > 0 ? (c * CH + t * KL) / group : 0);
+          sc[tl][h] = __bfloat162float(scale[idx]);
+          if (BITS == 4 && zero) zp[tl][h] = __bfloat162float(zero[idx]);
         }
       }
-      const uint32_t wv[2][4] = {{cur[tl][0].x, cur[tl][0].y, cur[tl][0].z, cur[tl][0].w},
-                                 {cur[tl][1].x, cur[tl][1].y, cur[tl][1].z, cur[tl][1].w}};
+  };
+
+#pragma unroll
+  for (int s = 0; s < S - 1; ++s) issue_w(warp + 8 * s, s);
+  uint32_t xw[KL / 2], xn[KL / 2];
+  float scw[TILES][2], zpw[TILES][2], scn[TILES][2], zpn[TILES][2];
+  load_x(warp, xw);
+  load_s(warp, scw, zpw);
+  int it = 0;
+  for (int c = warp; c < n_chunks; c += 8, ++it) {
+    issue_w(c + 8 * (S - 1), (it + S - 1) % S);
+    load_x(c + 8, xn);
+    load_s(c + 8, scn, zpn);
+    cp_async_wait<S - 1>();  // this chunk's group has landed (S - 1 younger ones may be pending)
+    const uint4* st = my_ring + (size_t)(it % S) * SV;
+#pragma unroll
+    for (int tl = 0; tl < TILES; ++tl) {
+      const uint4 w0 = st[(tl * 2 + 0) * 32 + lane], w1 = st[(tl * 2 + 1) * 32 + lane];
+      const uint32_t wv[2][4] = {{w0.x, w0.y, w0.z, w0.w}, {w1.x, w1.y, w1.z, w1.w}};
+      float sc[2], zs[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        // 4-bit: the nibble goes to the top mantissa bits of 1.0 (v = 1 + code / 16) and one FMA
+        // gives (code - zp) * sc = v * (16 sc) - (16 + zp) * sc, the constant exact to 2^-24 of 16 sc
+        sc[h] = BITS == 4 ? 16.f * scw[tl][h] : scw[tl][h];
+        zs[h] = -(16.f + zpw[tl][h]) * scw[tl][h];
+      }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         if (BITS == 8) {
@@ -454,21 +495,27 @@ wq_gemv_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restric
       }
     }
 #pragma unroll
+    for (int i = 0; i < KL / 2; ++i) xw[i] = xn[i];
+#pragma unroll
     for (int tl = 0; tl < TILES; ++tl)
 #pragma unroll
-      for (int h = 0; h < 2; ++h) cur[tl][h] = nxt[tl][h];
-#pragma unroll
-    for (int i = 0; i < KL / 2; ++i) xw[i] = xn[i];
+      for (int h = 0; h < 2; ++h) {
+        scw[tl][h] = scn[tl][h];
+        zpw[tl][h] = zpn[tl][h];
+      }
   }
+  cp_async_wait<0>();
+  __syncthreads();  // every warp is done with its ring: the reduction buffer reuses the memory
+  float* red = reinterpret_cast<float*>(gemv_ring);  // [8][TILES * 128]
 #pragma unroll
   for (int tl = 0; tl < TILES; ++tl)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) red[warp][tl * 128 + lane * 4 + i] = acc[tl][i];
+    for (int i = 0; i < 4; ++i) red[warp * (TILES * 128) + tl * 128 + lane * 4 + i] = acc[tl][i];
   __syncthreads();
   for (int o = threadIdx.x; o < TILES * 128; o += 256) {
     float a = 0.f;
 #pragma unroll
-    for (int wi = 0; wi < 8; ++wi) a += red[wi][o];
+    for (int wi = 0; wi < 8; ++wi) a += red[wi * (TILES * 128) + o];
     // accumulator element (lane l, register ci) = (column g + 8 * (ci / 2), row 2 t + (ci & 1))
     const int tl = o >> 7, l = (o >> 2) & 31, ci = o & 3;
     const int n = n_base + tl * 16 + (l >> 2) + ((ci & 2) ? 8 : 0);
@@ -677,14 +724,23 @@ int tpb_wq_gemv(const void* x, const void* w, const void* scale, const void* zer
     const uint8_t* wp = (const uint8_t*)w;
     if (mma_ok) {
       const int g2 = (N + 16 * tiles - 1) / (16 * tiles);
+      auto launch = [&](auto kern, int smem) {
+        static bool opted_in[4] = {false, false, false, false};  // per kernel variant
+        bool& done = opted_in[(bits == 8 ? 0 : 2) + (tiles == 2 ? 1 : 0)];
+        if (!done) {
+          cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+          done = true;
+        }
+        kern<<<g2, 256, smem, st>>>(xs, wp, sc, zp, bs, ys, rows, N, K, group, ldx, ldy);
+      };
       if (bits == 8 && tiles == 2)
-        wq_gemv_mma_kernel<8, 2><<<g2, 256, 0, st>>>(xs, wp, sc, zp, bs, ys, rows, N, K, group, ldx, ldy);
+        launch(wq_gemv_mma_kernel<8, 2>, GemvRing<2>::kBytes);
       else if (bits == 8)
-        wq_gemv_mma_kernel<8, 1><<<g2, 256, 0, st>>>(xs, wp, sc, zp, bs, ys, rows, N, K, group, ldx, ldy);
+        launch(wq_gemv_mma_kernel<8, 1>, GemvRing<1>::kBytes);
       else if (tiles == 2)
-        wq_gemv_mma_kernel<4, 2><<<g2, 256, 0, st>>>(xs, wp, sc, zp, bs, ys, rows, N, K, group, ldx, ldy);
+        launch(wq_gemv_mma_kernel<4, 2>, GemvRing<2>::kBytes);
       else
-        wq_gemv_mma_kernel<4, 1><<<g2, 256, 0, st>>>(xs, wp, sc, zp, bs, ys, rows, N, K, group, ldx, ldy);
+        launch(wq_gemv_mma_kernel<4, 1>, GemvRing<1>::kBytes);
     } else if (bits == 8) {
       wq_gemv_kernel<8><<<grid, 256, 0, st>>>(xs, wp, sc, zp, bs, ys, rows, N, K, group, ldx, ldy);
     } else {
