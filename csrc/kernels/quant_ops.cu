@@ -357,7 +357,7 @@ struct GemvRing {
   static constexpr int kBytes = 8 * kStages * kStageVecs * 16;
 };
 
-template <int BITS, int TILES>
+template <int BITS, int TILES, int KS>
 __global__ void __launch_bounds__(256)
 wq_gemv_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ w,
                    const __nv_bfloat16* __restrict__ scale, const __nv_bfloat16* __restrict__ zero,
@@ -371,7 +371,9 @@ wq_gemv_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restric
   extern __shared__ uint4 gemv_ring[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   uint4* my_ring = gemv_ring + (size_t)warp * S * SV;
-  const int n_base = blockIdx.x * TILES * 16;
+  // KS warps split K for one row tile (TILES x 16 columns); the CTA covers 8 / KS row tiles
+  const int kw = warp % KS;
+  const int n_base = (blockIdx.x * (8 / KS) + warp / KS) * TILES * 16;
   const int n_chunks = K / CH;
   const int gpr = group > 0 ? K / group : 1;
   const bool grouped = kScaled || group > 0;
@@ -431,16 +433,16 @@ wq_gemv_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restric
   };
 
 #pragma unroll
-  for (int s = 0; s < S - 1; ++s) issue_w(warp + 8 * s, s);
+  for (int s = 0; s < S - 1; ++s) issue_w(kw + KS * s, s);
   uint32_t xw[KL / 2], xn[KL / 2];
   float scw[TILES][2], zpw[TILES][2], scn[TILES][2], zpn[TILES][2];
-  load_x(warp, xw);
-  load_s(warp, scw, zpw);
+  load_x(kw, xw);
+  load_s(kw, scw, zpw);
   int it = 0;
-  for (int c = warp; c < n_chunks; c += 8, ++it) {
-    issue_w(c + 8 * (S - 1), (it + S - 1) % S);
-    load_x(c + 8, xn);
-    load_s(c + 8, scn, zpn);
+  for (int c = kw; c < n_chunks; c += KS, ++it) {
+    issue_w(c + KS * (S - 1), (it + S - 1) % S);
+    load_x(c + KS, xn);
+    load_s(c + KS, scn, zpn);
     cp_async_wait<S - 1>();  // this chunk's group has landed (S - 1 younger ones may be pending)
     const uint4* st = my_ring + (size_t)(it % S) * SV;
 #pragma unroll
@@ -512,13 +514,14 @@ wq_gemv_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restric
 #pragma unroll
     for (int i = 0; i < 4; ++i) red[warp * (TILES * 128) + tl * 128 + lane * 4 + i] = acc[tl][i];
   __syncthreads();
-  for (int o = threadIdx.x; o < TILES * 128; o += 256) {
+  for (int o = threadIdx.x; o < (8 / KS) * TILES * 128; o += 256) {
+    const int rt = o / (TILES * 128), e = o % (TILES * 128);  // row tile of the CTA, element in it
     float a = 0.f;
 #pragma unroll
-    for (int wi = 0; wi < 8; ++wi) a += red[wi * (TILES * 128) + o];
+    for (int wi = 0; wi < KS; ++wi) a += red[(rt * KS + wi) * (TILES * 128) + e];
     // accumulator element (lane l, register ci) = (column g + 8 * (ci / 2), row 2 t + (ci & 1))
-    const int tl = o >> 7, l = (o >> 2) & 31, ci = o & 3;
-    const int n = n_base + tl * 16 + (l >> 2) + ((ci & 2) ? 8 : 0);
+    const int tl = e >> 7, l = (e >> 2) & 31, ci = e & 3;
+    const int n = (blockIdx.x * (8 / KS) + rt) * TILES * 16 + tl * 16 + (l >> 2) + ((ci & 2) ? 8 : 0);
     const int r = 2 * (l & 3) + (ci & 1);
     if (n < N && r < M) {
       if (group <= 0 && BITS == 8) a *= __bfloat162float(scale[n]);  // per-channel scale applied once
@@ -723,7 +726,10 @@ int tpb_wq_gemv(const void* x, const void* w, const void* scale, const void* zer
     const int rows = M - m0 < 8 ? M - m0 : 8;
     const uint8_t* wp = (const uint8_t*)w;
     if (mma_ok) {
-      const int g2 = (N + 16 * tiles - 1) / (16 * tiles);
+      // int4 has half the chunks of int8 for the same K: four warps per row tile keep the loop long
+      const int ks = bits == 8 ? 8 : 4;
+      const int per_cta = 16 * tiles * (8 / ks);
+      const int g2 = (N + per_cta - 1) / per_cta;
       auto launch = [&](auto kern, int smem) {
         static bool opted_in[4] = {false, false, false, false};  // per kernel variant
         bool& done = opted_in[(bits == 8 ? 0 : 2) + (tiles == 2 ? 1 : 0)];
@@ -734,13 +740,13 @@ int tpb_wq_gemv(const void* x, const void* w, const void* scale, const void* zer
         kern<<<g2, 256, smem, st>>>(xs, wp, sc, zp, bs, ys, rows, N, K, group, ldx, ldy);
       };
       if (bits == 8 && tiles == 2)
-        launch(wq_gemv_mma_kernel<8, 2>, GemvRing<2>::kBytes);
+        launch(wq_gemv_mma_kernel<8, 2, 8>, GemvRing<2>::kBytes);
       else if (bits == 8)
-        launch(wq_gemv_mma_kernel<8, 1>, GemvRing<1>::kBytes);
+        launch(wq_gemv_mma_kernel<8, 1, 8>, GemvRing<1>::kBytes);
       else if (tiles == 2)
-        launch(wq_gemv_mma_kernel<4, 2>, GemvRing<2>::kBytes);
+        launch(wq_gemv_mma_kernel<4, 2, 4>, GemvRing<2>::kBytes);
       else
-        launch(wq_gemv_mma_kernel<4, 1>, GemvRing<1>::kBytes);
+        launch(wq_gemv_mma_kernel<4, 1, 4>, GemvRing<1>::kBytes);
     } else if (bits == 8) {
       wq_gemv_kernel<8><<<grid, 256, 0, st>>>(xs, wp, sc, zp, bs, ys, rows, N, K, group, ldx, ldy);
     } else {
