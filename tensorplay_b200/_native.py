@@ -51,6 +51,8 @@ _KERNEL_SIGS = {
     "tpb_gemm_i8": [P, P, P, P, P, P, I, I, I, I, I, I, P, P],
     "tpb_wq_gemv": [P, P, P, P, P, P, I, I, I, I, I, LL, LL, P],
     "tpb_wq_gemv_config": [I, I],
+    "tpb_lif_fwd": [P, P, P, P, I, LL, F, F, F, I, P],
+    "tpb_lif_bwd": [P, P, P, P, I, LL, F, F, F, F, I, I, P],
     "tpb_quant_i8_rowwise": [P, P, P, I, I, LL, P],
     "tpb_dequant_weight": [P, P, P, P, I, I, I, I, P],
     "tpb_fp8_quant": [P, P, P, LL, I, I, I, P],

@@ -21,7 +21,7 @@ def _worker(rank, world):
     tgts = torch.randint(0, cfg.vocab_size, (world, 2, 16), generator=g)
     ocfg = AdamWConfig(lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
     res = {}
-    for ckpt in (True, False):
+    for ckpt in (True, False, "selective"):
         eng = FSDPEngine(copy.deepcopy(base), ocfg, comm="torch", activation_checkpointing=ckpt)
         losses = []
         for _ in range(4):
@@ -38,7 +38,7 @@ def _worker(rank, world):
         loss.backward()
         opt.step()
         ref_losses.append(float(loss.detach()))
-    for ckpt in (True, False):
+    for ckpt in (True, False, "selective"):
         losses, state = res[ckpt]
         for a, b in zip(losses, ref_losses):
             assert abs(a - b) < 1e-5, (ckpt, losses, ref_losses)

@@ -163,3 +163,31 @@ def test_quantum_gate_kernel_matches_tensor_path(n, target, controls):
     torch.testing.assert_close(out.cpu(), ref, atol=1e-6, rtol=1e-5)
     from tensorplay_b200.quantum._native import apply_1q_native
     assert apply_1q_native(sd, ud, target, tuple(controls)) is not None   # the kernel is what ran
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("detach_reset", [False, True])
+def test_fused_multi_step_lif_matches_cell_loop(dtype, detach_reset):
+    """Fused LIF forward + BPTT against the per-step module under autograd (fp32 oracle on CPU)."""
+    from tensorplay_b200 import snn
+    T, B, N = 12, 3, 64
+    g = torch.Generator().manual_seed(3)
+    x = (torch.randn(T, B, N, generator=g) * 1.5).to(dtype)
+    gy = torch.randn(T, B, N, generator=g).to(dtype)
+    # oracle: the time loop on CPU in fp32 from the same (rounded) inputs
+    xr = x.float().clone().requires_grad_()
+    cell = snn.LIFCell(tau=2.0, v_threshold=1.0, v_reset=0.0, alpha=2.0, detach_reset=detach_reset)
+    v, out = None, []
+    for t in range(T):
+        s, v = cell(xr[t], v)
+        out.append(s)
+    ref = torch.stack(out)
+    ref.backward(gy.float())
+    xd = x.to(DEV).requires_grad_()
+    lif = snn.LIF(tau=2.0, v_threshold=1.0, v_reset=0.0, alpha=2.0, detach_reset=detach_reset)
+    sd = lif(xd)
+    assert snn.multi_step_lif(xd.detach()) is not None            # the fused kernel is what ran
+    sd.backward(gy.to(DEV))
+    assert torch.equal(sd.float().cpu(), ref.detach())
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    torch.testing.assert_close(xd.grad.float().cpu(), xr.grad, atol=tol, rtol=tol)
