@@ -108,3 +108,14 @@ def _metric_sync_worker(rank, world):
 def test_metrics_sync_over_process_group():
     from tests.distutil import run_ranks
     assert all(run_ranks(_metric_sync_worker, 2))
+
+
+def test_activation_checkpoint_plan_llama8b():
+    from tensorplay_b200.distributed._tools import activation_checkpoint_plan
+    from tensorplay_b200.models.llama import LlamaConfig
+    plan = activation_checkpoint_plan(LlamaConfig.llama3_8b(), 4096, 1)
+    # selective keeps ~0.4 GB per layer at seq 4096 (12-13 GB for 32 layers); full keeps only block inputs
+    assert 11e9 < plan["selective"]["kept_bytes"] < 14e9
+    assert plan["full"]["kept_bytes"] == 32 * 4096 * 4096 * 2
+    assert plan["none"]["kept_bytes"] > plan["selective"]["kept_bytes"] > plan["full"]["kept_bytes"]
+    assert plan["full"]["recompute_flops"] == plan["forward_flops"] and plan["selective"]["recompute_flops"] == 0
