@@ -21,20 +21,18 @@ from tensorplay_b200.parallel import AdamWConfig, FSDPEngine  # noqa: E402
 
 
 def batches(args, cfg, rank, world, device):
-    g = torch.Generator().manual_seed(1234 + rank)
-    data = None
+    """Synthetic tokens, or ``--data``: a flat int32 token file read by the native loader (worker
+    threads fill pinned batches ahead of the step; every rank gets its own share of each epoch)."""
     if args.data:
-        import numpy as np
-        data = torch.from_numpy(np.fromfile(args.data, dtype=np.int32).astype("int64"))
-    step = 0
+        from tensorplay_b200.utils.data import TokenFileLoader
+        loader = TokenFileLoader(args.data, args.seq, args.micro_batch, dtype=torch.int32, rank=rank, world=world,
+                                 seed=1234)
+        while True:
+            tok, tgt, _ = loader.next_batch()
+            yield tok.to(device, non_blocking=True), tgt.to(device, non_blocking=True)
+    g = torch.Generator().manual_seed(1234 + rank)
     while True:
-        if data is None:
-            tok = torch.randint(0, cfg.vocab_size, (args.micro_batch, args.seq + 1), generator=g)
-        else:
-            n = args.micro_batch * (args.seq + 1)
-            off = ((step * world + rank) * n) % max(1, data.numel() - n)
-            tok = data[off: off + n].view(args.micro_batch, args.seq + 1)
-        step += 1
+        tok = torch.randint(0, cfg.vocab_size, (args.micro_batch, args.seq + 1), generator=g)
         tok = tok.pin_memory() if device.type == "cuda" else tok
         tok = tok.to(device, non_blocking=True)
         yield tok[:, :-1].contiguous(), tok[:, 1:].contiguous()

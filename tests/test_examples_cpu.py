@@ -23,6 +23,15 @@ def test_train_example_saves_and_resumes(tmp_path):
     assert "step 9: loss" in out
 
 
+def test_train_example_reads_a_token_file(tmp_path):
+    import numpy as np
+    p = tmp_path / "tok.bin"
+    (np.arange(4000) % 97).astype(np.int32).tofile(p)
+    out = _run(["examples/train_llama_fsdp.py", "--preset", "tiny", "--steps", "4", "--seq", "32", "--log-every", "2",
+                "--data", str(p)])
+    assert "step 4: loss" in out
+
+
 def test_generate_example_cache_kinds():
     for kind in ("dynamic", "static", "paged"):
         out = _run(["examples/generate.py", "--new-tokens", "6", "--cache", kind])
