@@ -109,7 +109,10 @@ def main():
     def step():
         opt.zero_grad(set_to_none=True)
         losses = []
-        if pp_i == 0:
+        if a.pp == 1:
+            sched.step(tokens, target=targets, losses=losses, return_outputs=False)
+            last_loss.copy_(torch.stack(losses).sum() / a.microbatches)
+        elif pp_i == 0:
             sched.step(tokens)
         elif pp_i == a.pp - 1:
             sched.step(target=targets, losses=losses, return_outputs=False)

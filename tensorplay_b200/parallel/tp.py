@@ -135,7 +135,10 @@ class _AGLinearFn(torch.autograd.Function):
     def forward(ctx, x_local, weight, ag_plan: AGGemmPlan, rs_plan: Optional[GemmRSPlan]):
         ag_plan.local_view().copy_(x_local.reshape(-1, x_local.shape[-1]))
         y, x_full = ag_plan.run(weight)
-        ctx.save_for_backward(x_full, weight)
+        # the gathered rows live in the plan's rotating buffer, which the next calls of the same
+        # shape overwrite: backward gets its own copy (needed for dW only)
+        keep = x_full.clone() if weight.requires_grad else x_full.new_empty(0)
+        ctx.save_for_backward(keep, weight)
         ctx.rs_plan = rs_plan
         ctx.w_ref = weight if hasattr(weight, "_tpb_grad_view") else None
         return y
@@ -147,6 +150,8 @@ class _AGLinearFn(torch.autograd.Function):
         # dx_local = reduce_scatter(dy @ W)
         dx = ctx.rs_plan.run(dy, weight, b_mn=True)
         w_ref = ctx.w_ref
+        if not ctx.needs_input_grad[1]:
+            return dx, None, None, None
         if w_ref is not None and w_ref._tpb_grad_view is not None:
             ops.gemm(dy, x_full, a_mn=True, b_mn=True, out=w_ref._tpb_grad_view,
                      accumulate=getattr(w_ref, "_tpb_grad_written", False))
