@@ -105,8 +105,15 @@ def main():
     tokens = torch.randint(0, cfg.vocab_size, (a.microbatches, a.seq), generator=g).to(dev)
     targets = torch.randint(0, cfg.vocab_size, (a.microbatches, a.seq), generator=g).to(dev)
     last_loss = torch.zeros((), device=dev)
+    # the step draws its tokens from the device generator: tensor-parallel peers (same stage, same
+    # data-parallel rank) must draw the same ones
+    torch.manual_seed(1000 + dp_i)
 
     def step():
+        # fresh uniform tokens every step (a fixed batch is memorised within a few AdamW steps at
+        # this width, and the loss would say nothing about the step being right)
+        tokens.random_(0, cfg.vocab_size)
+        targets.random_(0, cfg.vocab_size)
         opt.zero_grad(set_to_none=True)
         losses = []
         if a.pp == 1:

@@ -1,7 +1,8 @@
 """Quantised kernels on one B200: int8 tensor-core GEMM (A8W8) against the bf16 GEMM of the same
 shape, and the weight-only GEMV (W8A16 / W4A16) against its weight-streaming roofline.
 
-    python benchmarks/bench_quant.py
+    python benchmarks/bench_quant.py                      # all numbers
+    python benchmarks/bench_quant.py --profile-gemv 8     # small case for a profiler capture (also 4)
 CUDA events, 3 warm-ups; every operand set is larger than the 126 MB L2 or rotated so that weights
 come from HBM.
 """
@@ -29,8 +30,29 @@ def timeit(fn, iters=10, warmup=3):
     return e0.elapsed_time(e1) / iters
 
 
+def profile_gemv(bits: int) -> None:
+    """A few eager calls of the default GEMV kernel over four weight sets (0.5-0.9 GB on the device):
+    the case to run under a profiler (``ncu -k regex:wq_gemv_mma -c 2``)."""
+    dev = "cuda"
+    N, K, M, group = 28672, 8192, 8, (0 if bits == 8 else 128)
+    x = torch.randn(M, K, device=dev).bfloat16()
+    ws = []
+    for _ in range(4):
+        w = torch.randn(N, K, device=dev)
+        ws.append(O.quantize_weight_int8(w) + (None,) if bits == 8 else O.quantize_weight_int4(w, group))
+        del w
+    for i in range(6):
+        q, s, z = ws[i % 4]
+        O.weight_only_linear(x, q, s, z, None, bits, group)
+    torch.cuda.synchronize()
+    O.check_status()
+    print(json.dumps({"profiled": f"W{bits}A16 GEMV", "calls": 6}), flush=True)
+
+
 def main():
     dev = "cuda"
+    if "--profile-gemv" in sys.argv:
+        return profile_gemv(int(sys.argv[sys.argv.index("--profile-gemv") + 1]))
     try:
         with open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")) as f:
             hbm = float(json.load(f).get("hbm_gbs", 6650.0))

@@ -80,6 +80,22 @@ def test_fsdp_symm_pull_kernel_transport():
     assert "RESULT" in r.stdout
 
 
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("tp,pp", [(2, 1), (1, 2)])
+def test_tensor_parallel_and_pipeline_training_on_two_gpus(tp, pp):
+    """Several tensor-parallel blocks trained through the fused linears (tp2), and two pipeline
+    stages over NCCL point-to-point (pp2): the step runs and the loss is that of a random model."""
+    import json
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+           os.path.join(ROOT, "benchmarks", "bench_llama_3d.py"), "--tp", str(tp), "--pp", str(pp), "--layers", "4",
+           "--microbatches", "4", "--seq", "1024", "--steps", "2", "--warmup", "2"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    line = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
+    assert 10.0 < line["loss"] < 13.5, line   # ln(128256) = 11.76
+
+
 @pytest.mark.skipif(_ngpu() < 4, reason="needs 4 GPUs")
 def test_composed_tp_pp_layout_trains():
     """TP2 x PP2 of the composed-layout benchmark on a short Llama-shaped model: runs, loss near ln(V)."""
