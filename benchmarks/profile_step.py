@@ -1,6 +1,6 @@
 """Kernel-time table of one training step of the sharded engine (torch.profiler, CUDA activities).
 
-    python benchmarks/profile_step.py --layers 4 [--out profiles/step_kernels.txt]
+    python benchmarks/profile_step.py --layers 4 [--ac full|selective] [--out profiles/step_kernels.txt]
 """
 import argparse
 import os
@@ -17,13 +17,14 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--ac", default="selective", choices=["full", "selective"])
     a = ap.parse_args()
     dev = torch.device("cuda", 0)
     cfg = LlamaConfig.llama3_8b()
     cfg.num_layers = a.layers
     model = Llama(cfg, device=dev, dtype=torch.bfloat16)
     model.reset_parameters(seed=0)
-    eng = FSDPEngine(model, AdamWConfig())
+    eng = FSDPEngine(model, AdamWConfig(), activation_checkpointing=True if a.ac == "full" else "selective")
     tok = torch.randint(0, cfg.vocab_size, (1, 4096), device=dev)
     for _ in range(3):
         eng.step(tok, tok)
@@ -47,7 +48,8 @@ def main():
             rows.append((e.device_time_total / 2, e.count // 2, e.key))
     rows.sort(reverse=True)
     total = sum(r[0] for r in rows)
-    lines = [f"# kernel time per step, Llama-3-8B shape with {a.layers} layers, seq 4096, 1 GPU (torch.profiler)",
+    lines = [f"# kernel time per step, Llama-3-8B shape with {a.layers} layers, seq 4096, 1 GPU, "
+             f"activation checkpointing {a.ac} (torch.profiler)",
              f"# total device kernel time per step: {total / 1e3:.2f} ms; CUDA-event step time without "
              f"the profiler: {step_ms:.2f} ms (kernels on side streams overlap, gaps are idle time)"]
     for t, c, k in rows[:30]:
