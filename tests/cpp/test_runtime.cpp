@@ -38,6 +38,13 @@ long long tpb_reducer_bucket_numel(void* h, int bucket);
 int tpb_reducer_mark_ready(void* h, int param);
 void tpb_reducer_rearm(void* h, int bucket);
 void tpb_reducer_reset(void* h);
+void* tpb_loader_open(const char* path, int elem_bytes, int seq_len, int batch, int rank, int world,
+                      unsigned long long seed, int shuffle, int n_workers, int depth, void** tok_slots,
+                      void** tgt_slots, int* err);
+long long tpb_loader_batches_per_epoch(void* h);
+int tpb_loader_next(void* h, long long* batch_number);
+void tpb_loader_release(void* h, int slot);
+void tpb_loader_close(void* h);
 }
 
 static int failures = 0;
@@ -155,7 +162,53 @@ static void test_reducer() {
   tpb_reducer_destroy(r);
 }
 
+static void test_loader(const char* dir) {
+  // token i of the file has value i: a batch row names its sample, targets are tokens + 1
+  const int seq = 8, batch = 2, depth = 3, n_samples = 20;
+  const std::string path = std::string(dir) + "/tokens_cpp.bin";
+  {
+    std::vector<int32_t> v(n_samples * seq + 1);
+    for (size_t i = 0; i < v.size(); ++i) v[i] = (int32_t)i;
+    FILE* f = std::fopen(path.c_str(), "wb");
+    CHECK(f != nullptr);
+    std::fwrite(v.data(), 4, v.size(), f);
+    std::fclose(f);
+  }
+  std::vector<std::vector<int64_t>> tok(depth, std::vector<int64_t>(batch * seq)), tgt = tok;
+  std::vector<void*> tp, gp;
+  for (int i = 0; i < depth; ++i) {
+    tp.push_back(tok[i].data());
+    gp.push_back(tgt[i].data());
+  }
+  int err = 0;
+  void* h = tpb_loader_open(path.c_str(), 4, seq, batch, 0, 1, 42, 1, 3, depth, tp.data(), gp.data(), &err);
+  CHECK(h != nullptr && err == 0);
+  if (!h) return;
+  CHECK(tpb_loader_batches_per_epoch(h) == n_samples / batch);
+  std::vector<int> seen(n_samples, 0);
+  for (long long b = 0; b < n_samples / batch; ++b) {
+    long long num = -1;
+    const int slot = tpb_loader_next(h, &num);
+    CHECK(slot >= 0 && slot < depth && num == b);
+    for (int r = 0; r < batch; ++r) {
+      const int64_t first = tok[slot][r * seq];
+      CHECK(first % seq == 0 && first / seq < n_samples);
+      seen[first / seq]++;
+      for (int t = 0; t < seq; ++t) {
+        CHECK(tok[slot][r * seq + t] == first + t);
+        CHECK(tgt[slot][r * seq + t] == first + t + 1);
+      }
+    }
+    tpb_loader_release(h, slot);
+  }
+  for (int i = 0; i < n_samples; ++i) CHECK(seen[i] == 1);
+  tpb_loader_close(h);
+  void* bad = tpb_loader_open("/nonexistent/file.bin", 4, seq, batch, 0, 1, 0, 1, 1, depth, tp.data(), gp.data(), &err);
+  CHECK(bad == nullptr && err != 0);
+}
+
 int main(int argc, char** argv) {
+  test_loader(argc > 1 ? argv[1] : "/tmp");
   test_store();
   test_reducer();
   test_file_io(argc > 1 ? argv[1] : "/tmp");
