@@ -357,6 +357,183 @@ struct GemvRing {
   static constexpr int kBytes = 8 * kStages * kStageVecs * 16;
 };
 
+template <int BITS, int TILES, int KS>
+__global__ void __launch_bounds__(256)
+wq_gemv_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ w,
+                   const __nv_bfloat16* __restrict__ scale, const __nv_bfloat16* __restrict__ zero,
+                   const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ y, int M, int N,
+                   int K, int group, long long ldx, long long ldy) {
+  constexpr int KL = BITS == 8 ? 16 : 32;  // k per lane per chunk = 16 bytes of packed weights
+  constexpr int CH = 4 * KL;
+  constexpr int S = GemvRing<TILES>::kStages;
+  constexpr int SV = GemvRing<TILES>::kStageVecs;
+  constexpr bool kScaled = BITS == 4;      // 8-bit: grouped scales are a run-time property
+  extern __shared__ uint4 gemv_ring[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  uint4* my_ring = gemv_ring + (size_t)warp * S * SV;
+  // KS warps split K for one row tile (TILES x 16 columns); the CTA covers 8 / KS row tiles
+  const int kw = warp % KS;
+  const int n_base = (blockIdx.x * (8 / KS) + warp / KS) * TILES * 16;
+  const int n_chunks = K / CH;
+  const int gpr = group > 0 ? K / group : 1;
+  const bool grouped = kScaled || group > 0;
+  const size_t row_bytes = BITS == 8 ? (size_t)K : (size_t)K / 2;
+  int rown[TILES][2];
+#pragma unroll
+  for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) rown[tl][h] = min(n_base + tl * 16 + g + 8 * h, N - 1);
+  float acc[TILES][4];
+#pragma unroll
+  for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[tl][i] = 0.f;
+
+  // one commit group per chunk, also when the chunk does not exist: the group count stays uniform
+  auto issue_w = [&](int c, int stage) {
+    if (c < n_chunks) {
+      const size_t off = (size_t)(c * CH + t * KL) * BITS / 8;
+#pragma unroll
+      for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          cp_async_16(my_ring + (size_t)stage * SV + (tl * 2 + h) * 32 + lane,
+                      w + (size_t)rown[tl][h] * row_bytes + off);
+    }
+    cp_async_commit();
+  };
+  // x rows of a chunk (KL bf16 of row g, zeros past M) and the chunk's group scales are requested
+  // one chunk ahead in registers: they come from L1 / L2
+  auto load_x = [&](int c, uint32_t (&dst)[KL / 2]) {
+    if (g < M && c < n_chunks) {
+      const uint4* xp = reinterpret_cast<const uint4*>(x + (size_t)g * ldx + c * CH + t * KL);
+#pragma unroll
+      for (int i = 0; i < KL / 8; ++i) {
+        const uint4 v = __ldg(xp + i);
+        dst[4 * i + 0] = v.x; dst[4 * i + 1] = v.y; dst[4 * i + 2] = v.z; dst[4 * i + 3] = v.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < KL / 2; ++i) dst[i] = 0u;
+    }
+  };
+  auto load_s = [&](int c, float (&sc)[TILES][2], float (&zp)[TILES][2]) {
+#pragma unroll
+    for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        sc[tl][h] = 1.f;
+        zp[tl][h] = 8.f;
+        if (grouped && c < n_chunks) {
+          const size_t idx = (size_t)rown[tl][h] * gpr + (group > 0 ? (c * CH + t * KL) / group : 0);
+          sc[tl][h] = __bfloat162float(scale[idx]);
+          if (BITS == 4 && zero) zp[tl][h] = __bfloat162float(zero[idx]);
+        }
+      }
+  };
+
+#pragma unroll
+  for (int s = 0; s < S - 1; ++s) issue_w(kw + KS * s, s);
+  uint32_t xw[KL / 2], xn[KL / 2];
+  float scw[TILES][2], zpw[TILES][2], scn[TILES][2], zpn[TILES][2];
+  load_x(kw, xw);
+  load_s(kw, scw, zpw);
+  int it = 0;
+  for (int c = kw; c < n_chunks; c += KS, ++it) {
+    issue_w(c + KS * (S - 1), (it + S - 1) % S);
+    load_x(c + KS, xn);
+    load_s(c + KS, scn, zpn);
+    cp_async_wait<S - 1>();  // this chunk's group has landed (S - 1 younger ones may be pending)
+    const uint4* st = my_ring + (size_t)(it % S) * SV;
+#pragma unroll
+    for (int tl = 0; tl < TILES; ++tl) {
+      const uint4 w0 = st[(tl * 2 + 0) * 32 + lane], w1 = st[(tl * 2 + 1) * 32 + lane];
+      const uint32_t wv[2][4] = {{w0.x, w0.y, w0.z, w0.w}, {w1.x, w1.y, w1.z, w1.w}};
+      float sc[2], zs[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        // 4-bit: the nibble goes to the top mantissa bits of 1.0 (v = 1 + code / 16) and one FMA
+        // gives (code - zp) * sc = v * (16 sc) - (16 + zp) * sc, the constant exact to 2^-24 of 16 sc
+        sc[h] = BITS == 4 ? 16.f * scw[tl][h] : scw[tl][h];
+        zs[h] = -(16.f + zpw[tl][h]) * scw[tl][h];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (BITS == 8) {
+          uint32_t a[2][2];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint32_t q = wv[h][i] ^ 0x80808080u;  // signed byte -> biased code, value = code - 128
+            float f[4];
+            f[0] = __uint_as_float(__byte_perm(q, 0x4B000000u, 0x7440)) - 8388736.f;
+            f[1] = __uint_as_float(__byte_perm(q, 0x4B000000u, 0x7441)) - 8388736.f;
+            f[2] = __uint_as_float(__byte_perm(q, 0x4B000000u, 0x7442)) - 8388736.f;
+            f[3] = __uint_as_float(__byte_perm(q, 0x4B000000u, 0x7443)) - 8388736.f;
+            if (group > 0) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) f[j] *= sc[h];
+            }
+            a[h][0] = pack_bf16x2(f[0], f[1]);
+            a[h][1] = pack_bf16x2(f[2], f[3]);
+          }
+          mma_bf16_16816(acc[tl], a[0][0], a[1][0], a[0][1], a[1][1], xw[2 * i], xw[2 * i + 1]);
+        } else {
+          uint32_t a[2][4];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint32_t q = wv[h][i];
+            float f[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint32_t sh = (4 * j <= 19) ? (q << (19 - 4 * j)) : (q >> (4 * j - 19));
+              f[j] = fmaf(__uint_as_float((sh & 0x00780000u) | 0x3F800000u), sc[h], zs[h]);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) a[h][j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
+          }
+          mma_bf16_16816(acc[tl], a[0][0], a[1][0], a[0][1], a[1][1], xw[4 * i], xw[4 * i + 1]);
+          mma_bf16_16816(acc[tl], a[0][2], a[1][2], a[0][3], a[1][3], xw[4 * i + 2], xw[4 * i + 3]);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < KL / 2; ++i) xw[i] = xn[i];
+#pragma unroll
+    for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        scw[tl][h] = scn[tl][h];
+        zpw[tl][h] = zpn[tl][h];
+      }
+  }
+  cp_async_wait<0>();
+  __syncthreads();  // every warp is done with its ring: the reduction buffer reuses the memory
+  float* red = reinterpret_cast<float*>(gemv_ring);  // [8][TILES * 128]
+#pragma unroll
+  for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) red[warp * (TILES * 128) + tl * 128 + lane * 4 + i] = acc[tl][i];
+  __syncthreads();
+  for (int o = threadIdx.x; o < (8 / KS) * TILES * 128; o += 256) {
+    const int rt = o / (TILES * 128), e = o % (TILES * 128);  // row tile of the CTA, element in it
+    float a = 0.f;
+#pragma unroll
+    for (int wi = 0; wi < KS; ++wi) a += red[(rt * KS + wi) * (TILES * 128) + e];
+    // accumulator element (lane l, register ci) = (column g + 8 * (ci / 2), row 2 t + (ci & 1))
+    const int tl = e >> 7, l = (e >> 2) & 31, ci = e & 3;
+    const int n = (blockIdx.x * (8 / KS) + rt) * TILES * 16 + tl * 16 + (l >> 2) + ((ci & 2) ? 8 : 0);
+    const int r = 2 * (l & 3) + (ci & 1);
+    if (n < N && r < M) {
+      if (group <= 0 && BITS == 8) a *= __bfloat162float(scale[n]);  // per-channel scale applied once
+      if (bias) a += __bfloat162float(bias[n]);
+      y[(size_t)r * ldy + n] = __float2bfloat16(a);
+    }
+  }
+}
+
+// Second version of the warp-MMA GEMV, selected with tpb_wq_gemv_config(tiles, 2). It has not run
+// on a GPU yet (written after the profile below, when no GPU time was left); the first version
+// above stays the default until the numerics tests have passed with this one.
 // GROUPED: scales (and, for 4 bits, zero points) per group of 2^gshift k; otherwise (8 bits only)
 // one scale per output column, applied once at the end. The loop is written for instruction count
 // (a profile showed ~70 % issue-slot utilisation with "not selected" as the top stall, i.e. the
@@ -364,7 +541,7 @@ struct GemvRing {
 // shift, the ring stage is a counter, and the x / scale registers ping-pong through two bodies.
 template <int BITS, int TILES, int KS, bool GROUPED>
 __global__ void __launch_bounds__(256)
-wq_gemv_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ w,
+wq_gemv_mma_v2_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ w,
                    const __nv_bfloat16* __restrict__ scale, const __nv_bfloat16* __restrict__ zero,
                    const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ y, int M, int N,
                    int K, int gshift, long long ldx, long long ldy) {
@@ -703,11 +880,11 @@ int tpb_gemm_i8(const void* A, const void* B, void* C, const float* a_scale, con
 }
 
 static int g_gemv_tiles = 0;       // 0: pick by N; 1 / 2: 16-column tiles per CTA of the MMA kernel
-static int g_gemv_force_simt = 0;  // 1: always the CUDA-core kernel (for comparison runs)
+static int g_gemv_force_simt = 0;  // 1: always the CUDA-core kernel (for comparison runs); 2: second MMA version
 // Tuning / comparison knobs of the weight-only GEMV (process-wide).
 int tpb_wq_gemv_config(int tiles, int force_simt) {
   g_gemv_tiles = (tiles == 1 || tiles == 2) ? tiles : 0;
-  g_gemv_force_simt = force_simt ? 1 : 0;
+  g_gemv_force_simt = (force_simt == 1 || force_simt == 2) ? force_simt : 0;
   return 0;
 }
 
@@ -725,7 +902,7 @@ int tpb_wq_gemv(const void* x, const void* w, const void* scale, const void* zer
   const __nv_bfloat16 *sc = (const __nv_bfloat16*)scale, *zp = (const __nv_bfloat16*)zero,
                       *bs = (const __nv_bfloat16*)bias;
   const int chunk = bits == 8 ? 64 : 128;
-  const bool mma_ok = !g_gemv_force_simt && K % chunk == 0 && (group <= 0 || (group % (chunk / 4) == 0 && (group & (group - 1)) == 0)) &&
+  const bool mma_ok = g_gemv_force_simt != 1 && K % chunk == 0 && (group <= 0 || group % (chunk / 4) == 0) &&
                       (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
   // two 16-column tiles per CTA halve the reads of x; one keeps more CTAs in flight when N is short
   const int tiles = g_gemv_tiles ? g_gemv_tiles : ((N + 31) / 32 >= sm_count() * 8 ? 2 : 1);
@@ -743,26 +920,46 @@ int tpb_wq_gemv(const void* x, const void* w, const void* scale, const void* zer
       const int ks = bits == 8 ? 8 : 4;
       const int per_cta = 16 * tiles * (8 / ks);
       const int g2 = (N + per_cta - 1) / per_cta;
-      int gshift = 0;
-      while (group > 0 && (1 << gshift) < group) ++gshift;
-      auto launch = [&](auto kern, int smem, int variant) {
-        static bool opted_in[6] = {false, false, false, false, false, false};  // per kernel variant
-        if (!opted_in[variant]) {
-          cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-          opted_in[variant] = true;
+      if (g_gemv_force_simt == 2 && (group <= 0 || (group & (group - 1)) == 0)) {
+        int gshift = 0;
+        while (group > 0 && (1 << gshift) < group) ++gshift;
+        auto launch = [&](auto kern, int smem, int variant) {
+          static bool opted_in[6] = {false, false, false, false, false, false};  // per kernel variant
+          if (!opted_in[variant]) {
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+            opted_in[variant] = true;
+          }
+          kern<<<g2, 256, smem, st>>>(xs, wp, sc, zp, bs, ys, rows, N, K, gshift, ldx, ldy);
+        };
+        if (bits == 8 && group <= 0) {
+          if (tiles == 2) launch(wq_gemv_mma_v2_kernel<8, 2, 8, false>, GemvRing<2>::kBytes, 0);
+          else launch(wq_gemv_mma_v2_kernel<8, 1, 8, false>, GemvRing<1>::kBytes, 1);
+        } else if (bits == 8) {
+          if (tiles == 2) launch(wq_gemv_mma_v2_kernel<8, 2, 8, true>, GemvRing<2>::kBytes, 2);
+          else launch(wq_gemv_mma_v2_kernel<8, 1, 8, true>, GemvRing<1>::kBytes, 3);
+        } else {
+          if (tiles == 2) launch(wq_gemv_mma_v2_kernel<4, 2, 4, true>, GemvRing<2>::kBytes, 4);
+          else launch(wq_gemv_mma_v2_kernel<4, 1, 4, true>, GemvRing<1>::kBytes, 5);
         }
-        kern<<<g2, 256, smem, st>>>(xs, wp, sc, zp, bs, ys, rows, N, K, gshift, ldx, ldy);
-      };
-      if (bits == 8 && group <= 0) {
-        if (tiles == 2) launch(wq_gemv_mma_kernel<8, 2, 8, false>, GemvRing<2>::kBytes, 0);
-        else launch(wq_gemv_mma_kernel<8, 1, 8, false>, GemvRing<1>::kBytes, 1);
-      } else if (bits == 8) {
-        if (tiles == 2) launch(wq_gemv_mma_kernel<8, 2, 8, true>, GemvRing<2>::kBytes, 2);
-        else launch(wq_gemv_mma_kernel<8, 1, 8, true>, GemvRing<1>::kBytes, 3);
-      } else {
-        if (tiles == 2) launch(wq_gemv_mma_kernel<4, 2, 4, true>, GemvRing<2>::kBytes, 4);
-        else launch(wq_gemv_mma_kernel<4, 1, 4, true>, GemvRing<1>::kBytes, 5);
+        continue;
       }
+      auto launch = [&](auto kern, int smem) {
+        static bool opted_in[4] = {false, false, false, false};  // per kernel variant
+        bool& done = opted_in[(bits == 8 ? 0 : 2) + (tiles == 2 ? 1 : 0)];
+        if (!done) {
+          cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+          done = true;
+        }
+        kern<<<g2, 256, smem, st>>>(xs, wp, sc, zp, bs, ys, rows, N, K, group, ldx, ldy);
+      };
+      if (bits == 8 && tiles == 2)
+        launch(wq_gemv_mma_kernel<8, 2, 8>, GemvRing<2>::kBytes);
+      else if (bits == 8)
+        launch(wq_gemv_mma_kernel<8, 1, 8>, GemvRing<1>::kBytes);
+      else if (tiles == 2)
+        launch(wq_gemv_mma_kernel<4, 2, 4>, GemvRing<2>::kBytes);
+      else
+        launch(wq_gemv_mma_kernel<4, 1, 4>, GemvRing<1>::kBytes);
     } else if (bits == 8) {
       wq_gemv_kernel<8><<<grid, 256, 0, st>>>(xs, wp, sc, zp, bs, ys, rows, N, K, group, ldx, ldy);
     } else {

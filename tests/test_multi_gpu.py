@@ -88,8 +88,8 @@ def test_tensor_parallel_and_pipeline_training_on_two_gpus(tp, pp):
     import json
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
-           os.path.join(ROOT, "benchmarks", "bench_llama_3d.py"), "--tp", str(tp), "--pp", str(pp), "--layers", "4",
-           "--microbatches", "4", "--seq", "1024", "--steps", "2", "--warmup", "2"]
+           os.path.join(ROOT, "benchmarks", "bench_llama_3d.py"), "--tp", str(tp), "--pp", str(pp), "--layers", "8",
+           "--microbatches", "4", "--steps", "2", "--warmup", "2"]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     line = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
@@ -102,8 +102,8 @@ def test_composed_tp_pp_layout_trains():
     import json
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
-           os.path.join(ROOT, "benchmarks", "bench_llama_3d.py"), "--layers", "4", "--microbatches", "4",
-           "--seq", "1024", "--steps", "2", "--warmup", "2"]
+           os.path.join(ROOT, "benchmarks", "bench_llama_3d.py"), "--layers", "8", "--microbatches", "4",
+           "--steps", "2", "--warmup", "2"]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     line = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
