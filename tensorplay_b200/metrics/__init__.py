@@ -15,7 +15,8 @@ from torch import Tensor
 
 __all__ = ["Metric", "MeanMetric", "SumMetric", "Accuracy", "Precision", "Recall", "F1Score",
            "ConfusionMatrix", "MeanSquaredError", "MeanAbsoluteError", "R2Score", "Perplexity",
-           "MetricCollection"]
+           "MetricCollection", "PearsonCorrCoef", "SpearmanCorrCoef", "KendallRankCorrCoef", "AUROC",
+           "AveragePrecision", "RetrievalNormalizedDCG", "RetrievalMRR", "CalibrationError", "functional"]
 
 
 class Metric:
@@ -248,3 +249,8 @@ class MetricCollection:
     def reset(self) -> None:
         for m in self.metrics.values():
             m.reset()
+
+
+from . import ranking as functional  # noqa: E402  (pearson_corrcoef, kendall_tau, binary_auroc, ndcg, ...)
+from .ranking import (AUROC, AveragePrecision, CalibrationError, KendallRankCorrCoef, PearsonCorrCoef,  # noqa: E402
+                      RetrievalMRR, RetrievalNormalizedDCG, SpearmanCorrCoef)
