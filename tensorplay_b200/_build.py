@@ -26,7 +26,7 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-Wno-unused-function",
 ]
-CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-pthread"]
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-pthread", "-fopenmp"]
 
 
 def _nvcc() -> str:
@@ -106,7 +106,7 @@ def build_runtime(verbose: bool = False) -> Path:
         with cf.ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(lambda c: _run(c, verbose), jobs))
     if jobs or _newer(objs, lib):
-        _run(["g++", "-shared", "-o", lib, *objs, "-pthread", "-ldl", "-lrt"], verbose)
+        _run(["g++", "-shared", "-o", lib, *objs, "-pthread", "-fopenmp", "-ldl", "-lrt"], verbose)
     return lib
 
 

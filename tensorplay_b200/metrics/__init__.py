@@ -156,6 +156,26 @@ class F1Score(_StatScores):
         return self._reduce(2 * tp, 2 * tp + fp + fn)
 
 
+def _native_diff_sum(preds: Tensor, target: Tensor, kind: str):
+    """Sum of squared / absolute differences by the host runtime's one-pass reduction for float32 CPU
+    inputs, or ``None`` when the inputs do not qualify (other device, dtype or layout)."""
+    if (preds.device.type != "cpu" or preds.dtype != torch.float32 or target.dtype != torch.float32
+            or preds.shape != target.shape or not preds.is_contiguous() or not target.is_contiguous()):
+        return None
+    try:
+        import ctypes as C
+
+        from .. import _native
+        rt = _native.runtime()
+        fn = rt.tpb_sum_sq_diff_f32 if kind == "sq" else rt.tpb_sum_abs_diff_f32
+        if fn.restype is not C.c_double:
+            fn.restype = C.c_double
+            fn.argtypes = [C.c_void_p, C.c_void_p, C.c_longlong]
+        return fn(preds.data_ptr(), target.data_ptr(), preds.numel())
+    except (OSError, AttributeError):
+        return None
+
+
 class MeanSquaredError(Metric):
     def __init__(self, squared: bool = True) -> None:
         super().__init__()
@@ -165,7 +185,11 @@ class MeanSquaredError(Metric):
 
     def update(self, preds: Tensor, target: Tensor) -> None:
         self._to(preds.device)
-        self.sse += ((preds.double() - target.double()) ** 2).sum()
+        # one pass in the input precision; the running sum is kept in double
+        v = _native_diff_sum(preds, target, "sq")
+        if v is None:
+            v = torch.nn.functional.mse_loss(preds.float(), target.float(), reduction="sum").double()
+        self.sse += v
         self.n += preds.numel()
 
     def compute(self) -> Tensor:
@@ -181,7 +205,10 @@ class MeanAbsoluteError(Metric):
 
     def update(self, preds: Tensor, target: Tensor) -> None:
         self._to(preds.device)
-        self.sae += (preds.double() - target.double()).abs().sum()
+        v = _native_diff_sum(preds, target, "abs")
+        if v is None:
+            v = torch.nn.functional.l1_loss(preds.float(), target.float(), reduction="sum").double()
+        self.sae += v
         self.n += preds.numel()
 
     def compute(self) -> Tensor:

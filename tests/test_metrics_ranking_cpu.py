@@ -66,3 +66,18 @@ def _sync_worker(rank, world):
 
 def test_collecting_metric_syncs_samples_across_ranks():
     assert all(run_ranks(_sync_worker, 2))
+
+
+def test_regression_metrics_native_reduction_matches_torch():
+    from tensorplay_b200.metrics import _native_diff_sum
+    g = torch.Generator().manual_seed(4)
+    for n in (1, 7, 4096, 65537, 300001):
+        a, b = torch.randn(n, generator=g), torch.randn(n, generator=g)
+        sq, ab = _native_diff_sum(a, b, "sq"), _native_diff_sum(a, b, "abs")
+        assert sq is not None and ab is not None
+        assert abs(sq - ((a.double() - b.double()) ** 2).sum().item()) < 1e-6 * max(1.0, sq)
+        assert abs(ab - (a.double() - b.double()).abs().sum().item()) < 1e-6 * max(1.0, ab)
+    assert _native_diff_sum(a.double(), b.double(), "sq") is None           # other dtypes take the torch path
+    m = M.MeanSquaredError(squared=False)
+    m.update(a.view(-1, 1)[:, 0], b)
+    torch.testing.assert_close(m.compute(), ((a - b) ** 2).mean().sqrt(), rtol=1e-5, atol=1e-6)
