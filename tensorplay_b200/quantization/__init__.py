@@ -112,3 +112,8 @@ class Float8Linear(torch.nn.Module):
         from .. import ops
         w = dequantize_affine_float8(self.qweight, self.scale, x.dtype)
         return ops.linear(x, w, self.bias)
+
+
+from .awq import AWQLinear, awq_quantize_, search_scales  # noqa: E402
+from .pruning import (WeightSparsifier, compare_models, cubic_sparsity, global_magnitude_masks,  # noqa: E402
+                      magnitude_mask, n_m_mask, sqnr)
