@@ -119,3 +119,23 @@ def test_activation_checkpoint_plan_llama8b():
     assert plan["full"]["kept_bytes"] == 32 * 4096 * 4096 * 2
     assert plan["none"]["kept_bytes"] > plan["selective"]["kept_bytes"] > plan["full"]["kept_bytes"]
     assert plan["full"]["recompute_flops"] == plan["forward_flops"] and plan["selective"]["recompute_flops"] == 0
+
+
+def test_distributed_submodule_paths_resolve():
+    """Every sub-module path of the reference's ``distributed`` package imports (own code, or PyTorch's
+    module of the same role); RPC answers feature probes and refuses use."""
+    import importlib
+
+    import pytest
+    for n in ("_functional_collectives", "_composable", "_shard", "_local_tensor", "nn", "utils", "_state_dict_utils",
+              "collective_utils", "argparse_util", "constants", "remote_device", "logging_handlers", "p10d_logger",
+              "device_mesh", "rendezvous", "checkpoint", "optim", "algorithms", "elastic", "launcher", "tensor",
+              "tensor.parallel", "tensor.experimental", "fsdp", "pipelining", "_symmetric_memory", "_token_switch",
+              "_tools", "debug", "flight_recorder", "watchdog", "run", "store", "ddp"):
+        assert importlib.import_module("tensorplay_b200.distributed." + n) is not None, n
+    from tensorplay_b200.distributed import rpc
+    assert rpc.is_available() is False
+    with pytest.raises(RuntimeError):
+        rpc.init_rpc
+    from tensorplay_b200.distributed._functional_collectives import all_reduce  # noqa: F401
+    from tensorplay_b200.distributed._composable import checkpoint, replicate  # noqa: F401
