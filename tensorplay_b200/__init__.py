@@ -69,6 +69,11 @@ def __getattr__(name):
         return mod
     if name == "graph":
         return _importlib.import_module("torch.fx")
+    if name == "_transforms":   # vmap / grad / jvp / vjp transforms (tensorplay/_transforms)
+        return _importlib.import_module("torch.func")
+    if name in ("stax", "_stax", "primitives"):
+        raise AttributeError(f"tensorplay_b200.{name}: the tracing compiler and its primitive IR are not part of this "
+                             "framework (hand-written kernels instead); see tensorplay_b200.compile for CUDA-graph capture")
     return getattr(_torch, name)
 
 
