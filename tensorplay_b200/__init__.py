@@ -53,6 +53,45 @@ _LAZY_TORCH = {"linalg", "fft", "special", "sparse", "distributions", "func", "f
                "signal", "overrides", "package", "storage", "types", "jit", "_numpy"}
 
 
+class _TorchAliasFinder:
+    """Import fallback for the thin packages: ``tensorplay_b200.<pkg>.<module>`` that is not a file of
+    this framework resolves to ``torch.<pkg>.<module>`` (e.g. ``optim.adam``, ``autograd.function``,
+    ``profiler.profiler``, ``multiprocessing.reductions``), so module paths of the reference that only
+    name PyTorch-equivalent code keep importing. Sits last on ``sys.meta_path``: own modules win."""
+
+    _PKGS = ("optim", "autograd", "profiler", "multiprocessing", "utils", "cuda", "amp", "testing", "nn")
+
+    def find_spec(self, fullname, path=None, target=None):
+        parts = fullname.split(".")
+        if len(parts) < 3 or parts[0] != __name__ or parts[1] not in self._PKGS:
+            return None
+        import importlib.util
+        torch_name = "torch." + ".".join(parts[1:])
+        try:
+            if importlib.util.find_spec(torch_name) is None:
+                return None
+        except (ImportError, ValueError, AttributeError):
+            return None
+        return importlib.util.spec_from_loader(fullname, _TorchAliasLoader(torch_name))
+
+
+class _TorchAliasLoader:
+    def __init__(self, torch_name):
+        self.torch_name = torch_name
+
+    def create_module(self, spec):
+        return _importlib.import_module(self.torch_name)
+
+    def exec_module(self, module):
+        pass
+
+
+import sys as _sys  # noqa: E402
+
+if not [f for f in _sys.meta_path if type(f).__name__ == "_TorchAliasFinder"]:
+    _sys.meta_path.append(_TorchAliasFinder())
+
+
 def __getattr__(name):
     if name in _LAZY_OWN:
         mod = _importlib.import_module(f"{__name__}.{name}")

@@ -139,3 +139,21 @@ def test_distributed_submodule_paths_resolve():
         rpc.init_rpc
     from tensorplay_b200.distributed._functional_collectives import all_reduce  # noqa: F401
     from tensorplay_b200.distributed._composable import checkpoint, replicate  # noqa: F401
+
+
+def test_module_paths_of_thin_packages_fall_back_to_torch():
+    import importlib
+
+    import pytest
+    import tensorplay_b200 as tp
+    from tensorplay_b200.optim.adam import Adam
+    assert Adam is tp.optim.Adam                                   # own file wins
+    for path, torch_path in (("optim.sgd", "torch.optim.sgd"), ("optim.lr_scheduler", "torch.optim.lr_scheduler"),
+                             ("autograd.function", "torch.autograd.function"), ("profiler.profiler", "torch.profiler.profiler"),
+                             ("multiprocessing.reductions", "torch.multiprocessing.reductions"),
+                             ("utils.hooks", "torch.utils.hooks"), ("cuda.nvtx", "torch.cuda.nvtx")):
+        assert importlib.import_module("tensorplay_b200." + path) is importlib.import_module(torch_path)
+    assert importlib.import_module("tensorplay_b200.utils.data").TokenFileLoader is not None   # own module
+    with pytest.raises(ModuleNotFoundError):
+        importlib.import_module("tensorplay_b200.optim.no_such_module")
+    assert tp._transforms.vmap is not None
