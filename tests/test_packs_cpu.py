@@ -157,3 +157,21 @@ def test_module_paths_of_thin_packages_fall_back_to_torch():
     with pytest.raises(ModuleNotFoundError):
         importlib.import_module("tensorplay_b200.optim.no_such_module")
     assert tp._transforms.vmap is not None
+
+
+def test_tensorplay_alias_shares_module_objects():
+    import importlib
+    import sys
+    from tensorplay_b200 import compat
+    compat.install_alias()
+    try:
+        a = importlib.import_module("tensorplay.distributed.fsdp")
+        b = importlib.import_module("tensorplay_b200.distributed.fsdp")
+        assert a is b and a.fully_shard is b.fully_shard
+        assert importlib.import_module("tensorplay.parallel.symm") is importlib.import_module("tensorplay_b200.parallel.symm")
+        assert importlib.import_module("tensorplay.optim.sgd").SGD is not None
+        from tensorplay.nn import RMSNorm  # noqa: F401
+    finally:
+        sys.meta_path[:] = [f for f in sys.meta_path if type(f).__name__ != "_AliasFinder"]
+        for k in [k for k in sys.modules if k == "tensorplay" or k.startswith("tensorplay.")]:
+            del sys.modules[k]
