@@ -7,7 +7,7 @@ from . import cache, functional, generation  # noqa: F401
 from .cache import (Cache, DynamicCache, LinearStateCache, PagedCache, QuantizedCache,
                     SlidingWindowCache, StaticCache)
 from .generation import generate, sample, top_k_top_p_filtering
-from .modules import (CausalEncoderDecoder, CompressedSparseAttention, CrossAttention, GatedDeltaNet, GroupedQueryAttention, KimiDeltaAttention, LayerNorm, Linear,
+from .modules import (DecoderLM, CausalEncoderDecoder, CompressedSparseAttention, CrossAttention, GatedDeltaNet, GroupedQueryAttention, KimiDeltaAttention, LayerNorm, Linear,
                       MultiheadLatentAttention, RMSNorm, RotaryEmbedding, SwiGLUMLP, TransformerBlock,
                       apply_rotary_emb, chunk_gated_delta_rule, gated_delta_rule)
 from . import parallel  # noqa: F401,E402

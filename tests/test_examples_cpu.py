@@ -48,3 +48,25 @@ def test_composed_layout_benchmark_runs_on_gloo_ranks():
     line = json.loads([l for l in out.splitlines() if l.startswith("{")][-1])
     assert line["config"]["parallelism"].startswith("tp2 x pp2") and line["n_gpus"] == 4
     assert 3.0 < line["loss"] < 6.0   # ln(128) = 4.85 at random init
+
+
+def test_quantize_example_recipes():
+    out = _run(["examples/quantize_model.py", "--steps", "60"])
+    lines = {l.split(":")[0]: l for l in out.splitlines() if "perplexity" in l}
+    assert {"bf16/fp32 reference", "int8 weight-only", "int4 weight-only (g128)", "int4 AWQ (g128)", "2:4 pruned"} <= set(lines)
+    ppl = lambda k: float(lines[k].split("perplexity")[1].split()[0])   # noqa: E731
+    assert abs(ppl("int8 weight-only") - ppl("bf16/fp32 reference")) < 0.05 * ppl("bf16/fp32 reference")
+
+
+def test_decoder_lm_cache_equals_recompute():
+    import torch
+    from tensorplay_b200 import nn
+    torch.manual_seed(0)
+    m = nn.DecoderLM(50, 32, 2, 4, 2, tie_embeddings=True)
+    assert m.lm_head.weight is m.embed.weight
+    t = torch.randint(0, 50, (2, 6))
+    assert torch.equal(nn.generate(m, t, max_new_tokens=5, use_cache=True),
+                       nn.generate(m, t, max_new_tokens=5, use_cache=False))
+    loss = m(t[:, :-1], t[:, 1:])
+    loss.backward()
+    assert m.embed.weight.grad is not None
