@@ -52,7 +52,7 @@ def test_composed_layout_benchmark_runs_on_gloo_ranks():
 
 def test_quantize_example_recipes():
     out = _run(["examples/quantize_model.py", "--steps", "60"])
-    lines = {l.split(":")[0]: l for l in out.splitlines() if "perplexity" in l}
+    lines = {l.split(": perplexity")[0]: l for l in out.splitlines() if ": perplexity" in l}
     assert {"bf16/fp32 reference", "int8 weight-only", "int4 weight-only (g128)", "int4 AWQ (g128)", "2:4 pruned"} <= set(lines)
     ppl = lambda k: float(lines[k].split("perplexity")[1].split()[0])   # noqa: E731
     assert abs(ppl("int8 weight-only") - ppl("bf16/fp32 reference")) < 0.05 * ppl("bf16/fp32 reference")
