@@ -55,11 +55,16 @@ class ColwiseParallel(ParallelStyle):
             if sharded and w > 1:
                 y = ctx.all_gather_linear(x2, module.weight)
             else:
+                if w > 1:
+                    # replicated input: every rank back-propagates only its columns' share of dx
+                    x2 = _CopyToRegion.apply(x2, ctx.group)
                 y = torch.nn.functional.linear(x2, module.weight) if not x2.is_cuda else _local_linear(x2, module.weight)
             if module.bias is not None:
                 y = y + module.bias
-            return y
+            # a replicated input keeps its leading dimensions; sequence shards stay [rows, out / world]
+            return y if (sharded and w > 1) else y.view(*shape[:-1], y.shape[-1])
         module.forward = forward
+        module._tp_style = "colwise"
         return module
 
 
@@ -77,7 +82,8 @@ class RowwiseParallel(ParallelStyle):
         scattered = self.output_sharded
 
         def forward(x):
-            x2 = x.reshape(-1, x.shape[-1])
+            shape = x.shape
+            x2 = x.reshape(-1, shape[-1])
             if w == 1:
                 y = torch.nn.functional.linear(x2, module.weight)
             elif scattered:
@@ -86,8 +92,9 @@ class RowwiseParallel(ParallelStyle):
                 y = _AllReduce.apply(torch.nn.functional.linear(x2, module.weight), ctx.group)
             if module.bias is not None:
                 y = y + module.bias
-            return y
+            return y if (scattered and w > 1) else y.view(*shape[:-1], y.shape[-1])
         module.forward = forward
+        module._tp_style = "rowwise"
         return module
 
 
@@ -104,6 +111,22 @@ class SequenceParallel(ParallelStyle):
 def _local_linear(x, w):
     from .... import ops
     return ops.linear(x, w)
+
+
+class _CopyToRegion(torch.autograd.Function):
+    """Identity in forward, all-reduce of the gradient in backward (entry of a tensor-parallel region
+    whose input is replicated)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous().clone()
+        dist.all_reduce(g, group=ctx.group)
+        return g, None
 
 
 class _AllReduce(torch.autograd.Function):
@@ -137,6 +160,17 @@ def parallelize_module(module: nn.Module, device_mesh=None, parallelize_plan: Un
             raise ValueError(f"parallelize_plan key {pattern!r} matches no sub-module")
         for n in matched:
             style.apply(names[n], ctx)
+    # attention modules whose projections were sharded over heads now own num_heads / world heads
+    for m in module.modules():
+        q = getattr(m, "q_proj", None)
+        if (q is not None and getattr(q, "_tp_style", None) == "colwise" and hasattr(m, "num_heads")
+                and not getattr(m, "_tp_heads_local", False)):
+            if m.num_heads % ctx.world or getattr(m, "num_kv_heads", ctx.world) % ctx.world:
+                raise ValueError("the head counts must be divisible by the tensor-parallel degree")
+            m.num_heads //= ctx.world
+            if hasattr(m, "num_kv_heads"):
+                m.num_kv_heads //= ctx.world
+            m._tp_heads_local = True
     return module
 
 
