@@ -1,0 +1,120 @@
+"""Single-process components that had no direct test: Muon, cache kinds, quantised linears, metric
+collection, format conversion, FLOP counter, TensorBoard writer, prefetcher, memory plan."""
+import os
+
+import torch
+from torch import nn as tnn
+
+import tensorplay_b200 as tp
+from tensorplay_b200 import metrics, nn, optim, quantization as Q
+
+
+def test_muon_orthogonalises_and_trains():
+    from tensorplay_b200.optim.muon import newton_schulz
+    g = torch.randn(32, 48, generator=torch.Generator().manual_seed(0))
+    o = newton_schulz(g, steps=8).float()
+    sv = torch.linalg.svdvals(o)
+    assert sv.max() < 1.3 and sv.min() > 0.3          # singular values pulled towards 1
+    torch.manual_seed(0)
+    lin = tnn.Linear(16, 16, bias=False)
+    opt = optim.Muon([lin.weight], lr=0.05)
+    x, y = torch.randn(64, 16), torch.randn(64, 16)
+    first = None
+    for _ in range(30):
+        loss = (lin(x) - y).pow(2).mean()
+        first = first or loss.item()
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+    assert loss.item() < 0.8 * first
+    import pytest
+    with pytest.raises(ValueError):
+        b = tnn.Parameter(torch.zeros(4))
+        b.grad = torch.ones(4)
+        optim.Muon([b]).step()
+
+
+def test_sliding_and_quantised_caches():
+    k = torch.randn(1, 2, 10, 8)
+    sw = nn.SlidingWindowCache(4)
+    sw.update(k[:, :, :6], k[:, :, :6])
+    kk, _ = sw.update(k[:, :, 6:7], k[:, :, 6:7])
+    assert sw.get_seq_length() == 7 and sw.get_window_length() == 4 and kk.shape[2] == 5
+    torch.testing.assert_close(kk[:, :, -1], k[:, :, 6])
+    qc = nn.QuantizedCache()
+    a, _ = qc.update(k[:, :, :5], k[:, :, :5])
+    b, _ = qc.update(k[:, :, 5:], k[:, :, 5:])
+    assert qc.get_seq_length() == 10 and b.shape == k.shape
+    assert (b - k).abs().max() < k.abs().max() / 100     # int8 per (token, head): < 1 % of the range
+    # a decoder produces (nearly) the same greedy tokens through the int8 cache
+    torch.manual_seed(0)
+    m = nn.DecoderLM(40, 32, 2, 4, 2)
+    t = torch.randint(0, 40, (1, 6))
+    ref = nn.generate(m, t, max_new_tokens=4)
+    got = nn.generate(m, t, max_new_tokens=4, past_key_values=nn.QuantizedCache())
+    assert got.shape == ref.shape and (got == ref).float().mean() > 0.8
+
+
+def test_quantised_linear_modules_track_the_float_layer():
+    torch.manual_seed(0)
+    lin = tnn.Linear(128, 64)
+    x = torch.randn(8, 128)
+    ref = lin(x)
+    for mode, tol in (("int8_weight_only", 0.03), ("int8_dynamic", 0.05), ("float8_weight_only", 0.12),
+                      ("int4_weight_only", 0.25)):
+        m = Q.quantize_(tnn.Sequential(tnn.Linear(128, 64)), mode)
+        m[0].load_state_dict(m[0].state_dict())         # buffers round-trip
+        q = Q.quantize_(tnn.Sequential(_copy(lin)), mode)
+        err = (q(x).float() - ref).norm() / ref.norm()
+        assert err < tol, (mode, float(err))
+    kinds = {type(Q.quantize_(tnn.Sequential(_copy(lin)), m)[0]).__name__ for m in ("int8_dynamic", "float8_weight_only")}
+    assert kinds == {"Int8DynamicLinear", "Float8Linear"}
+
+
+def _copy(lin):
+    import copy
+    return copy.deepcopy(lin)
+
+
+def test_metric_collection_and_conversion(tmp_path):
+    mc = metrics.MetricCollection({"acc": metrics.Accuracy(num_classes=3), "f1": metrics.F1Score(num_classes=3, average="macro")})
+    logits = torch.tensor([[2.0, 0, 0], [0, 2.0, 0], [0, 0, 2.0], [2.0, 0, 0]])
+    mc.update(logits, torch.tensor([0, 1, 2, 1]))
+    out = mc.compute()
+    assert abs(out["acc"].item() - 0.75) < 1e-6 and 0 < out["f1"].item() < 1
+    mc.reset()
+    mc.update(logits, torch.tensor([0, 1, 2, 0]))
+    assert mc.compute()["acc"].item() == 1.0
+    # torch zip -> .mega conversion keeps values and metadata is inspectable
+    src, dst = str(tmp_path / "w.pt"), str(tmp_path / "w.mega")
+    state = {"a": torch.arange(6.0).view(2, 3), "b": torch.ones(4, dtype=torch.bfloat16)}
+    tp.save(state, src)
+    tp.serialization.convert_to_mega(src, dst)
+    back = tp.load(dst)
+    assert set(back) == {"a", "b"} and torch.equal(back["a"], state["a"]) and back["b"].dtype == torch.bfloat16
+    assert tp.inspect_checkpoint(dst)["format"] == "mega"
+
+
+def test_flop_counter_tensorboard_prefetcher_and_memory_plan(tmp_path):
+    from tensorplay_b200.distributed._tools import engine_memory_plan
+    from tensorplay_b200.models.llama import Llama, LlamaConfig
+    from tensorplay_b200.parallel import AdamWConfig, FSDPEngine
+    from tensorplay_b200.utils.data import CudaPrefetcher
+    from tensorplay_b200.utils.flop_counter import FlopCounterMode
+    from tensorplay_b200.utils.tensorboard import SummaryWriter
+    lin = tnn.Linear(32, 16, bias=False)
+    with FlopCounterMode(display=False) as fc:
+        lin(torch.randn(8, 32))
+    assert fc.get_total_flops() == 2 * 8 * 32 * 16
+    w = SummaryWriter(str(tmp_path / "tb"))
+    w.add_scalar("loss", 1.0, 0)
+    w.close()
+    assert any(f.startswith("events.out") for f in os.listdir(tmp_path / "tb"))
+    batches = [(torch.full((2,), float(i)), {"y": torch.tensor(i)}) for i in range(3)]
+    got = list(CudaPrefetcher(batches, "cpu"))
+    assert len(got) == 3 and float(got[2][0][0]) == 2.0 and int(got[1][1]["y"]) == 1
+    cfg = LlamaConfig.tiny(hidden_size=32, num_heads=4, num_kv_heads=2, head_dim=8, ffn_size=48, vocab_size=64, num_layers=2)
+    eng = FSDPEngine(Llama(cfg), AdamWConfig())
+    plan = engine_memory_plan(eng)
+    n_params = sum(p.numel() for p in eng.model.parameters())
+    assert plan["units"] == len(eng.units) and plan["sharded_state_bytes"] >= n_params * 16
