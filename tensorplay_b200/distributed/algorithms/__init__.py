@@ -47,7 +47,11 @@ def powerSGD_hook(state, bucket):
     m = t[: side * side].view(side, side)
     err = state.setdefault("err", {}).setdefault(bucket.index(), torch.zeros_like(m))
     m.add_(err)
-    q = state.setdefault("q", {}).setdefault(bucket.index(), torch.randn(side, r, device=t.device, dtype=t.dtype))
+    if bucket.index() not in state.setdefault("q", {}):
+        # the same start matrix on every rank (P = sum_r M_r Q needs one Q): seeded, not the global RNG
+        g = torch.Generator().manual_seed(state.get("seed", 0) + bucket.index())
+        state["q"][bucket.index()] = torch.randn(side, r, generator=g).to(device=t.device, dtype=t.dtype)
+    q = state["q"][bucket.index()]
     p = m @ q
     dist.all_reduce(p, group=pg)
     p, _ = torch.linalg.qr(p.float())

@@ -1,0 +1,149 @@
+"""Distributed components that had no direct test, on gloo ranks: device mesh, ZeRO-1 optimizer,
+DDP communication hooks (bf16 compression, PowerSGD), Join, loss-parallel cross-entropy, sequence
+parallel gradient sync."""
+import copy
+
+import torch
+from torch import nn as tnn
+
+from tests.distutil import run_ranks
+
+
+def _mesh_worker(rank, world):
+    import torch.distributed as dist
+    from tensorplay_b200.distributed.device_mesh import init_device_mesh
+    mesh = init_device_mesh("cpu", (2, 2), mesh_dim_names=("dp", "tp"))
+    tp_g, dp_g = mesh.get_group("tp"), mesh.get_group("dp")
+    t = torch.tensor([float(rank)])
+    dist.all_reduce(t, group=tp_g)                     # tp pairs: {0,1}, {2,3}
+    assert t.item() == (1.0 if rank < 2 else 5.0)
+    t = torch.tensor([float(rank)])
+    dist.all_reduce(t, group=dp_g)                     # dp pairs: {0,2}, {1,3}
+    assert t.item() == (2.0 if rank % 2 == 0 else 4.0)
+    assert mesh["tp"].size() == 2 and mesh.get_local_rank("tp") == rank % 2
+    return True
+
+
+def test_device_mesh_2d_groups():
+    assert all(run_ranks(_mesh_worker, 4))
+
+
+def _zero_worker(rank, world):
+    import torch.distributed as dist
+    from tensorplay_b200.distributed.optim import ZeroRedundancyOptimizer
+    torch.manual_seed(0)
+    model = tnn.Sequential(tnn.Linear(8, 16), tnn.Tanh(), tnn.Linear(16, 4))
+    ref = copy.deepcopy(model)
+    zo = ZeroRedundancyOptimizer(model.parameters(), optimizer_class=torch.optim.AdamW, lr=1e-2)
+    ro = torch.optim.AdamW(ref.parameters(), lr=1e-2)
+    g = torch.Generator().manual_seed(1)
+    for _ in range(3):
+        x = torch.randn(world, 4, 8, generator=g)
+        for m, o, data in ((model, zo, x[rank]), (ref, ro, x.flatten(0, 1))):
+            o.zero_grad()
+            m(data).pow(2).mean().backward()
+            if m is model:
+                for p in m.parameters():
+                    dist.all_reduce(p.grad)
+                    p.grad.div_(world)
+            o.step()
+    for a, b in zip(model.parameters(), ref.parameters()):
+        torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
+    # each rank holds optimizer state for its partition only
+    assert 0 < len(zo.optim.state) < len(list(model.parameters()))
+    return True
+
+
+def test_zero_redundancy_optimizer_matches_full_optimizer():
+    assert all(run_ranks(_zero_worker, 2))
+
+
+def _hooks_worker(rank, world):
+    import torch.distributed as dist
+    from tensorplay_b200.distributed import algorithms as A
+    from tensorplay_b200.distributed.ddp import DistributedDataParallel as DDP
+    torch.manual_seed(0)
+    base = tnn.Sequential(tnn.Linear(32, 32, bias=False), tnn.Tanh(), tnn.Linear(32, 8, bias=False))
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(world, 16, 32, generator=g)
+    ref = copy.deepcopy(base)
+    ref(x.flatten(0, 1)).pow(2).mean().backward()
+    want = [p.grad.clone() for p in ref.parameters()]
+    # bf16 compression: the averaged gradient within bf16 rounding
+    m = DDP(copy.deepcopy(base))
+    m.register_comm_hook(None, A.bf16_compress_hook)
+    m(x[rank]).pow(2).mean().backward()
+    for p, w in zip(m.parameters(), want):
+        torch.testing.assert_close(p.grad, w, rtol=2e-2, atol=2e-3)
+    # PowerSGD at full rank reproduces the average; at rank 2 the error feedback holds the rest
+    for r, exact in ((32, True), (2, False)):
+        m = DDP(copy.deepcopy(base), bucket_cap_mb=1e-3)      # one parameter per bucket
+        state = {"process_group": None, "rank": r}
+        m.register_comm_hook(state, A.powerSGD_hook)
+        m(x[rank]).pow(2).mean().backward()
+        p0, w0 = next(iter(m.parameters())), want[0]
+        same = torch.tensor([float(p0.grad.sum())])
+        both = [torch.zeros(1) for _ in range(world)]
+        dist.all_gather(both, same)
+        assert abs(both[0].item() - both[1].item()) < 1e-5         # identical result on every rank
+        if exact:
+            torch.testing.assert_close(p0.grad, w0, rtol=1e-3, atol=1e-5)
+        else:
+            assert (p0.grad - w0).norm() < w0.norm() and len(state["err"]) > 0
+    return True
+
+
+def test_ddp_comm_hooks():
+    assert all(run_ranks(_hooks_worker, 2))
+
+
+def _join_worker(rank, world):
+    import torch.distributed as dist
+    from tensorplay_b200.distributed.algorithms import Join
+    from torch.nn.parallel import DistributedDataParallel as TorchDDP
+    torch.manual_seed(0)
+    m = TorchDDP(tnn.Linear(4, 2))
+    n_batches = 3 + rank                                     # uneven inputs
+    with Join([m]):
+        for _ in range(n_batches):
+            m(torch.randn(2, 4)).sum().backward()
+    dist.barrier()
+    return n_batches
+
+
+def test_join_with_uneven_inputs():
+    assert run_ranks(_join_worker, 2) == [3, 4]
+
+
+def _loss_parallel_worker(rank, world):
+    import torch.distributed as dist
+    from tensorplay_b200.distributed.tensor.parallel import (SequenceParallel, loss_parallel, parallelize_module,
+                                                             sync_replicated_grads)
+    g = torch.Generator().manual_seed(0)
+    logits = torch.randn(10, 16, generator=g)
+    target = torch.randint(0, 16, (10,), generator=g)
+    full = logits.clone().requires_grad_()
+    ref = torch.nn.functional.cross_entropy(full, target)
+    ref.backward()
+    shard = logits[:, rank * 8: (rank + 1) * 8].clone().requires_grad_()
+    with loss_parallel() as lp:
+        loss = lp.cross_entropy(shard, target)
+    loss.backward()
+    torch.testing.assert_close(loss, ref, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(shard.grad, full.grad[:, rank * 8: (rank + 1) * 8], rtol=1e-5, atol=1e-6)
+    # sequence parallel: a norm sees its rows only; the synchronised gradient is the full one
+    norm = tnn.LayerNorm(6)
+    wrap = tnn.Sequential(norm)
+    parallelize_module(wrap, None, {"0": SequenceParallel()})
+    x = torch.randn(8, 6, generator=g)
+    dense = tnn.LayerNorm(6)
+    dense(x).pow(3).sum().backward()
+    wrap(x[rank * 4: (rank + 1) * 4]).pow(3).sum().backward()
+    sync_replicated_grads(wrap)
+    torch.testing.assert_close(norm.weight.grad, dense.weight.grad, rtol=1e-4, atol=1e-5)
+    dist.barrier()
+    return True
+
+
+def test_loss_parallel_and_sequence_parallel():
+    assert all(run_ranks(_loss_parallel_worker, 2))
