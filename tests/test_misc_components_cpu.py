@@ -118,3 +118,55 @@ def test_flop_counter_tensorboard_prefetcher_and_memory_plan(tmp_path):
     plan = engine_memory_plan(eng)
     n_params = sum(p.numel() for p in eng.model.parameters())
     assert plan["units"] == len(eng.units) and plan["sharded_state_bytes"] >= n_params * 16
+
+
+def test_grad_scaler_with_fused_adamw_and_autocast():
+    from tensorplay_b200 import amp
+    torch.manual_seed(0)
+    lin = tnn.Linear(8, 4)
+    ref = tnn.Linear(8, 4)
+    ref.load_state_dict(lin.state_dict())
+    opt, ropt = optim.AdamW(lin.parameters(), lr=1e-2), torch.optim.AdamW(ref.parameters(), lr=1e-2)
+    scaler = amp.GradScaler("cpu", init_scale=1024.0)
+    x = torch.randn(16, 8)
+    for _ in range(3):
+        with amp.autocast("cpu", dtype=torch.bfloat16):
+            loss = lin(x).float().pow(2).mean()
+        opt.zero_grad()
+        scaler.scale(loss).backward()
+        scaler.step(opt)
+        scaler.update()
+        with amp.autocast("cpu", dtype=torch.bfloat16):
+            l2 = ref(x).float().pow(2).mean()
+        ropt.zero_grad()
+        l2.backward()
+        ropt.step()
+    torch.testing.assert_close(lin.weight, ref.weight, rtol=1e-5, atol=1e-6)   # unscaled inside the step
+    w0 = lin.weight.detach().clone()
+    opt.zero_grad()
+    scaler.scale(lin(x).pow(2).mean()).backward()
+    lin.weight.grad[0, 0] = float("inf")
+    scaler.step(opt)
+    scaler.update()
+    assert torch.equal(lin.weight, w0) and scaler.get_scale() == 512.0          # step skipped, scale halved
+
+
+def test_reexported_utilities_smoke():
+    from tensorplay_b200 import autograd, profiler
+    from tensorplay_b200.utils.checkpoint import checkpoint_sequential
+    from tensorplay_b200.utils.data import DistributedSampler, TensorDataset
+    ds = TensorDataset(torch.arange(10))
+    parts = [list(DistributedSampler(ds, num_replicas=2, rank=r, shuffle=False)) for r in range(2)]
+    assert sorted(parts[0] + parts[1]) == list(range(10))
+    seq = tnn.Sequential(tnn.Linear(4, 4), tnn.Tanh(), tnn.Linear(4, 4), tnn.Tanh())
+    x = torch.randn(3, 4, requires_grad=True)
+    y = checkpoint_sequential(seq, 2, x, use_reentrant=False)
+    torch.testing.assert_close(y, seq(x))
+    y.sum().backward()
+    assert x.grad is not None
+    f = lambda a: (a ** 3).sum()   # noqa: E731
+    assert autograd.gradcheck(f, (torch.randn(4, dtype=torch.float64, requires_grad=True),))
+    with profiler.profile(activities=[profiler.ProfilerActivity.CPU]) as prof:
+        with profiler.record_function("my_region"):
+            torch.randn(64, 64) @ torch.randn(64, 64)
+    assert any(e.key == "my_region" for e in prof.key_averages())
