@@ -170,3 +170,23 @@ def test_reexported_utilities_smoke():
         with profiler.record_function("my_region"):
             torch.randn(64, 64) @ torch.randn(64, 64)
     assert any(e.key == "my_region" for e in prof.key_averages())
+
+
+def test_every_cache_kind_reproduces_cache_free_generation():
+    torch.manual_seed(0)
+    m = nn.DecoderLM(48, 32, 2, 4, 2)
+    t = torch.randint(0, 48, (2, 5))
+    ref = nn.generate(m, t, max_new_tokens=6, use_cache=False)
+    for cache in (nn.DynamicCache(), nn.StaticCache(32), nn.PagedCache(block_size=4), nn.SlidingWindowCache(64)):
+        out = nn.generate(m, t, max_new_tokens=6, past_key_values=cache)
+        assert torch.equal(out, ref), type(cache).__name__
+        assert cache.get_seq_length(0) == 10               # 5 prompt + 5 fed-back tokens
+    # module-level pieces against formulas
+    x = torch.randn(3, 7, 32)
+    norm = nn.RMSNorm(32, eps=1e-6)
+    torch.testing.assert_close(norm(x), x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6) * norm.weight)
+    y, s = norm(x, residual=x)
+    torch.testing.assert_close(s, 2 * x)
+    att = nn.GroupedQueryAttention(32, 4, 2)
+    full = att(x)
+    torch.testing.assert_close(att(x[:, :4]), full[:, :4], rtol=1e-5, atol=1e-5)    # causal: a prefix is unchanged
