@@ -19,8 +19,8 @@ from torch import nn
 
 from ....parallel.tp import TPContext, _AllGatherRows, _ReduceScatterRows
 
-__all__ = ["ParallelStyle", "ColwiseParallel", "RowwiseParallel", "SequenceParallel", "parallelize_module",
-           "loss_parallel"]
+__all__ = ["ParallelStyle", "ColwiseParallel", "RowwiseParallel", "SequenceParallel", "PrepareModuleInput",
+           "PrepareModuleOutput", "PrepareModuleInputOutput", "input_reshard", "parallelize_module", "loss_parallel"]
 
 
 class ParallelStyle:
@@ -106,6 +106,159 @@ class SequenceParallel(ParallelStyle):
         for p in module.parameters():
             p._tp_replicated = True
         return module
+
+
+class _GatherToReplicate(torch.autograd.Function):
+    """Row shards -> replicated tensor. The gradient of a replicated tensor is the same on every
+    rank, so backward keeps this rank's rows (no reduction)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        w = dist.get_world_size(group)
+        out = x.new_empty(x.shape[0] * w, *x.shape[1:])
+        dist.all_gather_into_tensor(out, x.contiguous(), group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        w, r = dist.get_world_size(ctx.group), dist.get_rank(ctx.group)
+        n = g.shape[0] // w
+        return g[r * n: (r + 1) * n].contiguous(), None
+
+
+class _SliceToShard(torch.autograd.Function):
+    """Replicated tensor -> this rank's rows; backward gathers the row gradients of all ranks."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        w, r = dist.get_world_size(group), dist.get_rank(group)
+        assert x.shape[0] % w == 0, "rows not divisible by the tensor-parallel degree"
+        n = x.shape[0] // w
+        return x[r * n: (r + 1) * n].contiguous()
+
+    @staticmethod
+    def backward(ctx, g):
+        w = dist.get_world_size(ctx.group)
+        out = g.new_empty(g.shape[0] * w, *g.shape[1:])
+        dist.all_gather_into_tensor(out, g.contiguous(), group=ctx.group)
+        return out, None
+
+
+def _layout_name(layout) -> str:
+    """``"shard"`` / ``"replicate"`` from a string or a placement object (``Shard(0)``, ``Replicate()``)."""
+    name = layout if isinstance(layout, str) else type(layout).__name__
+    name = name.lower()
+    if name.startswith("shard"):
+        return "shard"
+    if name.startswith("replicate"):
+        return "replicate"
+    raise ValueError(f"unknown layout {layout!r}")
+
+
+def _convert(t, src, dst, ctx: TPContext):
+    if not isinstance(t, torch.Tensor) or src is None or dst is None or ctx.world == 1:
+        return t
+    a, b = _layout_name(src), _layout_name(dst)
+    if a == b:
+        return t
+    return _GatherToReplicate.apply(t, ctx.group) if a == "shard" else _SliceToShard.apply(t, ctx.group)
+
+
+def _as_tuple(x, n):
+    if isinstance(x, (tuple, list)):
+        return tuple(x)
+    return (x,) * n if n else (x,)
+
+
+class PrepareModuleInput(ParallelStyle):
+    """Convert the layouts of a module's positional inputs before its forward: ``"shard"`` (rows of
+    dimension 0 split over the group) or ``"replicate"``; ``None`` leaves an argument alone."""
+
+    def __init__(self, *, input_layouts=None, desired_input_layouts=None):
+        self.src, self.dst = input_layouts, desired_input_layouts
+
+    def apply(self, module: nn.Module, ctx: TPContext) -> nn.Module:
+        def pre(mod, args):
+            src, dst = _as_tuple(self.src, len(args)), _as_tuple(self.dst, len(args))
+            return tuple(_convert(a, src[i] if i < len(src) else None, dst[i] if i < len(dst) else None, ctx)
+                         for i, a in enumerate(args))
+        module.register_forward_pre_hook(pre)
+        return module
+
+
+class PrepareModuleOutput(ParallelStyle):
+    """Convert the layouts of a module's outputs after its forward."""
+
+    def __init__(self, *, output_layouts=None, desired_output_layouts=None):
+        self.src, self.dst = output_layouts, desired_output_layouts
+
+    def apply(self, module: nn.Module, ctx: TPContext) -> nn.Module:
+        def post(mod, args, out):
+            if isinstance(out, tuple):
+                src, dst = _as_tuple(self.src, len(out)), _as_tuple(self.dst, len(out))
+                return tuple(_convert(o, src[i] if i < len(src) else None, dst[i] if i < len(dst) else None, ctx)
+                             for i, o in enumerate(out))
+            return _convert(out, _as_tuple(self.src, 1)[0], _as_tuple(self.dst, 1)[0], ctx)
+        module.register_forward_hook(post)
+        return module
+
+
+class PrepareModuleInputOutput(ParallelStyle):
+    def __init__(self, *, input_layouts=None, desired_input_layouts=None, output_layouts=None,
+                 desired_output_layouts=None):
+        self.inp = PrepareModuleInput(input_layouts=input_layouts, desired_input_layouts=desired_input_layouts)
+        self.out = PrepareModuleOutput(output_layouts=output_layouts, desired_output_layouts=desired_output_layouts)
+
+    def apply(self, module: nn.Module, ctx: TPContext) -> nn.Module:
+        return self.out.apply(self.inp.apply(module, ctx), ctx)
+
+
+def input_reshard(module: nn.Module, tp_device_mesh=None, input_reshard_dim: Optional[int] = 0, *, group=None) -> nn.Module:
+    """Keep only this rank's slice (along ``input_reshard_dim``) of the replicated input that a
+    tensor-parallel module saves for backward, and all-gather it when backward needs it: activation
+    memory of the saved inputs drops by the tensor-parallel degree."""
+    if input_reshard_dim is None:
+        return module
+    if tp_device_mesh is not None:
+        group = tp_device_mesh.get_group()
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world == 1:
+        return module
+    rank = dist.get_rank(group)
+    state = {}
+
+    def pre(mod, args):
+        first = args[0] if args and isinstance(args[0], torch.Tensor) else None
+        marker = first.data_ptr() if first is not None else None
+        shape = tuple(first.shape) if first is not None else None
+
+        def pack(t):
+            if (marker is not None and t.data_ptr() == marker and tuple(t.shape) == shape
+                    and t.shape[input_reshard_dim] % world == 0):
+                n = t.shape[input_reshard_dim] // world
+                return ("shard", t.narrow(input_reshard_dim, rank * n, n).clone())
+            return ("full", t)
+
+        def unpack(item):
+            kind, t = item
+            if kind == "full":
+                return t
+            parts = [torch.empty_like(t) for _ in range(world)]
+            dist.all_gather(parts, t.contiguous(), group=group)
+            return torch.cat(parts, dim=input_reshard_dim)
+        cm = torch.autograd.graph.saved_tensors_hooks(pack, unpack)
+        cm.__enter__()
+        state["cm"] = cm
+
+    def post(mod, args, out):
+        cm = state.pop("cm", None)
+        if cm is not None:
+            cm.__exit__(None, None, None)
+    module.register_forward_pre_hook(pre)
+    module.register_forward_hook(post)
+    return module
 
 
 def _local_linear(x, w):

@@ -50,3 +50,59 @@ def _worker(rank, world):
 
 def test_parallelize_module_on_decoder_lm():
     assert all(run_ranks(_worker, 2))
+
+
+def _prepare_worker(rank, world):
+    import torch.distributed as dist
+    from torch import nn as tnn
+    from tensorplay_b200.distributed.tensor.parallel import (ColwiseParallel, PrepareModuleInput, PrepareModuleInputOutput,
+                                                             PrepareModuleOutput, RowwiseParallel, input_reshard,
+                                                             parallelize_module)
+    torch.manual_seed(0)
+
+    class MLP(tnn.Module):
+        def __init__(self):
+            super().__init__()
+            self.up, self.down = tnn.Linear(16, 32, bias=False), tnn.Linear(32, 16, bias=False)
+
+        def forward(self, x):
+            return self.down(torch.tanh(self.up(x)))
+    dense = MLP()
+    tp = copy.deepcopy(dense)
+    # sequence-sharded rows in and out; replicated inside the block
+    parallelize_module(tp, None, {
+        "": PrepareModuleInputOutput(input_layouts="shard", desired_input_layouts="replicate",
+                                     output_layouts="replicate", desired_output_layouts="shard"),
+        "up": ColwiseParallel(input_sharded=False), "down": RowwiseParallel(output_sharded=False)})
+    x = torch.randn(8, 16, generator=torch.Generator().manual_seed(1))
+    xl = x[rank * 4: (rank + 1) * 4].clone().requires_grad_()
+    xd = x.clone().requires_grad_()
+    y = tp(xl)
+    yd = dense(xd)
+    torch.testing.assert_close(y, yd[rank * 4: (rank + 1) * 4], rtol=1e-5, atol=1e-6)
+    # the loss is the sum over all rows: each rank contributes its rows
+    y.pow(2).sum().backward()
+    yd.pow(2).sum().backward()
+    torch.testing.assert_close(xl.grad, xd.grad[rank * 4: (rank + 1) * 4], rtol=1e-4, atol=1e-6)
+    torch.testing.assert_close(tp.up.weight.grad, dense.up.weight.grad[rank * 16: (rank + 1) * 16], rtol=1e-4, atol=1e-6)
+    # placement objects are accepted as layouts; the single-direction styles compose the same way
+    from torch.distributed.tensor import Replicate, Shard
+    m2 = copy.deepcopy(dense)
+    parallelize_module(m2, None, {"": PrepareModuleInput(input_layouts=Shard(0), desired_input_layouts=Replicate())})
+    parallelize_module(m2, None, {"": PrepareModuleOutput(output_layouts=Replicate(), desired_output_layouts=Shard(0))})
+    torch.testing.assert_close(m2(x[rank * 4: (rank + 1) * 4]), yd[rank * 4: (rank + 1) * 4].detach(), rtol=1e-5, atol=1e-6)
+    # input_reshard: same gradients, the saved input is a slice
+    m3, m4 = copy.deepcopy(dense), copy.deepcopy(dense)
+    input_reshard(m3.up, None, 0, group=dist.group.WORLD)
+    a = x.clone().requires_grad_()
+    b = x.clone().requires_grad_()
+    m3(a).pow(2).sum().backward()
+    m4(b).pow(2).sum().backward()
+    torch.testing.assert_close(a.grad, b.grad)
+    torch.testing.assert_close(m3.up.weight.grad, m4.up.weight.grad)
+    dist.barrier()
+    return True
+
+
+def test_prepare_module_styles_and_input_reshard():
+    assert all(run_ranks(_prepare_worker, 2))
