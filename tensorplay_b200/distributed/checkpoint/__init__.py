@@ -7,3 +7,14 @@ plus ``.metadata``; ``async_save`` stages to host memory and writes in the backg
 from .api import (ShardedTensor, Stateful, async_save, engine_state_dict, load, load_engine_state_dict, save)
 
 __all__ = ["ShardedTensor", "Stateful", "save", "async_save", "load", "engine_state_dict", "load_engine_state_dict"]
+
+
+def __getattr__(name):
+    """Planner, storage, metadata and state-dict helper names that this package does not define resolve to PyTorch's distributed checkpoint (usable through ``save(..., storage_writer=...)`` / ``load(..., storage_reader=...)``)."""
+    import importlib
+    for mod in ['torch.distributed.checkpoint', 'torch.distributed.checkpoint.state_dict', 'torch.distributed.checkpoint.metadata', 'torch.distributed.checkpoint.planner', 'torch.distributed.checkpoint.optimizer', 'torch.distributed.checkpoint.state_dict_saver', 'torch.distributed.checkpoint.state_dict_loader', 'torch.distributed.checkpoint.filesystem']:
+        try:
+            return getattr(importlib.import_module(mod), name)
+        except (ImportError, AttributeError):
+            continue
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

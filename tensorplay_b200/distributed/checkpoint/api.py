@@ -116,9 +116,16 @@ def _write(checkpoint_id: str, rank: int, tensors: Dict[str, torch.Tensor], all_
         os.replace(tmp, os.path.join(checkpoint_id, META_FILE))  # the checkpoint is valid once this exists
 
 
-def save(state_dict: Mapping[str, Any], *, checkpoint_id: str, process_group=None) -> None:
+def save(state_dict: Mapping[str, Any], *, checkpoint_id: Optional[str] = None, process_group=None,
+         storage_writer=None, planner=None, **kw) -> None:
     """Collective save of ``state_dict`` (tensors, ``ShardedTensor`` / DTensor shards, Stateful
-    objects, plain values) into the directory ``checkpoint_id``."""
+    objects, plain values) into the directory ``checkpoint_id``. A ``storage_writer`` or ``planner``
+    (``FileSystemWriter``, ``DefaultSavePlanner`` ...: PyTorch's planner / storage layer) selects
+    PyTorch's implementation and on-disk layout for the whole call."""
+    if storage_writer is not None or planner is not None:
+        import torch.distributed.checkpoint as tdcp
+        return tdcp.save(state_dict, checkpoint_id=checkpoint_id, storage_writer=storage_writer, planner=planner,
+                         process_group=process_group, **kw)
     world, rank = _world(process_group)
     tensors, meta = _plan_save(_flatten(state_dict), rank)
     all_meta = [meta]
@@ -160,10 +167,17 @@ def _overlap(dst_off, dst_size, src_off, src_size):
     return lo, hi
 
 
-def load(state_dict: Dict[str, Any], *, checkpoint_id: str, process_group=None) -> Dict[str, Any]:
+def load(state_dict: Dict[str, Any], *, checkpoint_id: Optional[str] = None, process_group=None,
+         storage_reader=None, planner=None, **kw) -> Dict[str, Any]:
     """Fill ``state_dict`` in place from the checkpoint: tensors are overwritten, ``ShardedTensor``
     entries receive the slices that overlap their ``[offsets, offsets + shape)`` window (whatever
-    the sharding was at save time), Stateful objects get ``load_state_dict``."""
+    the sharding was at save time), Stateful objects get ``load_state_dict``. With a
+    ``storage_reader`` or ``planner`` the call goes to PyTorch's implementation (see :func:`save`)."""
+    if storage_reader is not None or planner is not None:
+        import torch.distributed.checkpoint as tdcp
+        tdcp.load(state_dict, checkpoint_id=checkpoint_id, storage_reader=storage_reader, planner=planner,
+                  process_group=process_group, **kw)
+        return state_dict
     with open(os.path.join(checkpoint_id, META_FILE)) as f:
         meta = json.load(f)["state_dict_metadata"]
     files: Dict[int, dict] = {}

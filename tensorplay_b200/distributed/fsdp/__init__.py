@@ -21,3 +21,14 @@ from .api import (BackwardPrefetch, CPUOffload, CPUOffloadPolicy, FSDPModule, Fu
 
 __all__ = ["fully_shard", "FSDPModule", "MixedPrecisionPolicy", "CPUOffloadPolicy", "OffloadPolicy",
            "FullyShardedDataParallel", "ShardingStrategy", "MixedPrecision", "CPUOffload", "BackwardPrefetch"]
+
+
+def __getattr__(name):
+    """State-dict configuration classes, ``StateDictType``, ``FlatParameter``, ``UnshardHandle`` and ``register_fsdp_forward_method`` resolve to PyTorch's."""
+    import importlib
+    for mod in ['torch.distributed.fsdp', 'torch.distributed.fsdp._flat_param']:
+        try:
+            return getattr(importlib.import_module(mod), name)
+        except (ImportError, AttributeError):
+            continue
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

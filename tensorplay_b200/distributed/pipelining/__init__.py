@@ -10,3 +10,14 @@ from .stage import PipelineStage
 
 __all__ = ["PipelineStage", "ScheduleGPipe", "Schedule1F1B", "ScheduleInterleaved1F1B",
            "PipelineScheduleSingle", "PipelineScheduleMulti", "split_args_kwargs_into_chunks", "merge_chunks"]
+
+
+def __getattr__(name):
+    """The tracing front-end (``pipeline``, ``Pipe``, ``SplitPoint``, ``pipe_split``, ``build_stage``) and the zero-bubble schedule classes resolve to PyTorch's; they work with PyTorch's stage objects, the schedules defined here with :class:`PipelineStage`."""
+    import importlib
+    for mod in ['torch.distributed.pipelining', 'torch.distributed.pipelining.schedules']:
+        try:
+            return getattr(importlib.import_module(mod), name)
+        except (ImportError, AttributeError):
+            continue
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -6,3 +6,14 @@ from torch.distributed.tensor import (DTensor, Partial, Placement, Replicate, Sh
 from torch.distributed.tensor import (empty, full, init_device_mesh, ones, rand, randn, zeros)  # noqa: F401
 
 from . import experimental, parallel  # noqa: F401
+
+
+def __getattr__(name):
+    """Other DTensor factory and helper names resolve to PyTorch's."""
+    import importlib
+    for mod in ['torch.distributed.tensor', 'torch.distributed.device_mesh']:
+        try:
+            return getattr(importlib.import_module(mod), name)
+        except (ImportError, AttributeError):
+            continue
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -175,3 +175,33 @@ def test_tensorplay_alias_shares_module_objects():
         sys.meta_path[:] = [f for f in sys.meta_path if type(f).__name__ != "_AliasFinder"]
         for k in [k for k in sys.modules if k == "tensorplay" or k.startswith("tensorplay.")]:
             del sys.modules[k]
+
+
+def test_distributed_subpackage_names_and_dcp_storage_delegation(tmp_path):
+    import torch
+    import tensorplay_b200.distributed.checkpoint as dcp
+    import tensorplay_b200.distributed.fsdp as fsdp
+    import tensorplay_b200.distributed.optim as dopt
+    import tensorplay_b200.distributed.pipelining as pipe
+    import tensorplay_b200.distributed.tensor as dt
+    for mod, names in ((dcp, ["FileSystemWriter", "FileSystemReader", "DefaultSavePlanner", "DefaultLoadPlanner", "Metadata",
+                              "get_model_state_dict", "set_model_state_dict", "get_state_dict", "StateDictOptions"]),
+                       (fsdp, ["StateDictType", "FullStateDictConfig", "ShardedStateDictConfig", "register_fsdp_forward_method"]),
+                       (dt, ["DeviceMesh", "DTensor", "Shard"]), (dopt, ["PostLocalSGDOptimizer", "ZeroRedundancyOptimizer"]),
+                       (pipe, ["pipeline", "SplitPoint", "ScheduleLoopedBFS", "Schedule1F1B", "PipelineStage"])):
+        for n in names:
+            assert hasattr(mod, n), (mod.__name__, n)
+    assert pipe.Schedule1F1B.__module__.startswith("tensorplay_b200")          # own classes win
+    # a storage writer / reader routes the call to the planner-based implementation
+    state = {"w": torch.arange(12.0).view(3, 4), "step": 3}
+    d = str(tmp_path / "ck")
+    dcp.save(state, storage_writer=dcp.FileSystemWriter(d))
+    out = {"w": torch.zeros(3, 4), "step": 0}
+    dcp.load(out, storage_reader=dcp.FileSystemReader(d))
+    assert torch.equal(out["w"], state["w"]) and out["step"] == 3
+    # the default path keeps its own layout
+    d2 = str(tmp_path / "ck2")
+    dcp.save(state, checkpoint_id=d2)
+    out2 = {"w": torch.zeros(3, 4), "step": 0}
+    dcp.load(out2, checkpoint_id=d2)
+    assert torch.equal(out2["w"], state["w"])
