@@ -192,3 +192,6 @@ SURROGATES = {c.__name__: c for c in (
     ErfSurrogate, PiecewiseQuadraticSurrogate, PiecewiseExpSurrogate, SuperSpikeSurrogate,
     NonzeroSignLogAbsSurrogate, PiecewiseLeakyRELUSurrogate, LeakyKRELUSurrogate, S2NNSurrogate,
     QPseudoSpikeSurrogate, FourierSeriesSurrogate)}
+
+SquarewaveFourierSeriesSurrogate = FourierSeriesSurrogate
+SURROGATES["SquarewaveFourierSeriesSurrogate"] = FourierSeriesSurrogate
