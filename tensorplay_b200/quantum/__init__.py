@@ -18,7 +18,11 @@ from .measure import (apply_measurement_basis, apply_pauli_word, apply_readout_e
                       counts_from_indices, density_probs, expectation, expectation_from_counts,
                       expectation_from_density, gen_bitstrings, joint_expectation, marginal_probs, measure, probs,
                       readout_error_matrix, sample_indices)
-from .physics import (Hamiltonian, amplitude_damping_kraus, apply_amplitude_damping, apply_bit_flip, apply_channel,
+from .physics import (Hamiltonian, Lindbladian, apply_reset, sample_energy, amplitude_damping_kraus, apply_amplitude_damping, apply_bit_flip, apply_channel,
                       apply_depolarizing, apply_phase_flip, bit_flip_kraus, density_matrix, depolarizing_kraus,
                       dissipator, energy, energy_from_density, lindbladian, matrix_exp_evolve, mesolve, param_shift,
                       pauli_kraus, phase_flip_kraus, sesolve, trotter_evolve)
+from .states import (basis_state, bloch2dens, bloch2sv, dens2bloch, density_from_counts, density_mixture,  # noqa: E402
+                     density_to_state, encode_state, fidelity, flatten, global_phase, inner, norm, normalize,
+                     partial_trace, plus_state, product_state, random_state, state_from_bases, state_from_counts,
+                     sv2bloch, to_density, unflatten, zeros_state)

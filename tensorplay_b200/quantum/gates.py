@@ -69,9 +69,9 @@ def dagger(m: Tensor) -> Tensor:
 
 
 def _angle(theta: Angle, dtype=torch.complex64, device=None) -> Tensor:
-    if not isinstance(theta, Tensor):
-        theta = torch.tensor(float(theta), device=device)
     real = torch.float64 if _cdtype(dtype) == torch.complex128 else torch.float32
+    if not isinstance(theta, Tensor):
+        return torch.tensor(float(theta), dtype=real, device=device)   # no detour through float32
     return theta.to(real)
 
 
@@ -317,3 +317,101 @@ def apply_mcx(state: Tensor, controls: Sequence[int], target: int) -> Tensor:
 
 def apply_multirz(state: Tensor, theta: Angle, wires: Sequence[int]) -> Tensor:
     return apply_pauli_rotation(state, theta, "Z" * len(wires), wires)
+
+
+# ----------------------------------------------------------------------------- further fixed and parametrised gates
+def _matrix_power(m: Tensor, p: float) -> Tensor:
+    """Principal ``p``-th power of a unitary through its eigen-decomposition."""
+    vals, vecs = torch.linalg.eig(m.to(torch.complex128))
+    return ((vecs * vals.pow(p)) @ torch.linalg.inv(vecs)).to(m.dtype)
+
+
+def sh_matrix(dtype=torch.complex64, device=None): return _matrix_power(h_matrix(dtype, device), 0.5)
+def sswap_matrix(dtype=torch.complex64, device=None): return _matrix_power(swap_matrix(dtype, device), 0.5)
+
+
+def dcx_matrix(dtype=torch.complex64, device=None):
+    """Double CNOT: ``CX(0, 1)`` followed by ``CX(1, 0)``."""
+    cx01 = controlled_matrix(x_matrix(dtype, device))
+    sw = swap_matrix(dtype, device)
+    return (sw @ cx01 @ sw) @ cx01
+
+
+def ecr_matrix(dtype=torch.complex64, device=None):
+    r = 1 / math.sqrt(2)
+    return _const([[0, 0, r, 1j * r], [0, 0, 1j * r, r], [r, -1j * r, 0, 0], [-1j * r, r, 0, 0]], dtype, device)
+
+
+def rccx_matrix(dtype=torch.complex64, device=None):
+    """Relative-phase Toffoli (Margolus): CCX up to phases ``-1`` on |101> and ``-i / i`` swaps on the last block."""
+    m = torch.eye(8, dtype=_cdtype(dtype), device=device)
+    m[5, 5] = -1
+    m[6, 6], m[7, 7] = 0, 0
+    m[6, 7], m[7, 6] = -1j, 1j
+    return m
+
+
+def rc3x_matrix(dtype=torch.complex64, device=None):
+    """Relative-phase triple-controlled X."""
+    m = torch.eye(16, dtype=_cdtype(dtype), device=device)
+    m[12, 12], m[13, 13] = 1j, -1j
+    m[14, 14], m[15, 15] = 0, 0
+    m[14, 15], m[15, 14] = 1, -1
+    return m
+
+
+def single_excitation_matrix(theta: Angle, dtype=torch.complex64, device=None) -> Tensor:
+    """Givens rotation in the {|01>, |10>} subspace by ``theta / 2``."""
+    t = _angle(theta, dtype, device) / 2
+    cd = _cdtype(dtype)
+    c, s = torch.cos(t).to(cd), torch.sin(t).to(cd)
+    one, z = torch.ones_like(c), torch.zeros_like(c)
+    rows = [torch.stack(r, -1) for r in ((one, z, z, z), (z, c, -s, z), (z, s, c, z), (z, z, z, one))]
+    return torch.stack(rows, -2)
+
+
+def xx_plus_yy_matrix(theta: Angle, beta: Angle = 0.0, dtype=torch.complex64, device=None) -> Tensor:
+    """``exp(-i theta/2 (XX + YY)/2)`` conjugated by ``RZ(beta)`` on qubit 0: acts on {|01>, |10>}."""
+    t = _angle(theta, dtype, device) / 2
+    b = _angle(beta, dtype, device)
+    cd = _cdtype(dtype)
+    c, s = torch.cos(t).to(cd), torch.sin(t).to(cd)
+    em, ep = torch.polar(torch.ones_like(b), -b).to(cd), torch.polar(torch.ones_like(b), b).to(cd)
+    one, z = torch.ones_like(c), torch.zeros_like(c)
+    rows = [torch.stack(r, -1) for r in ((one, z, z, z), (z, c, -1j * s * em, z), (z, -1j * s * ep, c, z), (z, z, z, one))]
+    return torch.stack(rows, -2)
+
+
+def xx_minus_yy_matrix(theta: Angle, beta: Angle = 0.0, dtype=torch.complex64, device=None) -> Tensor:
+    """``exp(-i theta/2 (XX - YY)/2)`` with phase ``beta``: acts on {|00>, |11>}."""
+    t = _angle(theta, dtype, device) / 2
+    b = _angle(beta, dtype, device)
+    cd = _cdtype(dtype)
+    c, s = torch.cos(t).to(cd), torch.sin(t).to(cd)
+    em, ep = torch.polar(torch.ones_like(b), -b).to(cd), torch.polar(torch.ones_like(b), b).to(cd)
+    one, z = torch.ones_like(c), torch.zeros_like(c)
+    rows = [torch.stack(r, -1) for r in ((c, z, z, -1j * s * em), (z, one, z, z), (z, z, one, z), (-1j * s * ep, z, z, c))]
+    return torch.stack(rows, -2)
+
+
+def multirz_eigvals(theta: Angle, n: int, dtype=torch.complex64, device=None) -> Tensor:
+    """Diagonal of ``exp(-i theta/2 Z^{(x) n})``: ``exp(-+ i theta/2)`` by the parity of the index."""
+    t = _angle(theta, dtype, device) / 2
+    idx = torch.arange(2 ** n, device=t.device)
+    parity = torch.zeros_like(idx)
+    for k in range(n):
+        parity = parity ^ ((idx >> k) & 1)
+    sign = (1 - 2 * parity).to(t.dtype)
+    return torch.polar(torch.ones(2 ** n, dtype=t.dtype, device=t.device), -t[..., None] * sign).to(_cdtype(dtype))
+
+
+def multirz_matrix(theta: Angle, n: int, dtype=torch.complex64, device=None) -> Tensor:
+    return torch.diag_embed(multirz_eigvals(theta, n, dtype, device))
+
+
+apply_shadamard, apply_sswap = _fixed("shadamard", sh_matrix, 1), _fixed("sswap", sswap_matrix, 2)
+apply_dcx, apply_ecr = _fixed("dcx", dcx_matrix, 2), _fixed("ecr", ecr_matrix, 2)
+apply_rccx, apply_rc3x = _fixed("rccx", rccx_matrix, 3), _fixed("rc3x", rc3x_matrix, 4)
+apply_single_excitation = _param("single_excitation", single_excitation_matrix, 2)
+apply_xx_plus_yy = _param("xx_plus_yy", xx_plus_yy_matrix, 2, 2)
+apply_xx_minus_yy = _param("xx_minus_yy", xx_minus_yy_matrix, 2, 2)

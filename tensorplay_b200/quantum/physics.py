@@ -155,3 +155,59 @@ def param_shift(fn: Callable[[Tensor], Tensor], params: Tensor, shift: float = m
             d = fn(plus.view_as(params)) - fn(minus.view_as(params))
         grads.view(-1)[i] = d.sum() / (2 * math.sin(shift))
     return grads
+
+
+def apply_reset(rho: Tensor, wire: int, n: int) -> Tensor:
+    """Reset channel: the qubit is put in |0> whatever its state (Kraus operators |0><0| and |0><1|)."""
+    k0 = torch.tensor([[1, 0], [0, 0]], dtype=rho.dtype)
+    k1 = torch.tensor([[0, 1], [0, 0]], dtype=rho.dtype)
+    return apply_channel(rho, [k0, k1], wire, n)
+
+
+class Lindbladian:
+    """Generator of open-system dynamics ``d rho / dt = -i [H, rho] + sum_k D[c_k](rho)``."""
+
+    def __init__(self, hamiltonian: Tensor, collapse: Sequence[Tensor] = ()):
+        self.h, self.collapse = hamiltonian, list(collapse)
+
+    def __call__(self, rho: Tensor) -> Tensor:
+        return lindbladian(rho, self.h, self.collapse)
+
+    def evolve(self, rho: Tensor, times: Sequence[float], substeps: int = 20) -> List[Tensor]:
+        return mesolve(self.h, rho, times, self.collapse, substeps)
+
+    def superoperator(self) -> Tensor:
+        """Matrix of the generator on row-major vectorised density matrices."""
+        d = self.h.shape[-1]
+        eye = torch.eye(d, dtype=self.h.dtype)
+        sup = -1j * (torch.kron(self.h, eye) - torch.kron(eye, self.h.transpose(-1, -2).contiguous()))
+        for c in self.collapse:
+            cdc = c.conj().transpose(-1, -2) @ c
+            sup = sup + torch.kron(c, c.conj()) - 0.5 * (torch.kron(cdc, eye) + torch.kron(eye, cdc.transpose(-1, -2).contiguous()))
+        return sup
+
+
+def sample_energy(state: Tensor, h: Hamiltonian, shots: int = 1024, generator=None) -> Tensor:
+    """Energy estimated from measurements: one basis rotation and ``shots`` samples per group of
+    qubit-wise commuting terms, parities averaged per term."""
+    from .measure import apply_measurement_basis, commuting_groups, sample_indices
+    n = h.n_qubits
+    coeff = {}
+    for c, w in h.terms:
+        coeff[w] = coeff.get(w, 0.0) + c
+    total = torch.zeros(state.shape[0], dtype=torch.float64)
+    words = [w for w in coeff if set(w) != {"I"}]
+    total += sum(c for w, c in coeff.items() if set(w) == {"I"})
+    for group in commuting_groups(words):
+        basis = ["I"] * n
+        for w in group:
+            for i, ch in enumerate(w):
+                if ch != "I":
+                    basis[i] = ch
+        idx = sample_indices(apply_measurement_basis(state, "".join(basis)), shots, generator)
+        bits = (idx[..., None] >> torch.arange(n - 1, -1, -1)) & 1          # [batch, shots, n]
+        for w in group:
+            sel = torch.tensor([ch != "I" for ch in w])
+            par = bits[..., sel].sum(-1) & 1
+            total += coeff[w] * (1 - 2 * par).double().mean(-1)
+    return total
