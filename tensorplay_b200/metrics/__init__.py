@@ -281,3 +281,6 @@ class MetricCollection:
 from . import ranking as functional  # noqa: E402  (pearson_corrcoef, kendall_tau, binary_auroc, ndcg, ...)
 from .ranking import (AUROC, AveragePrecision, CalibrationError, KendallRankCorrCoef, PearsonCorrCoef,  # noqa: E402
                       RetrievalMRR, RetrievalNormalizedDCG, SpearmanCorrCoef)
+
+from . import classification  # noqa: E402
+from .classification import *  # noqa: E402,F401,F403
