@@ -284,3 +284,5 @@ from .ranking import (AUROC, AveragePrecision, CalibrationError, KendallRankCorr
 
 from . import classification  # noqa: E402
 from .classification import *  # noqa: E402,F401,F403
+from . import regression  # noqa: E402
+from .regression import *  # noqa: E402,F401,F403
