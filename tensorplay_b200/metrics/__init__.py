@@ -286,3 +286,5 @@ from . import classification  # noqa: E402
 from .classification import *  # noqa: E402,F401,F403
 from . import regression  # noqa: E402
 from .regression import *  # noqa: E402,F401,F403
+from . import domains  # noqa: E402
+from .domains import *  # noqa: E402,F401,F403
