@@ -5,10 +5,10 @@ stage.py:1039-1558, schedules.py: ``ScheduleGPipe`` :658, ``Schedule1F1B`` :766-
 ``ScheduleInterleaved1F1B`` :1636; microbatch.py)."""
 from .microbatch import merge_chunks, split_args_kwargs_into_chunks
 from .schedules import (PipelineScheduleMulti, PipelineScheduleSingle, Schedule1F1B, ScheduleGPipe,
-                        ScheduleInterleaved1F1B)
+                        ScheduleInterleaved1F1B, ScheduleLoopedBFS)
 from .stage import PipelineStage
 
-__all__ = ["PipelineStage", "ScheduleGPipe", "Schedule1F1B", "ScheduleInterleaved1F1B",
+__all__ = ["PipelineStage", "ScheduleGPipe", "Schedule1F1B", "ScheduleInterleaved1F1B", "ScheduleLoopedBFS",
            "PipelineScheduleSingle", "PipelineScheduleMulti", "split_args_kwargs_into_chunks", "merge_chunks"]
 
 

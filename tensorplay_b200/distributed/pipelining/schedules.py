@@ -179,3 +179,9 @@ class ScheduleInterleaved1F1B(PipelineScheduleMulti):
                 st.backward_one_chunk(i)
                 sends += _run_p2p(st.get_bwd_send_ops(i))
             _wait(sends)
+
+
+class ScheduleLoopedBFS(ScheduleInterleaved1F1B):
+    """Breadth-first looped schedule: every local stage runs all micro-batch forwards before the next
+    local stage starts, and the backwards mirror that order (the execution order this module also
+    uses for the interleaved placement)."""

@@ -7,6 +7,20 @@ from torch.distributed.tensor import (empty, full, init_device_mesh, ones, rand,
 
 from . import experimental, parallel  # noqa: F401
 
+from_local = DTensor.from_local
+
+
+def linspace(start, end, steps, *, device_mesh=None, placements=None, **kw):
+    """``torch.linspace`` distributed over ``device_mesh`` with ``placements`` (replicated by default)."""
+    import torch
+    return distribute_tensor(torch.linspace(start, end, steps, **kw), device_mesh, placements)
+
+
+def logspace(start, end, steps, base: float = 10.0, *, device_mesh=None, placements=None, **kw):
+    import torch
+    return distribute_tensor(torch.logspace(start, end, steps, base=base, **kw), device_mesh, placements)
+
+
 
 def __getattr__(name):
     """Other DTensor factory and helper names resolve to PyTorch's."""

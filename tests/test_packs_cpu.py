@@ -188,7 +188,7 @@ def test_distributed_subpackage_names_and_dcp_storage_delegation(tmp_path):
                               "get_model_state_dict", "set_model_state_dict", "get_state_dict", "StateDictOptions"]),
                        (fsdp, ["StateDictType", "FullStateDictConfig", "ShardedStateDictConfig", "register_fsdp_forward_method"]),
                        (dt, ["DeviceMesh", "DTensor", "Shard"]), (dopt, ["PostLocalSGDOptimizer", "ZeroRedundancyOptimizer"]),
-                       (pipe, ["pipeline", "SplitPoint", "ScheduleLoopedBFS", "Schedule1F1B", "PipelineStage"])):
+                       (pipe, ["pipeline", "SplitPoint", "ScheduleZBVZeroBubble", "Schedule1F1B", "PipelineStage"])):
         for n in names:
             assert hasattr(mod, n), (mod.__name__, n)
     assert pipe.Schedule1F1B.__module__.startswith("tensorplay_b200")          # own classes win
