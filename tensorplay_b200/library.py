@@ -26,3 +26,38 @@ def register_kernel_op(name: str, fn: Callable, fake: Callable, backward: Option
     if backward is not None:
         op.register_autograd(backward, setup_context=setup_context)
     return op
+
+
+def __getattr__(name):
+    """``CustomOpDef``, ``triton_op`` / ``wrap_triton``, ``register_vmap``, ``register_autocast``, ``infer_schema`` and ``get_kernel`` resolve to ``torch.library``."""
+    import importlib
+    for mod in ['torch.library']:
+        try:
+            return getattr(importlib.import_module(mod), name)
+        except (ImportError, AttributeError):
+            continue
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+
+
+def has_op(qualname: str) -> bool:
+    """Whether ``namespace::name`` is registered with the dispatcher."""
+    import torch
+    ns, _, name = qualname.partition("::")
+    return hasattr(getattr(torch.ops, ns, None), name.split(".")[0]) if ns and name else False
+
+
+def get_op(qualname: str):
+    """The ``torch.ops.namespace.name`` packet of a registered operator."""
+    import torch
+    ns, _, name = qualname.partition("::")
+    if not has_op(qualname):
+        raise KeyError(f"operator {qualname!r} is not registered")
+    return getattr(getattr(torch.ops, ns), name.split(".")[0])
+
+
+def tile_lang_op(*a, **k):
+    raise NotImplementedError("tile-language kernels are not part of this framework: write the kernel in CUDA and "
+                              "register it with register_kernel_op / custom_op, or load it with utils.cpp_jit")
+
+
+wrap_tilelang = tile_lang_op

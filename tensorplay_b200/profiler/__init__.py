@@ -27,3 +27,14 @@ class nvtx_range:
         if torch.cuda.is_available():
             torch.cuda.nvtx.range_pop()
         return False
+
+
+def __getattr__(name):
+    """Event containers, ``emit_nvtx`` / ``emit_itt`` and the rest of the profiler surface resolve to PyTorch's."""
+    import importlib
+    for mod in ['torch.profiler', 'torch.autograd.profiler', 'torch.autograd.profiler_util', 'torch.cuda.nvtx']:
+        try:
+            return getattr(importlib.import_module(mod), name)
+        except (ImportError, AttributeError):
+            continue
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -150,3 +150,14 @@ def load_sharded(path, map_location=None) -> dict:
 def convert_to_mega(src, dst, **kw) -> None:
     """Re-write any loadable checkpoint as ``.mega``."""
     save_mega(load(src), dst, **kw)
+
+
+def __getattr__(name):
+    """Safe-globals management, mmap / endianness / CRC options, ``skip_data`` and the pickle protocol constants resolve to ``torch.serialization`` (they govern the torch zip format handled here through ``torch.save`` / ``torch.load``)."""
+    import importlib
+    for mod in ['torch.serialization']:
+        try:
+            return getattr(importlib.import_module(mod), name)
+        except (ImportError, AttributeError):
+            continue
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
