@@ -22,3 +22,8 @@ from .layer import (InternalInfluence, LayerActivation, LayerAttribution, LayerC
 from .llm import LLMGradientAttribution, activation_patching, attention_rollout, logit_lens
 from .perturbation import (FeatureAblation, FeaturePermutation, KernelShap, Lime, Occlusion, ShapleyValues,
                            ShapleyValueSampling)
+from .variants import (ClassSummarizer, CommonStats, DeepLiftShap, GradientAttribution, GuidedGradCam, LRP,  # noqa: E402
+                       LayerDeepLift, LayerFeatureAblation, LayerFeaturePermutation, LayerGradientShap, LayerLRP,
+                       NeuronAttribution, NeuronDeconvolution, NeuronDeepLift, NeuronFeatureAblation, NeuronGradient,
+                       NeuronGradientShap, NeuronGuidedBackprop, NeuronIntegratedGradients, PerturbationAttribution,
+                       Summarizer)

@@ -142,3 +142,64 @@ def test_llm_tools_on_the_tiny_llama():
         return m.head(x)
     res = lumen.LLMGradientAttribution(m, m.embed_tokens, fwd_embeds).attribute(toks[:, :5], toks[:, 5:])
     assert res["token_attr"].shape == (2, 7) and res["log_prob"].shape == (2, 2)
+
+
+def test_lrp_conserves_relevance_and_matches_input_x_gradient_on_relu_nets():
+    torch.manual_seed(4)
+    m = nn.Sequential(nn.Linear(6, 10, bias=False), nn.ReLU(), nn.Linear(10, 3, bias=False))
+    x = torch.randn(5, 6)
+    rel, delta = lumen.LRP(m).attribute(x, target=1, return_convergence_delta=True)
+    assert delta.abs().max() < 1e-5                        # bias-free: relevance sums to the output
+    # epsilon-LRP on bias-free ReLU networks equals gradient x input
+    torch.testing.assert_close(rel, lumen.InputXGradient(m).attribute(x, target=1), rtol=1e-4, atol=1e-6)
+    at_hidden = lumen.LayerLRP(m, m[1]).attribute(x, target=1)
+    assert at_hidden.shape == (5, 10)
+    with torch.no_grad():
+        torch.testing.assert_close(at_hidden.sum(1), m(x)[:, 1], rtol=1e-4, atol=1e-5)
+
+
+def test_combined_layer_and_neuron_variants():
+    torch.manual_seed(5)
+    mlp = nn.Sequential(nn.Linear(4, 8), nn.ReLU(), nn.Linear(8, 2))
+    x = torch.randn(3, 4)
+    base = torch.randn(6, 4) * 0.1
+    dls = lumen.DeepLiftShap(mlp).attribute(x, base, target=0)
+    with torch.no_grad():
+        want = mlp(x)[:, 0] - mlp(base)[:, 0].mean()
+    torch.testing.assert_close(dls.sum(1), want, rtol=1e-4, atol=1e-5)      # completeness against the mean baseline output
+    # layer variants: attribution of the hidden layer's units
+    fa = lumen.LayerFeatureAblation(mlp, mlp[1]).attribute(x, target=0)
+    with torch.no_grad():
+        h = torch.relu(mlp[0](x))
+        exact = h * mlp[2].weight[0]                       # the tail is linear in the hidden units
+    torch.testing.assert_close(fa, exact, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(lumen.LayerDeepLift(mlp, mlp[1]).attribute(x, target=0), exact - 0 * exact + (
+        -torch.relu(mlp[0](torch.zeros(3, 4))).detach() * mlp[2].weight[0].detach()), rtol=1e-3, atol=1e-4)
+    gs = lumen.LayerGradientShap(mlp, mlp[1]).attribute(x, torch.zeros(3, 4), target=0, n_samples=3,
+                                                        generator=torch.Generator().manual_seed(0))
+    assert gs.shape == (3, 8)
+    assert lumen.LayerFeaturePermutation(mlp, mlp[1]).attribute(x, target=0, generator=torch.Generator().manual_seed(0)).shape == (3, 8)
+    # neuron variants: hidden unit 2 is relu(w_2 . x + b_2)
+    ng = lumen.NeuronGradient(mlp, mlp[0]).attribute(x, 2)
+    torch.testing.assert_close(ng, mlp[0].weight[2].detach().expand(3, 4))
+    nig = lumen.NeuronIntegratedGradients(mlp, mlp[0]).attribute(x, 2, n_steps=8)
+    torch.testing.assert_close(nig, (x * mlp[0].weight[2]).detach(), rtol=1e-4, atol=1e-5)
+    nfa = lumen.NeuronFeatureAblation(mlp, mlp[0]).attribute(x, 2)
+    torch.testing.assert_close(nfa, (x * mlp[0].weight[2]).detach(), rtol=1e-4, atol=1e-5)
+    assert lumen.NeuronGuidedBackprop(mlp, mlp[1]).attribute(x, 2).shape == x.shape
+    assert lumen.NeuronDeconvolution(mlp, mlp[1]).attribute(x, 2).shape == x.shape
+    # guided Grad-CAM on a small conv net
+    conv = nn.Conv2d(1, 3, 3, padding=1)
+    net = nn.Sequential(conv, nn.ReLU(), nn.AdaptiveAvgPool2d(1), nn.Flatten(), nn.Linear(3, 2))
+    img = torch.randn(2, 1, 6, 6)
+    assert lumen.GuidedGradCam(net, conv).attribute(img, target=1).shape == img.shape
+    # summarizers
+    s = lumen.Summarizer()
+    data = torch.randn(50, 4, generator=torch.Generator().manual_seed(1))
+    s.update(data[:20])
+    s.update(data[20:])
+    torch.testing.assert_close(s.summary["mean"].float(), data.mean(0), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(s.summary["var"].float(), data.var(0, unbiased=False), rtol=1e-5, atol=1e-6)
+    cs = lumen.ClassSummarizer(["mean"])
+    cs.update(data, torch.arange(50) % 2)
+    torch.testing.assert_close(cs.class_summaries[1]["mean"].float(), data[1::2].mean(0), rtol=1e-5, atol=1e-6)
