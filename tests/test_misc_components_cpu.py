@@ -190,3 +190,23 @@ def test_every_cache_kind_reproduces_cache_free_generation():
     att = nn.GroupedQueryAttention(32, 4, 2)
     full = att(x)
     torch.testing.assert_close(att(x[:, :4]), full[:, :4], rtol=1e-5, atol=1e-5)    # causal: a prefix is unchanged
+
+
+def test_swap_in_optimizer_params_and_state():
+    torch.manual_seed(0)
+    lin = tnn.Linear(4, 2)
+    opt = torch.optim.SGD(lin.parameters(), lr=0.1, momentum=0.9)
+    lin(torch.randn(3, 4)).sum().backward()
+    opt.step()
+    own = [p.detach().clone() for p in lin.parameters()]
+    copies = {n: p.detach().clone().requires_grad_() for n, p in lin.named_parameters()}
+    sd = opt.state_dict()
+    sd["param_groups"][0]["lr"] = 1.0
+    with optim.swap_in_optimizer_params_and_state(opt, copies, sd):
+        for p in copies.values():
+            p.grad = torch.ones_like(p)
+        opt.step()
+    assert opt.param_groups[0]["lr"] == 0.1                                   # hyper-parameters restored
+    for p, o in zip(lin.parameters(), own):
+        assert torch.equal(p, o)                                                # the live model did not move
+    assert all(not torch.equal(c, o) for c, o in zip(copies.values(), own))     # the copies did
