@@ -29,7 +29,8 @@ _LAZY = {"ddp", "fsdp", "device_mesh", "pipelining", "tensor", "checkpoint", "el
          "flight_recorder", "watchdog", "_symmetric_memory", "_token_switch", "algorithms", "optim",
          "rendezvous", "debug", "_tools", "rpc", "nn", "utils", "_functional_collectives", "_composable",
          "_composable_state", "_shard", "_local_tensor", "_state_dict_utils", "_checkpointable", "_serialization",
-         "collective_utils", "argparse_util", "constants", "remote_device", "logging_handlers", "p10d_logger"}
+         "collective_utils", "argparse_util", "constants", "remote_device", "logging_handlers", "p10d_logger",
+         "_watchdog", "_store", "_tensor", "distributed_core", "_mesh_layout", "_pycute", "config", "autograd"}
 # the star import above also copied torch's sub-modules of these names; ours must win
 for _n in _LAZY:
     globals().pop(_n, None)

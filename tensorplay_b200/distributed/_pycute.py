@@ -1,0 +1,5 @@
+"""CuTe-style layout algebra for mesh slicing: PyTorch's module of the same role."""
+import importlib
+import sys
+
+sys.modules[__name__] = importlib.import_module("torch.distributed._pycute")

@@ -37,23 +37,96 @@ def dump_native_stacks() -> str:
         return f.read()
 
 
+class DebugHandler:
+    """One endpoint of the debug server: ``path`` prefix, content type and ``handle() -> str``."""
+
+    path = "/"
+    content_type = "text/plain"
+
+    def handle(self, request_path: str) -> str:
+        raise NotImplementedError
+
+
+class StacksHandler(DebugHandler):
+    path = "/stacks"
+
+    def handle(self, request_path: str) -> str:
+        return dump_stacks()
+
+
+class NativeStacksHandler(DebugHandler):
+    path = "/native"
+
+    def handle(self, request_path: str) -> str:
+        return dump_native_stacks()
+
+
+class FlightRecorderHandler(DebugHandler):
+    path, content_type = "/flight", "application/json"
+
+    def handle(self, request_path: str) -> str:
+        from .. import flight_recorder
+        return json.dumps({"rank": os.environ.get("RANK"), "entries": flight_recorder.entries()})
+
+
+class StoreDumpHandler(DebugHandler):
+    """Keys of a store registered with :func:`register_store` (values are not dumped)."""
+
+    path, content_type = "/store", "application/json"
+    store = None
+
+    def handle(self, request_path: str) -> str:
+        st = type(self).store
+        if st is None:
+            return json.dumps({"error": "no store registered"})
+        n = st.num_keys() if hasattr(st, "num_keys") else None
+        return json.dumps({"num_keys": n, "type": type(st).__name__})
+
+
+class IndexHandler(DebugHandler):
+    path, content_type = "/", "application/json"
+
+    def handle(self, request_path: str) -> str:
+        return json.dumps({"pid": os.getpid(), "rank": os.environ.get("RANK"), "endpoints": list_handlers()})
+
+
+_handlers = {}
+
+
+def register_handler(handler: DebugHandler) -> None:
+    """Add (or replace) the endpoint at ``handler.path``."""
+    _handlers[handler.path] = handler
+
+
+def list_handlers():
+    return sorted(p for p in _handlers if p != "/")
+
+
+def default_handlers():
+    return [StacksHandler(), NativeStacksHandler(), FlightRecorderHandler(), StoreDumpHandler(), IndexHandler()]
+
+
+def register_store(store) -> None:
+    StoreDumpHandler.store = store
+
+
+for _h in default_handlers():
+    register_handler(_h)
+
+
 class _Handler(BaseHTTPRequestHandler):
     def log_message(self, *a):  # silence
         pass
 
     def do_GET(self):  # noqa: N802
-        if self.path.startswith("/stacks"):
-            body, ctype = dump_stacks(), "text/plain"
-        elif self.path.startswith("/native"):
-            body, ctype = dump_native_stacks(), "text/plain"
-        elif self.path.startswith("/flight"):
-            from .. import flight_recorder
-            body, ctype = json.dumps(flight_recorder.dump()), "application/json"
-        else:
-            body, ctype = json.dumps({"pid": os.getpid(), "rank": os.environ.get("RANK"),
-                                      "endpoints": ["/stacks", "/native", "/flight"]}), "application/json"
+        best = max((p for p in _handlers if p != "/" and self.path.startswith(p)), key=len, default="/")
+        h = _handlers[best]
+        try:
+            body, ctype, code = h.handle(self.path), h.content_type, 200
+        except Exception as e:  # a handler must not take the server down
+            body, ctype, code = json.dumps({"error": repr(e)}), "application/json", 500
         data = body.encode()
-        self.send_response(200)
+        self.send_response(code)
         self.send_header("Content-Type", ctype)
         self.send_header("Content-Length", str(len(data)))
         self.end_headers()

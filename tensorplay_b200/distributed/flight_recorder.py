@@ -65,3 +65,44 @@ def analyze(paths: List[str]) -> Dict:
     longest = max((len(s) for s in seqs.values()), default=0)
     behind = sorted(r for r, s in seqs.items() if len(s) < longest)
     return {"ranks": sorted(seqs), "common_prefix": n, "mismatch": mismatch, "behind": behind}
+
+
+class FlightRecorder:
+    """Object form of the module-level recorder (one per process): ``record``, ``entries``, ``dump``,
+    ``clear``; usable as a context manager that dumps on an exception."""
+
+    def __init__(self, dump_path: Optional[str] = None):
+        self.dump_path = dump_path
+
+    record = staticmethod(record)
+    entries = staticmethod(entries)
+    clear = staticmethod(clear)
+
+    def dump(self, path: Optional[str] = None) -> str:
+        return dump(path or self.dump_path)
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        if exc_type is not None:
+            self.dump()
+        return False
+
+
+_recorder: Optional[FlightRecorder] = None
+
+
+def start_flight_recorder(dump_path: Optional[str] = None, size: Optional[int] = None) -> FlightRecorder:
+    """Enable recording (optionally with a new ring size) and return the process's recorder."""
+    global _recorder, _enabled, _ring
+    _enabled = True
+    if size is not None and size != _ring.maxlen:
+        with _lock:
+            _ring = deque(_ring, maxlen=int(size))
+    _recorder = FlightRecorder(dump_path)
+    return _recorder
+
+
+def dump_flight_recorder(path: Optional[str] = None) -> str:
+    return (_recorder or FlightRecorder()).dump(path)

@@ -98,3 +98,52 @@ def test_debug_server_and_package_surface():
         json.loads(urllib.request.urlopen(f"http://127.0.0.1:{port}/flight", timeout=5).read())
     finally:
         d.debug.stop_debug_server()
+
+
+def test_debug_handler_registry_and_flight_recorder_object(tmp_path):
+    import json
+    import urllib.request
+
+    from tensorplay_b200.distributed import debug, flight_recorder as fr
+    assert {"/stacks", "/native", "/flight", "/store"} <= set(debug.list_handlers())
+
+    class Hello(debug.DebugHandler):
+        path = "/hello"
+
+        def handle(self, request_path):
+            return "hi " + request_path
+
+    debug.register_handler(Hello())
+    port = debug.start_debug_server(0)
+    try:
+        assert urllib.request.urlopen(f"http://127.0.0.1:{port}/hello?x=1").read().decode() == "hi /hello?x=1"
+        idx = json.loads(urllib.request.urlopen(f"http://127.0.0.1:{port}/").read())
+        assert "/hello" in idx["endpoints"]
+        rec = fr.start_flight_recorder(str(tmp_path / "fr.json"), size=4)
+        fr.clear()
+        for i in range(6):
+            rec.record("all_reduce", numel=i)
+        assert [e["numel"] for e in rec.entries()] == [2, 3, 4, 5]            # ring of four
+        flight = json.loads(urllib.request.urlopen(f"http://127.0.0.1:{port}/flight").read())
+        assert len(flight["entries"]) == 4
+        try:
+            with rec:
+                raise ValueError("boom")
+        except ValueError:
+            pass
+        assert json.load(open(tmp_path / "fr.json"))["entries"][-1]["numel"] == 5
+        assert fr.dump_flight_recorder(str(tmp_path / "fr2.json")).endswith("fr2.json")
+    finally:
+        debug.stop_debug_server()
+        fr.start_flight_recorder(size=2048)
+
+
+def test_private_module_paths_and_rpc_probe():
+    import importlib
+    import tensorplay_b200.distributed as dist
+    assert importlib.import_module("tensorplay_b200.distributed._watchdog").Watchdog is dist.watchdog.Watchdog
+    assert importlib.import_module("tensorplay_b200.distributed.distributed_core") is dist
+    assert importlib.import_module("tensorplay_b200.distributed._store").TCPStore is dist.TCPStore
+    for n in ("_mesh_layout", "_pycute", "config", "_tensor"):
+        assert importlib.import_module("tensorplay_b200.distributed." + n) is not None
+    assert not hasattr(dist.rpc, "init_rpc") and not dist.autograd.is_available()
