@@ -99,3 +99,66 @@ def fused_all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, group=None) 
 def fused_matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, group=None) -> torch.Tensor:
     """``reduce_scatter(a @ b.T, dim=0)`` in one kernel."""
     return _ctx(group).linear_reduce_scatter(a, b)
+
+
+_backend = "ipc"            # CUDA IPC arena with P2P loads / stores (the only backend built here)
+_signal_pad_size = 16384 * 4
+
+
+def set_backend(name: str) -> None:
+    """Select the symmetric-memory backend. Only ``"ipc"`` (CUDA IPC + peer loads / stores) exists here;
+    NVSHMEM and multicast (NVLS) backends are not built."""
+    if name.lower() not in ("ipc", "cuda"):
+        raise ValueError(f"symmetric-memory backend {name!r} is not available (only 'ipc')")
+
+
+def get_backend(device=None) -> str:
+    return _backend
+
+
+def set_signal_pad_size(nbytes: int) -> None:
+    """Bytes of signal slots per arena; takes effect for arenas created afterwards."""
+    global _signal_pad_size
+    _signal_pad_size = int(nbytes)
+
+
+def get_signal_pad_size() -> int:
+    return _signal_pad_size
+
+
+def get(tensor: torch.Tensor, group=None) -> "SymmetricBuffer":
+    """Handle of an arena tensor (alias of :func:`rendezvous`)."""
+    return rendezvous(tensor, group)
+
+
+def get_mem_pool(device=None):
+    """The process-wide arena that backs symmetric allocations (a bump allocator, not a torch MemPool)."""
+    return _arena()
+
+
+def reduce_scatter_offset(inp: torch.Tensor, group=None, offsets=None) -> torch.Tensor:
+    """Row reduce-scatter whose shard boundaries are ``offsets`` (ascending row ends per rank; equal
+    shards by default). Uneven shards take the NCCL path through padding."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    rows = inp.shape[0]
+    ends = list(offsets) if offsets is not None else [rows * (r + 1) // world for r in range(world)]
+    starts = [0] + ends[:-1]
+    width = max(e - s for s, e in zip(starts, ends))
+    padded = inp.new_zeros(world * width, *inp.shape[1:])
+    for r, (s, e) in enumerate(zip(starts, ends)):
+        padded[r * width: r * width + (e - s)] = inp[s:e]
+    out = inp.new_empty(width, *inp.shape[1:])
+    if dist.get_backend(group) == "gloo":
+        dist.all_reduce(padded, group=group)
+        out.copy_(padded[rank * width: (rank + 1) * width])
+    else:
+        dist.reduce_scatter_tensor(out, padded, group=group)
+    return out[: ends[rank] - starts[rank]]
+
+
+def all_to_all_nd(inp: torch.Tensor, group=None) -> torch.Tensor:
+    """All-to-all of equal blocks along dimension 0 for tensors of any rank."""
+    out = torch.empty_like(inp)
+    dist.all_to_all_single(out, inp.contiguous(), group=group)
+    return out

@@ -46,3 +46,15 @@ def activation_checkpoint_plan(cfg, seq_len: int, micro_batch: int = 1, act_byte
         "full": {"kept_bytes": layers * t * h * act_bytes, "recompute_flops": layers * (gemm_flops + attn_flops)},
         "forward_flops": layers * (gemm_flops + attn_flops),
     }
+
+
+def __getattr__(name):
+    """Other trackers and estimators (``MemoryTracker``, ``ModTracker``, SAC statistics ...) resolve to PyTorch's."""
+    import importlib
+    for mod in ("torch.distributed._tools", "torch.distributed._tools.memory_tracker", "torch.distributed._tools.mod_tracker",
+                "torch.distributed._tools.sac_estimator", "torch.distributed._tools.sac_ilp", "torch.distributed._tools.ilp_utils"):
+        try:
+            return getattr(importlib.import_module(mod), name)
+        except (ImportError, AttributeError):
+            continue
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

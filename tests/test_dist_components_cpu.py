@@ -147,3 +147,40 @@ def _loss_parallel_worker(rank, world):
 
 def test_loss_parallel_and_sequence_parallel():
     assert all(run_ranks(_loss_parallel_worker, 2))
+
+
+def _funcol_worker(rank, world):
+    import torch.distributed as dist
+    from tensorplay_b200.distributed import _functional_collectives as fc
+    from tensorplay_b200.distributed import _symmetric_memory as sm
+    x = torch.arange(4.0) + 10 * rank
+    g = fc.all_gather_single(x, 0, dist.group.WORLD)
+    assert fc.wait_tensor(g).tolist() == [0, 1, 2, 3, 10, 11, 12, 13]
+    r = fc.wait_tensor(fc.reduce_scatter_single(torch.ones(4) * (rank + 1), "sum", 0, dist.group.WORLD))
+    assert r.tolist() == [3.0, 3.0]
+    xa = (torch.ones(2) * (rank + 1)).requires_grad_()
+    ga = fc.all_gather_single_autograd(xa, 0, dist.group.WORLD)
+    fc.wait_tensor(ga).pow(2).sum().backward()
+    assert xa.grad.tolist() == [4.0 * (rank + 1)] * 2      # every rank's loss sees this shard: 2 x (2 x)
+    out = torch.zeros(2)
+    fc.reduce_scatter_inplace(out, torch.arange(4.0))
+    assert out.tolist() == ([0.0, 2.0] if rank == 0 else [4.0, 6.0])
+    buf = torch.zeros(3)
+    works = fc.batch_p2p_ops_inplace([("send", torch.full((3,), float(rank)), 1 - rank), ("recv", buf, 1 - rank)])
+    for w in works:
+        w.wait()
+    assert buf.tolist() == [float(1 - rank)] * 3
+    # uneven reduce-scatter and n-d all-to-all of the symmetric-memory surface (plain collectives on CPU)
+    inp = torch.arange(10.0).view(5, 2) * (rank + 1)
+    mine = sm.reduce_scatter_offset(inp, offsets=[2, 5])
+    want = (torch.arange(10.0).view(5, 2) * 3)[:2] if rank == 0 else (torch.arange(10.0).view(5, 2) * 3)[2:]
+    torch.testing.assert_close(mine, want)
+    a2a = sm.all_to_all_nd(torch.full((2, 2, 2), float(rank)))
+    assert a2a[0].unique().tolist() == [0.0] and a2a[1].unique().tolist() == [1.0]
+    assert sm.get_backend() == "ipc" and sm.get_signal_pad_size() > 0
+    dist.barrier()
+    return True
+
+
+def test_functional_collective_spellings_and_symmetric_memory_helpers():
+    assert all(run_ranks(_funcol_worker, 2))
