@@ -1,0 +1,5 @@
+"""Rendezvous handlers and registry of the elastic agent: PyTorch's module of the same role."""
+import importlib
+import sys
+
+sys.modules[__name__] = importlib.import_module("torch.distributed.elastic.rendezvous")

@@ -19,7 +19,18 @@ from __future__ import annotations
 from .api import (BackwardPrefetch, CPUOffload, CPUOffloadPolicy, FSDPModule, FullyShardedDataParallel,
                   MixedPrecision, MixedPrecisionPolicy, OffloadPolicy, ShardingStrategy, fully_shard)
 
-__all__ = ["fully_shard", "FSDPModule", "MixedPrecisionPolicy", "CPUOffloadPolicy", "OffloadPolicy",
+import dataclasses as _dc
+from typing import Optional as _Optional
+
+
+@_dc.dataclass
+class DataParallelMeshDims:
+    """Names of the mesh dimensions used for sharding and (hybrid) replication."""
+    shard: _Optional[str] = None
+    replicate: _Optional[str] = None
+
+
+__all__ = ["fully_shard", "DataParallelMeshDims", "FSDPModule", "MixedPrecisionPolicy", "CPUOffloadPolicy", "OffloadPolicy",
            "FullyShardedDataParallel", "ShardingStrategy", "MixedPrecision", "CPUOffload", "BackwardPrefetch"]
 
 

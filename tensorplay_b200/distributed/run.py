@@ -127,6 +127,11 @@ def elastic_launch(config: LaunchConfig, cmd: List[str]) -> int:
     return LocalElasticAgent(config, cmd).run()
 
 
+def run(args) -> int:
+    """Launch from a parsed argument namespace or an argv list (the function form of ``tprun``)."""
+    return main(args if isinstance(args, (list, tuple)) else None)
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="tprun")
     ap.add_argument("--nproc-per-node", "--nproc_per_node", type=int, default=int(os.environ.get("TP_NPROC", "1")))

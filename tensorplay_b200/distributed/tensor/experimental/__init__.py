@@ -7,3 +7,14 @@ from ....parallel.cp import (context_parallel, context_parallel_shard, context_p
 
 __all__ = ["context_parallel", "context_parallel_shard", "context_parallel_unshard", "ring_attention",
            "implicit_replication"]
+
+
+def __getattr__(name):
+    """``local_map``, ``register_sharding`` and other experimental DTensor helpers resolve to PyTorch's."""
+    import importlib
+    for mod in ("torch.distributed.tensor.experimental", "torch.distributed.tensor.experimental._attention"):
+        try:
+            return getattr(importlib.import_module(mod), name)
+        except (ImportError, AttributeError):
+            continue
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
