@@ -4,9 +4,9 @@ size included). On-disk layout follows the reference's (tensorplay/distributed/c
 filesystem.py:56-80): one data file per rank ``__{rank}_0.distcp`` (a ``.mega`` container here)
 plus ``.metadata``; ``async_save`` stages to host memory and writes in the background
 (state_dict_saver.py:235-346, staging.py)."""
-from .api import (ShardedTensor, Stateful, async_save, engine_state_dict, load, load_engine_state_dict, save)
+from .api import (MegaStorageReader, MegaStorageWriter, ShardedTensor, Stateful, async_save, engine_state_dict, load, load_engine_state_dict, save)
 
-__all__ = ["ShardedTensor", "Stateful", "save", "async_save", "load", "engine_state_dict", "load_engine_state_dict"]
+__all__ = ["MegaStorageReader", "MegaStorageWriter", "ShardedTensor", "Stateful", "save", "async_save", "load", "engine_state_dict", "load_engine_state_dict"]
 
 
 def __getattr__(name):

@@ -116,12 +116,27 @@ def _write(checkpoint_id: str, rank: int, tensors: Dict[str, torch.Tensor], all_
         os.replace(tmp, os.path.join(checkpoint_id, META_FILE))  # the checkpoint is valid once this exists
 
 
+class MegaStorageWriter:
+    """Selects this package's own layout (one ``.mega`` container per rank + ``.metadata``) explicitly:
+    ``save(state, storage_writer=MegaStorageWriter(directory))``."""
+
+    def __init__(self, path: str):
+        self.path = str(path)
+
+
+class MegaStorageReader:
+    def __init__(self, path: str):
+        self.path = str(path)
+
+
 def save(state_dict: Mapping[str, Any], *, checkpoint_id: Optional[str] = None, process_group=None,
          storage_writer=None, planner=None, **kw) -> None:
     """Collective save of ``state_dict`` (tensors, ``ShardedTensor`` / DTensor shards, Stateful
     objects, plain values) into the directory ``checkpoint_id``. A ``storage_writer`` or ``planner``
     (``FileSystemWriter``, ``DefaultSavePlanner`` ...: PyTorch's planner / storage layer) selects
     PyTorch's implementation and on-disk layout for the whole call."""
+    if isinstance(storage_writer, MegaStorageWriter):
+        checkpoint_id, storage_writer = storage_writer.path, None
     if storage_writer is not None or planner is not None:
         import torch.distributed.checkpoint as tdcp
         return tdcp.save(state_dict, checkpoint_id=checkpoint_id, storage_writer=storage_writer, planner=planner,
@@ -173,6 +188,8 @@ def load(state_dict: Dict[str, Any], *, checkpoint_id: Optional[str] = None, pro
     entries receive the slices that overlap their ``[offsets, offsets + shape)`` window (whatever
     the sharding was at save time), Stateful objects get ``load_state_dict``. With a
     ``storage_reader`` or ``planner`` the call goes to PyTorch's implementation (see :func:`save`)."""
+    if isinstance(storage_reader, MegaStorageReader):
+        checkpoint_id, storage_reader = storage_reader.path, None
     if storage_reader is not None or planner is not None:
         import torch.distributed.checkpoint as tdcp
         tdcp.load(state_dict, checkpoint_id=checkpoint_id, storage_reader=storage_reader, planner=planner,

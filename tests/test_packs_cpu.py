@@ -199,7 +199,12 @@ def test_distributed_subpackage_names_and_dcp_storage_delegation(tmp_path):
     out = {"w": torch.zeros(3, 4), "step": 0}
     dcp.load(out, storage_reader=dcp.FileSystemReader(d))
     assert torch.equal(out["w"], state["w"]) and out["step"] == 3
-    # the default path keeps its own layout
+    # the default path keeps its own layout, which the Mega storage classes name explicitly
+    d3 = str(tmp_path / "ck3")
+    dcp.save(state, storage_writer=dcp.MegaStorageWriter(d3))
+    out3 = {"w": torch.zeros(3, 4), "step": 0}
+    dcp.load(out3, storage_reader=dcp.MegaStorageReader(d3))
+    assert torch.equal(out3["w"], state["w"])
     d2 = str(tmp_path / "ck2")
     dcp.save(state, checkpoint_id=d2)
     out2 = {"w": torch.zeros(3, 4), "step": 0}
