@@ -133,3 +133,62 @@ def is_native_available() -> bool:
     """True when the sm_100a kernel library is built and loadable."""
     from . import _native
     return _native.kernels_available()
+
+
+# ---- remaining top-level names of the reference that PyTorch spells differently
+import enum as _enum  # noqa: E402
+import numbers as _numbers  # noqa: E402
+
+Scalar = _numbers.Number
+MemoryFormat = _torch.memory_format
+Layout = _torch.layout
+bcomplex32 = _torch.complex32          # the reference's name for half-precision complex
+quint1x8 = getattr(_torch, "quint2x4", _torch.quint8)   # no 1-bit quantised dtype in PyTorch: closest sub-byte type
+index = _torch.index_select
+
+
+class DeviceType(_enum.Enum):
+    CPU = "cpu"
+    CUDA = "cuda"
+    META = "meta"
+
+
+class QScheme(_enum.Enum):
+    PER_TENSOR_AFFINE = _torch.per_tensor_affine
+    PER_CHANNEL_AFFINE = _torch.per_channel_affine
+    PER_TENSOR_SYMMETRIC = _torch.per_tensor_symmetric
+    PER_CHANNEL_SYMMETRIC = _torch.per_channel_symmetric
+
+
+class DeviceMismatchError(RuntimeError):
+    """Operands of one operation live on different devices."""
+
+
+def get_thread_num() -> int:
+    """Index of the calling thread inside an intra-op parallel region (0 outside one)."""
+    return 0
+
+
+def in_parallel_region() -> bool:
+    return False
+
+
+def get_parallel_info() -> str:
+    return _torch.__config__.parallel_info()
+
+
+def fork_rng(devices=None, enabled: bool = True):
+    """Context manager: RNG states of the CPU and of ``devices`` are restored on exit."""
+    return _torch.random.fork_rng(devices=devices, enabled=enabled)
+
+
+def thread_safe_generator(seed: int = None, device="cpu"):
+    """A generator of its own (not the global one), seeded explicitly or from the global stream."""
+    g = _torch.Generator(device=device)
+    g.manual_seed(int(_torch.randint(0, 2 ** 62, ()).item()) if seed is None else int(seed))
+    return g
+
+
+def getArtifactLogger(name: str, artifact: str):
+    import logging
+    return logging.getLogger(f"{name}.__{artifact}")
