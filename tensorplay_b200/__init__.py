@@ -185,7 +185,8 @@ def fork_rng(devices=None, enabled: bool = True):
 def thread_safe_generator(seed: int = None, device="cpu"):
     """A generator of its own (not the global one), seeded explicitly or from the global stream."""
     g = _torch.Generator(device=device)
-    g.manual_seed(int(_torch.randint(0, 2 ** 62, ()).item()) if seed is None else int(seed))
+    import builtins
+    g.manual_seed(builtins.int(_torch.randint(0, 2 ** 62, ()).item()) if seed is None else builtins.int(seed))
     return g
 
 

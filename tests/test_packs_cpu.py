@@ -210,3 +210,17 @@ def test_distributed_subpackage_names_and_dcp_storage_delegation(tmp_path):
     out2 = {"w": torch.zeros(3, 4), "step": 0}
     dcp.load(out2, checkpoint_id=d2)
     assert torch.equal(out2["w"], state["w"])
+
+
+def test_top_level_names_of_the_reference():
+    import tensorplay_b200 as tp
+    for n in ("Scalar", "DeviceType", "MemoryFormat", "Layout", "QScheme", "DeviceMismatchError", "get_parallel_info",
+              "fork_rng", "thread_safe_generator", "getArtifactLogger", "Tensor", "compile", "save", "load"):
+        assert getattr(tp, n) is not None, n
+    assert tp.thread_safe_generator(3).initial_seed() == 3
+    tp.manual_seed(0)
+    with tp.fork_rng():
+        a = tp.rand(2)
+    tp.manual_seed(0)
+    assert tp.equal(a, tp.rand(2))
+    assert tp.MemoryFormat is tp.memory_format and tp.DeviceType.CUDA.value == "cuda"
