@@ -288,3 +288,5 @@ from . import regression  # noqa: E402
 from .regression import *  # noqa: E402,F401,F403
 from . import domains  # noqa: E402
 from .domains import *  # noqa: E402,F401,F403
+from . import more  # noqa: E402
+from .more import *  # noqa: E402,F401,F403

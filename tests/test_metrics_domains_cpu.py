@@ -86,3 +86,54 @@ def test_retrieval_metrics():
     assert abs(float(_once(M.RetrievalFallOut(top_k=2), scores, rel, q)) - (0.5 + 1.0) / 2) < 1e-6
     auc = [skm.roc_auc_score(rel[q == i].numpy(), scores[q == i].numpy()) for i in (0, 1)]
     assert abs(float(_once(M.RetrievalAUROC(), scores, rel, q)) - np.mean(auc)) < 1e-6
+
+
+def test_nominal_operating_point_and_spectral_metrics():
+    from scipy import stats
+    g = torch.Generator().manual_seed(3)
+    a = torch.randint(0, 4, (400,), generator=g)
+    b = (a + (torch.rand(400, generator=g) < 0.4).long() * torch.randint(0, 4, (400,), generator=g)) % 4
+    table = skm.confusion_matrix(b.numpy(), a.numpy())
+    chi2 = stats.chi2_contingency(table, correction=False)[0]
+    assert abs(float(_once(M.CramersV(4), a, b)) - stats.contingency.association(table, method="cramer")) < 1e-6
+    assert abs(float(_once(M.TschuprowsT(4), a, b)) - stats.contingency.association(table, method="tschuprow")) < 1e-6
+    assert abs(float(_once(M.PearsonsContingencyCoefficient(4), a, b)) - math.sqrt(chi2 / (chi2 + 400))) < 1e-6
+    u = float(_once(M.TheilsU(4), a, b))
+    assert 0 < u < 1 and abs(float(_once(M.TheilsU(4), a, a)) - 1.0) < 1e-9
+    # Fleiss' kappa on the textbook table (Fleiss 1971, 10 subjects x 5 categories, 14 raters): 0.210
+    tbl = torch.tensor([[0, 0, 0, 0, 14], [0, 2, 6, 4, 2], [0, 0, 3, 5, 6], [0, 3, 9, 2, 0], [2, 2, 8, 1, 1],
+                        [7, 7, 0, 0, 0], [3, 2, 6, 3, 0], [2, 5, 3, 2, 2], [6, 5, 2, 1, 0], [0, 2, 2, 3, 7]])
+    assert abs(float(_once(M.FleissKappa(), tbl)) - 0.210) < 1e-3
+    t = (torch.rand(300, generator=g) < 0.4).long()
+    s = t * 0.6 + torch.rand(300, generator=g) * 0.8
+    prec, thr = _once(M.BinaryPrecisionAtFixedRecall(min_value=0.8), s, t)
+    p_curve, r_curve, _ = skm.precision_recall_curve(t.numpy(), s.numpy())
+    assert abs(float(prec) - p_curve[r_curve >= 0.8].max()) < 1e-6
+    sens, _ = _once(M.BinarySensitivityAtSpecificity(min_value=0.9), s, t)
+    fpr, tpr, _ = skm.roc_curve(t.numpy(), s.numpy(), drop_intermediate=False)
+    assert abs(float(sens) - tpr[(1 - fpr) >= 0.9].max()) < 1e-6
+    csi = _once(M.CriticalSuccessIndex(0.5), torch.tensor([0.9, 0.2, 0.7, 0.1]), torch.tensor([0.8, 0.6, 0.1, 0.0]))
+    assert abs(float(csi) - 1 / 3) < 1e-6
+    curves = _once(M.ROC(task="multiclass", num_classes=3), torch.softmax(torch.randn(50, 3, generator=g), -1),
+                   torch.randint(0, 3, (50,), generator=g))
+    assert len(curves) == 3 and len(curves[0]) == 3
+    mt = M.MultitaskWrapper({"cls": M.BinaryAccuracy(), "reg": M.MeanSquaredError()})
+    mt.update({"cls": torch.tensor([0.9, 0.1]), "reg": torch.tensor([1.0, 2.0])}, {"cls": torch.tensor([1, 0]), "reg": torch.tensor([1.0, 4.0])})
+    out = mt.compute()
+    assert float(out["cls"]) == 1.0 and float(out["reg"]) == 2.0
+    # permutation-invariant SI-SDR: swapping the estimated sources does not change the value
+    src = torch.randn(2, 2, 400, generator=g)
+    est = src + 0.05 * torch.randn(2, 2, 400, generator=g)
+
+    def sisdr(p, t):
+        alpha = (p * t).sum(-1, keepdim=True) / (t * t).sum(-1, keepdim=True)
+        proj = alpha * t
+        return 10 * torch.log10((proj ** 2).sum(-1) / ((proj - p) ** 2).sum(-1))
+    v1 = float(_once(M.PermutationInvariantTraining(sisdr), est, src))
+    v2 = float(_once(M.PermutationInvariantTraining(sisdr), est.flip(1), src))
+    assert abs(v1 - v2) < 1e-4 and v1 > 20
+    img = torch.rand(2, 4, 16, 16, generator=g) + 0.5
+    assert float(_once(M.SpectralAngleMapper(), img, img * 1.7)) < 1e-3           # invariant to brightness
+    assert float(_once(M.ErrorRelativeGlobalDimensionlessSynthesis(), img, img)) == 0.0
+    assert float(_once(M.RelativeAverageSpectralError(), img * 1.1, img)) > 0
+    assert float(_once(M.RootMeanSquaredErrorUsingSlidingWindow(4), img + 0.1, img)) - 0.1 < 1e-6
