@@ -278,7 +278,6 @@ class MetricCollection:
             m.reset()
 
 
-from . import ranking as functional  # noqa: E402  (pearson_corrcoef, kendall_tau, binary_auroc, ndcg, ...)
 from .ranking import (AUROC, AveragePrecision, CalibrationError, KendallRankCorrCoef, PearsonCorrCoef,  # noqa: E402
                       RetrievalMRR, RetrievalNormalizedDCG, SpearmanCorrCoef)
 
@@ -290,3 +289,27 @@ from . import domains  # noqa: E402
 from .domains import *  # noqa: E402,F401,F403
 from . import more  # noqa: E402
 from .more import *  # noqa: E402,F401,F403
+from . import generative, panoptic, text_more  # noqa: E402
+from .generative import *  # noqa: E402,F401,F403
+from .panoptic import *  # noqa: E402,F401,F403
+from .text_more import *  # noqa: E402,F401,F403
+from . import functional, utilities  # noqa: E402
+
+
+def _domain_views() -> None:
+    """``metrics.text``, ``metrics.image`` ... resolve the same classes as the package itself: the
+    classes live in a few files by kind of state, the domain names are views for imports."""
+    import sys
+    import types
+    pkg = sys.modules[__name__]
+    for name in ("wrappers", "image", "text", "audio", "retrieval", "nominal", "detection", "multimodal", "aggregation",
+                 "collections"):
+        if name in pkg.__dict__:
+            continue
+        mod = types.ModuleType(f"{__name__}.{name}", f"View of {__name__} for the {name} metrics.")
+        mod.__getattr__ = lambda attr, _pkg=pkg: getattr(_pkg, attr)
+        sys.modules[mod.__name__] = mod
+        setattr(pkg, name, mod)
+
+
+_domain_views()
