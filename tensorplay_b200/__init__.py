@@ -63,15 +63,25 @@ class _TorchAliasFinder:
 
     def find_spec(self, fullname, path=None, target=None):
         parts = fullname.split(".")
-        if len(parts) < 3 or parts[0] != __name__ or parts[1] not in self._PKGS:
+        if len(parts) < 2 or parts[0] != __name__:
             return None
         import importlib.util
-        torch_name = "torch." + ".".join(parts[1:])
-        try:
-            if importlib.util.find_spec(torch_name) is None:
-                return None
-        except (ImportError, ValueError, AttributeError):
+        if parts[1] in ("vision", "audio"):
+            torch_name = ".".join(["torchvision" if parts[1] == "vision" else "torchaudio"] + parts[2:])
+        elif parts[1] == "_transforms":
+            torch_name = ".".join(["torch.func"] + parts[2:])
+        elif parts[1] in _LAZY_TORCH or (len(parts) >= 3 and parts[1] in self._PKGS):
+            # whole packages that are PyTorch's (``linalg``, ``func``, ``fx`` ...), or a module path below
+            # a thin package of this framework
+            torch_name = "torch." + ".".join(parts[1:])
+        else:
             return None
+        if torch_name not in _sys.modules:        # (a loaded module may have no __spec__: torch.backends)
+            try:
+                if importlib.util.find_spec(torch_name) is None:
+                    return None
+            except (ImportError, ValueError, AttributeError):
+                return None
         return importlib.util.spec_from_loader(fullname, _TorchAliasLoader(torch_name))
 
 

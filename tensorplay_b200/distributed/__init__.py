@@ -44,4 +44,7 @@ def __getattr__(name):
     if name in ("DeviceMesh", "init_device_mesh"):
         from . import device_mesh
         return getattr(device_mesh, name)
+    if name in ("default_pg_timeout", "default_pg_nccl_timeout"):
+        from torch.distributed import constants
+        return getattr(constants, name)
     return getattr(_td, name)

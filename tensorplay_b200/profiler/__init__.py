@@ -29,6 +29,40 @@ class nvtx_range:
         return False
 
 
+def merge_distributed_traces(paths, out_path) -> str:
+    """Merge the Chrome-trace files that the ranks of a job exported (``.json`` or ``.json.gz``) into
+    one document: the events of rank ``r`` keep their order and get process ids offset by
+    ``r * 10_000_000``, so the ranks show as separate process groups on one time axis. The rank is read
+    from the file's ``distributedInfo.rank`` (PyTorch's profiler writes it when the process group is
+    initialised), else it is the file's position in ``paths``.
+    After tensorplay/profiler/_chrome_trace_export.py:379-404."""
+    import gzip
+    import json
+    import os
+
+    def opener(path, mode):
+        path = os.fspath(path)
+        return gzip.open(path, mode + "t", encoding="utf-8") if path.endswith(".gz") else open(path, mode, encoding="utf-8")
+    merged = {"traceEvents": [], "displayTimeUnit": "ns", "distributedInfo": {"merged_ranks": []}}
+    for i, path in enumerate(paths):
+        with opener(path, "r") as f:
+            doc = json.load(f)
+        if isinstance(doc, list):                      # the bare-array form of the trace format
+            doc = {"traceEvents": doc}
+        rank = doc.get("distributedInfo", {}).get("rank")
+        rank = i if rank is None else int(rank)
+        merged["distributedInfo"]["merged_ranks"].append(rank)
+        for event in doc.get("traceEvents", []):
+            event = dict(event)
+            if isinstance(event.get("pid"), int) or (isinstance(event.get("pid"), str) and event["pid"].lstrip("-").isdigit()):
+                event["pid"] = rank * 10_000_000 + int(event["pid"])
+            merged["traceEvents"].append(event)
+    merged["traceName"] = os.fspath(out_path)
+    with opener(out_path, "w") as f:
+        json.dump(merged, f)
+    return os.fspath(out_path)
+
+
 def __getattr__(name):
     """Event containers, ``emit_nvtx`` / ``emit_itt`` and the rest of the profiler surface resolve to PyTorch's."""
     import importlib

@@ -26,3 +26,18 @@ from .states import (basis_state, bloch2dens, bloch2sv, dens2bloch, density_from
                      density_to_state, encode_state, fidelity, flatten, global_phase, inner, norm, normalize,
                      partial_trace, plus_state, product_state, random_state, state_from_bases, state_from_counts,
                      sv2bloch, to_density, unflatten, zeros_state)
+
+
+def encode_w(wires) -> str:
+    """Wire indices as a dictionary key: ``[1, 3, 2] -> "1.3.2"`` (tensorplay/quantum/_helpers.py:107)."""
+    import operator
+    if isinstance(wires, int):
+        wires = [wires]
+    return ".".join(str(operator.index(w)) for w in wires)
+
+
+def decode_w(key) -> list:
+    """Inverse of :func:`encode_w`: ``"1.3.2" -> [1, 3, 2]``."""
+    if not key:
+        raise ValueError("a wire key must not be empty")
+    return [int(part) for part in str(key).split(".")]

@@ -14,11 +14,12 @@ from typing import Any, Mapping, Optional
 
 import torch
 
-from .mega import load_mega, parse_mega, save_mega, verify_record
+from .mega import DEFAULT_ALIGNMENT, load_mega, parse_mega, save_mega, verify_record
 from .safetensors import load_safetensors, read_safetensors_header, save_safetensors
 
 __all__ = ["save", "load", "inspect_checkpoint", "sniff_format", "save_sharded", "load_sharded",
-           "convert_to_mega", "save_mega", "load_mega", "save_safetensors", "load_safetensors"]
+           "convert_to_mega", "convert_model", "save_mega", "load_mega", "save_safetensors", "load_safetensors",
+           "parse_mega_header", "resolve_map_location", "DEFAULT_ALIGNMENT", "MEGA_EXTENSION", "MEGA_INDEX_SUFFIX"]
 
 
 def sniff_format(path) -> str:
@@ -147,9 +148,86 @@ def load_sharded(path, map_location=None) -> dict:
     return out
 
 
-def convert_to_mega(src, dst, **kw) -> None:
-    """Re-write any loadable checkpoint as ``.mega``."""
-    save_mega(load(src), dst, **kw)
+MEGA_EXTENSION = ".mega"
+MEGA_INDEX_SUFFIX = ".mega.index.json"
+_CHECKPOINT_SUFFIXES = (".safetensors", ".pt", ".pth", ".bin", ".ckpt")
+
+
+def convert_to_mega(src, dst=None, **kw):
+    """Re-write a loadable checkpoint file, or every checkpoint file of a model directory, as
+    ``.mega`` and return the path written. A file goes to ``dst`` (a ``.mega`` path or a
+    directory; default: next to the source). A directory is converted file by file into ``dst``
+    (default: the directory itself); when it holds a shard index, a ``model.mega.index.json`` with the
+    same ``weight_map`` pointing at the new files is written too, so ``load`` accepts the result.
+    After tensorplay/serialization/mega.py:1438-1479."""
+    src = os.fspath(src)
+    if os.path.isfile(src):
+        stem = os.path.splitext(os.path.basename(src))[0]
+        if dst is None:
+            target = os.path.join(os.path.dirname(src), stem + MEGA_EXTENSION)
+        else:
+            dst = os.fspath(dst)
+            target = dst if dst.endswith(MEGA_EXTENSION) and not os.path.isdir(dst) else os.path.join(dst, stem + MEGA_EXTENSION)
+        os.makedirs(os.path.dirname(os.path.abspath(target)), exist_ok=True)
+        save_mega(load(src), target, **kw)
+        return target
+    if not os.path.isdir(src):
+        raise FileNotFoundError(src)
+    out_dir = os.fspath(dst) if dst is not None else src
+    os.makedirs(out_dir, exist_ok=True)
+    renamed = {}
+    for name in sorted(os.listdir(src)):
+        if name.endswith(_CHECKPOINT_SUFFIXES):
+            renamed[name] = os.path.basename(convert_to_mega(os.path.join(src, name), out_dir, **kw))
+    if not renamed:
+        raise FileNotFoundError(f"no checkpoint file ({', '.join(_CHECKPOINT_SUFFIXES)}) in {src!r}")
+    for name in os.listdir(src):
+        if name.endswith(".index.json") and not name.endswith(MEGA_INDEX_SUFFIX):
+            with open(os.path.join(src, name)) as f:
+                index = json.load(f)
+            index["weight_map"] = {k: renamed.get(v, v) for k, v in index.get("weight_map", {}).items()}
+            with open(os.path.join(out_dir, "model" + MEGA_INDEX_SUFFIX), "w") as f:
+                json.dump(index, f, indent=1)
+    return out_dir
+
+
+convert_model = convert_to_mega
+
+
+def parse_mega_header(path) -> dict:
+    """Metadata and tensor byte ranges of a ``.mega`` file without reading tensor data
+    (the native parser's document plus the file size)."""
+    doc = parse_mega(path)
+    doc["file_size"] = os.path.getsize(os.fspath(path))
+    return doc
+
+
+def resolve_map_location(map_location, location: str, nbytes: int = 0):
+    """Where one saved storage goes: ``None`` keeps the saved location (returns ``None``); a string
+    or ``torch.device`` names the target; a mapping translates saved locations (missing keys keep
+    theirs); a callable gets ``(storage_stub, location)`` like ``torch.load``'s and may return a
+    device, a destination tensor or ``None``. After tensorplay/serialization/common.py:68-100."""
+    if map_location is None:
+        return None
+    if isinstance(map_location, bytes):
+        map_location = map_location.decode()
+    if isinstance(map_location, (str, torch.device)):
+        return torch.device(map_location)
+    if isinstance(map_location, Mapping):
+        target = map_location.get(location, location)
+        return None if target is None else torch.device(target)
+    if callable(map_location):
+        stub = torch.empty(0, dtype=torch.uint8).untyped_storage()
+        stub.saved_nbytes = nbytes
+        result = map_location(stub, location)
+        if result is None or isinstance(result, torch.Tensor):
+            return result
+        if isinstance(result, (str, torch.device)):
+            return torch.device(result)
+        if hasattr(result, "device"):
+            return torch.device(result.device)
+        raise TypeError(f"map_location returned {type(result).__name__}; expected a device, a tensor or None")
+    raise TypeError(f"unsupported map_location of type {type(map_location).__name__}")
 
 
 def __getattr__(name):

@@ -210,3 +210,54 @@ def test_swap_in_optimizer_params_and_state():
     for p, o in zip(lin.parameters(), own):
         assert torch.equal(p, o)                                                # the live model did not move
     assert all(not torch.equal(c, o) for c, o in zip(copies.values(), own))     # the copies did
+
+
+def test_serialization_helpers_and_trace_merge(tmp_path):
+    import gzip
+    import json
+
+    import torch
+
+    import tensorplay_b200 as tp
+    from tensorplay_b200 import serialization as S
+    state = {"w": torch.arange(6.0).reshape(2, 3), "b": torch.ones(3, dtype=torch.bfloat16)}
+    src = tmp_path / "model.safetensors"
+    S.save_safetensors(state, str(src))
+    out = S.convert_model(str(src))
+    assert out == str(tmp_path / "model.mega") and S.sniff_format(out) == "mega"
+    hdr = S.parse_mega_header(out)
+    assert hdr["file_size"] == (tmp_path / "model.mega").stat().st_size
+    back = S.load(out)
+    assert torch.equal(back["w"], state["w"]) and back["b"].dtype == torch.bfloat16
+    # a sharded directory: every shard is converted and the index follows the new names
+    shard_dir = tmp_path / "sharded"
+    S.save_sharded({f"layer{i}.w": torch.full((4, 4), float(i)) for i in range(4)}, str(shard_dir), max_shard_bytes=100,
+                   format="safetensors")
+    mega_dir = S.convert_to_mega(str(shard_dir), str(tmp_path / "as_mega"))
+    files = sorted(p.name for p in (tmp_path / "as_mega").iterdir())
+    assert "model.mega.index.json" in files and all(f.endswith((".mega", ".json")) for f in files)
+    got = S.load_sharded(mega_dir)
+    assert sorted(got) == [f"layer{i}.w" for i in range(4)] and float(got["layer3.w"][0, 0]) == 3.0
+    assert S.resolve_map_location(None, "cuda:0") is None
+    assert S.resolve_map_location("cpu", "cuda:0") == torch.device("cpu")
+    assert S.resolve_map_location({"cuda:0": "cpu"}, "cuda:0") == torch.device("cpu")
+    assert S.resolve_map_location({"cuda:1": "cpu"}, "cuda:0") == torch.device("cuda:0")
+    assert S.resolve_map_location(lambda storage, loc: "cpu" if loc.startswith("cuda") else None, "cuda:3") == torch.device("cpu")
+    assert (S.DEFAULT_ALIGNMENT, S.MEGA_EXTENSION, S.MEGA_INDEX_SUFFIX) == (4096, ".mega", ".mega.index.json")
+
+    traces = []
+    for rank in (1, 0):
+        path = tmp_path / f"trace{rank}.json.gz"
+        with gzip.open(path, "wt") as f:
+            json.dump({"distributedInfo": {"rank": rank}, "traceEvents": [{"name": f"k{rank}", "pid": 7, "ts": rank}]}, f)
+        traces.append(str(path))
+    merged = tp.profiler.merge_distributed_traces(traces, str(tmp_path / "all.json"))
+    doc = json.load(open(merged))
+    assert doc["distributedInfo"]["merged_ranks"] == [1, 0]
+    assert sorted(e["pid"] for e in doc["traceEvents"]) == [7, 10_000_007]
+    assert tp.quantum.decode_w(tp.quantum.encode_w([1, 3, 2])) == [1, 3, 2] and tp.quantum.encode_w(4) == "4"
+    import datetime
+    assert isinstance(tp.distributed.default_pg_timeout, datetime.timedelta)
+    from tensorplay_b200.func import vmap
+    from tensorplay_b200.linalg import svd   # noqa: F401
+    assert float(vmap(lambda v: v.sum())(torch.ones(2, 3))[0]) == 3.0
