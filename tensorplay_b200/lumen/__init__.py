@@ -27,3 +27,10 @@ from .variants import (ClassSummarizer, CommonStats, DeepLiftShap, GradientAttri
                        NeuronAttribution, NeuronDeconvolution, NeuronDeepLift, NeuronFeatureAblation, NeuronGradient,
                        NeuronGradientShap, NeuronGuidedBackprop, NeuronIntegratedGradients, PerturbationAttribution,
                        Summarizer)
+from . import visualization  # noqa: E402
+from .extras import (DataLoaderAttribution, GraphDeconvolution, GraphGuidedBackprop, LayerDeepLiftShap, LimeBase,  # noqa: E402
+                     NeuronDeepLiftShap, graph_gradient_func, node_names, trace)
+from .inputs import (MSE, Count, ImageMaskInput, InterpretableEmbeddingBase, InterpretableInput, LLMAttribution,  # noqa: E402
+                     LLMAttributionResult, Max, Mean, Min, ProductBaselines, RemoteLLMAttribution, RemoteLLMProvider, Stat,
+                     StatValue, StdDev, Sum, SummarizerSingleTensor, TextTemplateInput, TextTokenInput, TokenReferenceBase, Var,
+                     VLLMProvider, configure_interpretable_embedding_layer, remove_interpretable_embedding_layer)
