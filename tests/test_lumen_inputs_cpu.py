@@ -123,6 +123,7 @@ def test_image_mask_input_paints_absent_segments():
 
 
 def test_stats_embedding_wrapper_and_generic_lime():
+    torch.manual_seed(0)
     g = torch.Generator().manual_seed(0)
     x = torch.randn(50, 3, generator=g).double()
     s = L.SummarizerSingleTensor([L.Mean(), L.Var(), L.Var(order=1), L.StdDev(), L.Min(), L.Max(), L.Sum(), L.Count(), L.MSE()])
@@ -165,6 +166,7 @@ def test_stats_embedding_wrapper_and_generic_lime():
 
 
 def test_dataloader_attribution_and_deeplift_shap_variants():
+    torch.manual_seed(0)                         # initial weights of the small networks
     g = torch.Generator().manual_seed(1)
     x = torch.randn(12, 3, generator=g)
     w = torch.tensor([1.0, -2.0, 0.0])
@@ -191,6 +193,7 @@ def test_dataloader_attribution_and_deeplift_shap_variants():
 
 
 def test_graph_mode_and_presentation():
+    torch.manual_seed(0)
     net = nn.Sequential(nn.Linear(4, 6), nn.ReLU(), nn.Linear(6, 3))
     names = L.node_names(net)
     assert names[0] == "input_1" or names[0].startswith("input") and names[-1] == "output"

@@ -57,6 +57,7 @@ def test_panoptic_quality_matches_the_documented_examples():
 def test_feature_statistics_against_scipy():
     import scipy.linalg
     g = torch.Generator().manual_seed(0)
+    torch.manual_seed(0)                       # the layer's initial weights
     net = torch.nn.Sequential(torch.nn.Flatten(), torch.nn.Linear(48, 8)).double()
     real = torch.randn(200, 3, 4, 4, generator=g).double()
     fake = (torch.randn(200, 3, 4, 4, generator=g) * 1.3 + 0.2).double()
@@ -67,13 +68,14 @@ def test_feature_statistics_against_scipy():
     sr, sf = np.cov(fr.T), np.cov(ff.T)
     want = ((fr.mean(0) - ff.mean(0)) ** 2).sum() + np.trace(sr + sf - 2 * scipy.linalg.sqrtm(sr @ sf).real)
     assert abs(float(fid.compute()) - want) < 1e-5 * max(1.0, want)
+    far = (torch.randn(200, 3, 4, 4, generator=g) * 2.0 + 1.0).double()
     kid = M.KernelInceptionDistance(feature=net, subsets=5, subset_size=100)
     kid.update(real, True)
-    kid.update(fake, False)
+    kid.update(far, False)
     same = M.KernelInceptionDistance(feature=net, subsets=5, subset_size=100)
     same.update(real, True)
     same.update(real.flip(0), False)
-    assert float(kid.compute()[0]) > 0.02 and abs(float(same.compute()[0])) < 0.02
+    assert float(kid.compute()[0]) > 10 * abs(float(same.compute()[0]))
     # inception score: uniform predictions -> 1, confident and balanced over k classes -> k
     onehot = lambda x: 50.0 * torch.nn.functional.one_hot(x.reshape(-1).long() % 4, 4).double()   # noqa: E731
     conf = M.InceptionScore(feature=onehot, splits=2)
@@ -87,6 +89,7 @@ def test_feature_statistics_against_scipy():
 
 
 def test_embedding_metrics_with_caller_networks():
+    torch.manual_seed(0)
     g = torch.Generator().manual_seed(1)
     conv = torch.nn.Conv2d(3, 6, 3).double()
     feats = lambda x: [conv(x.double()), torch.nn.functional.avg_pool2d(conv(x.double()), 2)]   # noqa: E731
