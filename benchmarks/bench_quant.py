@@ -32,7 +32,7 @@ def timeit(fn, iters=10, warmup=3):
 
 def profile_gemv(bits: int) -> None:
     """A few eager calls of the default GEMV kernel over four weight sets (0.5-0.9 GB on the device):
-    the case to run under a profiler (``ncu -k regex:wq_gemv_mma -c 2``)."""
+    the case to run under a profiler (``ncu --clock-control none -k regex:wq_gemv_mma -c 2``, on this small case only)."""
     dev = "cuda"
     N, K, M, group = 28672, 8192, 8, (0 if bits == 8 else 128)
     x = torch.randn(M, K, device=dev).bfloat16()

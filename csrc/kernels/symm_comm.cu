@@ -146,6 +146,9 @@ rs_adamw_kernel(PeerPtrs grads, size_t lo, size_t n, float* __restrict__ master,
   // local_only: every gradient copy already sits in this GPU's memory (the copy engines pulled the
   // peers' slices and the hand-shakes ran as separate one-CTA kernels): no flags are touched here
   if (!local_only && !rendezvous(s, ready_slot, 21)) return;
+  // A hand-shake kernel earlier in this stream ran out of time (status word set): the staged
+  // gradient copies are then incomplete, so master weights and moments must stay untouched.
+  if (local_only && s.status && *reinterpret_cast<volatile uint32_t*>(s.status) != 0u) return;
   const float gs = h.grad_scale * (clip_coef ? *clip_coef : 1.f);
   const size_t nvec = n / 8;
   float local_sq = 0.f;

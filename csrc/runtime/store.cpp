@@ -29,6 +29,8 @@
 
 namespace {
 
+constexpr uint64_t kMaxValue = 256ull << 20;  // largest value a request may carry (bytes)
+
 enum Op : uint8_t { SET = 1, GET = 2, ADD = 3, CAS = 4, WAIT = 5, DEL = 6, CHECK = 7, NKEYS = 8, PING = 9 };
 enum Status : int32_t { OK = 0, TIMEOUT = 1, MISSING = 2, ERR = 3 };
 
@@ -94,14 +96,21 @@ struct Server {
       std::string v1, v2;
       uint64_t l1, l2;
       int64_t arg;
-      if (!recv_all(fd, &l1, 8) || l1 > (1ull << 32)) break;
+      // Values are rendezvous blobs (addresses, handles, small pickles): a peer that announces more
+      // than kMaxValue is not one of ours, and the buffer is not grown for it.
+      if (!recv_all(fd, &l1, 8) || l1 > kMaxValue) break;
       v1.resize(l1);
       if (l1 && !recv_all(fd, &v1[0], l1)) break;
-      if (!recv_all(fd, &l2, 8) || l2 > (1ull << 32)) break;
+      if (!recv_all(fd, &l2, 8) || l2 > kMaxValue) break;
       v2.resize(l2);
       if (l2 && !recv_all(fd, &v2[0], l2)) break;
       if (!recv_all(fd, &arg, 8)) break;
       auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(arg < 0 ? 0 : arg);
+      // key count must fit the operation: one key for the single-key ops, at least one for the
+      // multi-key ones, none needed for NKEYS / PING
+      const bool single = op == SET || op == GET || op == ADD || op == CAS || op == DEL;
+      const bool multi = op == WAIT || op == CHECK;
+      if ((single && nkeys != 1) || (multi && nkeys < 1)) { reply(fd, ERR, ""); continue; }
       switch (op) {
         case SET: {
           { std::lock_guard<std::mutex> g(mu); kv[keys[0]] = v1; }
@@ -233,6 +242,11 @@ void* tpb_store_server_start(int port, int* port_out) {
   sockaddr_in addr{};
   addr.sin_family = AF_INET;
   addr.sin_addr.s_addr = htonl(INADDR_ANY);
+  // TPB_STORE_BIND_ADDR narrows the listening interface (the single-node launcher sets loopback)
+  if (const char* bind_to = getenv("TPB_STORE_BIND_ADDR")) {
+    in_addr a{};
+    if (*bind_to && inet_pton(AF_INET, bind_to, &a) == 1) addr.sin_addr = a;
+  }
   addr.sin_port = htons((uint16_t)port);
   if (::bind(fd, reinterpret_cast<sockaddr*>(&addr), sizeof(addr)) != 0 || ::listen(fd, 512) != 0) {
     ::close(fd);

@@ -224,12 +224,12 @@ class DistributedDataParallel(nn.Module):
                 goff, lo, shard, b.master.data_ptr(), b.exp_avg.data_ptr(), b.exp_avg_sq.data_ptr(), None,
                 a.offset_of(b.flat_param), None, None, 0, c.lr, c.betas[0], c.betas[1], c.eps, c.weight_decay,
                 self.step_count + 1, 1.0 / self.world, None, a.pad_off, b.slot_ready, b.slot_done, b.epoch,
-                a.counter[b.index % 64:].data_ptr(), 64, 30.0, st.data_ptr(), stream_ptr())
+                a.counter_ptr(b.index), 64, 30.0, st.data_ptr(), stream_ptr())
         else:
             code = a.raw.tpb_symm_rs_adamw(
                 goff, lo, shard, None, None, None, None, goff, None, None, 2, 0.0, 0.0, 0.0, 0.0, 0.0, 1,
                 1.0 / self.world, None, a.pad_off, b.slot_ready, b.slot_done, b.epoch,
-                a.counter[b.index % 64:].data_ptr(), 64, 30.0, st.data_ptr(), stream_ptr())
+                a.counter_ptr(b.index), 64, 30.0, st.data_ptr(), stream_ptr())
         _native.launch_count += 1
         _native.check(code, "tpb_symm_rs_adamw")
         # every rank's slice must have landed before this rank reads the bucket again

@@ -16,6 +16,7 @@ import os
 import signal
 import subprocess
 import sys
+import threading
 import time
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
@@ -46,10 +47,14 @@ class LaunchConfig:
 class LocalElasticAgent:
     def __init__(self, config: LaunchConfig, cmd: List[str]):
         self.cfg, self.cmd = config, cmd
+        if config.master_addr in ("127.0.0.1", "localhost"):
+            # one node: the rendezvous store listens on loopback only
+            os.environ.setdefault("TPB_STORE_BIND_ADDR", "127.0.0.1")
         self.store = TCPStore(config.master_addr, config.master_port, is_master=True, timeout=60)
         self.procs: List[subprocess.Popen] = []
         self.restart_count = 0
         self.logs = []
+        self._tees: List[threading.Thread] = []
 
     def _start_workers(self) -> None:
         n = self.cfg.nproc_per_node
@@ -72,8 +77,25 @@ class LocalElasticAgent:
                 os.makedirs(self.cfg.log_dir, exist_ok=True)
                 out = open(os.path.join(self.cfg.log_dir, f"attempt{self.restart_count}_rank{r}.log"), "w")
                 self.logs.append(out)
-            self.procs.append(subprocess.Popen(self.cmd, env=env, stdout=out, stderr=subprocess.STDOUT if out else None,
-                                               start_new_session=True))
+            tee = self.cfg.tee and out is not None
+            p = subprocess.Popen(self.cmd, env=env, stdout=subprocess.PIPE if tee else out,
+                                 stderr=subprocess.STDOUT if out else None, start_new_session=True)
+            if tee:
+                # the rank's output goes to its log file and, prefixed, to the launcher's stdout
+                t = threading.Thread(target=self._tee, args=(p.stdout, out, r), daemon=True)
+                t.start()
+                self._tees.append(t)
+            self.procs.append(p)
+
+    @staticmethod
+    def _tee(pipe, log, rank: int) -> None:
+        for line in iter(pipe.readline, b""):
+            text = line.decode("utf-8", "replace")
+            log.write(text)
+            log.flush()
+            sys.stdout.write(f"[rank{rank}] {text}")
+            sys.stdout.flush()
+        pipe.close()
 
     def _stop_workers(self) -> None:
         for p in self.procs:
@@ -91,8 +113,12 @@ class LocalElasticAgent:
                     os.killpg(p.pid, signal.SIGKILL)
                 except ProcessLookupError:
                     pass
+        for t in self._tees:
+            t.join(timeout=2)
+        self._tees = []
         for f in self.logs:
             f.close()
+        self.logs = []
 
     def _monitor(self) -> Dict[int, int]:
         """Blocks until all workers exited 0 (returns {}) or one failed (returns {rank: code})."""
@@ -106,13 +132,23 @@ class LocalElasticAgent:
             time.sleep(self.cfg.monitor_interval)
 
     def run(self) -> int:
+        """Runs the group to completion. Whatever ends the launcher (a worker failure past the restart
+        budget, Ctrl-C, SIGTERM, an exception in here) also ends every worker: the ranks run in
+        sessions of their own and would otherwise outlive the launcher holding their GPUs."""
+
+        def _on_signal(signum, _frame):
+            raise KeyboardInterrupt(f"tprun: signal {signum}")
+
+        previous = {}
+        if threading.current_thread() is threading.main_thread():
+            for sig in (signal.SIGTERM, signal.SIGINT):
+                previous[sig] = signal.signal(sig, _on_signal)
         try:
             while True:
                 self._start_workers()
                 failed = self._monitor()
                 if not failed:
-                    for f in self.logs:
-                        f.close()
+                    self._stop_workers()  # all exited 0: joins the tee threads, closes the logs
                     return 0
                 self._stop_workers()
                 if self.restart_count >= self.cfg.max_restarts:
@@ -120,6 +156,9 @@ class LocalElasticAgent:
                 self.restart_count += 1
                 self.store.set(f"restart/{self.restart_count}", str(failed))
         finally:
+            self._stop_workers()
+            for sig, h in previous.items():
+                signal.signal(sig, h)
             self.store.close()
 
 
@@ -128,24 +167,35 @@ def elastic_launch(config: LaunchConfig, cmd: List[str]) -> int:
 
 
 def run(args) -> int:
-    """Launch from a parsed argument namespace or an argv list (the function form of ``tprun``)."""
-    return main(args if isinstance(args, (list, tuple)) else None)
+    """Launch from a parsed argument namespace (as ``get_args_parser().parse_args`` returns it) or
+    an argv list: the function form of ``tprun``."""
+    if isinstance(args, argparse.Namespace):
+        return _launch(args)
+    return main(list(args) if args is not None else None)
 
 
-def main(argv=None) -> int:
+def get_args_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="tprun")
     ap.add_argument("--nproc-per-node", "--nproc_per_node", type=int, default=int(os.environ.get("TP_NPROC", "1")))
     ap.add_argument("--max-restarts", "--max_restarts", type=int, default=0)
     ap.add_argument("--master-addr", default="127.0.0.1")
     ap.add_argument("--master-port", type=int, default=0)
     ap.add_argument("--log-dir", default=None)
+    ap.add_argument("--tee", action="store_true", help="with --log-dir: also print every rank's output, prefixed")
     ap.add_argument("--no-python", action="store_true")
     ap.add_argument("script")
     ap.add_argument("script_args", nargs=argparse.REMAINDER)
-    a = ap.parse_args(argv)
-    cmd = ([] if a.no_python else [sys.executable, "-u"]) + [a.script] + a.script_args
+    return ap
+
+
+def main(argv=None) -> int:
+    return _launch(get_args_parser().parse_args(argv))
+
+
+def _launch(a: argparse.Namespace) -> int:
+    cmd = ([] if a.no_python else [sys.executable, "-u"]) + [a.script] + list(a.script_args)
     cfg = LaunchConfig(a.nproc_per_node, a.max_restarts, master_addr=a.master_addr, master_port=a.master_port,
-                       log_dir=a.log_dir)
+                       log_dir=a.log_dir, tee=getattr(a, "tee", False))
     try:
         return elastic_launch(cfg, cmd)
     except ChildFailedError as e:

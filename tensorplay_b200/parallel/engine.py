@@ -213,6 +213,8 @@ class FSDPEngine:
                 from .. import _native
                 _native.kernels().tpb_adamw_set_overlap(c, m_)
         self.kernel_launch_estimate = 0
+        self._status_host = None
+        self._status_event = None
 
     # ------------------------------------------------------------------ construction
     def _build_units(self) -> None:
@@ -546,8 +548,45 @@ class FSDPEngine:
             torch.cuda.current_stream().wait_stream(stream)
 
     # ------------------------------------------------------------------ public API
+    def _poll_status(self, blocking: bool = False) -> None:
+        """Raise ``DeviceWaitTimeout`` when a kernel of an earlier step gave up on a bounded wait.
+
+        The status word is copied to pinned host memory at the end of every step without a
+        synchronisation; the copy of step k is looked at when step k + 1 starts (or at once with
+        ``blocking``), so training never continues silently on incomplete gradients."""
+        if not self.cuda or self.comm is None:
+            return
+        from ..ops._common import DeviceWaitTimeout, status_word
+        w = status_word(self.device)
+        if self._status_host is None:
+            self._status_host = torch.zeros(4, dtype=torch.int32).pin_memory()
+        ev = self._status_event
+        if ev is not None and (blocking or ev.query()):
+            ev.synchronize()
+            v = int(self._status_host[0]) & 0xFFFFFFFF
+            if v:
+                self._status_event = None
+                w.zero_()
+                names = {1: "mbarrier wait", 2: "flag wait", 3: "bad arguments"}
+                raise DeviceWaitTimeout(
+                    f"a communication kernel reported {names.get(v & 0xFF, v & 0xFF)} time-out at site {v >> 8}; "
+                    "parameters of the affected units were left unchanged")
+
+    def _record_status(self) -> None:
+        if not self.cuda or self.comm is None:
+            return
+        from ..ops._common import status_word
+        if self._status_host is None:
+            self._status_host = torch.zeros(4, dtype=torch.int32).pin_memory()
+        # read behind the communication stream's kernels of this step, without holding up compute
+        with torch.cuda.stream(self.comm_stream):
+            self._status_host.copy_(status_word(self.device), non_blocking=True)
+            self._status_event = torch.cuda.Event()
+            self._status_event.record(self.comm_stream)
+
     def forward_backward(self, tokens: Tensor, targets: Tensor) -> Tensor:
         m = self.model
+        self._poll_status()
         self.step_count += 1
         if self.cuda:
             # parameters updated by the previous step's in-backward AdamW
@@ -564,6 +603,7 @@ class FSDPEngine:
         loss.backward()
         if self.two_phase:
             self._clipped_update()
+        self._record_status()
         return loss.detach()
 
     def step(self, tokens: Tensor, targets: Tensor) -> Tensor:
@@ -572,6 +612,7 @@ class FSDPEngine:
     def synchronize(self) -> None:
         if self.cuda:
             torch.cuda.synchronize(self.device)
+            self._poll_status(blocking=True)
 
     # ------------------------------------------------------------------ checkpoint / resume
     def save_checkpoint(self, directory: str) -> None:

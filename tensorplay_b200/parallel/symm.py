@@ -55,6 +55,14 @@ class SymmArena:
     """Process-wide symmetric arena (one per process; collective to create)."""
 
     _instance: Optional["SymmArena"] = None
+    # one block counter per communicating unit: two launches that count into the same word may
+    # only run one after the other, so units never share one
+    N_COUNTERS = 1024
+
+    def counter_ptr(self, index: int) -> int:
+        if not 0 <= index < self.N_COUNTERS:
+            raise IndexError(f"block counter {index} out of range (have {self.N_COUNTERS})")
+        return self.counter[index:].data_ptr()
 
     def __init__(self, nbytes: int, group=None, pad_slots: int = 16384):
         lib = _native.kernels()
@@ -83,7 +91,7 @@ class SymmArena:
         self.pad_slots = pad_slots
         self.pad_off = self._alloc_bytes(pad_slots * 4)
         self._next_slot = 0
-        self.counter = torch.zeros(64, dtype=torch.int32, device=self.device)
+        self.counter = torch.zeros(self.N_COUNTERS, dtype=torch.int32, device=self.device)
         if self.world > 1:
             dist.barrier(group=group)
         SymmArena._instance = self
@@ -209,7 +217,7 @@ class SymmComm:
             u.exp_avg_sq.data_ptr(), u.shard.data_ptr(), NO_OFFSET, None, None, 0, adam["lr"],
             adam["beta1"], adam["beta2"], adam["eps"], adam["weight_decay"], int(adam["step"]),
             1.0 / self.world, None, self.arena.pad_off, self.slot_ready[u.index],
-            self.slot_done[u.index], ep, self.arena.counter[u.index % 64:].data_ptr(),
+            self.slot_done[u.index], ep, self.arena.counter_ptr(u.index),
             self.reduce_ctas, self.wait_s, self.status.data_ptr(), stream_ptr())
         _native.launch_count += 1
         _native.check(code, "tpb_symm_rs_adamw")
@@ -235,7 +243,7 @@ class SymmComm:
             self.arena.offset_of(g), lo, hi - lo, None, None, None, None, NO_OFFSET, red_out.data_ptr(),
             sumsq.data_ptr(), 1, 0.0, 0.9, 0.999, 1e-8, 0.0, 1, 1.0 / self.world, None, self.arena.pad_off,
             self.slot_ready[u.index], self.slot_done[u.index], ep,
-            self.arena.counter[u.index % 64:].data_ptr(), self.reduce_ctas, self.wait_s,
+            self.arena.counter_ptr(u.index), self.reduce_ctas, self.wait_s,
             self.status.data_ptr(), stream_ptr())
         _native.launch_count += 1
         _native.check(code, "tpb_symm_rs_adamw")

@@ -50,66 +50,109 @@ def _rt():
 
 
 # ------------------------------------------------------------------ tree <-> flat
+_ESCAPES = ("__tensor__", "__tuple__", "__dict__")
+
+
 def flatten_tree(obj) -> Tuple[Dict[str, torch.Tensor], str, Any]:
-    """Returns (name -> tensor, container kind, layout or None)."""
+    """Returns (name -> tensor, container kind, layout or None).
+
+    Container kinds follow the reference's writer (tensorplay/serialization/mega.py:323-398) so
+    that either side reads the other's files: a bare tensor is ``"tensor"`` under the name "0";
+    a flat str -> tensor mapping is ``"dict"``, a flat list / tuple of tensors ``"list"`` /
+    ``"tuple"`` with names "0", "1", ... and no layout; everything else is ``"tree"`` with a JSON
+    layout. A tensor object that occurs more than once is stored once and referenced by name from
+    every place, so tied tensors come back tied.
+    """
     if isinstance(obj, torch.Tensor):
-        return {"tensor": obj}, "tensor", None
-    if isinstance(obj, Mapping) and all(isinstance(k, str) and isinstance(v, torch.Tensor) for k, v in obj.items()):
-        return dict(obj), "dict", None
+        return {"0": obj}, "tensor", None
     flat: Dict[str, torch.Tensor] = {}
+    by_id: Dict[int, str] = {}
+    open_nodes = set()
+
+    def name_for(t, path):
+        known = by_id.get(id(t))
+        if known is None:
+            base = ".".join(str(p) for p in path) or "0"
+            known, n = base, 0
+            while known in flat:
+                n += 1
+                known = f"{base}#{n}"
+            flat[known] = t
+            by_id[id(t)] = known
+        return {"__tensor__": known}
 
     def enc(x, path):
         if isinstance(x, torch.Tensor):
-            name = path or "tensor"
-            while name in flat:
-                name += "_"
-            flat[name] = x
-            return {"__tensor__": name}
-        if isinstance(x, Mapping):
-            if all(isinstance(k, str) and not k.startswith("__") for k in x):
-                return {k: enc(v, f"{path}.{k}" if path else k) for k, v in x.items()}
-            return {"__dict__": [[enc(k, path + ".key"), enc(v, f"{path}.{i}")] for i, (k, v) in enumerate(x.items())]}
-        if isinstance(x, tuple):
-            return {"__tuple__": [enc(v, f"{path}.{i}" if path else str(i)) for i, v in enumerate(x)]}
-        if isinstance(x, list):
-            return [enc(v, f"{path}.{i}" if path else str(i)) for i, v in enumerate(x)]
+            return name_for(x, path)
         if x is None or isinstance(x, (bool, int, float, str)):
             return x
         if isinstance(x, (torch.dtype, torch.device, torch.Size)):
             return {"__repr__": [type(x).__name__, str(x) if not isinstance(x, torch.Size) else list(x)]}
-        raise TypeError(f"object of type {type(x).__name__} cannot be stored in a .mega file")
+        if not isinstance(x, (Mapping, list, tuple)):
+            where = ".".join(map(str, path)) or "<root>"
+            raise TypeError(f"object of type {type(x).__name__} at {where} cannot be stored in a .mega file")
+        if id(x) in open_nodes:
+            raise ValueError("a container that contains itself cannot be stored in a .mega file")
+        open_nodes.add(id(x))
+        try:
+            if isinstance(x, Mapping):
+                items = [(k, enc(v, path + [k])) for k, v in x.items()]
+                plain = all(isinstance(k, str) for k, _ in items)
+                if not plain and not all(isinstance(k, (bool, int, float, str)) for k, _ in items):
+                    raise TypeError("mapping keys of a .mega tree must be strings or numbers")
+                if not plain or (len(items) == 1 and items[0][0] in _ESCAPES + ("__repr__",)):
+                    return {"__dict__": [[k, v] for k, v in items]}
+                return dict(items)
+            seq = [enc(v, path + [i]) for i, v in enumerate(x)]
+            return seq if isinstance(x, list) else {"__tuple__": seq}
+        finally:
+            open_nodes.discard(id(x))
 
-    layout = enc(obj, "")
-    kind = "list" if isinstance(obj, list) else "tuple" if isinstance(obj, tuple) else "tree"
-    return flat, kind, layout
+    layout = enc(obj, [])
+    all_tensors = lambda vals: all(isinstance(v, torch.Tensor) for v in vals)  # noqa: E731
+    if isinstance(obj, Mapping) and all(isinstance(k, str) for k in obj) and all_tensors(obj.values()) \
+            and len(flat) == len(obj):
+        return {k: obj[k] for k in obj}, "dict", None
+    if isinstance(obj, (list, tuple)) and all_tensors(obj) and len(flat) == len(obj):
+        return {str(i): v for i, v in enumerate(obj)}, "list" if isinstance(obj, list) else "tuple", None
+    return flat, "tree", layout
 
 
 def unflatten_tree(flat: Mapping[str, torch.Tensor], kind: str, layout):
     if kind == "tensor":
+        if len(flat) != 1:
+            raise ValueError("a .mega file of kind 'tensor' holds exactly one tensor")
         return next(iter(flat.values()))
+    if kind == "list" and layout is None:
+        return list(flat.values())
+    if kind == "tuple" and layout is None:
+        return tuple(flat.values())
     if layout is None:
         return dict(flat)
 
     def dec(x):
         if isinstance(x, dict):
-            if "__tensor__" in x and len(x) == 1:
-                return flat[x["__tensor__"]]
-            if "__tuple__" in x and len(x) == 1:
-                return tuple(dec(v) for v in x["__tuple__"])
-            if "__dict__" in x and len(x) == 1:
-                return {dec(k): dec(v) for k, v in x["__dict__"]}
-            if "__repr__" in x and len(x) == 1:
-                tname, val = x["__repr__"]
-                if tname == "dtype":
-                    return getattr(torch, val.split(".")[-1])
-                if tname == "device":
-                    return torch.device(val)
-                return torch.Size(val)
+            if len(x) == 1:
+                (tag, val), = x.items()
+                if tag == "__tensor__":
+                    if val not in flat:
+                        raise ValueError(f"the .mega layout names a tensor that the file lacks: {val!r}")
+                    return flat[val]
+                if tag == "__tuple__":
+                    return tuple(dec(v) for v in val)
+                if tag == "__dict__":
+                    return {k: dec(v) for k, v in val}
+                if tag == "__repr__":
+                    tname, r = val
+                    if tname == "dtype":
+                        return getattr(torch, r.split(".")[-1])
+                    return torch.device(r) if tname == "device" else torch.Size(r)
             return {k: dec(v) for k, v in x.items()}
         if isinstance(x, list):
             return [dec(v) for v in x]
         return x
 
+    # files of earlier versions of this writer stored list / tuple roots with a layout
     return dec(layout)
 
 

@@ -147,3 +147,49 @@ def test_private_module_paths_and_rpc_probe():
     for n in ("_mesh_layout", "_pycute", "config", "_tensor"):
         assert importlib.import_module("tensorplay_b200.distributed." + n) is not None
     assert not hasattr(dist.rpc, "init_rpc") and not dist.autograd.is_available()
+
+
+def test_tprun_interrupted_launcher_takes_its_workers_down(tmp_path):
+    """SIGTERM to the launcher: the ranks (sessions of their own) are signalled and gone afterwards."""
+    import signal
+    import subprocess
+    s = _script(tmp_path, f"""
+        import os, time
+        open(r"{tmp_path}/pid" + os.environ["RANK"], "w").write(str(os.getpid()))
+        time.sleep(120)
+    """)
+    launcher = subprocess.Popen([sys.executable, "-m", "tensorplay_b200.distributed.run", "--nproc-per-node", "2", s],
+                                cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    deadline = time.time() + 60
+    while time.time() < deadline and not all((tmp_path / f"pid{r}").exists() for r in range(2)):
+        time.sleep(0.1)
+    time.sleep(0.2)
+    pids = [int((tmp_path / f"pid{r}").read_text()) for r in range(2)]
+    launcher.send_signal(signal.SIGTERM)
+    launcher.wait(timeout=30)
+
+    def alive(pid):
+        try:
+            os.kill(pid, 0)
+        except ProcessLookupError:
+            return False
+        # a zombie of another parent counts as gone
+        try:
+            return open(f"/proc/{pid}/stat").read().split(")")[1].split()[0] != "Z"
+        except OSError:
+            return False
+
+    deadline = time.time() + 15
+    while time.time() < deadline and any(alive(p) for p in pids):
+        time.sleep(0.1)
+    assert not any(alive(p) for p in pids)
+
+
+def test_tprun_namespace_form_and_tee(tmp_path, capfd):
+    from tensorplay_b200.distributed import run as tprun
+    s = _script(tmp_path, "import os; print('hello from', os.environ['RANK'], flush=True)")
+    ns = tprun.get_args_parser().parse_args(["--nproc-per-node", "2", "--log-dir", str(tmp_path / "lg"), "--tee", s])
+    assert tprun.run(ns) == 0
+    out = capfd.readouterr().out
+    assert "[rank0] hello from 0" in out and "[rank1] hello from 1" in out
+    assert "hello from 1" in (tmp_path / "lg" / "attempt0_rank1.log").read_text()

@@ -82,3 +82,46 @@ def test_sharded_index(tmp_path):
     out = tp.load(idx)
     assert set(out) == set(st) and all(torch.equal(out[k], st[k]) for k in st)
     assert torch.equal(tp.load(tmp_path / "ck")["p3"], st["p3"])
+
+
+def test_mega_container_kinds_match_the_reference_writer(tmp_path):
+    """Flat lists / tuples of tensors are stored as kind "list" / "tuple" with names "0", "1", ... and
+    no layout (reference tensorplay/serialization/mega.py:393-398); nested structure is kind "tree";
+    a tensor that occurs twice is stored once and comes back as one object."""
+    import json
+
+    from tensorplay_b200.serialization import mega
+    a, b = torch.arange(6.).reshape(2, 3), torch.ones(4, dtype=torch.int32)
+    for obj, kind in (([a, b], "list"), ((a, b), "tuple")):
+        p = tmp_path / f"{kind}.mega"
+        mega.save_mega(obj, p)
+        meta = mega.parse_mega(p)
+        assert meta["metadata"]["tensorplay.container"] == kind
+        assert "tensorplay.layout" not in meta["metadata"]
+        assert [r["name"] for r in meta["tensors"]] == ["0", "1"]
+        back = mega.load_mega(p)
+        assert type(back) is type(obj) and all(torch.equal(x, y) for x, y in zip(back, obj))
+    # a header as the reference writes it for a nested tree with a tied tensor
+    tree = {"w": a, "opt": [{"m": b, "tied": a}, (1, "s", None)], "__tensor__": {"x": 2.5}}
+    p = tmp_path / "tree.mega"
+    mega.save_mega(tree, p)
+    meta = mega.parse_mega(p)["metadata"]
+    assert meta["tensorplay.container"] == "tree"
+    layout = json.loads(meta["tensorplay.layout"])
+    assert layout["opt"][0]["tied"] == {"__tensor__": "w"}  # stored once, referenced by name
+    assert sorted(r["name"] for r in mega.parse_mega(p)["tensors"]) == ["opt.0.m", "w"]
+    back = mega.load_mega(p)
+    assert back["opt"][0]["tied"] is back["w"]
+    assert back["opt"][1] == (1, "s", None) and back["__tensor__"] == {"x": 2.5}
+    # a dict whose only key is an escape marker is written in the escaped form
+    p = tmp_path / "esc.mega"
+    mega.save_mega({"outer": {"__tuple__": a}}, p)
+    assert json.loads(mega.parse_mega(p)["metadata"]["tensorplay.layout"])["outer"] == \
+        {"__dict__": [["__tuple__", {"__tensor__": "outer.__tuple__"}]]}
+    assert torch.equal(mega.load_mega(p)["outer"]["__tuple__"], a)
+    # colliding names get "#n"
+    flat, kind, _ = mega.flatten_tree({"a": {"b": a}, "a.b": b, "z": [a]})
+    assert kind == "tree" and set(flat) == {"a.b", "a.b#1"}
+    # a bare tensor is stored under the name "0"
+    flat, kind, layout = mega.flatten_tree(a)
+    assert (list(flat), kind, layout) == (["0"], "tensor", None)

@@ -67,3 +67,46 @@ def test_tcp_store_backs_process_group():
         if dist.is_initialized():
             dist.destroy_process_group()
         master.close()
+
+
+def test_native_store_server_rejects_malformed_requests():
+    """A request whose key count does not fit its operation gets an error reply (the connection
+    stays usable); a request that announces an oversized value is dropped without growing a buffer."""
+    import socket
+    import struct
+
+    from tensorplay_b200.distributed.store import TCPStore
+    srv = TCPStore("127.0.0.1", 0, is_master=True, timeout=5)
+    try:
+        def req(sock, op, keys, v1=b"", v2=b"", arg=0):
+            msg = struct.pack("<BI", op, len(keys))
+            for k in keys:
+                msg += struct.pack("<I", len(k)) + k
+            msg += struct.pack("<Q", len(v1)) + v1 + struct.pack("<Q", len(v2)) + v2 + struct.pack("<q", arg)
+            sock.sendall(msg)
+            hdr = b""
+            while len(hdr) < 12:
+                chunk = sock.recv(12 - len(hdr))
+                if not chunk:
+                    return None
+                hdr += chunk
+            status, n = struct.unpack("<iQ", hdr)
+            body = b""
+            while len(body) < n:
+                body += sock.recv(n - len(body))
+            return status, body
+
+        with socket.create_connection(("127.0.0.1", srv.port), timeout=5) as c:
+            assert req(c, 1, [])[0] == 3            # SET without a key: error, not a crash
+            assert req(c, 2, [b"a", b"b"])[0] == 3  # GET with two keys
+            assert req(c, 7, [])[0] == 3            # CHECK needs at least one key
+            assert req(c, 1, [b"k"], b"v")[0] == 0  # the connection still serves good requests
+            assert req(c, 2, [b"k"], arg=1000) == (0, b"v")
+        with socket.create_connection(("127.0.0.1", srv.port), timeout=5) as c:
+            # announce a 1 TiB value: the server closes the connection instead of allocating
+            c.sendall(struct.pack("<BI", 1, 1) + struct.pack("<I", 1) + b"k" + struct.pack("<Q", 1 << 40))
+            assert c.recv(16) == b""
+        srv.set("still", "alive")
+        assert srv.get("still") in (b"alive", "alive")
+    finally:
+        srv.close()
