@@ -32,6 +32,14 @@ def main():
     k = torch.randn(B, T, Hkv, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
     v = torch.randn(B, T, Hkv, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
     fl_fwd = 4.0 * B * Hq * T * T * D / 2  # causal
+    sweep = {}
+    if "--sweep" in sys.argv:
+        # share of the exponentials on the FMA pipe (n of every 4 column pairs)
+        from tensorplay_b200 import _native
+        for n in (0, 1, 2):
+            _native.kernels().tpb_flash_fwd_config(n)
+            sweep[f"fwd_ms_poly{n}"] = round(timeit(lambda: flash_attention(q, k, v, causal=True)), 4)
+        _native.kernels().tpb_flash_fwd_config(1)
     ms_f = timeit(lambda: flash_attention(q, k, v, causal=True))
     o = flash_attention(q, k, v, causal=True)
     g = torch.randn_like(o)
@@ -44,6 +52,7 @@ def main():
     ms_ref = timeit(lambda: torch.nn.functional.scaled_dot_product_attention(
         qq, kk, vv, is_causal=True, enable_gqa=True))
     res["torch_sdpa_fwd_tflops"] = round(fl_fwd / ms_ref / 1e9, 1)
+    res.update(sweep)
     print(json.dumps(res), flush=True)
 
 

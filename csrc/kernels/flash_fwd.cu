@@ -42,7 +42,21 @@ struct AttnFwdParams {
   long long o_split_stride, lse_split_stride;
   uint32_t* status;
   unsigned long long wait_ns;
+  unsigned long long* trace;  // optional: cycle stamps of CTA (0,0,0), see tpb_flash_fwd_set_trace
+  int trace_cap;
 };
+
+// Debug aid: cycle stamps of block (0,0,0), kept in shared memory while the kernel runs (a stamp
+// costs one shared store) and copied out at the end: trace[(who * 64 + it) * 8 + tag] = clock.
+//   who 0: MMA thread (tags 0/1: P half of tile 0/1 seen, 2/3: P complete, 4/5: S(j+1) issued)
+//   who 1/2: first softmax thread of tile 0/1 (tags 1: S seen, 2: S in registers, 3: maximum done,
+//            4: first half exponentiated, 5: first half handed over, 6: second half exponentiated,
+//            7: second half handed over)
+constexpr int kTraceIts = 64;
+constexpr int kTraceWords = 3 * kTraceIts * 8;
+__device__ __forceinline__ void fwd_trace(uint32_t* tr, int who, int tag, int it) {
+  if (tr && it < kTraceIts) tr[(who * kTraceIts + it) * 8 + tag] = (uint32_t)clock64();
+}
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -50,55 +64,116 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-// Maximum of one S row (raw scores); keys beyond `lim` are excluded in the masked variant.
-template <bool MASKED>
-__device__ __forceinline__ float row_max(const uint32_t (&sr)[128], int k0, int lim) {
-  float m0 = kNegBig, m1 = kNegBig;  // two chains for instruction-level parallelism
-#pragma unroll
-  for (int i = 0; i < 128; i += 4) {
-    float a = __uint_as_float(sr[i]), b = __uint_as_float(sr[i + 1]);
-    float c = __uint_as_float(sr[i + 2]), d = __uint_as_float(sr[i + 3]);
-    if (MASKED) {
-      a = (k0 + i <= lim) ? a : kNegBig;
-      b = (k0 + i + 1 <= lim) ? b : kNegBig;
-      c = (k0 + i + 2 <= lim) ? c : kNegBig;
-      d = (k0 + i + 3 <= lim) ? d : kNegBig;
-    }
-    m0 = fmaxf(m0, fmaxf(a, b));
-    m1 = fmaxf(m1, fmaxf(c, d));
-  }
-  return fmaxf(m0, m1);
+// Packed fp32x2 arithmetic on 64-bit register pairs (one issue slot for two elements).
+__device__ __forceinline__ uint64_t pk2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t pk2u(uint32_t a, uint32_t b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ void upk2(uint64_t v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2_down(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rm.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
 }
 
-// sr[i / 2] <- bf16 pair exp2(S[i] * scale - m), exp2(S[i+1] * scale - m) in place; returns the
-// row sum. Packed fp32x2 FMA / ADD and a bf16x2 pre-add of neighbouring pairs keep the count at
-// about three instructions per element (the pre-add rounds the sum of two values <= 2 to bf16:
-// a relative error of 2^-9 on a 64th of the row sum).
-template <bool MASKED>
-__device__ __forceinline__ float row_exp(uint32_t (&sr)[128], int k0, int lim, float scale_log2e, float m) {
-  const float2 sc = make_float2(scale_log2e, scale_log2e);
-  const float2 nm = make_float2(-m, -m);
-  float2 acc = make_float2(0.f, 0.f);
+// Maximum of one S row (raw scores): four chains of three-input maxima.
+__device__ __forceinline__ float row_max(const uint32_t (&sr)[128]) {
+  float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-  for (int i = 0; i < 128; i += 4) {
-    uint32_t e[2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[i + 2 * h]), __uint_as_float(sr[i + 2 * h + 1])), sc, nm);
-      if (MASKED) {
-        x.x = (k0 + i + 2 * h <= lim) ? x.x : kNegBig;
-        x.y = (k0 + i + 2 * h + 1 <= lim) ? x.y : kNegBig;
-      }
-      __nv_bfloat162 d = __floats2bfloat162_rn(x.x, x.y);
-      asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(e[h]) : "r"(*reinterpret_cast<uint32_t*>(&d)));
-    }
-    uint32_t pair;
-    asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(pair) : "r"(e[0]), "r"(e[1]));
-    acc = __fadd2_rn(acc, make_float2(__uint_as_float(pair << 16), __uint_as_float(pair & 0xffff0000u)));
-    sr[i / 2] = e[0];
-    sr[i / 2 + 1] = e[1];
+  for (int i = 0; i < 128; i += 8) {
+    m0 = max3(m0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
+    m1 = max3(m1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
+    m2 = max3(m2, __uint_as_float(sr[i + 4]), __uint_as_float(sr[i + 5]));
+    m3 = max3(m3, __uint_as_float(sr[i + 6]), __uint_as_float(sr[i + 7]));
   }
-  return acc.x + acc.y;
+  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+}
+
+// Keys beyond `lim` get the score -inf (masked tiles only: the diagonal and the ragged end of the
+// sequence): it never raises the running maximum and its exponential on the special-function
+// unit is exactly zero, also for a row without any valid key in this tile.
+__device__ __forceinline__ void row_mask(uint32_t (&sr)[128], int k0, int lim) {
+#pragma unroll
+  for (int i = 0; i < 128; ++i) sr[i] = (k0 + i <= lim) ? sr[i] : 0xff800000u;
+}
+
+// exp2 of a pair on the FMA pipe: floor by the magic-number add in round-down mode, cubic
+// polynomial on the fraction (relative error 1e-4, below the bf16 rounding of P), exponent added
+// as an integer. The special-function unit delivers 16 exp2 per cycle and SM while the tensor pipe
+// needs 16 per cycle for 128-wide head dimensions, so a share of the row goes this way.
+__device__ __forceinline__ uint64_t exp2_poly2(uint64_t x) {
+  float x0, x1;
+  upk2(x, x0, x1);
+  const uint64_t xc = pk2(fmaxf(x0, -127.f), fmaxf(x1, -127.f));
+  const uint64_t magic = pk2(12582912.f, 12582912.f);  // 2^23 + 2^22
+  const uint64_t r = add2_down(xc, magic);
+  const uint64_t fr = sub2(xc, sub2(r, magic));
+  uint64_t pl = fma2(fr, pk2(0.077119089663028717f, 0.077119089663028717f), pk2(0.227564394474029541f, 0.227564394474029541f));
+  pl = fma2(pl, fr, pk2(0.695146143436431885f, 0.695146143436431885f));
+  pl = fma2(pl, fr, pk2(1.f, 1.f));
+  uint32_t p0, p1, r0, r1;
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(p0), "=r"(p1) : "l"(pl));
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(r0), "=r"(r1) : "l"(r));
+  return pk2u(p0 + (r0 << 23), p1 + (r1 << 23));
+}
+
+// One half of a row: columns [HALF * 64, HALF * 64 + 64) of sr become 32 bf16 pairs
+// P = exp2(S * scale - m) in sr[HALF * 32 ...] (in place: the pairs land where scores were already
+// consumed); the fp32 values are added into two packed accumulators. Of every four column pairs,
+// NPOLY take the polynomial, the rest the special-function unit.
+template <int HALF, int NPOLY>
+__device__ __forceinline__ void row_exp_half(uint32_t (&sr)[128], uint64_t sc, uint64_t nm, uint64_t& acc0,
+                                             uint64_t& acc1) {
+#pragma unroll
+  for (int i = HALF * 32; i < HALF * 32 + 32; ++i) {
+    const uint64_t x = fma2(pk2u(sr[2 * i], sr[2 * i + 1]), sc, nm);
+    uint64_t e;
+    if ((i & 3) < NPOLY) {
+      e = exp2_poly2(x);
+    } else {
+      float x0, x1;
+      upk2(x, x0, x1);
+      e = pk2(fast_exp2(x0), fast_exp2(x1));
+    }
+    if (i & 1) acc1 = add2(acc1, e);
+    else acc0 = add2(acc0, e);
+    float e0, e1;
+    upk2(e, e0, e1);
+    sr[i] = pack_bf16(e0, e1);
+  }
 }
 
 template <int D>
@@ -111,11 +186,12 @@ struct AttnSmem {
   static constexpr int kRing = D == 128 ? 4 : 6;
   static constexpr int kKOff = kQOff + kTilesQ * kQBytes;
   static constexpr int kBarOff = kKOff + kRing * kKBytes;
-  static constexpr int kTotal = kBarOff + 256 + 1024;
+  static constexpr int kTraceOff = kBarOff + 256;
+  static constexpr int kTotal = kTraceOff + kTraceWords * 4 + 1024;
   static_assert(kTotal <= 227 * 1024, "attention forward exceeds the shared memory of one CTA");
 };
 
-template <int D>
+template <int D, int NPOLY>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const AttnFwdParams p) {
@@ -129,7 +205,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* kv_full = bars + 1;         // R
   uint64_t* kv_empty = kv_full + R;     // R
   uint64_t* s_full = kv_empty + R;      // 2: S of tile g is complete (and so is every earlier MMA)
-  uint64_t* p_full = s_full + 2;        // 2 (128 arrivals): P of tile g is in TMEM
+  uint64_t* p_half = s_full + 2;        // 2 (128 arrivals): keys 0..63 of P of tile g are in TMEM (and O is rescaled)
+  uint64_t* p_full = p_half + 2;        // 2 (128 arrivals): all of P of tile g is in TMEM
   uint64_t* o_done = p_full + 2;        // 2: last PV of tile g is complete
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
   volatile uint32_t* abort_w = tmem_slot + 1;
@@ -172,6 +249,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     for (int i = 0; i < kTilesQ; ++i) {
       mbar_init(&s_full[i], 1);
+      mbar_init(&p_half[i], 128);
       mbar_init(&p_full[i], 128);
       mbar_init(&o_done[i], 1);
     }
@@ -189,6 +267,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   WaitCtx wc{abort_w, p.status, p.wait_ns};
+  uint32_t* trc = (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
+                      ? reinterpret_cast<uint32_t*>(smem + L::kTraceOff) : nullptr;
+  if (trc) {
+    for (int i = threadIdx.x; i < kTraceWords; i += kAttnThreads) trc[i] = 0;
+    __syncthreads();
+    if (threadIdx.x == 0) fwd_trace(trc, 0, 1, 63);  // set-up done (slot 63 of the MMA row: CTA-level stamps)
+  }
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -219,65 +304,97 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // While the softmax warps of one tile work, the pipe runs the other tile's MMAs. P(j) lives
     // in the columns of S(j); S(j+1) is issued after PV(j) and the pipe executes in issue order,
     // so the overwrite needs no barrier.
-    if (lane == 0 && nkv > 0) {
+    // The whole warp runs this loop with uniform control flow and one elected lane issues: operands of
+    // tcgen05 instructions live in uniform registers, and inside a divergent `if (lane == 0)` region
+    // every one of them would first be moved there from a vector register, which costs the issuing
+    // thread about as many cycles as a 128 x 128 x 16 MMA takes to execute.
+    if (nkv > 0) {
       constexpr uint32_t idesc_s = make_idesc_f16(kBlockQ, kBlockKV, 1, 0, 0);
       constexpr uint32_t idesc_o = make_idesc_f16(kBlockQ, D, 1, 0, 1);
-      const uint32_t q_s = smem_u32(smem + L::kQOff);
+      // descriptor words: the high words are constants, the low words are a base plus a constant per k-step
+      constexpr uint32_t hi_k = smem_desc_hi(1024);  // K-major Q / K tiles and the MN-major V tile alike
+      const uint32_t q_lo = smem_desc_lo(smem_u32(smem + L::kQOff), 16);
+      const uint32_t k_lo = smem_desc_lo(smem_u32(smem + L::kKOff), 16);
+      const uint32_t v_lo = smem_desc_lo(smem_u32(smem + L::kKOff), kBlockKV * 128);
       auto issue_s = [&](int g, int j) {
         const int slot = (2 * j) % R;
-        const uint32_t k_s = smem_u32(smem + L::kKOff + slot * L::kKBytes);
+        const uint32_t qb_lo = q_lo + g * (L::kQBytes >> 4);
+        const uint32_t kb_lo = k_lo + slot * (L::kKBytes >> 4);
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * (kBlockQ * 128) + (kk % 4) * 32;
-          umma_f16_ss(tmem_base + g * 128, make_smem_desc_sw128(q_s + g * L::kQBytes + off, 16, 1024),
-                      make_smem_desc_sw128(k_s + off, 16, 1024), idesc_s, kk != 0);
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t off = ((kk / 4) * (kBlockQ * 128) + (kk % 4) * 32) >> 4;
+            umma_f16_ss_w(tmem_base + g * 128, qb_lo + off, hi_k, kb_lo + off, hi_k, idesc_s, kk != 0);
+          }
+          umma_commit(&s_full[g]);
         }
-        umma_commit(&s_full[g]);
+        __syncwarp();
       };
-      bool ok = mbar_wait(q_full, 0, wc, 5);
-      if (ok) ok = mbar_wait(&kv_full[0], 0, wc, 3);
+      auto commit = [&](uint64_t* bar) {
+        if (elect_one()) umma_commit(bar);
+        __syncwarp();
+      };
+      bool ok = mbar_wait_warp(q_full, 0, wc, 5);
+      if (ok) ok = mbar_wait_warp(&kv_full[0], 0, wc, 3);
       if (ok) {
         tc_fence_after_sync();
 #pragma unroll
         for (int g = 0; g < kTilesQ; ++g)
           if (nkv_t[g] > 0) issue_s(g, 0);
-        umma_commit(&kv_empty[0]);
+        commit(&kv_empty[0]);
       }
       for (int j = 0; j < nkv && ok; ++j) {
         const int vslot = (2 * j + 1) % R;
         const uint32_t vph = ((2 * j + 1) / R) & 1;
         const int kslot = (2 * j + 2) % R;
         const uint32_t kph = ((2 * j + 2) / R) & 1;
-        const uint32_t v_s = smem_u32(smem + L::kKOff + vslot * L::kKBytes);
+        const uint32_t vb_lo = v_lo + vslot * (L::kKBytes >> 4);
         bool have_v = false, have_k = false;
 #pragma unroll
         for (int g = 0; g < kTilesQ; ++g) {
           if (j >= nkv_t[g]) continue;
-          if (!mbar_wait(&p_full[g], j & 1, wc, 6)) { ok = false; break; }
+          // PV starts on the first 64 keys while the softmax warps still work on the other 64
+          if (!mbar_wait_warp(&p_half[g], j & 1, wc, 6)) { ok = false; break; }
+          if (lane == 0) fwd_trace(trc, 0, g, j);
           if (!have_v) {
-            if (!mbar_wait(&kv_full[vslot], vph, wc, 7)) { ok = false; break; }
+            if (!mbar_wait_warp(&kv_full[vslot], vph, wc, 7)) { ok = false; break; }
             have_v = true;
           }
           tc_fence_after_sync();
+          if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < kBlockKV / 16; ++kk)
-            umma_f16_ts(tmem_base + 256 + g * 128, tmem_base + g * 128 + kk * 8,
-                        make_smem_desc_sw128(v_s + kk * 2048, kBlockKV * 128, 1024), idesc_o,
-                        (j | kk) != 0);
+            for (int kk = 0; kk < kBlockKV / 32; ++kk)
+              umma_f16_ts_w(tmem_base + 256 + g * 128, tmem_base + g * 128 + kk * 8, vb_lo + kk * (2048 >> 4), hi_k,
+                            idesc_o, (j | kk) != 0);
+          }
+          __syncwarp();
+          if (!mbar_wait_warp(&p_full[g], j & 1, wc, 11)) { ok = false; break; }
+          if (lane == 0) fwd_trace(trc, 0, 2 + g, j);
+          tc_fence_after_sync();
+          if (elect_one()) {
+#pragma unroll
+            for (int kk = kBlockKV / 32; kk < kBlockKV / 16; ++kk)
+              umma_f16_ts_w(tmem_base + 256 + g * 128, tmem_base + g * 128 + kk * 8, vb_lo + kk * (2048 >> 4), hi_k,
+                            idesc_o, 1);
+          }
+          __syncwarp();
           if (j + 1 < nkv_t[g]) {
             if (!have_k) {
-              if (!mbar_wait(&kv_full[kslot], kph, wc, 3)) { ok = false; break; }
+              if (!mbar_wait_warp(&kv_full[kslot], kph, wc, 3)) { ok = false; break; }
               have_k = true;
               tc_fence_after_sync();
             }
+            if (g == 0 && lane == 0) fwd_trace(trc, 0, 6, j);
             issue_s(g, j + 1);
+            if (g == 0 && lane == 0) fwd_trace(trc, 0, 7, j);
+            if (lane == 0) fwd_trace(trc, 0, 4 + g, j);
           } else {
-            umma_commit(&o_done[g]);
+            commit(&o_done[g]);
           }
         }
         if (!ok) break;
-        umma_commit(&kv_empty[vslot]);
-        if (have_k) umma_commit(&kv_empty[kslot]);
+        commit(&kv_empty[vslot]);
+        if (have_k) commit(&kv_empty[kslot]);
       }
     }
   } else {
@@ -295,6 +412,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     bool ok = true;
     for (int j = 0; j < my_nkv; ++j) {
       if (!mbar_wait_warp(&s_full[g], j & 1, wc, 8)) { ok = false; break; }
+      const bool tr = (threadIdx.x & 127) == 64;  // first thread of each tile's first softmax warp
+      if (tr) fwd_trace(trc, 1 + g, 1, j);
       tc_fence_after_sync();
       const int k0 = (j0 + j) * kBlockKV;
       const bool need_mask = (p.causal && (k0 + kBlockKV - 1 > q0 + g * kBlockQ + p.kv_offset)) ||
@@ -304,26 +423,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(t_s + c * 32, &sr[c * 32]);
       tmem_ld_wait();
-      float mx;
-      if (need_mask) mx = row_max<true>(sr, k0, lim);
-      else mx = row_max<false>(sr, k0, lim);
-      mx = fmaxf(m, mx * p.scale_log2e);
-      // The reference maximum only moves when the row maximum grew by more than a factor of two:
-      // until then P stays below 2 and O needs no rescale. (A larger slack would cost accuracy:
-      // the exponent is rounded to bf16 before ex2, which is only harmless near zero.)
+      if (tr) fwd_trace(trc, 1 + g, 2, j);
+      if (need_mask) row_mask(sr, k0, lim);
+      const float mx = fmaxf(m, row_max(sr) * p.scale_log2e);
+      // The reference maximum only moves when the row maximum grew by more than 2^4: until then
+      // P stays below 16 (harmless in bf16, whose error is relative) and O needs no rescale.
       float alpha = 1.f;
-      if (mx - m > 1.f) {
+      if (mx - m > 4.f) {
         alpha = fast_exp2(m - mx);
         m = mx;
       }
-      // P = exp2(S * scale - m) as bf16 pairs (ex2.approx.bf16x2 halves the MUFU work; the row sum
-      // adds exactly the rounded values that the MMA multiplies with V), written over the first
-      // 64 columns of S
-      float sum;
-      if (need_mask) sum = row_exp<true>(sr, k0, lim, p.scale_log2e, m);
-      else sum = row_exp<false>(sr, k0, lim, p.scale_log2e, m);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_st_32x32b_x16(t_s + c * 16, &sr[c * 16]);
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
         // every MMA issued before S(j), PV(j-1) included, completed before s_full fired
 #pragma unroll 1
@@ -337,12 +446,36 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tmem_st_32x32b_x16(t_o + c * 32 + 16, &o[16]);
         }
       }
-      l = l * alpha + sum;
+      // P = exp2(S * scale - m) as bf16 pairs written over the first 64 columns of S, in two halves
+      // of 64 keys; the row sum adds the fp32 values
+      const uint64_t sc2 = pk2(p.scale_log2e, p.scale_log2e), nm2 = pk2(-m, -m);
+      uint64_t acc0 = pk2(0.f, 0.f), acc1 = acc0;
+      if (tr) fwd_trace(trc, 1 + g, 3, j);
+      // (masked tiles stay on the special-function unit, whose exp2(-inf) is an exact zero)
+      if (need_mask) row_exp_half<0, 0>(sr, sc2, nm2, acc0, acc1);
+      else row_exp_half<0, NPOLY>(sr, sc2, nm2, acc0, acc1);
+      if (tr) fwd_trace(trc, 1 + g, 4, j);
+      tmem_st_32x32b_x16(t_s, &sr[0]);
+      tmem_st_32x32b_x16(t_s + 16, &sr[16]);
+      tmem_st_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&p_half[g]);
+      if (tr) fwd_trace(trc, 1 + g, 5, j);
+      if (need_mask) row_exp_half<1, 0>(sr, sc2, nm2, acc0, acc1);
+      else row_exp_half<1, NPOLY>(sr, sc2, nm2, acc0, acc1);
+      if (tr) fwd_trace(trc, 1 + g, 6, j);
+      tmem_st_32x32b_x16(t_s + 32, &sr[32]);
+      tmem_st_32x32b_x16(t_s + 48, &sr[48]);
+      float s0, s1;
+      upk2(add2(acc0, acc1), s0, s1);
+      l = l * alpha + (s0 + s1);
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&p_full[g]);
+      if (tr) fwd_trace(trc, 1 + g, 7, j);
     }
     if (ok && my_nkv > 0) ok = mbar_wait_warp(&o_done[g], 0, wc, 10);
+    if ((threadIdx.x & 127) == 64) fwd_trace(trc, 0, 2 + g, 63);  // last PV of the tile complete
     if (ok) {
       tc_fence_after_sync();
       const float inv = (my_nkv > 0 && l > 0.f) ? 1.f / l : 0.f;
@@ -385,8 +518,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   }
 
+  if ((threadIdx.x & 127) == 64 && warp >= 2) fwd_trace(trc, 0, 4 + ((warp - 2) >> 2), 63);  // output written
   tc_fence_before_sync();
   __syncthreads();
+  if (trc)
+    for (int i = threadIdx.x; i < kTraceWords && i < p.trace_cap; i += kAttnThreads) p.trace[i] = trc[i];
   if (*abort_w) {
     unsigned long long t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
@@ -443,11 +579,11 @@ int make_tmap_bthd(CUtensorMap* out, const void* base, int B, int T, int H, int 
   return make_tmap_bf16(out, base, 4, dims, strides, box, 1);
 }
 
-template <int D>
+template <int D, int NPOLY>
 static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                       const AttnFwdParams& p, cudaStream_t stream) {
   using L = AttnSmem<D>;
-  auto kern = flash_fwd_kernel<D>;
+  auto kern = flash_fwd_kernel<D, NPOLY>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
@@ -501,6 +637,18 @@ attn_split_merge_kernel(const __nv_bfloat16* __restrict__ part, const float* __r
 
 using namespace tpb;
 
+static int g_fwd_npoly = 0;
+static unsigned long long* g_fwd_trace = nullptr;
+static int g_fwd_trace_cap = 0;
+
+// Debug aid: buf = device array of `cap` uint64 (3 * 64 * 8 are used). The next forward launches
+// copy the cycle stamps of block (0,0,0) into it (layout at fwd_trace). Pass null to switch it off.
+extern "C" int tpb_flash_fwd_set_trace(unsigned long long* buf, int cap) {
+  g_fwd_trace = buf;
+  g_fwd_trace_cap = cap;
+  return 0;
+}
+
 // q: [B, Tq, Hq, D], k/v: [B, Tk, Hkv, D] given by (token, head, batch) strides in elements;
 // o likewise; lse: [B, Hq, lse_stride] fp32 (lse_stride >= Tq). causal aligns the last query with the last key.
 extern "C" int tpb_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
@@ -536,9 +684,26 @@ extern "C" int tpb_flash_fwd(const void* q, const void* k, const void* v, void* 
     p.blocks_per_split = (blocks + p.n_splits - 1) / p.n_splits;
   }
   p.o_split_stride = o_split_stride; p.lse_split_stride = lse_split_stride;
+  p.trace = g_fwd_trace; p.trace_cap = g_fwd_trace_cap;
   if (p.n_splits > 1 && causal) return -3;  // splitting is for decode (one query tile, no causal mask)
-  if (D == 128) return launch_fwd<128>(tq, tk, tv, p, (cudaStream_t)stream);
-  return launch_fwd<64>(tq, tk, tv, p, (cudaStream_t)stream);
+  if (D == 128) {
+    switch (g_fwd_npoly) {
+      case 2: return launch_fwd<128, 2>(tq, tk, tv, p, (cudaStream_t)stream);
+      case 1: return launch_fwd<128, 1>(tq, tk, tv, p, (cudaStream_t)stream);
+      default: return launch_fwd<128, 0>(tq, tk, tv, p, (cudaStream_t)stream);
+    }
+  }
+  // head_dim 64 halves the tensor work per score, so the exponentials dominate: more of them
+  // go to the FMA pipe
+  return launch_fwd<64, 2>(tq, tk, tv, p, (cudaStream_t)stream);
+}
+
+// Share of the exponentials that the forward computes with the polynomial on the FMA pipe instead of
+// the special-function unit, for head_dim 128: n of every 4 column pairs (0, 1 or 2).
+extern "C" int tpb_flash_fwd_config(int npoly_of_4) {
+  if (npoly_of_4 < 0 || npoly_of_4 > 2) return -2;
+  g_fwd_npoly = npoly_of_4;
+  return 0;
 }
 
 // Merge the partials of a split-KV forward (see tpb_flash_fwd): part [n_splits][B, T, H, D] bf16

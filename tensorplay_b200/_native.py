@@ -39,6 +39,7 @@ _KERNEL_SIGS = {
     "tpb_cross_entropy": [P, P, P, P, P, LL, I, LL, LL, F, P],
     "tpb_cross_entropy_bwd": [P, P, P, P, P, P, P, LL, I, LL, LL, P],
     "tpb_flash_fwd": [P, P, P, P, P, I, I, I, I, I, I] + [LL] * 12 + [I, I, F, P, P, P, I, LL, LL],
+    "tpb_flash_fwd_config": [I],
     "tpb_attn_split_merge": [P, P, P, P, I, I, I, I, I, LL, LL, I, LL, LL, LL, P],
     "tpb_flash_bwd": [P] * 10 + [I, I, I, I, I, I] + [LL] * 21 + [I, I, F, P, P],
     "tpb_grouped_workspace_ints": [I, I],
@@ -86,7 +87,7 @@ def _load(name: str):
 
 # kernel launches issued by one call of each entry point (for launch accounting)
 _LAUNCHES = {"tpb_rmsnorm_bwd": 2, "tpb_layernorm_bwd": 3, "tpb_flash_bwd": 3, "tpb_rmsnorm_bwd_grid": 0,
-             "tpb_grouped_workspace_ints": 0, "tpb_adamw_set_overlap": 0, "tpb_gemm_set_splitk_workspace": 0, "tpb_grouped_gemm": 2}
+             "tpb_grouped_workspace_ints": 0, "tpb_adamw_set_overlap": 0, "tpb_flash_fwd_config": 0, "tpb_gemm_set_splitk_workspace": 0, "tpb_grouped_gemm": 2}
 launch_count = 0
 
 
