@@ -248,72 +248,78 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0 && n_it > 0) {
+    // The whole warp runs the loop with uniform control flow and an elected lane issues: tcgen05
+    // operands live in uniform registers, and a divergent `if (lane == 0)` region would move every
+    // one of them there per instruction, which costs more than a 128 x 64 x 16 MMA takes to run.
+    if (n_it > 0) {
       constexpr uint32_t idesc_s = make_idesc_f16(kStat, kStream, 1, 0, 0);
       constexpr uint32_t idesc_acc = make_idesc_f16(kStat, D, 1, 0, 1);
-      const uint32_t x0_s = smem_u32(smem + L::kX0);
-      const uint32_t x1_s = smem_u32(smem + L::kX1);
+      constexpr uint32_t hi = smem_desc_hi(1024);
+      const uint32_t x0_lo = smem_desc_lo(smem_u32(smem + L::kX0), 16);
+      const uint32_t x1_lo = smem_desc_lo(smem_u32(smem + L::kX1), 16);
+      const uint32_t yk_lo = smem_desc_lo(smem_u32(smem + L::kY), 16);               // streamed tiles, K-major view
+      const uint32_t ym_lo = smem_desc_lo(smem_u32(smem + L::kY), kStream * 128);    // the same tiles, MN-major view
       auto issue_sdp = [&](int it) -> bool {
         const int ys = it % kYStages;
         const uint32_t yph = (it / kYStages) & 1;
         const int s = it & 1;
-        if (!mbar_wait(&y_full[ys], yph, wc, 2)) return false;
-        trace_pt(p, 1, it, 1);
+        if (!mbar_wait_warp(&y_full[ys], yph, wc, 2)) return false;
+        if (lane == 0) trace_pt(p, 1, it, 1);
         // Slot s last held iteration it - 2: its S / dP were read by the P/dS warps before they
         // arrived on pds_full(it - 2), and its P / dS (same columns) are consumed by MMAs issued
-        // earlier by this thread, which the tensor pipe executes in order before these.
+        // earlier by this warp, which the tensor pipe executes in order before these.
         tc_fence_after_sync();
-        const uint32_t y0_s = smem_u32(smem + L::kY + ys * 2 * L::kStreamBytes);
-        const uint32_t y1_s = y0_s + L::kStreamBytes;
+        const uint32_t y0_lo = yk_lo + ys * ((2 * L::kStreamBytes) >> 4);
+        const uint32_t y1_lo = y0_lo + (L::kStreamBytes >> 4);
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t xo = (kk / 4) * (kStat * 128) + (kk % 4) * 32;
-          const uint32_t yo = (kk / 4) * (kStream * 128) + (kk % 4) * 32;
-          umma_f16_ss(tmem_base + s * 128, make_smem_desc_sw128(x0_s + xo, 16, 1024),
-                      make_smem_desc_sw128(y0_s + yo, 16, 1024), idesc_s, kk != 0);
-        }
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t xo = ((kk / 4) * (kStat * 128) + (kk % 4) * 32) >> 4;
+            const uint32_t yo = ((kk / 4) * (kStream * 128) + (kk % 4) * 32) >> 4;
+            umma_f16_ss_w(tmem_base + s * 128, x0_lo + xo, hi, y0_lo + yo, hi, idesc_s, kk != 0);
+          }
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t xo = (kk / 4) * (kStat * 128) + (kk % 4) * 32;
-          const uint32_t yo = (kk / 4) * (kStream * 128) + (kk % 4) * 32;
-          umma_f16_ss(tmem_base + s * 128 + 64, make_smem_desc_sw128(x1_s + xo, 16, 1024),
-                      make_smem_desc_sw128(y1_s + yo, 16, 1024), idesc_s, kk != 0);
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t xo = ((kk / 4) * (kStat * 128) + (kk % 4) * 32) >> 4;
+            const uint32_t yo = ((kk / 4) * (kStream * 128) + (kk % 4) * 32) >> 4;
+            umma_f16_ss_w(tmem_base + s * 128 + 64, x1_lo + xo, hi, y1_lo + yo, hi, idesc_s, kk != 0);
+          }
+          umma_commit(&sdp_full[s]);
         }
-        umma_commit(&sdp_full[s]);
+        __syncwarp();
         return true;
       };
-      bool ok = mbar_wait(x_full, 0, wc, 4);
+      bool ok = mbar_wait_warp(x_full, 0, wc, 4);
       if (ok) ok = issue_sdp(0);
       for (int it = 0; it < n_it && ok; ++it) {
         if (it + 1 < n_it) {
           if (!issue_sdp(it + 1)) break;
         }
         const int s = it % kYStages;
-        if (!mbar_wait(pds_full, it & 1, wc, 5)) break;
-        trace_pt(p, 1, it, 3);
+        if (!mbar_wait_warp(pds_full, it & 1, wc, 5)) break;
+        if (lane == 0) trace_pt(p, 1, it, 3);
         tc_fence_after_sync();
-        const uint32_t y0_s = smem_u32(smem + L::kY + s * 2 * L::kStreamBytes);
-        const uint32_t y1_s = y0_s + L::kStreamBytes;
+        const uint32_t y0_lo = ym_lo + s * ((2 * L::kStreamBytes) >> 4);
+        const uint32_t y1_lo = y0_lo + (L::kStreamBytes >> 4);
         // P and dS are the A operands straight from TMEM: bf16 pairs written over the S / dP
         // columns; k-step kk (16 streamed rows) sits at column (kk / 2) * 32 + (kk % 2) * 8
         const uint32_t t_p = tmem_base + (it & 1) * 128;
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < kStream / 16; ++kk) {
-          const uint32_t a_col = (kk >> 1) * 32 + (kk & 1) * 8;
-          // acc1 += dS * Y0  (dK += dS^T Q  or  dQ += dS K)
-          umma_f16_ts(tmem_acc1, t_p + 64 + a_col,
-                      make_smem_desc_sw128(y0_s + kk * 2048, kStream * 128, 1024), idesc_acc,
-                      (it | kk) != 0);
-          if (DKV) {
-            // acc0 += P^T * dO
-            umma_f16_ts(tmem_acc0, t_p + a_col,
-                        make_smem_desc_sw128(y1_s + kk * 2048, kStream * 128, 1024), idesc_acc,
-                        (it | kk) != 0);
+          for (int kk = 0; kk < kStream / 16; ++kk) {
+            const uint32_t a_col = (kk >> 1) * 32 + (kk & 1) * 8;
+            // acc1 += dS * Y0  (dK += dS^T Q  or  dQ += dS K)
+            umma_f16_ts_w(tmem_acc1, t_p + 64 + a_col, y0_lo + kk * (2048 >> 4), hi, idesc_acc, (it | kk) != 0);
+            if (DKV) {
+              // acc0 += P^T * dO
+              umma_f16_ts_w(tmem_acc0, t_p + a_col, y1_lo + kk * (2048 >> 4), hi, idesc_acc, (it | kk) != 0);
+            }
           }
+          umma_commit(&y_empty[s]);
+          if (it == n_it - 1) umma_commit(acc_done);
         }
-        umma_commit(&y_empty[s]);
-        if (it == n_it - 1) umma_commit(acc_done);
-        trace_pt(p, 1, it, 4);
+        __syncwarp();
+        if (lane == 0) trace_pt(p, 1, it, 4);
       }
     }
   } else {

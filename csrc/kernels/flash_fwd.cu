@@ -637,7 +637,7 @@ attn_split_merge_kernel(const __nv_bfloat16* __restrict__ part, const float* __r
 
 using namespace tpb;
 
-static int g_fwd_npoly = 0;
+static int g_fwd_npoly = 1;
 static unsigned long long* g_fwd_trace = nullptr;
 static int g_fwd_trace_cap = 0;
 
