@@ -50,20 +50,25 @@ struct GroupedParams {
   unsigned long long wait_ns;
 };
 
-// One thread: tile table for mode 0 (M tiles of every expert, expert-major).
-__global__ void grouped_prep_kernel(const int* __restrict__ offs, int G, int* __restrict__ tile_expert,
-                                    int* __restrict__ tile_row, int* __restrict__ n_mtiles,
-                                    int max_tiles) {
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
-  int n = 0;
-  for (int e = 0; e < G; ++e) {
-    for (int r = offs[e]; r < offs[e + 1] && n < max_tiles; r += kGBlockM) {
+// Tile table for mode 0 (M tiles of every expert, expert-major), one thread per expert: expert e
+// owns tiles [ceil(offs[e] / 128) ...) of its own row range, and because every offset is a multiple
+// of 128 the experts' tile ranges are disjoint and their positions follow from the offsets alone.
+__global__ void __launch_bounds__(256)
+grouped_prep_kernel(const int* __restrict__ offs, int G, int* __restrict__ tile_expert,
+                    int* __restrict__ tile_row, int* __restrict__ n_mtiles, int max_tiles) {
+  const int base = offs[0];
+  for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < G; e += gridDim.x * blockDim.x) {
+    const int r0 = offs[e], r1 = offs[e + 1];
+    int n = (r0 - base) / kGBlockM;
+    for (int r = r0; r < r1 && n < max_tiles; r += kGBlockM, ++n) {
       tile_expert[n] = e;
       tile_row[n] = r;
-      ++n;
+    }
+    if (e == G - 1) {
+      const int total = (r1 - base) / kGBlockM;
+      *n_mtiles = total < max_tiles ? total : max_tiles;
     }
   }
-  *n_mtiles = n;
 }
 
 template <int BLOCK_N, bool B_MN>
@@ -355,7 +360,7 @@ extern "C" int tpb_grouped_gemm(const void* A, const void* B, void* C, const int
   CUtensorMap ta, tb;
   int r;
   if (mode == 0) {
-    grouped_prep_kernel<<<1, 32, 0, stream>>>(offs, G, tile_expert, tile_row, n_mtiles, max_tiles);
+    grouped_prep_kernel<<<(G + 255) / 256, 256, 0, stream>>>(offs, G, tile_expert, tile_row, n_mtiles, max_tiles);
     p.ldc = N; p.c_expert_stride = 0;
     const int block_n = N > 128 ? 256 : 128;
     if ((r = make_tmap_2d_bf16(&ta, A, K, max_rows, K, kGBlockM))) return r;

@@ -47,9 +47,10 @@ __device__ __forceinline__ uint4 moe_ld_peer(const void* ptr) {
 //   topk_idx [n_assign] int32 expert ids (n_assign = tokens * k)
 //   counts_tbl: symmetric [world, E] int32; row s is written by rank s on every rank
 //   outputs: dst_rank[n_assign], dst_row[n_assign] (row -1 = dropped),
-//            offs_local[E_local + 1] padded expert offsets of THIS rank's buffer,
+//            offs_local[E_local + 1] padded expert offsets of THIS rank's buffer, followed by
+//            E_local entries: the first padding row of each local expert's segment (the rows from
+//            there to the next offset hold no token; moe_zero_pad_kernel clears them),
 //            recv_rows (device scalar) = rows in use on this rank (padded).
-//   zero_buf/zero_row_bytes: this rank's expert input buffer; its padding rows are zeroed here.
 __global__ void __launch_bounds__(1024)
 moe_route_kernel(const int* __restrict__ topk_idx, int n_assign, int E, int E_local,
                  int* const* counts_tbl_peer /* [world] pointers to each rank's table */,
@@ -85,6 +86,8 @@ moe_route_kernel(const int* __restrict__ topk_idx, int n_assign, int E, int E_lo
   __syncthreads();
   if (!ok_sh) {
     for (int a = tid; a < n_assign; a += blockDim.x) { dst_row[a] = -1; dst_rank[a] = 0; }
+    for (int j = tid; j < 2 * E_local + 1; j += blockDim.x) offs_local[j] = 0;
+    if (tid == 0) *recv_rows = 0;
     return;
   }
   // per expert: total over ranks and my sub-offset inside the segment
@@ -118,7 +121,7 @@ moe_route_kernel(const int* __restrict__ topk_idx, int n_assign, int E, int E_lo
   if (overflow_sh) {
     if (tid == 0 && s.status) atomicCAS(s.status, 0u, kStatusBadArgs | (31u << 8));
     for (int a = tid; a < n_assign; a += blockDim.x) { dst_row[a] = -1; dst_rank[a] = 0; }
-    if (tid < E_local + 1) offs_local[tid] = 0;
+    for (int j = tid; j < 2 * E_local + 1; j += blockDim.x) offs_local[j] = 0;
     if (tid == 0) *recv_rows = 0;
     return;
   }
@@ -133,17 +136,21 @@ moe_route_kernel(const int* __restrict__ topk_idx, int n_assign, int E, int E_lo
       dst_row[a] = -1;
     }
   }
-  // zero the padding rows of my own expert buffer (nobody writes them)
-  if (zero_buf) {
-    for (int j = 0; j < E_local; ++j) {
-      const int e = s.rank * E_local + j;
-      const int r0 = offs_local[j] + seg_total[e];
-      const int r1 = offs_local[j + 1];
-      const long long nvec = (long long)(r1 - r0) * zero_row_bytes / 16;
-      uint4* z = reinterpret_cast<uint4*>(zero_buf + (long long)r0 * zero_row_bytes);
-      for (long long i = tid; i < nvec; i += blockDim.x) z[i] = make_uint4(0, 0, 0, 0);
-    }
-  }
+  // first padding row of each of my expert segments (nobody writes those rows)
+  for (int j = tid; j < E_local; j += blockDim.x)
+    offs_local[E_local + 1 + j] = offs_local[j] + seg_total[s.rank * E_local + j];
+}
+
+// Clears the padding rows of this rank's expert buffer: CTA (j, c) takes a share of expert j's rows
+// [pad_begin[j], offs[j + 1]) (at most 127 rows).
+__global__ void __launch_bounds__(256)
+moe_zero_pad_kernel(const int* __restrict__ offs, int E_local, char* __restrict__ buf, int row_bytes) {
+  const int j = blockIdx.x;
+  const int r0 = offs[E_local + 1 + j], r1 = offs[j + 1];
+  const long long nvec = (long long)max(r1 - r0, 0) * row_bytes / 16;
+  uint4* z = reinterpret_cast<uint4*>(buf + (long long)r0 * row_bytes);
+  for (long long i = (long long)blockIdx.y * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.y * blockDim.x)
+    z[i] = make_uint4(0, 0, 0, 0);
 }
 
 struct MoePeerBufs {
@@ -196,6 +203,7 @@ moe_dispatch_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride, int
 // Warp per token: out[t] = sum_k w[t,k] * buf[dst_rank][dst_row] ; w == null means weight 1.
 // dots (optional, [tokens * k]): <g[t], row> for the gate-weight gradient (g given instead of out
 // accumulation when dots_only).
+template <int KB>  // rows of a token requested together: min(8, k rounded up to a power of two)
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(MoePeerBufs bufs, const int* __restrict__ dst_rank, const int* __restrict__ dst_row,
                    const float* __restrict__ w, int k, int tokens, int H,
@@ -216,22 +224,35 @@ moe_combine_kernel(MoePeerBufs bufs, const int* __restrict__ dst_rank, const int
   const int nvec = H / 8;
   for (long long t = (long long)blockIdx.x * wpb + (threadIdx.x >> 5); t < tokens;
        t += (long long)gridDim.x * wpb) {
+    // lane kk holds the source row of assignment kk (k0 + kk for k > 32); the k rows of a token are
+    // requested together, KB at a time: one NVLink round trip per group instead of one per row
     for (int v0 = lane; v0 < nvec; v0 += 32) {
       float acc[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-      for (int kk = 0; kk < k; ++kk) {
-        const long long a = t * k + kk;
-        const int row = dst_row[a];
-        if (row < 0) continue;
-        uint4 u = moe_ld_peer(reinterpret_cast<const uint4*>(bufs.p[dst_rank[a]] + (long long)row * H * 2) + v0);
-        const float wk = w ? w[a] : 1.f;
-        const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&u);
+      for (int k0 = 0; k0 < k; k0 += KB) {
+        uint4 u[KB];
+        float wk[KB];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float2 f = __bfloat1622float2(hb[j]);
-          acc[2 * j] += wk * f.x;
-          acc[2 * j + 1] += wk * f.y;
+        for (int kk = 0; kk < KB; ++kk) {
+          const long long a = t * k + k0 + kk;
+          const int row = (k0 + kk < k) ? dst_row[a] : -1;
+          wk[kk] = 0.f;
+          u[kk] = make_uint4(0, 0, 0, 0);
+          if (row >= 0) {
+            u[kk] = moe_ld_peer(reinterpret_cast<const uint4*>(bufs.p[dst_rank[a]] + (long long)row * H * 2) + v0);
+            wk[kk] = w ? w[a] : 1.f;
+          }
+        }
+#pragma unroll
+        for (int kk = 0; kk < KB; ++kk) {
+          const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&u[kk]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float2 f = __bfloat1622float2(hb[j]);
+            acc[2 * j] += wk[kk] * f.x;
+            acc[2 * j + 1] += wk[kk] * f.y;
+          }
         }
       }
       if (out) {
@@ -296,7 +317,8 @@ static MoeSync make_moe_sync(const SymmView* sv, size_t pad_off, uint32_t epoch,
 using namespace tpb;
 
 // counts_off: arena offset of the [world, E] int32 table; xbuf_off: arena offset of this rank's
-// expert input buffer (its padding rows get zeroed), or (size_t)-1.
+// expert input buffer (its padding rows get zeroed by a second, multi-CTA launch), or (size_t)-1.
+// offs_local: 2 * E_local + 1 ints (see moe_route_kernel).
 // peer_tbl_dev: device array of `world` pointers (filled by the caller once) to each rank's table.
 extern "C" int tpb_moe_route(const int* topk_idx, int n_assign, int E, int* const* peer_tbl_dev,
                              size_t counts_off, int* dst_rank, int* dst_row, int* offs_local,
@@ -311,6 +333,7 @@ extern "C" int tpb_moe_route(const int* topk_idx, int n_assign, int E, int* cons
       topk_idx, n_assign, E, E / sv->world, peer_tbl_dev,
       reinterpret_cast<int*>(sv->peer[sv->rank] + counts_off), dst_rank, dst_row, offs_local,
       recv_rows, zb, row_bytes, cap_rows, s, ready_slot);
+  if (zb) moe_zero_pad_kernel<<<dim3(E / sv->world, 4), 256, 0, (cudaStream_t)stream>>>(offs_local, E / sv->world, zb, row_bytes);
   return (int)cudaGetLastError();
 }
 
@@ -352,7 +375,9 @@ extern "C" int tpb_moe_combine(size_t buf_off, const int* dst_rank, const int* d
   for (int r = 0; r < sv->world; ++r) b.p[r] = sv->peer[r] + buf_off;
   MoeSync s = make_moe_sync(sv, pad_off, epoch, status, wait_s);
   int grid = ctas > 0 ? ctas : 4 * sm_count();
-  moe_combine_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
+  auto kern = k <= 1 ? moe_combine_kernel<1> : k <= 2 ? moe_combine_kernel<2> : k <= 4 ? moe_combine_kernel<4>
+                                                                                     : moe_combine_kernel<8>;
+  kern<<<grid, 256, 0, (cudaStream_t)stream>>>(
       b, dst_rank, dst_row, w, k, tokens, H, (__nv_bfloat16*)out, out_stride,
       (const __nv_bfloat16*)g, g_stride, dots, s, ready_slot);
   return (int)cudaGetLastError();

@@ -105,8 +105,13 @@ class MoEWorkspace:
             raw._moe_sigs = True
         self.raw = raw
         dev = a.device
-        self.xbuf = a.alloc(self.cap * hidden, torch.bfloat16).view(self.cap, hidden)   # expert inputs / dy rows
+        self.xbuf = a.alloc(self.cap * hidden, torch.bfloat16).view(self.cap, hidden)   # expert inputs
         self.ybuf = a.alloc(self.cap * hidden, torch.bfloat16).view(self.cap, hidden)   # expert outputs / dx rows
+        self.dbuf = a.alloc(self.cap * hidden, torch.bfloat16).view(self.cap, hidden)   # dy rows (backward)
+        # Which forward's rows xbuf / ybuf hold. A backward that finds its own forward's number here
+        # (the forward ran immediately before it, as under per-layer activation recomputation) reuses
+        # the dispatched inputs and the expert outputs instead of routing and computing them again.
+        self.generation = 0
         self.counts = a.alloc(self.world * num_experts, torch.int32)
         self.counts_off = a.offset_of(self.counts)
         ptrs = (C.c_void_p * self.world)()
@@ -127,14 +132,15 @@ class MoEWorkspace:
         dev = topk_idx.device
         dst_rank = torch.empty(n, dtype=torch.int32, device=dev)
         dst_row = torch.empty(n, dtype=torch.int32, device=dev)
-        offs = torch.empty(self.El + 1, dtype=torch.int32, device=dev)
+        offs2 = torch.empty(2 * self.El + 1, dtype=torch.int32, device=dev)  # offsets, then first padding rows
+        offs = offs2[: self.El + 1]
         rows = torch.empty(1, dtype=torch.int32, device=dev)
         idx = topk_idx.reshape(-1).to(torch.int32).contiguous()
         code = self.raw.tpb_moe_route(idx.data_ptr(), n, self.E, self.peer_tbl.data_ptr(), self.counts_off,
-                                      dst_rank.data_ptr(), dst_row.data_ptr(), offs.data_ptr(), rows.data_ptr(),
+                                      dst_rank.data_ptr(), dst_row.data_ptr(), offs2.data_ptr(), rows.data_ptr(),
                                       self.arena.offset_of(self.xbuf), self.H * 2, self.cap, self.arena.pad_off,
                                       self.slot_route, self.epoch, self.wait_s, self.status.data_ptr(), stream_ptr())
-        _native.launch_count += 1
+        _native.launch_count += 2
         _native.check(code, "tpb_moe_route")
         self.last_recv_rows = rows  # device scalar: padded rows this rank received (load statistic)
         return dst_rank, dst_row, offs
@@ -177,7 +183,6 @@ class _EPFFNFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, topk_idx, topk_w, w_gate_up, w_down, ws: MoEWorkspace):
         T, H = x.shape
-        I = w_down.shape[2]
         dst_rank, dst_row, offs = ws.route(topk_idx)
         ws.dispatch(x, dst_rank, dst_row, ws.xbuf)
         gu = grouped_gemm(ws.xbuf, w_gate_up, offs, workspace=ws.gws)                      # [cap, 2I]
@@ -185,32 +190,47 @@ class _EPFFNFn(torch.autograd.Function):
         grouped_gemm(act, w_down, offs, out=ws.ybuf, workspace=ws.gws)                      # [cap, H]
         wf = topk_w.reshape(-1).float().contiguous()
         y, _ = ws.combine(ws.ybuf, dst_rank, dst_row, w=wf, tokens=T)
-        ctx.save_for_backward(x, topk_idx, wf, w_gate_up, w_down)
+        ws.generation += 1
+        ctx.gen = ws.generation
         ctx.ws = ws
         ctx.refs = (w_gate_up if hasattr(w_gate_up, "_tpb_grad_view") else None,
                     w_down if hasattr(w_down, "_tpb_grad_view") else None)
+        if any(ctx.needs_input_grad):
+            # a graph is being recorded: keep the routing and the expert activations for the backward
+            ctx.save_for_backward(x, topk_idx, wf, w_gate_up, w_down, dst_rank, dst_row, offs, gu, act)
+        else:
+            ctx.save_for_backward(x, topk_idx, wf, w_gate_up, w_down)
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        x, topk_idx, wf, w_gate_up, w_down = ctx.saved_tensors
+        saved = ctx.saved_tensors
+        x, topk_idx, wf, w_gate_up, w_down = saved[:5]
         ws = ctx.ws
         T, H = x.shape
         dy = dy.contiguous()
-        # The buffers are shared between layers: route again (also re-zeroes the padding rows;
-        # the row assignment only has to be consistent within this backward) and recompute the
-        # expert activations.
-        dst_rank, dst_row, offs = ws.route(topk_idx)
-        ws.dispatch(x, dst_rank, dst_row, ws.xbuf)
-        xin = ws.xbuf.clone()
-        gu = grouped_gemm(xin, w_gate_up, offs, workspace=ws.gws)
-        act = ops.swiglu_packed(gu.detach())
-        grouped_gemm(act, w_down, offs, out=ws.ybuf, workspace=ws.gws)
+        if len(saved) > 5 and ws.generation == ctx.gen:
+            # no other forward used the workspace since: xbuf still holds this call's dispatched
+            # rows and ybuf its expert outputs
+            dst_rank, dst_row, offs, gu, act = saved[5:]
+            xin = ws.xbuf
+        else:
+            # The buffers are shared between layers: route again (the row assignment only has to be
+            # consistent within this backward) and recompute the expert activations.
+            dst_rank, dst_row, offs = ws.route(topk_idx)
+            ws.dispatch(x, dst_rank, dst_row, ws.xbuf)
+            xin = ws.xbuf
+            gu = grouped_gemm(xin, w_gate_up, offs, workspace=ws.gws)
+            act = ops.swiglu_packed(gu.detach())
+            grouped_gemm(act, w_down, offs, out=ws.ybuf, workspace=ws.gws)
+        ws.generation += 1  # ybuf is overwritten below
         # gate-weight gradient: <dy[t], y_row>
         _, dots = ws.combine(ws.ybuf, dst_rank, dst_row, tokens=T, g=dy, want_out=False)
-        # dy rows, scaled by the gate weights, to the expert owners
-        ws.dispatch(dy, dst_rank, dst_row, ws.xbuf, scale=wf)
-        dyr = ws.xbuf
+        # dy rows, scaled by the gate weights, to the expert owners (padding rows of dbuf may hold
+        # anything: they meet zero rows of xin / act in the weight gradients and their own output
+        # rows are never pulled)
+        ws.dispatch(dy, dst_rank, dst_row, ws.dbuf, scale=wf)
+        dyr = ws.dbuf
         dact = grouped_gemm(dyr, w_down, offs, b_mn=True, workspace=ws.gws)                # [cap, I]
         dwd = _wgrad(dyr, act, offs, ctx.refs[1], ws)
         # swiglu backward through the saved pre-activation
