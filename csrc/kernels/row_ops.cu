@@ -445,9 +445,10 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restri
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gate,
                                   const __nv_bfloat16* __restrict__ up,
                                   __nv_bfloat16* __restrict__ out, long long rows, int I,
-                                  long long in_stride) {
+                                  long long in_stride, const int* __restrict__ rows_dev) {
   const int nvec = I / 8;
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (rows_dev) rows = min(rows, (long long)*rows_dev);  // row count known only on the device (ragged buffers)
   if (idx >= rows * nvec) return;
   long long r = idx / nvec;
   int v = idx % nvec;
@@ -463,9 +464,10 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
                                   const __nv_bfloat16* __restrict__ up,
                                   __nv_bfloat16* __restrict__ dgate, __nv_bfloat16* __restrict__ dup,
                                   long long rows, int I, long long in_stride,
-                                  long long out_stride) {
+                                  long long out_stride, const int* __restrict__ rows_dev) {
   const int nvec = I / 8;
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (rows_dev) rows = min(rows, (long long)*rows_dev);
   if (idx >= rows * nvec) return;
   long long r = idx / nvec;
   int v = idx % nvec;
@@ -771,26 +773,38 @@ extern "C" int tpb_rope(void* x, const float* cos_t, const float* sin_t, const l
   return (int)cudaGetLastError();
 }
 
-extern "C" int tpb_swiglu_fwd(const void* gate, const void* up, void* out, long long rows, int I,
-                              long long in_stride, void* stream) {
+// rows_dev (optional): device word with the number of rows actually in use (<= rows); rows beyond it
+// are neither read nor written (expert buffers are sized for the worst case, filled to a
+// data-dependent row).
+extern "C" int tpb_swiglu_fwd_n(const void* gate, const void* up, void* out, long long rows, int I,
+                                long long in_stride, const int* rows_dev, void* stream) {
   if (I % 8 || in_stride % 8) return -2;
   long long total = rows * (I / 8);
   if (total <= 0) return 0;
   swiglu_fwd_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, (__nv_bfloat16*)out, rows, I,
-      in_stride);
+      in_stride, rows_dev);
   return (int)cudaGetLastError();
 }
-extern "C" int tpb_swiglu_bwd(const void* dy, const void* gate, const void* up, void* dgate,
-                              void* dup, long long rows, int I, long long in_stride,
-                              long long out_stride, void* stream) {
+extern "C" int tpb_swiglu_fwd(const void* gate, const void* up, void* out, long long rows, int I,
+                              long long in_stride, void* stream) {
+  return tpb_swiglu_fwd_n(gate, up, out, rows, I, in_stride, nullptr, stream);
+}
+extern "C" int tpb_swiglu_bwd_n(const void* dy, const void* gate, const void* up, void* dgate,
+                                void* dup, long long rows, int I, long long in_stride,
+                                long long out_stride, const int* rows_dev, void* stream) {
   if (I % 8 || in_stride % 8 || out_stride % 8) return -2;
   long long total = rows * (I / 8);
   if (total <= 0) return 0;
   swiglu_bwd_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)dy, (const __nv_bfloat16*)gate, (const __nv_bfloat16*)up,
-      (__nv_bfloat16*)dgate, (__nv_bfloat16*)dup, rows, I, in_stride, out_stride);
+      (__nv_bfloat16*)dgate, (__nv_bfloat16*)dup, rows, I, in_stride, out_stride, rows_dev);
   return (int)cudaGetLastError();
+}
+extern "C" int tpb_swiglu_bwd(const void* dy, const void* gate, const void* up, void* dgate,
+                              void* dup, long long rows, int I, long long in_stride,
+                              long long out_stride, void* stream) {
+  return tpb_swiglu_bwd_n(dy, gate, up, dgate, dup, rows, I, in_stride, out_stride, nullptr, stream);
 }
 extern "C" int tpb_gelu_fwd(const void* x, void* y, long long n, int approx, void* stream) {
   if (n % 8) return -2;

@@ -26,10 +26,27 @@ struct SymmState {
   int world = 0, rank = 0;
   char* base = nullptr;           // local arena
   char* peer[kMaxRanks] = {};     // mapped arenas (peer[rank] == base)
+  char* mc_base = nullptr;        // multicast mapping of all arenas (virtual-memory allocator only), or null
   size_t bytes = 0, used = 0;
   bool opened = false;
+  bool vmm = false;               // arenas come from symm_vmm.cu (cuMemCreate), not cudaMalloc + IPC
 };
 static SymmState g_symm;
+
+// Called by the virtual-memory allocator (symm_vmm.cu) once all arenas are mapped; world == 0 clears.
+void symm_adopt(int world, int rank, char* const* peers, size_t bytes, char* mc_base) {
+  g_symm = SymmState();
+  if (world <= 0) return;
+  g_symm.world = world;
+  g_symm.rank = rank;
+  for (int r = 0; r < world; ++r) g_symm.peer[r] = peers[r];
+  g_symm.base = peers[rank];
+  g_symm.bytes = bytes;
+  g_symm.mc_base = mc_base;
+  g_symm.opened = true;
+  g_symm.vmm = true;
+}
+void symm_set_mc_base(char* mc_base) { g_symm.mc_base = mc_base; }
 
 const SymmView* symm_view() {
   static SymmView v;
@@ -59,6 +76,23 @@ __device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
                : "l"(p)
                : "memory");
   return v;
+}
+
+// Loads 8 bf16 from the same address of every rank's arena and returns their sum (added inside the
+// switch with fp32 accumulation, rounded once to bf16): `p` is a multicast address.
+__device__ __forceinline__ uint4 mc_ld_reduce_bf16x8(const void* p) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+// Stores 16 bytes to the same address of every rank's arena (`p` is a multicast address).
+__device__ __forceinline__ void mc_st_v4(void* p, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
 }
 
 // Cross-rank rendezvous at kernel start. Thread 0 of block 0 publishes `epoch` into slot
@@ -118,6 +152,41 @@ allgather_pull_kernel(PeerPtrs shards, char* __restrict__ out, size_t shard_byte
   for (; i < nvec; i += stride) dst[i] = ld_relaxed_sys_v4(src + i);
 }
 
+// ---------------------------------------------------------------- all-gather (multicast push)
+// Every rank stores its shard once through the multicast mapping; the switch delivers it into the
+// `out` buffer of every rank (own included) at [rank * shard_bytes, ...). The rendezvous at the
+// start says "my destination buffer is free and my shard is valid"; after the last block every
+// rank is told that this rank's shard has landed (done_slot), which the consumer waits for.
+__global__ void __launch_bounds__(512)
+allgather_mc_kernel(const char* __restrict__ shard, char* __restrict__ mc_out, size_t shard_bytes, SyncArgs s,
+                    int ready_slot, int done_slot, uint32_t* block_counter) {
+  if (!rendezvous(s, ready_slot, 25)) return;
+  const size_t nvec = shard_bytes / 16;
+  const uint4* src = reinterpret_cast<const uint4*>(shard);
+  uint4* dst = reinterpret_cast<uint4*>(mc_out);
+  constexpr int kUnroll = 4;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + (kUnroll - 1) * stride < nvec; i += kUnroll * stride) {
+    uint4 v[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) v[u] = src[i + u * stride];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) mc_st_v4(dst + i + u * stride, v[u]);
+  }
+  for (; i < nvec; i += stride) mc_st_v4(dst + i, src[i]);
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned prev = atomicAdd(block_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *block_counter = 0;
+      __threadfence_system();
+      for (int r = 0; r < s.world; ++r) st_release_sys(s.pad_peer[r] + done_slot + s.rank, s.epoch);
+    }
+  }
+}
+
 // ---------------------------------------------------------------- reduce-scatter + AdamW
 struct AdamArgs {
   float lr, beta1, beta2, eps, weight_decay, bias_c1, bias_c2, grad_scale;
@@ -142,7 +211,8 @@ rs_adamw_kernel(PeerPtrs grads, size_t lo, size_t n, float* __restrict__ master,
                 float* __restrict__ m, float* __restrict__ v, __nv_bfloat16* __restrict__ shard_out,
                 PeerPtrs bcast_out, size_t bcast_off, int do_bcast, float* __restrict__ red_out,
                 float* __restrict__ sumsq, int mode, AdamArgs h, const float* clip_coef, SyncArgs s,
-                int ready_slot, int done_slot, uint32_t* block_counter, int local_only) {
+                int ready_slot, int done_slot, uint32_t* block_counter, int local_only,
+                const char* __restrict__ mc_grads, char* __restrict__ mc_bcast) {
   // local_only: every gradient copy already sits in this GPU's memory (the copy engines pulled the
   // peers' slices and the hand-shakes ran as separate one-CTA kernels): no flags are touched here
   if (!local_only && !rendezvous(s, ready_slot, 21)) return;
@@ -157,8 +227,20 @@ rs_adamw_kernel(PeerPtrs grads, size_t lo, size_t n, float* __restrict__ master,
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    if (mc_grads) {
+      // one load, reduced over all ranks inside the switch: this rank receives its slice once instead
+      // of once per peer
+      const uint4 raw = mc_ld_reduce_bf16x8(reinterpret_cast<const uint4*>(mc_grads) + lo / 8 + i);
+      const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __bfloat1622float2(hb[j]);
+        acc[2 * j] = f.x;
+        acc[2 * j + 1] = f.y;
+      }
+    }
     // loads of up to eight ranks are issued together, then summed in rank order (deterministic)
-    for (int r0 = 0; r0 < s.world; r0 += 8) {
+    for (int r0 = 0; !mc_grads && r0 < s.world; r0 += 8) {
       uint4 raw[8];
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
@@ -189,6 +271,10 @@ rs_adamw_kernel(PeerPtrs grads, size_t lo, size_t n, float* __restrict__ master,
       __nv_bfloat162* ob2 = reinterpret_cast<__nv_bfloat162*>(&o2);
 #pragma unroll
       for (int j = 0; j < 4; ++j) ob2[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+      if (mc_bcast) {
+        mc_st_v4(reinterpret_cast<uint4*>(mc_bcast + bcast_off) + lo / 8 + i, o2);  // one store reaches every rank
+        continue;
+      }
       for (int r = 0; r < s.world; ++r) {
         int rr = (s.rank + r) % s.world;
         uint4* dst = reinterpret_cast<uint4*>(const_cast<char*>(bcast_out.p[rr]) + bcast_off) + lo / 8 + i;
@@ -227,7 +313,9 @@ rs_adamw_kernel(PeerPtrs grads, size_t lo, size_t n, float* __restrict__ master,
 #pragma unroll
     for (int j = 0; j < 4; ++j) ob[j] = __floats2bfloat162_rn(pw[2 * j], pw[2 * j + 1]);
     if (shard_out) reinterpret_cast<uint4*>(shard_out)[i] = o;
-    if (do_bcast) {
+    if (do_bcast && mc_bcast) {
+      mc_st_v4(reinterpret_cast<uint4*>(mc_bcast + bcast_off) + lo / 8 + i, o);
+    } else if (do_bcast) {
       for (int r = 0; r < s.world; ++r) {
         int rr = (s.rank + r) % s.world;
         uint4* dst = reinterpret_cast<uint4*>(const_cast<char*>(bcast_out.p[rr]) + bcast_off) + lo / 8 + i;
@@ -349,8 +437,10 @@ extern "C" int tpb_symm_open(const void* handles) {
   return 0;
 }
 
+extern "C" int tpb_symm_vmm_destroy();
 extern "C" int tpb_symm_destroy() {
   if (!g_symm.base) return 0;
+  if (g_symm.vmm) return tpb_symm_vmm_destroy();
   for (int r = 0; r < g_symm.world; ++r)
     if (r != g_symm.rank && g_symm.peer[r]) cudaIpcCloseMemHandle(g_symm.peer[r]);
   cudaFree(g_symm.base);
@@ -372,6 +462,18 @@ extern "C" void* tpb_symm_ptr(int rank, size_t off) {
 extern "C" size_t tpb_symm_used() { return g_symm.used; }
 
 // ------------------------------------------------------------------ collectives
+// Multicast (in-switch) forms of the kernels are used when the arena has a multicast mapping and
+// they are not switched off (tpb_symm_set_multicast(0): plain peer loads and stores, the form that
+// tests of rank failure must use).
+static bool g_mc_enabled = true;
+static bool use_mc() { return g_mc_enabled && g_symm.mc_base != nullptr && g_symm.world > 1; }
+extern "C" int tpb_symm_set_multicast(int on) {
+  g_mc_enabled = on != 0;
+  return 0;
+}
+extern "C" int tpb_symm_has_multicast() { return g_symm.mc_base != nullptr && g_symm.world > 1; }
+extern "C" void* tpb_symm_mc_ptr(size_t off) { return g_symm.mc_base ? g_symm.mc_base + off : nullptr; }
+
 static PeerPtrs peers_at(size_t off) {
   PeerPtrs pp;
   memset(&pp, 0, sizeof(pp));
@@ -392,6 +494,22 @@ extern "C" int tpb_symm_allgather(size_t shard_off, size_t shard_bytes, void* ou
   SyncArgs s = make_sync(pad_off, epoch, status, wait_s);
   allgather_pull_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(
       peers_at(shard_off), static_cast<char*>(out), shard_bytes, s, slot_base);
+  return (int)cudaGetLastError();
+}
+
+// All-gather by multicast stores (arenas of the virtual-memory allocator with a multicast mapping
+// only). shard: local device pointer; the result appears at arena offset out_off on every rank once
+// its done_slot flags reached `epoch` (wait with tpb_symm_wait_slots). ready_slot / done_slot:
+// `world` flag slots each.
+extern "C" int tpb_symm_allgather_mc(const void* shard, size_t shard_bytes, size_t out_off, size_t pad_off,
+                                     int ready_slot, int done_slot, uint32_t epoch, uint32_t* block_counter,
+                                     int ctas, double wait_s, uint32_t* status, void* stream) {
+  if (!g_symm.mc_base || g_symm.world < 2) return -4;
+  if (shard_bytes % 16 || (reinterpret_cast<uintptr_t>(shard) & 15) || out_off % 16) return -2;
+  SyncArgs s = make_sync(pad_off, epoch, status, wait_s);
+  allgather_mc_kernel<<<ctas > 0 ? ctas : 32, 512, 0, (cudaStream_t)stream>>>(
+      static_cast<const char*>(shard), g_symm.mc_base + out_off + (size_t)g_symm.rank * shard_bytes, shard_bytes, s,
+      ready_slot, done_slot, block_counter);
   return (int)cudaGetLastError();
 }
 
@@ -423,7 +541,8 @@ extern "C" int tpb_symm_rs_adamw(size_t grad_off, size_t lo, size_t n, float* ma
   rs_adamw_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(
       peers_at(grad_off), lo, n, master, m, v, (__nv_bfloat16*)shard_out,
       do_bcast ? peers_at(0) : peers_at(0), do_bcast ? bcast_off : 0, do_bcast, red_out, sumsq, mode,
-      h, clip_coef, s, ready_slot, done_slot, block_counter, 0);
+      h, clip_coef, s, ready_slot, done_slot, block_counter, 0,
+      use_mc() ? g_symm.mc_base + grad_off : nullptr, use_mc() ? g_symm.mc_base : nullptr);
   return (int)cudaGetLastError();
 }
 
@@ -545,6 +664,6 @@ extern "C" int tpb_symm_rs_adamw_ce(size_t grad_off, size_t lo, size_t n, void* 
   const int grid = ctas > 0 ? ctas : 148;
   rs_adamw_kernel<<<grid, rs_threads(), 0, st>>>(local, lo, n, master, m, v, (__nv_bfloat16*)shard_out, local, 0, 0,
                                         red_out, sumsq, mode, h, clip_coef, s, ready_slot, done_slot,
-                                        nullptr, 1);
+                                        nullptr, 1, nullptr, nullptr);
   return (int)cudaGetLastError();
 }

@@ -34,6 +34,8 @@ _KERNEL_SIGS = {
     "tpb_rope": [P, P, P, P, LL, I, I, LL, LL, I, I, I, P],
     "tpb_swiglu_fwd": [P, P, P, LL, I, LL, P],
     "tpb_swiglu_bwd": [P, P, P, P, P, LL, I, LL, LL, P],
+    "tpb_swiglu_fwd_n": [P, P, P, LL, I, LL, P, P],
+    "tpb_swiglu_bwd_n": [P, P, P, P, P, LL, I, LL, LL, P, P],
     "tpb_gelu_fwd": [P, P, LL, I, P],
     "tpb_gelu_bwd": [P, P, P, LL, I, P],
     "tpb_cross_entropy": [P, P, P, P, P, LL, I, LL, LL, F, P],

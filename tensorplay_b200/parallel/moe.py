@@ -83,6 +83,35 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, offs: torch.Tensor, *, mode: 
     return out
 
 
+def _swiglu_rows(gu: torch.Tensor, rows_dev: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` of the packed ``[cap, 2I]`` expert pre-activations, for the first
+    ``rows_dev[0]`` rows only (a device scalar: the buffer is sized for the worst case)."""
+    cap, two_i = gu.shape
+    I = two_i // 2
+    if not (gu.is_cuda and gu.dtype == torch.bfloat16 and I % 8 == 0):
+        return ops.swiglu_packed(gu)
+    out = torch.empty(cap, I, dtype=gu.dtype, device=gu.device)
+    code = lib().tpb_swiglu_fwd_n(gu.data_ptr(), gu.data_ptr() + I * 2, out.data_ptr(), cap, I, two_i,
+                                  rows_dev.data_ptr(), stream_ptr())
+    _native.check(code, "tpb_swiglu_fwd_n")
+    return out
+
+
+def _swiglu_rows_bwd(dact: torch.Tensor, gu: torch.Tensor, rows_dev: torch.Tensor) -> torch.Tensor:
+    cap, two_i = gu.shape
+    I = two_i // 2
+    if not (gu.is_cuda and gu.dtype == torch.bfloat16 and I % 8 == 0):
+        g = gu.detach().float().requires_grad_()
+        with torch.enable_grad():
+            a = torch.nn.functional.silu(g[:, :I]) * g[:, I:]
+        return torch.autograd.grad(a, g, dact.float())[0].to(gu.dtype)
+    dgu = torch.empty_like(gu)
+    code = lib().tpb_swiglu_bwd_n(dact.data_ptr(), gu.data_ptr(), gu.data_ptr() + I * 2, dgu.data_ptr(),
+                                  dgu.data_ptr() + I * 2, cap, I, two_i, two_i, rows_dev.data_ptr(), stream_ptr())
+    _native.check(code, "tpb_swiglu_bwd_n")
+    return dgu
+
+
 class MoEWorkspace:
     """Symmetric buffers for expert-parallel layers of one model (call collectively)."""
 
@@ -185,8 +214,9 @@ class _EPFFNFn(torch.autograd.Function):
         T, H = x.shape
         dst_rank, dst_row, offs = ws.route(topk_idx)
         ws.dispatch(x, dst_rank, dst_row, ws.xbuf)
+        rows_dev = offs[ws.El:]  # device scalar: rows of the expert buffers that are in use
         gu = grouped_gemm(ws.xbuf, w_gate_up, offs, workspace=ws.gws)                      # [cap, 2I]
-        act = ops.swiglu_packed(gu)                                                         # [cap, I]
+        act = _swiglu_rows(gu, rows_dev)                                                    # [cap, I]
         grouped_gemm(act, w_down, offs, out=ws.ybuf, workspace=ws.gws)                      # [cap, H]
         wf = topk_w.reshape(-1).float().contiguous()
         y, _ = ws.combine(ws.ybuf, dst_rank, dst_row, w=wf, tokens=T)
@@ -221,7 +251,7 @@ class _EPFFNFn(torch.autograd.Function):
             ws.dispatch(x, dst_rank, dst_row, ws.xbuf)
             xin = ws.xbuf
             gu = grouped_gemm(xin, w_gate_up, offs, workspace=ws.gws)
-            act = ops.swiglu_packed(gu.detach())
+            act = _swiglu_rows(gu, offs[ws.El:])
             grouped_gemm(act, w_down, offs, out=ws.ybuf, workspace=ws.gws)
         ws.generation += 1  # ybuf is overwritten below
         # gate-weight gradient: <dy[t], y_row>
@@ -233,11 +263,7 @@ class _EPFFNFn(torch.autograd.Function):
         dyr = ws.dbuf
         dact = grouped_gemm(dyr, w_down, offs, b_mn=True, workspace=ws.gws)                # [cap, I]
         dwd = _wgrad(dyr, act, offs, ctx.refs[1], ws)
-        # swiglu backward through the saved pre-activation
-        gu_r = gu.detach().requires_grad_()
-        with torch.enable_grad():
-            a2 = ops.swiglu_packed(gu_r)
-        (dgu,) = torch.autograd.grad(a2, gu_r, dact)
+        dgu = _swiglu_rows_bwd(dact, gu, offs[ws.El:])   # rows beyond the limit stay unwritten: no tile reads them
         dxr = grouped_gemm(dgu, w_gate_up, offs, b_mn=True, out=ws.ybuf, workspace=ws.gws)  # [cap, H]
         dwg = _wgrad(dgu, xin, offs, ctx.refs[0], ws)
         dx, _ = ws.combine(dxr, dst_rank, dst_row, tokens=T)

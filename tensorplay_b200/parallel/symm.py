@@ -39,6 +39,17 @@ _SIGS = {
     "tpb_symm_wait_slots": [C.c_size_t, C.c_int, C.c_uint32, C.c_double, C.c_void_p, C.c_void_p],
     "tpb_symm_barrier": [C.c_size_t, C.c_int, C.c_uint32, C.c_double, C.c_void_p, C.c_void_p],
     "tpb_symm_peer_copy": [C.c_int, C.c_size_t, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p],
+    "tpb_symm_vmm_supported": [C.c_int],
+    "tpb_symm_vmm_create": [C.c_int, C.c_int, C.c_size_t, C.POINTER(C.c_int), C.POINTER(C.c_size_t)],
+    "tpb_symm_vmm_map_peer": [C.c_int, C.c_int],
+    "tpb_symm_mc_create": [C.POINTER(C.c_int)],
+    "tpb_symm_mc_import": [C.c_int],
+    "tpb_symm_mc_add_device": [],
+    "tpb_symm_mc_bind": [],
+    "tpb_symm_set_multicast": [C.c_int],
+    "tpb_symm_has_multicast": [],
+    "tpb_symm_allgather_mc": [C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_int, C.c_int, C.c_uint32,
+                              C.c_void_p, C.c_int, C.c_double, C.c_void_p, C.c_void_p],
 }
 NO_OFFSET = C.c_size_t(-1).value
 
@@ -51,8 +62,50 @@ class _DevMem:
                                          "version": 2, "strides": None}
 
 
+def _send_fd_to_peers(fd: int, n_receivers: int, name: str):
+    """Serve ``fd`` to ``n_receivers`` connections on the abstract Unix socket ``name`` (file
+    descriptors cannot travel through a key-value store; SCM_RIGHTS over a local socket can)."""
+    import socket
+    import threading
+    srv = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+    srv.bind("\0" + name)
+    srv.listen(max(n_receivers, 1))
+    srv.settimeout(120)
+
+    def serve():
+        try:
+            for _ in range(n_receivers):
+                c, _ = srv.accept()
+                with c:
+                    socket.send_fds(c, [b"f"], [fd])
+        finally:
+            srv.close()
+
+    t = threading.Thread(target=serve, daemon=True)
+    t.start()
+    return t
+
+
+def _recv_fd(name: str) -> int:
+    import socket
+    with socket.socket(socket.AF_UNIX, socket.SOCK_STREAM) as c:
+        c.settimeout(120)
+        c.connect("\0" + name)
+        _, fds, _, _ = socket.recv_fds(c, 1, 1)
+    if not fds:
+        raise RuntimeError(f"no file descriptor received on {name!r}")
+    return fds[0]
+
+
 class SymmArena:
-    """Process-wide symmetric arena (one per process; collective to create)."""
+    """Process-wide symmetric arena (one per process; collective to create).
+
+    Two allocators: ``"vmm"`` (default where the device supports it) creates the arena with the CUDA
+    virtual-memory API, passes its file descriptor to the peers over Unix sockets and binds all
+    arenas to an NVSwitch multicast object, which gives the kernels ``multimem`` loads (reduced in
+    the switch) and stores (delivered to every rank); ``"ipc"`` uses ``cudaMalloc`` + CUDA IPC and
+    has peer loads / stores only. ``TPB_SYMM_ALLOC`` / ``TPB_SYMM_MULTICAST=0`` select.
+    """
 
     _instance: Optional["SymmArena"] = None
     # one block counter per communicating unit: two launches that count into the same word may
@@ -78,14 +131,23 @@ class SymmArena:
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.device = torch.device("cuda", torch.cuda.current_device())
-        handle = (C.c_char * 64)()
-        _native.check(raw.tpb_symm_create(self.world, self.rank, nbytes, handle), "tpb_symm_create")
-        if self.world > 1:
-            gathered = [None] * self.world
-            dist.all_gather_object(gathered, bytes(handle.raw), group=group)
-            blob = b"".join(gathered)
-            buf = (C.c_char * len(blob)).from_buffer_copy(blob)
-            _native.check(raw.tpb_symm_open(buf), "tpb_symm_open")
+        raw.tpb_symm_mc_ptr.argtypes = [C.c_size_t]
+        raw.tpb_symm_mc_ptr.restype = C.c_void_p
+        want = os.environ.get("TPB_SYMM_ALLOC", "vmm")
+        self.allocator = "ipc"
+        self.multicast = False
+        if want == "vmm" and self._all_ranks(bool(raw.tpb_symm_vmm_supported(0))):
+            nbytes = self._create_vmm(nbytes)
+            self.allocator = "vmm"
+        else:
+            handle = (C.c_char * 64)()
+            _native.check(raw.tpb_symm_create(self.world, self.rank, nbytes, handle), "tpb_symm_create")
+            if self.world > 1:
+                gathered = [None] * self.world
+                dist.all_gather_object(gathered, bytes(handle.raw), group=group)
+                blob = b"".join(gathered)
+                buf = (C.c_char * len(blob)).from_buffer_copy(blob)
+                _native.check(raw.tpb_symm_open(buf), "tpb_symm_open")
         self.nbytes = nbytes
         self._offsets: Dict[int, int] = {}
         self.pad_slots = pad_slots
@@ -95,6 +157,65 @@ class SymmArena:
         if self.world > 1:
             dist.barrier(group=group)
         SymmArena._instance = self
+
+    def _all_ranks(self, flag: bool) -> bool:
+        """True when ``flag`` holds on every rank (collective)."""
+        if self.world == 1:
+            return flag
+        got = [None] * self.world
+        dist.all_gather_object(got, bool(flag), group=self.group)
+        return all(got)
+
+    def _create_vmm(self, nbytes: int) -> int:
+        raw, w, r = self.raw, self.world, self.rank
+        fd, size = C.c_int(-1), C.c_size_t(0)
+        _native.check(raw.tpb_symm_vmm_create(w, r, nbytes, C.byref(fd), C.byref(size)), "tpb_symm_vmm_create")
+        if w == 1:
+            os.close(fd.value)
+            return size.value
+        tag = [f"tpb_symm_{os.getpid()}_{int.from_bytes(os.urandom(4), 'little')}"]
+        dist.broadcast_object_list(tag, src=dist.get_global_rank(self.group, 0) if self.group is not None else 0,
+                                   group=self.group)
+        tag = tag[0]
+        server = _send_fd_to_peers(fd.value, w - 1, f"{tag}_{r}")
+        dist.barrier(group=self.group)  # every rank is listening
+        for p in range(w):
+            if p != r:
+                pfd = _recv_fd(f"{tag}_{p}")
+                try:
+                    _native.check(raw.tpb_symm_vmm_map_peer(p, pfd), "tpb_symm_vmm_map_peer")
+                finally:
+                    os.close(pfd)
+        server.join()
+        os.close(fd.value)
+        dist.barrier(group=self.group)
+        want_mc = os.environ.get("TPB_SYMM_MULTICAST", "1") != "0"
+        if want_mc and self._all_ranks(bool(raw.tpb_symm_vmm_supported(1))):
+            if r == 0:
+                mfd = C.c_int(-1)
+                _native.check(raw.tpb_symm_mc_create(C.byref(mfd)), "tpb_symm_mc_create")
+                server = _send_fd_to_peers(mfd.value, w - 1, f"{tag}_mc")
+                dist.barrier(group=self.group)
+                server.join()
+                os.close(mfd.value)
+            else:
+                dist.barrier(group=self.group)
+                mfd = _recv_fd(f"{tag}_mc")
+                try:
+                    _native.check(raw.tpb_symm_mc_import(mfd), "tpb_symm_mc_import")
+                finally:
+                    os.close(mfd)
+            dist.barrier(group=self.group)
+            _native.check(raw.tpb_symm_mc_add_device(), "tpb_symm_mc_add_device")
+            dist.barrier(group=self.group)  # every device joined before any memory is bound
+            _native.check(raw.tpb_symm_mc_bind(), "tpb_symm_mc_bind")
+            dist.barrier(group=self.group)
+            self.multicast = True
+        return size.value
+
+    def multicast_ptr(self, t: torch.Tensor) -> int:
+        """Multicast address of an arena tensor (0 without a multicast mapping)."""
+        return int(self.raw.tpb_symm_mc_ptr(self.offset_of(t)) or 0) if self.multicast else 0
 
     def _alloc_bytes(self, nbytes: int) -> int:
         off = self.raw.tpb_symm_alloc(nbytes)
@@ -127,6 +248,10 @@ class SymmArena:
         return s
 
     def close(self) -> None:
+        """Release the arena (collective: no rank may still read a peer's memory)."""
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(group=self.group)
         self.raw.tpb_symm_destroy()
         SymmArena._instance = None
 
@@ -154,6 +279,7 @@ class SymmComm:
         self.reduce_ctas = int(os.environ.get("TPB_REDUCE_CTAS", reduce_ctas))
         w = self.world
         self.slot_gather = {u.index: self.arena.slots(w) for u in units}
+        self.slot_gather_done = {u.index: self.arena.slots(w) for u in units}
         self.slot_ready = {u.index: self.arena.slots(w) for u in units}
         self.slot_done = {u.index: self.arena.slots(w) for u in units}
         self.epoch_gather = {u.index: 0 for u in units}
@@ -161,12 +287,17 @@ class SymmComm:
         self.grad_slot_last = {}  # grad pool slot -> (unit index, epoch) whose readers must finish
         self.status = status_word(engine.device)
         # "ce": bulk transfers by the copy engines (no SM time; the fused reduce + AdamW kernel then
-        # reads local memory only); "sm": pull kernels that load from peer memory themselves.
+        # reads local memory only); "sm": kernels that load from peer memory themselves (with a
+        # multicast mapping the reduce + AdamW kernel takes its slice through one in-switch reducing
+        # load per 16 bytes); "mc": as "sm", and the all-gather is a multicast push (every rank
+        # stores its shard once, the switch delivers it to all ranks).
         spec = os.environ.get("TPB_REDUCE_OVERLAP", "")  # "threads,max_shared" for the reduce + AdamW kernel
         if spec:
             th, ms = (int(x) for x in spec.split(","))
             _native.check(self.arena.raw.tpb_symm_set_overlap(th, ms), "tpb_symm_set_overlap")
         self.transport = os.environ.get("TPB_COMM_TRANSPORT", "ce")
+        if self.transport == "mc" and not self.arena.multicast:
+            raise RuntimeError("TPB_COMM_TRANSPORT=mc needs the virtual-memory arena with a multicast mapping")
         self.staging = None
         if self.transport == "ce":
             shard_max = max(u.shard_numel for u in units)
@@ -189,6 +320,18 @@ class SymmComm:
                 stream_ptr())
             _native.launch_count += 1
             _native.check(code, "tpb_symm_allgather_ce")
+            return
+        if self.transport == "mc":
+            ep = self.epoch_gather[u.index]
+            code = self.arena.raw.tpb_symm_allgather_mc(
+                u.shard.data_ptr(), u.shard_numel * buf.element_size(), self.arena.offset_of(buf), self.arena.pad_off,
+                self.slot_gather[u.index], self.slot_gather_done[u.index], ep, self.arena.counter_ptr(512 + u.index),
+                self.gather_ctas, self.wait_s, self.status.data_ptr(), stream_ptr())
+            _native.check(code, "tpb_symm_allgather_mc")
+            code = self.arena.raw.tpb_symm_wait_slots(self.arena.pad_off, self.slot_gather_done[u.index], ep,
+                                                      self.wait_s, self.status.data_ptr(), stream_ptr())
+            _native.launch_count += 2
+            _native.check(code, "tpb_symm_wait_slots")
             return
         code = self.arena.raw.tpb_symm_allgather(
             u._shard_off, u.shard_numel * buf.element_size(), buf.data_ptr(), self.arena.pad_off,

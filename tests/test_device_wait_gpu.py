@@ -90,3 +90,19 @@ def test_timed_out_handshake_leaves_optimizer_state_untouched():
     ops.check_status()
     assert not torch.equal(master, keep[0])
     assert (m - 0.1 * g.float()).abs().max().item() < 1e-6
+
+
+def test_virtual_memory_arena_on_one_gpu():
+    """The arena of a single rank comes from the virtual-memory allocator (no peers, no multicast
+    object): tensors carved from it are ordinary device memory at 256-byte aligned offsets."""
+    arena = _arena()
+    assert arena.allocator == "vmm" and not arena.multicast
+    a = arena.alloc(1000, torch.float32)
+    b = arena.alloc(7, torch.bfloat16)
+    assert arena.offset_of(a) % 256 == 0 and arena.offset_of(b) % 256 == 0
+    assert arena.offset_of(b) >= arena.offset_of(a) + 4000
+    a.copy_(torch.arange(1000, device=a.device, dtype=torch.float32))
+    b.fill_(3.0)
+    torch.cuda.synchronize()
+    assert float(a.sum()) == 999 * 1000 / 2 and float(b.float().sum()) == 21.0
+    assert arena.multicast_ptr(a) == 0

@@ -40,6 +40,23 @@ def test_fsdp_symm_matches_nccl_and_dense():
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_symmetric_collectives_match_nccl_bit_for_bit():
+    """All-gather (pull, copy engines, multicast push), reduce-scatter and all-reduce (multimem and
+    plain peer loads) against NCCL on integer patterns, on every GPU of the box."""
+    r = _run_workers("symm_collectives_worker.py", _ngpu())
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "RESULT" in r.stdout
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_fsdp_multicast_transport():
+    n = 2 if _ngpu() < 4 else 4
+    r = _run_workers("fsdp_symm_worker.py", n, extra_env={"TPB_COMM_TRANSPORT": "mc"})
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "RESULT" in r.stdout
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 def test_tp_fused_ag_gemm_and_gemm_rs():
     n = 2 if _ngpu() < 4 else 4
     r = _run_workers("tp_fused_worker.py", n)
