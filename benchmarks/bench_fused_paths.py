@@ -134,36 +134,49 @@ def main():
         nccl_buf = torch.empty(u.padded, device=dev, dtype=torch.bfloat16)
         shard_copy = u.shard.clone()
 
-        def gather_fused():
-            eng.comm.all_gather(u, buf)
-
-        def gather_base():
-            dist.all_gather_into_tensor(nccl_buf, shard_copy)
-
-        t_f, t_b = timed(gather_fused, args.iters), timed(gather_base, args.iters)
-        report(rank, f"fsdp_all_gather {u.padded * 2 / 1e6:.0f} MB / {world} ranks", t_f, t_b, 0.0,
-               (world - 1) * u.shard_numel * 2, u.padded * 2, tf_peak, hbm_peak, which,
-               {"transport": eng.comm.transport})
-
         g = eng.grad_pool[0][: u.padded]
         g.normal_()
         u._grad_slot = 0
         eng.step_count = 1
         gs = torch.empty(u.shard_numel, device=dev, dtype=torch.bfloat16)
 
-        def rs_adamw_fused():
-            eng.comm.reduce_scatter_adamw(u, g, eng._adam_kwargs())
-            eng.comm.before_grad_reuse(0)
+        def gather_base():
+            dist.all_gather_into_tensor(nccl_buf, shard_copy)
 
         def rs_adamw_base():
             dist.reduce_scatter_tensor(gs, g, op=dist.ReduceOp.AVG)
             O.adamw_flat_(u.master, u.exp_avg, u.exp_avg_sq, gs, shard_copy, **eng._adam_kwargs())
 
-        t_f, t_b = timed(rs_adamw_fused, args.iters), timed(rs_adamw_base, args.iters)
-        # per rank: pulls (world-1) peer slices of its shard; AdamW streams 28 B per owned parameter
-        report(rank, f"fsdp_rs_adamw {u.padded * 2 / 1e6:.0f} MB / {world} ranks", t_f, t_b, 0.0,
-               (world - 1) * u.shard_numel * 2, u.shard_numel * (2 + 28), tf_peak, hbm_peak, which,
-               {"transport": eng.comm.transport})
+        t_gb, t_rb = timed(gather_base, args.iters), timed(rs_adamw_base, args.iters)
+        comm = eng.comm
+        raw = comm.arena.raw
+        # every transport of the engine: copy engines; kernels with peer loads; the same kernels with the
+        # in-switch reducing load; multicast push for the gather
+        variants = [("ce", 1, "copy engines"), ("sm", 0, "peer loads")]
+        if comm.arena.multicast:
+            variants += [("sm", 1, "peer-load gather, multimem reduce"), ("mc", 1, "multicast-store gather, multimem reduce")]
+        for transport, mc, label in variants:
+            comm.transport = transport
+            raw.tpb_symm_set_multicast(mc)
+            if transport == "ce" and comm.staging is None:
+                comm.staging = torch.empty(world * u.shard_numel, dtype=torch.bfloat16, device=dev)
+
+            def gather_fused():
+                comm.all_gather(u, buf)
+
+            def rs_adamw_fused():
+                comm.reduce_scatter_adamw(u, g, eng._adam_kwargs())
+                comm.before_grad_reuse(0)
+
+            t_f = timed(gather_fused, args.iters)
+            report(rank, f"fsdp_all_gather {u.padded * 2 / 1e6:.0f} MB / {world} ranks", t_f, t_gb, 0.0,
+                   (world - 1) * u.shard_numel * 2, u.padded * 2, tf_peak, hbm_peak, which, {"transport": label})
+            t_f = timed(rs_adamw_fused, args.iters)
+            # per rank: (world-1) slices of its shard leave every peer; AdamW streams 28 B per owned parameter
+            report(rank, f"fsdp_rs_adamw {u.padded * 2 / 1e6:.0f} MB / {world} ranks", t_f, t_rb, 0.0,
+                   (world - 1) * u.shard_numel * 2, u.shard_numel * (2 + 28), tf_peak, hbm_peak, which,
+                   {"transport": label})
+        raw.tpb_symm_set_multicast(1)
     torch.cuda.synchronize()
     O.check_status()
     dist.barrier()

@@ -5,10 +5,11 @@ Two implementations live in this package:
 
 * ``fully_shard`` below is the general, API-compatible path for arbitrary modules: parameters are
   sharded on dim 0 (ceil chunks, padded to the first chunk like the reference,
-  tensorplay/distributed/fsdp/_fully_shard/_fsdp_param.py:284-374), a forward pre-hook all-gathers
-  a unit's parameters, a post-hook frees them, and a backward hook re-gathers, then
-  reduce-scatters gradients into ``param.grad`` shards. It runs on gloo and NCCL through
-  torch.distributed and is what the CPU oracle configuration uses.
+  tensorplay/distributed/fsdp/_fully_shard/_fsdp_param.py:284-374) into one flat shard per unit, a
+  forward pre-hook all-gathers the unit with ONE collective and copies the full parameters out, a
+  post-hook frees them, and a backward hook reduce-scatters the unit's gradients with one
+  collective into ``param.grad`` shards (plus an all-reduce over the replicate dimension of a 2-D
+  mesh). It runs on gloo and NCCL through torch.distributed and is what the CPU oracle uses.
 * ``tensorplay_b200.parallel.FSDPEngine`` is the performance path for transformer stacks (flat
   per-layer buffers, peer-memory kernels, optimizer fused into backward).
 
@@ -16,22 +17,13 @@ Knobs follow tensorplay/distributed/fsdp/_fully_shard/_fully_shard.py:66-455 and
 """
 from __future__ import annotations
 
-from .api import (BackwardPrefetch, CPUOffload, CPUOffloadPolicy, FSDPModule, FullyShardedDataParallel,
-                  MixedPrecision, MixedPrecisionPolicy, OffloadPolicy, ShardingStrategy, fully_shard)
-
-import dataclasses as _dc
-from typing import Optional as _Optional
-
-
-@_dc.dataclass
-class DataParallelMeshDims:
-    """Names of the mesh dimensions used for sharding and (hybrid) replication."""
-    shard: _Optional[str] = None
-    replicate: _Optional[str] = None
-
+from .api import (AllGather, BackwardPrefetch, Comm, CPUOffload, CPUOffloadPolicy, DataParallelMeshDims, FSDPModule,
+                  FullyShardedDataParallel, MixedPrecision, MixedPrecisionPolicy, OffloadPolicy, ReduceScatter,
+                  ShardingStrategy, UnshardHandle, fully_shard, register_fsdp_forward_method, share_comm_ctx)
 
 __all__ = ["fully_shard", "DataParallelMeshDims", "FSDPModule", "MixedPrecisionPolicy", "CPUOffloadPolicy", "OffloadPolicy",
-           "FullyShardedDataParallel", "ShardingStrategy", "MixedPrecision", "CPUOffload", "BackwardPrefetch"]
+           "FullyShardedDataParallel", "ShardingStrategy", "MixedPrecision", "CPUOffload", "BackwardPrefetch",
+           "Comm", "AllGather", "ReduceScatter", "UnshardHandle", "register_fsdp_forward_method", "share_comm_ctx"]
 
 
 def __getattr__(name):
