@@ -62,7 +62,29 @@ class DistributedDataParallel(nn.Module):
         self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(process_group) if dist.is_initialized() else 0
         self.broadcast_buffers = broadcast_buffers
+        # Parameters that take no part in a backward never fire their hook, so their bucket would never
+        # fill. With find_unused_parameters the buckets that are still open when the backward ends are
+        # completed with zeros for those parameters and reduced; without it an open bucket is an error
+        # (it would otherwise skip its reduction silently). static_graph needs nothing here: readiness
+        # is counted by hooks on the parameters, not discovered from the autograd graph.
         self.find_unused_parameters = find_unused_parameters
+        self.static_graph = static_graph
+        if device_ids is not None:
+            if len(device_ids) != 1:
+                raise ValueError("device_ids must name exactly one device: one process drives one GPU")
+            want = device_ids[0] if isinstance(device_ids[0], int) else torch.device(device_ids[0]).index
+            have = next(module.parameters()).device
+            if have.type != "cuda" or have.index != want:
+                raise ValueError(f"the module lives on {have}, device_ids says cuda:{want}; move the module first")
+        if output_device is not None and device_ids is not None and output_device != device_ids[0]:
+            raise NotImplementedError("output_device other than the module's device is not implemented")
+        if dim != 0:
+            raise NotImplementedError("scattering inputs along a dimension (dim) is not implemented: pass each rank its batch")
+        self._ready_in_bucket = {}
+        self._reduced = set()
+        self._complete = set()
+        self._next_bucket = 0
+        self._cb_queued = False
         self.require_backward_grad_sync = True
         self._hook = None
         self._hook_state = None
@@ -174,10 +196,51 @@ class DistributedDataParallel(nn.Module):
             if param.grad.data_ptr() != v.data_ptr():
                 v.copy_(param.grad.reshape(-1))
                 param.grad = v.view(param.shape)
+            if not self._cb_queued:
+                self._cb_queued = True
+                torch.autograd.Variable._execution_engine.queue_callback(self._finalize_backward)
+            self._ready_in_bucket.setdefault(b.index, set()).add(id(param))
             done = self._rt.tpb_reducer_mark_ready(self._reducer, self._param_index[id(param)])
             if done >= 0:
-                self._reduce(self.buckets[done])
+                self._complete.add(done)
+                self._launch_in_order()
         return hook
+
+    def _launch_in_order(self) -> None:
+        """Reductions are issued strictly in bucket order (the order in which a full backward fills
+        them): ranks whose buckets fill in different orders - some parameters unused on some ranks -
+        still issue the same sequence of collectives."""
+        while self._next_bucket < len(self.buckets) and self._next_bucket in self._complete:
+            b = self.buckets[self._next_bucket]
+            self._next_bucket += 1
+            self._reduced.add(b.index)
+            self._reduce(b)
+
+    def _finalize_backward(self) -> None:
+        """End of a synchronised backward: every bucket must have been reduced."""
+        ready, reduced, complete = self._ready_in_bucket, self._reduced, self._complete
+        self._ready_in_bucket, self._reduced, self._complete, self._cb_queued = {}, set(), set(), False
+        self._next_bucket = 0
+        open_buckets = [b for b in self.buckets if b.index not in reduced]
+        if not open_buckets:
+            return
+        if not self.find_unused_parameters:
+            for b in open_buckets:
+                self._rt.tpb_reducer_rearm(self._reducer, b.index)
+            names = {id(p): n for n, p in self.module.named_parameters()}
+            missing = [names.get(id(p), "?") for b in open_buckets for p in b.params if id(p) not in ready.get(b.index, ())]
+            raise RuntimeError("DistributedDataParallel: these parameters received no gradient in this backward, so "
+                               f"their buckets were not reduced: {missing[:8]}{' ...' if len(missing) > 8 else ''}. "
+                               "Pass find_unused_parameters=True if parts of the model are skipped on purpose.")
+        for b in open_buckets:   # ascending bucket order, after everything that was launched during the backward
+            got = ready.get(b.index, ())
+            for p in b.params:
+                if id(p) not in got:
+                    o = b.offset_of[id(p)]
+                    b.flat_grad[o: o + p.numel()].zero_()   # unused this step: contributes zeros to the average
+            if b.index not in complete:
+                self._rt.tpb_reducer_rearm(self._reducer, b.index)
+            self._reduce(b)
 
     def _reduce(self, b: _Bucket) -> None:
         last = b.index == len(self.buckets) - 1

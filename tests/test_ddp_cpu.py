@@ -59,3 +59,45 @@ def _worker(rank, world):
 
 def test_ddp_two_ranks():
     assert all(run_ranks(_worker, 2))
+
+
+def _unused_worker(rank, world):
+    import pytest
+    from torch import nn
+    from tensorplay_b200.distributed.ddp import DistributedDataParallel as DDP
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.used = nn.Linear(6, 6)
+            self.skipped = nn.Linear(6, 6)   # takes part in the forward only on rank 0
+            self.head = nn.Linear(6, 2)
+
+        def forward(self, x, use_skipped):
+            h = torch.tanh(self.used(x))
+            if use_skipped:
+                h = h + self.skipped(x)
+            return self.head(h)
+
+    torch.manual_seed(0)
+    x = torch.randn(world, 4, 6)
+    m = Net()
+    ddp = DDP(m, bucket_cap_mb=1e-4, find_unused_parameters=True)   # tiny buckets: one per parameter
+    ddp(x[rank], rank == 0).sum().backward()
+    ddp.synchronize()
+    ref = Net()
+    ref.load_state_dict(m.state_dict())
+    sum(ref(x[r], r == 0).sum() for r in range(world)).backward()
+    for (n, p), (_, q) in zip(m.named_parameters(), ref.named_parameters()):
+        assert torch.allclose(p.grad, q.grad / world, atol=1e-6), n
+    # without the flag an unfinished bucket is reported instead of being skipped silently
+    strict = DDP(Net(), bucket_cap_mb=1e-4)
+    with pytest.raises(RuntimeError, match="find_unused_parameters"):
+        strict(x[rank], False).sum().backward()
+    with pytest.raises(NotImplementedError):
+        DDP(Net(), dim=1)
+    return True
+
+
+def test_ddp_unused_parameters_are_reduced_as_zeros_or_reported():
+    assert all(run_ranks(_unused_worker, 2))
