@@ -157,11 +157,11 @@ class PipelineScheduleMulti:
         return out
 
 
-class ScheduleInterleaved1F1B(PipelineScheduleMulti):
-    """Looped placement (stage s on rank s % world). Executed breadth-first per local stage:
-    all micro-batch forwards of local stage 0, then of local stage 1, ...; backwards in reverse.
-    This keeps the interleaved placement's smaller bubble per stage while remaining
-    deadlock-free with plain batched p2p."""
+class ScheduleLoopedBFS(PipelineScheduleMulti):
+    """Looped placement (stage s on rank s % world), breadth-first: all micro-batch forwards of local
+    stage 0, then of local stage 1, ...; backwards in reverse. Simple and deadlock-free with plain
+    batched p2p, but every micro-batch's activations are alive at the turn: the depth-first
+    :class:`ScheduleInterleaved1F1B` (runtime.py) bounds them."""
 
     def _step_microbatches(self, a, k, t):
         for st in self.stages:
@@ -179,9 +179,3 @@ class ScheduleInterleaved1F1B(PipelineScheduleMulti):
                 st.backward_one_chunk(i)
                 sends += _run_p2p(st.get_bwd_send_ops(i))
             _wait(sends)
-
-
-class ScheduleLoopedBFS(ScheduleInterleaved1F1B):
-    """Breadth-first looped schedule: every local stage runs all micro-batch forwards before the next
-    local stage starts, and the backwards mirror that order (the execution order this module also
-    uses for the interleaved placement)."""

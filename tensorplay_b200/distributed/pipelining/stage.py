@@ -137,3 +137,48 @@ class PipelineStage:
         self.fwd_cache.clear()
         self.recv_fwd.clear()
         self.recv_bwd.clear()
+
+
+# ---------------------------------------------------------------- split backward (input / weight)
+def _stage_backward_input(stage: "PipelineStage", mb: int) -> None:
+    """Gradient of the micro-batch with respect to the stage's INPUT only (the part of backward
+    that the previous stage waits for); the graph is kept for the weight pass
+    (tensorplay/distributed/pipelining/_backward.py: ``stage_backward_input``)."""
+    inputs, out, loss = stage.fwd_cache[mb]
+    if stage.is_last:
+        if loss is None:
+            raise RuntimeError("the last stage needs a loss_fn to run backward")
+        root, seed = loss * stage.grad_scale, None
+    else:
+        root, seed = out, stage.recv_bwd.pop(mb)
+    wrt = [t for t in inputs if isinstance(t, torch.Tensor) and t.requires_grad]
+    params = [p for p in stage.submod.parameters() if p.requires_grad]
+    if wrt:
+        grads = torch.autograd.grad(root, wrt, seed, retain_graph=bool(params), allow_unused=True)
+        if not stage.is_first:
+            stage.fwd_cache[("in_grad", mb)] = grads[0]
+    stage.fwd_cache[("w_pending", mb)] = (root, seed)
+    stage.fwd_cache[mb] = (None, None, None)   # inputs / outputs are not needed again
+
+
+def _stage_backward_weight(stage: "PipelineStage", mb: int) -> None:
+    """Gradient with respect to the stage's PARAMETERS, accumulated into ``.grad``
+    (``stage_backward_weight``): runs whenever the schedule has a free slot."""
+    root, seed = stage.fwd_cache.pop(("w_pending", mb))
+    stage.fwd_cache.pop(mb, None)
+    params = [p for p in stage.submod.parameters() if p.requires_grad]
+    if not params:
+        return
+    grads = torch.autograd.grad(root, params, seed, allow_unused=True)
+    for p, g in zip(params, grads):
+        if g is None:
+            continue
+        if p.grad is None:
+            p.grad = g.detach()
+        else:
+            p.grad.add_(g)
+    stage.outputs.pop(mb, None) if not stage.is_last else None
+
+
+PipelineStage.backward_input_one_chunk = _stage_backward_input
+PipelineStage.backward_weight_one_chunk = _stage_backward_weight

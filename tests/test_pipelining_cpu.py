@@ -48,11 +48,11 @@ def test_pipeline_schedules(sched, world, n_mb):
 
 
 def _worker_interleaved(rank, world):
-    from tensorplay_b200.distributed.pipelining import PipelineStage, ScheduleInterleaved1F1B
+    from tensorplay_b200.distributed.pipelining import PipelineStage, ScheduleLoopedBFS
     full = _make()
     stages = [PipelineStage(full[s], s, 4, device="cpu") for s in range(4) if s % world == rank]
     loss_fn = lambda out, tgt: ((out - tgt) ** 2).mean()
-    sched = ScheduleInterleaved1F1B(stages, 4, loss_fn)
+    sched = ScheduleLoopedBFS(stages, 4, loss_fn)
     g = torch.Generator().manual_seed(1)
     x, y = torch.randn(8, 16, generator=g), torch.randn(8, 16, generator=g)
     if rank == 0:
@@ -69,3 +69,96 @@ def _worker_interleaved(rank, world):
 
 def test_interleaved_two_ranks_four_stages():
     assert all(run_ranks(_worker_interleaved, 2))
+
+
+def _make_deep(n_stages, seed=0):
+    torch.manual_seed(seed)
+    return nn.Sequential(*[nn.Sequential(nn.Linear(16, 16), nn.Tanh()) for _ in range(n_stages)])
+
+
+def _worker_runtime(rank, world, name, n_stages, n_mb, tmp):
+    import tensorplay_b200.distributed.pipelining as pp
+    full = _make_deep(n_stages)
+    place = pp.v_placement(world) if name in ("zbv", "dualpipev") else pp.loop_placement(world)
+    stages = [pp.PipelineStage(full[s], s, n_stages, device="cpu") for s in range(n_stages) if place(s) == rank]
+    loss_fn = lambda out, tgt: ((out - tgt) ** 2).mean()
+    if name == "csv":
+        # a hand-written table: all forwards depth-first, then split backwards with the weight passes last
+        if rank == 0:
+            order = pp.interleaved_1f1b_order(world, n_stages // world, n_mb, split_backward=True)
+            ref_sched = pp.PipelineScheduleRuntime(stages, n_mb, loss_fn, order=order, fill_with_weight=True, max_pending_w=2)
+            ref_sched.dump_csv(tmp)
+        import torch.distributed as dist
+        dist.barrier()
+        sched = pp.ScheduleFromCSV(stages, n_mb, loss_fn, csv_path=tmp)
+        kinds = {a.kind for acts in sched.order.values() for a in acts}
+        assert kinds == {"F", "I", "W"}
+    else:
+        cls = {"interleaved": pp.ScheduleInterleaved1F1B, "zb": pp.ScheduleInterleavedZeroBubble,
+               "zbv": pp.ScheduleZBVZeroBubble, "dualpipev": pp.ScheduleDualPipeV}[name]
+        sched = cls(stages, n_mb, loss_fn)
+    g = torch.Generator().manual_seed(1)
+    x, y = torch.randn(2 * n_mb, 16, generator=g), torch.randn(2 * n_mb, 16, generator=g)
+    has_first, has_last = place(0) == rank, place(n_stages - 1) == rank
+    for it in range(2):
+        for st in stages:
+            for p in st.submod.parameters():
+                p.grad = None
+        losses = []
+        args = (x,) if has_first else ()
+        sched.step(*args, target=y if has_last else None, losses=losses if has_last else None)
+        ref = _make_deep(n_stages)
+        loss_fn(ref(x), y).backward()
+        for st in stages:
+            for p, q in zip(st.submod.parameters(), ref[st.stage_index].parameters()):
+                assert torch.allclose(p.grad, q.grad, atol=1e-6), (name, rank, st.stage_index)
+        if has_last:
+            assert abs(torch.stack(losses).mean().item() - loss_fn(ref(x), y).item()) < 1e-6
+    # the depth-first order bounds the activations alive on a rank; breadth-first keeps the whole batch
+    alive = worst = 0
+    for a in sched.order[rank]:
+        alive += 1 if a.kind == "F" else (-1 if a.kind in ("B", "I") else 0)
+        worst = max(worst, alive)
+    return worst, sched.bubble_fraction()
+
+
+@pytest.mark.parametrize("name,world,n_stages,n_mb", [("interleaved", 2, 4, 4), ("interleaved", 4, 8, 8), ("zb", 2, 4, 4),
+                                                      ("zb", 4, 8, 4), ("zbv", 2, 4, 4), ("zbv", 4, 8, 8),
+                                                      ("dualpipev", 2, 4, 6), ("csv", 2, 4, 4)])
+def test_runtime_schedules_match_the_dense_model(name, world, n_stages, n_mb, tmp_path):
+    out = run_ranks(_worker_runtime, world, name, n_stages, n_mb, str(tmp_path / "sched.csv"))
+    local = n_stages // world
+    for rank, (worst, bubble) in enumerate(out):
+        if name == "interleaved":
+            assert worst <= 2 * (world - rank - 1) + (local - 1) * world + 1 < local * n_mb + 1 or n_mb <= world
+        assert bubble < 0.5
+
+
+def test_schedule_tables_are_consistent_without_ranks():
+    """Every action appears once, dependencies hold tick by tick, transfers connect the right ranks."""
+    import tensorplay_b200.distributed.pipelining as pp
+    for order, S, place, fill in (
+            (pp.interleaved_1f1b_order(4, 2, 8), 8, pp.loop_placement(4), False),
+            (pp.interleaved_1f1b_order(4, 3, 8, split_backward=True), 12, pp.loop_placement(4), True),
+            (pp.greedy_zero_bubble_order(8, pp.v_placement(4), 8, 8, 8), 8, pp.v_placement(4), False)):
+        ticks = pp.simulate(order, S, place, fill, 8)
+        seen = {}
+        for t, tick in enumerate(ticks):
+            for r, a in tick.actions.items():
+                assert place(a.stage) == r and (a.stage, a.kind, a.mb) not in seen
+                seen[(a.stage, a.kind, a.mb)] = t
+            for src, dst, kind, stage, mb in tick.transfers:
+                assert place(stage) == dst and src != dst
+        for (s, k, m), t in seen.items():
+            if k == "F" and s > 0:
+                assert seen[(s - 1, "F", m)] < t
+            if k in ("B", "I"):
+                assert seen[(s, "F", m)] < t
+                if s < S - 1:
+                    assert seen.get((s + 1, "B", m), seen.get((s + 1, "I", m))) < t
+            if k == "W":
+                assert seen[(s, "I", m)] < t
+        n_f = sum(1 for key in seen if key[1] == "F")
+        assert n_f == S * 8
+    with pytest.raises(ValueError):
+        pp.interleaved_1f1b_order(4, 2, 6)
