@@ -5,8 +5,16 @@ filesystem.py:56-80): one data file per rank ``__{rank}_0.distcp`` (a ``.mega`` 
 plus ``.metadata``; ``async_save`` stages to host memory and writes in the background
 (state_dict_saver.py:235-346, staging.py)."""
 from .api import (MegaStorageReader, MegaStorageWriter, ShardedTensor, Stateful, async_save, engine_state_dict, load, load_engine_state_dict, save)
+from .hf_storage import (HuggingFaceStorageReader, HuggingFaceStorageWriter, consolidate_to_hf, load_hf, save_hf)
+from .planner import DefaultLoadPlanner, DefaultSavePlanner, ReadItem, SavePlan, WriteItem
+from .state_dict import (StateDictOptions, get_model_state_dict, get_optimizer_state_dict, get_state_dict,
+                         set_model_state_dict, set_optimizer_state_dict, set_state_dict)
 
-__all__ = ["MegaStorageReader", "MegaStorageWriter", "ShardedTensor", "Stateful", "save", "async_save", "load", "engine_state_dict", "load_engine_state_dict"]
+__all__ = ["MegaStorageReader", "MegaStorageWriter", "ShardedTensor", "Stateful", "save", "async_save", "load",
+           "engine_state_dict", "load_engine_state_dict", "DefaultSavePlanner", "DefaultLoadPlanner", "SavePlan",
+           "WriteItem", "ReadItem", "HuggingFaceStorageWriter", "HuggingFaceStorageReader", "save_hf", "load_hf",
+           "consolidate_to_hf", "StateDictOptions", "get_model_state_dict", "get_optimizer_state_dict",
+           "get_state_dict", "set_model_state_dict", "set_optimizer_state_dict", "set_state_dict"]
 
 
 def __getattr__(name):

@@ -58,15 +58,13 @@ def _as_sharded(v) -> Optional[ShardedTensor]:
     try:
         from torch.distributed.tensor import DTensor, Shard
         if isinstance(v, DTensor):
+            # offsets from the placement arithmetic itself: two mesh dimensions sharding one tensor
+            # dimension, strided shards and uneven / empty trailing shards all come out right
+            from torch.distributed.tensor._utils import compute_local_shape_and_global_offset
+            shape, offs = compute_local_shape_and_global_offset(v.shape, v.device_mesh, v.placements)
             local = v.to_local()
-            offs = [0] * v.dim()
-            for mesh_dim, pl in enumerate(v.placements):
-                if isinstance(pl, Shard):
-                    coord = v.device_mesh.get_local_rank(mesh_dim)
-                    n = v.shape[pl.dim]
-                    size = v.device_mesh.size(mesh_dim)
-                    chunk = (n + size - 1) // size
-                    offs[pl.dim] += coord * chunk
+            if tuple(local.shape) != tuple(shape):   # padded local storage: keep the logical part
+                local = local[tuple(slice(0, n) for n in shape)]
             return ShardedTensor(local, tuple(v.shape), tuple(offs))
     except Exception:
         pass
@@ -98,11 +96,29 @@ def _jsonable(v) -> bool:
         return False
 
 
-def _write(checkpoint_id: str, rank: int, tensors: Dict[str, torch.Tensor], all_meta: Optional[List[dict]]) -> None:
+def _write(checkpoint_id: str, rank: int, tensors: Dict[str, torch.Tensor], all_meta: Optional[List[dict]],
+           wait_for: int = 0, timeout_s: float = 1800.0) -> None:
+    """Writes this rank's shard file; the coordinator (``all_meta`` given) writes ``.metadata`` LAST.
+    ``wait_for`` > 0 (asynchronous saves, where no collective orders the ranks' background threads):
+    every rank drops a ``.done_<rank>`` marker after its shard, and the coordinator waits for that many
+    markers before the metadata, so a directory with ``.metadata`` always holds every shard."""
+    import time
     os.makedirs(checkpoint_id, exist_ok=True)
     host = {k: t.detach().to("cpu") for k, t in tensors.items()}
     serialization.save_mega(host, os.path.join(checkpoint_id, f"__{rank}_0.distcp"))
+    if wait_for:
+        with open(os.path.join(checkpoint_id, f".done_{rank}"), "w") as f:
+            f.write("1")
     if all_meta is not None:
+        if wait_for:
+            deadline = time.time() + timeout_s
+            names = [os.path.join(checkpoint_id, f".done_{r}") for r in range(wait_for)]
+            while not all(os.path.exists(n) for n in names):
+                if time.time() > deadline:
+                    raise TimeoutError(f"async_save: not every rank finished its shard of {checkpoint_id!r}")
+                time.sleep(0.01)
+            for n in names:
+                os.remove(n)
         merged: Dict[str, dict] = {}
         for m in all_meta:
             for k, e in m.items():
@@ -135,26 +151,54 @@ def save(state_dict: Mapping[str, Any], *, checkpoint_id: Optional[str] = None, 
     objects, plain values) into the directory ``checkpoint_id``. A ``storage_writer`` or ``planner``
     (``FileSystemWriter``, ``DefaultSavePlanner`` ...: PyTorch's planner / storage layer) selects
     PyTorch's implementation and on-disk layout for the whole call."""
+    from .hf_storage import HuggingFaceStorageWriter, save_hf
+    from .planner import DefaultSavePlanner
+    if isinstance(storage_writer, HuggingFaceStorageWriter):
+        flat = _flatten(state_dict)
+        if any(_as_sharded(v) is not None for v in flat.values()):
+            raise ValueError("the Hugging Face layout stores whole tensors: gather sharded entries first "
+                             "(get_model_state_dict(..., StateDictOptions(full_state_dict=True))) or consolidate a "
+                             "sharded checkpoint with consolidate_to_hf")
+        return save_hf({k: v for k, v in flat.items() if isinstance(v, torch.Tensor)}, storage_writer.path,
+                       process_group=process_group, fqn_to_file_index=storage_writer.fqn_to_index_mapping)
     if isinstance(storage_writer, MegaStorageWriter):
         checkpoint_id, storage_writer = storage_writer.path, None
-    if storage_writer is not None or planner is not None:
+    own_planner = planner if isinstance(planner, DefaultSavePlanner) else None
+    if storage_writer is not None or (planner is not None and own_planner is None):
         import torch.distributed.checkpoint as tdcp
         return tdcp.save(state_dict, checkpoint_id=checkpoint_id, storage_writer=storage_writer, planner=planner,
                          process_group=process_group, **kw)
     world, rank = _world(process_group)
-    tensors, meta = _plan_save(_flatten(state_dict), rank)
-    all_meta = [meta]
+    flat = _flatten(state_dict)
+    pl = own_planner or DefaultSavePlanner()
+    local = pl.create_local_plan(rank, flat)
+    plans = [local]
     if world > 1:
-        all_meta = [None] * world
-        dist.all_gather_object(all_meta, meta, group=process_group)
-    _write(checkpoint_id, rank, tensors, all_meta if rank == 0 else None)
+        plans = [None] * world
+        dist.all_gather_object(plans, local, group=process_group)
+    final, meta = pl.create_global_plan(plans)    # every rank computes the same global plan
+    mine = {it.key for it in final[rank].items if it.kind != "object"}
+    tensors = {}
+    for k in mine:
+        st = _as_sharded(flat[k])
+        tensors[k] = st.local if st is not None else flat[k]
+    _write(checkpoint_id, rank, tensors, None)
+    if world > 1:
+        dist.barrier(group=process_group)   # every shard is on disk before the metadata vouches for it
+    if rank == 0:
+        tmp = os.path.join(checkpoint_id, META_FILE + ".tmp")
+        with open(tmp, "w") as f:
+            json.dump({"version": "1.0.0", "world_size": world, "state_dict_metadata": meta}, f)
+        os.replace(tmp, os.path.join(checkpoint_id, META_FILE))
     if world > 1:
         dist.barrier(group=process_group)
 
 
 def async_save(state_dict: Mapping[str, Any], *, checkpoint_id: str, process_group=None) -> Future:
     """Stage to host memory now, write in a background thread; the returned future resolves when
-    this rank's files are on disk (collectives happen before the function returns)."""
+    this rank's files are on disk (collectives happen before the function returns). ``.metadata``
+    appears only after every rank's shard is complete. Ranks are the ranks of ``process_group``:
+    groups that save at the same time need directories of their own."""
     world, rank = _world(process_group)
     tensors, meta = _plan_save(_flatten(state_dict), rank)
     staged = {k: t.detach().to("cpu", copy=True) for k, t in tensors.items()}
@@ -164,9 +208,15 @@ def async_save(state_dict: Mapping[str, Any], *, checkpoint_id: str, process_gro
         dist.all_gather_object(all_meta, meta, group=process_group)
     fut: Future = Future()
 
+    # a stale metadata file of an earlier save into this directory must not vouch for new shards
+    if rank == 0 and os.path.exists(os.path.join(checkpoint_id, META_FILE)):
+        os.remove(os.path.join(checkpoint_id, META_FILE))
+    if world > 1:
+        dist.barrier(group=process_group)
+
     def work():
         try:
-            _write(checkpoint_id, rank, staged, all_meta if rank == 0 else None)
+            _write(checkpoint_id, rank, staged, all_meta if rank == 0 else None, wait_for=world)
             fut.set_result(checkpoint_id)
         except Exception as e:  # pragma: no cover
             fut.set_exception(e)
@@ -188,8 +238,22 @@ def load(state_dict: Dict[str, Any], *, checkpoint_id: Optional[str] = None, pro
     entries receive the slices that overlap their ``[offsets, offsets + shape)`` window (whatever
     the sharding was at save time), Stateful objects get ``load_state_dict``. With a
     ``storage_reader`` or ``planner`` the call goes to PyTorch's implementation (see :func:`save`)."""
+    from .hf_storage import HuggingFaceStorageReader, load_hf
+    from .planner import DefaultLoadPlanner
+    if isinstance(storage_reader, HuggingFaceStorageReader):
+        flat = _flatten(state_dict)
+        got = load_hf(storage_reader.path, keys=set(flat))
+        for k, v in flat.items():
+            st = _as_sharded(v)
+            if st is not None:
+                st.local.copy_(got[k][tuple(slice(o, o + n) for o, n in zip(st.offsets, st.local.shape))])
+            elif isinstance(v, torch.Tensor):
+                v.copy_(got[k])
+        return state_dict
     if isinstance(storage_reader, MegaStorageReader):
         checkpoint_id, storage_reader = storage_reader.path, None
+    if isinstance(planner, DefaultLoadPlanner):
+        planner = None
     if storage_reader is not None or planner is not None:
         import torch.distributed.checkpoint as tdcp
         tdcp.load(state_dict, checkpoint_id=checkpoint_id, storage_reader=storage_reader, planner=planner,

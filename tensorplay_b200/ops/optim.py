@@ -104,3 +104,55 @@ def clip_coef_(sumsq: torch.Tensor, max_norm: float, coef: torch.Tensor,
         if norm_out is not None:
             norm_out.copy_(nrm)
         coef.copy_(torch.clamp(max_norm / (nrm + 1e-6), max=1.0))
+
+
+OPT_SGD, OPT_ADAGRAD, OPT_RMSPROP = 0, 1, 2
+FLAG_NESTEROV, FLAG_MAXIMIZE, FLAG_CENTERED, FLAG_FIRST_STEP, FLAG_MOMENTUM = 1, 2, 4, 8, 16
+
+
+def optim_multi_(algo: int, flags: int, params: List[torch.Tensor], s1: Optional[List[torch.Tensor]],
+                 s2: Optional[List[torch.Tensor]], s3: Optional[List[torch.Tensor]], grads: List[torch.Tensor],
+                 models: Optional[List[torch.Tensor]], *, lr: float, weight_decay: float = 0.0, a: float = 0.0,
+                 b: float = 0.0, eps: float = 0.0, grad_scale: float = 1.0,
+                 found_inf: Optional[torch.Tensor] = None) -> None:
+    """One multi-tensor step of SGD / Adagrad / RMSprop on CUDA (``params``: fp32 weights or master
+    copies; ``models``: the bf16 parameters to write alongside, or None). The meaning of ``a`` / ``b``
+    and of the state lists follows ``tpb_optim_multi``."""
+    if not params:
+        return
+    use_native(params[0], grads[0])
+    gb = grads[0].dtype == torch.bfloat16
+    assert all((g.dtype == torch.bfloat16) == gb for g in grads)
+    numel = (C.c_longlong * len(params))(*[t.numel() for t in params])
+    arr = lambda ts: _ptr_array(ts) if ts is not None else None  # noqa: E731
+    code = lib().tpb_optim_multi(algo, flags, len(params), _ptr_array(params), arr(s1), arr(s2), arr(s3),
+                                 _ptr_array(grads), arr(models), numel, int(gb), lr, weight_decay, a, b, eps,
+                                 float(grad_scale), ptr(found_inf), stream_ptr())
+    _native.check(code, "tpb_optim_multi")
+
+
+def amp_unscale_(grads: List[torch.Tensor], inv_scale: torch.Tensor, found_inf: torch.Tensor) -> None:
+    """``g *= inv_scale`` for every gradient (in place), ``found_inf[0] = 1`` if any holds inf / nan."""
+    by_dtype = {}
+    for g in grads:
+        by_dtype.setdefault(g.dtype, []).append(g)
+    for dt, gs in by_dtype.items():
+        if gs[0].is_cuda and dt in (torch.float32, torch.bfloat16) and all(g.is_contiguous() for g in gs):
+            use_native(gs[0])
+            numel = (C.c_longlong * len(gs))(*[g.numel() for g in gs])
+            code = lib().tpb_amp_unscale_multi(len(gs), _ptr_array(gs), numel, int(dt == torch.bfloat16),
+                                               inv_scale.data_ptr(), found_inf.data_ptr(), stream_ptr())
+            _native.check(code, "tpb_amp_unscale_multi")
+        else:
+            torch._amp_foreach_non_finite_check_and_unscale_(gs, found_inf, inv_scale)
+
+
+def amp_update_scale_(scale: torch.Tensor, growth_tracker: torch.Tensor, found_inf: torch.Tensor,
+                      growth_factor: float, backoff_factor: float, growth_interval: int) -> None:
+    if scale.is_cuda:
+        use_native(scale)
+        code = lib().tpb_amp_update_scale(scale.data_ptr(), growth_tracker.data_ptr(), found_inf.data_ptr(),
+                                          growth_factor, backoff_factor, int(growth_interval), stream_ptr())
+        _native.check(code, "tpb_amp_update_scale")
+    else:
+        torch._amp_update_scale_(scale, growth_tracker, found_inf, growth_factor, backoff_factor, growth_interval)

@@ -1,10 +1,11 @@
-"""``optim``: the optimizer zoo. AdamW / Adam run the fused multi-tensor sm_100a kernel on CUDA
-(fp32 master + moments, bf16 parameter emit in the same pass); the rest of the zoo is torch's;
-``Muon`` is implemented here (the reference ships it in tensorplay/optim, P3)."""
-from torch.optim import (ASGD, LBFGS, SGD, Adadelta, Adafactor, Adagrad, Adamax, NAdam, Optimizer,  # noqa: F401
-                         RAdam, RMSprop, Rprop, SparseAdam, lr_scheduler, swa_utils)
+"""``optim``: the optimizer zoo. AdamW / Adam, SGD, Adagrad and RMSprop run fused multi-tensor
+sm_100a kernels on CUDA (fp32 state and master weights, bf16 parameter emit in the same pass); the
+rest of the zoo is torch's; ``Muon`` is implemented here (the reference ships it in tensorplay/optim, P3)."""
+from torch.optim import (ASGD, LBFGS, Adadelta, Adafactor, Adamax, NAdam, Optimizer,  # noqa: F401
+                         RAdam, Rprop, SparseAdam, lr_scheduler, swa_utils)
 
 from .adamw import Adam, AdamW
+from .fused import SGD, Adagrad, RMSprop
 from .muon import Muon
 
 __all__ = ["ASGD", "LBFGS", "SGD", "Adadelta", "Adafactor", "Adagrad", "Adamax", "NAdam", "Optimizer",

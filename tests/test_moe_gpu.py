@@ -84,3 +84,33 @@ def test_expert_parallel_single_rank_matches_reference():
         assert _rel(w.grad, wr.grad) < 2e-2
         assert _rel(wgu.grad, gur.grad) < 2e-2
         assert _rel(wd.grad, dr.grad) < 2e-2
+
+
+def test_token_switch_dispatch_combine_have_gradients():
+    """``TokenSwitch.dispatch`` / ``combine`` composed with a per-row expert function against the
+    dense formula, forward and backward (tokens, expert output rows and routing weights)."""
+    from tensorplay_b200.distributed._token_switch import TokenSwitch
+    torch.manual_seed(0)
+    T, H, E, k = 96, 256, 4, 2
+    sw = TokenSwitch(E, k, H, T)
+    x = torch.randn(T, H, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    logits = torch.randn(T, E, device=DEV)
+    scale = torch.linspace(0.5, 2.0, E, device=DEV)          # "expert e" multiplies its rows by scale[e]
+    r = sw.create_routing(logits)
+    r.topk_weight = r.topk_weight.to(torch.bfloat16).requires_grad_()
+    rows = sw.dispatch(x, r)                                  # [cap, H], expert-sorted
+    offs = r.offsets.tolist()
+    per_row = torch.zeros(rows.shape[0], 1, device=DEV)
+    for e in range(E):
+        per_row[offs[e]: offs[e + 1]] = scale[e]
+    y = sw.combine((rows.float() * per_row).to(torch.bfloat16), r)
+    g = torch.randn_like(y)
+    y.backward(g)
+    O.check_status()
+    xr = x.detach().float().requires_grad_()
+    wr = r.topk_weight.detach().float().requires_grad_()
+    ref = (xr[:, None, :] * scale[r.topk_idx][..., None] * wr[..., None]).sum(1)
+    ref.backward(g.float())
+    assert _rel(y, ref) < 2e-2
+    assert _rel(x.grad, xr.grad) < 2e-2
+    assert _rel(r.topk_weight.grad, wr.grad) < 2e-2
