@@ -1,9 +1,11 @@
 """Elastic training: the local agent that supervises and restarts workers lives in
-``distributed.run`` (``tprun``); events, metrics, timers and the rendezvous registry are torch's
-(tensorplay/distributed/elastic/**)."""
-from torch.distributed.elastic import events, metrics, multiprocessing, rendezvous, timer, utils  # noqa: F401
+``distributed.run`` (``tprun``); the dynamic rendezvous over this package's stores, the file-based
+watchdog timers and the agent's health-check server are implemented in the sub-packages here;
+events, metrics and the multiprocessing helpers are torch's (tensorplay/distributed/elastic/**)."""
+from torch.distributed.elastic import events, metrics, multiprocessing, utils  # noqa: F401
 
 from ..run import ChildFailedError, LaunchConfig, LocalElasticAgent, elastic_launch  # noqa: F401
+from . import agent, rendezvous, timer  # noqa: F401
 
 __all__ = ["ChildFailedError", "LaunchConfig", "LocalElasticAgent", "elastic_launch", "events", "metrics",
-           "multiprocessing", "rendezvous", "timer", "utils"]
+           "multiprocessing", "rendezvous", "timer", "utils", "agent"]

@@ -1,0 +1,12 @@
+"""Elastic agents: the launcher of this framework is ``distributed.run.LocalElasticAgent``; the
+health-check server of an agent lives in ``agent.server.health_check_server``; other names resolve
+to PyTorch's package of the same role."""
+from . import server  # noqa: F401
+
+
+def __getattr__(name):
+    import importlib
+    try:
+        return getattr(importlib.import_module("torch.distributed.elastic.agent"), name)
+    except (ImportError, AttributeError):
+        raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
