@@ -3,14 +3,22 @@ from torch.nn import *  # noqa: F401,F403
 from torch.nn import Module, Parameter, init, utils  # noqa: F401
 import torch.nn as _tnn
 
-from . import cache, functional, generation  # noqa: F401
+import importlib as _importlib
+
+# ``from torch.nn import *`` above has already bound ``functional``, ``attention``, ``parallel`` and
+# ``modules`` to torch's sub-packages, and ``from . import x`` keeps an existing attribute: this
+# package's own sub-modules of those names are imported by path and bound explicitly.
+functional = _importlib.import_module(__name__ + ".functional")
+attention = _importlib.import_module(__name__ + ".attention")
+modules = _importlib.import_module(__name__ + ".modules")
+from . import cache, generation  # noqa: F401,E402
 from .cache import (Cache, DynamicCache, LinearStateCache, PagedCache, QuantizedCache,
                     SlidingWindowCache, StaticCache)
 from .generation import generate, sample, top_k_top_p_filtering
 from .modules import (DecoderLM, CausalEncoderDecoder, CompressedSparseAttention, CrossAttention, GatedDeltaNet, GroupedQueryAttention, KimiDeltaAttention, LayerNorm, Linear,
                       MultiheadLatentAttention, RMSNorm, RotaryEmbedding, SwiGLUMLP, TransformerBlock,
                       apply_rotary_emb, chunk_gated_delta_rule, gated_delta_rule)
-from . import parallel  # noqa: F401,E402
+parallel = _importlib.import_module(__name__ + ".parallel")
 
 
 def __getattr__(name):

@@ -78,12 +78,14 @@ def scaled_dot_product_attention(query, key, value, attn_mask=None, dropout_p: f
                                  is_causal: bool = False, scale: Optional[float] = None,
                                  enable_gqa: bool = False):
     """``[B, H, T, D]`` attention. bf16 CUDA inputs without an explicit mask or dropout run on the
-    tcgen05 flash kernels (grouped heads natively); anything else takes torch's path."""
-    D = query.shape[-1]
-    if (attn_mask is None and dropout_p == 0.0 and query.is_cuda and query.dtype == torch.bfloat16
-            and query.dim() == 4 and D in (64, 128) and query.shape[1] % key.shape[1] == 0):
-        o = _flash_attention(query.transpose(1, 2), key.transpose(1, 2), value.transpose(1, 2),
-                             causal=is_causal, scale=scale)
+    tcgen05 flash kernels (grouped heads natively); anything else takes the fp32 formula or torch's
+    library kernels, as ``nn.attention.sdpa_kernel`` allows."""
+    from .attention import SDPBackend, _flash, select_backend
+    backend = select_backend(query, key, value, attn_mask, dropout_p)
+    if backend == SDPBackend.FLASH_ATTENTION:
+        import math as _math
+        sc = scale if scale is not None else 1.0 / _math.sqrt(query.shape[-1])
+        o = _flash(query.transpose(1, 2), key.transpose(1, 2), value.transpose(1, 2), is_causal, sc)
         return o.transpose(1, 2)
     if enable_gqa and query.shape[1] != key.shape[1]:
         g = query.shape[1] // key.shape[1]
@@ -95,8 +97,16 @@ def scaled_dot_product_attention(query, key, value, attn_mask=None, dropout_p: f
         j = torch.arange(Tk, device=query.device).view(1, -1)
         attn_mask = j <= i + (Tk - Tq)
         is_causal = False
-    return _F.scaled_dot_product_attention(query, key, value, attn_mask=attn_mask,
-                                           dropout_p=dropout_p, is_causal=is_causal, scale=scale)
+    if backend == SDPBackend.MATH or not query.is_cuda:
+        tb = [torch.nn.attention.SDPBackend.MATH]
+    elif backend == SDPBackend.CUDNN_ATTENTION:
+        tb = [torch.nn.attention.SDPBackend.CUDNN_ATTENTION, torch.nn.attention.SDPBackend.EFFICIENT_ATTENTION,
+              torch.nn.attention.SDPBackend.MATH]
+    else:
+        tb = [torch.nn.attention.SDPBackend.EFFICIENT_ATTENTION, torch.nn.attention.SDPBackend.MATH]
+    with torch.nn.attention.sdpa_kernel(tb):
+        return _F.scaled_dot_product_attention(query, key, value, attn_mask=attn_mask,
+                                               dropout_p=dropout_p, is_causal=is_causal, scale=scale)
 
 
 def fused_rope(x, cos, sin, position_ids=None, interleaved: bool = False):
