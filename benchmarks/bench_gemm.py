@@ -8,6 +8,7 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import tensorplay_b200.ops as O  # noqa: E402
+from tensorplay_b200.ops._common import lib as _lib  # noqa: E402
 
 
 def timeit(fn, iters=20, warmup=5):
@@ -40,6 +41,10 @@ def main():
         fl = 2.0 * M * N * K
         for name, fn in [
             ("tn", lambda: O.gemm(a, b, out=out)),
+            ("tn_single", lambda: O.gemm(a, b, out=out, impl="single")),
+            ("tn_pair", lambda: O.gemm(a, b, out=out, impl="pair")),
+            ("nn_bmn_pair", lambda: O.gemm(a, bt, b_mn=True, out=out, impl="pair")),
+            ("amn_bmn_pair", lambda: O.gemm(at, bt, a_mn=True, b_mn=True, out=out, impl="pair")),
             ("nn_bmn", lambda: O.gemm(a, bt, b_mn=True, out=out)),
             ("amn_bmn", lambda: O.gemm(at, bt, a_mn=True, b_mn=True, out=out)),
             ("cublas", lambda: torch.matmul(a, b.t(), out=out)),
@@ -47,6 +52,7 @@ def main():
             ms = timeit(fn)
             res[name + "_tflops"] = round(fl / ms / 1e9, 1)
         O.check_status()
+        res["resident_pairs"] = _lib().tpb_gemm_pair_resident()
         print(json.dumps(res), flush=True)
 
 

@@ -446,7 +446,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (w.nsplit > 1) {
         sk_tile = p.sk_ws + ((size_t)w.tail_idx * (w.nsplit - 1)) * (size_t)(kBlockM * BLOCK_N);
         if (w.split > 0) {
-          float* dst = sk_tile + (size_t)(w.split - 1) * (kBlockM * BLOCK_N) + (size_t)(q * 32 + lane) * BLOCK_N;
+          // layout [column / 4][row][4]: the 32 lanes of a warp (32 rows) write 512 contiguous bytes
+          float* dst = sk_tile + (size_t)(w.split - 1) * (kBlockM * BLOCK_N) + (size_t)(q * 32 + lane) * 4;
 #pragma unroll 1
           for (int c = 0; c < BLOCK_N; c += 32) {
             uint32_t r[32];
@@ -454,7 +455,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; i += 4)
-              *reinterpret_cast<float4*>(dst + c + i) =
+              *reinterpret_cast<float4*>(dst + (size_t)((c + i) >> 2) * (kBlockM * 4)) =
                   make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
                               __uint_as_float(r[i + 3]));
           }
@@ -487,10 +488,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
           if (sk_tile) {
             for (int h = 0; h < w.nsplit - 1; ++h) {
-              const float* src = sk_tile + (size_t)h * (kBlockM * BLOCK_N) + (size_t)(q * 32 + lane) * BLOCK_N + c;
+              const float* src = sk_tile + (size_t)h * (kBlockM * BLOCK_N) + (size_t)(q * 32 + lane) * 4;
 #pragma unroll
               for (int i = 0; i < 32; i += 4) {
-                float4 t4 = __ldcg(reinterpret_cast<const float4*>(src + i));
+                float4 t4 = __ldcg(reinterpret_cast<const float4*>(src + (size_t)((c + i) >> 2) * (kBlockM * 4)));
                 v[i] += t4.x; v[i + 1] += t4.y; v[i + 2] += t4.z; v[i + 3] += t4.w;
               }
             }
@@ -727,6 +728,10 @@ int sm_count() {
 // per device; GEMMs that use it must be stream-ordered with respect to each other.
 static float* g_sk_ws = nullptr;
 static uint32_t* g_sk_flags = nullptr;
+void splitk_workspace(float** ws, uint32_t** flags) {
+  *ws = g_sk_ws;
+  *flags = g_sk_flags;
+}
 
 template <int BLOCK_N, bool A_MN, bool B_MN>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
@@ -820,10 +825,28 @@ int gemm_bf16_dispatch(const void* A, const void* B, void* C, const void* bias, 
 
 }  // namespace tpb
 
+// Shapes that go to the CTA-pair kernel when nothing pins the choice: at least `g_pair_min_tiles`
+// tiles of 256 x 256 (one full wave of CTA pairs by default) and A stored K-major (with both
+// operands MN-major the two kernels measure the same). 0 = never.
+static int g_pair_min_tiles = 74;
+extern "C" void tpb_gemm_set_pair_min_tiles(int tiles) { g_pair_min_tiles = tiles; }
+
+extern "C" int tpb_gemm_bf16_single(const void* A, const void* B, void* C, const void* bias, int M, int N,
+                                    int K, int lda, int ldb, int ldc, int a_mn, int b_mn, int out_f32,
+                                    int bias_f32, int accumulate, float alpha, uint32_t* status,
+                                    void* stream) {
+  return tpb::gemm_bf16_dispatch(A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_f32,
+                                 bias_f32, accumulate, alpha, nullptr, 0, 0, 0, status,
+                                 static_cast<cudaStream_t>(stream), nullptr);
+}
+
 extern "C" int tpb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N,
                              int K, int lda, int ldb, int ldc, int a_mn, int b_mn, int out_f32,
                              int bias_f32, int accumulate, float alpha, uint32_t* status,
                              void* stream) {
+  if (g_pair_min_tiles > 0 && !a_mn && (long long)((M + 255) / 256) * ((N + 255) / 256) >= g_pair_min_tiles)
+    return tpb::gemm_pair_dispatch(A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_f32, bias_f32,
+                                   accumulate, alpha, 0, status, static_cast<cudaStream_t>(stream));
   return tpb::gemm_bf16_dispatch(A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_f32,
                                  bias_f32, accumulate, alpha, nullptr, 0, 0, 0, status,
                                  static_cast<cudaStream_t>(stream), nullptr);

@@ -46,6 +46,11 @@ struct GemmFused {
   __nv_bfloat16* rs_out;
   unsigned long long wait_ns;
 };
+// The registered split-K workspace (null when none): fp32 partial tiles and one flag per tail tile.
+void splitk_workspace(float** ws, uint32_t** flags);
+int gemm_pair_dispatch(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda,
+                       int ldb, int ldc, int a_mn, int b_mn, int out_f32, int bias_f32, int accumulate,
+                       float alpha, int max_ctas, uint32_t* status, cudaStream_t stream, int block_n = 0);
 int gemm_bf16_dispatch(const void* A, const void* B, void* C, const void* bias, int M, int N,
                        int K, int lda, int ldb, int ldc, int a_mn, int b_mn, int out_f32,
                        int bias_f32, int accumulate, float alpha, const uint32_t* b_flags,

@@ -25,6 +25,12 @@ U32 = C.c_uint32
 
 _KERNEL_SIGS = {
     "tpb_gemm_bf16": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P],
+    "tpb_gemm_bf16_pair": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P],
+    "tpb_gemm_bf16_single": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P],
+    "tpb_gemm_set_pair_min_tiles": [I],
+    "tpb_gemm_pair_resident": [],
+    "tpb_gemm_pair_block_n": [I],
+    "tpb_gemm_pair_trace": [P],
     "tpb_gemm_set_splitk_workspace": [P, P],
     "tpb_rmsnorm_fwd": [P, P, P, P, P, P, I, I, LL, LL, F, P],
     "tpb_rmsnorm_bwd_grid": [I, I],

@@ -48,12 +48,13 @@ def _rowmajor(t: torch.Tensor) -> torch.Tensor:
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
          accumulate: bool = False, out_dtype: torch.dtype = torch.bfloat16,
-         alpha: float = 1.0) -> torch.Tensor:
+         alpha: float = 1.0, impl: Optional[str] = None) -> torch.Tensor:
     """``C[m, n] (+)= alpha * sum_k A(m, k) * B(n, k) (+ bias[n])``.
 
     ``a`` is ``[M, K]`` (``a_mn=False``) or stored transposed ``[K, M]`` (``a_mn=True``);
     ``b`` is ``[N, K]`` or stored ``[K, N]`` (``b_mn=True``). Operands are bf16, the
-    accumulator fp32, ``out`` bf16 or fp32.
+    accumulator fp32, ``out`` bf16 or fp32. ``impl`` pins the kernel: ``"pair"`` = the CTA-pair
+    (``cta_group::2``) kernel, ``"single"`` = the one-CTA kernel, ``None`` = chosen by shape.
     """
     if a_mn:
         K, M = a.shape
@@ -86,12 +87,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if K % 8 or a.stride(0) % 8 or b.stride(0) % 8:
         raise ValueError("gemm: leading dimensions must be multiples of 8 elements")
     st = status_word(a.device)
-    code = lib().tpb_gemm_bf16(
+    fn = {None: "tpb_gemm_bf16", "pair": "tpb_gemm_bf16_pair", "single": "tpb_gemm_bf16_single"}[impl]
+    code = getattr(lib(), fn)(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), ptr(bias), M, N, K,
         a.stride(0), b.stride(0), out.stride(0), int(a_mn), int(b_mn),
         int(out.dtype == torch.float32), int(bias is not None and bias.dtype == torch.float32),
         int(accumulate), float(alpha), st.data_ptr(), stream_ptr())
-    _native.check(code, "tpb_gemm_bf16")
+    _native.check(code, fn)
     return out
 
 

@@ -34,6 +34,63 @@ def test_gemm_layouts(a_mn, b_mn, M, N, K):
     assert _rel(out32, ref) < 1e-4
 
 
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 320), (384, 200, 136), (1000, 328, 72),
+                                   (8192, 4096, 1024), (2048, 2304, 4096 + 8)])
+@pytest.mark.parametrize("block_n", [256, 128])
+def test_gemm_cta_pair(a_mn, b_mn, M, N, K, block_n):
+    """The cta_group::2 kernel: 256-row tiles computed by two CTAs, each staging half of B."""
+    from tensorplay_b200.ops._common import lib
+    torch.manual_seed(3)
+    lib().tpb_gemm_pair_block_n(block_n)
+    try:
+        _check_gemm_cta_pair(a_mn, b_mn, M, N, K)
+    finally:
+        lib().tpb_gemm_pair_block_n(0)
+
+
+def _check_gemm_cta_pair(a_mn, b_mn, M, N, K):
+    if (a_mn and M % 8) or (b_mn and N % 8):
+        pytest.skip("MN-major operands need a leading dimension that is a multiple of 8")
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    A = a.t().contiguous() if a_mn else a
+    B = b.t().contiguous() if b_mn else b
+    out32 = O.gemm(A, B, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32, impl="pair")
+    O.check_status()
+    assert _rel(out32, ref) < 1e-4
+    bias = torch.randn(N, device=DEV, dtype=torch.float32)
+    out = torch.ones(M, N, device=DEV, dtype=torch.bfloat16)
+    O.gemm(A, B, a_mn=a_mn, b_mn=b_mn, out=out, bias=bias, accumulate=True, alpha=0.5, impl="pair")
+    O.check_status()
+    assert _rel(out, 0.5 * ref + bias + 1.0) < 5e-3
+
+
+@pytest.mark.parametrize("M,N,K", [(4096, 4096, 4096), (512, 1024, 8192), (4096, 6144, 2048), (1280, 2304, 1024 + 64)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (True, True)])
+def test_gemm_cta_pair_split_tail(M, N, K, a_mn, b_mn):
+    """CTA-pair kernel with the last wave split along K: same result as the unsplit run, call after call."""
+    from tensorplay_b200.ops.gemm import enable_splitk
+    torch.manual_seed(6)
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
+    A = a.t().contiguous() if a_mn else a
+    B = b.t().contiguous() if b_mn else b
+    enable_splitk(enable=False)
+    base = O.gemm(A, B, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32, impl="pair")
+    enable_splitk()
+    try:
+        for _ in range(3):  # flags must re-arm between calls
+            out = O.gemm(A, B, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32, impl="pair")
+            O.check_status()
+            assert _rel(out, base) < 2e-5
+        outb = O.gemm(A, B, a_mn=a_mn, b_mn=b_mn, impl="pair")
+        assert _rel(outb, a.float() @ b.float().t()) < 5e-3
+    finally:
+        enable_splitk(enable=False)
+
+
 def test_gemm_bias_accumulate_alpha():
     torch.manual_seed(1)
     M, N, K = 512, 768, 320
