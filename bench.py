@@ -32,7 +32,9 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--model", default="llama3_8b", choices=["llama3_8b", "tiny"])
+    ap.add_argument("--model", default="llama3_8b", choices=["llama3_8b", "tiny", "qwen3_moe"],
+                    help="llama3_8b = the headline config; qwen3_moe = the Qwen3-30B-A3B-shape MoE config with expert "
+                         "parallelism over all ranks (same JSON contract, its own metric name)")
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--micro-batch", type=int, default=1)
     ap.add_argument("--comm", default="auto", choices=["auto", "symm", "torch"])
@@ -46,14 +48,30 @@ def parse_args():
 
 
 def reference_arm(args):
+    """Runs the unmodified reference from ``baseline/_ref`` when an install exists there; prints the
+    ``unavailable`` line otherwise. The install was attempted offline (pip --no-index --no-build-isolation
+    from a copy of the source tree): 565 of its 567 objects compile for sm_100 once the cuDNN-frontend and
+    CUTLASS headers of this image are staged into the copy, then the build stops because
+    src/distributed/bindings.cpp and src/distributed/mpi/ProcessGroupMPI.cpp include gloo headers
+    unconditionally (also with gloo, MPI and the distributed package switched off in CMake) and no gloo
+    source or headers exist on a machine without network."""
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
     why = None
     if not os.path.isdir(os.path.join(ref_dir, "tensorplay")):
-        why = ("reference not installed: its CUDA build stops at CMake configure (cuDNN frontend, "
-               "CUTLASS, flash-attention and gloo submodules are empty in the offline source tree)")
+        why = ("reference not installed: offline build compiles 565/567 objects for sm_100, then fails on "
+               "<gloo/context.h> (src/distributed/bindings.cpp, src/distributed/mpi/ProcessGroupMPI.cpp include "
+               "gloo unconditionally; no gloo headers on this image, no network)")
+    else:
+        sys.path.insert(0, ref_dir)
+        try:
+            import tensorplay  # noqa: F401
+            why = ("reference imports, but no Llama-3-8B FSDP training recipe of it has been validated on this "
+                   "box; not timed")
+        except Exception as e:  # pragma: no cover - depends on an install that cannot be produced offline
+            why = f"reference import failed: {type(e).__name__}: {str(e)[:160]}"
     rank = int(os.environ.get("RANK", "0"))
     if rank == 0:
-        print(json.dumps({"impl": "reference", "unavailable": why or "reference import failed"}))
+        print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
 
 
@@ -132,22 +150,44 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
 
-    if args.model == "tiny":
-        cfg = LlamaConfig.tiny(max_seq_len=args.seq)
-        name = "llama-tiny"
-    else:
-        cfg = LlamaConfig.llama3_8b(max_seq_len=args.seq)
-        name = "Llama-3-8B-shape"
-    if args.layers is not None:
-        cfg.num_layers = args.layers
-        name += f"-{args.layers}layers(debug)"
-
-    torch.manual_seed(1234)
-    model = Llama(cfg, device=dev, dtype=torch.bfloat16)
-    model.reset_parameters(seed=1234)
-    engine = FSDPEngine(model, AdamWConfig(lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1),
-                        comm=args.comm, activation_checkpointing=True if args.ac == "full" else "selective")
     B, T = args.micro_batch, args.seq
+    opt = AdamWConfig(lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    torch.manual_seed(1234)
+    if args.model == "qwen3_moe":
+        from tensorplay_b200.models.qwen3_moe import Qwen3MoE, Qwen3MoEConfig
+        cfg = Qwen3MoEConfig.qwen3_30b_a3b(max_seq_len=T)
+        name = "Qwen3-30B-A3B-shape"
+        metric = "train tokens/s/box, Qwen3-30B-A3B-shape MoE expert-parallel bf16, max over ranks"
+        if args.layers is not None:
+            cfg.num_layers = args.layers
+            name += f"-{args.layers}layers(debug)"
+        model = Qwen3MoE(cfg, device=dev, dtype=torch.bfloat16)
+        model.reset_parameters(seed=1234)
+        # arena head-room for the expert-parallel workspace (3 row buffers of `world` x the mean load)
+        ws_bytes = 3 * (B * T * cfg.top_k * world + 4096) * cfg.hidden_size * 2 + (256 << 20)
+        engine = FSDPEngine(model, opt, comm=args.comm, activation_checkpointing=True, symm_extra_bytes=ws_bytes)
+        # drop-less for any routing: one rank may receive every token of the box
+        model.attach_workspace(B * T, capacity_factor=float(world))
+        parallelism = f"ep{world} experts, fsdp{world} attention/embeddings"
+        ac_text = "per block, full recompute"
+    else:
+        if args.model == "tiny":
+            cfg = LlamaConfig.tiny(max_seq_len=T)
+            name = "llama-tiny"
+        else:
+            cfg = LlamaConfig.llama3_8b(max_seq_len=T)
+            name = "Llama-3-8B-shape"
+        metric = "train tokens/s/box, Llama-3-8B-shape FSDP bf16, max over ranks"
+        if args.layers is not None:
+            cfg.num_layers = args.layers
+            name += f"-{args.layers}layers(debug)"
+        model = Llama(cfg, device=dev, dtype=torch.bfloat16)
+        model.reset_parameters(seed=1234)
+        engine = FSDPEngine(model, opt, comm=args.comm,
+                            activation_checkpointing=True if args.ac == "full" else "selective")
+        parallelism = f"fsdp{world}" if world > 1 else "single-gpu (fsdp1)"
+        ac_text = ("per block, full recompute" if args.ac == "full" else
+                   "per block, selective: GEMM and attention outputs kept, norms / RoPE / SwiGLU recomputed")
     gen = torch.Generator(device="cpu")
     gen.manual_seed(100 + rank)
     n_batches = max(args.steps, 1)
@@ -206,16 +246,17 @@ def main():
     value = tokens_per_step * args.steps / (ms_max / 1e3)
     e2e_value = tokens_per_step * args.steps / (e2e_ms_max / 1e3)
     if rank == 0:
-        flops = cfg.flops_per_token(T, backward=True, recompute=False) * tokens_per_step * args.steps
+        flops = (cfg.flops_per_token(T, backward=True, recompute=False) * tokens_per_step * args.steps
+                 if hasattr(cfg, "flops_per_token") else 0.0)
         out = {
-            "metric": "train tokens/s/box, Llama-3-8B-shape FSDP bf16, max over ranks",
+            "metric": metric,
             "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms_max / args.steps, 3),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic (uniform random token ids, random-init N(0, 0.02) weights)",
             "config": {"model": name, "global_batch": world * B, "seq_len": T,
-                       "parallelism": f"fsdp{world}" if world > 1 else "single-gpu (fsdp1)",
-                       "activation_checkpointing": ("per block, full recompute" if args.ac == "full" else "per block, selective: GEMM and attention outputs kept, norms / RoPE / SwiGLU recomputed"), "optimizer": "AdamW fp32 state + fp32 master",
+                       "parallelism": parallelism,
+                       "activation_checkpointing": ac_text, "optimizer": "AdamW fp32 state + fp32 master",
                        "comm": engine.comm_kind,
                        "l2": "per-step working set (parameters + optimizer state, >100 GB/box) "
                              "exceeds the 126 MB L2; no explicit flush"},

@@ -23,7 +23,7 @@ namespace tpb {
 
 constexpr int kPairM = 256;   // rows of a tile (128 per CTA)
 constexpr int kPairK = 64;
-constexpr int kPairThreads = 192;  // warp 0 TMA, warp 1 MMA (leader) / relay (peer), warps 2..5 epilogue
+constexpr int kPairThreads = 192;  // warp 0 TMA, warp 1 TMEM owner + MMA issue (leader), warps 2..5 epilogue
 constexpr int kPairABytes = 128 * kPairK * 2;
 // BN = columns of a tile (256 or 128); each CTA stages BN / 2 of them.
 template <int BN>

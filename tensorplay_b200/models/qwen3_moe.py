@@ -52,6 +52,20 @@ class Qwen3MoEConfig:
         return Qwen3MoEConfig(**base)
 
 
+def _qwen3_flops_per_token(self, seq_len: int, backward: bool = True, recompute: bool = False) -> float:
+    """Model FLOPs per token: 2 x the matmul parameters a token activates (attention projections, router,
+    ``top_k`` experts, LM head) plus causal attention, x3 with backward."""
+    H, D = self.hidden_size, self.head_dim
+    per_layer = (H * (self.num_heads + 2 * self.num_kv_heads) * D + self.num_heads * D * H
+                 + H * self.num_experts + self.top_k * 3 * H * self.moe_intermediate)
+    mm = self.num_layers * per_layer + self.vocab_size * H
+    fwd = 2.0 * mm + 2.0 * 2 * self.num_layers * self.num_heads * D * seq_len / 2
+    return fwd * (1.0 + (2.0 if backward else 0.0) + (1.0 if recompute else 0.0))
+
+
+Qwen3MoEConfig.flops_per_token = _qwen3_flops_per_token
+
+
 class _AuxLoss(torch.autograd.Function):
     """Identity on ``x`` that injects d(aux)/d(router) into backward with weight ``scale``, so the
     auxiliary loss is optimised without threading a scalar through every layer boundary."""
