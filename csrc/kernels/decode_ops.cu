@@ -23,7 +23,7 @@ embedding_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __r
     const int c = (int)(i - r * vec_per_row);
     long long id = ids[r];
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (id >= 0 && id < V) v = __ldg(reinterpret_cast<const uint4*>(table + id * H) + c);
+    if (TPB_DBG_CHECK(id >= 0 && id < V, 40)) v = __ldg(reinterpret_cast<const uint4*>(table + id * H) + c);
     reinterpret_cast<uint4*>(out + r * H)[c] = v;
   }
 }
@@ -39,7 +39,7 @@ embedding_bwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __r
     const long long r = i / pairs;
     const int c = (int)(i - r * pairs);
     const long long id = ids[r];
-    if (id < 0 || id >= V) continue;
+    if (!TPB_DBG_CHECK(id >= 0 && id < V, 41)) continue;
     const __nv_bfloat162 g = reinterpret_cast<const __nv_bfloat162*>(dy + r * H)[c];
     if (F32) {
       float* d = static_cast<float*>(dw) + id * H + 2 * c;
@@ -78,7 +78,7 @@ __global__ void __launch_bounds__(256) kv_append_kernel(const KvAppendParams p) 
     long long off;
     if (p.block_table) {
       const int blk = at / p.block;
-      if (blk >= p.max_blocks) continue;
+      if (!TPB_DBG_CHECK(blk < p.max_blocks, 42)) continue;
       const int phys = p.block_table[(long long)b * p.max_blocks + blk];
       if (phys < 0) continue;
       off = (long long)phys * p.d_b + (long long)(at % p.block) * p.d_t;

@@ -714,6 +714,14 @@ int make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
+#ifdef TPB_KERNEL_DEBUG
+static DbgSetter g_dbg_setters[64];
+static int g_dbg_n = 0;
+void dbg_register_setter(DbgSetter fn) {
+  if (g_dbg_n < 64) g_dbg_setters[g_dbg_n++] = fn;
+}
+#endif
+
 int sm_count() {
   static int n = 0;
   if (n == 0) {
@@ -830,6 +838,27 @@ int gemm_bf16_dispatch(const void* A, const void* B, void* C, const void* bias, 
 // operands MN-major the two kernels measure the same). 0 = never.
 static int g_pair_min_tiles = 74;
 extern "C" void tpb_gemm_set_pair_min_tiles(int tiles) { g_pair_min_tiles = tiles; }
+
+// 1 if this library was built with index checks (TPB_KERNEL_DEBUG), and the word they report to.
+extern "C" int tpb_debug_build() {
+#ifdef TPB_KERNEL_DEBUG
+  return 1;
+#else
+  return 0;
+#endif
+}
+extern "C" int tpb_debug_set_status(uint32_t* status) {
+#ifdef TPB_KERNEL_DEBUG
+  for (int i = 0; i < tpb::g_dbg_n; ++i) {
+    const int r = tpb::g_dbg_setters[i](status);
+    if (r) return r;
+  }
+  return 0;
+#else
+  (void)status;
+  return -1;
+#endif
+}
 
 extern "C" int tpb_gemm_bf16_single(const void* A, const void* B, void* C, const void* bias, int M, int N,
                                     int K, int lda, int ldb, int ldc, int a_mn, int b_mn, int out_f32,

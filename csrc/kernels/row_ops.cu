@@ -583,7 +583,7 @@ cross_entropy_kernel(const __nv_bfloat16* __restrict__ logits, const long long* 
   for (int i = 0; i < kCeThreads / 32; ++i)
     gs += (sm[i] == -INFINITY) ? 0.f : ss[i] * __expf(sm[i] - gm);
   const float lse = gm + __logf(gs);
-  const bool ignored = (tgt == ignore_index) || tgt < 0 || tgt >= V;
+  const bool ignored = (tgt == ignore_index) || !TPB_DBG_CHECK(tgt >= 0 && tgt < V, 43);
   if (threadIdx.x == 0) {
     if (lse_out) lse_out[row] = lse;
     if (loss) loss[row] = ignored ? 0.f : lse - __bfloat162float(lr[tgt]);
@@ -619,7 +619,7 @@ cross_entropy_bwd_kernel(const __nv_bfloat16* __restrict__ logits,
                          long long stride, long long ignore_index) {
   const long long row = blockIdx.y;
   const long long tgt = target[row];
-  const bool ignored = (tgt == ignore_index) || tgt < 0 || tgt >= V;
+  const bool ignored = (tgt == ignore_index) || !TPB_DBG_CHECK(tgt >= 0 && tgt < V, 43);
   float g = g_rows ? g_rows[row] : 1.f;
   if (g_scalar) g *= *g_scalar;
   if (scale) g *= *scale;

@@ -19,7 +19,34 @@ enum : uint32_t {
   kStatusMbarTimeout = 1,
   kStatusFlagTimeout = 2,
   kStatusBadArgs = 3,
+  kStatusBounds = 4,   // debug build: an index check failed (the access was skipped)
 };
+
+// Index checks of the debug build (-DTPB_KERNEL_DEBUG): TPB_DBG_CHECK(cond, site) evaluates to
+// `cond`; when it is false the debug build also records kStatusBounds | site << 8 in the status
+// word registered with tpb_debug_set_status, so that a guard which silently skips an access in the
+// release build names its site in the debug build. Never traps: the caller skips the access.
+#ifdef TPB_KERNEL_DEBUG
+static __device__ uint32_t* g_dbg_status = nullptr;
+__device__ __forceinline__ bool dbg_check(bool cond, uint32_t site) {
+  if (!cond && g_dbg_status) atomicCAS(g_dbg_status, 0u, kStatusBounds | (site << 8));
+  return cond;
+}
+#define TPB_DBG_CHECK(cond, site) ::tpb::dbg_check((cond), (site))
+// Each translation unit has its own copy of g_dbg_status; it registers a setter here and
+// tpb_debug_set_status calls them all.
+typedef int (*DbgSetter)(uint32_t*);
+void dbg_register_setter(DbgSetter fn);
+static int dbg_set_local(uint32_t* p) { return (int)cudaMemcpyToSymbol(g_dbg_status, &p, sizeof(p)); }
+namespace {
+struct DbgRegistrar {
+  DbgRegistrar() { dbg_register_setter(&dbg_set_local); }
+};
+static DbgRegistrar dbg_registrar_instance;
+}  // namespace
+#else
+#define TPB_DBG_CHECK(cond, site) (cond)
+#endif
 
 // Default wait budget: 2 s of globaltimer. Host code may override per launch.
 constexpr unsigned long long kDefaultWaitNs = 2000000000ull;

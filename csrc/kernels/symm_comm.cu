@@ -187,6 +187,78 @@ allgather_mc_kernel(const char* __restrict__ shard, char* __restrict__ mc_out, s
   }
 }
 
+// ---------------------------------------------------------------- all-to-all(v) (pull)
+// Rank s keeps, in its arena, a send buffer and a table meta[d] = {byte offset in the send buffer,
+// byte count} of what it has for rank d. The receiver pulls its segment from every source into `out`,
+// packed in source order (offset of source s = sum of the counts of sources < s), and records the counts
+// in out_bytes[world] (device memory, optional). Counts and offsets must be multiples of 16 bytes; a
+// table entry that is not, or a total above out_capacity, sets the status word and moves nothing.
+// After its last block a rank tells every source "I have read your buffer" (done_slot), which the
+// source waits for before it rewrites its send buffer.
+struct A2AMeta {
+  const long long* p[kMaxRanks];  // every rank's table
+};
+
+__global__ void __launch_bounds__(512)
+all_to_all_pull_kernel(PeerPtrs send, A2AMeta meta, char* __restrict__ out, size_t out_capacity,
+                       long long* __restrict__ out_bytes, SyncArgs s, int ready_slot, int done_slot,
+                       uint32_t* block_counter) {
+  if (!rendezvous(s, ready_slot, 26)) return;
+  __shared__ long long off_sh[kMaxRanks], cnt_sh[kMaxRanks], dst_sh[kMaxRanks + 1];
+  __shared__ int bad_sh;
+  if (threadIdx.x == 0) {
+    int bad = 0;
+    long long acc = 0;
+    for (int r = 0; r < s.world; ++r) {
+      const long long* t = meta.p[r] + 2 * s.rank;
+      const long long o = *reinterpret_cast<const volatile long long*>(t);
+      const long long c = *reinterpret_cast<const volatile long long*>(t + 1);
+      if (o < 0 || c < 0 || (o & 15) || (c & 15)) bad = 1;
+      off_sh[r] = o; cnt_sh[r] = c; dst_sh[r] = acc;
+      acc += c;
+    }
+    dst_sh[s.world] = acc;
+    if ((unsigned long long)acc > out_capacity) bad = 1;
+    bad_sh = bad;
+    if (bad && s.status) atomicCAS(s.status, 0u, kStatusBadArgs | (27u << 8));
+    if (!bad && out_bytes && blockIdx.x == 0)
+      for (int r = 0; r < s.world; ++r) out_bytes[r] = cnt_sh[r];
+  }
+  __syncthreads();
+  if (!bad_sh) {
+    const int per_rank_blocks = gridDim.x / s.world;
+    const int pr = blockIdx.x / per_rank_blocks;
+    if (pr < s.world) {
+      const int r = (s.rank + pr) % s.world;  // own segment first: it needs no link
+      const int bid = blockIdx.x % per_rank_blocks;
+      const uint4* src = reinterpret_cast<const uint4*>(send.p[r] + off_sh[r]);
+      uint4* dst = reinterpret_cast<uint4*>(out + dst_sh[r]);
+      const size_t nvec = (size_t)cnt_sh[r] / 16;
+      constexpr int kUnroll = 8;
+      const size_t stride = (size_t)per_rank_blocks * blockDim.x;
+      size_t i = (size_t)bid * blockDim.x + threadIdx.x;
+      for (; i + (kUnroll - 1) * stride < nvec; i += kUnroll * stride) {
+        uint4 v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) v[u] = ld_relaxed_sys_v4(src + i + u * stride);
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) dst[i + u * stride] = v[u];
+      }
+      for (; i < nvec; i += stride) dst[i] = ld_relaxed_sys_v4(src + i);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned prev = atomicAdd(block_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *block_counter = 0;
+      __threadfence_system();
+      for (int r = 0; r < s.world; ++r) st_release_sys(s.pad_peer[r] + done_slot + s.rank, s.epoch);
+    }
+  }
+}
+
 // ---------------------------------------------------------------- reduce-scatter + AdamW
 struct AdamArgs {
   float lr, beta1, beta2, eps, weight_decay, bias_c1, bias_c2, grad_scale;
@@ -510,6 +582,28 @@ extern "C" int tpb_symm_allgather_mc(const void* shard, size_t shard_bytes, size
   allgather_mc_kernel<<<ctas > 0 ? ctas : 32, 512, 0, (cudaStream_t)stream>>>(
       static_cast<const char*>(shard), g_symm.mc_base + out_off + (size_t)g_symm.rank * shard_bytes, shard_bytes, s,
       ready_slot, done_slot, block_counter);
+  return (int)cudaGetLastError();
+}
+
+// All-to-all with per-pair byte counts. send_off: arena offset of the send buffer; meta_off: arena
+// offset of this rank's table of `world` {offset, bytes} pairs (int64, written by the caller before the
+// launch, stream-ordered). out: local pointer with room for out_capacity bytes; out_bytes: optional device
+// int64[world]. ready_slot / done_slot: `world` flag slots each; wait on done_slot (tpb_symm_wait_slots)
+// before rewriting the send buffer or the table.
+extern "C" int tpb_symm_all_to_all(size_t send_off, size_t meta_off, void* out, size_t out_capacity,
+                                   long long* out_bytes, size_t pad_off, int ready_slot, int done_slot,
+                                   uint32_t epoch, uint32_t* block_counter, int ctas, double wait_s,
+                                   uint32_t* status, void* stream) {
+  if (!g_symm.opened && g_symm.world > 1) return -4;
+  if ((reinterpret_cast<uintptr_t>(out) & 15) || send_off % 16 || meta_off % 8) return -2;
+  SyncArgs s = make_sync(pad_off, epoch, status, wait_s);
+  A2AMeta meta;
+  memset(&meta, 0, sizeof(meta));
+  for (int r = 0; r < g_symm.world; ++r) meta.p[r] = reinterpret_cast<const long long*>(g_symm.peer[r] + meta_off);
+  const int per_rank = ctas > 0 ? ctas : 8;
+  all_to_all_pull_kernel<<<per_rank * g_symm.world, 512, 0, (cudaStream_t)stream>>>(
+      peers_at(send_off), meta, static_cast<char*>(out), out_capacity, out_bytes, s, ready_slot, done_slot,
+      block_counter);
   return (int)cudaGetLastError();
 }
 

@@ -54,7 +54,9 @@ def _run(cmd, verbose):
     return r.stdout + r.stderr
 
 
-def build_kernels(verbose: bool = False, ptxas_info: bool = False) -> Path:
+def build_kernels(verbose: bool = False, ptxas_info: bool = False, debug: bool = False) -> Path:
+    """``debug=True`` builds ``libtpb200_dbg.so`` with ``-DTPB_KERNEL_DEBUG``: index guards that only skip
+    an access in the release build also report their site to the status word (``TPB_DEBUG=1`` loads it)."""
     src_dir = CSRC / "kernels"
     headers = list(src_dir.glob("*.cuh")) + list(src_dir.glob("*.h"))
     sources = sorted(src_dir.glob("*.cu"))
@@ -62,10 +64,10 @@ def build_kernels(verbose: bool = False, ptxas_info: bool = False) -> Path:
     LIBDIR.mkdir(parents=True, exist_ok=True)
     objs, jobs = [], []
     for s in sources:
-        o = OBJDIR / (s.stem + ".o")
+        o = OBJDIR / (s.stem + ("_dbg.o" if debug else ".o"))
         objs.append(o)
         if _newer([s, *headers], o) or ptxas_info:
-            cmd = [_nvcc(), *NVCC_FLAGS, "-I", src_dir, "-c", s, "-o", o]
+            cmd = [_nvcc(), *NVCC_FLAGS, *(["-DTPB_KERNEL_DEBUG"] if debug else []), "-I", src_dir, "-c", s, "-o", o]
             if ptxas_info:
                 cmd[1:1] = ["-Xptxas", "-v"]
             jobs.append(cmd)
@@ -74,7 +76,7 @@ def build_kernels(verbose: bool = False, ptxas_info: bool = False) -> Path:
         with cf.ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             for out in ex.map(lambda c: _run(c, verbose), jobs):
                 log.append(out)
-    lib = LIBDIR / "libtpb200.so"
+    lib = LIBDIR / ("libtpb200_dbg.so" if debug else "libtpb200.so")
     if jobs or _newer(objs, lib):
         # The CUDA runtime is linked dynamically so that the library shares the runtime state
         # (per-thread current device, primary context, error state) of the process that loads

@@ -28,6 +28,8 @@ _KERNEL_SIGS = {
     "tpb_gemm_bf16_pair": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P],
     "tpb_gemm_bf16_single": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P],
     "tpb_gemm_set_pair_min_tiles": [I],
+    "tpb_debug_build": [],
+    "tpb_debug_set_status": [P],
     "tpb_gemm_pair_resident": [],
     "tpb_gemm_pair_block_n": [I],
     "tpb_gemm_pair_trace": [P],
@@ -137,7 +139,11 @@ def kernels():
     if _kernels is None:
         with _lock:
             if _kernels is None:
-                lib = _load("libtpb200.so")
+                debug = os.environ.get("TPB_DEBUG") == "1"
+                if debug and not (_LIBDIR / "libtpb200_dbg.so").exists() and os.environ.get("TPB_NO_AUTOBUILD") != "1":
+                    from . import _build
+                    _build.build_kernels(debug=True)
+                lib = _load("libtpb200_dbg.so" if debug else "libtpb200.so")
                 register_sigs(lib, _KERNEL_SIGS)
                 _kernels = _Counting(lib)
     return _kernels

@@ -101,19 +101,26 @@ def fused_matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, group=None) ->
     return _ctx(group).linear_reduce_scatter(a, b)
 
 
-_backend = "ipc"            # CUDA IPC arena with P2P loads / stores (the only backend built here)
 _signal_pad_size = 16384 * 4
 
 
 def set_backend(name: str) -> None:
-    """Select the symmetric-memory backend. Only ``"ipc"`` (CUDA IPC + peer loads / stores) exists here;
-    NVSHMEM and multicast (NVLS) backends are not built."""
-    if name.lower() not in ("ipc", "cuda"):
-        raise ValueError(f"symmetric-memory backend {name!r} is not available (only 'ipc')")
+    """Select the allocator of arenas created afterwards: ``"vmm"`` / ``"cuda"`` (virtual-memory arena with
+    an NVSwitch multicast mapping where the device supports it; the default) or ``"ipc"`` (``cudaMalloc`` +
+    CUDA IPC, peer loads / stores only). NVSHMEM is not built."""
+    import os
+    name = name.lower()
+    if name not in ("vmm", "cuda", "ipc"):
+        raise ValueError(f"symmetric-memory backend {name!r} is not available ('vmm' or 'ipc')")
+    os.environ["TPB_SYMM_ALLOC"] = "ipc" if name == "ipc" else "vmm"
 
 
 def get_backend(device=None) -> str:
-    return _backend
+    a = SymmArena._instance
+    if a is not None:
+        return a.allocator
+    import os
+    return os.environ.get("TPB_SYMM_ALLOC", "vmm")
 
 
 def set_signal_pad_size(nbytes: int) -> None:
@@ -157,8 +164,96 @@ def reduce_scatter_offset(inp: torch.Tensor, group=None, offsets=None) -> torch.
     return out[: ends[rank] - starts[rank]]
 
 
+class AllToAll:
+    """All-to-all(v) over peer memory: every rank copies what it sends into an arena buffer, publishes a
+    table of {offset, bytes} per destination, and one kernel per rank pulls its segments from all
+    sources (``csrc/kernels/symm_comm.cu`` ``all_to_all_pull_kernel``). The receiver needs no host-side
+    knowledge of the counts: they are read from the sources' tables on the device and returned as a
+    device tensor. The reference issues grouped NCCL send / recv here
+    (p10/src/backend/cuda/NCCLContext.cpp:369-458).
+
+    ``capacity_bytes`` bounds what a rank may send and receive per call. Construction is collective."""
+
+    def __init__(self, capacity_bytes: int, group=None, ctas_per_peer: int = 8, wait_s: float = 30.0):
+        a = _arena(group)
+        self.arena, self.group = a, group
+        self.capacity = (int(capacity_bytes) + 15) // 16 * 16
+        self.send = a.alloc(self.capacity, torch.uint8)
+        self.meta = a.alloc(2 * a.world, torch.int64)
+        self.meta_host = torch.empty(2 * a.world, dtype=torch.int64).pin_memory()
+        self.ready_slot = a.slots(a.world)
+        self.done_slot = a.slots(a.world)
+        self.counter = torch.zeros(1, dtype=torch.int32, device=a.device)
+        self.recv_bytes = torch.zeros(a.world, dtype=torch.int64, device=a.device)
+        self.epoch = 0
+        self.ctas, self.wait_s = ctas_per_peer, wait_s
+
+    def __call__(self, out: torch.Tensor, inp: torch.Tensor, input_split_sizes=None) -> torch.Tensor:
+        """``inp`` is split along dimension 0 into ``world`` parts (``input_split_sizes`` rows each, equal
+        parts by default); part ``d`` goes to rank ``d``. The parts received are packed into ``out`` in
+        source order. Returns the device tensor of bytes received from each source."""
+        from .. import _native
+        from ..ops._common import status_word, stream_ptr
+        a = self.arena
+        inp = inp.contiguous()
+        row_bytes = inp[0].numel() * inp.element_size() if inp.dim() > 0 and inp.shape[0] else inp.element_size()
+        rows = inp.shape[0]
+        splits = list(input_split_sizes) if input_split_sizes is not None else [rows // a.world] * a.world
+        if sum(splits) != rows or len(splits) != a.world:
+            raise ValueError("all_to_all: input_split_sizes must have one entry per rank and sum to the rows of the input")
+        if row_bytes % 16:
+            raise ValueError("all_to_all: a row must be a multiple of 16 bytes")
+        nbytes = rows * row_bytes
+        if nbytes > self.capacity:
+            raise ValueError(f"all_to_all: {nbytes} bytes to send exceed the capacity of {self.capacity}")
+        if not out.is_contiguous():
+            raise ValueError("all_to_all: out must be contiguous")
+        self.epoch += 1
+        off = 0
+        for d, n in enumerate(splits):
+            self.meta_host[2 * d] = off
+            self.meta_host[2 * d + 1] = n * row_bytes
+            off += n * row_bytes
+        st = status_word(a.device)
+        if self.epoch > 1:
+            # the previous call's readers must be done with the send buffer and the table
+            _native.check(a.raw.tpb_symm_wait_slots(a.pad_off, self.done_slot, self.epoch - 1, self.wait_s,
+                                                    st.data_ptr(), stream_ptr()), "tpb_symm_wait_slots")
+        self.meta.copy_(self.meta_host, non_blocking=True)
+        self.send[:nbytes].copy_(inp.view(-1).view(torch.uint8))
+        _native.check(a.raw.tpb_symm_all_to_all(
+            a.offset_of(self.send), a.offset_of(self.meta), out.data_ptr(), out.numel() * out.element_size(),
+            self.recv_bytes.data_ptr(), a.pad_off, self.ready_slot, self.done_slot, self.epoch,
+            self.counter.data_ptr(), self.ctas, self.wait_s, st.data_ptr(), stream_ptr()), "tpb_symm_all_to_all")
+        return self.recv_bytes
+
+
+_a2a: Optional[AllToAll] = None
+
+
+def all_to_all_single(out: torch.Tensor, inp: torch.Tensor, output_split_sizes=None, input_split_sizes=None,
+                      group=None) -> torch.Tensor:
+    """``torch.distributed.all_to_all_single`` over peer memory for CUDA tensors (``output_split_sizes`` is
+    not needed: the counts come from the senders' tables); NCCL / gloo otherwise."""
+    global _a2a
+    if not inp.is_cuda or dist.get_world_size(group) == 1:
+        dist.all_to_all_single(out, inp.contiguous(), output_split_sizes, input_split_sizes, group=group)
+        return out
+    need = inp.numel() * inp.element_size()
+    if _a2a is None:
+        # first call (collective): room for four times the largest message of this call, 64 MiB at least;
+        # larger exchanges construct AllToAll(capacity_bytes) themselves
+        cap = torch.tensor([need], dtype=torch.int64, device=inp.device)
+        dist.all_reduce(cap, op=dist.ReduceOp.MAX, group=group)
+        _a2a = AllToAll(max(4 * int(cap), 64 << 20), group=group)
+    _a2a(out, inp, input_split_sizes)
+    return out
+
+
 def all_to_all_nd(inp: torch.Tensor, group=None) -> torch.Tensor:
     """All-to-all of equal blocks along dimension 0 for tensors of any rank."""
     out = torch.empty_like(inp)
+    if inp.is_cuda and inp[0].numel() * inp.element_size() % 16 == 0:
+        return all_to_all_single(out, inp.contiguous(), group=group)
     dist.all_to_all_single(out, inp.contiguous(), group=group)
     return out

@@ -41,7 +41,16 @@ def status_word(device=None) -> torch.Tensor:
     if w is None:
         w = torch.zeros(4, dtype=torch.int32, device=dev)
         _status[key] = w
+        L = lib()
+        if L.tpb_debug_build():
+            # debug build: failed index checks report to the same word (site << 8 | 4)
+            with torch.cuda.device(dev):
+                _native.check(L.tpb_debug_set_status(w.data_ptr()), "tpb_debug_set_status")
     return w
+
+
+class DeviceIndexError(IndexError):
+    """Debug build only (``TPB_DEBUG=1``): a kernel's index guard found an out-of-range index."""
 
 
 class DeviceWaitTimeout(RuntimeError):
@@ -56,8 +65,10 @@ def check_status(device=None, reset: bool = True) -> None:
         if reset:
             w.zero_()
         code, where = v & 0xFF, v >> 8
-        names = {1: "mbarrier wait", 2: "flag wait", 3: "bad arguments"}
-        raise DeviceWaitTimeout(f"device kernel reported {names.get(code, code)} time-out at site {where}")
+        if code == 4:
+            raise DeviceIndexError(f"device kernel skipped an out-of-range index at check site {where}")
+        names = {1: "mbarrier wait time-out", 2: "flag wait time-out", 3: "bad arguments"}
+        raise DeviceWaitTimeout(f"device kernel reported {names.get(code, code)} at site {where}")
 
 
 def as_2d(x: torch.Tensor):

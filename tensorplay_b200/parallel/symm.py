@@ -35,6 +35,8 @@ _SIGS = {
                              C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_float, C.c_float, C.c_float,
                              C.c_float, C.c_float, C.c_int, C.c_float, C.c_void_p, C.c_size_t, C.c_int, C.c_int,
                              C.c_uint32, C.c_int, C.c_double, C.c_void_p, C.c_void_p],
+    "tpb_symm_all_to_all": [C.c_size_t, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_int, C.c_int,
+                            C.c_uint32, C.c_void_p, C.c_int, C.c_double, C.c_void_p, C.c_void_p],
     "tpb_symm_set_overlap": [C.c_int, C.c_int],
     "tpb_symm_wait_slots": [C.c_size_t, C.c_int, C.c_uint32, C.c_double, C.c_void_p, C.c_void_p],
     "tpb_symm_barrier": [C.c_size_t, C.c_int, C.c_uint32, C.c_double, C.c_void_p, C.c_void_p],
@@ -150,6 +152,10 @@ class SymmArena:
                 _native.check(raw.tpb_symm_open(buf), "tpb_symm_open")
         self.nbytes = nbytes
         self._offsets: Dict[int, int] = {}
+        self.canaries = [] if os.environ.get("TPB_SYMM_CANARY", "0") == "1" else None
+        if self.canaries is not None:
+            import atexit
+            atexit.register(self._check_at_exit)
         self.pad_slots = pad_slots
         self.pad_off = self._alloc_bytes(pad_slots * 4)
         self._next_slot = 0
@@ -223,14 +229,56 @@ class SymmArena:
             raise MemoryError(f"symmetric arena exhausted (asked {nbytes} bytes of {self.nbytes})")
         return off
 
+    # Debug aid (TPB_SYMM_CANARY=1): every allocation is followed by CANARY_BYTES of a fixed pattern
+    # that no kernel may touch; check_canaries() names the allocations whose guard was overwritten
+    # (a store past the end of the buffer before it, by this rank or by a peer).
+    CANARY_BYTES = 256
+    CANARY_BYTE = 0xA5
+
+    def _raw_bytes(self, off: int, nbytes: int) -> torch.Tensor:
+        ptr = self.raw.tpb_symm_ptr(self.rank, off)
+        return torch.as_tensor(_DevMem(ptr, nbytes), device=self.device)
+
     def alloc(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
         """Tensor backed by the arena at the same offset on every rank (call collectively)."""
         nbytes = numel * torch.empty(0, dtype=dtype).element_size()
-        off = self._alloc_bytes(max(nbytes, 16))
-        ptr = self.raw.tpb_symm_ptr(self.rank, off)
-        t = torch.as_tensor(_DevMem(ptr, max(nbytes, 16)), device=self.device)[:nbytes].view(dtype)
+        size = max(nbytes, 16)
+        if self.canaries is not None:
+            size = (size + 15) // 16 * 16
+            off = self._alloc_bytes(size + self.CANARY_BYTES)
+            self._raw_bytes(off + size, self.CANARY_BYTES).fill_(self.CANARY_BYTE)
+            self.canaries.append((off, size))
+        else:
+            off = self._alloc_bytes(size)
+        t = self._raw_bytes(off, size)[:nbytes].view(dtype)
         self._offsets[t.data_ptr()] = off
         return t
+
+    def _check_at_exit(self) -> None:
+        # guards on and the arena never closed: verify once at interpreter exit, fail the process loudly
+        if SymmArena._instance is not self:
+            return
+        try:
+            bad = self.check_canaries()
+        except Exception:
+            return
+        if bad:
+            import sys
+            print(f"symmetric arena: guard bytes overwritten after allocations {bad}", file=sys.stderr, flush=True)
+            os._exit(66)
+
+    def check_canaries(self) -> list:
+        """``[(offset, bytes), ...]`` of the allocations whose trailing guard no longer holds the pattern
+        (empty when all are intact, or when guards are off). Synchronises the device."""
+        if not self.canaries:
+            return []
+        torch.cuda.synchronize(self.device)
+        bad = []
+        for off, size in self.canaries:
+            g = self._raw_bytes(off + size, self.CANARY_BYTES)
+            if not bool((g == self.CANARY_BYTE).all()):
+                bad.append((off, size))
+        return bad
 
     def offset_of(self, t: torch.Tensor) -> int:
         """Arena offset of a tensor returned by ``alloc`` (or of a slice of one)."""
@@ -248,12 +296,16 @@ class SymmArena:
         return s
 
     def close(self) -> None:
-        """Release the arena (collective: no rank may still read a peer's memory)."""
+        """Release the arena (collective: no rank may still read a peer's memory). With guards on, raises
+        if one was overwritten."""
         torch.cuda.synchronize(self.device)
+        bad = self.check_canaries()
         if self.world > 1:
             dist.barrier(group=self.group)
         self.raw.tpb_symm_destroy()
         SymmArena._instance = None
+        if bad:
+            raise RuntimeError(f"symmetric arena: guard bytes overwritten after allocations {bad}")
 
 
 class SymmComm:

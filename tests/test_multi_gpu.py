@@ -19,6 +19,7 @@ def _free_port():
 
 def _run_workers(script, nproc, timeout=600, extra_env=None):
     env = dict(os.environ)
+    env.setdefault("TPB_SYMM_CANARY", "1")  # guard bytes behind every symmetric allocation, checked at close / exit
     env.update(extra_env or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),

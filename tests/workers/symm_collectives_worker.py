@@ -148,6 +148,28 @@ def main():
         assert err < 8e-3, err
         dist.barrier()
     raw.tpb_symm_set_multicast(1)
+
+    # ---------------------------------------------------------------- all-to-all(v) against NCCL
+    from tensorplay_b200.distributed._symmetric_memory import AllToAll
+    a2a = AllToAll(8 << 20)
+    width = 64                        # bf16: 128-byte rows
+    for trial in range(3):            # repeated calls reuse the send buffer: exercises the done hand-shake
+        g2 = torch.Generator(device="cpu").manual_seed(900 + trial)
+        counts = torch.randint(0, 400, (world, world), generator=g2)   # counts[s][d]: rows from s to d
+        if trial == 2:
+            counts[:, 0] = 0          # a rank that receives nothing
+        send_rows = int(counts[rank].sum())
+        recv_rows = int(counts[:, rank].sum())
+        x = (torch.arange(send_rows * width, dtype=torch.float32) % 251 + rank).to(torch.bfloat16).to(dev).view(send_rows, width)
+        out = torch.zeros(max(recv_rows, 1), width, dtype=torch.bfloat16, device=dev)
+        ref = torch.zeros(max(recv_rows, 1), width, dtype=torch.bfloat16, device=dev)
+        dist.all_to_all_single(ref[:recv_rows], x, counts[:, rank].tolist(), counts[rank].tolist())
+        got_bytes = a2a(out, x, counts[rank].tolist())
+        torch.cuda.synchronize()
+        O.check_status()
+        check(f"all_to_all_v trial {trial}", out[:recv_rows], ref[:recv_rows])
+        assert got_bytes.tolist() == [int(c) * width * 2 for c in counts[:, rank]], got_bytes.tolist()
+        dist.barrier()
     print("RESULT " + json.dumps(res), flush=True)
     arena.close()
     dist.destroy_process_group()
