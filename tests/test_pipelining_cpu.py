@@ -162,3 +162,118 @@ def test_schedule_tables_are_consistent_without_ranks():
         assert n_f == S * 8
     with pytest.raises(ValueError):
         pp.interleaved_1f1b_order(4, 2, 6)
+
+
+# ------------------------------------------------------------------ graph-splitting front end
+class _Block(nn.Module):
+    def __init__(self, d):
+        super().__init__()
+        self.fc = nn.Linear(d, d)
+
+    def forward(self, x):
+        # a branch on a tensor property: blocks stay opaque calls, so this never meets the tracer
+        if x.dtype == torch.float64:
+            x = x.float()
+        return x + torch.tanh(self.fc(x))
+
+
+class _TinyLM(nn.Module):
+    def __init__(self, d=16, n=4, vocab=32):
+        super().__init__()
+        self.embed = nn.Embedding(vocab, d)
+        self.layers = nn.ModuleList([_Block(d) for _ in range(n)])
+        self.norm = nn.LayerNorm(d)
+        self.head = nn.Linear(d, vocab)
+
+    def forward(self, ids):
+        x = self.embed(ids)
+        for l in self.layers:
+            x = l(x)
+        return self.head(self.norm(x))
+
+
+def test_pipeline_frontend_splits_and_composes():
+    import tensorplay_b200.distributed.pipelining as pp
+    torch.manual_seed(0)
+    m = _TinyLM()
+    ids = torch.randint(0, 32, (2, 8))
+    pipe = pp.pipeline(m, (ids,), split_spec={"layers.1": pp.SplitPoint.END, "layers.3": pp.SplitPoint.BEGINNING})
+    assert pipe.num_stages == 3
+    assert torch.allclose(pipe(ids), m(ids), atol=1e-6)
+    x = ids
+    for i in range(3):
+        x = pipe.get_stage_module(i)(x)
+    assert torch.allclose(x, m(ids), atol=1e-6)
+    # parameters are shared with the original model and every one lands in exactly one stage
+    names = [n for i in range(3) for n, _ in pipe.get_stage_module(i).named_parameters()]
+    assert len(names) == len(list(m.parameters()))
+    st = pipe.build_stage(1)
+    assert st.in_meta == ((2, 8, 16), torch.float32) and st.out_meta == ((2, 8, 16), torch.float32)
+    with pytest.raises(ValueError):
+        pp.pipeline(m, (ids,), split_spec={"layers.9": pp.SplitPoint.BEGINNING})
+
+
+def test_pipeline_frontend_marker_and_refused_cut():
+    import tensorplay_b200.distributed.pipelining as pp
+    from tensorplay_b200.distributed.pipelining import pipe_split
+
+    class Marked(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a, self.b = nn.Linear(8, 8), nn.Linear(8, 8)
+
+        def forward(self, x):
+            x = torch.relu(self.a(x))
+            pipe_split()
+            return self.b(x)
+
+    torch.manual_seed(1)
+    m = Marked()
+    x = torch.randn(4, 8)
+    pipe = pp.pipeline(m, (x,))
+    assert pipe.num_stages == 2 and torch.allclose(pipe(x), m(x))
+
+    class Skip(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a, self.b = nn.Linear(8, 8), nn.Linear(8, 8)
+
+        def forward(self, x):
+            h = self.a(x)
+            return self.b(h) + x          # x crosses the cut beside h
+
+    with pytest.raises(NotImplementedError):
+        pp.pipeline(Skip(), (x,), split_spec={"b": pp.SplitPoint.BEGINNING})
+
+
+def _worker_frontend(rank, world):
+    import tensorplay_b200.distributed.pipelining as pp
+    torch.manual_seed(0)
+    m = _TinyLM()
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, 32, (8, 8), generator=g)
+    tgt = torch.randint(0, 32, (8, 8), generator=g)
+    pipe = pp.pipeline(m, (ids[:2],), split_spec={"layers.2": pp.SplitPoint.BEGINNING})
+    stage = pipe.build_stage(rank, device="cpu")
+    loss_fn = lambda out, t: torch.nn.functional.cross_entropy(out.reshape(-1, 32), t.reshape(-1))
+    sched = pp.Schedule1F1B(stage, 4, loss_fn)
+    losses = []
+    if rank == 0:
+        sched.step(ids)
+    else:
+        sched.step(target=tgt, losses=losses)
+    torch.manual_seed(0)
+    ref = _TinyLM()
+    loss_fn(ref(ids), tgt).backward()
+    refp = dict(ref.named_parameters())
+    checked = 0
+    for n, p in m.named_parameters():
+        if p.grad is not None:
+            assert torch.allclose(p.grad, refp[n].grad, atol=1e-5), n
+            checked += 1
+    assert checked > 0
+    return True
+
+
+def test_pipeline_frontend_runs_under_1f1b():
+    assert all(run_ranks(_worker_frontend, 2))
