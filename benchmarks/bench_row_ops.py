@@ -44,7 +44,7 @@ def timeit(fn, iters, warmup=5):
 
 
 def cases():
-    rows, H, I, V = 16384, 4096, 14336, 128256
+    rows, H, I, V = 65536, 4096, 14336, 128256
     out = []
 
     # ---- RMSNorm (with and without the fused residual add)
@@ -72,6 +72,7 @@ def cases():
     out.append(("rope_inplace", lambda: O.apply_rope(q, cos, sin, inplace=True), 2 * q.numel() * 2))
 
     # ---- SwiGLU / GELU
+    rows = 16384
     gu = torch.randn(rows, 2 * I, device=DEV, dtype=BF)
     out.append(("swiglu_packed_fwd", lambda: O.swiglu_packed(gu), 3 * rows * I * 2))
     gug = gu.clone().requires_grad_(True)

@@ -32,6 +32,12 @@ constexpr int kYStages = 4;  // streamed-tile ring: loads run three tiles ahead 
 struct AttnBwdParams {
   int B, Tq, Tk, Hq, Hkv;
   int causal, kv_offset;
+  // optional key bounds of a query, as in the forward: window > 0 = local attention; seg_start / seg_end
+  // [B * Tq] = keys [start, end) of every query, which with Tq == Tk (packed self-attention, the only form
+  // that takes them) are also the queries [start, end) of every key
+  int window;
+  const int* seg_start;
+  const int* seg_end;
   float scale, scale_log2e;
   const float* lse;    // [B, Hq, lse_stride]
   const float* delta;  // [B, Hq, lse_stride]
@@ -154,31 +160,56 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int G = p.Hq / p.Hkv;
-  const int b = blockIdx.z;
-  const int hx = blockIdx.y;  // DKV: kv head ; dQ: query head
-  const int xb = (DKV || !p.causal) ? blockIdx.x : (gridDim.x - 1 - blockIdx.x);
+  // CTAs start in the order of their linear index; with a causal mask the tile index is the slowest
+  // coordinate, heaviest tile first (key tile 0 for dK/dV, the last query tile for dQ), heads and
+  // batches the fastest, so that the light CTAs of all heads fill the tail.
+  int b = blockIdx.z;
+  int hx = blockIdx.y;  // DKV: kv head ; dQ: query head
+  int xi = blockIdx.x;
+  if (p.causal) {
+    const int lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    const int hb = gridDim.y * gridDim.z;
+    xi = lin / hb;
+    hx = (lin % hb) % gridDim.y;
+    b = (lin % hb) / gridDim.y;
+  }
+  const int xb = (DKV || !p.causal) ? xi : (gridDim.x - 1 - xi);
   const int x0 = xb * kStat;  // first key (DKV) or first query (dQ) of this CTA
 
   // iteration space over streamed tiles
   int y_first = 0, y_count, n_it;
+  const long long seg_base = (long long)b * p.Tq;
   if (DKV) {
-    const int nqb = (p.Tq + kStream - 1) / kStream;
+    // queries of this key tile: from the first key's lower bound to the last key's upper bound
+    int q_hi = p.Tq;
+    const int k_last = min(x0 + kStat - 1, p.Tk - 1);
     if (p.causal) {
       int qmin = x0 - p.kv_offset;
       y_first = qmin > 0 ? qmin / kStream : 0;
     }
+    if (p.window > 0) q_hi = min(q_hi, k_last - p.kv_offset + p.window);
+    if (p.seg_start && x0 < p.Tk) y_first = max(y_first, p.seg_start[seg_base + x0] / kStream);
+    if (p.seg_end && x0 < p.Tk) q_hi = min(q_hi, p.seg_end[seg_base + k_last]);
+    const int nqb = (max(q_hi, 0) + kStream - 1) / kStream;
     y_count = nqb - y_first;
     if (y_count < 0) y_count = 0;
     n_it = y_count * G;
   } else {
+    // keys of this query tile: from the first query's lower bound to the last query's upper bound
     int nkb = (p.Tk + kStream - 1) / kStream;
+    const int q_last = min(x0 + kStat - 1, p.Tq - 1);
     if (p.causal) {
       int last_key = x0 + kStat - 1 + p.kv_offset;
       int lim = last_key < 0 ? 0 : last_key / kStream + 1;
       nkb = min(nkb, lim);
     }
-    y_count = nkb;
-    n_it = nkb;
+    if (p.seg_end && x0 < p.Tq) nkb = min(nkb, (p.seg_end[seg_base + q_last] + kStream - 1) / kStream);
+    int lo_first = 0;
+    if (p.window > 0) lo_first = max(lo_first, x0 + p.kv_offset - p.window + 1);
+    if (p.seg_start && x0 < p.Tq) lo_first = max(lo_first, p.seg_start[seg_base + x0]);
+    y_first = lo_first / kStream;
+    y_count = max(nkb - y_first, 0);
+    n_it = y_count;
   }
 
   if (threadIdx.x == 0) {
@@ -228,7 +259,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
         trace_pt(p, 0, it, 1);
         int hy, yb;
         if (DKV) { hy = hx * G + it / y_count; yb = y_first + it % y_count; }
-        else { hy = hx / G; yb = it; }
+        else { hy = hx / G; yb = y_first + it; }
         uint8_t* y0 = smem + L::kY + s * 2 * L::kStreamBytes;
         uint8_t* y1 = y0 + L::kStreamBytes;
         mbar_arrive_expect_tx(&y_full[s], 2 * L::kStreamBytes + (DKV ? 2 * kStream * 4 : 0));
@@ -343,9 +374,19 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
     if (DKV) {
       y_lo = (xi < p.Tk) ? (p.causal ? max(xi - p.kv_offset, 0) : 0) : 0x3fffffff;
       y_hi = p.Tq;
+      if (p.window > 0) y_hi = min(y_hi, xi - p.kv_offset + p.window);
+      if (xi < p.Tk) {
+        if (p.seg_start) y_lo = max(y_lo, p.seg_start[seg_base + xi]);
+        if (p.seg_end) y_hi = min(y_hi, p.seg_end[seg_base + xi]);
+      }
     } else {
       y_lo = 0;
       y_hi = (xi < p.Tq) ? (p.causal ? min(p.Tk, xi + p.kv_offset + 1) : p.Tk) : 0;
+      if (p.window > 0) y_lo = max(y_lo, xi + p.kv_offset - p.window + 1);
+      if (xi < p.Tq) {
+        if (p.seg_start) y_lo = max(y_lo, p.seg_start[seg_base + xi]);
+        if (p.seg_end) y_hi = min(y_hi, p.seg_end[seg_base + xi]);
+      }
     }
     lse_row *= log2e;
     delta_row *= p.scale;
@@ -355,7 +396,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant
       const uint32_t ph = (it >> 1) & 1;
       int yb;
       if (DKV) yb = y_first + it % y_count;
-      else yb = it;
+      else yb = y_first + it;
       const int y0i = yb * kStream + half * 32;  // first query (DKV) or key (dQ) of this warp's columns
       if (!mbar_wait_warp(&sdp_full[s], ph, wc, 6)) { ok = false; break; }
       if (threadIdx.x == 64) trace_pt(p, 2, it, 1);
@@ -497,19 +538,22 @@ using namespace tpb;
 
 // lse / delta: [B, Hq, lse_stride] fp32 with lse_stride a multiple of 64 and >= Tq rounded up
 // to 64 (the dKV pass reads whole 64-query vectors). delta is scratch written here.
-extern "C" int tpb_flash_bwd(const void* dout, const void* q, const void* k, const void* v,
-                             const void* o, const float* lse, float* delta, void* dq, void* dk,
-                             void* dv, int B, int Tq, int Tk, int Hq, int Hkv, int D,
-                             long long q_tok, long long q_head, long long q_batch, long long k_tok,
-                             long long k_head, long long k_batch, long long v_tok,
-                             long long v_head, long long v_batch, long long o_tok,
-                             long long o_head, long long o_batch, long long do_tok,
-                             long long do_head, long long do_batch, long long dq_tok,
-                             long long dq_head, long long dq_batch, long long dkv_tok,
-                             long long dkv_head, long long dkv_batch, int lse_stride, int causal,
-                             float scale, uint32_t* status, void* stream_) {
+// window / seg_start / seg_end as in tpb_flash_fwd_ex; segment bounds need Tq == Tk.
+extern "C" int tpb_flash_bwd_ex(const void* dout, const void* q, const void* k, const void* v,
+                                const void* o, const float* lse, float* delta, void* dq, void* dk,
+                                void* dv, int B, int Tq, int Tk, int Hq, int Hkv, int D,
+                                long long q_tok, long long q_head, long long q_batch, long long k_tok,
+                                long long k_head, long long k_batch, long long v_tok,
+                                long long v_head, long long v_batch, long long o_tok,
+                                long long o_head, long long o_batch, long long do_tok,
+                                long long do_head, long long do_batch, long long dq_tok,
+                                long long dq_head, long long dq_batch, long long dkv_tok,
+                                long long dkv_head, long long dkv_batch, int lse_stride, int causal,
+                                float scale, uint32_t* status, void* stream_, int window, const int* seg_start,
+                                const int* seg_end) {
   cudaStream_t stream = (cudaStream_t)stream_;
   if (B <= 0 || Tq <= 0 || Hq <= 0) return 0;
+  if ((seg_start || seg_end) && Tq != Tk) return -2;
   if ((D != 64 && D != 128) || Hkv <= 0 || Hq % Hkv || Tk <= 0) return -2;
   if (lse_stride % 64 || lse_stride < (Tq + 63) / 64 * 64) return -2;
   if ((q_tok | q_head | q_batch | k_tok | k_head | k_batch | v_tok | v_head | v_batch | do_tok |
@@ -529,6 +573,7 @@ extern "C" int tpb_flash_bwd(const void* dout, const void* q, const void* k, con
   p.lse = lse; p.delta = delta; p.lse_stride = lse_stride; p.status = status;
   p.wait_ns = kDefaultWaitNs;
   p.trace = g_bwd_trace; p.trace_cap = g_bwd_trace_cap;
+  p.window = window > 0 ? window : 0; p.seg_start = seg_start; p.seg_end = seg_end;
   int r;
   // ---- dK / dV: [B, Tk, Hkv, D] by the dkv strides (dk and dv share them)
   {
@@ -564,6 +609,23 @@ extern "C" int tpb_flash_bwd(const void* dout, const void* q, const void* k, con
 // Debug aid: buf = device array of 1 + 2 * cap uint64 (buf[0] = record count, zero it first). The
 // next backward launches record role / iteration / phase timestamps of block (0,0,0) of BOTH
 // passes into it. Pass null to switch tracing off.
+extern "C" int tpb_flash_bwd(const void* dout, const void* q, const void* k, const void* v,
+                             const void* o, const float* lse, float* delta, void* dq, void* dk,
+                             void* dv, int B, int Tq, int Tk, int Hq, int Hkv, int D,
+                             long long q_tok, long long q_head, long long q_batch, long long k_tok,
+                             long long k_head, long long k_batch, long long v_tok,
+                             long long v_head, long long v_batch, long long o_tok,
+                             long long o_head, long long o_batch, long long do_tok,
+                             long long do_head, long long do_batch, long long dq_tok,
+                             long long dq_head, long long dq_batch, long long dkv_tok,
+                             long long dkv_head, long long dkv_batch, int lse_stride, int causal,
+                             float scale, uint32_t* status, void* stream_) {
+  return tpb_flash_bwd_ex(dout, q, k, v, o, lse, delta, dq, dk, dv, B, Tq, Tk, Hq, Hkv, D, q_tok, q_head, q_batch,
+                          k_tok, k_head, k_batch, v_tok, v_head, v_batch, o_tok, o_head, o_batch, do_tok, do_head,
+                          do_batch, dq_tok, dq_head, dq_batch, dkv_tok, dkv_head, dkv_batch, lse_stride, causal, scale,
+                          status, stream_, 0, nullptr, nullptr);
+}
+
 extern "C" int tpb_flash_bwd_set_trace(unsigned long long* buf, int cap) {
   tpb::g_bwd_trace = buf;
   tpb::g_bwd_trace_cap = cap;

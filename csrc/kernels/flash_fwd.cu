@@ -36,6 +36,13 @@ struct AttnFwdParams {
   float* lse;  // [B, Hq, lse_stride]
   int lse_stride;
   const int* kv_len;  // optional device word: number of valid keys (<= Tk), for graph-replayed decode
+  // Optional lower / upper bounds of the keys of a query (local attention and packed sequences):
+  //   window > 0: query i attends keys > i + kv_offset - window;
+  //   seg_start / seg_end [B * Tq] (null = none): query i attends keys in [seg_start[i], seg_end[i]);
+  //   both arrays are non-decreasing along a sequence (segments are contiguous token ranges).
+  int window;
+  const int* seg_start;
+  const int* seg_end;
   // split-KV (decode): CTA (x = tile * n_splits + split) handles KV blocks [split * blocks_per_split, ...)
   // and writes a partial O / LSE at split * o_split_stride / lse_split_stride (merged by a second kernel)
   int n_splits, blocks_per_split;
@@ -122,12 +129,14 @@ __device__ __forceinline__ float row_max(const uint32_t (&sr)[128]) {
   return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
 }
 
-// Keys beyond `lim` get the score -inf (masked tiles only: the diagonal and the ragged end of the
-// sequence): it never raises the running maximum and its exponential on the special-function
-// unit is exactly zero, also for a row without any valid key in this tile.
-__device__ __forceinline__ void row_mask(uint32_t (&sr)[128], int k0, int lim) {
+// Keys outside [lo, lim] get the score -inf (masked tiles only: the diagonal, the ragged end of the
+// sequence, the left edge of a window or segment): it never raises the running maximum and its
+// exponential on the special-function unit is exactly zero, also for a row without any valid key
+// in this tile.
+__device__ __forceinline__ void row_mask(uint32_t (&sr)[128], int k0, int lo, int lim) {
+  const int a = lo - k0, b = lim - k0;   // valid columns: a <= i <= b
 #pragma unroll
-  for (int i = 0; i < 128; ++i) sr[i] = (k0 + i <= lim) ? sr[i] : 0xff800000u;
+  for (int i = 0; i < 128; ++i) sr[i] = (i >= a && i <= b) ? sr[i] : 0xff800000u;
 }
 
 // exp2 of a pair on the FMA pipe: floor by the magic-number add in round-down mode, cubic
@@ -214,16 +223,38 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n_splits = p.n_splits > 1 ? p.n_splits : 1;
-  const int split = blockIdx.x % n_splits;
   const int q_tiles = gridDim.x / n_splits;
-  const int qt = blockIdx.x / n_splits;
+  int split, qt, h, b;
+  if (p.causal && n_splits == 1) {
+    // CTAs start in the order of their linear index. With a causal mask the work of a CTA grows with
+    // its query tile, so the tile index is made the slowest coordinate, heaviest first, and the heads
+    // of all batches the fastest: the light CTAs of every head come last and fill the tail evenly
+    // (tile-major order within each head left the last head's CTAs to a few SMs).
+    const int lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    const int hb = gridDim.y * gridDim.z;
+    split = 0;
+    qt = lin / hb;
+    h = (lin % hb) % gridDim.y;
+    b = (lin % hb) / gridDim.y;
+  } else {
+    split = blockIdx.x % n_splits;
+    qt = blockIdx.x / n_splits;
+    h = blockIdx.y;
+    b = blockIdx.z;
+  }
   const int qb = p.causal ? (q_tiles - 1 - qt) : qt;  // heavy tiles first
-  const int j0 = split * p.blocks_per_split;  // first KV block of this CTA (0 without splitting)
-  const int h = blockIdx.y;
-  const int b = blockIdx.z;
   const int hk = h / (p.Hq / p.Hkv);
   const int q0 = qb * (kTilesQ * kBlockQ);
   const int Tk = p.kv_len ? min(p.Tk, *p.kv_len) : p.Tk;
+  // first KV block of this CTA: the split's share, or the block of the smallest key that the CTA's
+  // first query may attend (bounds grow with the query index, so later rows need no earlier key)
+  int j0 = split * p.blocks_per_split;
+  if (n_splits == 1 && q0 < p.Tq) {
+    int lo_first = 0;
+    if (p.window > 0) lo_first = max(lo_first, q0 + p.kv_offset - p.window + 1);
+    if (p.seg_start) lo_first = max(lo_first, p.seg_start[(long long)b * p.Tq + q0]);
+    j0 = lo_first / kBlockKV;
+  }
   // KV blocks needed by each of the two query tiles
   int nkv_t[kTilesQ];
   int nkv = 0;
@@ -235,7 +266,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       n = last_key < 0 ? 0 : min(n, last_key / kBlockKV + 1);
     }
     if (q0 + g * kBlockQ >= p.Tq) n = 0;  // tile past the end of the sequence
+    if (p.seg_end && n > 0) {
+      // the tile's last query has the largest upper bound
+      const int qlast = min(q0 + g * kBlockQ + kBlockQ - 1, p.Tq - 1);
+      n = min(n, (p.seg_end[(long long)b * p.Tq + qlast] + kBlockKV - 1) / kBlockKV);
+    }
     if (n_splits > 1) n = max(0, min(n - j0, p.blocks_per_split));  // this split's share
+    else n = max(0, n - j0);
     nkv_t[g] = n;
     nkv = max(nkv, n);
   }
@@ -267,7 +304,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   WaitCtx wc{abort_w, p.status, p.wait_ns};
-  uint32_t* trc = (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
+  uint32_t* trc = (p.trace && qt == 0 && h == 0 && b == 0)
                       ? reinterpret_cast<uint32_t*>(smem + L::kTraceOff) : nullptr;
   if (trc) {
     for (int i = threadIdx.x; i < kTraceWords; i += kAttnThreads) trc[i] = 0;
@@ -407,7 +444,24 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t t_s = tmem_base + ((uint32_t)(qd * 32) << 16) + g * 128;
     const uint32_t t_o = tmem_base + ((uint32_t)(qd * 32) << 16) + 256 + g * 128;
     const int my_nkv = nkv_t[g];
-    const int lim = p.causal ? min(qi + p.kv_offset, Tk - 1) : (Tk - 1);  // last valid key
+    int lim = p.causal ? min(qi + p.kv_offset, Tk - 1) : (Tk - 1);  // last valid key
+    int lo = 0;                                                            // first valid key
+    // largest lower / smallest upper bound among the tile's rows decide which KV blocks need the mask
+    int lo_tile = 0, lim_tile = 0x3fffffff;
+    if (p.window > 0) {
+      lo = qi + p.kv_offset - p.window + 1;
+      lo_tile = q0 + g * kBlockQ + kBlockQ - 1 + p.kv_offset - p.window + 1;
+    }
+    if (p.seg_start) {
+      const long long base = (long long)b * p.Tq;
+      lo = max(lo, p.seg_start[base + min(qi, p.Tq - 1)]);
+      lo_tile = max(lo_tile, p.seg_start[base + min(q0 + g * kBlockQ + kBlockQ - 1, p.Tq - 1)]);
+    }
+    if (p.seg_end) {
+      const long long base = (long long)b * p.Tq;
+      lim = min(lim, p.seg_end[base + min(qi, p.Tq - 1)] - 1);
+      lim_tile = p.seg_end[base + min(q0 + g * kBlockQ, p.Tq - 1)] - 1;
+    }
     float m = kNegBig, l = 0.f;
     bool ok = true;
     for (int j = 0; j < my_nkv; ++j) {
@@ -417,14 +471,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_after_sync();
       const int k0 = (j0 + j) * kBlockKV;
       const bool need_mask = (p.causal && (k0 + kBlockKV - 1 > q0 + g * kBlockQ + p.kv_offset)) ||
-                             (k0 + kBlockKV > Tk);
+                             (k0 + kBlockKV > Tk) || (k0 < lo_tile) || (k0 + kBlockKV - 1 > lim_tile);
       // the whole S row (128 fp32) in one TMEM round trip
       uint32_t sr[128];
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(t_s + c * 32, &sr[c * 32]);
       tmem_ld_wait();
       if (tr) fwd_trace(trc, 1 + g, 2, j);
-      if (need_mask) row_mask(sr, k0, lim);
+      if (need_mask) row_mask(sr, k0, lo, lim);
       const float mx = fmaxf(m, row_max(sr) * p.scale_log2e);
       // The reference maximum only moves when the row maximum grew by more than 2^4: until then
       // P stays below 16 (harmless in bf16, whose error is relative) and O needs no rescale.
@@ -651,14 +705,17 @@ extern "C" int tpb_flash_fwd_set_trace(unsigned long long* buf, int cap) {
 
 // q: [B, Tq, Hq, D], k/v: [B, Tk, Hkv, D] given by (token, head, batch) strides in elements;
 // o likewise; lse: [B, Hq, lse_stride] fp32 (lse_stride >= Tq). causal aligns the last query with the last key.
-extern "C" int tpb_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
-                             int B, int Tq, int Tk, int Hq, int Hkv, int D, long long q_tok,
-                             long long q_head, long long q_batch, long long k_tok,
-                             long long k_head, long long k_batch, long long v_tok,
-                             long long v_head, long long v_batch, long long o_tok,
-                             long long o_head, long long o_batch, int lse_stride, int causal,
-                             float scale, uint32_t* status, void* stream, const int* kv_len, int n_splits,
-                             long long o_split_stride, long long lse_split_stride) {
+// window > 0: local attention (a query attends its last `window` keys); seg_start / seg_end: int32
+// [B * Tq] bounds [start, end) of the keys of every query (packed sequences; null = none).
+extern "C" int tpb_flash_fwd_ex(const void* q, const void* k, const void* v, void* o, float* lse,
+                                int B, int Tq, int Tk, int Hq, int Hkv, int D, long long q_tok,
+                                long long q_head, long long q_batch, long long k_tok,
+                                long long k_head, long long k_batch, long long v_tok,
+                                long long v_head, long long v_batch, long long o_tok,
+                                long long o_head, long long o_batch, int lse_stride, int causal,
+                                float scale, uint32_t* status, void* stream, const int* kv_len, int n_splits,
+                                long long o_split_stride, long long lse_split_stride, int window,
+                                const int* seg_start, const int* seg_end) {
   if (B <= 0 || Tq <= 0 || Hq <= 0) return 0;
   if ((D != 64 && D != 128) || Hkv <= 0 || Hq % Hkv || Tk <= 0) return -2;
   if ((q_tok | q_head | q_batch | k_tok | k_head | k_batch | v_tok | v_head | v_batch | o_tok |
@@ -685,6 +742,7 @@ extern "C" int tpb_flash_fwd(const void* q, const void* k, const void* v, void* 
   }
   p.o_split_stride = o_split_stride; p.lse_split_stride = lse_split_stride;
   p.trace = g_fwd_trace; p.trace_cap = g_fwd_trace_cap;
+  p.window = window > 0 ? window : 0; p.seg_start = seg_start; p.seg_end = seg_end;
   if (p.n_splits > 1 && causal) return -3;  // splitting is for decode (one query tile, no causal mask)
   if (D == 128) {
     switch (g_fwd_npoly) {
@@ -696,6 +754,19 @@ extern "C" int tpb_flash_fwd(const void* q, const void* k, const void* v, void* 
   // head_dim 64 halves the tensor work per score, so the exponentials dominate: more of them
   // go to the FMA pipe
   return launch_fwd<64, 2>(tq, tk, tv, p, (cudaStream_t)stream);
+}
+
+extern "C" int tpb_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
+                             int B, int Tq, int Tk, int Hq, int Hkv, int D, long long q_tok,
+                             long long q_head, long long q_batch, long long k_tok,
+                             long long k_head, long long k_batch, long long v_tok,
+                             long long v_head, long long v_batch, long long o_tok,
+                             long long o_head, long long o_batch, int lse_stride, int causal,
+                             float scale, uint32_t* status, void* stream, const int* kv_len, int n_splits,
+                             long long o_split_stride, long long lse_split_stride) {
+  return tpb_flash_fwd_ex(q, k, v, o, lse, B, Tq, Tk, Hq, Hkv, D, q_tok, q_head, q_batch, k_tok, k_head, k_batch,
+                          v_tok, v_head, v_batch, o_tok, o_head, o_batch, lse_stride, causal, scale, status, stream,
+                          kv_len, n_splits, o_split_stride, lse_split_stride, 0, nullptr, nullptr);
 }
 
 // Share of the exponentials that the forward computes with the polynomial on the FMA pipe instead of

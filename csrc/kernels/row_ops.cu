@@ -704,7 +704,9 @@ extern "C" int tpb_rmsnorm_bwd_grid(int rows, int H) {
   if (H % 8 || H > 256 * kMaxVec * 8) return -2;
   int tpr = pick_tpr(H);
   int g = row_grid(rows, tpr);
-  int cap = sm_count() * 2;
+  // 4 CTAs of 62-64 registers x 256 threads fit an SM; each CTA works through its rows one after the
+  // other (load, row reduction, store), so resident CTAs are what hides the memory latency
+  int cap = sm_count() * 4;
   return g < cap ? g : cap;
 }
 

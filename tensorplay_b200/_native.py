@@ -49,6 +49,8 @@ _KERNEL_SIGS = {
     "tpb_cross_entropy": [P, P, P, P, P, LL, I, LL, LL, F, P],
     "tpb_cross_entropy_bwd": [P, P, P, P, P, P, P, LL, I, LL, LL, P],
     "tpb_flash_fwd": [P, P, P, P, P, I, I, I, I, I, I] + [LL] * 12 + [I, I, F, P, P, P, I, LL, LL],
+    "tpb_flash_fwd_ex": [P, P, P, P, P, I, I, I, I, I, I] + [LL] * 12 + [I, I, F, P, P, P, I, LL, LL, I, P, P],
+    "tpb_flash_bwd_ex": [P] * 10 + [I, I, I, I, I, I] + [LL] * 21 + [I, I, F, P, P, I, P, P],
     "tpb_flash_fwd_config": [I],
     "tpb_attn_split_merge": [P, P, P, P, I, I, I, I, I, LL, LL, I, LL, LL, LL, P],
     "tpb_flash_bwd": [P] * 10 + [I, I, I, I, I, I] + [LL] * 21 + [I, I, F, P, P],

@@ -1,11 +1,13 @@
 """Variable-length attention over packed sequences.
 
 ``query [total_q, Hq, D]``, ``key / value [total_k, Hkv, D]`` hold the tokens of all sequences back
-to back; ``cu_seq_q / cu_seq_k`` (int32, ``[n + 1]``) are the cumulative lengths. Every sequence is
-attended on its own: its rows are a strided view of the packed tensors, which the tcgen05 flash
-kernels take in place (one launch per sequence, no padding, no copy). A local window
-(``window_size=(left, right)``) and head dims other than 64 / 128 run the fp32 formula per
-sequence. Differentiable. (tensorplay/nn/attention/varlen.py:287 ``varlen_attn``; the reference's
+to back; ``cu_seq_q / cu_seq_k`` (int32, ``[n + 1]``) are the cumulative lengths. Self-attention over
+the packed tokens (``cu_seq_q == cu_seq_k``; causal, optionally with a left window) is ONE launch of
+the tcgen05 flash kernels over the whole packed row: every token carries the bounds of its sequence,
+query tiles skip the KV blocks of other sequences and mask inside the blocks on a boundary. Cross
+attention between packed sets of different lengths takes one launch per sequence on strided views
+(no padding, no copy); a right-bounded non-causal window and head dims other than 64 / 128 run the
+fp32 formula per sequence. Differentiable. (tensorplay/nn/attention/varlen.py:287 ``varlen_attn``; the reference's
 kernels take ``cu_seqlens`` inside one launch, p10/src/backend/cuda/transformers/AttentionKernels.cu:1782-1969.)
 """
 from __future__ import annotations
@@ -64,6 +66,16 @@ def varlen_attn(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, cu_
     use_kernel = (window == (-1, -1) and not want_lse and query.is_cuda and query.dtype == torch.bfloat16
                   and D in (64, 128))
     from . import _flash
+    left, right = window
+    one_launch = (query.is_cuda and query.dtype == torch.bfloat16 and D in (64, 128) and not want_lse and bq == bk
+                  and key.shape[0] == query.shape[0] and max(a1 - a0 for a0, a1 in zip(bq[:-1], bq[1:])) <= max_q
+                  and (right < 0 or (is_causal and right >= 0)) and (is_causal or left < 0))
+    if one_launch:
+        from ...ops.attention import flash_attention, segment_bounds
+        seg_start, seg_end = segment_bounds(cu_seq_q.to(query.device), query.shape[0])
+        return flash_attention(query.unsqueeze(0), key.unsqueeze(0), value.unsqueeze(0), causal=is_causal,
+                               scale=scale, window=(left + 1) if left >= 0 else 0,
+                               seg_start=seg_start.view(1, -1), seg_end=seg_end.view(1, -1)).squeeze(0)
     outs, lses = [], []
     for a0, a1, b0, b1 in zip(bq[:-1], bq[1:], bk[:-1], bk[1:]):
         if a1 - a0 > max_q or b1 - b0 > max_k:

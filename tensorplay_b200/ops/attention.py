@@ -25,8 +25,20 @@ def _strides_ok(t: torch.Tensor) -> bool:
     return t.stride(3) == 1 and all(s % 8 == 0 for s in t.stride()[:3]) and t.data_ptr() % 16 == 0
 
 
-def attention_reference(q, k, v, causal: bool = True, scale: Optional[float] = None):
-    """Plain fp32 attention in ``[B, T, H, D]`` layout (the correctness oracle)."""
+def segment_bounds(cu_seqlens: torch.Tensor, total: int):
+    """Per-token ``(seg_start, seg_end)`` int32 arrays of ``total`` packed tokens whose sequence boundaries are
+    ``cu_seqlens`` (``[n + 1]``, first 0, last ``total``): token ``i`` of sequence ``s`` gets
+    ``(cu_seqlens[s], cu_seqlens[s + 1])``."""
+    cu = cu_seqlens.to(torch.int64)
+    pos = torch.arange(total, device=cu.device)
+    seq = torch.searchsorted(cu[1:].contiguous(), pos, right=True).clamp_(max=cu.numel() - 2)
+    return cu[seq].to(torch.int32).contiguous(), cu[seq + 1].to(torch.int32).contiguous()
+
+
+def attention_reference(q, k, v, causal: bool = True, scale: Optional[float] = None, window: int = 0,
+                        seg_start: Optional[torch.Tensor] = None, seg_end: Optional[torch.Tensor] = None):
+    """Plain fp32 attention in ``[B, T, H, D]`` layout (the correctness oracle). ``window`` / ``seg_start`` /
+    ``seg_end`` as in :func:`flash_attention`; a query without any admissible key gives zeros."""
     B, Tq, Hq, D = q.shape
     Tk, Hkv = k.shape[1], k.shape[2]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
@@ -35,16 +47,24 @@ def attention_reference(q, k, v, causal: bool = True, scale: Optional[float] = N
     kf = k.float().permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
     vf = v.float().permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
     s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    i = torch.arange(Tq, device=q.device).view(-1, 1)
+    j = torch.arange(Tk, device=q.device).view(1, -1)
     if causal:
-        i = torch.arange(Tq, device=q.device).view(-1, 1)
-        j = torch.arange(Tk, device=q.device).view(1, -1)
         s = s.masked_fill(j > i + (Tk - Tq), float("-inf"))
-    p = torch.softmax(s, dim=-1)
+    if window and window > 0:
+        s = s.masked_fill(j < i + (Tk - Tq) - window + 1, float("-inf"))
+    if seg_start is not None:
+        s = s.masked_fill((j.view(1, 1, 1, Tk) < seg_start.view(B, 1, Tq, 1)), float("-inf"))
+    if seg_end is not None:
+        s = s.masked_fill((j.view(1, 1, 1, Tk) >= seg_end.view(B, 1, Tq, 1)), float("-inf"))
+    empty = torch.isinf(s).all(dim=-1, keepdim=True)
+    p = torch.softmax(s.masked_fill(empty, 0.0), dim=-1).masked_fill(empty, 0.0)
     o = torch.matmul(p, vf)
     return o.permute(0, 2, 1, 3).to(q.dtype)
 
 
-def flash_fwd(q, k, v, causal: bool, scale: float, kv_len: Optional[torch.Tensor] = None, n_splits: int = 1):
+def flash_fwd(q, k, v, causal: bool, scale: float, kv_len: Optional[torch.Tensor] = None, n_splits: int = 1,
+              window: int = 0, seg_start: Optional[torch.Tensor] = None, seg_end: Optional[torch.Tensor] = None):
     """Forward kernel. ``kv_len`` (int32 device scalar) limits the keys to the first ``kv_len`` of
     ``k``/``v`` without a host-side shape change, so that a decode step over a preallocated cache
     can be captured in a CUDA graph. ``n_splits > 1`` (non-causal, i.e. decode) spreads the keys of
@@ -63,12 +83,13 @@ def flash_fwd(q, k, v, causal: bool, scale: float, kv_len: Optional[torch.Tensor
         o_split, lse_split = part.stride(0), lse_part.stride(0)
     else:
         dst, dst_lse, o_split, lse_split = o, lse, 0, 0
-    code = lib().tpb_flash_fwd(
+    code = lib().tpb_flash_fwd_ex(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), dst.data_ptr(), dst_lse.data_ptr(), B, Tq, Tk, Hq, Hkv,
         D, q.stride(1), q.stride(2), q.stride(0), k.stride(1), k.stride(2), k.stride(0),
         v.stride(1), v.stride(2), v.stride(0), dst.stride(1), dst.stride(2), dst.stride(0), lse_stride,
         int(causal), float(scale), status_word(q.device).data_ptr(), stream_ptr(),
-        None if kv_len is None else kv_len.data_ptr(), n_splits, o_split, lse_split)
+        None if kv_len is None else kv_len.data_ptr(), n_splits, o_split, lse_split, int(window or 0),
+        None if seg_start is None else seg_start.data_ptr(), None if seg_end is None else seg_end.data_ptr())
     _native.check(code, "tpb_flash_fwd")
     if n_splits > 1:
         code = lib().tpb_attn_split_merge(part.data_ptr(), lse_part.data_ptr(), o.data_ptr(), lse.data_ptr(),
@@ -78,7 +99,8 @@ def flash_fwd(q, k, v, causal: bool, scale: float, kv_len: Optional[torch.Tensor
     return o, lse
 
 
-def flash_bwd(do, q, k, v, o, lse, causal: bool, scale: float, dq=None, dk=None, dv=None):
+def flash_bwd(do, q, k, v, o, lse, causal: bool, scale: float, dq=None, dk=None, dv=None, window: int = 0,
+              seg_start: Optional[torch.Tensor] = None, seg_end: Optional[torch.Tensor] = None):
     """Backward of ``flash_fwd``. ``dq``/``dk``/``dv`` may be preallocated (strided) views, e.g.
     slices of one fused dQKV buffer; ``dk`` and ``dv`` must share their strides."""
     B, Tq, Hq, D = q.shape
@@ -93,52 +115,67 @@ def flash_bwd(do, q, k, v, o, lse, causal: bool, scale: float, dq=None, dk=None,
     delta = torch.empty_like(lse)
     if not _strides_ok(do):
         do = do.contiguous()
-    code = lib().tpb_flash_bwd(
+    code = lib().tpb_flash_bwd_ex(
         do.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
         delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, Tq, Tk, Hq, Hkv, D,
         q.stride(1), q.stride(2), q.stride(0), k.stride(1), k.stride(2), k.stride(0),
         v.stride(1), v.stride(2), v.stride(0), o.stride(1), o.stride(2), o.stride(0),
         do.stride(1), do.stride(2), do.stride(0), dq.stride(1), dq.stride(2), dq.stride(0),
         dk.stride(1), dk.stride(2), dk.stride(0), lse.shape[2], int(causal), float(scale),
-        status_word(q.device).data_ptr(), stream_ptr())
+        status_word(q.device).data_ptr(), stream_ptr(), int(window or 0),
+        None if seg_start is None else seg_start.data_ptr(), None if seg_end is None else seg_end.data_ptr())
     _native.check(code, "tpb_flash_bwd")
     return dq, dk, dv
 
 
 class _FlashAttnFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, causal, scale):
-        o, lse = flash_fwd(q, k, v, causal, scale)
+    def forward(ctx, q, k, v, causal, scale, window=0, seg_start=None, seg_end=None):
+        o, lse = flash_fwd(q, k, v, causal, scale, window=window, seg_start=seg_start, seg_end=seg_end)
         ctx.save_for_backward(q, k, v, o, lse)
-        ctx.causal, ctx.scale = causal, scale
+        ctx.causal, ctx.scale, ctx.window, ctx.seg = causal, scale, window, (seg_start, seg_end)
         return o
 
     @staticmethod
     def backward(ctx, do):
         q, k, v, o, lse = ctx.saved_tensors
-        dq, dk, dv = flash_bwd(do, q, k, v, o, lse, ctx.causal, ctx.scale)
-        return dq, dk, dv, None, None
+        dq, dk, dv = flash_bwd(do, q, k, v, o, lse, ctx.causal, ctx.scale, window=ctx.window,
+                               seg_start=ctx.seg[0], seg_end=ctx.seg[1])
+        return dq, dk, dv, None, None, None, None, None
 
 
 def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = True,
-                    scale: Optional[float] = None) -> torch.Tensor:
-    """``softmax(q k^T * scale [+ causal mask]) v`` for ``q [B, Tq, Hq, D]``, ``k/v [B, Tk, Hkv, D]``.
+                    scale: Optional[float] = None, window: int = 0, seg_start: Optional[torch.Tensor] = None,
+                    seg_end: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``softmax(q k^T * scale [+ mask]) v`` for ``q [B, Tq, Hq, D]``, ``k/v [B, Tk, Hkv, D]``.
 
     ``Hq`` must be a multiple of ``Hkv`` (grouped-query attention). With ``causal`` the last
-    query is aligned with the last key.
+    query is aligned with the last key. ``window > 0`` is local attention: a query sees its last
+    ``window`` keys (its own position included). ``seg_start`` / ``seg_end`` (int32 ``[B, Tq]``,
+    non-decreasing along the sequence, see :func:`segment_bounds`) restrict query ``i`` to the keys
+    ``[seg_start[i], seg_end[i])``: several sequences packed into one row attend only within
+    themselves (``Tq == Tk``). The kernels skip the KV blocks that lie outside the bounds of a
+    whole query tile and mask inside the blocks on their edges
+    (p10/src/backend/cuda/transformers/AttentionKernels.cu:1907-1918 has the window of the reference).
     """
     D = q.shape[-1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if (seg_start is not None or seg_end is not None) and q.shape[1] != k.shape[1]:
+        raise ValueError("flash_attention: segment bounds need Tq == Tk (packed self-attention)")
+    if seg_start is not None:
+        seg_start = seg_start.to(torch.int32).contiguous()
+    if seg_end is not None:
+        seg_end = seg_end.to(torch.int32).contiguous()
     native = (q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128) and use_native(q, k, v))
     if not native:
-        return attention_reference(q, k, v, causal, scale)
+        return attention_reference(q, k, v, causal, scale, window, seg_start, seg_end)
     if not _strides_ok(q):
         q = q.contiguous()
     if not _strides_ok(k):
         k = k.contiguous()
     if not _strides_ok(v):
         v = v.contiguous()
-    return _FlashAttnFn.apply(q, k, v, causal, scale)
+    return _FlashAttnFn.apply(q, k, v, causal, scale, int(window or 0), seg_start, seg_end)
 
 
 class _QKVAttnFn(torch.autograd.Function):
