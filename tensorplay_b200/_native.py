@@ -59,6 +59,7 @@ _KERNEL_SIGS = {
     "tpb_adamw_flat": [P, P, P, P, I, P, I, LL, F, F, F, F, F, I, F, I, P, P, P],
     "tpb_adamw_set_overlap": [I, I],
     "tpb_adamw_multi": [I, P, P, P, P, P, P, I, I, F, F, F, F, F, I, F, I, P, P, P],
+    "tpb_adafactor_step": [P, P, I, P, P, P, P, P, LL, LL, F, F, F, F, F, F, F, F, P, P],
     "tpb_optim_multi": [I, I, I, P, P, P, P, P, P, P, I, F, F, F, F, F, F, P, P],
     "tpb_amp_unscale_multi": [I, P, P, I, P, P, P],
     "tpb_amp_update_scale": [P, P, P, F, F, I, P],

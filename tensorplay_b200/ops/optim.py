@@ -156,3 +156,26 @@ def amp_update_scale_(scale: torch.Tensor, growth_tracker: torch.Tensor, found_i
         _native.check(code, "tpb_amp_update_scale")
     else:
         torch._amp_update_scale_(scale, growth_tracker, found_inf, growth_factor, backoff_factor, growth_interval)
+
+
+def adafactor_step_(master: torch.Tensor, grad: torch.Tensor, model: Optional[torch.Tensor],
+                    row_var: Optional[torch.Tensor], col_var: Optional[torch.Tensor], variance: Optional[torch.Tensor],
+                    state: dict, *, lr: float, weight_decay: float, eps1: float, eps2: float, d: float, omb2: float,
+                    rho: float, grad_scale: float = 1.0, found_inf: Optional[torch.Tensor] = None) -> None:
+    """One fused Adafactor step of a vector or matrix on CUDA (fp32 weights and state; ``grad`` bf16 or fp32;
+    ``model``: optional bf16 copy written in the same pass). ``state`` caches the scratch buffer."""
+    if master.dim() > 1:
+        R, C = master.shape
+    else:
+        R, C = 1, master.numel()
+    L = lib()
+    need = 4 + (R + C if R > 1 else 0)
+    sc = state.get("_scratch")
+    if sc is None or sc.numel() < need:
+        sc = torch.empty(need, dtype=torch.float32, device=master.device)
+        state["_scratch"] = sc
+    code = L.tpb_adafactor_step(master.data_ptr(), grad.data_ptr(), int(grad.dtype == torch.bfloat16), ptr(model),
+                                ptr(row_var), ptr(col_var), ptr(variance), sc.data_ptr(), R, C, float(lr),
+                                float(weight_decay), float(eps1), float(eps2), float(d), float(omb2), float(rho),
+                                float(grad_scale), ptr(found_inf), stream_ptr())
+    _native.check(code, "tpb_adafactor_step")

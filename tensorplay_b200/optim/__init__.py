@@ -1,11 +1,11 @@
-"""``optim``: the optimizer zoo. AdamW / Adam, SGD, Adagrad and RMSprop run fused multi-tensor
+"""``optim``: the optimizer zoo. AdamW / Adam, SGD, Adagrad, RMSprop and Adafactor run fused
 sm_100a kernels on CUDA (fp32 state and master weights, bf16 parameter emit in the same pass); the
 rest of the zoo is torch's; ``Muon`` is implemented here (the reference ships it in tensorplay/optim, P3)."""
-from torch.optim import (ASGD, LBFGS, Adadelta, Adafactor, Adamax, NAdam, Optimizer,  # noqa: F401
+from torch.optim import (ASGD, LBFGS, Adadelta, Adamax, NAdam, Optimizer,  # noqa: F401
                          RAdam, Rprop, SparseAdam, lr_scheduler, swa_utils)
 
 from .adamw import Adam, AdamW
-from .fused import SGD, Adagrad, RMSprop
+from .fused import SGD, Adafactor, Adagrad, RMSprop
 from .muon import Muon
 
 __all__ = ["ASGD", "LBFGS", "SGD", "Adadelta", "Adafactor", "Adagrad", "Adamax", "NAdam", "Optimizer",

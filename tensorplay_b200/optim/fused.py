@@ -1,4 +1,4 @@
-"""SGD, Adagrad and RMSprop with a fused multi-tensor CUDA step.
+"""SGD, Adagrad, RMSprop and Adafactor with fused CUDA steps.
 
 Constructor arguments, state-dict keys and update rules are torch's (and the reference's,
 tensorplay/optim/sgd.py, adagrad.py, rmsprop.py over p10/include/OptimizerMTA.cuh:438 / :847 /
@@ -13,6 +13,7 @@ from typing import Dict, List
 
 import torch
 from torch.optim import SGD as _SGD
+from torch.optim import Adafactor as _Adafactor
 from torch.optim import Adagrad as _Adagrad
 from torch.optim import RMSprop as _RMSprop
 
@@ -141,4 +142,58 @@ class RMSprop(_FusedMixin, _RMSprop):
                 ga = [self.state[p]["grad_avg"].view(-1) for p in ps] if group["centered"] else None
                 self._run(ps, K.OPT_RMSPROP, flags, (sq, mb, ga), lr=float(group["lr"]),
                           weight_decay=group["weight_decay"], a=group["alpha"], b=group["momentum"], eps=group["eps"])
+        return loss
+
+
+class Adafactor(_Adafactor):
+    """torch's Adafactor (same arguments, state keys and rule; the reference's fused kernels are
+    p10/include/OptimizerMTA.cuh:1522-1753) with the step of every vector and matrix parameter on CUDA
+    done by ``tpb_adafactor_step``: two launches for a vector, four for a matrix, every norm and mean
+    of the rule kept on the device. State is fp32 (bf16 parameters keep an fp32 ``master``). Tensors of
+    three or more dimensions, CPU tensors and other dtypes take torch's step of the same class."""
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        fusable = [p for g in self.param_groups for p in g["params"] if p.grad is not None]
+        if not fusable or not all(_fusable(p) and p.dim() in (1, 2) for p in fusable) or \
+                any(isinstance(g["lr"], torch.Tensor) for g in self.param_groups):
+            return super().step(closure)
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        found_inf = getattr(self, "found_inf", None)
+        gs = getattr(self, "grad_scale", None)
+        grad_scale = 1.0 / float(gs) if gs is not None else 1.0
+        for group in self.param_groups:
+            eps1, eps2 = group["eps"]
+            lr = float(group["lr"])
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                st = self.state[p]
+                if len(st) == 0:
+                    st["step"] = torch.tensor(0.0)
+                    if p.dim() > 1:
+                        st["row_var"] = torch.zeros(p.shape[0], 1, dtype=torch.float32, device=p.device)
+                        st["col_var"] = torch.zeros(1, p.shape[1], dtype=torch.float32, device=p.device)
+                    else:
+                        st["variance"] = torch.zeros(p.shape, dtype=torch.float32, device=p.device)
+                for key in ("row_var", "col_var", "variance"):
+                    if key in st and st[key].dtype != torch.float32:
+                        st[key] = st[key].float()
+                st["step"] += 1
+                step = float(st["step"])
+                if p.dtype == torch.float32:
+                    master, model = p.data, None
+                else:
+                    if "master" not in st:
+                        st["master"] = p.detach().float().clone()
+                    master, model = st["master"], p.data
+                e1 = eps1 if eps1 is not None else torch.finfo(p.dtype).eps
+                grad = p.grad.contiguous()
+                K.adafactor_step_(master, grad, model, st.get("row_var"), st.get("col_var"), st.get("variance"), st,
+                                  lr=lr, weight_decay=group["weight_decay"], eps1=e1, eps2=eps2, d=group["d"],
+                                  omb2=step ** group["beta2_decay"], rho=min(lr, 1.0 / (step ** 0.5)),
+                                  grad_scale=-grad_scale if group["maximize"] else grad_scale, found_inf=found_inf)
         return loss

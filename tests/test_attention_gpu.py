@@ -90,6 +90,11 @@ def test_decode_attention_device_length_and_split_kv(n_splits):
     torch.testing.assert_close(lse[:, :, :G], torch.logsumexp(s, -1), rtol=1e-2, atol=2e-2)
 
 
+def _close(a, b, tol):
+    """Relative error in norm, or both negligibly small (a window of one key has exactly zero dq and dk)."""
+    return _rel(a, b) < tol or (a.float() - b.float()).abs().max().item() < 1e-4
+
+
 def _fwd_bwd(q, k, v, **kw):
     q = q.clone().requires_grad_(True)
     k = k.clone().requires_grad_(True)
@@ -115,7 +120,7 @@ def test_flash_sliding_window(T, window, D):
     O.check_status()
     ro, rq, rk, rv = _fwd_bwd(q.float(), k.float(), v.float(), causal=True, window=window)
     assert _rel(o, ro) < 1e-2
-    assert _rel(dq, rq) < 2e-2 and _rel(dk, rk) < 2e-2 and _rel(dv, rv) < 2e-2
+    assert _close(dq, rq, 2e-2) and _close(dk, rk, 2e-2) and _close(dv, rv, 2e-2)
 
 
 @pytest.mark.parametrize("lens", [[128, 128], [100, 300, 57], [1, 255, 640, 3], [513], [64, 64, 64, 64, 700]])

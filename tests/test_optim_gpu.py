@@ -103,3 +103,42 @@ def test_grad_scaler_with_fused_sgd_skips_non_finite_steps():
             sc.update()
     assert float(s1.get_scale()) == float(s2.get_scale())
     assert torch.allclose(m.weight, ref.weight, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("kw", [dict(lr=1e-2), dict(lr=5e-3, weight_decay=0.05, d=1.5, eps=(1e-30, 1e-3)),
+                                dict(lr=1e-2, maximize=True, beta2_decay=-0.6)])
+def test_fused_adafactor_matches_torch(kw):
+    """Factored (matrices) and plain (vectors) second moments, parameter-RMS step size and update clipping,
+    all on the device, against torch.optim.Adafactor over several steps."""
+    ours, ref = _params(torch.float32, seed=3), _params(torch.float32, seed=3)
+    o1, o2 = TO.Adafactor(ours, **kw), torch.optim.Adafactor(ref, **kw)
+    for step in range(5):
+        torch.manual_seed(300 + step)
+        for a, b in zip(ours, ref):
+            g = torch.randn_like(a) * (0.1 + step)
+            a.grad, b.grad = g.clone(), g.clone()
+        o1.step()
+        o2.step()
+    for a, b in zip(ours, ref):
+        assert torch.allclose(a, b, rtol=2e-4, atol=2e-5), (kw, a.shape, (a - b).abs().max().item())
+        sa, sb = o1.state[a], o2.state[b]
+        for key in ("row_var", "col_var", "variance"):
+            if key in sb:
+                assert torch.allclose(sa[key].view(-1), sb[key].view(-1), rtol=2e-4, atol=1e-7), key
+
+
+def test_fused_adafactor_bf16_parameters():
+    ours = _params(torch.bfloat16, seed=4)
+    ref = [p.detach().float().requires_grad_() for p in ours]
+    kw = dict(lr=1e-2, eps=(1e-30, 1e-3))   # the default eps1 is the dtype's epsilon, which differs between bf16 and fp32
+    o1, o2 = TO.Adafactor(ours, **kw), torch.optim.Adafactor(ref, **kw)
+    for step in range(4):
+        torch.manual_seed(400 + step)
+        for a, b in zip(ours, ref):
+            g = torch.randn_like(b).to(torch.bfloat16)
+            a.grad, b.grad = g, g.float()
+        o1.step()
+        o2.step()
+    for a, b in zip(ours, ref):
+        assert torch.allclose(o1.state[a]["master"], b, rtol=2e-4, atol=2e-5)
+        assert (a.float() - b).abs().max().item() < 2e-2
