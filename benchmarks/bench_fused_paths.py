@@ -127,6 +127,39 @@ def main():
     report(rank, f"gemm_rs tp{world} [{M}x{k_loc}]x[{H}x{k_loc}]", t_f, t_b, 2.0 * M * k_loc * H,
            (world - 1) * (M // world) * H * 2, 0, tf_peak, hbm_peak, which, {"local_gemm_only_ms": round(t_g, 4)})
 
+    # ---- FSDP parameter all-gather fused into the GEMM that consumes the weight: the Llama-8B gate/up projection,
+    # [tokens, 4096] x gather([28672, 4096])^T, against (a) NCCL all-gather then GEMM and (b) the GEMM alone on an
+    # already gathered weight (what an all-gather hidden a unit ahead leaves on the critical path)
+    if world > 1:
+        from tensorplay_b200.parallel.tp import WeightAGGemmPlan
+        from tensorplay_b200.parallel.symm import SymmArena
+        Mt, Kw, Nw = 4096, 4096, 28672
+        plan = WeightAGGemmPlan(SymmArena._instance, Nw, Kw, rows_per_flag=256)
+        plan.shard_view().normal_(0, 0.02)
+        xw = torch.randn(Mt, Kw, device=dev, dtype=torch.bfloat16)
+        w_full = torch.empty(Nw, Kw, device=dev, dtype=torch.bfloat16)
+        w_shard = plan.shard_view().clone()
+        out_w = torch.empty(Mt, Nw, device=dev, dtype=torch.bfloat16)
+
+        def wag_fused():
+            plan.run(xw, out=out_w)
+
+        def wag_base():
+            dist.all_gather_into_tensor(w_full, w_shard)
+            O.gemm(xw, w_full, out=out_w)
+
+        t_f, t_b = timed(wag_fused, args.iters), timed(wag_base, args.iters)
+        t_g = timed(lambda: O.gemm(xw, w_full, out=out_w), args.iters)
+        t_single = timed(lambda: O.gemm(xw, w_full, out=out_w, impl="single"), args.iters)
+        ref = O.gemm(xw, w_full)
+        plan.run(xw, out=out_w)
+        torch.cuda.synchronize()
+        err = ((out_w.float() - ref.float()).norm() / ref.float().norm()).item()
+        report(rank, f"fsdp weight all-gather -> gemm fsdp{world} [{Mt}x{Kw}]x gather[{Nw}x{Kw}]", t_f, t_b,
+               2.0 * Mt * Kw * Nw, (world - 1) * (Nw // world) * Kw * 2, 0, tf_peak, hbm_peak, which,
+               {"local_gemm_only_ms": round(t_g, 4), "local_gemm_one_cta_kernel_ms": round(t_single, 4),
+                "rel_err_vs_unfused": round(err, 6)})
+
     # ---- FSDP: parameter all-gather by peer pulls; reduce-scatter fused with scale + AdamW + bf16 emit
     u = max(eng.units, key=lambda t: t.padded)  # one transformer layer (218 M parameters)
     if world > 1:

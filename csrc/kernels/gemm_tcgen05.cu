@@ -86,6 +86,7 @@ struct GemmParams {
   const uint32_t* epoch_dev;
   uint32_t rs_per_call;     // arrivals per launch and source (rs_expect = epoch * rs_per_call)
   int tile_m_shift;         // rotate M tiles so that locally available rows are computed first
+  int tile_n_shift;         // the same along N (gathered B operand)
   // ---- fused reduce-scatter epilogue (rs_mode = 1): row block d of the product belongs to
   // rank d; tiles are stored (bf16) into rank d's staging slice [rank][rows_per_rank, N] and a
   // per-source counter on rank d is bumped; after its tiles every CTA helps reducing the slices
@@ -347,6 +348,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int tm, tn;
         tile_coords(tile, tiles_m, tiles_n, tm, tn);
         tm = (tm + p.tile_m_shift) % tiles_m;
+      tn = (tn + p.tile_n_shift) % tiles_n;
+        tn = (tn + p.tile_n_shift) % tiles_n;
         if (p.ag_operand) {
           ok = ag_wait_rows(p, p.ag_operand == 1 ? tm * kBlockM : tn * BLOCK_N,
                             p.ag_operand == 1 ? min(tm * kBlockM + kBlockM, p.M) : min(tn * BLOCK_N + BLOCK_N, p.N));
@@ -434,6 +437,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int tm, tn;
       tile_coords(tile, tiles_m, tiles_n, tm, tn);
       tm = (tm + p.tile_m_shift) % tiles_m;
+      tn = (tn + p.tile_n_shift) % tiles_n;
       int as = lt & 1;
       uint32_t aph = (lt >> 1) & 1;
       if (!mbar_wait_warp(&tfull[as], aph, wc, 4)) break;
@@ -796,7 +800,7 @@ int gemm_bf16_dispatch(const void* A, const void* B, void* C, const void* bias, 
   p.b_flags = b_flags; p.rows_per_flag = rows_per_flag > 0 ? rows_per_flag : 1;
   p.flag_want = flag_want;
   p.epoch_dev = nullptr; p.rs_per_call = 0;
-  p.n_copy = 0; p.ag_operand = 0; p.rs_mode = 0; p.tile_m_shift = 0; p.world = 1; p.rank = 0;
+  p.n_copy = 0; p.ag_operand = 0; p.rs_mode = 0; p.tile_m_shift = 0; p.tile_n_shift = 0; p.world = 1; p.rank = 0;
   p.sk_ws = g_sk_ws; p.sk_flags = g_sk_flags;
   if (fused) {
     p.n_copy = fused->n_copy; p.ag_operand = fused->ag_operand; p.world = fused->world;
@@ -804,7 +808,7 @@ int gemm_bf16_dispatch(const void* A, const void* B, void* C, const void* bias, 
     p.ag_chunk_bytes = fused->ag_chunk_bytes; p.ag_rows_per_rank = fused->ag_rows_per_rank;
     p.ag_rows_per_flag = fused->ag_rows_per_flag; p.ag_flags = fused->ag_flags;
     p.pad_local = fused->pad_local; p.ready_slot = fused->ready_slot; p.done_slot = fused->done_slot;
-    p.epoch = fused->epoch; p.epoch_dev = fused->epoch_dev; p.rs_per_call = fused->rs_per_call; p.tile_m_shift = fused->tile_m_shift; p.rs_mode = fused->rs_mode;
+    p.epoch = fused->epoch; p.epoch_dev = fused->epoch_dev; p.rs_per_call = fused->rs_per_call; p.tile_m_shift = fused->tile_m_shift; p.tile_n_shift = fused->tile_n_shift; p.rs_mode = fused->rs_mode;
     p.rs_rows_per_rank = fused->rs_rows_per_rank; p.rs_expect = fused->rs_expect;
     p.rs_out = fused->rs_out;
     for (int r = 0; r < 16; ++r) {
@@ -919,6 +923,45 @@ extern "C" int tpb_ag_gemm(size_t a_off, const void* B, void* C, const void* bia
   return tpb::gemm_bf16_dispatch(sv->peer[rank] + a_off, B, C, bias, M, N, K, K, ldb, ldc, 0, b_mn,
                                  out_f32, 0, 0, 1.f, nullptr, 0, 0, 0, status,
                                  static_cast<cudaStream_t>(stream), &f);
+}
+
+// C[M, N] = A[M, K] * gather_rows(W)[N, K]^T where the WEIGHT is row-sharded over the ranks (a fully
+// sharded parameter): rank r's rows [r * N/world, (r+1) * N/world) live in rank r's copy of the symmetric
+// buffer at arena offset w_off (shape [N, K], ld = K); after the call the local copy holds all rows.
+// Copy CTAs of the same launch pull the peers' shards while the tensor-core CTAs start on the tiles of
+// the local rows; a tile of remote rows waits (bounded) for the flags of its row blocks.
+// flags / slots / epoch as in tpb_ag_gemm.
+extern "C" int tpb_ag_gemm_weight(const void* A, size_t w_off, void* C, const void* bias, int M, int N, int K,
+                                  int lda, int ldc, int a_mn, int out_f32, uint32_t* flags, int rows_per_flag,
+                                  size_t pad_off, int ready_slot, int done_slot, uint32_t epoch, int n_copy,
+                                  double wait_s, uint32_t* status, void* stream, const uint32_t* epoch_dev) {
+  const tpb::SymmView* sv = tpb::symm_view();
+  if (!sv || sv->world < 1 || N % sv->world) return -2;
+  const int world = sv->world, rank = sv->rank;
+  const int rows_per_rank = N / world;
+  if (rows_per_flag <= 0 || rows_per_rank % rows_per_flag) return -2;
+  tpb::GemmFused f;
+  memset(&f, 0, sizeof(f));
+  f.world = world; f.rank = rank;
+  f.n_copy = world > 1 ? (n_copy > 0 ? n_copy : 16) : 0;
+  f.ag_operand = world > 1 ? 2 : 0;
+  f.ag_shard_bytes = (unsigned long long)rows_per_rank * K * 2;
+  f.ag_chunk_bytes = (unsigned long long)rows_per_flag * K * 2;
+  f.ag_rows_per_rank = rows_per_rank; f.ag_rows_per_flag = rows_per_flag;
+  f.ag_flags = flags;
+  f.ag_dst = sv->peer[rank] + w_off;
+  for (int r = 0; r < world; ++r) {
+    f.ag_src[r] = sv->peer[r] + w_off + (size_t)r * f.ag_shard_bytes;
+    f.pad_peer[r] = reinterpret_cast<uint32_t*>(sv->peer[r] + pad_off);
+  }
+  f.pad_local = reinterpret_cast<uint32_t*>(sv->peer[rank] + pad_off);
+  f.ready_slot = ready_slot; f.done_slot = done_slot; f.epoch = epoch; f.epoch_dev = epoch_dev;
+  const int block_n = tpb::pick_block_n(M, N);
+  const int tiles_n = (N + block_n - 1) / block_n;
+  f.tile_n_shift = (rows_per_rank % block_n == 0) ? (int)(((long long)rank * rows_per_rank / block_n) % tiles_n) : 0;
+  f.wait_ns = wait_s > 0 ? (unsigned long long)(wait_s * 1e9) : 0;
+  return tpb::gemm_bf16_dispatch(A, sv->peer[rank] + w_off, C, bias, M, N, K, lda, K, ldc, a_mn, 0, out_f32, 0, 0,
+                                 1.f, nullptr, 0, 0, 0, status, static_cast<cudaStream_t>(stream), &f);
 }
 
 // out[M/world, N] (local) = sum over ranks of (A_r[M, K] * B_r[N, K]^T)[rows of this rank].

@@ -39,6 +39,7 @@ struct GemmFused {
   const uint32_t* epoch_dev;  // device-side epoch word (epoch = *epoch_dev + 1) or null
   uint32_t rs_per_call;
   int tile_m_shift;
+  int tile_n_shift;
   int rs_mode, rs_rows_per_rank;
   char* rs_stage[16];
   uint32_t* rs_cnt[16];

@@ -29,6 +29,9 @@ _SIGS = {
     "tpb_ag_gemm": [C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                     C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_size_t, C.c_int, C.c_int,
                     C.c_uint32, C.c_int, C.c_double, C.c_void_p, C.c_void_p, C.c_void_p],
+    "tpb_ag_gemm_weight": [C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                           C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_size_t, C.c_int, C.c_int,
+                           C.c_uint32, C.c_int, C.c_double, C.c_void_p, C.c_void_p, C.c_void_p],
     "tpb_gemm_rs": [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                     C.c_int, C.c_int, C.c_size_t, C.c_size_t, C.c_int, C.c_uint32, C.c_double,
                     C.c_void_p, C.c_void_p, C.c_void_p],
@@ -95,6 +98,57 @@ class AGGemmPlan:
         _native.check(raw.tpb_symm_bump(self.epoch_dev[i:].data_ptr(), stream_ptr()), "tpb_symm_bump")
         _native.launch_count += 2
         return out, self.full[i]
+
+
+class WeightAGGemmPlan:
+    """A fully sharded weight ``[N, K]`` (rank ``r`` owns rows ``[r N / world, (r + 1) N / world)``) gathered INSIDE
+    the GEMM that consumes it: ``C[M, N] = x[M, K] @ gather(W)^T``. Copy CTAs of the launch pull the peers' shards
+    into the local full buffer while the tensor-core CTAs begin with the tiles of the local rows; after the call
+    the full weight is resident for the other uses of the unit (the fused form of an FSDP all-gather followed by
+    the first GEMM of the unit; the reference runs copy-in, ``all_gather_single``, copy-out before the GEMM,
+    tensorplay/distributed/fsdp/_fully_shard/_fsdp_collectives.py:337-470)."""
+
+    def __init__(self, arena: SymmArena, n_total: int, k: int, rows_per_flag: int = 256, n_copy: int = 16,
+                 wait_s: float = 30.0):
+        w = arena.world
+        assert n_total % w == 0 and (n_total // w) % rows_per_flag == 0
+        self.arena, self.n, self.k, self.world, self.rank = arena, n_total, k, w, arena.rank
+        self.rows = n_total // w
+        self.rpf, self.n_copy, self.wait_s = rows_per_flag, n_copy, wait_s
+        self.full = arena.alloc(n_total * k, torch.bfloat16).view(n_total, k)
+        self.flags = torch.zeros(w * (self.rows // rows_per_flag) + 1, dtype=torch.int32, device=arena.device)
+        self.ready, self.done = arena.slots(w), arena.slots(w)
+        self.epoch_dev = torch.zeros(1, dtype=torch.int32, device=arena.device)
+        self.status = status_word(arena.device)
+
+    def shard_view(self) -> torch.Tensor:
+        """This rank's rows of the full buffer: the shard lives here (peers read it from this place)."""
+        return self.full[self.rank * self.rows: (self.rank + 1) * self.rows]
+
+    def wait_readers(self) -> None:
+        """Order the stream after every peer's reads of this rank's shard in the previous call (call before
+        the shard is rewritten, e.g. by the optimizer step)."""
+        if self.world > 1:
+            raw = _raw(self.arena)
+            _native.check(raw.tpb_symm_wait_slots_dev(self.arena.pad_off, self.done, self.epoch_dev.data_ptr(),
+                                                      self.wait_s, self.status.data_ptr(), stream_ptr()),
+                          "tpb_symm_wait_slots_dev")
+            _native.launch_count += 1
+
+    def run(self, x: torch.Tensor, bias=None, out=None) -> torch.Tensor:
+        m = x.shape[0]
+        if out is None:
+            out = torch.empty(m, self.n, dtype=torch.bfloat16, device=x.device)
+        raw = _raw(self.arena)
+        code = raw.tpb_ag_gemm_weight(x.data_ptr(), self.arena.offset_of(self.full), out.data_ptr(),
+                                      None if bias is None else bias.data_ptr(), m, self.n, self.k, x.stride(0),
+                                      out.stride(0), 0, 0, self.flags.data_ptr(), self.rpf, self.arena.pad_off,
+                                      self.ready, self.done, 0, self.n_copy, self.wait_s, self.status.data_ptr(),
+                                      stream_ptr(), self.epoch_dev.data_ptr())
+        _native.check(code, "tpb_ag_gemm_weight")
+        _native.check(raw.tpb_symm_bump(self.epoch_dev.data_ptr(), stream_ptr()), "tpb_symm_bump")
+        _native.launch_count += 2
+        return out
 
 
 class GemmRSPlan:
