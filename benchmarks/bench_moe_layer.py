@@ -8,6 +8,11 @@ memory instead of NVLink).
 Prints one JSON line; roofline fractions use the measured peaks (`--peak-tflops`, `--peak-gbs`).
 
     python benchmarks/bench_moe_layer.py
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 benchmarks/bench_moe_layer.py
+
+Under torchrun every rank brings `--tokens` tokens and owns `--experts` experts (N x experts in total), rows
+cross NVLink, and the times are the maximum over the ranks (uniform random routing, so the load is balanced
+and the numbers show the kernels, not the waiting for a slower rank).
 """
 import argparse
 import json
@@ -22,8 +27,11 @@ from tensorplay_b200.parallel.moe import MoEWorkspace, expert_parallel_ffn, grou
 
 
 def timed(fn, iters=10, warmup=3):
+    import torch.distributed as dist
     for _ in range(warmup):
         fn()
+    if dist.is_initialized():
+        dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
     e0.record()
@@ -31,7 +39,10 @@ def timed(fn, iters=10, warmup=3):
         fn()
     e1.record()
     torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / iters
+    t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda")
+    if dist.is_initialized():
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item()
 
 
 def main():
@@ -44,18 +55,25 @@ def main():
     ap.add_argument("--peak-tflops", type=float, default=1620.4)
     ap.add_argument("--peak-gbs", type=float, default=6541.1)
     a = ap.parse_args()
-    dev = torch.device("cuda", 0)
+    import torch.distributed as dist
+    world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        from tensorplay_b200.parallel.symm import SymmArena
+        SymmArena(4 << 30)
     T, E, k, H, I = a.tokens, a.experts, a.top_k, a.hidden, a.inter
-    torch.manual_seed(0)
+    torch.manual_seed(rank)
     x = torch.randn(T, H, device=dev, dtype=torch.bfloat16)
-    idx = torch.randint(0, E, (T, k), device=dev)
+    idx = torch.randint(0, E * world, (T, k), device=dev)
     w = torch.rand(T, k, device=dev).to(torch.bfloat16)
     wgu = (0.02 * torch.randn(E, 2 * I, H, device=dev)).to(torch.bfloat16).requires_grad_()
     wd = (0.02 * torch.randn(E, H, I, device=dev)).to(torch.bfloat16).requires_grad_()
-    ws = MoEWorkspace(T, k, H, E, capacity_factor=1.0)
+    ws = MoEWorkspace(T, k, H, E * world, capacity_factor=1.0 if world == 1 else 1.25)
     rows = T * k
-    res = {"tokens": T, "experts": E, "top_k": k, "hidden": H, "inter": I, "expert_rows": rows}
+    res = {"ranks": world, "tokens": T, "experts_per_rank": E, "top_k": k, "hidden": H, "inter": I,
+           "expert_rows_per_rank": rows}
 
     dst_rank, dst_row, offs = ws.route(idx)
     res["route_ms"] = round(timed(lambda: ws.route(idx)), 4)
@@ -101,7 +119,14 @@ def main():
     res["ffn_forward_backward_ms"] = round(timed(fwd_bwd, iters=5), 4)
     res["ffn_fwd_bwd_model_tflops"] = round(3.0 * (fl_gu + fl_d) / res["ffn_forward_backward_ms"] / 1e9, 1)
     O.check_status()
-    print(json.dumps(res), flush=True)
+    if world > 1:
+        remote = (world - 1) / world * rows * H * 2   # bytes that cross NVLink per rank and direction
+        res["dispatch_nvlink_gbs"] = round(remote / res["dispatch_ms"] / 1e6, 1)
+        res["combine_nvlink_gbs"] = round(remote / res["combine_ms"] / 1e6, 1)
+    if rank == 0:
+        print(json.dumps(res), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -298,6 +298,43 @@ __global__ void moe_signal_kernel(MoeSync s, int slot) {
   }
 }
 
+// Warp per row: out[r] = <a[r], b[r]> in fp32, stored as the bf16 pair (hi, lo) with hi + lo == the
+// fp32 value to 16 bits, in columns 0 and 1 of an 8-column bf16 row (columns 2..7 zero), so that the
+// row-pull kernel above can fetch it like any other expert row. rows_dev: device word with the number
+// of rows in use.
+__global__ void __launch_bounds__(256)
+moe_rowdot_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
+                  __nv_bfloat16* __restrict__ out, const int* __restrict__ rows_dev, int cap_rows, int H) {
+  const int rows = min(*rows_dev, cap_rows);
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  const int nvec = H / 8;
+  for (long long r = (long long)blockIdx.x * wpb + (threadIdx.x >> 5); r < rows; r += (long long)gridDim.x * wpb) {
+    float acc = 0.f;
+    for (int v = lane; v < nvec; v += 32) {
+      const uint4 ua = reinterpret_cast<const uint4*>(a + r * H)[v];
+      const uint4 ub = reinterpret_cast<const uint4*>(b + r * H)[v];
+      const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&ua);
+      const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&ub);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 x = __bfloat1622float2(ha[j]), y = __bfloat1622float2(hb[j]);
+        acc += x.x * y.x + x.y * y.y;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) {
+      const __nv_bfloat16 hi = __float2bfloat16(acc);
+      const __nv_bfloat16 lo = __float2bfloat16(acc - __bfloat162float(hi));
+      uint4 o4 = make_uint4(0, 0, 0, 0);
+      __nv_bfloat162 p2 = __halves2bfloat162(hi, lo);
+      o4.x = *reinterpret_cast<uint32_t*>(&p2);
+      reinterpret_cast<uint4*>(out)[r] = o4;
+    }
+  }
+}
+
 static MoeSync make_moe_sync(const SymmView* sv, size_t pad_off, uint32_t epoch, uint32_t* status,
                              double wait_s) {
   MoeSync s;
@@ -388,5 +425,16 @@ extern "C" int tpb_moe_signal(size_t pad_off, int slot, uint32_t epoch, void* st
   if (!sv) return -2;
   MoeSync s = make_moe_sync(sv, pad_off, epoch, nullptr, 0);
   moe_signal_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(s, slot);
+  return (int)cudaGetLastError();
+}
+
+// out [cap_rows, 8] bf16 <- per-row dot products of a and b ([cap_rows, H] bf16), rows limited by *rows_dev.
+extern "C" int tpb_moe_rowdot(const void* a, const void* b, void* out, const int* rows_dev, int cap_rows, int H,
+                              void* stream) {
+  if (H % 8 || cap_rows <= 0) return -2;
+  int blocks = (cap_rows + 7) / 8;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  moe_rowdot_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b,
+                                                              (__nv_bfloat16*)out, rows_dev, cap_rows, H);
   return (int)cudaGetLastError();
 }

@@ -37,6 +37,7 @@ _SIGS = {
                         C.c_longlong, C.c_void_p, C.c_longlong, C.c_void_p, C.c_size_t, C.c_int, C.c_uint32,
                         C.c_int, C.c_double, C.c_void_p, C.c_void_p],
     "tpb_moe_signal": [C.c_size_t, C.c_int, C.c_uint32, C.c_void_p],
+    "tpb_moe_rowdot": [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p],
 }
 
 
@@ -137,6 +138,8 @@ class MoEWorkspace:
         self.xbuf = a.alloc(self.cap * hidden, torch.bfloat16).view(self.cap, hidden)   # expert inputs
         self.ybuf = a.alloc(self.cap * hidden, torch.bfloat16).view(self.cap, hidden)   # expert outputs / dx rows
         self.dbuf = a.alloc(self.cap * hidden, torch.bfloat16).view(self.cap, hidden)   # dy rows (backward)
+        self.rbuf = a.alloc(self.cap * 8, torch.bfloat16).view(self.cap, 8)             # per-row scalars (backward)
+        self._ones8 = None
         # Which forward's rows xbuf / ybuf hold. A backward that finds its own forward's number here
         # (the forward ran immediately before it, as under per-layer activation recomputation) reuses
         # the dispatched inputs and the expert outputs instead of routing and computing them again.
@@ -188,17 +191,33 @@ class MoEWorkspace:
         _native.launch_count += 2
         _native.check(code, "tpb_symm_wait_slots")
 
-    def combine(self, buf: torch.Tensor, dst_rank, dst_row, w=None, tokens=None, g=None, want_out=True):
+    def row_dots(self, a_rows: torch.Tensor, b_rows: torch.Tensor, rows_dev: torch.Tensor, dst_rank, dst_row,
+                 tokens: int) -> torch.Tensor:
+        """``out[t * k + j] = <a_rows[r], b_rows[r]>`` for the expert row ``r`` of assignment ``(t, j)``: the dot
+        products are taken where the rows live and only the scalars cross NVLink (16 bytes per row instead of
+        the row itself)."""
+        code = self.raw.tpb_moe_rowdot(a_rows.data_ptr(), b_rows.data_ptr(), self.rbuf.data_ptr(), rows_dev.data_ptr(),
+                                       self.cap, self.H, stream_ptr())
+        _native.launch_count += 1
+        _native.check(code, "tpb_moe_rowdot")
+        if self._ones8 is None or self._ones8.shape[0] < tokens:
+            self._ones8 = torch.zeros(tokens, 8, dtype=torch.bfloat16, device=a_rows.device)
+            self._ones8[:, :2] = 1.0
+        _, dots = self.combine(self.rbuf, dst_rank, dst_row, tokens=tokens, g=self._ones8, want_out=False, width=8)
+        return dots
+
+    def combine(self, buf: torch.Tensor, dst_rank, dst_row, w=None, tokens=None, g=None, want_out=True, width=None):
         """Signal that ``buf`` is complete on this rank, then pull: ``out[t] = sum_k w * buf_row``."""
         self.epoch += 1
+        H = self.H if width is None else width
         tokens = tokens if tokens is not None else dst_row.numel() // self.k
         code = self.raw.tpb_moe_signal(self.arena.pad_off, self.slot_done, self.epoch, stream_ptr())
         _native.check(code, "tpb_moe_signal")
-        out = torch.empty(tokens, self.H, dtype=torch.bfloat16, device=buf.device) if want_out else None
+        out = torch.empty(tokens, H, dtype=torch.bfloat16, device=buf.device) if want_out else None
         dots = torch.empty(tokens * self.k, dtype=torch.float32, device=buf.device) if g is not None else None
         code = self.raw.tpb_moe_combine(self.arena.offset_of(buf), dst_rank.data_ptr(), dst_row.data_ptr(),
-                                        None if w is None else w.data_ptr(), self.k, tokens, self.H,
-                                        None if out is None else out.data_ptr(), self.H,
+                                        None if w is None else w.data_ptr(), self.k, tokens, H,
+                                        None if out is None else out.data_ptr(), H,
                                         None if g is None else g.data_ptr(), 0 if g is None else g.stride(0),
                                         None if dots is None else dots.data_ptr(), self.arena.pad_off,
                                         self.slot_done, self.epoch, 0, self.wait_s, self.status.data_ptr(),
@@ -254,13 +273,17 @@ class _EPFFNFn(torch.autograd.Function):
             act = _swiglu_rows(gu, offs[ws.El:])
             grouped_gemm(act, w_down, offs, out=ws.ybuf, workspace=ws.gws)
         ws.generation += 1  # ybuf is overwritten below
-        # gate-weight gradient: <dy[t], y_row>
-        _, dots = ws.combine(ws.ybuf, dst_rank, dst_row, tokens=T, g=dy, want_out=False)
         # dy rows, scaled by the gate weights, to the expert owners (padding rows of dbuf may hold
         # anything: they meet zero rows of xin / act in the weight gradients and their own output
         # rows are never pulled)
         ws.dispatch(dy, dst_rank, dst_row, ws.dbuf, scale=wf)
         dyr = ws.dbuf
+        # gate-weight gradient <dy[t], y_row>: the owner of the row has w * dy[t] (just dispatched) and
+        # y_row side by side, so it takes the dot product and only that scalar travels back; the token's
+        # rank divides by w (top-k weights of a softmax are positive; a weight of exactly zero gets a
+        # zero gradient)
+        wdots = ws.row_dots(ws.dbuf, ws.ybuf, offs[ws.El:], dst_rank, dst_row, T)
+        dots = torch.where(wf != 0, wdots / wf, torch.zeros_like(wdots))
         dact = grouped_gemm(dyr, w_down, offs, b_mn=True, workspace=ws.gws)                # [cap, I]
         dwd = _wgrad(dyr, act, offs, ctx.refs[1], ws)
         dgu = _swiglu_rows_bwd(dact, gu, offs[ws.El:])   # rows beyond the limit stay unwritten: no tile reads them
