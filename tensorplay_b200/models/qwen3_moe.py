@@ -124,7 +124,8 @@ class Qwen3MoEBlock(nn.Module):
         logits = ops.linear(flat, self.router)
         idx, w, aux = topk_route(logits, cfg.top_k, cfg.norm_topk_prob)
         y = expert_parallel_ffn(flat, idx, w.to(flat.dtype), self.w_gate_up, self.w_down, self.workspace,
-                                cfg.num_experts, self.ep_group)
+                                cfg.num_experts, self.ep_group,
+                                result_is_region_output=getattr(self, "_tpb_region_is_layer", False))
         if cfg.aux_loss_coef and torch.is_grad_enabled():
             y = _AuxLoss.apply(y, aux, cfg.aux_loss_coef * self.loss_scale)
         return x + y.view(B, T, H)

@@ -61,3 +61,20 @@ def take() -> Optional[Tuple]:
     item = rep["items"][rep["next"]]
     rep["next"] += 1
     return item
+
+
+@contextlib.contextmanager
+def recompute():
+    """Marks the forward that a checkpointing driver runs again in backward only to rebuild the autograd
+    graph: the VALUE of the region's result is discarded (backward starts from the incoming gradient), so an
+    op that produces that result as its last step may skip the step (see :func:`recomputing`)."""
+    prev = getattr(_tls, "recompute", False)
+    _tls.recompute = True
+    try:
+        yield
+    finally:
+        _tls.recompute = prev
+
+
+def recomputing() -> bool:
+    return bool(getattr(_tls, "recompute", False))

@@ -155,7 +155,8 @@ class _UnitFn(torch.autograd.Function):
         if ctx.checkpoint:
             tensors = [t.detach().requires_grad_(t.requires_grad) if t.is_floating_point() else t
                        for t in ctx.saved_tensors]
-            with torch.enable_grad(), (_ckpt.replay(ctx.kept) if ctx.kept is not None else contextlib.nullcontext()):
+            with torch.enable_grad(), _ckpt.recompute(), \
+                    (_ckpt.replay(ctx.kept) if ctx.kept is not None else contextlib.nullcontext()):
                 out = ctx.fn(*tensors, *ctx.extra)
             ctx.kept = None
         else:
@@ -598,6 +599,8 @@ class FSDPEngine:
         x = _UnitFn.apply(self, 0, lambda d, t: m.embed_tokens(t), False, 1, self._dummy, tokens)
         extra = m.layer_extra_args(tokens) if hasattr(m, "layer_extra_args") else ()
         for i, layer in enumerate(m.layers):
+            # each layer is a checkpointed region of its own: what it returns is the region's result
+            layer._tpb_region_is_layer = True
             x = _UnitFn.apply(self, 1 + i, layer, self.checkpoint, 1, x, *extra)
         loss = _UnitFn.apply(self, len(self.units) - 1, lambda h, t: m.head(h, t), False, 1, x, targets)
         loss.backward()

@@ -21,6 +21,8 @@ from typing import Optional, Tuple
 import torch
 import torch.distributed as dist
 
+from ..ops import _ckpt
+
 from .. import _native, ops
 from ..ops._common import lib, status_word, stream_ptr
 from .symm import NO_OFFSET, SymmArena
@@ -229,7 +231,7 @@ class MoEWorkspace:
 
 class _EPFFNFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, topk_idx, topk_w, w_gate_up, w_down, ws: MoEWorkspace):
+    def forward(ctx, x, topk_idx, topk_w, w_gate_up, w_down, ws: MoEWorkspace, result_is_region_output=False):
         T, H = x.shape
         dst_rank, dst_row, offs = ws.route(topk_idx)
         ws.dispatch(x, dst_rank, dst_row, ws.xbuf)
@@ -238,7 +240,12 @@ class _EPFFNFn(torch.autograd.Function):
         act = _swiglu_rows(gu, rows_dev)                                                    # [cap, I]
         grouped_gemm(act, w_down, offs, out=ws.ybuf, workspace=ws.gws)                      # [cap, H]
         wf = topk_w.reshape(-1).float().contiguous()
-        y, _ = ws.combine(ws.ybuf, dst_rank, dst_row, w=wf, tokens=T)
+        if result_is_region_output and _ckpt.recomputing():
+            # recomputation of a checkpointed block whose result this is: nobody reads the value (backward
+            # starts from the incoming gradient), so the pull of the expert rows over NVLink is skipped
+            y = x.new_empty(T, H)
+        else:
+            y, _ = ws.combine(ws.ybuf, dst_rank, dst_row, w=wf, tokens=T)
         ws.generation += 1
         ctx.gen = ws.generation
         ctx.ws = ws
@@ -290,7 +297,7 @@ class _EPFFNFn(torch.autograd.Function):
         dxr = grouped_gemm(dgu, w_gate_up, offs, b_mn=True, out=ws.ybuf, workspace=ws.gws)  # [cap, H]
         dwg = _wgrad(dgu, xin, offs, ctx.refs[0], ws)
         dx, _ = ws.combine(dxr, dst_rank, dst_row, tokens=T)
-        return dx, None, dots.view(T, -1).to(dy.dtype), dwg, dwd, None
+        return dx, None, dots.view(T, -1).to(dy.dtype), dwg, dwd, None, None
 
 
 def _wgrad(dy_rows, x_rows, offs, ref, ws):
@@ -305,11 +312,13 @@ def _wgrad(dy_rows, x_rows, offs, ref, ws):
 def expert_parallel_ffn(x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor,
                         w_gate_up: torch.Tensor, w_down: torch.Tensor,
                         ws: Optional[MoEWorkspace] = None, num_experts: Optional[int] = None,
-                        group=None) -> torch.Tensor:
+                        group=None, result_is_region_output: bool = False) -> torch.Tensor:
     """SwiGLU experts sharded over ranks. ``x [T, H]``, ``topk_idx/topk_w [T, k]`` (global expert
-    ids), ``w_gate_up [E_local, 2I, H]``, ``w_down [E_local, H, I]`` (this rank's experts)."""
+    ids), ``w_gate_up [E_local, 2I, H]``, ``w_down [E_local, H, I]`` (this rank's experts).
+    ``result_is_region_output``: the caller only adds the result to the residual stream and returns it as
+    the result of a checkpointed region; its recomputation then skips the final pull of the expert rows."""
     if ws is not None and x.is_cuda and x.dtype == torch.bfloat16:
-        return _EPFFNFn.apply(x, topk_idx, topk_w, w_gate_up, w_down, ws)
+        return _EPFFNFn.apply(x, topk_idx, topk_w, w_gate_up, w_down, ws, result_is_region_output)
     return expert_ffn_reference(x, topk_idx, topk_w, w_gate_up, w_down, group)
 
 
