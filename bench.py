@@ -165,11 +165,15 @@ def main():
         model.reset_parameters(seed=1234)
         # arena head-room for the expert-parallel workspace (3 row buffers of `world` x the mean load)
         ws_bytes = 3 * (B * T * cfg.top_k * world + 4096) * cfg.hidden_size * 2 + (256 << 20)
-        engine = FSDPEngine(model, opt, comm=args.comm, activation_checkpointing=True, symm_extra_bytes=ws_bytes)
+        engine = FSDPEngine(model, opt, comm=args.comm,
+                            activation_checkpointing=True if args.ac == "full" else "selective",
+                            symm_extra_bytes=ws_bytes)
         # drop-less for any routing: one rank may receive every token of the box
         model.attach_workspace(B * T, capacity_factor=float(world))
         parallelism = f"ep{world} experts, fsdp{world} attention/embeddings"
-        ac_text = "per block, full recompute"
+        ac_text = ("per block, full recompute" if args.ac == "full" else
+                   "per block, selective: dense projection and attention outputs kept, norms / RoPE / router top-k / "
+                   "expert FFN recomputed")
     else:
         if args.model == "tiny":
             cfg = LlamaConfig.tiny(max_seq_len=T)

@@ -26,6 +26,9 @@ def main():
     ap.add_argument("--layers", type=int, default=48)
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--experts", type=int, default=128)
+    ap.add_argument("--ac", default="selective", choices=["full", "selective"],
+                    help="per-block activation checkpointing: recompute everything, or keep the outputs of the dense "
+                         "projections and of the attention (92 MB per layer) and recompute the rest")
     a = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -41,7 +44,7 @@ def main():
     # arena head-room for the expert-parallel workspace (3 row buffers of `world` x the mean load)
     ws_bytes = 3 * (a.seq * cfg.top_k * world + 4096) * cfg.hidden_size * 2 + (256 << 20)
     eng = FSDPEngine(model, AdamWConfig(lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1),
-                     activation_checkpointing=True, symm_extra_bytes=ws_bytes)
+                     activation_checkpointing=True if a.ac == "full" else "selective", symm_extra_bytes=ws_bytes)
     # drop-less for any routing: one rank may receive every token of the box (a random-init router
     # over 48 layers concentrates tokens on few experts, which shows up as load imbalance below)
     ws = model.attach_workspace(a.seq, capacity_factor=float(world))
@@ -75,6 +78,7 @@ def main():
         print(json.dumps({"config": f"Qwen3-30B-A3B-shape MoE ({a.layers} layers, {a.experts} experts, top-8), EP={world}, seq {a.seq}, bf16",
                           "n_gpus": world, "tokens_per_s": round(world * a.seq / (ms / 1e3), 1),
                           "ms_per_step": round(ms, 3), "loss": round(float(loss), 4), "data": "synthetic",
+                          "activation_checkpointing": a.ac,
                           "expert_load_max_over_mean_last_layer": round(float(rows_max) * world / max(float(rows), 1.0), 2)}),
               flush=True)
     if world > 1:
