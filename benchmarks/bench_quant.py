@@ -103,7 +103,7 @@ def main():
             out.append({"kernel": f"W{bits}A16 GEMV ({label})", "shape": [M, N, K], "group": group,
                         "ms": round(t, 4), "weight_gbs": round(wbytes / t / 1e6, 1),
                         "fraction_of_measured_hbm": round(wbytes / t / 1e6 / hbm, 3)})
-        gemv_config(0, False)
+        gemv_config(0, False, 2)
     O.check_status()
     for o in out:
         print(json.dumps(o), flush=True)

@@ -54,16 +54,22 @@ def generate(model, input_ids: Tensor, max_new_tokens: int = 20, do_sample: bool
              past_key_values=None) -> Tensor:
     """Returns ``[batch, prompt_len + n_generated]`` (prompt followed by generated / pad tokens)."""
     if input_ids.dim() != 2:
-        raise ValueError(f"input_ids must be [batch, seq], got shape {tuple(input_ids.shape)}")
-    if max_new_tokens <= 0:
-        return input_ids
-    if pad_token_id is None:
-        pad_token_id = eos_token_id if eos_token_id is not None else 0
-    if use_cache and past_key_values is None:
-        create = getattr(model, "create_empty_cache", None)
-        past_key_values = create() if create is not None else DynamicCache()
+        raise ValueError(f"generate: expected a [batch, prompt_len] tensor of token ids, got {input_ids.dim()} dimensions")
     B, T0 = input_ids.shape
     device = input_ids.device
+    if max_new_tokens < 1:
+        return input_ids
+    # finished sequences are filled with the padding id; without one, the end-of-sequence id (or 0) stands in
+    fill = pad_token_id
+    if fill is None:
+        fill = 0 if eos_token_id is None else eos_token_id
+    pad_token_id = fill
+    cache = past_key_values
+    if use_cache and cache is None:
+        # models that need a particular cache kind (static, paged, linear-state) build it themselves
+        factory = getattr(model, "create_empty_cache", None)
+        cache = DynamicCache() if factory is None else factory()
+    past_key_values = cache
     out = torch.full((B, T0 + max_new_tokens), pad_token_id, dtype=input_ids.dtype, device=device)
     out[:, :T0] = input_ids
     finished = torch.zeros(B, dtype=torch.bool, device=device)

@@ -41,7 +41,18 @@ def test_int8_rowwise_quantise():
                                           (8, 16, 2048),   # one group per lane slice of the MMA kernel
                                           (8, 0, 2064), (4, 16, 2064)])  # K off the MMA chunk: CUDA-core kernel
 @pytest.mark.parametrize("M", [1, 3, 16])
-def test_weight_only_gemv(bits, group, K, M):
+@pytest.mark.parametrize("version", [1, 2])
+def test_weight_only_gemv(bits, group, K, M, version):
+    """Both versions of the warp-MMA kernel (2 = the loop written for instruction count)."""
+    from tensorplay_b200.ops.quant import gemv_config
+    gemv_config(0, False, version)
+    try:
+        _check_weight_only_gemv(bits, group, K, M)
+    finally:
+        gemv_config(0, False, 2)
+
+
+def _check_weight_only_gemv(bits, group, K, M):
     torch.manual_seed(1)
     N = 1000
     w = torch.randn(N, K, device=DEV)
