@@ -30,6 +30,9 @@ def main():
     ap.add_argument("--prompt", type=int, default=4096)
     ap.add_argument("--decode-batch", type=int, default=64)
     ap.add_argument("--model", default="70b", choices=["70b", "8b", "tiny"])
+    ap.add_argument("--decode-layout", default="replicated", choices=["replicated", "sequence"],
+                    help="replicated activations + one-launch all-reduce/residual/norm, or rows sharded over the ranks "
+                         "with fused all-gather / reduce-scatter GEMMs")
     a = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -46,6 +49,7 @@ def main():
     enable_splitk()
     model = LlamaTP(cfg, tp, device=dev, dtype=torch.bfloat16)
     model.reset_parameters(0)
+    model.decode_layout = a.decode_layout
     g = torch.Generator().manual_seed(0)
     # ---- prefill: batch x prompt
     prompts = torch.randint(0, cfg.vocab_size, (a.prefill_batch, a.prompt), generator=g).to(dev)
@@ -81,6 +85,7 @@ def main():
         print(json.dumps({"config": f"Llama-3-{a.model}-shape TP={world} inference, {a.layers} layers, bf16",
                           "prefill_tokens_per_s": round(a.prefill_batch * a.prompt / (float(t[0]) / 1e3), 1),
                           "prefill_ms": round(float(t[0]), 2),
+                          "decode_layout": a.decode_layout,
                           "decode_batch": a.decode_batch, "decode_ms_per_token_p50": round(float(t[1]), 3),
                           "decode_tokens_per_s": round(a.decode_batch / (float(t[1]) / 1e3), 1),
                           "new_tokens": a.new_tokens, "data": "synthetic", "timing": "CUDA events, max over ranks"}),

@@ -187,6 +187,116 @@ allgather_mc_kernel(const char* __restrict__ shard, char* __restrict__ mc_out, s
   }
 }
 
+// ---------------------------------------------------------------- one-shot all-reduce + residual + RMSNorm
+// Small row-parallel outputs (decode: [rows <= a few hundred, H]): every rank holds a partial sum of
+// the same [rows, H] bf16 matrix in its arena. One CTA per row: after the cross-rank rendezvous ("my
+// partial is complete") each thread loads 8 elements of the SUM (one multimem.ld_reduce through the
+// switch, or one load per peer), adds the residual stream, writes the new residual and, from the
+// row's sum of squares, the RMS-normalised row for the next projection. All-reduce, residual add and
+// norm are one launch, and every rank ends with the full result (no second phase). The partial buffers
+// alternate between two arena slices from call to call, so a rank that runs ahead writes its next
+// partial into the slice that no peer can still be reading; no closing rendezvous is needed.
+// The epoch lives in device memory and is advanced by the kernel: the launch can be replayed from a
+// CUDA graph.
+struct ArNormArgs {
+  const char* mc_partial;       // multicast address of the partial slice (null: plain peer loads)
+  PeerPtrs peer_partial;        // the slice on every rank
+  __nv_bfloat16* x;             // [rows, H] residual stream, updated in place (local, replicated)
+  const __nv_bfloat16* norm_w;  // [H] or null (no norm output)
+  __nv_bfloat16* h_out;         // [rows, H] normalised rows, or null
+  int rows, H;
+  float eps;
+  uint32_t* epoch_dev;          // device word: calls completed so far
+  uint32_t* block_counter;
+  int slot;
+};
+
+__global__ void __launch_bounds__(1024)
+allreduce_residual_norm_kernel(ArNormArgs a, SyncArgs s) {
+  __shared__ int ok_sh;
+  __shared__ float red[32];
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(a.epoch_dev) + 1u;
+  if (blockIdx.x == 0 && threadIdx.x < s.world) {
+    __threadfence_system();
+    st_release_sys(s.pad_peer[threadIdx.x] + a.slot + s.rank, epoch);
+  }
+  if (threadIdx.x == 0) ok_sh = 1;
+  __syncthreads();
+  if (threadIdx.x < s.world) {
+    if (!flag_wait_ge(s.pad_local + a.slot + threadIdx.x, epoch, true, s.status, s.wait_ns, 28)) ok_sh = 0;
+  }
+  __syncthreads();
+  if (ok_sh) {
+    const int row = blockIdx.x;
+    const int nvec = a.H / 8;
+    float ss = 0.f;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      const size_t off = ((size_t)row * a.H + (size_t)v * 8) * 2;
+      float f[8];
+      if (a.mc_partial) {
+        const uint4 u = mc_ld_reduce_bf16x8(a.mc_partial + off);
+        const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const float2 t = __bfloat1622float2(hb[j]); f[2 * j] = t.x; f[2 * j + 1] = t.y; }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = 0.f;
+        for (int r = 0; r < s.world; ++r) {
+          const uint4 u = ld_relaxed_sys_v4(a.peer_partial.p[r] + off);
+          const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { const float2 t = __bfloat1622float2(hb[j]); f[2 * j] += t.x; f[2 * j + 1] += t.y; }
+        }
+      }
+      uint4 xr = reinterpret_cast<const uint4*>(a.x + (size_t)row * a.H)[v];
+      __nv_bfloat162* xb = reinterpret_cast<__nv_bfloat162*>(&xr);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 t = __bfloat1622float2(xb[j]);
+        xb[j] = __floats2bfloat162_rn(t.x + f[2 * j], t.y + f[2 * j + 1]);
+        const float2 q = __bfloat1622float2(xb[j]);   // the norm sees the stored (rounded) residual
+        f[2 * j] = q.x; f[2 * j + 1] = q.y;
+        ss += q.x * q.x + q.y * q.y;
+      }
+      reinterpret_cast<uint4*>(a.x + (size_t)row * a.H)[v] = xr;
+    }
+    if (a.h_out) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+      __syncthreads();
+      float tot = 0.f;
+      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += red[w];
+      const float rstd = rsqrtf(tot / (float)a.H + a.eps);
+      for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+        const uint4 xr = reinterpret_cast<const uint4*>(a.x + (size_t)row * a.H)[v];
+        const uint4 wr = reinterpret_cast<const uint4*>(a.norm_w)[v];
+        const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&xr);
+        const __nv_bfloat162* wb = reinterpret_cast<const __nv_bfloat162*>(&wr);
+        uint4 o4;
+        __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 t = __bfloat1622float2(xb[j]), w2 = __bfloat1622float2(wb[j]);
+          // same arithmetic as the stand-alone norm: x * rstd * w in fp32, rounded once
+          ob[j] = __floats2bfloat162_rn(t.x * rstd * w2.x, t.y * rstd * w2.y);
+        }
+        reinterpret_cast<uint4*>(a.h_out + (size_t)row * a.H)[v] = o4;
+      }
+    }
+  }
+  // the last block advances the epoch for the next call
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned prev = atomicAdd(a.block_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *a.block_counter = 0;
+      *a.epoch_dev = epoch;
+    }
+  }
+}
+
 // ---------------------------------------------------------------- all-to-all(v) (pull)
 // Rank s keeps, in its arena, a send buffer and a table meta[d] = {byte offset in the send buffer,
 // byte count} of what it has for rank d. The receiver pulls its segment from every source into `out`,
@@ -582,6 +692,30 @@ extern "C" int tpb_symm_allgather_mc(const void* shard, size_t shard_bytes, size
   allgather_mc_kernel<<<ctas > 0 ? ctas : 32, 512, 0, (cudaStream_t)stream>>>(
       static_cast<const char*>(shard), g_symm.mc_base + out_off + (size_t)g_symm.rank * shard_bytes, shard_bytes, s,
       ready_slot, done_slot, block_counter);
+  return (int)cudaGetLastError();
+}
+
+// x[rows, H] += sum over ranks of the partial at arena offset partial_off; h_out = rmsnorm(x) * norm_w
+// (norm_w / h_out may be null). One CTA per row. epoch_dev: device word owned by the caller (starts at 0,
+// advanced here); slot: `world` flag slots; block_counter: zeroed device word. Consecutive calls must
+// alternate between two partial slices (see the kernel's comment).
+extern "C" int tpb_symm_allreduce_residual_norm(size_t partial_off, void* x, const void* norm_w, void* h_out,
+                                                int rows, int H, float eps, size_t pad_off, int slot,
+                                                uint32_t* epoch_dev, uint32_t* block_counter, double wait_s,
+                                                uint32_t* status, void* stream) {
+  if (!g_symm.opened && g_symm.world > 1) return -4;
+  if (rows <= 0) return 0;
+  if (H % 8 || partial_off % 16 || (h_out && !norm_w)) return -2;
+  ArNormArgs a;
+  memset(&a, 0, sizeof(a));
+  a.mc_partial = use_mc() ? g_symm.mc_base + partial_off : nullptr;
+  a.peer_partial = peers_at(partial_off);
+  a.x = (__nv_bfloat16*)x; a.norm_w = (const __nv_bfloat16*)norm_w; a.h_out = (__nv_bfloat16*)h_out;
+  a.rows = rows; a.H = H; a.eps = eps; a.epoch_dev = epoch_dev; a.block_counter = block_counter; a.slot = slot;
+  SyncArgs s = make_sync(pad_off, 0, status, wait_s);
+  int threads = H / 8;
+  threads = threads > 1024 ? 1024 : (threads < 32 ? 32 : (threads + 31) / 32 * 32);
+  allreduce_residual_norm_kernel<<<rows, threads, 0, (cudaStream_t)stream>>>(a, s);
   return (int)cudaGetLastError();
 }
 

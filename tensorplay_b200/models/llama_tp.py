@@ -112,6 +112,32 @@ class LlamaTPBlock(nn.Module):
         return x_local + tp.linear_reduce_scatter(a, self.w_down)
 
 
+    def decode_replicated(self, x: Tensor, h: Tensor, B: int, cos: Tensor, sin: Tensor, pos64: Tensor, pos32: Tensor,
+                          kv_len: Tensor, next_norm: Tensor) -> Tensor:
+        """One-token step on REPLICATED activations: ``x [B, H]`` is the residual stream (the same on every
+        rank, updated in place), ``h`` its normalised rows for this block's QKV projection. The column-parallel
+        projections need no communication, each of the two row-parallel ones ends in one launch that sums the
+        partials over the ranks (inside the switch), adds the residual and normalises for the next projection;
+        returns the normalised rows for the next block (``next_norm``: its attention-norm weight, or the final
+        norm's). Two rendezvous per layer instead of four, and none of them moves more than ``B x H`` values."""
+        cfg, tp = self.cfg, self.tp
+        D = cfg.head_dim
+        qkv = ops.gemm(h, self.wqkv).view(B, 1, self.hq + 2 * self.hkv, D)
+        qk = ops.apply_rope(qkv[:, :, : self.hq + self.hkv], cos, sin, pos64.view(B, 1))
+        q, k, v = qk[:, :, : self.hq], qk[:, :, self.hq:], qkv[:, :, self.hq + self.hkv:]
+        ops.kv_append(self.k_cache[:B].permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), pos32)
+        ops.kv_append(self.v_cache[:B].permute(0, 2, 1, 3), v.permute(0, 2, 1, 3), pos32)
+        G = self.hq // self.hkv
+        cap_blocks = (self.k_cache.shape[1] + 127) // 128
+        n_splits = max(1, min(8, cap_blocks // 4, (2 * 148) // max(1, B * self.hkv)))
+        o, _ = flash_fwd(q.reshape(B, self.hkv, G, D).transpose(1, 2), self.k_cache[:B], self.v_cache[:B],
+                         False, 1.0 / math.sqrt(D), kv_len=kv_len, n_splits=n_splits)
+        o = o.transpose(1, 2).reshape(B, self.hq * D)
+        h2 = tp.linear_allreduce_add_norm(o, self.wo, x, self.ffn_norm, cfg.rms_eps)
+        a = ops.swiglu_packed(ops.gemm(h2, self.w_gate_up))
+        return tp.linear_allreduce_add_norm(a, self.w_down, x, next_norm, cfg.rms_eps)
+
+
 class LlamaTP(nn.Module):
     def __init__(self, cfg: LlamaConfig, tp: TPContext, device=None, dtype=None):
         super().__init__()
@@ -223,7 +249,7 @@ class LlamaTP(nn.Module):
                                "pos32": torch.full((B,), pos, dtype=torch.int32, device=dev),
                                "kv_len": torch.full((1,), pos + 1, dtype=torch.int32, device=dev)}
             out = self._decode_body(g)
-            nxt = self.greedy_next(self.last_token_hidden(out, B, 1))
+            nxt = self.greedy_next(out if g.get("replicated") else self.last_token_hidden(out, B, 1))
             torch.cuda.synchronize(dev)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
@@ -237,12 +263,30 @@ class LlamaTP(nn.Module):
         g["tok"].copy_(last_tokens.view(B, 1))
         g["graph"].replay()
         g["pos"] = pos + 1  # the graph advanced the device-side positions itself
-        return self.greedy_next(self.last_token_hidden(g["out"], B, 1))
+        return self.greedy_next(g["out"] if g.get("replicated") else self.last_token_hidden(g["out"], B, 1))
+
+    # "replicated": activations of the decode step are the same on every rank and the row-parallel projections
+    # end in a one-launch all-reduce + residual + norm (2 rendezvous per layer); "sequence": the rows of the batch
+    # are sharded over the ranks and every projection is a fused all-gather -> GEMM or GEMM -> reduce-scatter
+    # (4 rendezvous per layer). Replicated is the default: at decode sizes a projection is bound by streaming its
+    # weights and the collectives by their latency.
+    decode_layout = "replicated"
 
     def _decode_body(self, g) -> Tensor:
         B = g["B"]
         cap = max(self.cfg.max_seq_len, self.layers[0].k_cache.shape[1])  # every cache position has a row
         cos, sin = self.rope_tables(cap, g["tok"].device)
+        if self.decode_layout == "replicated" and self.tp.world > 1 and self.tp.arena is not None:
+            x = self.embed.index_select(0, g["tok"].reshape(-1))      # [B, H] on every rank
+            h = ops.rms_norm(x, self.layers[0].attn_norm, self.cfg.rms_eps)
+            for i, l in enumerate(self.layers):
+                nxt = self.layers[i + 1].attn_norm if i + 1 < len(self.layers) else None
+                h = l.decode_replicated(x, h, B, cos, sin, g["pos64"], g["pos32"], g["kv_len"], nxt)
+            g["pos64"] += 1
+            g["pos32"] += 1
+            g["kv_len"] += 1
+            g["replicated"] = True   # x holds every sequence's hidden state on every rank
+            return x
         x = self._local_rows(g["tok"])
         for l in self.layers:
             x = l.decode(x, B, cos, sin, g["pos64"], g["pos32"], g["kv_len"])

@@ -32,6 +32,9 @@ _SIGS = {
     "tpb_ag_gemm_weight": [C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                            C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_size_t, C.c_int, C.c_int,
                            C.c_uint32, C.c_int, C.c_double, C.c_void_p, C.c_void_p, C.c_void_p],
+    "tpb_symm_allreduce_residual_norm": [C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_float,
+                                         C.c_size_t, C.c_int, C.c_void_p, C.c_void_p, C.c_double, C.c_void_p,
+                                         C.c_void_p],
     "tpb_gemm_rs": [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                     C.c_int, C.c_int, C.c_size_t, C.c_size_t, C.c_int, C.c_uint32, C.c_double,
                     C.c_void_p, C.c_void_p, C.c_void_p],
@@ -151,6 +154,47 @@ class WeightAGGemmPlan:
         return out
 
 
+class AllReduceNormPlan:
+    """Row-parallel outputs of a small batch (decode): every rank writes its partial ``[rows, H]`` product into
+    ``partial()`` (an arena slice, e.g. as the ``out=`` of the GEMM), then ``run(x, norm_w, eps)`` adds the sum over
+    ranks to the replicated residual stream ``x`` in place and returns ``rmsnorm(x) * norm_w`` for the next
+    projection: all-reduce, residual add and norm in one launch, the sum taken inside the switch where the arena
+    has a multicast mapping. The two partial slices alternate from call to call, which is what makes a closing
+    rendezvous unnecessary; the epoch lives on the device, so the call sequence can be replayed from a CUDA
+    graph. (The reference's row-parallel linear is an NCCL all-reduce after the GEMM,
+    tensorplay/distributed/tensor/parallel/style.py ``RowwiseParallel``.)"""
+
+    def __init__(self, arena: SymmArena, rows: int, hidden: int, wait_s: float = 30.0):
+        self.arena, self.rows, self.H, self.wait_s = arena, rows, hidden, wait_s
+        self.bufs = [arena.alloc(rows * hidden, torch.bfloat16).view(rows, hidden) for _ in range(2)]
+        self.slot = arena.slots(arena.world)
+        self.epoch_dev = torch.zeros(1, dtype=torch.int32, device=arena.device)
+        self.counter = torch.zeros(1, dtype=torch.int32, device=arena.device)
+        self.calls = 0
+        self.status = status_word(arena.device)
+
+    def partial(self) -> torch.Tensor:
+        """Where the partial of the next ``run`` goes."""
+        return self.bufs[self.calls & 1]
+
+    def run(self, x: torch.Tensor, norm_w: Optional[torch.Tensor] = None, eps: float = 1e-5,
+            h_out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        buf = self.bufs[self.calls & 1]
+        self.calls += 1
+        rows = x.shape[0]
+        assert rows <= self.rows and x.shape[1] == self.H and x.is_contiguous()
+        if norm_w is not None and h_out is None:
+            h_out = torch.empty_like(x)
+        raw = _raw(self.arena)
+        code = raw.tpb_symm_allreduce_residual_norm(
+            self.arena.offset_of(buf), x.data_ptr(), None if norm_w is None else norm_w.data_ptr(),
+            None if h_out is None else h_out.data_ptr(), rows, self.H, float(eps), self.arena.pad_off, self.slot,
+            self.epoch_dev.data_ptr(), self.counter.data_ptr(), self.wait_s, self.status.data_ptr(), stream_ptr())
+        _native.check(code, "tpb_symm_allreduce_residual_norm")
+        _native.launch_count += 1
+        return h_out
+
+
 class GemmRSPlan:
     """Buffers and counters for GEMM -> reduce-scatter(rows) with a fixed [M_total, N]."""
 
@@ -255,7 +299,28 @@ class TPContext:
         self.arena = None
         if self.cuda:
             self.arena = SymmArena._instance or SymmArena(arena_bytes, group=group)
-        self._ag, self._rs = {}, {}
+        self._ag, self._rs, self._ar = {}, {}, {}
+
+    def ar_plan(self, rows: int, hidden: int) -> "AllReduceNormPlan":
+        key = (rows, hidden)
+        if key not in self._ar:
+            self._ar[key] = AllReduceNormPlan(self.arena, rows, hidden)
+        return self._ar[key]
+
+    def linear_allreduce_add_norm(self, a: torch.Tensor, weight: torch.Tensor, x: torch.Tensor,
+                                  norm_w: Optional[torch.Tensor], eps: float) -> Optional[torch.Tensor]:
+        """Row-parallel linear of a replicated small batch: ``x += sum_ranks(a @ weight.T)`` in place (``x`` is the
+        replicated residual stream ``[rows, H]``) and returns ``rmsnorm(x) * norm_w`` (None without ``norm_w``).
+        The GEMM writes its partial straight into the arena slice that the one-launch all-reduce reads."""
+        if self.arena is not None and a.is_cuda and a.dtype == torch.bfloat16 and self.world > 1:
+            plan = self.ar_plan(x.shape[0], x.shape[1])
+            ops.gemm(a, weight, out=plan.partial()[: x.shape[0]])
+            return plan.run(x, norm_w, eps)
+        y = ops.linear(a, weight)
+        if self.world > 1:
+            dist.all_reduce(y, group=self.group)
+        x += y
+        return None if norm_w is None else ops.rms_norm(x, norm_w, eps)
 
     def ag_plan(self, m_total: int, k: int) -> AGGemmPlan:
         key = (m_total, k)

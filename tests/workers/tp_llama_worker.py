@@ -68,14 +68,22 @@ def main():
             res["msgs"].append(f"prefill logits rel {e}")
         agree = (nxt == ref_next).float().mean().item()
         # decode 4 tokens with the cache vs dense recompute
-        seq = torch.cat((toks, ref_next[:, None]), 1)
-        last = ref_next
-        for i in range(4):
-            nx = m.decode_step(last, T + i)
-            ref_nx = dense(seq).float()[:, -1].argmax(-1)
-            agree = min(agree, (nx == ref_nx).float().mean().item())
-            seq = torch.cat((seq, ref_nx[:, None]), 1)
-            last = ref_nx
+        # both decode layouts: replicated activations with the one-launch all-reduce + residual + norm (the default),
+        # and rows sharded over the ranks with the fused all-gather / reduce-scatter GEMMs
+        for layout in ("replicated", "sequence"):
+            m.decode_layout = layout
+            m._graph = None
+            seq = torch.cat((toks, ref_next[:, None]), 1)
+            last = ref_next
+            for i in range(4):   # the first step runs eagerly and is captured, the others replay the graph
+                nx = m.decode_step(last, T + i)
+                ref_nx = dense(seq).float()[:, -1].argmax(-1)
+                a = (nx == ref_nx).float().mean().item()
+                if a < 0.75:
+                    res["msgs"].append(f"{layout} decode step {i}: agreement {a}")
+                agree = min(agree, a)
+                seq = torch.cat((seq, ref_nx[:, None]), 1)
+                last = ref_nx
         res["agree"] = agree
         if agree < 0.75:
             res["ok"] = False
