@@ -187,12 +187,12 @@ def set_optimizer_state_dict(model: nn.Module, optimizers, optim_state_dict: Dic
                         src = v.local if isinstance(v, ShardedTensor) else v
                         if k in dst and isinstance(dst[k], torch.Tensor) and dst[k].shape == src.shape:
                             dst[k].copy_(src.to(dst[k].device))
-                        elif tuple(src.shape) == tuple(p.shape) or src.dim() == 0 or getattr(p, "_fsdp_info", None) is None:
+                        elif tuple(src.shape) == tuple(p.shape) or k == "step" or getattr(p, "_fsdp_info", None) is None:
                             dst[k] = src.detach().clone().to(p.device if src.dim() else src.device)
                         else:   # full tensor for a sharded parameter: keep this rank's rows
                             info, fst = p._fsdp_info, p._fsdp_state
                             rows = src.reshape((info.n0,) + info.rest)[fst.rank * info.chunk: fst.rank * info.chunk + info.local_rows]
-                            dst[k] = rows.detach().clone().to(p.device)
+                            dst[k] = rows.reshape(p.shape).detach().clone().to(p.device)
                     else:
                         dst[k] = v
 

@@ -21,13 +21,19 @@ from .api import (AllGather, BackwardPrefetch, Comm, CPUOffload, CPUOffloadPolic
                   FullyShardedDataParallel, MixedPrecision, MixedPrecisionPolicy, OffloadPolicy, ReduceScatter,
                   ShardingStrategy, UnshardHandle, fully_shard, register_fsdp_forward_method, share_comm_ctx)
 
-__all__ = ["fully_shard", "DataParallelMeshDims", "FSDPModule", "MixedPrecisionPolicy", "CPUOffloadPolicy", "OffloadPolicy",
+from .state_dict_api import (FullOptimStateDictConfig, FullStateDictConfig, LocalOptimStateDictConfig,
+                             LocalStateDictConfig, OptimStateDictConfig, ShardedGradScaler, ShardedOptimStateDictConfig,
+                             ShardedStateDictConfig, StateDictConfig, StateDictSettings, StateDictType)
+
+__all__ = ["StateDictType", "StateDictConfig", "FullStateDictConfig", "LocalStateDictConfig", "ShardedStateDictConfig",
+           "OptimStateDictConfig", "FullOptimStateDictConfig", "LocalOptimStateDictConfig", "ShardedOptimStateDictConfig",
+           "StateDictSettings", "ShardedGradScaler", "fully_shard", "DataParallelMeshDims", "FSDPModule", "MixedPrecisionPolicy", "CPUOffloadPolicy", "OffloadPolicy",
            "FullyShardedDataParallel", "ShardingStrategy", "MixedPrecision", "CPUOffload", "BackwardPrefetch",
            "Comm", "AllGather", "ReduceScatter", "UnshardHandle", "register_fsdp_forward_method", "share_comm_ctx"]
 
 
 def __getattr__(name):
-    """State-dict configuration classes, ``StateDictType``, ``FlatParameter``, ``UnshardHandle`` and ``register_fsdp_forward_method`` resolve to PyTorch's."""
+    """``FlatParameter`` and other names without a definition here resolve to PyTorch's."""
     import importlib
     for mod in ['torch.distributed.fsdp', 'torch.distributed.fsdp._flat_param']:
         try:

@@ -649,8 +649,11 @@ def _owned_by_inner(root: nn.Module, sub: nn.Module) -> bool:
     return False
 
 
+from .state_dict_api import StateDictMixin, StateDictSettings  # noqa: E402
+
+
 # ------------------------------------------------------------------------------------------ FSDP1 facade
-class FullyShardedDataParallel(nn.Module):
+class FullyShardedDataParallel(StateDictMixin, nn.Module):
     """FSDP1-style wrapper implemented on ``fully_shard`` (the reference does the same,
     tensorplay/distributed/fsdp/fully_sharded_data_parallel.py:367-376). State-dict keys carry no
     extra prefix: ``full_state_dict`` returns full (unsharded) tensors on every rank."""
@@ -661,6 +664,7 @@ class FullyShardedDataParallel(nn.Module):
                  forward_prefetch: bool = False, limit_all_gathers: bool = True, use_orig_params: bool = True,
                  ignored_states=None, device_mesh=None):
         super().__init__()
+        self._sd_settings = StateDictSettings()
         if not use_orig_params:
             raise NotImplementedError("use_orig_params=False (a FlatParameter per wrapper) is not implemented: the "
                                       "original parameters stay visible, sharded on dim 0")

@@ -205,3 +205,75 @@ def test_unimplemented_arguments_raise():
     dense(x).sum().backward()
     for (n, p), (_, q) in zip(m.named_parameters(), dense.named_parameters()):
         assert torch.allclose(p.grad.reshape(q.grad.shape), q.grad, atol=1e-6), n
+
+
+def _state_dict_types_worker(rank, world):
+    """Model and optimizer state in the FULL and SHARDED forms: a second model + optimizer loaded from either
+    continues training exactly like the first."""
+    from tensorplay_b200.distributed.fsdp import (FullOptimStateDictConfig, FullStateDictConfig, ShardedGradScaler,
+                                                  StateDictType)
+    from tensorplay_b200.distributed.fsdp import FullyShardedDataParallel as FSDP
+    wrap = dict(auto_wrap_policy=lambda mod, recurse, n: isinstance(mod, nn.Sequential))
+    f = FSDP(_net(3), **wrap)
+    opt = torch.optim.AdamW(f.parameters(), lr=1e-2)
+    torch.manual_seed(50 + rank)
+    for _ in range(2):
+        opt.zero_grad()
+        f(torch.randn(4, 12)).pow(2).mean().backward()
+        opt.step()
+    assert FSDP.get_state_dict_type(f).state_dict_type == StateDictType.FULL_STATE_DICT
+    full_sd = f.state_dict()
+    dense = _net(3)
+    assert set(full_sd) == set(dense.state_dict()) and full_sd["a.weight"].shape == dense.a.weight.shape
+    full_osd = FSDP.optim_state_dict(f, opt)
+    assert full_osd["state"]["a.weight"]["exp_avg"].shape == dense.a.weight.shape
+    with FSDP.state_dict_type(f, StateDictType.FULL_STATE_DICT, FullStateDictConfig(rank0_only=True, offload_to_cpu=True),
+                              FullOptimStateDictConfig(rank0_only=True)):
+        r0 = f.state_dict()
+        r0o = FSDP.optim_state_dict(f, opt)
+    assert (len(r0) > 0) == (rank == 0) and (len(r0o) > 0) == (rank == 0)
+    with FSDP.state_dict_type(f, StateDictType.SHARDED_STATE_DICT):
+        sh_sd = f.state_dict()
+        sh_osd = FSDP.optim_state_dict(f, opt)
+    assert FSDP.get_state_dict_type(f).state_dict_type == StateDictType.FULL_STATE_DICT   # restored
+    errs = []
+    for sd, osd in ((full_sd, full_osd), (sh_sd, sh_osd)):
+        g = FSDP(_net(4), **wrap)             # other initial weights
+        gopt = torch.optim.AdamW(g.parameters(), lr=1e-2)
+        g.load_state_dict(sd)
+        gopt.load_state_dict(FSDP.optim_state_dict_to_load(g, gopt, osd))
+        # one more identical step on both
+        torch.manual_seed(70 + rank)
+        x = torch.randn(4, 12)
+        for model, o in ((g, gopt),):
+            o.zero_grad()
+            model(x).pow(2).mean().backward()
+            o.step()
+        ref = FSDP(_net(4), **wrap)
+        ropt = torch.optim.AdamW(ref.parameters(), lr=1e-2)
+        ref.load_state_dict(full_sd)
+        ropt.load_state_dict(FSDP.optim_state_dict_to_load(ref, ropt, full_osd))
+        ropt.zero_grad()
+        ref(x).pow(2).mean().backward()
+        ropt.step()
+        a, b = g.state_dict(), ref.state_dict()
+        errs.append(max(float((a[k] - b[k]).abs().max()) for k in a))
+    # the sharded scaler: a non-finite gradient on ONE rank skips the step on every rank
+    scaler = ShardedGradScaler(device="cpu", init_scale=4.0)
+    before = {k: v.clone() for k, v in f.state_dict().items()}
+    opt.zero_grad()
+    loss = f(torch.randn(4, 12)).pow(2).mean()
+    scaler.scale(loss).backward()
+    if rank == 1:
+        next(p for p in f.parameters() if p.grad is not None and p.grad.numel() > 0).grad.view(-1)[0] = float("inf")
+    scaler.step(opt)
+    scaler.update()
+    after = f.state_dict()
+    skipped = all(torch.equal(before[k], after[k]) for k in before)
+    return errs, skipped, float(scaler.get_scale())
+
+
+def test_fsdp1_state_dict_types_optim_state_and_sharded_scaler():
+    for errs, skipped, scale in run_ranks(_state_dict_types_worker, 2):
+        assert errs[0] < 1e-6 and errs[1] < 1e-6, errs   # loaded from the full form, from the sharded form
+        assert skipped and scale == 2.0
