@@ -68,3 +68,79 @@ def powerSGD_hook(state, bucket):
         dist.all_reduce(tail, group=pg)
         tail.div_(w)
     return _done(t)
+
+
+# ---------------------------------------------------------------- quantisation and local-SGD hooks
+def _quantize_per_tensor(x: torch.Tensor):
+    lo, hi = x.min(), x.max()
+    scale = ((hi - lo) / 255.0).clamp_min(1e-12)
+    q = ((x - lo) / scale).round_().clamp_(0, 255).to(torch.uint8)
+    return q, scale.reshape(1), lo.reshape(1)
+
+
+def quantization_pertensor_hook(process_group, bucket):
+    """All-gather of the bucket quantised to 8 bits with one (scale, zero point) per rank, de-quantised and
+    averaged locally: a quarter of the bytes of an fp32 all-reduce on the wire
+    (tensorplay/distributed/algorithms/ddp_comm_hooks/quantization_hooks.py)."""
+    t = bucket.buffer()
+    pg = process_group if process_group is not None else dist.group.WORLD
+    w = dist.get_world_size(pg)
+    q, scale, lo = _quantize_per_tensor(t.float())
+    qs = [torch.empty_like(q) for _ in range(w)]
+    meta = torch.cat((scale, lo))
+    metas = [torch.empty_like(meta) for _ in range(w)]
+    dist.all_gather(qs, q, group=pg)
+    dist.all_gather(metas, meta, group=pg)
+    acc = torch.zeros_like(t, dtype=torch.float32)
+    for qi, mi in zip(qs, metas):
+        acc += qi.float() * mi[0] + mi[1]
+    return _done(t.copy_((acc / w).to(t.dtype)))
+
+
+def quantization_perchannel_hook(process_group, bucket, bucket_size: int = 512):
+    """Like the per-tensor hook with one (scale, zero point) per ``bucket_size`` consecutive elements."""
+    t = bucket.buffer()
+    pg = process_group if process_group is not None else dist.group.WORLD
+    w = dist.get_world_size(pg)
+    n = t.numel()
+    pad = (-n) % bucket_size
+    x = torch.nn.functional.pad(t.float(), (0, pad)).view(-1, bucket_size)
+    lo, hi = x.min(dim=1, keepdim=True).values, x.max(dim=1, keepdim=True).values
+    scale = ((hi - lo) / 255.0).clamp_min(1e-12)
+    q = ((x - lo) / scale).round_().clamp_(0, 255).to(torch.uint8)
+    meta = torch.cat((scale, lo), dim=1)
+    qs = [torch.empty_like(q) for _ in range(w)]
+    metas = [torch.empty_like(meta) for _ in range(w)]
+    dist.all_gather(qs, q, group=pg)
+    dist.all_gather(metas, meta, group=pg)
+    acc = torch.zeros_like(x)
+    for qi, mi in zip(qs, metas):
+        acc += qi.float() * mi[:, :1] + mi[:, 1:]
+    return _done(t.copy_((acc / w).view(-1)[:n].to(t.dtype)))
+
+
+class PostLocalSGDState:
+    """State of :func:`post_localSGD_hook`: gradients are all-reduced over ``process_group`` for the first
+    ``start_localSGD_iter`` iterations, afterwards only over ``subgroup`` (``None``: not at all), and the model
+    is averaged globally by a ``PeriodicModelAverager`` (post_localSGD_hook.py in the reference)."""
+
+    def __init__(self, process_group, subgroup, start_localSGD_iter: int, post_local_gradient_allreduce: bool = True):
+        self.process_group, self.subgroup = process_group, subgroup
+        self.start_localSGD_iter = start_localSGD_iter
+        self.post_local_gradient_allreduce = post_local_gradient_allreduce
+        self.iter = 0
+
+    def maybe_increase_iter(self, bucket) -> None:
+        if bucket.is_last():
+            self.iter += 1
+
+
+def post_localSGD_hook(state: PostLocalSGDState, bucket):
+    t = bucket.buffer()
+    if state.iter < state.start_localSGD_iter:
+        state.maybe_increase_iter(bucket)
+        return allreduce_hook(state.process_group, bucket)
+    state.maybe_increase_iter(bucket)
+    if not state.post_local_gradient_allreduce or state.subgroup is None:
+        return _done(t)
+    return allreduce_hook(state.subgroup, bucket)

@@ -18,6 +18,7 @@ Counterpart in the reference: tensorplay/distributed/elastic/rendezvous/dynamic_
 """
 from __future__ import annotations
 
+import itertools
 import json
 import os
 import socket
@@ -71,6 +72,7 @@ class DynamicRendezvousHandler:
         self._clock = clock
         self._stop = threading.Event()
         self._beat: Optional[threading.Thread] = None
+        self._write_seq = itertools.count(1)   # shared by the caller's thread and the heartbeat thread
 
     # ---- fenced state updates
     def _read(self) -> Tuple[dict, bytes]:
@@ -79,16 +81,23 @@ class DynamicRendezvousHandler:
 
     def _update(self, fn: Callable[[dict], Optional[dict]]) -> dict:
         """Apply ``fn`` to the shared record until the compare-and-set wins; ``fn`` returns the new
-        record, or None to leave it unchanged."""
+        record, or None to leave it unchanged. Every written record carries a tag that is unique to the
+        writer and the attempt: two writers that derive the same new record from the same old one would
+        otherwise both read their own bytes back from the compare-and-set and both count it as won."""
         for _ in range(10000):
             state, raw = self._read()
+            state.pop("_w", None)
+            base = json.dumps(state, sort_keys=True)
             self._evict_dead(state)
             new = fn(state)
             if new is None:
                 return state
-            blob = json.dumps(new, sort_keys=True).encode()
-            if blob == raw:
+            new.pop("_w", None)
+            if json.dumps(new, sort_keys=True) == base:
                 return new
+            tagged = dict(new)
+            tagged["_w"] = f"{self.node}#{id(self)}#{next(self._write_seq)}"
+            blob = json.dumps(tagged, sort_keys=True).encode()
             got = self.store.compare_set(self._key, raw, blob)
             if got == blob:
                 return new
