@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import torch
 import torch.distributed as dist
-from torch.distributed.algorithms import Join, Joinable, JoinHook  # noqa: F401
+from .join import Join, Joinable, JoinHook  # noqa: F401
 
 
 def _done(t):

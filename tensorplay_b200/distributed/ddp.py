@@ -25,6 +25,7 @@ import torch.distributed as dist
 from torch import nn
 
 from ..parallel.engine import AdamWConfig
+from .algorithms.join import Join, Joinable, JoinHook
 from .. import ops
 
 
@@ -50,13 +51,42 @@ class GradBucket:
     def is_last(self): return self._last
 
 
-class DistributedDataParallel(nn.Module):
+class _DDPJoinHook(JoinHook):
+    """A rank without inputs left answers one iteration of the others: the buffer broadcasts of their
+    forward and every bucket's reduction, in bucket order, with zero gradients (the average still divides
+    by the full world size). Afterwards the parameters of a rank that trained to the end are published."""
+
+    def __init__(self, ddp: "DistributedDataParallel"):
+        self.ddp = ddp
+
+    def main_hook(self) -> None:
+        d = self.ddp
+        if d.broadcast_buffers and d.world > 1:
+            for buf in d.module.buffers():
+                dist.broadcast(buf, src=0, group=d.process_group)
+        for b in d.buckets:
+            b.flat_grad.zero_()
+            d._reduce(b)
+        d.synchronize()
+
+    def post_hook(self, is_last_joiner: bool) -> None:
+        d = self.ddp
+        who = torch.tensor([d.rank if is_last_joiner else -1], device=d.device)
+        dist.all_reduce(who, op=dist.ReduceOp.MAX, group=d.process_group)
+        src = int(who.item())
+        src = dist.get_global_rank(d.process_group, src) if d.process_group is not None else src
+        for t in list(d.module.parameters()) + list(d.module.buffers()):
+            dist.broadcast(t.data, src=src, group=d.process_group)
+
+
+class DistributedDataParallel(nn.Module, Joinable):
     def __init__(self, module: nn.Module, device_ids=None, output_device=None, dim: int = 0,
                  broadcast_buffers: bool = True, process_group=None, bucket_cap_mb: float = 25.0,
                  find_unused_parameters: bool = False, gradient_as_bucket_view: bool = True,
                  static_graph: bool = False, comm: str = "auto",
                  fused_adamw: Optional[AdamWConfig] = None):
         super().__init__()
+        Joinable.__init__(self)
         self.module = module
         self.process_group = process_group
         self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
@@ -302,6 +332,8 @@ class DistributedDataParallel(nn.Module):
 
     # ---------------------------------------------------------------- module API
     def forward(self, *args, **kwargs):
+        if self.require_backward_grad_sync:
+            Join.notify_join_context(self)
         if self.cuda:
             for b in self.buckets:
                 if b.event is not None:
@@ -324,6 +356,27 @@ class DistributedDataParallel(nn.Module):
         """Order the current stream after all outstanding bucket reductions."""
         if self.cuda:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
+
+    # ---------------------------------------------------------------- uneven inputs
+    def join(self, divide_by_initial_world_size: bool = True, enable: bool = True,
+             throw_on_early_termination: bool = False):
+        """Context manager for training with a different number of batches per rank
+        (tensorplay/nn/parallel/distributed.py ``join``). Gradients are always averaged over the full
+        world size."""
+        if not divide_by_initial_world_size:
+            raise NotImplementedError("dividing by the number of ranks still training is not implemented")
+        return Join([self], enable, throw_on_early_termination)
+
+    def join_hook(self, **kwargs) -> JoinHook:
+        return _DDPJoinHook(self)
+
+    @property
+    def join_device(self) -> torch.device:
+        return self.device
+
+    @property
+    def join_process_group(self):
+        return self.process_group if self.process_group is not None else dist.group.WORLD
 
     @contextlib.contextmanager
     def no_sync(self):

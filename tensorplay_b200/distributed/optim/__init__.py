@@ -1,10 +1,10 @@
-"""Distributed optimizers: ``ZeroRedundancyOptimizer`` (ZeRO-1; torch's implementation). The
-sharded training engine and the fused DDP path of this package shard optimizer state natively."""
-from torch.distributed.optim import ZeroRedundancyOptimizer  # noqa: F401
+"""Distributed optimizers: ``ZeroRedundancyOptimizer`` (ZeRO stage 1, ``zero.py``). The sharded training
+engine and the fused DDP path of this package shard optimizer state natively as well."""
+from .zero import ZeroRedundancyOptimizer  # noqa: F401
 
 
 def __getattr__(name):
-    """Functional / post-local-SGD / RPC-based optimizers resolve to PyTorch's."""
+    """Functional / post-local-SGD / named optimizers resolve to PyTorch's."""
     import importlib
     for mod in ['torch.distributed.optim']:
         try:
