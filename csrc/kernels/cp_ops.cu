@@ -64,6 +64,7 @@ extern "C" int tpb_attn_merge(float* acc, float* lse_acc, const void* part, cons
                               int B, int T, int H, int D, long long p_tok, long long p_head,
                               long long p_batch, int lse_acc_stride, int lse_part_stride, int first,
                               void* stream) {
+  TPB_NVTX("tpb_attn_merge");
   if (B <= 0 || T <= 0 || H <= 0) return 0;
   if (D <= 0 || (D & 1) || ((p_tok | p_head | p_batch) & 1)) return -1;
   const long long warps = (long long)B * T * H;

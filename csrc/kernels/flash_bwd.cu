@@ -551,6 +551,7 @@ extern "C" int tpb_flash_bwd_ex(const void* dout, const void* q, const void* k, 
                                 long long dkv_head, long long dkv_batch, int lse_stride, int causal,
                                 float scale, uint32_t* status, void* stream_, int window, const int* seg_start,
                                 const int* seg_end) {
+  TPB_NVTX("tpb_flash_bwd_ex");
   cudaStream_t stream = (cudaStream_t)stream_;
   if (B <= 0 || Tq <= 0 || Hq <= 0) return 0;
   if ((seg_start || seg_end) && Tq != Tk) return -2;
@@ -620,6 +621,7 @@ extern "C" int tpb_flash_bwd(const void* dout, const void* q, const void* k, con
                              long long dq_head, long long dq_batch, long long dkv_tok,
                              long long dkv_head, long long dkv_batch, int lse_stride, int causal,
                              float scale, uint32_t* status, void* stream_) {
+  TPB_NVTX("tpb_flash_bwd");
   return tpb_flash_bwd_ex(dout, q, k, v, o, lse, delta, dq, dk, dv, B, Tq, Tk, Hq, Hkv, D, q_tok, q_head, q_batch,
                           k_tok, k_head, k_batch, v_tok, v_head, v_batch, o_tok, o_head, o_batch, do_tok, do_head,
                           do_batch, dq_tok, dq_head, dq_batch, dkv_tok, dkv_head, dkv_batch, lse_stride, causal, scale,

@@ -716,6 +716,7 @@ extern "C" int tpb_flash_fwd_ex(const void* q, const void* k, const void* v, voi
                                 float scale, uint32_t* status, void* stream, const int* kv_len, int n_splits,
                                 long long o_split_stride, long long lse_split_stride, int window,
                                 const int* seg_start, const int* seg_end) {
+  TPB_NVTX("tpb_flash_fwd_ex");
   if (B <= 0 || Tq <= 0 || Hq <= 0) return 0;
   if ((D != 64 && D != 128) || Hkv <= 0 || Hq % Hkv || Tk <= 0) return -2;
   if ((q_tok | q_head | q_batch | k_tok | k_head | k_batch | v_tok | v_head | v_batch | o_tok |
@@ -764,6 +765,7 @@ extern "C" int tpb_flash_fwd(const void* q, const void* k, const void* v, void* 
                              long long o_head, long long o_batch, int lse_stride, int causal,
                              float scale, uint32_t* status, void* stream, const int* kv_len, int n_splits,
                              long long o_split_stride, long long lse_split_stride) {
+  TPB_NVTX("tpb_flash_fwd");
   return tpb_flash_fwd_ex(q, k, v, o, lse, B, Tq, Tk, Hq, Hkv, D, q_tok, q_head, q_batch, k_tok, k_head, k_batch,
                           v_tok, v_head, v_batch, o_tok, o_head, o_batch, lse_stride, causal, scale, status, stream,
                           kv_len, n_splits, o_split_stride, lse_split_stride, 0, nullptr, nullptr);
@@ -783,6 +785,7 @@ extern "C" int tpb_attn_split_merge(const void* part, const float* lse_part, voi
                                     int n_splits, int B, int T, int H, int D, long long part_split_stride,
                                     long long lse_split_stride, int lse_stride, long long o_tok,
                                     long long o_head, long long o_batch, void* stream) {
+  TPB_NVTX("tpb_attn_split_merge");
   if (B <= 0 || T <= 0 || H <= 0 || n_splits <= 0) return 0;
   if (D & 1) return -1;
   const long long warps = (long long)B * T * H;

@@ -563,6 +563,7 @@ extern "C" int tpb_gemm_pair_resident() { return tpb::g_last_resident_pairs; }
 extern "C" int tpb_gemm_bf16_pair(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
                                   int lda, int ldb, int ldc, int a_mn, int b_mn, int out_f32, int bias_f32,
                                   int accumulate, float alpha, uint32_t* status, void* stream) {
+  TPB_NVTX("tpb_gemm_bf16_pair");
   return tpb::gemm_pair_dispatch(A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_f32, bias_f32, accumulate,
                                  alpha, 0, status, static_cast<cudaStream_t>(stream), tpb::g_pair_block_n);
 }

@@ -875,6 +875,10 @@ int gemm_bf16_dispatch(const void* A, const void* B, void* C, const void* bias, 
 static int g_pair_min_tiles = 74;
 extern "C" void tpb_gemm_set_pair_min_tiles(int tiles) { g_pair_min_tiles = tiles; }
 
+namespace tpb { int g_nvtx_on = 0; }
+extern "C" void tpb_nvtx_enable(int on) { tpb::g_nvtx_on = on; }
+extern "C" int tpb_nvtx_enabled() { return tpb::g_nvtx_on; }
+
 // 1 if this library was built with index checks (TPB_KERNEL_DEBUG), and the word they report to.
 extern "C" int tpb_debug_build() {
 #ifdef TPB_KERNEL_DEBUG
@@ -900,6 +904,7 @@ extern "C" int tpb_gemm_bf16_single(const void* A, const void* B, void* C, const
                                     int K, int lda, int ldb, int ldc, int a_mn, int b_mn, int out_f32,
                                     int bias_f32, int accumulate, float alpha, uint32_t* status,
                                     void* stream) {
+  TPB_NVTX("tpb_gemm_bf16_single");
   return tpb::gemm_bf16_dispatch(A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_f32,
                                  bias_f32, accumulate, alpha, nullptr, 0, 0, 0, status,
                                  static_cast<cudaStream_t>(stream), nullptr);
@@ -909,6 +914,7 @@ extern "C" int tpb_gemm_bf16(const void* A, const void* B, void* C, const void* 
                              int K, int lda, int ldb, int ldc, int a_mn, int b_mn, int out_f32,
                              int bias_f32, int accumulate, float alpha, uint32_t* status,
                              void* stream) {
+  TPB_NVTX("tpb_gemm_bf16");
   if (g_pair_min_tiles > 0 && (long long)((M + 255) / 256) * ((N + 255) / 256) >= g_pair_min_tiles)
     return tpb::gemm_pair_dispatch(A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_f32, bias_f32,
                                    accumulate, alpha, 0, status, static_cast<cudaStream_t>(stream));
@@ -928,6 +934,7 @@ extern "C" int tpb_ag_gemm(size_t a_off, const void* B, void* C, const void* bia
                            int rows_per_flag, size_t pad_off, int ready_slot, int done_slot,
                            uint32_t epoch, int n_copy, double wait_s, uint32_t* status,
                            void* stream, const uint32_t* epoch_dev) {
+  TPB_NVTX("tpb_ag_gemm");
   const tpb::SymmView* sv = tpb::symm_view();
   if (!sv || sv->world < 1 || M % sv->world) return -2;
   const int world = sv->world, rank = sv->rank;
@@ -967,6 +974,7 @@ extern "C" int tpb_ag_gemm_weight(const void* A, size_t w_off, void* C, const vo
                                   int lda, int ldc, int a_mn, int out_f32, uint32_t* flags, int rows_per_flag,
                                   size_t pad_off, int ready_slot, int done_slot, uint32_t epoch, int n_copy,
                                   double wait_s, uint32_t* status, void* stream, const uint32_t* epoch_dev) {
+  TPB_NVTX("tpb_ag_gemm_weight");
   const tpb::SymmView* sv = tpb::symm_view();
   if (!sv || sv->world < 1 || N % sv->world) return -2;
   const int world = sv->world, rank = sv->rank;
@@ -1003,6 +1011,7 @@ extern "C" int tpb_gemm_rs(const void* A, const void* B, void* out, int M, int N
                            int ldb, int a_mn, int b_mn, size_t stage_off, size_t pad_off,
                            int cnt_slot, uint32_t epoch, double wait_s, uint32_t* status,
                            void* stream, const uint32_t* epoch_dev) {
+  TPB_NVTX("tpb_gemm_rs");
   const tpb::SymmView* sv = tpb::symm_view();
   if (!sv || sv->world < 1 || M % sv->world || N % 8) return -2;
   const int world = sv->world, rank = sv->rank;

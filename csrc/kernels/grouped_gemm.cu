@@ -346,6 +346,7 @@ extern "C" int tpb_grouped_workspace_ints(int max_rows, int G) {
 extern "C" int tpb_grouped_gemm(const void* A, const void* B, void* C, const int* offs, int G,
                                 int max_rows, int N, int K, int mode, int b_mn, int out_f32,
                                 int accumulate, int* workspace, uint32_t* status, void* stream_) {
+  TPB_NVTX("tpb_grouped_gemm");
   cudaStream_t stream = (cudaStream_t)stream_;
   if (G <= 0 || max_rows <= 0) return 0;
   if (N % 8 || K % 8 || max_rows % kGBlockM) return -2;

@@ -362,6 +362,7 @@ extern "C" int tpb_moe_route(const int* topk_idx, int n_assign, int E, int* cons
                              int* recv_rows, size_t xbuf_off, int row_bytes, int cap_rows,
                              size_t pad_off, int ready_slot, uint32_t epoch, double wait_s,
                              uint32_t* status, void* stream) {
+  TPB_NVTX("tpb_moe_route");
   const SymmView* sv = symm_view();
   if (!sv || E > kMoeMaxExperts || E % sv->world) return -2;
   MoeSync s = make_moe_sync(sv, pad_off, epoch, status, wait_s);
@@ -387,6 +388,7 @@ extern "C" int tpb_moe_dispatch(const void* x, long long x_stride, int k, int n_
                                 size_t buf_off, int H, size_t pad_off, int done_slot,
                                 uint32_t epoch, uint32_t* block_counter, int ctas,
                                 uint32_t* status, void* stream) {
+  TPB_NVTX("tpb_moe_dispatch");
   const SymmView* sv = symm_view();
   if (!sv || H % 8) return -2;
   MoePeerBufs b;
@@ -405,6 +407,7 @@ extern "C" int tpb_moe_combine(size_t buf_off, const int* dst_rank, const int* d
                                long long out_stride, const void* g, long long g_stride, float* dots,
                                size_t pad_off, int ready_slot, uint32_t epoch, int ctas,
                                double wait_s, uint32_t* status, void* stream) {
+  TPB_NVTX("tpb_moe_combine");
   const SymmView* sv = symm_view();
   if (!sv || H % 8) return -2;
   MoePeerBufs b;
@@ -421,6 +424,7 @@ extern "C" int tpb_moe_combine(size_t buf_off, const int* dst_rank, const int* d
 }
 
 extern "C" int tpb_moe_signal(size_t pad_off, int slot, uint32_t epoch, void* stream) {
+  TPB_NVTX("tpb_moe_signal");
   const SymmView* sv = symm_view();
   if (!sv) return -2;
   MoeSync s = make_moe_sync(sv, pad_off, epoch, nullptr, 0);
@@ -431,6 +435,7 @@ extern "C" int tpb_moe_signal(size_t pad_off, int slot, uint32_t epoch, void* st
 // out [cap_rows, 8] bf16 <- per-row dot products of a and b ([cap_rows, H] bf16), rows limited by *rows_dev.
 extern "C" int tpb_moe_rowdot(const void* a, const void* b, void* out, const int* rows_dev, int cap_rows, int H,
                               void* stream) {
+  TPB_NVTX("tpb_moe_rowdot");
   if (H % 8 || cap_rows <= 0) return -2;
   int blocks = (cap_rows + 7) / 8;
   if (blocks > 148 * 8) blocks = 148 * 8;

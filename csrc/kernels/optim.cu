@@ -200,6 +200,7 @@ extern "C" int tpb_adamw_flat(float* master, float* m, float* v, const void* gra
                               float beta2, float eps, float wd, int step, float grad_scale,
                               int maximize, const float* clip_coef, const float* found_inf,
                               void* stream) {
+  TPB_NVTX("tpb_adamw_flat");
   if (n <= 0) return 0;
   if ((reinterpret_cast<uintptr_t>(master) | reinterpret_cast<uintptr_t>(m) |
        reinterpret_cast<uintptr_t>(v)) & 15)
@@ -242,6 +243,7 @@ extern "C" int tpb_adamw_multi(int count, void* const* master, void* const* m, v
                                float beta1, float beta2, float eps, float wd, int step,
                                float grad_scale, int maximize, const float* clip_coef,
                                const float* found_inf, void* stream) {
+  TPB_NVTX("tpb_adamw_multi");
   AdamHyper h = make_hyper(lr, beta1, beta2, eps, wd, step, grad_scale, maximize);
   cudaStream_t s = (cudaStream_t)stream;
   MtaArgs a;
@@ -279,6 +281,7 @@ extern "C" int tpb_adamw_multi(int count, void* const* master, void* const* m, v
 
 extern "C" int tpb_sumsq(const void* x, int is_bf16, long long n, float scale, float* out,
                          void* stream) {
+  TPB_NVTX("tpb_sumsq");
   if (n <= 0) return 0;
   long long blocks = (n + 256 * 8 - 1) / (256 * 8);
   long long cap = (long long)sm_count() * 8;
@@ -291,6 +294,7 @@ extern "C" int tpb_sumsq(const void* x, int is_bf16, long long n, float scale, f
 
 extern "C" int tpb_clip_coef(const float* sumsq, float max_norm, float* coef, float* norm_out,
                              void* stream) {
+  TPB_NVTX("tpb_clip_coef");
   clip_coef_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(sumsq, max_norm, coef, norm_out);
   return (int)cudaGetLastError();
 }

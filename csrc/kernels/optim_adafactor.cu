@@ -222,6 +222,7 @@ extern "C" int tpb_adafactor_step(float* p, const void* g, int grad_bf16, void* 
                                   float* var, float* scratch, long long R, long long C, float lr, float weight_decay,
                                   float eps1, float eps2, float d, float omb2, float rho, float grad_scale,
                                   const float* found_inf, void* stream) {
+  TPB_NVTX("tpb_adafactor_step");
   if (R <= 0 || C <= 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   AfArgs a;

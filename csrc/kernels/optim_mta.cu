@@ -176,6 +176,7 @@ extern "C" int tpb_optim_multi(int algo, int flags, int count, void* const* para
                                void* const* s2, void* const* s3, const void* const* grad, void* const* model,
                                const long long* numel, int grad_bf16, float lr, float weight_decay, float a,
                                float b, float eps, float grad_scale, const float* found_inf, void* stream) {
+  TPB_NVTX("tpb_optim_multi");
   if (algo < 0 || algo > 2) return -2;
   OptHyper h;
   h.algo = algo; h.flags = flags; h.lr = lr; h.weight_decay = weight_decay; h.a = a; h.b = b; h.eps = eps;
@@ -192,6 +193,7 @@ extern "C" int tpb_optim_multi(int algo, int flags, int count, void* const* para
 // (the caller zeroes it before the first call of a step).
 extern "C" int tpb_amp_unscale_multi(int count, void* const* grads, const long long* numel, int is_bf16,
                                      const float* inv_scale, float* found_inf, void* stream) {
+  TPB_NVTX("tpb_amp_unscale_multi");
   cudaStream_t s = (cudaStream_t)stream;
   return for_each_batch(count, grads, nullptr, nullptr, nullptr, nullptr, nullptr, numel,
                         [&](const OptArgs& args, int nb) {
@@ -203,6 +205,7 @@ extern "C" int tpb_amp_unscale_multi(int count, void* const* grads, const long l
 
 extern "C" int tpb_amp_update_scale(float* scale, int* growth_tracker, const float* found_inf, float growth_factor,
                                     float backoff_factor, int growth_interval, void* stream) {
+  TPB_NVTX("tpb_amp_update_scale");
   amp_update_scale_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(scale, growth_tracker, found_inf, growth_factor,
                                                               backoff_factor, growth_interval);
   return (int)cudaGetLastError();

@@ -689,6 +689,7 @@ using namespace tpb;
 extern "C" int tpb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* res_out,
                                float* rstd, int rows, int H, long long x_stride,
                                long long y_stride, float eps, void* stream) {
+  TPB_NVTX("tpb_rmsnorm_fwd");
   if (H % 8 || H > 256 * kMaxVec * 8) return -2;
   if (rows <= 0) return 0;
   int tpr = pick_tpr(H);
@@ -716,6 +717,7 @@ extern "C" int tpb_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
                                void* dw_bf16, int dw_accumulate, int rows, int H,
                                long long x_stride, long long dy_stride, long long dx_stride,
                                void* stream) {
+  TPB_NVTX("tpb_rmsnorm_bwd");
   if (H % 8 || H > 256 * kMaxVec * 8) return -2;
   if (rows <= 0) return 0;
   int tpr = pick_tpr(H);
@@ -731,6 +733,7 @@ extern "C" int tpb_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
 
 extern "C" int tpb_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean,
                                  float* rstd, int rows, int H, float eps, void* stream) {
+  TPB_NVTX("tpb_layernorm_fwd");
   if (H % 8 || H > 256 * kMaxVec * 8) return -2;
   if (rows <= 0) return 0;
   int tpr = pick_tpr(H);
@@ -746,6 +749,7 @@ extern "C" int tpb_layernorm_bwd(const void* dy, const void* x, const void* w, c
                                  const float* rstd, void* dx, float* dw_part, float* db_part,
                                  float* dw_f32, void* dw_bf16, float* db_f32, void* db_bf16,
                                  int accumulate, int rows, int H, void* stream) {
+  TPB_NVTX("tpb_layernorm_bwd");
   if (H % 8 || H > 256 * kMaxVec * 8) return -2;
   if (rows <= 0) return 0;
   int tpr = pick_tpr(H);
@@ -765,6 +769,7 @@ extern "C" int tpb_rope(void* x, const float* cos_t, const float* sin_t, const l
                         long long tokens, int heads, int D, long long tok_stride,
                         long long head_stride, int seq_len, int interleaved, int backward,
                         void* stream) {
+  TPB_NVTX("tpb_rope");
   if (D % 16 || tok_stride % 8 || head_stride % 8) return -2;
   long long total = tokens * heads * (D / 16);
   if (total <= 0) return 0;
@@ -780,6 +785,7 @@ extern "C" int tpb_rope(void* x, const float* cos_t, const float* sin_t, const l
 // data-dependent row).
 extern "C" int tpb_swiglu_fwd_n(const void* gate, const void* up, void* out, long long rows, int I,
                                 long long in_stride, const int* rows_dev, void* stream) {
+  TPB_NVTX("tpb_swiglu_fwd_n");
   if (I % 8 || in_stride % 8) return -2;
   long long total = rows * (I / 8);
   if (total <= 0) return 0;
@@ -790,11 +796,13 @@ extern "C" int tpb_swiglu_fwd_n(const void* gate, const void* up, void* out, lon
 }
 extern "C" int tpb_swiglu_fwd(const void* gate, const void* up, void* out, long long rows, int I,
                               long long in_stride, void* stream) {
+  TPB_NVTX("tpb_swiglu_fwd");
   return tpb_swiglu_fwd_n(gate, up, out, rows, I, in_stride, nullptr, stream);
 }
 extern "C" int tpb_swiglu_bwd_n(const void* dy, const void* gate, const void* up, void* dgate,
                                 void* dup, long long rows, int I, long long in_stride,
                                 long long out_stride, const int* rows_dev, void* stream) {
+  TPB_NVTX("tpb_swiglu_bwd_n");
   if (I % 8 || in_stride % 8 || out_stride % 8) return -2;
   long long total = rows * (I / 8);
   if (total <= 0) return 0;
@@ -806,9 +814,11 @@ extern "C" int tpb_swiglu_bwd_n(const void* dy, const void* gate, const void* up
 extern "C" int tpb_swiglu_bwd(const void* dy, const void* gate, const void* up, void* dgate,
                               void* dup, long long rows, int I, long long in_stride,
                               long long out_stride, void* stream) {
+  TPB_NVTX("tpb_swiglu_bwd");
   return tpb_swiglu_bwd_n(dy, gate, up, dgate, dup, rows, I, in_stride, out_stride, nullptr, stream);
 }
 extern "C" int tpb_gelu_fwd(const void* x, void* y, long long n, int approx, void* stream) {
+  TPB_NVTX("tpb_gelu_fwd");
   if (n % 8) return -2;
   if (n <= 0) return 0;
   gelu_fwd_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
@@ -817,6 +827,7 @@ extern "C" int tpb_gelu_fwd(const void* x, void* y, long long n, int approx, voi
 }
 extern "C" int tpb_gelu_bwd(const void* dy, const void* x, void* dx, long long n, int approx,
                             void* stream) {
+  TPB_NVTX("tpb_gelu_bwd");
   if (n % 8) return -2;
   if (n <= 0) return 0;
   gelu_bwd_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
@@ -827,6 +838,7 @@ extern "C" int tpb_gelu_bwd(const void* dy, const void* x, void* dx, long long n
 extern "C" int tpb_cross_entropy(const void* logits, const long long* target, float* loss,
                                  float* lse, void* dlogits, long long rows, int V, long long stride,
                                  long long ignore_index, float gscale, void* stream) {
+  TPB_NVTX("tpb_cross_entropy");
   if (stride % 8) return -2;
   if (rows <= 0) return 0;
   cross_entropy_kernel<<<(unsigned)rows, kCeThreads, 0, (cudaStream_t)stream>>>(
@@ -839,6 +851,7 @@ extern "C" int tpb_cross_entropy_bwd(const void* logits, const long long* target
                                      void* dlogits, const float* g_scalar, const float* scale,
                                      const float* g_rows, long long rows, int V, long long stride,
                                      long long ignore_index, void* stream) {
+  TPB_NVTX("tpb_cross_entropy_bwd");
   if (stride % 8) return -2;
   if (rows <= 0) return 0;
   int chunks = (V / 8 + 256 * 4 - 1) / (256 * 4);
@@ -878,6 +891,7 @@ extern "C" int tpb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void
                                        void* dw_bf16, int dw_accumulate, int rows, int H,
                                        long long x_stride, long long dy_stride, long long dx_stride,
                                        void* stream) {
+  TPB_NVTX("tpb_rmsnorm_bwd_noalloc");
   if (H <= 0 || H % 8 || x_stride % 8 || dy_stride % 8 || dx_stride % 8) return TPB_NOALLOC_BAD_ARGS;
   if (H > TPB_NOALLOC_RMSNORM_MAX_H) return TPB_NOALLOC_TOO_LARGE;
   if (rows <= 0) return 0;

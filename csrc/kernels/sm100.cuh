@@ -10,8 +10,22 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <nvtx3/nvToolsExt.h>
 
 namespace tpb {
+
+// NVTX ranges around the host side of every launching entry point, off unless tpb_nvtx_enable(1)
+// was called (the profiler module does it inside `profiler.nvtx_kernels()`): a timeline then shows
+// which library call queued which kernels. One global switch for all translation units.
+extern int g_nvtx_on;
+struct NvtxScope {
+  bool on;
+  explicit NvtxScope(const char* name) : on(g_nvtx_on != 0) { if (on) nvtxRangePushA(name); }
+  ~NvtxScope() { if (on) nvtxRangePop(); }
+  NvtxScope(const NvtxScope&) = delete;
+  NvtxScope& operator=(const NvtxScope&) = delete;
+};
+#define TPB_NVTX(name) ::tpb::NvtxScope tpb_nvtx_scope_(name)
 
 // Status codes written to the global status word (0 = ok).
 enum : uint32_t {

@@ -669,6 +669,7 @@ static PeerPtrs peers_at(size_t off) {
 extern "C" int tpb_symm_allgather(size_t shard_off, size_t shard_bytes, void* out, size_t pad_off,
                                   int slot_base, uint32_t epoch, int ctas, double wait_s,
                                   uint32_t* status, void* stream) {
+  TPB_NVTX("tpb_symm_allgather");
   if (!g_symm.opened && g_symm.world > 1) return -4;
   if (shard_bytes % 16 || (reinterpret_cast<uintptr_t>(out) & 15)) return -2;
   int per_rank = ctas > 0 ? ctas : 8;
@@ -686,6 +687,7 @@ extern "C" int tpb_symm_allgather(size_t shard_off, size_t shard_bytes, void* ou
 extern "C" int tpb_symm_allgather_mc(const void* shard, size_t shard_bytes, size_t out_off, size_t pad_off,
                                      int ready_slot, int done_slot, uint32_t epoch, uint32_t* block_counter,
                                      int ctas, double wait_s, uint32_t* status, void* stream) {
+  TPB_NVTX("tpb_symm_allgather_mc");
   if (!g_symm.mc_base || g_symm.world < 2) return -4;
   if (shard_bytes % 16 || (reinterpret_cast<uintptr_t>(shard) & 15) || out_off % 16) return -2;
   SyncArgs s = make_sync(pad_off, epoch, status, wait_s);
@@ -703,6 +705,7 @@ extern "C" int tpb_symm_allreduce_residual_norm(size_t partial_off, void* x, con
                                                 int rows, int H, float eps, size_t pad_off, int slot,
                                                 uint32_t* epoch_dev, uint32_t* block_counter, double wait_s,
                                                 uint32_t* status, void* stream) {
+  TPB_NVTX("tpb_symm_allreduce_residual_norm");
   if (!g_symm.opened && g_symm.world > 1) return -4;
   if (rows <= 0) return 0;
   if (H % 8 || partial_off % 16 || (h_out && !norm_w)) return -2;
@@ -728,6 +731,7 @@ extern "C" int tpb_symm_all_to_all(size_t send_off, size_t meta_off, void* out, 
                                    long long* out_bytes, size_t pad_off, int ready_slot, int done_slot,
                                    uint32_t epoch, uint32_t* block_counter, int ctas, double wait_s,
                                    uint32_t* status, void* stream) {
+  TPB_NVTX("tpb_symm_all_to_all");
   if (!g_symm.opened && g_symm.world > 1) return -4;
   if ((reinterpret_cast<uintptr_t>(out) & 15) || send_off % 16 || meta_off % 8) return -2;
   SyncArgs s = make_sync(pad_off, epoch, status, wait_s);
@@ -756,6 +760,7 @@ extern "C" int tpb_symm_rs_adamw(size_t grad_off, size_t lo, size_t n, float* ma
                                  const float* clip_coef, size_t pad_off, int ready_slot,
                                  int done_slot, uint32_t epoch, uint32_t* block_counter, int ctas,
                                  double wait_s, uint32_t* status, void* stream) {
+  TPB_NVTX("tpb_symm_rs_adamw");
   if (!g_symm.opened && g_symm.world > 1) return -4;
   if (n % 8 || lo % 8) return -2;
   AdamArgs h;
@@ -776,6 +781,7 @@ extern "C" int tpb_symm_rs_adamw(size_t grad_off, size_t lo, size_t n, float* ma
 
 extern "C" int tpb_symm_wait_slots(size_t pad_off, int slot_base, uint32_t epoch, double wait_s,
                                    uint32_t* status, void* stream) {
+  TPB_NVTX("tpb_symm_wait_slots");
   SyncArgs s = make_sync(pad_off, epoch, status, wait_s);
   wait_slots_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(s, slot_base, 23);
   return (int)cudaGetLastError();
@@ -784,18 +790,21 @@ extern "C" int tpb_symm_wait_slots(size_t pad_off, int slot_base, uint32_t epoch
 // Wait until all `world` slots reached the value stored at epoch_dev (device memory).
 extern "C" int tpb_symm_wait_slots_dev(size_t pad_off, int slot_base, const uint32_t* epoch_dev, double wait_s,
                                        uint32_t* status, void* stream) {
+  TPB_NVTX("tpb_symm_wait_slots_dev");
   SyncArgs s = make_sync(pad_off, 0, status, wait_s);
   wait_slots_dev_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(s, slot_base, epoch_dev, 24);
   return (int)cudaGetLastError();
 }
 // *ctr += 1 in stream order (advances a device-side epoch after the launch that used it).
 extern "C" int tpb_symm_bump(uint32_t* ctr, void* stream) {
+  TPB_NVTX("tpb_symm_bump");
   bump_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(ctr);
   return (int)cudaGetLastError();
 }
 
 extern "C" int tpb_symm_barrier(size_t pad_off, int slot_base, uint32_t epoch, double wait_s,
                                 uint32_t* status, void* stream) {
+  TPB_NVTX("tpb_symm_barrier");
   SyncArgs s = make_sync(pad_off, epoch, status, wait_s);
   barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(s, slot_base);
   return (int)cudaGetLastError();
@@ -804,6 +813,7 @@ extern "C" int tpb_symm_barrier(size_t pad_off, int slot_base, uint32_t epoch, d
 // dst (local) <- [src_off, src_off + bytes) of rank src_rank's arena.
 extern "C" int tpb_symm_peer_copy(int src_rank, size_t src_off, void* dst, size_t bytes, int ctas,
                                   void* stream) {
+  TPB_NVTX("tpb_symm_peer_copy");
   if (bytes % 16) return -2;
   peer_copy_kernel<<<ctas > 0 ? ctas : 32, 512, 0, (cudaStream_t)stream>>>(
       g_symm.peer[src_rank] + src_off, static_cast<char*>(dst), bytes);
@@ -842,6 +852,7 @@ static int rs_threads() {
 extern "C" int tpb_symm_allgather_ce(size_t shard_off, size_t shard_bytes, void* out, size_t pad_off,
                                      int slot_base, uint32_t epoch, double wait_s, uint32_t* status,
                                      void* stream) {
+  TPB_NVTX("tpb_symm_allgather_ce");
   if (!g_symm.opened && g_symm.world > 1) return -4;
   cudaStream_t st = (cudaStream_t)stream;
   SyncArgs s = make_sync(pad_off, epoch, status, wait_s);
@@ -865,6 +876,7 @@ extern "C" int tpb_symm_rs_adamw_ce(size_t grad_off, size_t lo, size_t n, void* 
                                     int step, float grad_scale, const float* clip_coef, size_t pad_off,
                                     int ready_slot, int done_slot, uint32_t epoch, int ctas,
                                     double wait_s, uint32_t* status, void* stream) {
+  TPB_NVTX("tpb_symm_rs_adamw_ce");
   if (!g_symm.opened && g_symm.world > 1) return -4;
   if (n % 8 || lo % 8 || (mode != 0 && mode != 1)) return -2;
   cudaStream_t st = (cudaStream_t)stream;

@@ -28,6 +28,8 @@ _KERNEL_SIGS = {
     "tpb_gemm_bf16_pair": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P],
     "tpb_gemm_bf16_single": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P],
     "tpb_gemm_set_pair_min_tiles": [I],
+    "tpb_nvtx_enable": [I],
+    "tpb_nvtx_enabled": [],
     "tpb_debug_build": [],
     "tpb_debug_set_status": [P],
     "tpb_gemm_pair_resident": [],

@@ -29,6 +29,22 @@ class nvtx_range:
         return False
 
 
+class nvtx_kernels:
+    """While active, every launching entry point of the kernel library pushes an NVTX range named after
+    itself (``tpb_gemm_bf16``, ``tpb_flash_fwd_ex``, ...) around its host side, so a timeline attributes
+    each kernel to the library call that queued it. Off otherwise: one predictable branch per call."""
+
+    def __enter__(self):
+        lib = _native.kernels()
+        self._was = lib.tpb_nvtx_enabled()
+        lib.tpb_nvtx_enable(1)
+        return self
+
+    def __exit__(self, *exc):
+        _native.kernels().tpb_nvtx_enable(self._was)
+        return False
+
+
 def merge_distributed_traces(paths, out_path) -> str:
     """Merge the Chrome-trace files that the ranks of a job exported (``.json`` or ``.json.gz``) into
     one document: the events of rank ``r`` keep their order and get process ids offset by

@@ -307,3 +307,22 @@ def test_adamw_flat_and_multi():
         O.sumsq_(gg, ss)
     tot = sum((gg.double() ** 2).sum() for gg in gs)
     assert abs(ss.item() - tot.item()) / tot.item() < 1e-4
+
+
+def test_nvtx_ranges_inside_the_kernel_library():
+    """With ``profiler.nvtx_kernels()`` the launching entry points push an NVTX range each; results are the
+    same and the switch goes back to its previous state."""
+    from tensorplay_b200 import profiler
+    from tensorplay_b200.ops._common import lib
+    a = torch.randn(512, 256, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(384, 256, device=DEV, dtype=torch.bfloat16)
+    w = torch.ones(256, device=DEV, dtype=torch.bfloat16)
+    plain = O.gemm(a, b), O.rms_norm(a, w)
+    assert lib().tpb_nvtx_enabled() == 0
+    with profiler.nvtx_kernels():
+        assert lib().tpb_nvtx_enabled() == 1
+        ranged = O.gemm(a, b), O.rms_norm(a, w)
+    assert lib().tpb_nvtx_enabled() == 0
+    O.check_status()
+    for x, y in zip(plain, ranged):
+        assert torch.equal(x, y)
