@@ -25,6 +25,19 @@ constexpr int kGemmThreads = 192;  // warp0 TMA, warp1 MMA, warps 2..5 epilogue
 constexpr int kGroupM = 16;        // rasterisation: 16 M-tiles share a column sweep for L2 reuse
 
 // One unit of work of a CTA: a whole tile, or one K range of a tile of the split last wave.
+// Ways in which each of the `tail` tiles of the last, partially filled wave is split along K over
+// `nctas` CTAs (1 = not split). A split costs about five L2 round trips (partial store, fence, flag,
+// wait, partial loads), as much as some sixteen k-blocks of MMAs: below that saving it does not pay.
+// The host (grid size, tile width) and the kernel's schedule both call this.
+__host__ __device__ inline int tail_nsplit(int tail, int nctas, int k_blocks) {
+  int ns = nctas / tail;
+  if (ns > k_blocks / 4) ns = k_blocks / 4;
+  if (ns > 32) ns = 32;
+  if (ns < 2) return 1;
+  if (k_blocks - (k_blocks + ns - 1) / ns < 16) return 1;
+  return ns;
+}
+
 struct WorkItem {
   int tile, kb0, kb1, split, nsplit, tail_idx;
 };
@@ -45,6 +58,10 @@ struct GemmCfg {
 
 struct GemmParams {
   int M, N, K;
+  // Rows of A that one TMA box brings (128, or 64 when the whole product has at most 64 rows: the MMA
+  // still multiplies 128 rows, the upper 64 being whatever the stage held before - their results land in
+  // accumulator rows that no epilogue reads - but each SM fills 8 KB less shared memory per k-block).
+  int a_box_rows;
   int ldc;
   void* C;
   const void* bias;  // bf16 or fp32 [N], may be null
@@ -317,12 +334,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   // schedule: full waves of whole tiles, then the tail tiles split along K over the idle CTAs
   const int full_per_cta = n_tiles / nctas;
   const int tail = n_tiles - full_per_cta * nctas;
-  int nsplit = 1;
-  if (p.sk_ws && tail > 0) {
-    nsplit = min(nctas / tail, k_blocks / 4);
-    if (nsplit > 16) nsplit = 16;
-    if (nsplit < 1) nsplit = 1;
-  }
+  const int nsplit = (p.sk_ws && tail > 0) ? tail_nsplit(tail, nctas, k_blocks) : 1;
   const int n_units = tail * nsplit;
   const int n_items = full_per_cta + ((nsplit > 1 ? bid < n_units : bid < tail) ? 1 : 0);
   auto get_work = [&](int i) {
@@ -402,7 +414,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (!mbar_wait(&empty[s], ph ^ 1, wc, 1)) { ok = false; break; }
           uint8_t* sa = smem + s * Cfg::kStageBytes;
           uint8_t* sb = sa + Cfg::kABytes;
-          mbar_arrive_expect_tx(&full[s], Cfg::kStageBytes);
+          mbar_arrive_expect_tx(&full[s], A_MN ? Cfg::kStageBytes : p.a_box_rows * (kBlockK * 2) + Cfg::kBBytes);
           if (!A_MN) {
             tma_load_2d(sa, &tmA, &full[s], kb * kBlockK, tm * kBlockM);
           } else {
@@ -474,8 +486,129 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after_sync();
       const int row = tm * kBlockM + q * 32 + lane;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + as * BLOCK_N;
-      // split last wave: helpers park their fp32 partial tile in the workspace; the owner waits
-      // for them and folds them in below
+      // split last wave, plain epilogue: EVERY split parks its fp32 partial rows in the workspace, then
+      // each split sums a column slice of the tile over all partials and stores it: the reduction is
+      // spread over the nsplit CTAs instead of queued on one owner
+      if (w.nsplit > 1 && !p.rs_mode) {
+        const int valid_rows = min(kBlockM, p.M - tm * kBlockM);
+        float* tile_ws = p.sk_ws + (size_t)w.tail_idx * w.nsplit * (size_t)(kBlockM * BLOCK_N);
+        if (q * 32 < valid_rows) {  // warp-uniform: row blocks past M are never read
+          // layout [column / 4][row][4]: the 32 lanes of a warp (32 rows) write 512 contiguous bytes
+          float* dst = tile_ws + (size_t)w.split * (kBlockM * BLOCK_N) + (size_t)(q * 32 + lane) * 4;
+#pragma unroll 1
+          for (int c = 0; c < BLOCK_N; c += 32) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(t_row + c, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              __stcg(reinterpret_cast<float4*>(dst + (size_t)((c + i) >> 2) * (kBlockM * 4)),
+                     make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
+                                 __uint_as_float(r[i + 3])));
+          }
+        }
+        tc_fence_before_sync();
+        __threadfence();
+        __syncwarp();
+        bool got = true;
+        if (lane == 0) {
+          mbar_arrive(&tempty[as]);
+          red_release_gpu_add(p.sk_flags + w.tail_idx, 1u);
+          got = flag_wait_ge(p.sk_flags + w.tail_idx, 4u * w.nsplit, false, p.status, p.wait_ns, 14);
+        }
+        got = __all_sync(0xffffffffu, got);
+        if (!got) { *abort_w = 1; break; }
+        constexpr int kGroups = BLOCK_N / 4;
+        const int g0 = w.split * kGroups / w.nsplit, g1 = (w.split + 1) * kGroups / w.nsplit;
+        // Work unit of the reduction: one column group (4 columns) x one block of 32 rows, a row per
+        // lane, so that a warp reads 512 contiguous bytes of every partial. The partials sit in L2
+        // (written by other SMs) and every load is a full L2 round trip: eight splits of two units are
+        // in flight per lane before anything is added.
+        const int row_blocks = (valid_rows + 31) / 32;
+        const int units = (g1 - g0) * row_blocks;
+        const size_t part_stride = (size_t)(kBlockM * BLOCK_N);
+        const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        auto finish = [&](int u, float4 acc) {
+          const int g = g0 + u / row_blocks, r = (u % row_blocks) * 32 + lane;
+          if (r >= valid_rows) return;
+          float v[4] = {acc.x * p.alpha, acc.y * p.alpha, acc.z * p.alpha, acc.w * p.alpha};
+          const int col = tn * BLOCK_N + g * 4;
+          if (col >= p.N) return;
+          const size_t off = (size_t)(tm * kBlockM + r) * p.ldc + col;
+          const bool whole = col + 4 <= p.N;
+          if (p.bias) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              if (whole || col + i < p.N)
+                v[i] += p.bias_f32 ? reinterpret_cast<const float*>(p.bias)[col + i]
+                                   : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[col + i]);
+          }
+          if (p.out_f32) {
+            float* c = reinterpret_cast<float*>(p.C) + off;
+            if (whole && (reinterpret_cast<uintptr_t>(c) & 15) == 0) {
+              float4 o = make_float4(v[0], v[1], v[2], v[3]);
+              if (p.accumulate) {
+                const float4 old = *reinterpret_cast<const float4*>(c);
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              *reinterpret_cast<float4*>(c) = o;
+            } else {
+              for (int i = 0; i < 4 && col + i < p.N; ++i) c[i] = p.accumulate ? c[i] + v[i] : v[i];
+            }
+          } else {
+            __nv_bfloat16* c = reinterpret_cast<__nv_bfloat16*>(p.C) + off;
+            if (whole && (reinterpret_cast<uintptr_t>(c) & 7) == 0) {
+              if (p.accumulate) {
+                const uint2 old = *reinterpret_cast<const uint2*>(c);
+                const float2 f0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&old.x));
+                const float2 f1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&old.y));
+                v[0] += f0.x; v[1] += f0.y; v[2] += f1.x; v[3] += f1.y;
+              }
+              uint2 o;
+              *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(v[0], v[1]);
+              *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(v[2], v[3]);
+              *reinterpret_cast<uint2*>(c) = o;
+            } else {
+              for (int i = 0; i < 4 && col + i < p.N; ++i)
+                c[i] = __float2bfloat16(p.accumulate ? __bfloat162float(c[i]) + v[i] : v[i]);
+            }
+          }
+        };
+        for (int u = q; u < units; u += 8) {
+          const int u2 = u + 4;
+          const bool has2 = u2 < units;
+          const int r1 = (u % row_blocks) * 32 + lane, r2 = (u2 % row_blocks) * 32 + lane;
+          const bool ok1 = r1 < valid_rows, ok2 = has2 && r2 < valid_rows;
+          const float* s1 = tile_ws + (size_t)(g0 + u / row_blocks) * (kBlockM * 4) + (size_t)r1 * 4;
+          const float* s2 = tile_ws + (size_t)(g0 + (has2 ? u2 : u) / row_blocks) * (kBlockM * 4) + (size_t)r2 * 4;
+          float4 a1 = zero4, a2 = zero4;
+          for (int h0 = 0; h0 < w.nsplit; h0 += 8) {
+            float4 t1[8], t2[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const bool in = h0 + j < w.nsplit;
+              t1[j] = (in && ok1) ? __ldcg(reinterpret_cast<const float4*>(s1 + (size_t)(h0 + j) * part_stride)) : zero4;
+              t2[j] = (in && ok2) ? __ldcg(reinterpret_cast<const float4*>(s2 + (size_t)(h0 + j) * part_stride)) : zero4;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              a1.x += t1[j].x; a1.y += t1[j].y; a1.z += t1[j].z; a1.w += t1[j].w;
+              a2.x += t2[j].x; a2.y += t2[j].y; a2.z += t2[j].z; a2.w += t2[j].w;
+            }
+          }
+          finish(u, a1);
+          if (has2) finish(u2, a2);
+        }
+        __syncwarp();
+        if (lane == 0) {
+          // check-out: the last of the 4 * nsplit warps re-arms the flag (none can still be waiting)
+          const unsigned old = atomicAdd(p.sk_flags + w.tail_idx, 1u);
+          if (old == 8u * w.nsplit - 1u) p.sk_flags[w.tail_idx] = 0;
+        }
+        continue;
+      }
+      // split last wave with a fused reduce-scatter epilogue: helpers park their fp32 partial tile in the
+      // workspace; the owner waits for them and folds them in below
       float* sk_tile = nullptr;
       if (w.nsplit > 1) {
         sk_tile = p.sk_ws + ((size_t)w.tail_idx * (w.nsplit - 1)) * (size_t)(kBlockM * BLOCK_N);
@@ -790,7 +923,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
   int tiles = ((p.M + kBlockM - 1) / kBlockM) * ((p.N + BLOCK_N - 1) / BLOCK_N);
   int grid = tiles < max_ctas ? tiles : max_ctas;
   // few tiles and a deep reduction: launch every SM and let the tail split along K
-  if (p.sk_ws && tiles * 2 <= max_ctas && (p.K + kBlockK - 1) / kBlockK >= 8) grid = max_ctas;
+  if (p.sk_ws && tiles < max_ctas && tail_nsplit(tiles, max_ctas, (p.K + kBlockK - 1) / kBlockK) > 1) grid = max_ctas;
   grid += p.n_copy;
   if (grid <= 0) return 0;
   kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
@@ -799,10 +932,23 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
 
 // Tile width: 256 columns, except when that leaves more than half of the SMs without a tile
 // (small-M decode shapes): then 128-column tiles double the number of CTAs that stream weights.
-static int pick_block_n(int M, int N) {
+// With the split-K workspace registered both widths are costed after their tiles are split along K
+// (same rule as the kernel's schedule): what bounds a few-row product is the rate at which one SM
+// fills its shared memory (about 100 GB/s), so the cost is the kilobytes one CTA brings in - k-blocks
+// per split x (A box + B box) - plus the price of a split, in the same unit.
+static int pick_block_n(int M, int N, int K, bool splitk) {
   if (N <= 128) return 128;
-  const long long tiles256 = (long long)((M + kBlockM - 1) / kBlockM) * ((N + 255) / 256);
-  return tiles256 * 2 <= sm_count() ? 128 : 256;
+  const long long tm = (M + kBlockM - 1) / kBlockM;
+  const long long tiles256 = tm * ((N + 255) / 256);
+  if (tiles256 * 2 > sm_count()) return 256;
+  if (!splitk) return 128;
+  const int kb = (K + kBlockK - 1) / kBlockK;
+  const int a_kb = M <= 64 ? 8 : 16;
+  auto cost = [&](long long tiles, int b_kb) {
+    const int ns = tiles < sm_count() ? tail_nsplit((int)tiles, sm_count(), kb) : 1;
+    return (long long)((kb + ns - 1) / ns) * (a_kb + b_kb) + (ns > 1 ? 640 : 0);
+  };
+  return cost(tiles256, 32) <= cost(tm * ((N + 127) / 128), 16) ? 256 : 128;
 }
 
 int gemm_bf16_dispatch(const void* A, const void* B, void* C, const void* bias, int M, int N,
@@ -814,17 +960,18 @@ int gemm_bf16_dispatch(const void* A, const void* B, void* C, const void* bias, 
   if (K <= 0 || (lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) ||
       (reinterpret_cast<uintptr_t>(B) & 15))
     return -2;
-  const int block_n = pick_block_n(M, N);
+  const int block_n = pick_block_n(M, N, K, g_sk_ws != nullptr && fused == nullptr);
   CUtensorMap ta, tb;
   int r;
-  if (!a_mn) r = make_tmap_2d_bf16(&ta, A, K, M, lda, kBlockM);
+  const int a_box_rows = (!a_mn && M <= 64) ? 64 : kBlockM;
+  if (!a_mn) r = make_tmap_2d_bf16(&ta, A, K, M, lda, a_box_rows);
   else r = make_tmap_2d_bf16(&ta, A, M, K, lda, kBlockK);
   if (r) return r;
   if (!b_mn) r = make_tmap_2d_bf16(&tb, B, K, N, ldb, block_n);
   else r = make_tmap_2d_bf16(&tb, B, N, K, ldb, kBlockK);
   if (r) return r;
   GemmParams p;
-  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.C = C; p.bias = bias; p.bias_f32 = bias_f32;
+  p.M = M; p.N = N; p.K = K; p.a_box_rows = a_box_rows; p.ldc = ldc; p.C = C; p.bias = bias; p.bias_f32 = bias_f32;
   p.out_f32 = out_f32; p.accumulate = accumulate; p.alpha = alpha; p.status = status;
   p.wait_ns = kDefaultWaitNs;
   p.b_flags = b_flags; p.rows_per_flag = rows_per_flag > 0 ? rows_per_flag : 1;
@@ -996,7 +1143,7 @@ extern "C" int tpb_ag_gemm_weight(const void* A, size_t w_off, void* C, const vo
   }
   f.pad_local = reinterpret_cast<uint32_t*>(sv->peer[rank] + pad_off);
   f.ready_slot = ready_slot; f.done_slot = done_slot; f.epoch = epoch; f.epoch_dev = epoch_dev;
-  const int block_n = tpb::pick_block_n(M, N);
+  const int block_n = tpb::pick_block_n(M, N, K, false);
   const int tiles_n = (N + block_n - 1) / block_n;
   f.tile_n_shift = (rows_per_rank % block_n == 0) ? (int)(((long long)rank * rows_per_rank / block_n) % tiles_n) : 0;
   f.wait_ns = wait_s > 0 ? (unsigned long long)(wait_s * 1e9) : 0;
@@ -1024,7 +1171,7 @@ extern "C" int tpb_gemm_rs(const void* A, const void* B, void* out, int M, int N
     f.rs_stage[r] = sv->peer[r] + stage_off;
     f.rs_cnt[r] = reinterpret_cast<uint32_t*>(sv->peer[r] + pad_off) + cnt_slot;
   }
-  const int block_n = tpb::pick_block_n(M, N);
+  const int block_n = tpb::pick_block_n(M, N, K, false);
   // arrivals this rank expects from each source per call: one per (N tile, 32-row block that
   // overlaps this rank's rows)
   const int my0 = rank * f.rs_rows_per_rank, my1 = my0 + f.rs_rows_per_rank - 1;

@@ -388,12 +388,14 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
 }
 
 // ------------------------------------------------------------------ RoPE (in place capable)
-// x viewed as [tokens, heads, D] with explicit token/head strides (elements). cos/sin tables
-// are fp32 [max_pos, D/2]; pos[token] optional (else token % seq_len). sign = -1 for backward.
-__global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ cos_t,
+// x viewed as [tokens, heads, D] with explicit token/head strides (elements), y likewise with its
+// own strides (y == x rotates in place: each thread reads all it needs before it writes). cos/sin
+// tables are fp32 [max_pos, D/2]; pos[token] optional (else token % seq_len). sign = -1 for backward.
+__global__ void rope_kernel(const __nv_bfloat16* x, __nv_bfloat16* y, const float* __restrict__ cos_t,
                             const float* __restrict__ sin_t, const long long* __restrict__ pos,
                             long long tokens, int heads, int D, long long tok_stride,
-                            long long head_stride, int seq_len, int interleaved, float sign) {
+                            long long head_stride, long long y_tok_stride, long long y_head_stride,
+                            int seq_len, int interleaved, float sign) {
   const int half = D / 2;
   const int vec_per_head = half / 8;  // NeoX: 8 pairs per thread from both halves
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -404,12 +406,13 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restri
   int h = th % heads;
   long long tok = th / heads;
   long long p = pos ? pos[tok] : (tok % seq_len);
-  __nv_bfloat16* base = x + tok * tok_stride + (long long)h * head_stride;
+  const __nv_bfloat16* base = x + tok * tok_stride + (long long)h * head_stride;
+  __nv_bfloat16* obase = y + tok * y_tok_stride + (long long)h * y_head_stride;
   const float* c = cos_t + p * half;
   const float* s = sin_t + p * half;
   if (!interleaved) {
-    uint4 a = reinterpret_cast<uint4*>(base)[v];
-    uint4 b = reinterpret_cast<uint4*>(base + half)[v];
+    uint4 a = reinterpret_cast<const uint4*>(base)[v];
+    uint4 b = reinterpret_cast<const uint4*>(base + half)[v];
     float af[8], bf[8], oa[8], ob[8];
     unpack8(a, af);
     unpack8(b, bf);
@@ -419,13 +422,13 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restri
       oa[j] = af[j] * cc - bf[j] * sn;
       ob[j] = bf[j] * cc + af[j] * sn;
     }
-    reinterpret_cast<uint4*>(base)[v] = pack8(oa);
-    reinterpret_cast<uint4*>(base + half)[v] = pack8(ob);
+    reinterpret_cast<uint4*>(obase)[v] = pack8(oa);
+    reinterpret_cast<uint4*>(obase + half)[v] = pack8(ob);
   } else {
     // 16 consecutive elements = 8 (even, odd) pairs: two vectors per thread
 #pragma unroll
     for (int q = 0; q < 2; ++q) {
-      uint4 a = reinterpret_cast<uint4*>(base)[v * 2 + q];
+      uint4 a = reinterpret_cast<const uint4*>(base)[v * 2 + q];
       float f[8], o[8];
       unpack8(a, f);
 #pragma unroll
@@ -435,7 +438,7 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restri
         o[2 * j] = f[2 * j] * cc - f[2 * j + 1] * sn;
         o[2 * j + 1] = f[2 * j + 1] * cc + f[2 * j] * sn;
       }
-      reinterpret_cast<uint4*>(base)[v * 2 + q] = pack8(o);
+      reinterpret_cast<uint4*>(obase)[v * 2 + q] = pack8(o);
     }
   }
 }
@@ -765,19 +768,29 @@ extern "C" int tpb_layernorm_bwd(const void* dy, const void* x, const void* w, c
   return (int)cudaGetLastError();
 }
 
+extern "C" int tpb_rope_out(const void* x, void* y, const float* cos_t, const float* sin_t,
+                            const long long* pos, long long tokens, int heads, int D,
+                            long long tok_stride, long long head_stride, long long y_tok_stride,
+                            long long y_head_stride, int seq_len, int interleaved, int backward,
+                            void* stream) {
+  TPB_NVTX("tpb_rope_out");
+  if (D % 16 || tok_stride % 8 || head_stride % 8 || y_tok_stride % 8 || y_head_stride % 8) return -2;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) return -2;
+  long long total = tokens * heads * (D / 16);
+  if (total <= 0) return 0;
+  int grid = (int)((total + 255) / 256);
+  rope_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, (__nv_bfloat16*)y, cos_t, sin_t, pos, tokens, heads, D, tok_stride,
+      head_stride, y_tok_stride, y_head_stride, seq_len, interleaved, backward ? -1.f : 1.f);
+  return (int)cudaGetLastError();
+}
 extern "C" int tpb_rope(void* x, const float* cos_t, const float* sin_t, const long long* pos,
                         long long tokens, int heads, int D, long long tok_stride,
                         long long head_stride, int seq_len, int interleaved, int backward,
                         void* stream) {
   TPB_NVTX("tpb_rope");
-  if (D % 16 || tok_stride % 8 || head_stride % 8) return -2;
-  long long total = tokens * heads * (D / 16);
-  if (total <= 0) return 0;
-  int grid = (int)((total + 255) / 256);
-  rope_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)x, cos_t, sin_t, pos, tokens,
-                                                      heads, D, tok_stride, head_stride, seq_len,
-                                                      interleaved, backward ? -1.f : 1.f);
-  return (int)cudaGetLastError();
+  return tpb_rope_out(x, x, cos_t, sin_t, pos, tokens, heads, D, tok_stride, head_stride, tok_stride,
+                      head_stride, seq_len, interleaved, backward, stream);
 }
 
 // rows_dev (optional): device word with the number of rows actually in use (<= rows); rows beyond it

@@ -89,6 +89,10 @@ int tpb_layernorm_bwd(const void* dy, const void* x, const void* w, const float*
 int tpb_rope(void* x, const float* cos_t, const float* sin_t, const long long* pos,
              long long tokens, int heads, int D, long long tok_stride, long long head_stride,
              int seq_len, int interleaved, int backward, void* stream);
+int tpb_rope_out(const void* x, void* y, const float* cos_t, const float* sin_t, const long long* pos,
+                 long long tokens, int heads, int D, long long tok_stride, long long head_stride,
+                 long long y_tok_stride, long long y_head_stride, int seq_len, int interleaved,
+                 int backward, void* stream);
 int tpb_swiglu_fwd(const void* gate, const void* up, void* out, long long rows, int I,
                    long long in_stride, void* stream);
 int tpb_swiglu_bwd(const void* dy, const void* gate, const void* up, void* dgate, void* dup,

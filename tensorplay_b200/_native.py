@@ -42,6 +42,7 @@ _KERNEL_SIGS = {
     "tpb_layernorm_fwd": [P, P, P, P, P, P, I, I, F, P],
     "tpb_layernorm_bwd": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, P],
     "tpb_rope": [P, P, P, P, LL, I, I, LL, LL, I, I, I, P],
+    "tpb_rope_out": [P, P, P, P, P, LL, I, I, LL, LL, LL, LL, I, I, I, P],
     "tpb_swiglu_fwd": [P, P, P, LL, I, LL, P],
     "tpb_swiglu_bwd": [P, P, P, P, P, LL, I, LL, LL, P],
     "tpb_swiglu_fwd_n": [P, P, P, LL, I, LL, P, P],

@@ -181,7 +181,8 @@ def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: b
 class _QKVAttnFn(torch.autograd.Function):
     """RoPE + flash attention on a packed QKV projection ``[B, T, (Hq + 2 Hkv) * D]``.
 
-    Forward rotates q and k into a fresh ``[B, T, Hq + Hkv, D]`` buffer with one launch and
+    Forward rotates q and k out of the packed buffer into a fresh ``[B, T, Hq + Hkv, D]`` one with one launch
+    (no copy before the rotation) and
     attends with v read in place from the packed buffer. Backward has the flash kernels
     write dq, dk and dv straight into the slices of one packed gradient buffer and un-rotates
     its q/k part in place, so that no concatenation or copy is needed around the projection.
@@ -189,12 +190,12 @@ class _QKVAttnFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, qkv, cos, sin, pos, Hq, Hkv, D, causal, scale, interleaved):
-        from .rope import _rope_native_
+        from .rope import _rope_native_out
         B, T, _ = qkv.shape
         tot = Hq + 2 * Hkv
         packed = qkv.view(B, T, tot, D)
-        qk = packed[:, :, : Hq + Hkv].contiguous()
-        _rope_native_(qk, cos, sin, pos, interleaved, False)
+        qk = torch.empty((B, T, Hq + Hkv, D), device=qkv.device, dtype=qkv.dtype)
+        _rope_native_out(packed[:, :, : Hq + Hkv], qk, cos, sin, pos, interleaved, False)
         q, k, v = qk[:, :, :Hq], qk[:, :, Hq:], packed[:, :, Hq + Hkv:]
         kept = _ckpt.take()  # selective checkpointing: output and LSE of the first forward pass
         if kept is not None:

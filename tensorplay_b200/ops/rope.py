@@ -53,6 +53,20 @@ def _rope_native_(x, cos, sin, pos, interleaved, backward):
     return x
 
 
+def _rope_native_out(x, out, cos, sin, pos, interleaved, backward):
+    """Rotates ``x`` (any token/head strides) into ``out``: the gather from a strided source and the rotation
+    are one pass."""
+    B, T, H, D = x.shape
+    for t in (x, out):
+        if t.stride(3) != 1 or t.stride(0) != T * t.stride(1):
+            raise ValueError("rope: needs [B, T, H, D] with contiguous D and uniform token stride")
+    code = lib().tpb_rope_out(x.data_ptr(), out.data_ptr(), cos.data_ptr(), sin.data_ptr(), ptr(pos), B * T, H, D,
+                              x.stride(1), x.stride(2), out.stride(1), out.stride(2), T, int(interleaved),
+                              int(backward), stream_ptr())
+    _native.check(code, "tpb_rope_out")
+    return out
+
+
 class _RopeFn(torch.autograd.Function):
     """Rotates ``x`` in place (the input buffer is consumed) and marks it dirty."""
 
@@ -68,10 +82,37 @@ class _RopeFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         cos, sin, pos = ctx.saved_tensors
-        dy = dy.contiguous() if dy.stride(3) != 1 else dy
-        dy = dy.clone() if not dy.is_contiguous() else dy.clone()
-        _rope_native_(dy, cos, sin, pos if ctx.has_pos else None, ctx.interleaved, True)
-        return dy, None, None, None, None
+        return _rotate_into_new(dy, cos, sin, pos if ctx.has_pos else None, ctx.interleaved, True), None, None, None, None
+
+
+def _strided_ok(x) -> bool:
+    B, T = x.shape[:2]
+    return x.stride(3) == 1 and x.stride(0) == T * x.stride(1) and x.stride(1) % 8 == 0 and x.stride(2) % 8 == 0 \
+        and x.data_ptr() % 16 == 0
+
+
+def _rotate_into_new(x, cos, sin, pos, interleaved, backward):
+    """Rotation of ``x`` into a fresh contiguous tensor; a strided ``x`` is read where it lies."""
+    if not _strided_ok(x):
+        x = x.contiguous()
+    out = torch.empty(x.shape, device=x.device, dtype=x.dtype)
+    return _rope_native_out(x, out, cos, sin, pos, interleaved, backward)
+
+
+class _RopeOutFn(torch.autograd.Function):
+    """Out-of-place rotation: one pass over the input, whatever its strides."""
+
+    @staticmethod
+    def forward(ctx, x, cos, sin, pos, interleaved):
+        ctx.save_for_backward(cos, sin, pos if pos is not None else torch.empty(0))
+        ctx.has_pos = pos is not None
+        ctx.interleaved = interleaved
+        return _rotate_into_new(x, cos, sin, pos, interleaved, False)
+
+    @staticmethod
+    def backward(ctx, dy):
+        cos, sin, pos = ctx.saved_tensors
+        return _rotate_into_new(dy, cos, sin, pos if ctx.has_pos else None, ctx.interleaved, True), None, None, None, None
 
 
 def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
@@ -82,9 +123,12 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
         pos = None
         if position_ids is not None:
             pos = position_ids.reshape(-1).to(torch.int64).contiguous()
+        needs_grad = x.requires_grad or torch.is_grad_enabled() and x.grad_fn is not None
         if not inplace:
-            x = x.clone(memory_format=torch.preserve_format)
-        if x.requires_grad or torch.is_grad_enabled() and x.grad_fn is not None:
+            if needs_grad:
+                return _RopeOutFn.apply(x, cos, sin, pos, interleaved)
+            return _rotate_into_new(x, cos, sin, pos, interleaved, False)
+        if needs_grad:
             return _RopeFn.apply(x, cos, sin, pos, interleaved)
         return _rope_native_(x, cos, sin, pos, interleaved, False)
     return _rope_ref(x, cos, sin, position_ids, interleaved, 1.0)

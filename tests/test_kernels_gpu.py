@@ -141,6 +141,37 @@ def test_gemm_splitk_tail(M, N, K, a_mn, b_mn):
         enable_splitk(enable=False)
 
 
+@pytest.mark.parametrize("M,N,K", [(64, 1280, 8192), (64, 8192, 1024), (64, 7168, 8192), (100, 1000, 3584),
+                                   (8, 8192, 3584), (130, 520, 2048)])
+def test_gemm_few_rows_split_with_distributed_reduction(M, N, K):
+    """Decode-sized products: every tile is split along K, each split parks its partial rows and reduces a
+    column slice of the tile. Plain, biased, scaled and accumulating epilogues; flags re-arm between calls."""
+    from tensorplay_b200.ops.gemm import enable_splitk
+    torch.manual_seed(11)
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
+    bias = torch.randn(N, device=DEV, dtype=torch.float32)
+    ref = a.float() @ b.float().t()
+    enable_splitk()
+    try:
+        outs = [O.gemm(a, b, out_dtype=torch.float32, impl="single") for _ in range(12)]  # back to back
+        O.check_status()
+        for out32 in outs:
+            assert _rel(out32, ref) < 2e-5
+        out = O.gemm(a, b, impl="single")
+        assert _rel(out, ref) < 5e-3
+        acc = torch.ones(M, N, device=DEV, dtype=torch.float32)
+        O.gemm(a, b, out=acc, bias=bias, accumulate=True, alpha=0.5, impl="single")
+        O.check_status()
+        assert _rel(acc, 0.5 * ref + bias + 1.0) < 2e-5
+        accb = torch.ones(M, N, device=DEV, dtype=torch.bfloat16)
+        O.gemm(a, b, out=accb, bias=bias, accumulate=True, alpha=0.5, impl="single")
+        O.check_status()
+        assert _rel(accb, 0.5 * ref + bias + 1.0) < 5e-3
+    finally:
+        enable_splitk(enable=False)
+
+
 def test_linear_autograd():
     torch.manual_seed(3)
     x = torch.randn(4, 96, 256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
@@ -225,6 +256,34 @@ def test_rope(interleaved):
         yr.backward(g.float())
         assert _rel(y, yr) < 8e-3
         assert _rel(x.grad, xr.grad) < 8e-3
+
+
+def test_rope_from_a_strided_source_and_in_place():
+    """The q/k heads of a packed QKV projection are rotated straight out of the packed buffer; the in-place
+    form gives the same values."""
+    torch.manual_seed(8)
+    B, T, Hq, Hkv, D = 2, 33, 8, 2, 128
+    packed = torch.randn(B, T, Hq + 2 * Hkv, D, device=DEV, dtype=torch.bfloat16)
+    cos, sin = O.rope_tables(64, D, 500000.0, device=DEV)
+    from tensorplay_b200.ops.rope import _rope_ref
+    src = packed[:, :, : Hq + Hkv]
+    keep = packed.clone()
+    want = _rope_ref(src.float(), cos, sin, None, False, 1.0)
+    out = O.apply_rope(src, cos, sin)
+    assert out.is_contiguous() and torch.equal(packed, keep)          # the source is untouched
+    assert _rel(out, want) < 8e-3
+    inpl = src.contiguous()
+    O.apply_rope(inpl, cos, sin, inplace=True)
+    assert torch.equal(inpl, out)
+    # gradient through the strided source
+    pk = packed.clone().requires_grad_(True)
+    y = O.apply_rope(pk[:, :, : Hq + Hkv], cos, sin)
+    g = torch.randn_like(y)
+    y.backward(g)
+    pr = packed.float().requires_grad_(True)
+    _rope_ref(pr[:, :, : Hq + Hkv], cos, sin, None, False, 1.0).backward(g.float())
+    assert _rel(pk.grad, pr.grad) < 8e-3
+    O.check_status()
 
 
 def test_swiglu_gelu():
