@@ -1,8 +1,9 @@
 """Elastic training: the local agent that supervises and restarts workers lives in
 ``distributed.run`` (``tprun``); the dynamic rendezvous over this package's stores, the file-based
-watchdog timers and the agent's health-check server are implemented in the sub-packages here;
-events, metrics and the multiprocessing helpers are torch's (tensorplay/distributed/elastic/**)."""
-from torch.distributed.elastic import events, metrics, multiprocessing, utils  # noqa: F401
+watchdog timers, the agent's health-check server, structured events, metric streams, the process contexts
+with error files and log teeing, and the store helpers are implemented in the sub-packages here
+(tensorplay/distributed/elastic/**)."""
+from . import events, metrics, multiprocessing, utils  # noqa: F401
 
 from ..run import ChildFailedError, LaunchConfig, LocalElasticAgent, elastic_launch  # noqa: F401
 from . import agent, rendezvous, timer  # noqa: F401

@@ -25,11 +25,21 @@ from .store import TCPStore
 
 
 class ChildFailedError(RuntimeError):
-    def __init__(self, name: str, failures: Dict[int, int]):
-        self.name, self.failures = name, failures
+    """``failures`` maps rank to exit code; ``details`` (when the agent could read them) maps rank to the
+    ``ProcessFailure`` built from the rank's error file: the exception and traceback that a worker wrapped in
+    ``elastic.multiprocessing.errors.record`` wrote before it died."""
+
+    def __init__(self, name: str, failures: Dict[int, int], details: Optional[dict] = None):
+        self.name, self.failures, self.details = name, failures, details or {}
         first = min(failures)
-        super().__init__(f"{name} failed: rank {first} exited with code {failures[first]} "
-                         f"(all failures: {failures})")
+        msg = f"{name} failed: rank {first} exited with code {failures[first]} (all failures: {failures})"
+        d = self.details.get(first)
+        if d is not None and d.message:
+            msg += f"\nrank {first}: {d.message}"
+            tb = d.traceback()
+            if tb:
+                msg += "\n" + tb.rstrip()
+        super().__init__(msg)
 
 
 @dataclass
@@ -55,6 +65,7 @@ class LocalElasticAgent:
         self.restart_count = 0
         self.logs = []
         self._tees: List[threading.Thread] = []
+        self._error_dir: Optional[str] = None
 
     def _start_workers(self) -> None:
         n = self.cfg.nproc_per_node
@@ -71,7 +82,8 @@ class LocalElasticAgent:
                         "MASTER_ADDR": self.cfg.master_addr, "MASTER_PORT": str(port),
                         "TP_STORE_ADDR": self.cfg.master_addr, "TP_STORE_PORT": str(self.store.port),
                         "TP_RESTART_COUNT": str(self.restart_count),
-                        "TORCHELASTIC_RESTART_COUNT": str(self.restart_count)})
+                        "TORCHELASTIC_RESTART_COUNT": str(self.restart_count),
+                        "TORCHELASTIC_ERROR_FILE": self._error_file(r)})
             out = None
             if self.cfg.log_dir:
                 os.makedirs(self.cfg.log_dir, exist_ok=True)
@@ -86,6 +98,17 @@ class LocalElasticAgent:
                 t.start()
                 self._tees.append(t)
             self.procs.append(p)
+
+    def _error_file(self, rank: int) -> str:
+        if self._error_dir is None:
+            import tempfile
+            self._error_dir = self.cfg.log_dir or tempfile.mkdtemp(prefix="tprun_errors_")
+            os.makedirs(self._error_dir, exist_ok=True)
+        return os.path.join(self._error_dir, f"attempt{self.restart_count}_rank{rank}_error.json")
+
+    def _failure_details(self, failed: Dict[int, int]) -> dict:
+        from .elastic.multiprocessing import ProcessFailure
+        return {r: ProcessFailure(r, self.procs[r].pid, c, self._error_file(r)) for r, c in failed.items()}
 
     @staticmethod
     def _tee(pipe, log, rank: int) -> None:
@@ -152,7 +175,7 @@ class LocalElasticAgent:
                     return 0
                 self._stop_workers()
                 if self.restart_count >= self.cfg.max_restarts:
-                    raise ChildFailedError(" ".join(self.cmd[:3]), failed)
+                    raise ChildFailedError(" ".join(self.cmd[:3]), failed, self._failure_details(failed))
                 self.restart_count += 1
                 self.store.set(f"restart/{self.restart_count}", str(failed))
         finally:
