@@ -109,6 +109,16 @@ _LAUNCHES = {"tpb_rmsnorm_bwd": 2, "tpb_layernorm_bwd": 3, "tpb_flash_bwd": 3, "
              "tpb_grouped_workspace_ints": 0, "tpb_adamw_set_overlap": 0, "tpb_flash_fwd_config": 0, "tpb_gemm_set_splitk_workspace": 0, "tpb_grouped_gemm": 2}
 launch_count = 0
 
+# FLOP accounting of the native kernels: the op wrappers report every launch's floating-point work here, and an
+# active ``utils.flop_counter.FlopCounterMode`` (which otherwise only sees ATen operators) adds it to its tables.
+flop_sinks: list = []
+
+
+def add_flops(name: str, flops: int) -> None:
+    for sink in flop_sinks:
+        sink(name, int(flops))
+
+
 
 class _Counting:
     """Proxy over the ctypes library that counts kernel launches per entry point."""

@@ -91,6 +91,8 @@ def flash_fwd(q, k, v, causal: bool, scale: float, kv_len: Optional[torch.Tensor
         None if kv_len is None else kv_len.data_ptr(), n_splits, o_split, lse_split, int(window or 0),
         None if seg_start is None else seg_start.data_ptr(), None if seg_end is None else seg_end.data_ptr())
     _native.check(code, "tpb_flash_fwd")
+    if _native.flop_sinks:   # QK^T and PV over the unmasked part (a causal square is half full)
+        _native.add_flops("tpb.flash_attention_forward", 4 * B * Hq * Tq * Tk * D // (2 if causal and Tq == Tk else 1))
     if n_splits > 1:
         code = lib().tpb_attn_split_merge(part.data_ptr(), lse_part.data_ptr(), o.data_ptr(), lse.data_ptr(),
                                           n_splits, B, Tq, Hq, D, o_split, lse_split, lse_stride, o.stride(1),
@@ -125,6 +127,8 @@ def flash_bwd(do, q, k, v, o, lse, causal: bool, scale: float, dq=None, dk=None,
         status_word(q.device).data_ptr(), stream_ptr(), int(window or 0),
         None if seg_start is None else seg_start.data_ptr(), None if seg_end is None else seg_end.data_ptr())
     _native.check(code, "tpb_flash_bwd")
+    if _native.flop_sinks:   # five products: S and dP again, dV, dK, dQ
+        _native.add_flops("tpb.flash_attention_backward", 10 * B * Hq * Tq * Tk * D // (2 if causal and Tq == Tk else 1))
     return dq, dk, dv
 
 

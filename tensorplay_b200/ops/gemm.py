@@ -94,6 +94,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         int(out.dtype == torch.float32), int(bias is not None and bias.dtype == torch.float32),
         int(accumulate), float(alpha), st.data_ptr(), stream_ptr())
     _native.check(code, fn)
+    if _native.flop_sinks:
+        _native.add_flops("tpb.gemm", 2 * M * N * K)
     return out
 
 

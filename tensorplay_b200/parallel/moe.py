@@ -83,6 +83,10 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, offs: torch.Tensor, *, mode: 
                               int(b_mn), int(out.dtype == torch.float32), int(accumulate), workspace.data_ptr(),
                               status_word(a.device).data_ptr(), stream_ptr())
     _native.check(code, "tpb_grouped_gemm")
+    if _native.flop_sinks:
+        # the rows in use are a device-side quantity: count the rows of the buffer (an upper bound when the
+        # buffer is sized for the worst case)
+        _native.add_flops("tpb.grouped_gemm", 2 * rows * nn * kk)
     return out
 
 

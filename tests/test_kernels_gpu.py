@@ -385,3 +385,19 @@ def test_nvtx_ranges_inside_the_kernel_library():
     O.check_status()
     for x, y in zip(plain, ranged):
         assert torch.equal(x, y)
+
+
+def test_flop_counter_sees_native_kernels():
+    from tensorplay_b200.utils.flop_counter import FlopCounterMode
+    M, N, K = 256, 384, 128
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    B, T, H, D = 1, 256, 2, 128
+    q, k, v = (torch.randn(B, T, H, D, device=DEV, dtype=torch.bfloat16, requires_grad=True) for _ in range(3))
+    with FlopCounterMode(display=False) as fc:
+        O.linear(a, w).float().sum().backward()                 # forward + dgrad + wgrad
+        O.flash_attention(q, k, v, causal=True).float().sum().backward()
+    c = fc.get_flop_counts()["Global"]
+    assert c["tpb.gemm"] == 3 * 2 * M * N * K
+    assert c["tpb.flash_attention_forward"] == 4 * B * H * T * T * D // 2
+    assert c["tpb.flash_attention_backward"] == 10 * B * H * T * T * D // 2
