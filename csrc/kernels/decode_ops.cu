@@ -90,6 +90,78 @@ __global__ void __launch_bounds__(256) kv_append_kernel(const KvAppendParams p) 
   }
 }
 
+// ------------------------------------------------------------------ decode-step QKV preparation
+// One token per sequence: qkv [B, Hq + 2 Hkv, D] packed. Rotates the Hq query heads into q_out
+// [B, Hq, D], rotates the Hkv key heads straight into the key cache at row pos[b], and copies the
+// value heads into the value cache at the same row: rotation and both cache appends in one launch.
+// NeoX (half-split) rotation; cos/sin are fp32 [max_pos, D / 2]. A position outside the cache or the
+// tables is skipped (and reported by the debug build).
+struct DecodeQkvParams {
+  const __nv_bfloat16* qkv;
+  __nv_bfloat16* q_out;
+  __nv_bfloat16* k_cache;
+  __nv_bfloat16* v_cache;
+  const float* cos_t;
+  const float* sin_t;
+  const int* pos;
+  int B, Hq, Hkv, D, cap, max_pos;
+  long long qkv_b;             // batch stride of qkv (elements)
+  long long c_b, c_t, c_h;     // cache strides: batch, token, head
+};
+
+__device__ __forceinline__ void unpack8_bf16(const uint4& u, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x; f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8_bf16(const float (&f)[8]) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return u;
+}
+
+__global__ void __launch_bounds__(256) decode_qkv_prep_kernel(const DecodeQkvParams p) {
+  const int half = p.D / 2, vec = half / 8;          // a thread: 8 elements of each half of one head
+  const int heads = p.Hq + 2 * p.Hkv;
+  const long long total = (long long)p.B * heads * vec;
+  for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < total; i += (long long)gridDim.x * 256) {
+    const int c = (int)(i % vec);
+    long long r = i / vec;
+    const int h = (int)(r % heads);
+    const int b = (int)(r / heads);
+    const int at = p.pos[b];
+    if (!TPB_DBG_CHECK(at >= 0 && at < p.cap && at < p.max_pos, 44)) continue;
+    const __nv_bfloat16* src = p.qkv + b * p.qkv_b + (long long)h * p.D;
+    uint4 lo = reinterpret_cast<const uint4*>(src)[c];
+    uint4 hi = reinterpret_cast<const uint4*>(src + half)[c];
+    __nv_bfloat16* dst;
+    if (h < p.Hq) dst = p.q_out + ((long long)b * p.Hq + h) * p.D;
+    else if (h < p.Hq + p.Hkv) dst = p.k_cache + b * p.c_b + (long long)at * p.c_t + (long long)(h - p.Hq) * p.c_h;
+    else dst = p.v_cache + b * p.c_b + (long long)at * p.c_t + (long long)(h - p.Hq - p.Hkv) * p.c_h;
+    if (h < p.Hq + p.Hkv) {
+      float a[8], bb[8], oa[8], ob[8];
+      unpack8_bf16(lo, a);
+      unpack8_bf16(hi, bb);
+      const float* cs = p.cos_t + (long long)at * half + c * 8;
+      const float* sn = p.sin_t + (long long)at * half + c * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        oa[j] = a[j] * cs[j] - bb[j] * sn[j];
+        ob[j] = bb[j] * cs[j] + a[j] * sn[j];
+      }
+      lo = pack8_bf16(oa);
+      hi = pack8_bf16(ob);
+    }
+    reinterpret_cast<uint4*>(dst)[c] = lo;
+    reinterpret_cast<uint4*>(dst + half)[c] = hi;
+  }
+}
+
 // ------------------------------------------------------------------ sampling
 // One CTA per row. The support is found without sorting: a 32-step radix descent over the
 // order-preserving integer image of the logits gives the exact k-th largest value (top-k) and
@@ -308,6 +380,30 @@ int tpb_kv_append(const void* src, void* dst, const int* pos, const int* block_t
   const long long total = (long long)B * T * H * (D / 8);
   const int grid = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   kv_append_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return (int)cudaGetLastError();
+}
+
+// qkv [B, Hq + 2 Hkv, D] (batch stride qkv_b); q_out [B, Hq, D] contiguous; caches addressed as
+// base + b * c_b + t * c_t + h * c_h with `cap` token rows; pos int32 [B].
+int tpb_decode_qkv_prep(const void* qkv, void* q_out, void* k_cache, void* v_cache, const float* cos_t,
+                        const float* sin_t, const int* pos, int B, int Hq, int Hkv, int D, int cap,
+                        int max_pos, long long qkv_b, long long c_b, long long c_t, long long c_h,
+                        void* stream) {
+  TPB_NVTX("tpb_decode_qkv_prep");
+  if (B <= 0) return 0;
+  if (D <= 0 || (D & 15) || ((qkv_b | c_b | c_t | c_h) & 7) || !pos) return -2;
+  if ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_cache) |
+       reinterpret_cast<uintptr_t>(v_cache)) & 15)
+    return -2;
+  DecodeQkvParams p;
+  p.qkv = (const __nv_bfloat16*)qkv; p.q_out = (__nv_bfloat16*)q_out;
+  p.k_cache = (__nv_bfloat16*)k_cache; p.v_cache = (__nv_bfloat16*)v_cache;
+  p.cos_t = cos_t; p.sin_t = sin_t; p.pos = pos;
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.cap = cap; p.max_pos = max_pos;
+  p.qkv_b = qkv_b; p.c_b = c_b; p.c_t = c_t; p.c_h = c_h;
+  const long long total = (long long)B * (Hq + 2 * Hkv) * (D / 16);
+  const int grid = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+  decode_qkv_prep_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
   return (int)cudaGetLastError();
 }
 

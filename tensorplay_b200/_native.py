@@ -80,6 +80,7 @@ _KERNEL_SIGS = {
     "tpb_embedding_fwd": [P, P, P, LL, I, LL, P],
     "tpb_embedding_bwd": [P, P, P, LL, I, LL, I, P],
     "tpb_kv_append": [P, P, P, P, I, I, I, I, I, I, I, LL, LL, LL, LL, LL, LL, P],
+    "tpb_decode_qkv_prep": [P, P, P, P, P, P, P, I, I, I, I, I, I, LL, LL, LL, LL, P],
     "tpb_sample": [P, P, P, P, I, I, LL, I, F, I, F, P],
 }
 

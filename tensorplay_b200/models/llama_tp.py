@@ -122,17 +122,18 @@ class LlamaTPBlock(nn.Module):
         norm's). Two rendezvous per layer instead of four, and none of them moves more than ``B x H`` values."""
         cfg, tp = self.cfg, self.tp
         D = cfg.head_dim
-        qkv = ops.gemm(h, self.wqkv).view(B, 1, self.hq + 2 * self.hkv, D)
-        qk = ops.apply_rope(qkv[:, :, : self.hq + self.hkv], cos, sin, pos64.view(B, 1))
-        q, k, v = qk[:, :, : self.hq], qk[:, :, self.hq:], qkv[:, :, self.hq + self.hkv:]
-        ops.kv_append(self.k_cache[:B].permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), pos32)
-        ops.kv_append(self.v_cache[:B].permute(0, 2, 1, 3), v.permute(0, 2, 1, 3), pos32)
+        qkv = ops.gemm(h, self.wqkv).view(B, self.hq + 2 * self.hkv, D)
+        # rotation of q and k and both cache appends in one launch
+        q = ops.decode_qkv_prep(qkv, cos, sin, pos32, self.hq, self.hkv, self.k_cache[:B], self.v_cache[:B])
         G = self.hq // self.hkv
         cap_blocks = (self.k_cache.shape[1] + 127) // 128
         n_splits = max(1, min(8, cap_blocks // 4, (2 * 148) // max(1, B * self.hkv)))
-        o, _ = flash_fwd(q.reshape(B, self.hkv, G, D).transpose(1, 2), self.k_cache[:B], self.v_cache[:B],
-                         False, 1.0 / math.sqrt(D), kv_len=kv_len, n_splits=n_splits)
-        o = o.transpose(1, 2).reshape(B, self.hq * D)
+        # the kernel sees the G query heads of a KV head as G query rows; its output goes straight into the
+        # [B, Hq * D] layout of the output projection (head = kv_head * G + g)
+        o = torch.empty((B, self.hq * D), dtype=qkv.dtype, device=qkv.device)
+        flash_fwd(q.view(B, self.hkv, G, D).transpose(1, 2), self.k_cache[:B], self.v_cache[:B],
+                  False, 1.0 / math.sqrt(D), kv_len=kv_len, n_splits=n_splits,
+                  out=o.view(B, self.hkv, G, D).transpose(1, 2))
         h2 = tp.linear_allreduce_add_norm(o, self.wo, x, self.ffn_norm, cfg.rms_eps)
         a = ops.swiglu_packed(ops.gemm(h2, self.w_gate_up))
         return tp.linear_allreduce_add_norm(a, self.w_down, x, next_norm, cfg.rms_eps)

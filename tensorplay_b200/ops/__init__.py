@@ -3,7 +3,7 @@
 from ._common import DeviceWaitTimeout, check_status, status_word
 from .activation import gelu, swiglu, swiglu_packed
 from .attention import attention_reference, flash_attention, qkv_attention
-from .decode import embedding, kv_append, sample, sample_reference
+from .decode import decode_qkv_prep, embedding, kv_append, sample, sample_reference
 from .gemm import gemm, linear
 from .loss import cross_entropy
 from .norm import layer_norm, rms_norm

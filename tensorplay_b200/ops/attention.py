@@ -64,14 +64,23 @@ def attention_reference(q, k, v, causal: bool = True, scale: Optional[float] = N
 
 
 def flash_fwd(q, k, v, causal: bool, scale: float, kv_len: Optional[torch.Tensor] = None, n_splits: int = 1,
-              window: int = 0, seg_start: Optional[torch.Tensor] = None, seg_end: Optional[torch.Tensor] = None):
+              window: int = 0, seg_start: Optional[torch.Tensor] = None, seg_end: Optional[torch.Tensor] = None,
+              out: Optional[torch.Tensor] = None):
     """Forward kernel. ``kv_len`` (int32 device scalar) limits the keys to the first ``kv_len`` of
     ``k``/``v`` without a host-side shape change, so that a decode step over a preallocated cache
     can be captured in a CUDA graph. ``n_splits > 1`` (non-causal, i.e. decode) spreads the keys of
-    every (batch, head) over that many CTAs and merges the partial outputs by their LSE."""
+    every (batch, head) over that many CTAs and merges the partial outputs by their LSE. ``out``: a
+    ``[B, Tq, Hq, D]`` view (any batch / token / head strides, contiguous ``D``) that receives the output, e.g.
+    one laid out for the projection that follows."""
     B, Tq, Hq, D = q.shape
     Tk, Hkv = k.shape[1], k.shape[2]
-    o = torch.empty((B, Tq, Hq, D), dtype=q.dtype, device=q.device)
+    if out is not None:
+        if out.shape != (B, Tq, Hq, D) or out.stride(3) != 1 or out.dtype != q.dtype or \
+                any(s % 8 for s in out.stride()[:3]) or out.data_ptr() % 16:
+            raise ValueError("flash_fwd: out must be [B, Tq, Hq, D] with contiguous D and 16-byte aligned rows")
+        o = out
+    else:
+        o = torch.empty((B, Tq, Hq, D), dtype=q.dtype, device=q.device)
     # rows padded to the backward kernels' 64-query vector loads
     lse_stride = (Tq + 127) // 128 * 128
     lse = torch.empty((B, Hq, lse_stride), dtype=torch.float32, device=q.device)

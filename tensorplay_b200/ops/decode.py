@@ -105,6 +105,31 @@ def kv_append(cache: Tensor, new: Tensor, pos, block_table: Optional[Tensor] = N
     return cache
 
 
+def decode_qkv_prep(qkv: Tensor, cos: Tensor, sin: Tensor, pos: Tensor, num_heads: int, num_kv_heads: int,
+                    k_cache: Tensor, v_cache: Tensor) -> Tensor:
+    """One decode step's QKV projection ``[B, Hq + 2 Hkv, D]`` -> rotated queries ``[B, Hq, D]``; the rotated keys
+    and the values are written into the caches ``[B, S, Hkv, D]`` at row ``pos[b]`` (int32 ``[B]``, also the
+    rotary position). One launch for the rotation and both appends (NeoX half-split rotation)."""
+    B, heads, D = qkv.shape
+    Hq, Hkv = num_heads, num_kv_heads
+    assert heads == Hq + 2 * Hkv and k_cache.shape == v_cache.shape and k_cache.stride() == v_cache.stride()
+    if use_native(qkv, k_cache) and qkv.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and D % 16 == 0 \
+            and qkv.stride(2) == 1 and qkv.stride(1) == D and k_cache.stride(3) == 1 and pos.dtype == torch.int32:
+        q = torch.empty((B, Hq, D), dtype=qkv.dtype, device=qkv.device)
+        _native.check(lib().tpb_decode_qkv_prep(
+            ptr(qkv), ptr(q), ptr(k_cache), ptr(v_cache), ptr(cos), ptr(sin), ptr(pos), B, Hq, Hkv, D,
+            k_cache.shape[1], cos.shape[0], qkv.stride(0), k_cache.stride(0), k_cache.stride(1), k_cache.stride(2),
+            stream_ptr()), "tpb_decode_qkv_prep")
+        return q
+    from .rope import _rope_ref
+    pos64 = pos.to(torch.int64)
+    qk = _rope_ref(qkv[:, None, : Hq + Hkv], cos, sin, pos64.view(B, 1), False, 1.0)[:, 0]
+    idx = torch.arange(B, device=qkv.device)
+    k_cache[idx, pos64] = qk[:, Hq:].to(k_cache.dtype)
+    v_cache[idx, pos64] = qkv[:, Hq + Hkv:].to(v_cache.dtype)
+    return qk[:, :Hq].contiguous()
+
+
 def sample_reference(logits: Tensor, uniform: Tensor, temperature: float = 1.0, top_k: int = 0,
                      top_p: float = 1.0) -> Tensor:
     """Oracle of ``sample``: same support rule and the same inverse CDF in index order."""

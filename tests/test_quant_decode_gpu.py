@@ -202,3 +202,44 @@ def test_fused_multi_step_lif_matches_cell_loop(dtype, detach_reset):
     assert torch.equal(sd.float().cpu(), ref.detach())
     tol = 1e-5 if dtype == torch.float32 else 2e-2
     torch.testing.assert_close(xd.grad.float().cpu(), xr.grad, atol=tol, rtol=tol)
+
+
+def test_decode_qkv_prep_rotates_and_appends_in_one_launch():
+    """q rotated out of the packed projection, k rotated into the key cache, v copied into the value cache, all at
+    each sequence's own position; against the plain formulation of the same step."""
+    import tensorplay_b200.ops as O
+    torch.manual_seed(4)
+    B, Hq, Hkv, D, S = 5, 8, 2, 128, 96
+    qkv = torch.randn(B, Hq + 2 * Hkv, D, device="cuda", dtype=torch.bfloat16)
+    cos, sin = O.rope_tables(S, D, 500000.0, device="cuda")
+    pos = torch.tensor([0, 7, 95, 33, 64], device="cuda", dtype=torch.int32)
+    kc = torch.randn(B + 1, S, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.randn(B + 1, S, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    kr, vr = kc.clone(), vc.clone()
+    q = O.decode_qkv_prep(qkv, cos, sin, pos, Hq, Hkv, kc[:B], vc[:B])
+    O.check_status()
+    # reference: the CPU formulation of the same function
+    qr = O.decode_qkv_prep(qkv.cpu(), cos.cpu(), sin.cpu(), pos.cpu(), Hq, Hkv, (kr := kr.cpu())[:B], (vr := vr.cpu())[:B])
+    assert (q.cpu().float() - qr.float()).abs().max() < 0.04
+    assert (kc.cpu().float() - kr.float()).abs().max() < 0.04          # untouched rows are bit-equal, new ones close
+    assert torch.equal(vc.cpu(), vr)
+    assert torch.equal(kc[B].cpu(), kr[B])                             # the row past the batch is untouched
+
+
+def test_flash_fwd_writes_into_a_strided_output():
+    """Decode attention with the query heads of a KV head as rows: the output lands directly in the [B, Hq * D]
+    layout of the next projection, with and without split keys."""
+    from tensorplay_b200.ops.attention import flash_fwd
+    torch.manual_seed(5)
+    B, Hkv, G, D, S = 3, 2, 4, 128, 1024
+    q = torch.randn(B, Hkv * G, D, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(B, S, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(B, S, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    kv_len = torch.tensor(700, device="cuda", dtype=torch.int32)
+    qv = q.view(B, Hkv, G, D).transpose(1, 2)
+    for n_splits in (1, 4):
+        ref, _ = flash_fwd(qv, k, v, False, D ** -0.5, kv_len=kv_len, n_splits=n_splits)
+        ref = ref.transpose(1, 2).reshape(B, Hkv * G * D)
+        out = torch.full((B, Hkv * G * D), float("nan"), device="cuda", dtype=torch.bfloat16)
+        flash_fwd(qv, k, v, False, D ** -0.5, kv_len=kv_len, n_splits=n_splits, out=out.view(B, Hkv, G, D).transpose(1, 2))
+        assert torch.equal(out, ref)
