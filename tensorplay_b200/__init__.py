@@ -47,7 +47,7 @@ from .serialization import inspect_checkpoint, load, save  # noqa: E402
 from .nn.generation import sample  # noqa: E402
 
 _LAZY_OWN = {"distributed", "utils", "models", "parallel", "cuda", "profiler", "autograd", "compat",
-             "multiprocessing", "testing", "quantization", "metrics", "snn", "library", "quantum", "lumen"}
+             "multiprocessing", "testing", "quantization", "metrics", "snn", "library", "quantum", "lumen", "vision"}
 _LAZY_TORCH = {"linalg", "fft", "special", "sparse", "distributions", "func", "futures", "hub", "onnx",
                "masked", "nested", "monitor", "backends", "accelerator", "export", "fx", "random",
                "signal", "overrides", "package", "storage", "types", "jit", "_numpy"}
@@ -111,9 +111,9 @@ def __getattr__(name):
         mod = _importlib.import_module(f"torch.{name}")
         globals()[name] = mod
         return mod
-    if name in ("vision", "audio"):
-        # the domain packs resolve to torchvision / torchaudio when they are installed
-        mod = _importlib.import_module("torchvision" if name == "vision" else "torchaudio")
+    if name == "audio":
+        # the audio pack resolves to torchaudio when it is installed
+        mod = _importlib.import_module("torchaudio")
         globals()[name] = mod
         return mod
     if name == "graph":

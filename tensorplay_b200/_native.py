@@ -80,6 +80,9 @@ _KERNEL_SIGS = {
     "tpb_embedding_fwd": [P, P, P, LL, I, LL, P],
     "tpb_embedding_bwd": [P, P, P, LL, I, LL, I, P],
     "tpb_kv_append": [P, P, P, P, I, I, I, I, I, I, I, LL, LL, LL, LL, LL, LL, P],
+    "tpb_nms": [P, P, I, F, P, P, P, P],
+    "tpb_roi_align_fwd": [P, P, P, I, I, I, I, I, I, I, I, F, I, I, P],
+    "tpb_roi_align_bwd": [P, P, P, I, I, I, I, I, I, I, I, F, I, I, P],
     "tpb_decode_qkv_prep": [P, P, P, P, P, P, P, I, I, I, I, I, I, LL, LL, LL, LL, P],
     "tpb_sample": [P, P, P, P, I, I, LL, I, F, I, F, P],
 }
