@@ -86,11 +86,14 @@ def main():
             O.weight_only_linear(x, q, s, z, None, bits, group)
 
         wbytes = N * K * bits // 8
-        for label, tiles, simt, ver in (("warp-MMA, chosen tiles", 0, False, 1), ("warp-MMA, 1 tile per CTA", 1, False, 1),
-                                        ("warp-MMA, 2 tiles per CTA", 2, False, 1),
-                                        ("warp-MMA second version, chosen tiles", 0, False, 2),
-                                        ("CUDA-core FMA kernel", 0, True, 1)):
-            gemv_config(tiles, simt, ver)
+        for label, tiles, simt, ver, fold in (
+                ("warp-MMA, chosen tiles", 0, False, 1, True), ("warp-MMA, 1 tile per CTA", 1, False, 1, True),
+                ("warp-MMA, 2 tiles per CTA", 2, False, 1, True),
+                ("warp-MMA second version, scaling per weight", 0, False, 2, False),
+                ("warp-MMA second version (4 bits: scaling per 128-k chunk), chosen tiles", 0, False, 2, True),
+                ("warp-MMA second version (4 bits: scaling per 128-k chunk), 2 tiles per CTA", 2, False, 2, True),
+                ("CUDA-core FMA kernel", 0, True, 1, True)):
+            gemv_config(tiles, simt, ver, fold)
             # sixteen calls (two passes over the eight weight sets) replayed from a CUDA graph: the
             # kernel is shorter than the host-side cost of one call, so eager timing would measure Python
             run()

@@ -131,11 +131,13 @@ def weight_only_linear(x: Tensor, q: Tensor, scale: Tensor, zero: Optional[Tenso
     return linear(x, w.to(x.dtype), bias)
 
 
-def gemv_config(tiles: int = 0, force_simt: bool = False, version: int = 2) -> None:
+def gemv_config(tiles: int = 0, force_simt: bool = False, version: int = 2, fold: bool = True) -> None:
     """Knobs of the weight-only GEMV for comparison runs: 16-column tiles per CTA of the warp-MMA
-    kernel (0 = chosen from N), whether to force the CUDA-core kernel, and which warp-MMA version runs
-    (2: the default, its loop written for instruction count; 1: the first version)."""
-    mode = 1 if force_simt else (3 if version == 1 else 0)
+    kernel (0 = chosen from N), whether to force the CUDA-core kernel, which warp-MMA version runs
+    (2: the default, its loop written for instruction count; 1: the first version), and whether 4-bit
+    weights in groups of 128 or more take the form that applies scale and zero point per 128-k chunk
+    (the default) or per weight."""
+    mode = 1 if force_simt else (3 if version == 1 else (0 if fold else 4))
     lib()._lib.tpb_wq_gemv_config(int(tiles), mode)
 
 

@@ -41,15 +41,40 @@ def test_int8_rowwise_quantise():
                                           (8, 16, 2048),   # one group per lane slice of the MMA kernel
                                           (8, 0, 2064), (4, 16, 2064)])  # K off the MMA chunk: CUDA-core kernel
 @pytest.mark.parametrize("M", [1, 3, 16])
-@pytest.mark.parametrize("version", [1, 2])
-def test_weight_only_gemv(bits, group, K, M, version):
-    """Both versions of the warp-MMA kernel (2 = the loop written for instruction count)."""
+@pytest.mark.parametrize("version,fold", [(1, True), (2, True), (2, False)])
+def test_weight_only_gemv(bits, group, K, M, version, fold):
+    """Both versions of the warp-MMA kernel (2 = the loop written for instruction count), the second with scale
+    and zero point applied per 128-k chunk (4 bits, groups >= 128: the default) or per weight."""
     from tensorplay_b200.ops.quant import gemv_config
-    gemv_config(0, False, version)
+    gemv_config(0, False, version, fold)
     try:
         _check_weight_only_gemv(bits, group, K, M)
     finally:
         gemv_config(0, False, 2)
+
+
+@pytest.mark.parametrize("group,K", [(128, 4096), (256, 4096), (512, 2048)])
+def test_w4a16_chunk_scaling_keeps_the_accuracy_with_biased_activations(group, K):
+    """Activations with a large common offset make the 128 * sum(x) term of the chunk-scaled form large; the
+    result must still sit within bf16 output rounding of the per-weight form and of the fp32 oracle."""
+    from tensorplay_b200.ops.quant import gemv_config
+    torch.manual_seed(2)
+    N, M = 520, 5
+    w = torch.randn(N, K, device=DEV)
+    x = (torch.rand(M, K, device=DEV) * 2 + 3).bfloat16()          # every element in [3, 5)
+    q, s, z = O.quantize_weight_int4(w, group)
+    wd = O.dequantize_weight(q, s, z, 4, group).float()
+    ref = x.float() @ wd.t()
+    try:
+        gemv_config(0, False, 2, True)
+        y_fold = O.weight_only_linear(x, q, s, z, None, 4, group).float()
+        gemv_config(0, False, 2, False)
+        y_each = O.weight_only_linear(x, q, s, z, None, 4, group).float()
+    finally:
+        gemv_config(0, False, 2)
+    scale = ref.abs().max().item()
+    assert (y_fold - ref).abs().max() <= 1.2 * (y_each - ref).abs().max() + 2e-3 * scale
+    assert (y_fold - ref).abs().max() < 8e-3 * scale
 
 
 def _check_weight_only_gemv(bits, group, K, M):
