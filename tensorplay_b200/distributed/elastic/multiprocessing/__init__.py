@@ -156,14 +156,6 @@ def record(fn: Optional[Callable] = None, *, error_file: Optional[str] = None):
     return wrap(fn) if fn is not None else wrap
 
 
-class _Errors:
-    ProcessFailure, ChildFailedError, record = ProcessFailure, ChildFailedError, staticmethod(record)
-    ERROR_FILE_ENV = ERROR_FILE_ENV
-
-
-errors = _Errors()
-
-
 # ------------------------------------------------------------------------------------------- tail
 class TailLog:
     """Copies lines appended to per-rank log files to ``dst`` with a ``[name rank]:`` prefix until stopped."""
@@ -420,3 +412,6 @@ def start_processes(name: str, entrypoint: Union[Callable, str], args: Dict[int,
         ctx = MultiprocessContext(name, entrypoint, args, envs, logs_dir, redirects, tee, start_method=start_method)
     ctx.start()
     return ctx
+
+
+from . import errors  # noqa: E402,F401  (sub-module view of ProcessFailure / ChildFailedError / record)
