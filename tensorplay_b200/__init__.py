@@ -59,7 +59,7 @@ class _TorchAliasFinder:
     ``profiler.profiler``, ``multiprocessing.reductions``), so module paths of the reference that only
     name PyTorch-equivalent code keep importing. Sits last on ``sys.meta_path``: own modules win."""
 
-    _PKGS = ("optim", "autograd", "profiler", "multiprocessing", "utils", "cuda", "amp", "testing", "nn")
+    _PKGS = ("optim", "autograd", "profiler", "multiprocessing", "utils", "cuda", "amp", "testing", "nn", "distributed")
 
     def find_spec(self, fullname, path=None, target=None):
         parts = fullname.split(".")
@@ -96,10 +96,36 @@ class _TorchAliasLoader:
         pass
 
 
+class _AliasedParentFinder:
+    """First on ``sys.meta_path``: a sub-module of a name that already resolved to a PyTorch (or torchvision /
+    torchaudio) package must resolve to the SAME module object as its PyTorch spelling. Without this the path
+    finder would follow the aliased package's ``__path__`` and execute PyTorch's source file a second time under
+    the new name: duplicate classes, and operator registrations that fail the second time."""
+
+    def find_spec(self, fullname, path=None, target=None):
+        if not fullname.startswith(__name__ + "."):
+            return None
+        parent_name, _, tail = fullname.rpartition(".")
+        parent = _sys.modules.get(parent_name)
+        real = getattr(parent, "__name__", "")
+        if parent is None or real == parent_name or real.split(".")[0] not in ("torch", "torchvision", "torchaudio"):
+            return None
+        import importlib.util
+        target_name = f"{real}.{tail}"
+        try:
+            if target_name not in _sys.modules and importlib.util.find_spec(target_name) is None:
+                return None
+        except (ImportError, ValueError, AttributeError):
+            return None
+        return importlib.util.spec_from_loader(fullname, _TorchAliasLoader(target_name))
+
+
 import sys as _sys  # noqa: E402
 
 if not [f for f in _sys.meta_path if type(f).__name__ == "_TorchAliasFinder"]:
     _sys.meta_path.append(_TorchAliasFinder())
+if not [f for f in _sys.meta_path if type(f).__name__ == "_AliasedParentFinder"]:
+    _sys.meta_path.insert(0, _AliasedParentFinder())
 
 
 def __getattr__(name):

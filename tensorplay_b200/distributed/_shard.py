@@ -9,3 +9,7 @@ from torch.distributed._shard.sharded_tensor import (Shard, ShardedTensor, Shard
 from torch.distributed._shard.sharding_plan import ShardingPlan, ShardingPlanner  # noqa: F401
 from torch.distributed._shard.sharding_spec import (ChunkShardingSpec, DevicePlacementSpec, EnumerableShardingSpec,  # noqa: F401
                                                     PlacementSpec, ShardingSpec, ShardMetadata)
+
+
+# the reference has a package at this path: sub-module names without a file here resolve to PyTorch's
+__path__: list = []

@@ -142,15 +142,4 @@ class HierarchicalModelAverager(ModelAverager):
         self.step += 1
 
 
-# the reference's sub-module paths
-class _Namespace:
-    pass
-
-
-averagers = _Namespace()
-averagers.ModelAverager, averagers.PeriodicModelAverager = ModelAverager, PeriodicModelAverager
-hierarchical_model_averager = _Namespace()
-hierarchical_model_averager.HierarchicalModelAverager = HierarchicalModelAverager
-utils = _Namespace()
-utils.average_parameters, utils.get_params_to_average = average_parameters, get_params_to_average
-utils.average_parameters_or_parameter_groups = average_parameters_or_parameter_groups
+from . import averagers, hierarchical_model_averager, utils  # noqa: E402,F401  (the reference's sub-module paths)

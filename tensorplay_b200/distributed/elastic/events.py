@@ -156,3 +156,7 @@ def construct_and_record_rdzv_event(run_id: str, message: str, node_state: NodeS
     record_rdzv_event(RdzvEvent(name=name, run_id=run_id, message=message, hostname=hostname or socket.getfqdn(),
                                 pid=pid or os.getpid(), node_state=node_state, master_endpoint=master_endpoint,
                                 rank=rank, local_id=local_id, error_trace=trace))
+
+
+# the reference has a package at this path: sub-module names without a file here resolve to PyTorch's
+__path__: list = []

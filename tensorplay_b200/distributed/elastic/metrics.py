@@ -110,3 +110,7 @@ def prof(fn=None, group: str = "tensorplay_elastic"):
 def profile(group=None):
     """Older spelling of :func:`prof` with the group as the only argument."""
     return prof(group=group or "tensorplay_elastic")
+
+
+# the reference has a package at this path: sub-module names without a file here resolve to PyTorch's
+__path__: list = []

@@ -103,3 +103,7 @@ def barrier(store, world_size: int, key_prefix: str, barrier_timeout: Union[floa
                 names = [rank_tracing_decoder(r) if rank_tracing_decoder else str(r) for r in missing]
                 raise type(e)(f"barrier {key_prefix!r} timed out; ranks that did not arrive: {', '.join(names)}") from e
             raise
+
+
+# the reference has a package at this path: sub-module names without a file here resolve to PyTorch's
+__path__: list = []

@@ -106,3 +106,7 @@ def start_flight_recorder(dump_path: Optional[str] = None, size: Optional[int] =
 
 def dump_flight_recorder(path: Optional[str] = None) -> str:
     return (_recorder or FlightRecorder()).dump(path)
+
+
+# the reference has a package at this path: sub-module names without a file here resolve to PyTorch's
+__path__: list = []

@@ -34,3 +34,7 @@ from .inputs import (MSE, Count, ImageMaskInput, InterpretableEmbeddingBase, Int
                      LLMAttributionResult, Max, Mean, Min, ProductBaselines, RemoteLLMAttribution, RemoteLLMProvider, Stat,
                      StatValue, StdDev, Sum, SummarizerSingleTensor, TextTemplateInput, TextTokenInput, TokenReferenceBase, Var,
                      VLLMProvider, configure_interpretable_embedding_layer, remove_interpretable_embedding_layer)
+
+from .. import _views as _views  # noqa: E402
+
+_views.install(__name__, max_depth=3)

@@ -82,3 +82,7 @@ class Attribution:
 
     def has_convergence_delta(self) -> bool:
         return False
+
+
+# the reference has a package at this path: deeper module names resolve to views of the pack
+__path__: list = []

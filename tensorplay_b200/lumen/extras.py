@@ -239,3 +239,7 @@ class GraphDeconvolution(_GraphModifiedRelu):
 
 __all__ = ["LimeBase", "LayerDeepLiftShap", "NeuronDeepLiftShap", "DataLoaderAttribution", "trace", "node_names",
            "graph_gradient_func", "GraphGuidedBackprop", "GraphDeconvolution"]
+
+
+# the reference has a package at this path: deeper module names resolve to views of the pack
+__path__: list = []

@@ -223,3 +223,7 @@ class DeepLift(Attribution):
             return like_input(attr, inputs)
         delta = sum(a.reshape(n, -1).sum(1) for a in attr) - (out[:n] - out[n:]).detach()
         return like_input(attr, inputs), delta
+
+
+# the reference has a package at this path: deeper module names resolve to views of the pack
+__path__: list = []

@@ -625,3 +625,7 @@ class RemoteLLMAttribution(LLMAttribution):
         if len(lp) != target_ids.numel():
             raise ValueError(f"the provider returned {len(lp)} log-probabilities for {target_ids.numel()} target tokens")
         return torch.tensor(lp, dtype=torch.float32)
+
+
+# the reference has a package at this path: deeper module names resolve to views of the pack
+__path__: list = []

@@ -148,3 +148,7 @@ class InternalInfluence(LayerAttribution):
                 g = torch.autograd.grad(out.sum(), act)[0] * w
             total = g if total is None else total + g
         return total
+
+
+# the reference has a package at this path: deeper module names resolve to views of the pack
+__path__: list = []

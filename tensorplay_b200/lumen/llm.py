@@ -88,3 +88,7 @@ class LLMGradientAttribution:
             g = torch.autograd.grad(total, e)[0]
         scores = (g * e).sum(-1).detach()
         return {"token_attr": scores, "log_prob": sel.detach(), "seq_attr": scores[:, :P]}
+
+
+# the reference has a package at this path: deeper module names resolve to views of the pack
+__path__: list = []

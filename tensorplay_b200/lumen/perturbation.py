@@ -187,3 +187,7 @@ class KernelShap(Lime):
         w = torch.ones(len(z))
         w[:2] = 1e6      # the full and the empty coalition pin f(x) and f(baseline)
         return w
+
+
+# the reference has a package at this path: deeper module names resolve to views of the pack
+__path__: list = []

@@ -295,3 +295,7 @@ class ClassSummarizer:
     @property
     def class_summaries(self):
         return {k: v.summary for k, v in self.per.items()}
+
+
+# the reference has a package at this path: deeper module names resolve to views of the pack
+__path__: list = []

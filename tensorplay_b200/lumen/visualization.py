@@ -172,3 +172,7 @@ def visualize_text(datarecords: Iterable[VisualizationDataRecord], legend: bool 
 __all__ = ["VisualizeSign", "ImageVisualizationMethod", "normalize_attr", "heat_map", "save_heat_map", "visualize_image_attr",
            "visualize_image_attr_multiple", "visualize_timeseries_attr", "VisualizationDataRecord", "format_classname",
            "format_special_tokens", "format_word_importances", "visualize_text"]
+
+
+# the reference has a package at this path: deeper module names resolve to views of the pack
+__path__: list = []

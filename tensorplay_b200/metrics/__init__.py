@@ -308,8 +308,13 @@ def _domain_views() -> None:
             continue
         mod = types.ModuleType(f"{__name__}.{name}", f"View of {__name__} for the {name} metrics.")
         mod.__getattr__ = lambda attr, _pkg=pkg: getattr(_pkg, attr)
+        mod.__path__ = []   # deeper module names (metrics.text.bleu ...) resolve through the view finder
         sys.modules[mod.__name__] = mod
         setattr(pkg, name, mod)
 
 
 _domain_views()
+
+from .. import _views as _view_finder  # noqa: E402
+
+_view_finder.install(__name__, max_depth=2)

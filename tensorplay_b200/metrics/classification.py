@@ -432,3 +432,7 @@ class ExactMatch(Metric):
 
 
 __all__ = sorted(n for n in globals() if n[0].isupper() and n not in ("Metric", "Tensor", "Optional"))
+
+
+# the reference has a package at this path: deeper module names resolve to views of the pack
+__path__: list = []

@@ -397,3 +397,7 @@ class RetrievalAUROC(_Retrieval):
 
 __all__ = sorted(n for n in globals() if n[0].isupper() and n not in ("Metric", "Tensor", "Optional", "Counter", "List",
                                                                       "Sequence", "Union")) + ["edit_distance", "ssim"]
+
+
+# the reference has a package at this path: deeper module names resolve to views of the pack
+__path__: list = []

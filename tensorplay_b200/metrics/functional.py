@@ -60,3 +60,7 @@ def __getattr__(name: str):
 
 def __dir__():
     return sorted(set(globals()) | set(dir(_ranking)))
+
+
+# the reference has a package at this path: deeper module names resolve to views of the pack
+__path__: list = []

@@ -348,3 +348,7 @@ __all__ = ["FrechetInceptionDistance", "KernelInceptionDistance", "InceptionScor
            "short_time_objective_intelligibility", "PerceptualEvaluationSpeechQuality",
            "SpeechReverberationModulationEnergyRatio", "DeepNoiseSuppressionMeanOpinionScore",
            "NonIntrusiveSpeechQualityAssessment", "InfoLM"]
+
+
+# the reference has a package at this path: deeper module names resolve to views of the pack
+__path__: list = []

@@ -662,3 +662,7 @@ def pit_permutate(preds: Tensor, perm: Tensor) -> Tensor:
 
 __all__ = sorted(n for n in globals() if n[0].isupper() and n not in ("Metric", "Tensor", "Optional", "Callable", "Dict")) + ["cramers_v_matrix", "tschuprows_t_matrix", "pearsons_contingency_coefficient_matrix", "theils_u_matrix",
            "pit_permutate", "signal_distortion_ratio"]
+
+
+# the reference has a package at this path: deeper module names resolve to views of the pack
+__path__: list = []

@@ -114,3 +114,7 @@ class ModifiedPanopticQuality(PanopticQuality):
 
 
 __all__ = ["PanopticQuality", "ModifiedPanopticQuality"]
+
+
+# the reference has a package at this path: deeper module names resolve to views of the pack
+__path__: list = []

@@ -168,3 +168,7 @@ class RetrievalMRR(_Collecting):
 
 class CalibrationError(_Collecting):
     fn = staticmethod(expected_calibration_error)
+
+
+# the reference has a package at this path: deeper module names resolve to views of the pack
+__path__: list = []

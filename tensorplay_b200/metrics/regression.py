@@ -414,3 +414,7 @@ class CompositionalMetric(Metric):
 
 
 __all__ = sorted(n for n in globals() if n[0].isupper() and n not in ("Metric", "Tensor", "Optional", "Dict", "List", "Sequence"))
+
+
+# the reference has a package at this path: deeper module names resolve to views of the pack
+__path__: list = []

@@ -264,3 +264,7 @@ class SQuAD(Metric):
 
 
 __all__ = ["SacreBLEUScore", "CHRFScore", "TranslationEditRate", "ExtendedEditDistance", "SQuAD"]
+
+
+# the reference has a package at this path: deeper module names resolve to views of the pack
+__path__: list = []

@@ -121,3 +121,7 @@ def check_forward_full_state_property(metric_class, init_args=None, input_args=N
 
 __all__ = ["check_forward_full_state_property", "class_reduce", "dim_zero_cat", "dim_zero_max", "dim_zero_mean",
            "dim_zero_min", "dim_zero_sum", "rank_zero_debug", "rank_zero_info", "rank_zero_warn", "reduce"]
+
+
+# the reference has a package at this path: deeper module names resolve to views of the pack
+__path__: list = []

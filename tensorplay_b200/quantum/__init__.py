@@ -41,3 +41,7 @@ def decode_w(key) -> list:
     if not key:
         raise ValueError("a wire key must not be empty")
     return [int(part) for part in str(key).split(".")]
+
+from .. import _views as _views  # noqa: E402
+
+_views.install(__name__, max_depth=1)

@@ -36,3 +36,7 @@ def apply_1q_native(state: Tensor, matrix: Tensor, target: int, controls: Tuple[
                                              C.cast(carr, C.c_void_p), len(controls),
                                              C.cast(marr, C.c_void_p), stream_ptr()), "tpb_quantum_apply_1q")
     return out
+
+
+# the reference has a package at this path: deeper module names resolve to views of the pack
+__path__: list = []

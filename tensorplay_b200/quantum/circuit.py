@@ -148,3 +148,7 @@ def expand_to_register(matrix: Tensor, wires: Sequence[int], n: int) -> Tensor:
     d = 2 ** n
     eye = torch.eye(d, dtype=matrix.dtype, device=matrix.device).reshape([d] + [2] * n)
     return G.apply_gate(eye, matrix, list(wires)).reshape(d, d).transpose(0, 1)
+
+
+# the reference has a package at this path: deeper module names resolve to views of the pack
+__path__: list = []

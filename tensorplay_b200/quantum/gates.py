@@ -415,3 +415,7 @@ apply_rccx, apply_rc3x = _fixed("rccx", rccx_matrix, 3), _fixed("rc3x", rc3x_mat
 apply_single_excitation = _param("single_excitation", single_excitation_matrix, 2)
 apply_xx_plus_yy = _param("xx_plus_yy", xx_plus_yy_matrix, 2, 2)
 apply_xx_minus_yy = _param("xx_minus_yy", xx_minus_yy_matrix, 2, 2)
+
+
+# the reference has a package at this path: deeper module names resolve to views of the pack
+__path__: list = []

@@ -133,3 +133,7 @@ def commuting_groups(words: Sequence[str]) -> List[List[str]]:
         else:
             groups.append([w])
     return groups
+
+
+# the reference has a package at this path: deeper module names resolve to views of the pack
+__path__: list = []

@@ -211,3 +211,7 @@ def sample_energy(state: Tensor, h: Hamiltonian, shots: int = 1024, generator=No
             par = bits[..., sel].sum(-1) & 1
             total += coeff[w] * (1 - 2 * par).double().mean(-1)
     return total
+
+
+# the reference has a package at this path: deeper module names resolve to views of the pack
+__path__: list = []

@@ -111,10 +111,10 @@ def _hooks_worker(rank, world):
 
     # post-local SGD: all-reduced for two iterations, then local (no subgroup)
     st = H.PostLocalSGDState(None, None, start_localSGD_iter=2)
-    a = grads(H.post_localSGD_hook, st, steps=2)
+    a = grads(H.post_localSGD.post_localSGD_hook, st, steps=2)
     assert st.iter == 2
     st2 = H.PostLocalSGDState(None, None, start_localSGD_iter=2)
-    b = grads(H.post_localSGD_hook, st2, steps=3)
+    b = grads(H.post_localSGD.post_localSGD_hook, st2, steps=3)
     gathered = [torch.empty_like(a) for _ in range(world)]
     dist.all_gather(gathered, a)
     assert all(torch.allclose(g, gathered[0]) for g in gathered)          # still synchronised

@@ -1,0 +1,62 @@
+"""Module paths of the reference keep importing: own files first, PyTorch's module of the same path next (as the
+SAME module object, never a second execution of its source), views of the domain packs last."""
+import importlib
+
+import pytest
+
+
+@pytest.mark.parametrize("name,torch_name", [
+    ("distributed.tensor._ops._math_ops", "torch.distributed.tensor._ops._math_ops"),
+    ("distributed.fsdp._fully_shard._fsdp_collectives", "torch.distributed.fsdp._fully_shard._fsdp_collectives"),
+    ("distributed.elastic.rendezvous.etcd_store", "torch.distributed.elastic.rendezvous.etcd_store"),
+    ("distributed._shard.sharded_tensor.api", "torch.distributed._shard.sharded_tensor.api"),
+    ("distributed.algorithms.ddp_comm_hooks.ddp_zero_hook", "torch.distributed.algorithms.ddp_comm_hooks.ddp_zero_hook"),
+    ("distributed.flight_recorder.components.types", "torch.distributed.flight_recorder.components.types"),
+    ("nn.utils.rnn", "torch.nn.utils.rnn"),
+    ("optim.lbfgs", "torch.optim.lbfgs"),
+])
+def test_paths_without_a_file_here_are_pytorchs_module_objects(name, torch_name):
+    ours = importlib.import_module("tensorplay_b200." + name)
+    assert ours is importlib.import_module(torch_name)
+
+
+def test_own_modules_win_and_submodule_paths_exist():
+    from tensorplay_b200.distributed.algorithms import ddp_comm_hooks as H
+    from tensorplay_b200.distributed.algorithms.ddp_comm_hooks.default_hooks import allreduce_hook
+    from tensorplay_b200.distributed.algorithms.ddp_comm_hooks.powerSGD_hook import PowerSGDState, powerSGD_hook
+    from tensorplay_b200.distributed.algorithms.ddp_comm_hooks.post_localSGD_hook import PostLocalSGDState
+    from tensorplay_b200.distributed.algorithms.model_averaging.averagers import PeriodicModelAverager
+    from tensorplay_b200.distributed.algorithms.model_averaging.utils import average_parameters
+    from tensorplay_b200.distributed.elastic.multiprocessing.errors import record
+    from tensorplay_b200.distributed.optim import ZeroRedundancyOptimizer
+    import tensorplay_b200.distributed.algorithms as A
+    assert allreduce_hook is A.allreduce_hook and PostLocalSGDState is A.PostLocalSGDState
+    assert H.powerSGD_hook.powerSGD_hook is powerSGD_hook and PowerSGDState(None, 2)["rank"] == 2
+    assert PeriodicModelAverager.__module__.startswith("tensorplay_b200")
+    assert ZeroRedundancyOptimizer.__module__ == "tensorplay_b200.distributed.optim.zero"
+    assert average_parameters.__module__.startswith("tensorplay_b200") and callable(record)
+
+
+def test_domain_pack_views():
+    import tensorplay_b200.lumen as L
+    import tensorplay_b200.metrics as M
+    from tensorplay_b200.lumen._core.layer.grad_cam import LayerGradCam
+    from tensorplay_b200.metrics.classification.accuracy import BinaryAccuracy
+    from tensorplay_b200.metrics.functional.classification.accuracy import binary_accuracy
+    from tensorplay_b200.metrics.text.bleu import BLEUScore
+    assert BinaryAccuracy is M.BinaryAccuracy and BLEUScore is M.BLEUScore and LayerGradCam is L.LayerGradCam
+    assert binary_accuracy is M.functional.binary_accuracy
+    with pytest.raises(ImportError):
+        from tensorplay_b200.metrics.classification.accuracy import NoSuchMetric  # noqa: F401
+
+
+def test_alias_spelling_reaches_the_same_objects():
+    import tensorplay_b200.compat as compat
+    compat.install_alias()
+    from tensorplay.distributed.elastic.multiprocessing.errors import record
+    from tensorplay.metrics.regression.mse import MeanSquaredError
+    from tensorplay.vision.ops import nms
+    import tensorplay_b200.metrics as M
+    from tensorplay_b200.distributed.elastic.multiprocessing import record as r0
+    from tensorplay_b200.vision.ops import nms as n0
+    assert record is r0 and MeanSquaredError is M.MeanSquaredError and nms is n0
