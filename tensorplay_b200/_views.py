@@ -13,11 +13,11 @@ import types
 
 
 class _ViewLoader:
-    def __init__(self, package: str):
-        self.package = package
+    def __init__(self, package: str, namespace: str):
+        self.package, self.namespace = package, namespace
 
     def create_module(self, spec):
-        pkg = importlib.import_module(self.package)
+        pkg = importlib.import_module(self.namespace)
         target = pkg
         if ".functional" in spec.name[len(self.package):] and hasattr(pkg, "functional"):
             target = pkg.functional
@@ -49,8 +49,8 @@ class _ViewFinder:
     that cannot be module names of the reference are refused: anything with an upper-case letter, and anything
     deeper below the pack than its module tree goes (one level more below ``functional``)."""
 
-    def __init__(self, package: str, max_depth: int):
-        self.package, self.max_depth = package, max_depth
+    def __init__(self, package: str, max_depth: int, namespace: str):
+        self.package, self.max_depth, self.namespace = package, max_depth, namespace
 
     def find_spec(self, fullname, path=None, target=None):
         if not fullname.startswith(self.package + "."):
@@ -59,11 +59,12 @@ class _ViewFinder:
         depth = len(parts) - (1 if parts[0] == "functional" else 0)
         if depth > self.max_depth or any(c.isupper() for c in parts[-1]):
             return None
-        return importlib.util.spec_from_loader(fullname, _ViewLoader(self.package))
+        return importlib.util.spec_from_loader(fullname, _ViewLoader(self.package, self.namespace))
 
 
-def install(package: str, max_depth: int = 3) -> None:
-    """Appended to ``sys.meta_path``: real files of the pack are found first. ``max_depth``: levels of module names
-    below the pack in the reference's tree."""
+def install(package: str, max_depth: int = 3, namespace: str = "") -> None:
+    """Appended to ``sys.meta_path``: real files of the pack are found first (and PyTorch's module of the same path
+    where the package falls back to PyTorch). ``max_depth``: levels of module names below the pack in the reference's
+    tree; ``namespace``: the module whose attributes the views show (default: the package itself)."""
     if not [f for f in sys.meta_path if isinstance(f, _ViewFinder) and f.package == package]:
-        sys.meta_path.append(_ViewFinder(package, max_depth))
+        sys.meta_path.append(_ViewFinder(package, max_depth, namespace or package))

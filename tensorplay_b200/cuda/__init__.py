@@ -73,3 +73,7 @@ def __getattr__(name):  # noqa: F811
         from torch.cuda import gds
         return gds.GdsFile
     return getattr(_tc, name)
+
+from .. import _views as _views  # noqa: E402
+
+_views.install(__name__, max_depth=1)

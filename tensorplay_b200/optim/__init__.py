@@ -46,3 +46,7 @@ def swap_in_optimizer_params_and_state(optimizer, swapin_parameters, swapin_opti
             g.clear()
             g.update(snap)
         optimizer.state = original_state
+
+from .. import _views as _views  # noqa: E402
+
+_views.install(__name__, max_depth=1)

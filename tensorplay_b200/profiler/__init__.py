@@ -88,3 +88,7 @@ def __getattr__(name):
         except (ImportError, AttributeError):
             continue
     raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+
+from .. import _views as _views  # noqa: E402
+
+_views.install(__name__, max_depth=1)

@@ -14,3 +14,7 @@ def __getattr__(name):
         return getattr(tv, name)
     except AttributeError:
         return importlib.import_module(f"torchvision.{name}")
+
+from .. import _views as _views  # noqa: E402
+
+_views.install(__name__, max_depth=1)
