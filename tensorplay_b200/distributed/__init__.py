@@ -25,6 +25,10 @@ from .store import FileStore, HashStore, PrefixStore, StoreTimeoutError, TCPStor
 all_gather_single = all_gather_into_tensor
 reduce_scatter_single = reduce_scatter_tensor
 
+from ._collective_extras import (SHRINK_ABORT, SHRINK_DEFAULT, AllgatherOptions, all_gather_single_coalesced,  # noqa: E402,F401
+                                 gather_into_tensor, gather_single, record_comm, reduce_scatter_coalesced,
+                                 reduce_scatter_single_coalesced, register_device_backend, set_timeout)
+
 _LAZY = {"ddp", "fsdp", "device_mesh", "pipelining", "tensor", "checkpoint", "elastic", "run", "launcher",
          "flight_recorder", "watchdog", "_symmetric_memory", "_token_switch", "algorithms", "optim",
          "rendezvous", "debug", "_tools", "rpc", "nn", "utils", "_functional_collectives", "_composable",

@@ -55,6 +55,17 @@ def to_map(val_or_map: Union[Std, Dict[int, Std]], local_world_size: int) -> Dic
     return {r: val_or_map for r in range(local_world_size)}
 
 
+class SignalException(Exception):
+    """Raised in the launcher when it receives a termination signal, so that ``finally`` blocks end the workers."""
+
+    def __init__(self, msg: str, sigval: signal.Signals):
+        super().__init__(msg)
+        self.sigval = sigval
+
+
+Redirects = Std   # older name of the same flags
+
+
 # ------------------------------------------------------------------------------------------- errors
 @dataclass
 class ProcessFailure:
@@ -192,6 +203,89 @@ class TailLog:
         for t in self._threads:
             t.join(timeout=5)
         self._threads = []
+
+
+def tail_logfile(header: str, file: str, dst, finished: threading.Event, interval_sec: float = 0.1) -> None:
+    """Copies lines appended to ``file`` to ``dst`` behind ``header`` until ``finished`` is set and the file is read
+    to its end."""
+    while not os.path.exists(file):
+        if finished.is_set():
+            return
+        time.sleep(interval_sec)
+    with open(file, errors="replace") as f:
+        while True:
+            line = f.readline()
+            if line:
+                dst.write(f"{header}{line}")
+            elif finished.is_set():
+                return
+            else:
+                time.sleep(interval_sec)
+
+
+# ------------------------------------------------------------------------------------------- log destinations
+@dataclass
+class LogsDest:
+    """Per local rank: files for redirected stdout / stderr, the subset that is also teed, and the error files."""
+    stdouts: Dict[int, str] = field(default_factory=dict)
+    stderrs: Dict[int, str] = field(default_factory=dict)
+    tee_stdouts: Dict[int, str] = field(default_factory=dict)
+    tee_stderrs: Dict[int, str] = field(default_factory=dict)
+    error_files: Dict[int, str] = field(default_factory=dict)
+
+
+class LogsSpecs(abc.ABC):
+    def __init__(self, log_dir: Optional[str] = None, redirects: Union[Std, Dict[int, Std]] = Std.NONE,
+                 tee: Union[Std, Dict[int, Std]] = Std.NONE, local_ranks_filter: Optional[set] = None):
+        self._root_log_dir, self._redirects, self._tee, self._local_ranks_filter = log_dir, redirects, tee, local_ranks_filter
+
+    @abc.abstractmethod
+    def reify(self, envs: Dict[int, Dict[str, str]]) -> LogsDest: ...
+
+    @property
+    @abc.abstractmethod
+    def root_log_dir(self) -> str: ...
+
+
+class DefaultLogsSpecs(LogsSpecs):
+    """``<log_dir>/<run id>_<random>/attempt_<n>/<local rank>/{stdout,stderr}.log`` and ``error.json``."""
+
+    def __init__(self, log_dir=None, redirects=Std.NONE, tee=Std.NONE, local_ranks_filter=None):
+        import tempfile
+        if log_dir is None:
+            log_dir = tempfile.mkdtemp(prefix="tensorplay_elastic_")
+        elif not os.path.exists(log_dir):
+            os.makedirs(log_dir, exist_ok=True)
+        super().__init__(log_dir, redirects, tee, local_ranks_filter)
+        self._run_log_dir: Optional[str] = None
+
+    @property
+    def root_log_dir(self) -> str:
+        return str(self._root_log_dir)
+
+    def reify(self, envs: Dict[int, Dict[str, str]]) -> LogsDest:
+        import tempfile
+        n = len(envs)
+        first = envs.get(0, {}) if n else {}
+        if self._run_log_dir is None:
+            run_id = str(first.get("TORCHELASTIC_RUN_ID", first.get("TP_RUN_ID", "run")))
+            self._run_log_dir = tempfile.mkdtemp(prefix=f"{run_id}_", dir=self._root_log_dir)
+        attempt = os.path.join(self._run_log_dir, f"attempt_{first.get('TORCHELASTIC_RESTART_COUNT', first.get('TP_RESTART_COUNT', 0))}")
+        red, te = to_map(self._redirects, n), to_map(self._tee, n)
+        dest = LogsDest()
+        for r in range(n):
+            d = os.path.join(attempt, str(r))
+            os.makedirs(d, exist_ok=True)
+            want = red[r] | te[r]
+            dest.stdouts[r] = os.path.join(d, "stdout.log") if want & Std.OUT else ""
+            dest.stderrs[r] = os.path.join(d, "stderr.log") if want & Std.ERR else ""
+            shown = self._local_ranks_filter is None or r in self._local_ranks_filter
+            if te[r] & Std.OUT and shown:
+                dest.tee_stdouts[r] = dest.stdouts[r]
+            if te[r] & Std.ERR and shown:
+                dest.tee_stderrs[r] = dest.stderrs[r]
+            dest.error_files[r] = os.path.join(d, "error.json")
+        return dest
 
 
 # ------------------------------------------------------------------------------------------- contexts

@@ -184,3 +184,47 @@ def _funcol_worker(rank, world):
 
 def test_functional_collective_spellings_and_symmetric_memory_helpers():
     assert all(run_ranks(_funcol_worker, 2))
+
+
+def _extras_worker(rank, world):
+    import torch.distributed as dist
+    import tensorplay_b200.distributed as tpd
+
+    # gather into one tensor on a destination rank
+    t = torch.full((3,), float(rank))
+    out = torch.empty(world, 3) if rank == 1 else None
+    tpd.gather_single(t, out, dst=1)
+    if rank == 1:
+        assert out.tolist() == [[float(r)] * 3 for r in range(world)]
+    # coalesced all-gather: two dtypes, three tensors, one collective per dtype
+    ins = [torch.arange(4.0) + rank, torch.tensor([rank], dtype=torch.int64), torch.full((2, 2), float(rank))]
+    outs = [torch.empty(world * 4), torch.empty(world, dtype=torch.int64), torch.empty(world, 2, 2)]
+    tpd.all_gather_single_coalesced(outs, ins)
+    assert outs[0].view(world, 4)[1].tolist() == [1.0, 2.0, 3.0, 4.0] and outs[1].tolist() == list(range(world))
+    assert outs[2][1].tolist() == [[1.0, 1.0], [1.0, 1.0]]
+    work = tpd.all_gather_single_coalesced(outs, ins, async_op=True)
+    work.wait()
+    assert outs[1].tolist() == list(range(world))
+    # coalesced reduce-scatter, both spellings
+    ins = [torch.arange(2.0 * world) * (rank + 1), torch.ones(world * 3) * (rank + 1)]
+    outs = [torch.empty(2), torch.empty(3)]
+    tpd.reduce_scatter_single_coalesced(outs, ins)
+    tot = sum(range(1, world + 1))
+    assert outs[0].tolist() == [2.0 * rank * tot, (2.0 * rank + 1) * tot] and outs[1].tolist() == [float(tot)] * 3
+    outs2 = [torch.empty(2)]
+    tpd.reduce_scatter_coalesced(outs2, [[torch.full((2,), float(rank + r)) for r in range(world)]])
+    assert outs2[0].tolist() == [float(sum(q + rank for q in range(world)))] * 2
+    # names of communication regions and the timeout setter
+    with tpd.record_comm("grad-bucket-3"):
+        from tensorplay_b200.distributed._collective_extras import current_comm_name
+        assert current_comm_name() == "grad-bucket-3"
+        dist.barrier()
+    assert current_comm_name() is None
+    from datetime import timedelta
+    tpd.set_timeout(timedelta(seconds=120))
+    assert tpd.SHRINK_DEFAULT == 0 and tpd.SHRINK_ABORT == 1 and tpd.AllgatherOptions is not None
+    return True
+
+
+def test_collective_spellings_beyond_pytorchs():
+    assert all(run_ranks(_extras_worker, 2))

@@ -152,3 +152,57 @@ def test_launcher_reports_the_failing_ranks_exception(tmp_path):
         elastic_launch(LaunchConfig(nproc_per_node=2, log_dir=str(tmp_path / "logs"), env=env), [sys.executable, str(script)])
     assert ei.value.failures == {1: 1}
     assert "missing shard 17" in str(ei.value) and "KeyError" in str(ei.value) and "in main" in str(ei.value)
+
+
+def test_rendezvous_helpers_backend_and_registry():
+    from datetime import timedelta
+    from tensorplay_b200.distributed.elastic import rendezvous as R
+    assert R.parse_rendezvous_endpoint("node3:29400", 1) == ("node3", 29400)
+    assert R.parse_rendezvous_endpoint("node3", 29500) == ("node3", 29500)
+    assert R.parse_rendezvous_endpoint("[::1]:80", 1) == ("::1", 80) and R.parse_rendezvous_endpoint("", 7) == ("localhost", 7)
+    with pytest.raises(ValueError):
+        R.parse_rendezvous_endpoint("host:99999", 1)
+    assert R._parse_rendezvous_config("timeout=30, read_timeout = 5") == {"timeout": "30", "read_timeout": "5"}
+    with pytest.raises(ValueError):
+        R._parse_rendezvous_config("timeout")
+    assert R._matches_machine_hostname("localhost") and R._matches_machine_hostname("127.0.0.1")
+    t = R.RendezvousTimeout(join=timedelta(seconds=3))
+    assert t.join.total_seconds() == 3 and t.heartbeat.total_seconds() == 5
+    with pytest.raises(ValueError):
+        R.RendezvousTimeout(close=timedelta(0))
+    ticks = []
+    timer = R._PeriodicTimer(timedelta(milliseconds=20), ticks.append, 1)
+    timer.start()
+    import time
+    time.sleep(0.15)
+    timer.cancel()
+    assert 3 <= len(ticks) <= 9
+    # fenced state back end: a writer with a stale token loses and is told the current state
+    be = R.StoreRendezvousBackend(HashStore(), "job")
+    assert be.get_state() is None
+    state, token, ok = be.set_state(b"v1")
+    assert ok and state == b"v1"
+    _, _, ok_stale = be.set_state(b"v2-from-stale", token=b"something-else")
+    assert not ok_stale and be.get_state()[0] == b"v1"
+    _, token2, ok2 = be.set_state(b"v2", token=token)
+    assert ok2 and be.get_state()[0] == b"v2" and token2 == b"v2"
+    # registry: the static handler needs no negotiation; the dynamic one is reachable by name
+    reg = R.get_registry()
+    assert {"static", "dynamic"} <= set(reg.backends())
+    h = reg.create_handler("dynamic", HashStore(), "j2", 1, 1)
+    store, rank, world = h.next_rendezvous()
+    assert (rank, world) == (0, 1)
+    h.shutdown()
+    with pytest.raises(ValueError):
+        reg.create_handler("nope")
+
+
+def test_logs_specs_layout(tmp_path):
+    specs = emp.DefaultLogsSpecs(str(tmp_path), redirects=emp.Std.OUT, tee={1: emp.Std.ERR}, local_ranks_filter={1})
+    dest = specs.reify({0: {"TORCHELASTIC_RUN_ID": "jobx", "TORCHELASTIC_RESTART_COUNT": 2}, 1: {}})
+    assert specs.root_log_dir == str(tmp_path)
+    assert dest.stdouts[0].endswith("attempt_2/0/stdout.log") and "jobx_" in dest.stdouts[0]
+    assert dest.stderrs[0] == "" and dest.stderrs[1].endswith("1/stderr.log") and dest.tee_stderrs == {1: dest.stderrs[1]}
+    assert os.path.isdir(os.path.dirname(dest.error_files[1])) and emp.Redirects is emp.Std
+    e = emp.SignalException("got it", __import__("signal").SIGTERM)
+    assert e.sigval.name == "SIGTERM"
