@@ -4,6 +4,19 @@ size included). On-disk layout follows the reference's (tensorplay/distributed/c
 filesystem.py:56-80): one data file per rank ``__{rank}_0.distcp`` (a ``.mega`` container here)
 plus ``.metadata``; ``async_save`` stages to host memory and writes in the background
 (state_dict_saver.py:235-346, staging.py)."""
+from typing import Protocol, Tuple, runtime_checkable
+
+
+@runtime_checkable
+class CheckpointableTensor(Protocol):
+    """A tensor subclass that tells the checkpoint where its local pieces sit in the global tensor (duck-typed:
+    anything with these four attributes is saved piece by piece and re-sharded on load)."""
+    global_shape: Tuple[int, ...]
+    global_offsets: Tuple[Tuple[int, ...], ...]
+    local_offsets: Tuple[Tuple[int, ...], ...]
+    local_sizes: Tuple[Tuple[int, ...], ...]
+
+
 from .api import (MegaStorageReader, MegaStorageWriter, ShardedTensor, Stateful, async_save, engine_state_dict, load, load_engine_state_dict, save)
 from .hf_storage import (HuggingFaceStorageReader, HuggingFaceStorageWriter, consolidate_to_hf, load_hf, save_hf)
 from .planner import DefaultLoadPlanner, DefaultSavePlanner, ReadItem, SavePlan, WriteItem

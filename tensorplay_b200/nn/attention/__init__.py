@@ -150,6 +150,13 @@ from . import bias  # noqa: E402,F401
 def __getattr__(name):
     """``flex_attention`` and the experimental sub-packages resolve to PyTorch's ``torch.nn.attention``."""
     import importlib
+    if name == "omni_attention":
+        # the reference's name of score-mod / block-mask attention: PyTorch's flex attention module, whose
+        # ``flex_attention`` function is also reachable as ``omni_attention``
+        mod = importlib.import_module("torch.nn.attention.flex_attention")
+        if not hasattr(mod, "omni_attention"):
+            mod.omni_attention = mod.flex_attention
+        return mod
     for mod in ("torch.nn.attention", "torch.nn.attention.flex_attention", "torch.nn.attention.bias"):
         try:
             return getattr(importlib.import_module(mod), name)

@@ -185,4 +185,11 @@ def __getattr__(name):
         tvo = importlib.import_module("torchvision.ops")
     except ImportError as e:
         raise AttributeError(f"tensorplay_b200.vision.ops.{name}: no kernel here and torchvision is not installed") from e
-    return getattr(tvo, name)
+    try:
+        return getattr(tvo, name)
+    except AttributeError:
+        for sub in ("poolers", "boxes", "misc", "feature_pyramid_network"):
+            m = importlib.import_module(f"torchvision.ops.{sub}")
+            if hasattr(m, name):
+                return getattr(m, name)
+        raise
