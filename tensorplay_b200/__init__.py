@@ -47,8 +47,8 @@ from .serialization import inspect_checkpoint, load, save  # noqa: E402
 from .nn.generation import sample  # noqa: E402
 
 _LAZY_OWN = {"distributed", "utils", "models", "parallel", "cuda", "profiler", "autograd", "compat",
-             "multiprocessing", "testing", "quantization", "metrics", "snn", "library", "quantum", "lumen", "vision"}
-_LAZY_TORCH = {"linalg", "fft", "special", "sparse", "distributions", "func", "futures", "hub", "onnx",
+             "multiprocessing", "testing", "quantization", "metrics", "snn", "library", "quantum", "lumen", "vision", "linalg", "sparse", "func"}
+_LAZY_TORCH = {"fft", "special", "distributions", "futures", "hub", "onnx", "ao", "mps",
                "masked", "nested", "monitor", "backends", "accelerator", "export", "fx", "random",
                "signal", "overrides", "package", "storage", "types", "jit", "_numpy"}
 
@@ -70,6 +70,8 @@ class _TorchAliasFinder:
             torch_name = ".".join(["torchvision" if parts[1] == "vision" else "torchaudio"] + parts[2:])
         elif parts[1] == "_transforms":
             torch_name = ".".join(["torch.func"] + parts[2:])
+        elif parts[1] == "graph":            # the reference's name of the graph IR package
+            torch_name = ".".join(["torch.fx"] + parts[2:])
         elif parts[1] in _LAZY_TORCH or (len(parts) >= 3 and parts[1] in self._PKGS):
             # whole packages that are PyTorch's (``linalg``, ``func``, ``fx`` ...), or a module path below
             # a thin package of this framework
@@ -123,7 +125,10 @@ class _AliasedParentFinder:
 import sys as _sys  # noqa: E402
 
 if not [f for f in _sys.meta_path if type(f).__name__ == "_TorchAliasFinder"]:
-    _sys.meta_path.append(_TorchAliasFinder())
+    # after the standard finders (own files win), before the view finders of the packs that were imported while
+    # this module was still executing (PyTorch's module of the same path wins over a view)
+    _views_at = [i for i, f in enumerate(_sys.meta_path) if type(f).__name__ == "_ViewFinder"]
+    _sys.meta_path.insert(_views_at[0] if _views_at else len(_sys.meta_path), _TorchAliasFinder())
 if not [f for f in _sys.meta_path if type(f).__name__ == "_AliasedParentFinder"]:
     _sys.meta_path.insert(0, _AliasedParentFinder())
 

@@ -6,7 +6,13 @@ from . import server  # noqa: F401
 
 def __getattr__(name):
     import importlib
-    try:
-        return getattr(importlib.import_module("torch.distributed.elastic.agent"), name)
-    except (ImportError, AttributeError):
-        raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+    if name == "LocalElasticAgent":
+        from ...run import LocalElasticAgent
+        return LocalElasticAgent
+    for mod in ("torch.distributed.elastic.agent", "torch.distributed.elastic.agent.server",
+                "torch.distributed.elastic.agent.server.api"):
+        try:
+            return getattr(importlib.import_module(mod), name)
+        except (ImportError, AttributeError):
+            continue
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -15,7 +15,3 @@ def is_available() -> bool:
 def __getattr__(name):
     raise RPCUnavailableError(f"tensorplay_b200.distributed.rpc.{name}: RPC and distributed autograd are not provided "
                        "(single-box framework); use process-group collectives or the TCP store")
-
-
-# the reference has a package at this path: sub-module names without a file here resolve to PyTorch's
-__path__: list = []

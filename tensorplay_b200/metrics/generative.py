@@ -352,3 +352,14 @@ __all__ = ["FrechetInceptionDistance", "KernelInceptionDistance", "InceptionScor
 
 # the reference has a package at this path: deeper module names resolve to views of the pack
 __path__: list = []
+
+
+def __getattr__(name):
+    """Names of this domain that live in another file of the pack (task wrappers, shared bases)."""
+    if name.startswith("__"):
+        raise AttributeError(name)
+    import importlib
+    pkg = importlib.import_module(__name__.rsplit(".", 1)[0])
+    if name in pkg.__dict__:
+        return pkg.__dict__[name]
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -18,6 +18,8 @@ from .generation import generate, sample, top_k_top_p_filtering
 from .modules import (DecoderLM, CausalEncoderDecoder, CompressedSparseAttention, CrossAttention, GatedDeltaNet, GroupedQueryAttention, KimiDeltaAttention, LayerNorm, Linear,
                       MultiheadLatentAttention, RMSNorm, RotaryEmbedding, SwiGLUMLP, TransformerBlock,
                       apply_rotary_emb, chunk_gated_delta_rule, gated_delta_rule)
+from .modules import (DepthwiseConv2d, GatedRMSNorm, chunk_kimi_delta_rule, recurrent_gated_delta_rule,  # noqa: E402
+                      recurrent_kimi_delta_rule)
 parallel = _importlib.import_module(__name__ + ".parallel")
 
 

@@ -2,12 +2,23 @@ from .llm import (GroupedQueryAttention, LayerNorm, Linear, RMSNorm, RotaryEmbed
                   TransformerBlock, apply_rotary_emb)
 
 from .lm import DecoderLM
-from .mixers import (CausalEncoderDecoder, CompressedSparseAttention, CrossAttention, GatedDeltaNet, KimiDeltaAttention, MultiheadLatentAttention, chunk_gated_delta_rule,
-                     gated_delta_rule)
+from .mixers import (CausalEncoderDecoder, CompressedSparseAttention, CrossAttention, DepthwiseConv2d, GatedDeltaNet,
+                     GatedRMSNorm, KimiDeltaAttention, MultiheadLatentAttention, chunk_gated_delta_rule,
+                     chunk_kimi_delta_rule, gated_delta_rule, recurrent_gated_delta_rule, recurrent_kimi_delta_rule)
 
 __all__ = ["GroupedQueryAttention", "LayerNorm", "Linear", "RMSNorm", "RotaryEmbedding", "SwiGLUMLP",
            "TransformerBlock", "apply_rotary_emb", "MultiheadLatentAttention", "GatedDeltaNet", "gated_delta_rule",
-           "chunk_gated_delta_rule", "KimiDeltaAttention", "CrossAttention", "CausalEncoderDecoder", "CompressedSparseAttention", "DecoderLM"]
+           "chunk_gated_delta_rule", "KimiDeltaAttention", "CrossAttention", "CausalEncoderDecoder", "CompressedSparseAttention", "DecoderLM", "GatedRMSNorm", "DepthwiseConv2d",
+           "recurrent_gated_delta_rule", "recurrent_kimi_delta_rule", "chunk_kimi_delta_rule"]
+
+def __getattr__(name):
+    """The long tail of layers (``Conv2d``, ``BatchNorm1d``, ``LSTM`` ...) is PyTorch's."""
+    import torch.nn as _nn
+    try:
+        return getattr(_nn.modules, name)
+    except AttributeError:
+        return getattr(_nn, name)
+
 
 from ... import _views as _views  # noqa: E402
 

@@ -222,6 +222,103 @@ class GatedDeltaNet(Module):
         return self.o_proj(o.reshape(B, T, H * dv).to(hidden_states.dtype))
 
 
+def _l2norm(x: Tensor) -> Tensor:
+    return F.normalize(x.float(), dim=-1)
+
+
+def recurrent_gated_delta_rule(query: Tensor, key: Tensor, value: Tensor, g: Tensor, beta: Tensor,
+                               initial_state: Optional[Tensor] = None, output_final_state: bool = False,
+                               use_qk_l2norm_in_kernel: bool = False) -> Tuple[Tensor, Optional[Tensor]]:
+    """The reference's spelling of the token-by-token gated delta rule (nn/modules/gated_delta.py:171): queries are
+    scaled by ``key_dim ** -0.5``, ``q`` / ``k`` optionally L2-normalised here, and the final state is returned only
+    on request. ``g``: ``[B, T, H]``."""
+    if use_qk_l2norm_in_kernel:
+        query, key = _l2norm(query), _l2norm(key)
+    out, state = gated_delta_rule(query.float() * key.shape[-1] ** -0.5, key, value, g, beta, initial_state)
+    return out.to(value.dtype), (state if output_final_state else None)
+
+
+def recurrent_kimi_delta_rule(query: Tensor, key: Tensor, value: Tensor, g: Tensor, beta: Tensor,
+                              initial_state: Optional[Tensor] = None, output_final_state: bool = False,
+                              use_qk_l2norm_in_kernel: bool = False) -> Tuple[Tensor, Optional[Tensor]]:
+    """Token-by-token delta rule with one decay per key channel, ``g``: ``[B, T, H, Dk]``
+    (nn/modules/kimi_delta.py:38)."""
+    if g.dim() != 4:
+        raise ValueError("recurrent_kimi_delta_rule: g must be [batch, seq, heads, key_dim]")
+    if use_qk_l2norm_in_kernel:
+        query, key = _l2norm(query), _l2norm(key)
+    out, state = gated_delta_rule(query.float() * key.shape[-1] ** -0.5, key, value, g, beta, initial_state)
+    return out.to(value.dtype), (state if output_final_state else None)
+
+
+def chunk_kimi_delta_rule(query: Tensor, key: Tensor, value: Tensor, g: Tensor, beta: Tensor, chunk_size: int = 64,
+                          initial_state: Optional[Tensor] = None, output_final_state: bool = False,
+                          use_qk_l2norm_in_kernel: bool = False) -> Tuple[Tensor, Optional[Tensor]]:
+    """Chunked form of :func:`recurrent_kimi_delta_rule` (nn/modules/kimi_delta.py:92). With a decay per key channel
+    the decay between two tokens of a chunk factorises over the channels, ``exp(G_i - G_j) = exp(G_i) * exp(-G_j)``
+    (``G``: cumulative log-decay inside the chunk), so the chunk's interaction matrices are plain products of decayed
+    keys: ``K+ = K * exp(G)``, ``K- = K * exp(-G)``, ``A = tril(beta * K+ K-^T, -1)``. ``exp(-G)`` grows with the
+    chunk length: the chunk matrices are formed in float64."""
+    if use_qk_l2norm_in_kernel:
+        query, key = _l2norm(query), _l2norm(key)
+    B, T, H, Dk = key.shape
+    Dv = value.shape[-1]
+    f64 = torch.float64
+    S = (torch.zeros(B, H, Dk, Dv, dtype=f64, device=key.device) if initial_state is None else initial_state.to(f64))
+    qf = (query.to(f64) * Dk ** -0.5).transpose(1, 2)
+    kf, vf = key.to(f64).transpose(1, 2), value.to(f64).transpose(1, 2)          # [B, H, T, D]
+    gf, bf = g.to(f64).transpose(1, 2), beta.to(f64).transpose(1, 2)              # [B, H, T, Dk], [B, H, T]
+    outs = []
+    for c0 in range(0, T, chunk_size):
+        c1 = min(c0 + chunk_size, T)
+        n = c1 - c0
+        qc, kc, vc, bc = qf[:, :, c0:c1], kf[:, :, c0:c1], vf[:, :, c0:c1], bf[:, :, c0:c1]
+        G = torch.cumsum(gf[:, :, c0:c1], dim=2)                                  # [B, H, n, Dk]
+        kp, km, qp = kc * torch.exp(G), kc * torch.exp(-G), qc * torch.exp(G)
+        A = torch.tril(torch.einsum("bhik,bhjk->bhij", kp, km) * bc.unsqueeze(-1), diagonal=-1)
+        rhs = bc.unsqueeze(-1) * (vc - torch.einsum("bhik,bhkv->bhiv", kp, S))
+        eye = torch.eye(n, dtype=f64, device=key.device).expand(B, H, n, n)
+        U = torch.linalg.solve_triangular(eye + A, rhs, upper=False)
+        qk = torch.tril(torch.einsum("bhik,bhjk->bhij", qp, km))
+        outs.append(torch.einsum("bhik,bhkv->bhiv", qp, S) + torch.einsum("bhij,bhjv->bhiv", qk, U))
+        tail = torch.exp(G[:, :, -1:] - G)                                        # decay from token j to the chunk end
+        S = torch.exp(G[:, :, -1]).unsqueeze(-1) * S + torch.einsum("bhjk,bhjv->bhkv", kc * tail, U)
+    out = torch.cat(outs, dim=2).transpose(1, 2).to(value.dtype)
+    return out, (S.float() if output_final_state else None)
+
+
+class GatedRMSNorm(Module):
+    """RMSNorm whose output is multiplied by an activated gate: ``norm(x) * weight * act(gate)``, computed in fp32
+    (nn/modules/gated_delta.py:214; ``activation``: ``"silu"`` or ``"sigmoid"``)."""
+
+    def __init__(self, dim: int, eps: float = 1e-6, activation: str = "silu", device=None, dtype=None) -> None:
+        super().__init__()
+        if activation not in ("silu", "sigmoid"):
+            raise ValueError(f"unsupported gate activation {activation!r}")
+        self.weight = torch.nn.Parameter(torch.ones(dim, device=device, dtype=dtype))
+        self.eps, self.activation = eps, activation
+
+    def forward(self, x: Tensor, gate: Tensor) -> Tensor:
+        xf = x.float()
+        y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps) * self.weight.float()
+        a = F.silu(gate.float()) if self.activation == "silu" else torch.sigmoid(gate.float())
+        return (y * a).to(x.dtype)
+
+    def extra_repr(self) -> str:
+        return f"{self.weight.numel()}, eps={self.eps}, activation={self.activation}"
+
+
+class DepthwiseConv2d(torch.nn.Conv2d):
+    """``Conv2d`` with one group per input channel (nn/modules/conv.py:292)."""
+
+    def __init__(self, in_channels, out_channels, kernel_size, stride=1, padding=0, dilation=1, bias=True,
+                 padding_mode="zeros", device=None, dtype=None):
+        if out_channels % in_channels != 0:
+            raise ValueError("out_channels must be divisible by in_channels for DepthwiseConv2d")
+        super().__init__(in_channels, out_channels, kernel_size, stride, padding, dilation, groups=in_channels,
+                         bias=bias, padding_mode=padding_mode, device=device, dtype=dtype)
+
+
 class KimiDeltaAttention(GatedDeltaNet):
     """Gated delta rule with the decay resolved per key channel: the forget gate comes from a
     low-rank projection and has shape ``[B, T, H, Dk]``, so that different key coordinates keep

@@ -13,7 +13,22 @@ def __getattr__(name):
     try:
         return getattr(tv, name)
     except AttributeError:
+        pass
+    # helpers that the reference lists at the top of the pack: image grids and saving, tensor conversion
+    for mod in ("torchvision.utils", "torchvision.transforms.functional", "torchvision.io"):
+        m = importlib.import_module(mod)
+        if hasattr(m, name):
+            return getattr(m, name)
+    aliases = {"from_image": ("torchvision.transforms.functional", "pil_to_tensor"),
+               "from_file": ("torchvision.io", "read_image"),
+               "set_backend": ("torchvision", "set_image_backend"), "get_backend": ("torchvision", "get_image_backend")}
+    if name in aliases:
+        mod, attr = aliases[name]
+        return getattr(importlib.import_module(mod), attr)
+    try:
         return importlib.import_module(f"torchvision.{name}")
+    except ImportError:
+        raise AttributeError(f"tensorplay_b200.vision has no attribute {name!r}") from None
 
 from .. import _views as _views  # noqa: E402
 

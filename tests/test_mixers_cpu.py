@@ -127,3 +127,31 @@ def test_compressed_sparse_attention_causality_and_tiers():
     assert (m(x3)[:, 23] - y[:, 23]).abs().max() > 1e-6
     y.pow(2).mean().backward()
     assert m.sinks.grad is not None and m.compress_gate.weight.grad is not None
+
+
+def test_reference_spellings_of_the_delta_rules_and_gated_norm():
+    """Per-channel decay: the chunked form (factorised decay, float64 chunk matrices) equals the token-by-token form,
+    with an initial state and over a ragged last chunk; the head-scalar recurrent spelling equals the chunked one."""
+    import torch
+    from tensorplay_b200 import nn
+    torch.manual_seed(0)
+    B, T, H, Dk, Dv = 2, 150, 3, 16, 8
+    q, k, v = torch.randn(B, T, H, Dk), torch.randn(B, T, H, Dk), torch.randn(B, T, H, Dv)
+    beta, s0 = torch.rand(B, T, H), torch.randn(B, H, Dk, Dv) * 0.1
+    g = -torch.rand(B, T, H, Dk) * 0.3
+    o1, s1 = nn.recurrent_kimi_delta_rule(q, k, v, g, beta, s0, True, True)
+    o2, s2 = nn.chunk_kimi_delta_rule(q, k, v, g, beta, 64, s0, True, True)
+    assert (o1 - o2).abs().max() < 1e-5 and (s1 - s2).abs().max() < 1e-5
+    assert nn.chunk_kimi_delta_rule(q, k, v, g, beta)[1] is None
+    gs = -torch.rand(B, T, H) * 0.3
+    o3, s3 = nn.recurrent_gated_delta_rule(q, k, v, gs, beta, None, True, True)
+    kn = torch.nn.functional.normalize(k, dim=-1)
+    qn = torch.nn.functional.normalize(q, dim=-1) * Dk ** -0.5
+    o4, s4 = nn.chunk_gated_delta_rule(qn, kn, v, gs, beta)
+    assert (o3 - o4).abs().max() < 1e-5 and (s3 - s4).abs().max() < 1e-5
+    norm = nn.GatedRMSNorm(8, activation="sigmoid")
+    x, gate = torch.randn(4, 8), torch.randn(4, 8)
+    want = torch.nn.functional.rms_norm(x, (8,), eps=1e-6) * torch.sigmoid(gate)
+    assert torch.allclose(norm(x, gate), want, atol=1e-6)
+    conv = nn.DepthwiseConv2d(4, 8, 3, padding=1)
+    assert conv.groups == 4 and conv(torch.randn(1, 4, 9, 9)).shape == (1, 8, 9, 9)

@@ -60,3 +60,34 @@ def test_alias_spelling_reaches_the_same_objects():
     from tensorplay_b200.distributed.elastic.multiprocessing import record as r0
     from tensorplay_b200.vision.ops import nms as n0
     assert record is r0 and MeanSquaredError is M.MeanSquaredError and nms is n0
+
+
+def test_linalg_sparse_func_additions():
+    import torch
+    import tensorplay_b200 as tp
+    torch.manual_seed(0)
+    A = torch.randn(6, 4, dtype=torch.float64)
+    U, P = tp.linalg.polar(A)
+    assert torch.allclose(U @ P, A) and torch.allclose(U.mH @ U, torch.eye(4, dtype=torch.float64))
+    assert torch.allclose(P, P.mH) and torch.linalg.eigvalsh(P).min() > -1e-12
+    U2, P2 = tp.linalg.polar(A.T, side="left")
+    assert torch.allclose(P2 @ U2, A.T)
+    S = A.T @ A
+    R = tp.linalg.matrix_sqrth(S)
+    assert torch.allclose(R @ R, S) and torch.allclose(R, R.mH)
+    z = torch.randn(5, dtype=torch.complex128)
+    assert torch.allclose(tp.linalg.vdot(z, z), (z.conj() * z).sum()) and tp.linalg.svd is torch.linalg.svd
+    sp = torch.tensor([[4.0, 1.0], [1.0, 3.0]]).to_sparse()
+    b = torch.tensor([1.0, 2.0])
+    assert torch.allclose(sp.to_dense() @ tp.sparse.solve(sp, b), b)
+    assert tp.sparse.sparse_coo_tensor is torch.sparse_coo_tensor and tp.sparse.to_dense(sp).shape == (2, 2)
+    x = torch.randn(7, 4)
+    assert torch.allclose(tp.func.chunk_vmap(lambda r: r.sin().sum(), chunks=3)(x), x.sin().sum(1))
+    assert tp.func.rearrange(torch.arange(6).view(2, 3), "a b -> b a").shape == (3, 2)
+    net = torch.nn.Sequential(torch.nn.Linear(3, 3), torch.nn.BatchNorm1d(3))
+    tp.func.batch_norm_without_running_stats(net)
+    assert net[1].running_mean is None and not net[1].track_running_stats
+    import tensorplay_b200.graph.passes as gp
+    assert gp is importlib.import_module("torch.fx.passes")
+    from tensorplay_b200.nn.modules import BatchNorm2d, GatedDeltaNet  # PyTorch's long tail next to own layers
+    assert BatchNorm2d is torch.nn.BatchNorm2d and GatedDeltaNet.__module__.startswith("tensorplay_b200")
