@@ -35,6 +35,10 @@ from .inputs import (MSE, Count, ImageMaskInput, InterpretableEmbeddingBase, Int
                      StatValue, StdDev, Sum, SummarizerSingleTensor, TextTemplateInput, TextTokenInput, TokenReferenceBase, Var,
                      VLLMProvider, configure_interpretable_embedding_layer, remove_interpretable_embedding_layer)
 
+from . import concept  # noqa: E402
+from .concept import CAV, TCAV, Classifier, Concept, ConceptInterpreter, DefaultClassifier  # noqa: E402
+from .llm import (ActivationPatching, LogitLens, SparseAutoencoder, collect_hidden_states, extract_attention,  # noqa: E402
+                  feature_frequency, reconstruction_error, token_attention, top_activating_indices, train_sae)
 from .. import _views as _views  # noqa: E402
 
 _views.install(__name__, max_depth=3)

@@ -90,5 +90,155 @@ class LLMGradientAttribution:
         return {"token_attr": scores, "log_prob": sel.detach(), "seq_attr": scores[:, :P]}
 
 
+# ------------------------------------------------------------------------------------------- class spellings
+class LogitLens:
+    """Object form of :func:`logit_lens` (lumen/llm/logit_lens.py): ``LogitLens(model).attribute(tokens)`` returns the
+    per-layer logits, ``top_tokens`` the ``k`` most likely next tokens per layer at one position."""
+
+    def __init__(self, model: nn.Module, layers: Optional[Sequence[nn.Module]] = None,
+                 head: Optional[Callable[[Tensor], Tensor]] = None):
+        self.model, self.layers, self.head = model, layers, head
+
+    def attribute(self, tokens: Tensor) -> Tensor:
+        return logit_lens(self.model, tokens, self.layers, self.head)
+
+    def top_tokens(self, tokens: Tensor, position: int = -1, k: int = 5) -> Tensor:
+        return self.attribute(tokens)[:, :, position].topk(k, dim=-1).indices
+
+
+class ActivationPatching:
+    """Object form of :func:`activation_patching` (lumen/llm/patching.py)."""
+
+    def __init__(self, model: nn.Module, layers: Optional[Sequence[nn.Module]] = None):
+        self.model, self.layers = model, layers
+
+    def attribute(self, clean_tokens: Tensor, corrupt_tokens: Tensor, metric: Callable[[Tensor], Tensor],
+                  positions: Optional[Sequence[int]] = None) -> Tensor:
+        return activation_patching(self.model, clean_tokens, corrupt_tokens, metric, self.layers, positions)
+
+
+def collect_hidden_states(model: nn.Module, tokens: Tensor, layers: Optional[Sequence[nn.Module]] = None) -> List[Tensor]:
+    """Residual stream after every block, ``[B, T, H]`` each (the training set of a sparse autoencoder)."""
+    layers = list(model.layers) if layers is None else list(layers)
+    with torch.no_grad():
+        _, acts = _block_outputs(model, layers, lambda: model(tokens))
+    return acts
+
+
+def extract_attention(model: nn.Module, tokens: Tensor, attention_modules: Optional[Sequence[nn.Module]] = None) -> List[Tensor]:
+    """Attention probabilities ``[B, heads, T, T]`` of every attention module, recomputed from the module's query and
+    key projections as the causal softmax of ``q k^T / sqrt(d)`` (the fused kernels never materialise them). A module
+    takes part if it exposes ``last_qk`` after a forward pass, or returns ``(output, probabilities)``."""
+    mods = list(attention_modules) if attention_modules is not None else [
+        m for m in model.modules() if hasattr(m, "last_qk") or getattr(m, "returns_attention", False)]
+    got: List[Tensor] = []
+    hooks = []
+    for m in mods:
+        def hook(mod, i, o):
+            if isinstance(o, tuple) and len(o) > 1 and isinstance(o[1], Tensor) and o[1].dim() == 4:
+                got.append(o[1].detach())
+            elif getattr(mod, "last_qk", None) is not None:
+                q, k = mod.last_qk                                        # [B, heads, T, d]
+                s = (q.float() @ k.float().transpose(-1, -2)) / q.shape[-1] ** 0.5
+                T = s.shape[-1]
+                s = s.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool, device=s.device), 1), float("-inf"))
+                got.append(torch.softmax(s, dim=-1))
+        hooks.append(m.register_forward_hook(hook))
+    try:
+        with torch.no_grad():
+            model(tokens)
+    finally:
+        for h in hooks:
+            h.remove()
+    return got
+
+
+def token_attention(attentions: Sequence[Tensor], query_position: int = -1, layer: Optional[int] = None,
+                    head: Optional[int] = None) -> Tensor:
+    """How much the token at ``query_position`` attends to every earlier token: ``[B, T]``, averaged over the layers and
+    heads that are not fixed."""
+    maps = [attentions[layer]] if layer is not None else list(attentions)
+    rows = []
+    for a in maps:
+        a = a[:, head: head + 1] if head is not None else a
+        rows.append(a[:, :, query_position].mean(1))
+    return torch.stack(rows).mean(0)
+
+
+class SparseAutoencoder(nn.Module):
+    """Overcomplete dictionary of a hidden-state distribution (lumen/llm/sae.py): ``f = relu(W_e (x - b_d) + b_e)``,
+    ``x_hat = W_d f + b_d``, decoder columns of unit norm, trained on reconstruction error plus an L1 penalty on ``f``."""
+
+    def __init__(self, d_model: int, d_dict: int, l1_coeff: float = 1e-3):
+        super().__init__()
+        self.d_model, self.d_dict, self.l1_coeff = d_model, d_dict, l1_coeff
+        self.encoder = nn.Linear(d_model, d_dict)
+        self.decoder = nn.Linear(d_dict, d_model)
+        with torch.no_grad():
+            self.decoder.weight.copy_(torch.nn.functional.normalize(self.decoder.weight, dim=0))
+            self.encoder.weight.copy_(self.decoder.weight.t())
+            self.encoder.bias.zero_()
+            self.decoder.bias.zero_()
+
+    def encode(self, x: Tensor) -> Tensor:
+        return torch.relu(self.encoder(x - self.decoder.bias))
+
+    def decode(self, f: Tensor) -> Tensor:
+        return self.decoder(f)
+
+    def forward(self, x: Tensor):
+        f = self.encode(x)
+        return self.decode(f), f
+
+    def loss(self, x: Tensor) -> Tensor:
+        x_hat, f = self(x)
+        return (x_hat - x).pow(2).sum(-1).mean() + self.l1_coeff * f.abs().sum(-1).mean()
+
+    @torch.no_grad()
+    def normalize_decoder(self) -> None:
+        self.decoder.weight.copy_(torch.nn.functional.normalize(self.decoder.weight, dim=0))
+
+
+def train_sae(sae: SparseAutoencoder, activations: Tensor, steps: int = 200, batch_size: int = 256, lr: float = 1e-3,
+              seed: int = 0) -> List[float]:
+    """Adam on random batches of ``activations`` ``[N, d_model]``; the decoder columns are renormalised after every
+    step. Returns the loss curve."""
+    x = activations.reshape(-1, activations.shape[-1]).float()
+    opt = torch.optim.Adam(sae.parameters(), lr=lr)
+    g = torch.Generator().manual_seed(seed)
+    curve = []
+    for _ in range(steps):
+        idx = torch.randint(0, x.shape[0], (min(batch_size, x.shape[0]),), generator=g)
+        loss = sae.loss(x[idx.to(x.device)])
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        sae.normalize_decoder()
+        curve.append(float(loss.detach()))
+    return curve
+
+
+@torch.no_grad()
+def feature_frequency(sae: SparseAutoencoder, activations: Tensor, threshold: float = 0.0) -> Tensor:
+    """Share of the inputs on which each dictionary feature fires: ``[d_dict]``."""
+    f = sae.encode(activations.reshape(-1, activations.shape[-1]).float())
+    return (f > threshold).float().mean(0)
+
+
+@torch.no_grad()
+def top_activating_indices(sae: SparseAutoencoder, activations: Tensor, feature: int, k: int = 10) -> Tensor:
+    """Indices (into the flattened inputs) of the ``k`` inputs on which ``feature`` is largest."""
+    f = sae.encode(activations.reshape(-1, activations.shape[-1]).float())[:, feature]
+    return f.topk(min(k, f.numel())).indices
+
+
+@torch.no_grad()
+def reconstruction_error(sae: SparseAutoencoder, activations: Tensor) -> Tensor:
+    """Fraction of the variance of ``activations`` that the reconstruction misses."""
+    x = activations.reshape(-1, activations.shape[-1]).float()
+    x_hat, _ = sae(x)
+    return (x_hat - x).pow(2).sum() / (x - x.mean(0, keepdim=True)).pow(2).sum().clamp_min(1e-12)
+
+
 # the reference has a package at this path: deeper module names resolve to views of the pack
 __path__: list = []

@@ -203,3 +203,86 @@ def test_combined_layer_and_neuron_variants():
     cs = lumen.ClassSummarizer(["mean"])
     cs.update(data, torch.arange(50) % 2)
     torch.testing.assert_close(cs.class_summaries[1]["mean"].float(), data[1::2].mean(0), rtol=1e-5, atol=1e-6)
+
+
+def test_tcav_finds_the_direction_a_model_uses():
+    """A model whose output is driven by one hidden direction: the concept whose examples move the hidden state along
+    that direction gets a TCAV score near 1, its opposite near 0, and the classifier separates the two."""
+    import torch
+    from torch import nn
+    from tensorplay_b200.lumen import TCAV, Concept
+    torch.manual_seed(0)
+    d = 12
+    body = nn.Linear(d, d, bias=False)
+    with torch.no_grad():
+        body.weight.copy_(torch.eye(d))
+    direction = torch.zeros(d)
+    direction[3] = 1.0
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.body = body
+
+        def forward(self, x):
+            h = self.body(x)
+            return torch.stack((h @ direction, -(h @ direction)), dim=1)
+
+    net = Net()
+    plus = Concept(0, "along", [torch.randn(64, d) + 3 * direction for _ in range(2)])
+    rand = Concept(1, "random", [torch.randn(64, d) for _ in range(2)])
+    tcav = TCAV(net, "body")
+    scores = tcav.interpret(torch.randn(40, d), [[plus, rand]], target=0)
+    s = scores["0-1"]["body"]
+    assert s["sign_count"][0] > 0.95 and s["sign_count"][1] < 0.05 and s["magnitude"][0] > 0.95
+    cav = tcav.cavs["0-1"]["body"]
+    assert float(cav.stats["accs"]) > 0.9
+    v = cav.vector(plus)
+    assert v[3] / v.norm() > 0.9                     # the learnt vector points along the planted direction
+    # target 1 is the negated read-out: the scores swap
+    s1 = tcav.interpret(torch.randn(40, d), [[plus, rand]], target=1)["0-1"]["body"]
+    assert s1["sign_count"][0] < 0.05
+
+
+def test_sparse_autoencoder_recovers_a_planted_dictionary():
+    import torch
+    from tensorplay_b200.lumen import (SparseAutoencoder, feature_frequency, reconstruction_error,
+                                       top_activating_indices, train_sae)
+    torch.manual_seed(0)
+    d, k, n = 16, 6, 4096
+    atoms = torch.nn.functional.normalize(torch.randn(k, d), dim=1)
+    codes = (torch.rand(n, k) < 0.15).float() * (torch.rand(n, k) + 0.5)
+    x = codes @ atoms
+    sae = SparseAutoencoder(d, 24, l1_coeff=3e-2)
+    before = float(reconstruction_error(sae, x))
+    curve = train_sae(sae, x, steps=1500, batch_size=512, lr=3e-3)
+    after = float(reconstruction_error(sae, x))
+    assert curve[-1] < curve[0] and after < 0.1 < before
+    # every planted atom has a dictionary column pointing its way
+    cols = torch.nn.functional.normalize(sae.decoder.weight.t(), dim=1)            # [dict, d]
+    assert (atoms @ cols.t()).max(dim=1).values.min() > 0.9
+    freq = feature_frequency(sae, x)
+    assert freq.shape == (24,) and 0 < freq.max() < 0.6
+    best = int(freq.argmax())
+    top = top_activating_indices(sae, x, best, k=5)
+    assert sae.encode(x[top])[:, best].min() >= sae.encode(x)[:, best].median()
+
+
+def test_llm_wrappers_and_attention_helpers():
+    import torch
+    from tensorplay_b200.lumen import LogitLens, collect_hidden_states, token_attention
+    from tensorplay_b200.models.llama import Llama, LlamaConfig
+    torch.manual_seed(0)
+    cfg = LlamaConfig.tiny(max_seq_len=16)
+    model = Llama(cfg)
+    model.reset_parameters(0)
+    toks = torch.randint(0, cfg.vocab_size, (2, 8))
+    lens = LogitLens(model)
+    out = lens.attribute(toks)
+    assert out.shape[:3] == (cfg.num_layers, 2, 8) and lens.top_tokens(toks, k=3).shape == (cfg.num_layers, 2, 3)
+    hs = collect_hidden_states(model, toks)
+    assert len(hs) == cfg.num_layers and hs[0].shape == (2, 8, cfg.hidden_size)
+    att = [torch.softmax(torch.randn(2, 4, 8, 8), -1) for _ in range(3)]
+    ta = token_attention(att, query_position=-1)
+    assert ta.shape == (2, 8) and torch.allclose(ta.sum(-1), torch.ones(2), atol=1e-5)
+    assert torch.allclose(token_attention(att, -1, layer=1, head=2), att[1][:, 2, -1])
