@@ -47,7 +47,7 @@ from .serialization import inspect_checkpoint, load, save  # noqa: E402
 from .nn.generation import sample  # noqa: E402
 
 _LAZY_OWN = {"distributed", "utils", "models", "parallel", "cuda", "profiler", "autograd", "compat",
-             "multiprocessing", "testing", "quantization", "metrics", "snn", "library", "quantum", "lumen", "vision", "linalg", "sparse", "func"}
+             "multiprocessing", "testing", "quantization", "metrics", "snn", "library", "quantum", "lumen", "vision", "linalg", "sparse", "func", "audio"}
 _LAZY_TORCH = {"fft", "special", "distributions", "futures", "hub", "onnx", "ao", "mps",
                "masked", "nested", "monitor", "backends", "accelerator", "export", "fx", "random",
                "signal", "overrides", "package", "storage", "types", "jit", "_numpy"}
@@ -66,7 +66,7 @@ class _TorchAliasFinder:
         if len(parts) < 2 or parts[0] != __name__:
             return None
         import importlib.util
-        if parts[1] in ("vision", "audio"):
+        if parts[1] in ("vision", "audio"):       # sub-modules without a file here: torchvision / torchaudio
             torch_name = ".".join(["torchvision" if parts[1] == "vision" else "torchaudio"] + parts[2:])
         elif parts[1] == "_transforms":
             torch_name = ".".join(["torch.func"] + parts[2:])
@@ -140,11 +140,6 @@ def __getattr__(name):
         return mod
     if name in _LAZY_TORCH:
         mod = _importlib.import_module(f"torch.{name}")
-        globals()[name] = mod
-        return mod
-    if name == "audio":
-        # the audio pack resolves to torchaudio when it is installed
-        mod = _importlib.import_module("torchaudio")
         globals()[name] = mod
         return mod
     if name == "graph":
