@@ -1,7 +1,7 @@
 """``vision``: the detection operators with kernels of this framework (``vision.ops``: ``nms``, ``batched_nms``,
 ``box_iou``, ``box_area``, ``roi_align`` / ``RoIAlign``); models, transforms, datasets, io and the remaining operators
 resolve to torchvision when it is installed (tensorplay/vision/**)."""
-from . import ops  # noqa: F401
+from . import io, ops  # noqa: F401
 
 
 def __getattr__(name):

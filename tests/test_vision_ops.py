@@ -64,3 +64,12 @@ def test_roi_align_kernels_match_reference(dtype, aligned, sampling_ratio):
     tol = 1e-5 if dtype == torch.float32 else 3e-2
     assert (y.float().cpu() - yr).abs().max() < tol * max(1.0, yr.abs().max().item())
     assert (gx.float().cpu() - gr).abs().max() < tol * max(1.0, gr.abs().max().item())
+
+
+def test_batch_image_codecs_round_trip():
+    from tensorplay_b200.vision import io as vio
+    ims = [torch.randint(0, 255, (3, 32 + i, 40), dtype=torch.uint8) for i in range(5)]
+    back = vio.decode_png_batch(vio.encode_png_batch(ims))
+    assert all(torch.equal(a, b) for a, b in zip(ims, back))                       # PNG is lossless, order kept
+    jp = vio.decode_jpeg_batch(vio.encode_jpeg_batch(ims, quality=95))
+    assert [tuple(t.shape) for t in jp] == [tuple(t.shape) for t in ims]
