@@ -49,8 +49,9 @@ class _ViewFinder:
     that cannot be module names of the reference are refused: anything with an upper-case letter, and anything
     deeper below the pack than its module tree goes (one level more below ``functional``)."""
 
-    def __init__(self, package: str, max_depth: int, namespace: str):
+    def __init__(self, package: str, max_depth: int, namespace: str, names=None):
         self.package, self.max_depth, self.namespace = package, max_depth, namespace
+        self.names = None if names is None else frozenset(names)
 
     def find_spec(self, fullname, path=None, target=None):
         if not fullname.startswith(self.package + "."):
@@ -59,12 +60,16 @@ class _ViewFinder:
         depth = len(parts) - (1 if parts[0] == "functional" else 0)
         if depth > self.max_depth or any(c.isupper() for c in parts[-1]):
             return None
+        if self.names is not None and parts[0] not in self.names:
+            return None
         return importlib.util.spec_from_loader(fullname, _ViewLoader(self.package, self.namespace))
 
 
-def install(package: str, max_depth: int = 3, namespace: str = "") -> None:
+def install(package: str, max_depth: int = 3, namespace: str = "", names=None) -> None:
     """Appended to ``sys.meta_path``: real files of the pack are found first (and PyTorch's module of the same path
     where the package falls back to PyTorch). ``max_depth``: levels of module names below the pack in the reference's
-    tree; ``namespace``: the module whose attributes the views show (default: the package itself)."""
+    tree; ``namespace``: the module whose attributes the views show (default: the package itself); ``names``: the only
+    first-level module names that get a view (a package outside the domain packs lists them, so that a misspelt module
+    name still raises ``ModuleNotFoundError``)."""
     if not [f for f in sys.meta_path if isinstance(f, _ViewFinder) and f.package == package]:
-        sys.meta_path.append(_ViewFinder(package, max_depth, namespace or package))
+        sys.meta_path.append(_ViewFinder(package, max_depth, namespace or package, names))

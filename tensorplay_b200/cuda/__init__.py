@@ -76,4 +76,5 @@ def __getattr__(name):  # noqa: F811
 
 from .. import _views as _views  # noqa: E402
 
-_views.install(__name__, max_depth=1)
+_views.install(__name__, max_depth=1,
+               names=("graph_annotations",))

@@ -5,4 +5,5 @@ from torch.multiprocessing import ProcessContext, get_context, spawn, start_proc
 
 from .. import _views as _views  # noqa: E402
 
-_views.install(__name__, max_depth=1)
+_views.install(__name__, max_depth=1,
+               names=("_fdsharer",))

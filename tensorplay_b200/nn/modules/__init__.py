@@ -23,4 +23,6 @@ def __getattr__(name):
 from ... import _views as _views  # noqa: E402
 
 # the reference's one-class-per-file module names (nn.modules.gated_delta, .rotary, .modern_block ...)
-_views.install(__name__, max_depth=1, namespace=__name__.rsplit(".", 1)[0])
+_views.install(__name__, max_depth=1, namespace=__name__.rsplit(".", 1)[0],
+               names=("latent_attention", "multihead_attention", "kimi_delta", "compressed_attention", "gated_delta",
+                      "causal_attention", "causal_encoder_decoder", "folding", "modern_block", "rotary"))

@@ -49,4 +49,5 @@ def swap_in_optimizer_params_and_state(optimizer, swapin_parameters, swapin_opti
 
 from .. import _views as _views  # noqa: E402
 
-_views.install(__name__, max_depth=1)
+_views.install(__name__, max_depth=1,
+               names=("_stateless", "_utils", "adafactor"))

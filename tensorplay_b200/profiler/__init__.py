@@ -91,4 +91,5 @@ def __getattr__(name):
 
 from .. import _views as _views  # noqa: E402
 
-_views.install(__name__, max_depth=1)
+_views.install(__name__, max_depth=1,
+               names=("_chrome_trace_export", "_schedule", "profiler_util"))

@@ -6,4 +6,5 @@ from . import checkpoint, data  # noqa: F401
 
 from .. import _views as _views  # noqa: E402
 
-_views.install(__name__, max_depth=1)
+_views.install(__name__, max_depth=1,
+               names=("_dispatch",))
