@@ -20,3 +20,12 @@ def noop_hook(_state, bucket):
 from . import debugging_hooks, default_hooks, post_localSGD_hook, powerSGD_hook, quantization_hooks  # noqa: E402,F401
 
 post_localSGD, powerSGD = post_localSGD_hook, powerSGD_hook
+
+
+
+def __getattr__(name):
+    """``ddp_zero_hook``, ``optimizer_overlap_hooks``, ``mixed_precision_hooks``: PyTorch's modules (they act on PyTorch's DDP)."""
+    if name in ("ddp_zero_hook", "optimizer_overlap_hooks", "mixed_precision_hooks"):
+        import importlib
+        return importlib.import_module(f"torch.distributed.algorithms.ddp_comm_hooks.{name}")
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -6,6 +6,9 @@ __all__ = ["HealthCheckServer", "create_healthcheck_server"]
 
 def __getattr__(name):
     import importlib
+    if name == "LocalElasticAgent":
+        from ....run import LocalElasticAgent
+        return LocalElasticAgent
     for mod in ("torch.distributed.elastic.agent.server", "torch.distributed.elastic.agent.server.api"):
         try:
             return getattr(importlib.import_module(mod), name)

@@ -7,7 +7,13 @@ __all__ = ["FileTimerClient", "FileTimerRequest", "FileTimerServer", "configure"
 
 def __getattr__(name):
     import importlib
-    try:
-        return getattr(importlib.import_module("torch.distributed.elastic.timer"), name)
-    except (ImportError, AttributeError):
-        raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+    for mod in ("torch.distributed.elastic.timer", "torch.distributed.elastic.timer.api",
+                "torch.distributed.elastic.timer.local_timer", "torch.distributed.elastic.timer.file_based_local_timer"):
+        try:
+            return getattr(importlib.import_module(mod), name)
+        except (ImportError, AttributeError):
+            continue
+    if name == "FileTimerRequestQueue":          # the file-based server reads its pipe itself: the queue is its private part
+        from .file_based_local_timer import FileTimerServer
+        return FileTimerServer
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

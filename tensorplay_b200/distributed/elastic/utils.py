@@ -10,6 +10,17 @@ from datetime import timedelta
 from typing import Iterable, List, Optional, Union
 
 
+def get_logger(name=None):
+    """Logger named after the calling module (or ``name``), at the level in ``LOGLEVEL`` (default WARNING)."""
+    import logging
+    import sys as _sys
+    if name is None:
+        name = _sys._getframe(1).f_globals.get("__name__", "tensorplay_b200.distributed.elastic")
+    log = logging.getLogger(name)
+    log.setLevel(os.environ.get("LOGLEVEL", "WARNING"))
+    return log
+
+
 def get_env_variable_or_raise(env_name: str) -> str:
     value = os.environ.get(env_name)
     if value is None:
