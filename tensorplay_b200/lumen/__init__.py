@@ -35,10 +35,35 @@ from .inputs import (MSE, Count, ImageMaskInput, InterpretableEmbeddingBase, Int
                      StatValue, StdDev, Sum, SummarizerSingleTensor, TextTemplateInput, TextTokenInput, TokenReferenceBase, Var,
                      VLLMProvider, configure_interpretable_embedding_layer, remove_interpretable_embedding_layer)
 
-from . import concept  # noqa: E402
+from . import concept, models  # noqa: E402
+from .models import (LinearModel, Model, SGDLasso, SGDLinearModel, SGDLinearRegression, SGDRidge, SkLearnLasso,  # noqa: E402
+                     SkLearnLinearModel, SkLearnLinearRegression, SkLearnRidge)
+_models = models   # the reference's private package name
 from .concept import CAV, TCAV, Classifier, Concept, ConceptInterpreter, DefaultClassifier  # noqa: E402
 from .llm import (ActivationPatching, LogitLens, SparseAutoencoder, collect_hidden_states, extract_attention,  # noqa: E402
                   feature_frequency, reconstruction_error, token_attention, top_activating_indices, train_sae)
+
+
+def compute_gradients(forward_fn, inputs, target_ind=None, additional_forward_args=None):
+    """Gradients of ``forward_fn(*inputs, *additional_forward_args)`` (its ``target_ind`` column when given, summed over
+    the batch) with respect to every tensor of ``inputs``: the primitive the gradient methods share
+    (lumen/_utils/gradient.py in the reference)."""
+    import torch as _torch
+    single = isinstance(inputs, _torch.Tensor)
+    ins = (inputs,) if single else tuple(inputs)
+    extra = () if additional_forward_args is None else (additional_forward_args if isinstance(additional_forward_args, tuple)
+                                                         else (additional_forward_args,))
+    with _torch.enable_grad():
+        ins = tuple(i if i.requires_grad else i.detach().requires_grad_(True) for i in ins)
+        out = forward_fn(*ins, *extra)
+        if target_ind is not None:
+            out = out[:, target_ind] if isinstance(target_ind, int) else out.gather(1, _torch.as_tensor(target_ind).view(-1, 1))[:, 0]
+        grads = _torch.autograd.grad(out.sum(), ins)
+    return grads[0] if single else grads
+
+
+InternalAttribution = LayerAttribution   # base of the layer- and neuron-level methods
+
 from .. import _views as _views  # noqa: E402
 
 _views.install(__name__, max_depth=3)

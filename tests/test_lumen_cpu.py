@@ -286,3 +286,35 @@ def test_llm_wrappers_and_attention_helpers():
     ta = token_attention(att, query_position=-1)
     assert ta.shape == (2, 8) and torch.allclose(ta.sum(-1), torch.ones(2), atol=1e-5)
     assert torch.allclose(token_attention(att, -1, layer=1, head=2), att[1][:, 2, -1])
+
+
+def test_surrogate_linear_models_recover_planted_weights():
+    import torch
+    from tensorplay_b200 import lumen as L
+    torch.manual_seed(0)
+    n, d = 512, 6
+    x = torch.randn(n, d)
+    w_true = torch.tensor([2.0, -1.0, 0.0, 0.0, 0.5, 0.0])
+    y = x @ w_true + 0.3
+    loader = [(x[i: i + 128], y[i: i + 128], torch.ones(128)) for i in range(0, n, 128)]
+    for cls, kw, tol in ((L.SkLearnLinearRegression, {}, 1e-4), (L.SkLearnRidge, {"alpha": 1e-3}, 1e-3),
+                         (L.SkLearnLasso, {"alpha": 1e-3}, 2e-2)):
+        m = cls(**kw)
+        stats = m.fit(loader)
+        assert (m.representation()[0] - w_true).abs().max() < tol and abs(float(m.bias()) - 0.3) < tol and stats["train_loss"] < 1e-3
+    m = L.SGDLinearRegression()
+    m.fit(loader, max_epoch=300, initial_lr=0.05)
+    assert (m.representation()[0] - w_true).abs().max() < 0.05
+    lasso = L.SGDLasso()
+    lasso.fit(loader, max_epoch=300, initial_lr=0.05, alpha=0.05)
+    rep = lasso.representation()[0]
+    assert rep[[2, 3, 5]].abs().max() < 0.05 < rep[[0, 1, 4]].abs().min()          # the penalty zeroes the unused features
+    # sample weights: rows with weight zero do not count
+    y_bad = y.clone()
+    y_bad[:256] += 100.0
+    wts = torch.cat((torch.zeros(256), torch.ones(256)))
+    m = L.SkLearnLinearRegression()
+    m.fit([(x, y_bad, wts)])
+    assert (m.representation()[0] - w_true).abs().max() < 1e-3
+    g = L.compute_gradients(lambda a: (a * a).sum(1, keepdim=True), x[:4], target_ind=0)
+    assert torch.allclose(g, 2 * x[:4])
