@@ -70,6 +70,10 @@ def cases():
     q = torch.randn(4, 4096, 32, 128, device=DEV, dtype=BF)
     cos, sin = O.rope_tables(4096, 128, theta=500000.0, device=DEV)
     out.append(("rope_inplace", lambda: O.apply_rope(q, cos, sin, inplace=True), 2 * q.numel() * 2))
+    # the training path: q and k heads rotated out of the packed QKV projection into a fresh buffer
+    packed = torch.randn(4, 4096, 48, 128, device=DEV, dtype=BF)
+    qk_src = packed[:, :, :40]
+    out.append(("rope_from_packed_qkv", lambda: O.apply_rope(qk_src, cos, sin), 2 * qk_src.numel() * 2))
 
     # ---- SwiGLU / GELU
     rows = 16384

@@ -416,9 +416,15 @@ __global__ void rope_kernel(const __nv_bfloat16* x, __nv_bfloat16* y, const floa
     float af[8], bf[8], oa[8], ob[8];
     unpack8(a, af);
     unpack8(b, bf);
+    // cos / sin of this thread's eight pairs as four 16-byte loads (half is a multiple of 8 floats, the tables
+    // are 16-byte aligned rows)
+    const float4 c0 = __ldg(reinterpret_cast<const float4*>(c + v * 8)), c1 = __ldg(reinterpret_cast<const float4*>(c + v * 8) + 1);
+    const float4 s0 = __ldg(reinterpret_cast<const float4*>(s + v * 8)), s1 = __ldg(reinterpret_cast<const float4*>(s + v * 8) + 1);
+    const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sn8[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      float cc = c[v * 8 + j], sn = sign * s[v * 8 + j];
+      const float cc = cs[j], sn = sign * sn8[j];
       oa[j] = af[j] * cc - bf[j] * sn;
       ob[j] = bf[j] * cc + af[j] * sn;
     }
@@ -775,7 +781,9 @@ extern "C" int tpb_rope_out(const void* x, void* y, const float* cos_t, const fl
                             void* stream) {
   TPB_NVTX("tpb_rope_out");
   if (D % 16 || tok_stride % 8 || head_stride % 8 || y_tok_stride % 8 || y_head_stride % 8) return -2;
-  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) return -2;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(cos_t) |
+       reinterpret_cast<uintptr_t>(sin_t)) & 15)
+    return -2;
   long long total = tokens * heads * (D / 16);
   if (total <= 0) return 0;
   int grid = (int)((total + 255) / 256);
