@@ -53,6 +53,9 @@ _LAZY_TORCH = {"fft", "special", "distributions", "futures", "hub", "onnx", "ao"
                "signal", "overrides", "package", "storage", "types", "jit", "_numpy"}
 
 
+_FALLBACK = ("export", "graph", "accelerator", "mps", "monitor", "package")
+
+
 class _TorchAliasFinder:
     """Import fallback for the thin packages: ``tensorplay_b200.<pkg>.<module>`` that is not a file of
     this framework resolves to ``torch.<pkg>.<module>`` (e.g. ``optim.adam``, ``autograd.function``,
@@ -66,6 +69,8 @@ class _TorchAliasFinder:
         if len(parts) < 2 or parts[0] != __name__:
             return None
         import importlib.util
+        if len(parts) == 2 and parts[1] in _FALLBACK:
+            return importlib.util.spec_from_loader(fullname, _FallbackLoader(parts[1]))
         if parts[1] in ("vision", "audio"):       # sub-modules without a file here: torchvision / torchaudio
             torch_name = ".".join(["torchvision" if parts[1] == "vision" else "torchaudio"] + parts[2:])
         elif parts[1] == "_transforms":
@@ -85,6 +90,17 @@ class _TorchAliasFinder:
             except (ImportError, ValueError, AttributeError):
                 return None
         return importlib.util.spec_from_loader(fullname, _TorchAliasLoader(torch_name))
+
+
+class _FallbackLoader:
+    def __init__(self, short):
+        self.short = short
+
+    def create_module(self, spec):
+        return _sys.modules.get(spec.name) or _build_fallback(self.short)
+
+    def exec_module(self, module):
+        pass
 
 
 class _TorchAliasLoader:
@@ -109,7 +125,8 @@ class _AliasedParentFinder:
             return None
         parent_name, _, tail = fullname.rpartition(".")
         parent = _sys.modules.get(parent_name)
-        real = getattr(parent, "__name__", "")
+        base = getattr(parent, "__dict__", {}).get("__wrapped_base__") if parent is not None else None
+        real = getattr(base if base is not None else parent, "__name__", "")
         if parent is None or real == parent_name or real.split(".")[0] not in ("torch", "torchvision", "torchaudio"):
             return None
         import importlib.util
@@ -133,7 +150,53 @@ if not [f for f in _sys.meta_path if type(f).__name__ == "_AliasedParentFinder"]
     _sys.meta_path.insert(0, _AliasedParentFinder())
 
 
+def _build_fallback(name):
+    """``export``, ``graph``, ``accelerator``, ``mps``, ``monitor``, ``package``, ``backends``: PyTorch's packages with
+    the reference's extra top-level names looked up in PyTorch's sub-modules."""
+    from . import _fallback
+    full = f"{__name__}.{name}"
+    if name == "export":
+        return _fallback.make(full, "torch.export", search=(
+            "torch.export.graph_signature", "torch.export.dynamic_shapes", "torch.export.exported_program",
+            "torch.export.pt2_archive._package", "torch.export.pt2_archive", "torch.export.unflatten"),
+            extra={"export_for_training": getattr(_torch.export, "export_for_training", _torch.export.export),
+                   "GraphSignature": _torch.export.graph_signature.ExportGraphSignature})
+    if name == "graph":
+        return _fallback.make(full, "torch.fx", search=(
+            "torch.fx.tensor_type", "torch.fx.annotate", "torch.fx.subgraph_rewriter", "torch.fx.immutable_collections",
+            "torch.fx.experimental.refinement_types", "torch.fx.experimental.graph_gradual_typechecker",
+            "torchvision.models.feature_extraction", "torch.jit", "torch._higher_order_ops.while_loop",
+            "torch._higher_order_ops"),
+            extra={"GraphCaptureError": RuntimeError})
+    if name == "accelerator":
+        import contextlib
+        return _fallback.make(full, "torch.accelerator", search=("torch.cuda", "torch.cuda.graphs", "torch.cuda.random"),
+                              extra={"Graph": _torch.cuda.CUDAGraph, "graphs": _torch.cuda.graphs, "random": _torch.cuda.random,
+                                     "empty_host_cache": getattr(_torch._C, "_host_emptyCache", lambda: None)})
+    if name == "mps":
+        return _fallback.make(full, "torch.mps", extra={"current_device": lambda: 0,
+                                                        "memory_allocated": _torch.mps.current_allocated_memory,
+                                                        "memory_reserved": _torch.mps.driver_allocated_memory})
+    if name == "monitor":
+        import collections
+        return _fallback.make(full, "torch.monitor", extra={"StatResult": collections.namedtuple(
+            "StatResult", ["name", "aggregation", "value", "count"])})
+    if name == "package":
+        import enum
+        return _fallback.make(full, "torch.package", search=("torch.package.package_exporter",), extra={
+            "PackagingErrorReason": getattr(importlib_import("torch.package.package_exporter"), "PackagingErrorReason", enum.Enum)})
+    raise AttributeError(name)
+
+
+def importlib_import(name):
+    return _importlib.import_module(name)
+
+
 def __getattr__(name):
+    if name in _FALLBACK:
+        mod = _sys.modules.get(f"{__name__}.{name}") or _build_fallback(name)
+        globals()[name] = mod
+        return mod
     if name in _LAZY_OWN:
         mod = _importlib.import_module(f"{__name__}.{name}")
         globals()[name] = mod

@@ -91,3 +91,18 @@ def test_linalg_sparse_func_additions():
     assert gp is importlib.import_module("torch.fx.passes")
     from tensorplay_b200.nn.modules import BatchNorm2d, GatedDeltaNet  # PyTorch's long tail next to own layers
     assert BatchNorm2d is torch.nn.BatchNorm2d and GatedDeltaNet.__module__.startswith("tensorplay_b200")
+
+
+def test_fallback_packages_show_pytorchs_names_and_the_references_extras():
+    import torch
+    import tensorplay_b200 as tp
+    import tensorplay_b200.export as E
+    import tensorplay_b200.export.graph_signature as gs
+    import tensorplay_b200.graph as G
+    assert E is tp.export and E.Dim is torch.export.Dim and E.InputKind is torch.export.graph_signature.InputKind
+    assert gs is importlib.import_module("torch.export.graph_signature")          # same object, not a second execution
+    assert G.symbolic_trace is torch.fx.symbolic_trace and G.TensorType is torch.fx.tensor_type.TensorType
+    assert importlib.import_module("tensorplay_b200.graph.passes") is importlib.import_module("torch.fx.passes")
+    assert tp.accelerator.Graph is torch.cuda.CUDAGraph and tp.monitor.StatResult._fields[0] == "name"
+    with pytest.raises(AttributeError):
+        tp.export.no_such_name
