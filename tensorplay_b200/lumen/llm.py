@@ -240,5 +240,126 @@ def reconstruction_error(sae: SparseAutoencoder, activations: Tensor) -> Tensor:
     return (x_hat - x).pow(2).sum() / (x - x.mean(0, keepdim=True)).pow(2).sum().clamp_min(1e-12)
 
 
+# ------------------------------------------------------------------------------------------- cross-layer transcoder
+def collect_component_updates(model: nn.Module, tokens: Tensor, layers: Optional[Sequence[nn.Module]] = None):
+    """Per block: the residual stream that enters it and the update it adds (output minus input), both ``[B, T, H]``:
+    the training pairs of a transcoder (lumen/llm/clt.py:111)."""
+    layers = list(model.layers) if layers is None else list(layers)
+    ins: List[Tensor] = []
+    outs: List[Tensor] = []
+    hooks = []
+    for l in layers:
+        hooks.append(l.register_forward_pre_hook(lambda m, a: ins.append(a[0].detach())))
+        hooks.append(l.register_forward_hook(lambda m, a, o: outs.append((o[0] if isinstance(o, tuple) else o).detach())))
+    try:
+        with torch.no_grad():
+            model(tokens)
+    finally:
+        for h in hooks:
+            h.remove()
+    return ins, [o - i for i, o in zip(ins, outs)]
+
+
+class CrossLayerTranscoder(nn.Module):
+    """Sparse features read from the residual stream at every layer and written to the updates of that layer and all
+    later ones (lumen/llm/clt.py:20): ``f_l = relu(W_enc[l] x_l + b_enc[l])``, ``y_hat_m = sum_{l <= m} W_dec[l -> m] f_l +
+    b_dec[m]``. A feature's effect on the output then runs through linear decoders only, which is what makes attribution
+    between features exact."""
+
+    def __init__(self, n_layers: int, d_model: int, d_dict: int, l1_coeff: float = 1e-3):
+        super().__init__()
+        self.n_layers, self.d_model, self.d_dict, self.l1_coeff = n_layers, d_model, d_dict, l1_coeff
+        self.encoders = nn.ModuleList([nn.Linear(d_model, d_dict) for _ in range(n_layers)])
+        # decoders[l][m - l]: features of layer l -> update of layer m >= l
+        self.decoders = nn.ModuleList([nn.ModuleList([nn.Linear(d_dict, d_model, bias=False) for _ in range(n_layers - l)])
+                                       for l in range(n_layers)])
+        self.b_dec = nn.Parameter(torch.zeros(n_layers, d_model))
+        with torch.no_grad():
+            for l in range(n_layers):
+                for dec in self.decoders[l]:
+                    dec.weight.mul_(0.1)
+
+    def encode(self, xs: Sequence[Tensor]) -> List[Tensor]:
+        return [torch.relu(enc(x)) for enc, x in zip(self.encoders, xs)]
+
+    def decode(self, feats: Sequence[Tensor]) -> List[Tensor]:
+        out = []
+        for m in range(self.n_layers):
+            y = self.b_dec[m]
+            for l in range(m + 1):
+                y = y + self.decoders[l][m - l](feats[l])
+            out.append(y)
+        return out
+
+    def forward(self, xs: Sequence[Tensor]):
+        feats = self.encode(xs)
+        return self.decode(feats), feats
+
+    def loss(self, xs: Sequence[Tensor], ys: Sequence[Tensor]) -> Tensor:
+        preds, feats = self(xs)
+        rec = sum((p - y).pow(2).sum(-1).mean() for p, y in zip(preds, ys))
+        return rec + self.l1_coeff * sum(f.abs().sum(-1).mean() for f in feats)
+
+
+def train_clt(clt: CrossLayerTranscoder, inputs: Sequence[Tensor], updates: Sequence[Tensor], steps: int = 200,
+              batch_size: int = 256, lr: float = 1e-3, seed: int = 0) -> List[float]:
+    """Adam on random rows of the per-layer (input, update) pairs (``[N, d_model]`` each, or ``[B, T, d_model]``)."""
+    xs = [x.reshape(-1, x.shape[-1]).float() for x in inputs]
+    ys = [y.reshape(-1, y.shape[-1]).float() for y in updates]
+    opt = torch.optim.Adam(clt.parameters(), lr=lr)
+    g = torch.Generator().manual_seed(seed)
+    curve = []
+    for _ in range(steps):
+        idx = torch.randint(0, xs[0].shape[0], (min(batch_size, xs[0].shape[0]),), generator=g)
+        loss = clt.loss([x[idx] for x in xs], [y[idx] for y in ys])
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        curve.append(float(loss.detach()))
+    return curve
+
+
+# ------------------------------------------------------------------------------------------- attention pictures
+def _attention_grid(maps: Tensor):
+    """``[rows, cols, T, T]`` maps -> one image array with a one-pixel gutter (values in [0, 1] per map)."""
+    import numpy as np
+    r, c, t, _ = maps.shape
+    m = maps.detach().float().cpu()
+    m = m / m.amax(dim=(-1, -2), keepdim=True).clamp_min(1e-12)
+    img = np.ones((r * (t + 1) - 1, c * (t + 1) - 1), dtype=np.float32)
+    for i in range(r):
+        for j in range(c):
+            img[i * (t + 1): i * (t + 1) + t, j * (t + 1): j * (t + 1) + t] = m[i, j].numpy()
+    return img
+
+
+def visualize_attention_heads(attention: Tensor, batch_index: int = 0, path: Optional[str] = None):
+    """Every head of one layer's attention ``[B, heads, T, T]`` side by side as a grey-scale array (saved as PNG when
+    ``path`` is given; no plotting library is needed)."""
+    img = _attention_grid(attention[batch_index].unsqueeze(0))
+    if path is not None:
+        from .visualization import save_heat_map
+        save_heat_map(path, torch.from_numpy(img))
+    return img
+
+
+def visualize_attention_multi_layer(attentions: Sequence[Tensor], batch_index: int = 0, path: Optional[str] = None):
+    """Layers down, heads across."""
+    img = _attention_grid(torch.stack([a[batch_index] for a in attentions]))
+    if path is not None:
+        from .visualization import save_heat_map
+        save_heat_map(path, torch.from_numpy(img))
+    return img
+
+
+def visualize_token_attention(attentions: Sequence[Tensor], tokens: Sequence[str], query_position: int = -1,
+                              batch_index: int = 0) -> str:
+    """HTML line of the tokens shaded by how much the query position attends to each."""
+    w = token_attention(attentions, query_position)[batch_index]
+    w = (w / w.max().clamp_min(1e-12)).tolist()
+    spans = [f'<span style="background-color: rgba(255, 120, 0, {a:.3f})">{t}</span>' for t, a in zip(tokens, w)]
+    return "<div>" + " ".join(spans) + "</div>"
+
+
 # the reference has a package at this path: deeper module names resolve to views of the pack
 __path__: list = []

@@ -318,3 +318,29 @@ def test_surrogate_linear_models_recover_planted_weights():
     assert (m.representation()[0] - w_true).abs().max() < 1e-3
     g = L.compute_gradients(lambda a: (a * a).sum(1, keepdim=True), x[:4], target_ind=0)
     assert torch.allclose(g, 2 * x[:4])
+
+
+def test_cross_layer_transcoder_learns_the_blocks_updates():
+    import torch
+    from tensorplay_b200.lumen import (CrossLayerTranscoder, collect_component_updates, train_clt,
+                                       visualize_attention_heads, visualize_attention_multi_layer, visualize_token_attention)
+    from tensorplay_b200.models.llama import Llama, LlamaConfig
+    torch.manual_seed(0)
+    cfg = LlamaConfig.tiny(max_seq_len=16)
+    model = Llama(cfg)
+    model.reset_parameters(0)
+    toks = torch.randint(0, cfg.vocab_size, (16, 16))
+    ins, ups = collect_component_updates(model, toks)
+    assert len(ins) == len(ups) == cfg.num_layers and ins[0].shape == ups[0].shape == (16, 16, cfg.hidden_size)
+    # the update of block l is its output minus its input: the residual stream entering block l + 1
+    assert torch.allclose(ins[0] + ups[0], ins[1], atol=1e-5)
+    clt = CrossLayerTranscoder(cfg.num_layers, cfg.hidden_size, 4 * cfg.hidden_size, l1_coeff=1e-4)
+    curve = train_clt(clt, ins, ups, steps=150, batch_size=128, lr=3e-3)
+    assert curve[-1] < 0.5 * curve[0]
+    preds, feats = clt([x.reshape(-1, cfg.hidden_size) for x in ins])
+    assert len(preds) == cfg.num_layers and feats[0].shape[-1] == 4 * cfg.hidden_size and (feats[0] >= 0).all()
+    att = [torch.softmax(torch.randn(2, 3, 6, 6), -1) for _ in range(2)]
+    assert visualize_attention_heads(att[0]).shape == (6, 3 * 7 - 1)
+    assert visualize_attention_multi_layer(att).shape == (2 * 7 - 1, 3 * 7 - 1)
+    html = visualize_token_attention(att, list("abcdef"))
+    assert html.count("<span") == 6 and "rgba(255, 120, 0, 1.000)" in html
