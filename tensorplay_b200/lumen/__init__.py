@@ -40,6 +40,8 @@ from .models import (LinearModel, Model, SGDLasso, SGDLinearModel, SGDLinearRegr
                      SkLearnLinearModel, SkLearnLinearRegression, SkLearnRidge)
 _models = models   # the reference's private package name
 from .concept import CAV, TCAV, Classifier, Concept, ConceptInterpreter, DefaultClassifier  # noqa: E402
+from .llm import (AttributionGraph, AttributionGraphData, CircuitEdge, CircuitNode, FeatureCircuit, FeatureCircuitData,  # noqa: E402
+                  GraphEdge, GraphNode, top_attention_heads, top_mlp_features)
 from .llm import (CrossLayerTranscoder, collect_component_updates, train_clt, visualize_attention_heads,  # noqa: E402
                   visualize_attention_multi_layer, visualize_token_attention)
 from .llm import (ActivationPatching, LogitLens, SparseAutoencoder, collect_hidden_states, extract_attention,  # noqa: E402

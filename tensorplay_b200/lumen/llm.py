@@ -361,5 +361,141 @@ def visualize_token_attention(attentions: Sequence[Tensor], tokens: Sequence[str
     return "<div>" + " ".join(spans) + "</div>"
 
 
+# ------------------------------------------------------------------------------------------- attribution graphs
+from dataclasses import dataclass, field  # noqa: E402
+
+
+@dataclass(frozen=True)
+class GraphNode:
+    layer: int
+    feature: int
+    activation: float
+
+
+@dataclass(frozen=True)
+class GraphEdge:
+    src: int        # index into ``nodes``
+    dst: int
+    weight: float
+
+
+@dataclass
+class AttributionGraphData:
+    nodes: List[GraphNode] = field(default_factory=list)
+    edges: List[GraphEdge] = field(default_factory=list)
+
+    def incoming(self, node: int) -> List[GraphEdge]:
+        return [e for e in self.edges if e.dst == node]
+
+    def outgoing(self, node: int) -> List[GraphEdge]:
+        return [e for e in self.edges if e.src == node]
+
+
+class AttributionGraph:
+    """Direct effects between the active features of a cross-layer transcoder at one token (lumen/llm/attribution_graph.py).
+    A feature ``(l, i)`` with activation ``a`` writes ``a * W_dec[l -> k][:, i]`` into the update of every layer ``k >= l``;
+    a later feature ``(m, j)``, ``m > l``, reads the residual stream through ``W_enc[m][j]``. Its pre-activation therefore
+    contains ``a * sum_{k = l}^{m - 1} W_enc[m][j] . W_dec[l -> k][:, i]``: the weight of the edge. Everything on the way is
+    linear, so the edges into a node add up to the part of its pre-activation that the earlier features explain."""
+
+    def __init__(self, clt: "CrossLayerTranscoder"):
+        self.clt = clt
+
+    @torch.no_grad()
+    def build(self, xs: Sequence[Tensor], top_k: int = 8, min_weight: float = 0.0) -> AttributionGraphData:
+        """``xs``: the residual stream entering every layer at ONE token, ``[d_model]`` each. Keeps the ``top_k`` most
+        active features per layer."""
+        clt = self.clt
+        feats = clt.encode([x.reshape(1, -1).float() for x in xs])
+        data = AttributionGraphData()
+        per_layer: List[List[int]] = []
+        for l, f in enumerate(feats):
+            f = f[0]
+            k = min(top_k, int((f > 0).sum()))
+            idx = f.topk(k).indices.tolist() if k else []
+            per_layer.append(list(range(len(data.nodes), len(data.nodes) + len(idx))))
+            data.nodes += [GraphNode(l, i, float(f[i])) for i in idx]
+        for l in range(clt.n_layers):
+            for m in range(l + 1, clt.n_layers):
+                if not per_layer[l] or not per_layer[m]:
+                    continue
+                src_f = [data.nodes[n].feature for n in per_layer[l]]
+                dst_f = [data.nodes[n].feature for n in per_layer[m]]
+                written = sum(clt.decoders[l][k - l].weight[:, src_f] for k in range(l, m))       # [d_model, |src|]
+                w = clt.encoders[m].weight[dst_f] @ written                                      # [|dst|, |src|]
+                acts = torch.tensor([data.nodes[n].activation for n in per_layer[l]])
+                w = w * acts
+                for bi, b in enumerate(per_layer[m]):
+                    for ai, a in enumerate(per_layer[l]):
+                        if abs(float(w[bi, ai])) > min_weight:
+                            data.edges.append(GraphEdge(a, b, float(w[bi, ai])))
+        return data
+
+
+@dataclass(frozen=True)
+class CircuitNode:
+    layer: int
+    feature: int
+    score: float
+
+
+@dataclass(frozen=True)
+class CircuitEdge:
+    src: int
+    dst: int
+    weight: float
+
+
+@dataclass
+class FeatureCircuitData:
+    nodes: List[CircuitNode] = field(default_factory=list)
+    edges: List[CircuitEdge] = field(default_factory=list)
+
+
+class FeatureCircuit:
+    """The part of an attribution graph that matters for one output direction (lumen/llm/feature_circuit.py): every
+    feature is scored by its direct effect on ``direction`` (a vector in the residual stream, e.g. the difference of two
+    unembedding rows) through all its decoders, the ``top_k`` features per layer are kept, and the edges between them
+    are those of the attribution graph."""
+
+    def __init__(self, clt: "CrossLayerTranscoder"):
+        self.clt, self.graph = clt, AttributionGraph(clt)
+
+    @torch.no_grad()
+    def build(self, xs: Sequence[Tensor], direction: Tensor, top_k: int = 4) -> FeatureCircuitData:
+        clt = self.clt
+        feats = clt.encode([x.reshape(1, -1).float() for x in xs])
+        keep: List[List[int]] = []
+        out = FeatureCircuitData()
+        for l, f in enumerate(feats):
+            effect = sum(dec.weight.t() @ direction.float() for dec in clt.decoders[l]) * f[0]   # [d_dict]
+            k = min(top_k, int((f[0] > 0).sum()))
+            idx = effect.abs().topk(k).indices.tolist() if k else []
+            keep.append(idx)
+            out.nodes += [CircuitNode(l, i, float(effect[i])) for i in idx]
+        full = self.graph.build(xs, top_k=clt.d_dict)
+        pos = {(n.layer, n.feature): i for i, n in enumerate(out.nodes)}
+        for e in full.edges:
+            a, b = full.nodes[e.src], full.nodes[e.dst]
+            if (a.layer, a.feature) in pos and (b.layer, b.feature) in pos:
+                out.edges.append(CircuitEdge(pos[(a.layer, a.feature)], pos[(b.layer, b.feature)], e.weight))
+        return out
+
+
+@torch.no_grad()
+def top_mlp_features(sae: "SparseAutoencoder", hidden: Tensor, k: int = 10) -> List[tuple]:
+    """The ``k`` dictionary features most active on ``hidden`` (any leading shape), as ``(feature, mean activation)``."""
+    f = sae.encode(hidden.reshape(-1, hidden.shape[-1]).float()).mean(0)
+    top = f.topk(min(k, f.numel()))
+    return [(int(i), float(v)) for i, v in zip(top.indices, top.values)]
+
+
+def top_attention_heads(attentions: Sequence[Tensor], query_position: int = -1, key_position: int = 0, k: int = 5) -> List[tuple]:
+    """The ``k`` (layer, head) pairs whose attention from ``query_position`` to ``key_position`` is largest (batch mean)."""
+    scores = [(float(a[:, h, query_position, key_position].mean()), l, h)
+              for l, a in enumerate(attentions) for h in range(a.shape[1])]
+    return [(l, h, s) for s, l, h in sorted(scores, reverse=True)[:k]]
+
+
 # the reference has a package at this path: deeper module names resolve to views of the pack
 __path__: list = []

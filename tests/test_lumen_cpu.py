@@ -344,3 +344,43 @@ def test_cross_layer_transcoder_learns_the_blocks_updates():
     assert visualize_attention_multi_layer(att).shape == (2 * 7 - 1, 3 * 7 - 1)
     html = visualize_token_attention(att, list("abcdef"))
     assert html.count("<span") == 6 and "rgba(255, 120, 0, 1.000)" in html
+
+
+def test_attribution_graph_edges_sum_to_the_explained_preactivation():
+    """With zero encoder biases and inputs that are exactly what the earlier features wrote, the edges into a node add up
+    to its pre-activation: the linearity the graph relies on."""
+    import torch
+    from tensorplay_b200.lumen import AttributionGraph, CrossLayerTranscoder, FeatureCircuit, top_attention_heads
+    torch.manual_seed(0)
+    L, d, D = 3, 8, 12
+    clt = CrossLayerTranscoder(L, d, D)
+    with torch.no_grad():
+        for enc in clt.encoders:
+            enc.bias.zero_()
+        clt.b_dec.zero_()
+        for l in range(L):
+            for dec in clt.decoders[l]:
+                dec.weight.copy_(torch.randn(d, D) * 0.3)
+    # build a residual stream that the transcoder itself explains: x_0 random, x_{m} = sum of updates written for layers < m
+    x0 = torch.randn(d)
+    xs = [x0]
+    feats = []
+    for m in range(1, L + 1):
+        feats.append(torch.relu(clt.encoders[m - 1](xs[m - 1])))
+        if m < L:
+            xs.append(sum(clt.decoders[l][k - l](feats[l]) for l in range(m) for k in range(l, m)))
+    g = AttributionGraph(clt).build(xs, top_k=D)
+    assert all(e.src != e.dst and g.nodes[e.src].layer < g.nodes[e.dst].layer for e in g.edges)
+    for i, n in enumerate(g.nodes):
+        if n.layer == 0:
+            continue
+        incoming = sum(e.weight for e in g.incoming(i))
+        pre = float((clt.encoders[n.layer].weight[n.feature] @ xs[n.layer]).detach())
+        assert abs(incoming - pre) < 1e-4 * max(1.0, abs(pre)) and abs(pre - n.activation) < 1e-5   # active: relu is the identity
+    direction = torch.randn(d)
+    circ = FeatureCircuit(clt).build(xs, direction, top_k=2)
+    assert len(circ.nodes) <= 2 * L and all(abs(e.weight) >= 0 for e in circ.edges)
+    att = [torch.zeros(1, 2, 4, 4) for _ in range(2)]
+    att[1][0, 1, -1, 0] = 0.9
+    att[0][0, 0, -1, 0] = 0.4
+    assert [(l, h) for l, h, _ in top_attention_heads(att, k=2)] == [(1, 1), (0, 0)]
