@@ -14,10 +14,12 @@ __all__ = ["GroupedQueryAttention", "LayerNorm", "Linear", "RMSNorm", "RotaryEmb
 def __getattr__(name):
     """The long tail of layers (``Conv2d``, ``BatchNorm1d``, ``LSTM`` ...) is PyTorch's."""
     import torch.nn as _nn
-    try:
-        return getattr(_nn.modules, name)
-    except AttributeError:
-        return getattr(_nn, name)
+    for ns in (_nn.modules, _nn, _nn.modules.linear, _nn.modules.activation):
+        try:
+            return getattr(ns, name)
+        except AttributeError:
+            continue
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
 
 
 from ... import _views as _views  # noqa: E402
