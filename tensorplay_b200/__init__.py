@@ -47,7 +47,7 @@ from .serialization import inspect_checkpoint, load, save  # noqa: E402
 from .nn.generation import sample  # noqa: E402
 
 _LAZY_OWN = {"distributed", "utils", "models", "parallel", "cuda", "profiler", "autograd", "compat",
-             "multiprocessing", "testing", "quantization", "metrics", "snn", "library", "quantum", "lumen", "vision", "linalg", "sparse", "func", "audio"}
+             "multiprocessing", "testing", "quantization", "metrics", "snn", "library", "quantum", "lumen", "vision", "linalg", "sparse", "func", "audio", "config"}
 _LAZY_TORCH = {"fft", "special", "distributions", "futures", "hub", "onnx", "ao", "mps",
                "masked", "nested", "monitor", "backends", "accelerator", "export", "fx", "random",
                "signal", "overrides", "package", "storage", "types", "jit", "_numpy"}
