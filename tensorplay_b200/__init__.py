@@ -47,8 +47,8 @@ from .serialization import inspect_checkpoint, load, save  # noqa: E402
 from .nn.generation import sample  # noqa: E402
 
 _LAZY_OWN = {"distributed", "utils", "models", "parallel", "cuda", "profiler", "autograd", "compat",
-             "multiprocessing", "testing", "quantization", "metrics", "snn", "library", "quantum", "lumen", "vision", "linalg", "sparse", "func", "audio", "config"}
-_LAZY_TORCH = {"fft", "special", "distributions", "futures", "hub", "onnx", "ao", "mps",
+             "multiprocessing", "testing", "quantization", "metrics", "snn", "library", "quantum", "lumen", "vision", "linalg", "sparse", "func", "audio", "config", "ao"}
+_LAZY_TORCH = {"fft", "special", "distributions", "futures", "hub", "onnx", "mps",
                "masked", "nested", "monitor", "backends", "accelerator", "export", "fx", "random",
                "signal", "overrides", "package", "storage", "types", "jit", "_numpy"}
 
@@ -62,7 +62,7 @@ class _TorchAliasFinder:
     ``profiler.profiler``, ``multiprocessing.reductions``), so module paths of the reference that only
     name PyTorch-equivalent code keep importing. Sits last on ``sys.meta_path``: own modules win."""
 
-    _PKGS = ("optim", "autograd", "profiler", "multiprocessing", "utils", "cuda", "amp", "testing", "nn", "distributed")
+    _PKGS = ("optim", "autograd", "profiler", "multiprocessing", "utils", "cuda", "amp", "testing", "nn", "distributed", "ao")
 
     def find_spec(self, fullname, path=None, target=None):
         parts = fullname.split(".")

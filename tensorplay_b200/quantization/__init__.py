@@ -117,3 +117,7 @@ class Float8Linear(torch.nn.Module):
 from .awq import AWQLinear, awq_quantize_, search_scales  # noqa: E402
 from .pruning import (WeightSparsifier, compare_models, cubic_sparsity, global_magnitude_masks,  # noqa: E402
                       magnitude_mask, n_m_mask, sqnr)
+
+
+from .bitnet import (BitNetLinear, BitNetPacked2bitLinearWeight, BitNetTrainingConfig, BitNetTrainingLinearWeight,  # noqa: E402,F401
+                     bitnet_linear, bitnet_linear_packed, bitnet_training, pack_ternary, ternary_quantize, unpack_ternary)
