@@ -121,3 +121,5 @@ from .pruning import (WeightSparsifier, compare_models, cubic_sparsity, global_m
 
 from .bitnet import (BitNetLinear, BitNetPacked2bitLinearWeight, BitNetTrainingConfig, BitNetTrainingLinearWeight,  # noqa: E402,F401
                      bitnet_linear, bitnet_linear_packed, bitnet_training, pack_ternary, ternary_quantize, unpack_ternary)
+from .workflows import *  # noqa: E402,F401,F403
+from .workflows import quantize_  # noqa: E402,F401  (handles the BitNet configuration too)
