@@ -181,6 +181,14 @@ def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: b
         seg_end = seg_end.to(torch.int32).contiguous()
     native = (q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128) and use_native(q, k, v))
     if not native:
+        if (q.is_cuda and q.dtype in (torch.bfloat16, torch.float16) and not window and seg_start is None and seg_end is None
+                and (not causal or q.shape[1] == k.shape[1]) and q.shape[2] % k.shape[2] == 0):
+            # head dims without a kernel here (32, 96, 256 ...): PyTorch's library attention instead of the fp32
+            # formula, which materialises the whole score matrix
+            o = torch.nn.functional.scaled_dot_product_attention(
+                q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=causal, scale=scale,
+                enable_gqa=q.shape[2] != k.shape[2])
+            return o.transpose(1, 2)
         return attention_reference(q, k, v, causal, scale, window, seg_start, seg_end)
     if not _strides_ok(q):
         q = q.contiguous()

@@ -179,3 +179,26 @@ def test_varlen_attn_single_launch_matches_per_sequence():
         assert _rel(o[a:a + n], ref) < 1e-2
         assert _rel(ow[a:a + n], refw) < 1e-2
         a += n
+
+
+@pytest.mark.parametrize("D,Hq,Hkv", [(96, 4, 2), (256, 2, 2), (32, 8, 1)])
+@pytest.mark.parametrize("causal", [True, False])
+def test_head_dims_without_a_kernel_use_library_attention(D, Hq, Hkv, causal):
+    """Head dims other than 64 / 128 run through PyTorch's attention (no score matrix in memory) with the same
+    semantics: grouped heads, causal or full, gradients."""
+    from tensorplay_b200.ops.attention import attention_reference, flash_attention
+    torch.manual_seed(0)
+    B, T = 2, 200
+    q = torch.randn(B, T, Hq, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(B, T, Hkv, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(B, T, Hkv, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    o = flash_attention(q, k, v, causal=causal)
+    g = torch.randn_like(o)
+    o.backward(g)
+    qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    ref = attention_reference(qr, kr, vr, causal, D ** -0.5)
+    ref.backward(g.float())
+    assert o.shape == (B, T, Hq, D) and (o.float() - ref).abs().max() < 0.03
+    for a, b in ((q.grad, qr.grad), (k.grad, kr.grad), (v.grad, vr.grad)):
+        assert (a.float() - b).abs().max() < 0.05 * max(1.0, b.abs().max().item())
+
