@@ -10,7 +10,7 @@ globals().update({_n: getattr(_torch.ao.quantization, _n) for _n in dir(_torch.a
 from ..quantization import bitnet as _bitnet
 from ..quantization.bitnet import *  # noqa: F401,F403
 from ..quantization.workflows import *  # noqa: F401,F403
-from ..quantization.workflows import quantize_  # noqa: F401
+from ..quantization import quantize_  # noqa: F401  (recipe names and configuration objects)
 
 
 def dequantize(t):

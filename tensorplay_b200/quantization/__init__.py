@@ -80,10 +80,15 @@ class WeightOnlyLinear(torch.nn.Module):
         return weight_only_linear(x, self.qweight, self.scale, self.zero, self.bias, self.bits, self.group_size)
 
 
-def quantize_(module: torch.nn.Module, mode: str = "int8_weight_only", group_size: int = 0,
+def quantize_(module: torch.nn.Module, mode="int8_weight_only", group_size: int = 0,
               filter_fn=None) -> torch.nn.Module:
     """Swap every ``nn.Linear`` (accepted by ``filter_fn``) for its quantised counterpart in place.
-    Modes: ``int8_weight_only``, ``int4_weight_only``, ``int8_dynamic``, ``float8_weight_only``."""
+    ``mode``: a recipe name (``int8_weight_only``, ``int4_weight_only``, ``int8_dynamic``, ``float8_weight_only``) or a
+    configuration object / class of ``quantization.workflows`` (int8 mixed-precision training, the weight-only and fp8
+    configurations, BitNet training)."""
+    if not isinstance(mode, str):
+        from .workflows import quantize_ as _by_config
+        return _by_config(module, mode, filter_fn)
     make = {
         "int8_weight_only": lambda m: WeightOnlyLinear(m, 8, group_size),
         "int4_weight_only": lambda m: WeightOnlyLinear(m, 4, group_size or 128),
@@ -121,5 +126,4 @@ from .pruning import (WeightSparsifier, compare_models, cubic_sparsity, global_m
 
 from .bitnet import (BitNetLinear, BitNetPacked2bitLinearWeight, BitNetTrainingConfig, BitNetTrainingLinearWeight,  # noqa: E402,F401
                      bitnet_linear, bitnet_linear_packed, bitnet_training, pack_ternary, ternary_quantize, unpack_ternary)
-from .workflows import *  # noqa: E402,F401,F403
-from .workflows import quantize_  # noqa: E402,F401  (handles the BitNet configuration too)
+from .workflows import *  # noqa: E402,F401,F403  (``quantize_`` above dispatches configuration objects to it)

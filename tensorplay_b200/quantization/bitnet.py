@@ -17,7 +17,7 @@ import torch
 from torch import Tensor, nn
 
 __all__ = ["ternary_quantize", "pack_ternary", "unpack_ternary", "bitnet_linear", "bitnet_linear_packed", "BitNetLinear",
-           "BitNetTrainingLinearWeight", "BitNetPacked2bitLinearWeight", "BitNetTrainingConfig", "bitnet_training", "quantize_"]
+           "BitNetTrainingLinearWeight", "BitNetPacked2bitLinearWeight", "BitNetTrainingConfig", "bitnet_training"]
 
 
 def ternary_quantize(weight: Tensor, eps: float = 1e-5) -> Tuple[Tensor, Tensor]:

@@ -17,7 +17,7 @@ from torch import Tensor, nn
 
 from .. import ops
 
-__all__ = ["quantize_", "Int8MixedPrecisionTrainingConfig", "Int8MixedPrecisionTrainingLinear", "int8_mixed_precision_training",
+__all__ = ["Int8MixedPrecisionTrainingConfig", "Int8MixedPrecisionTrainingLinear", "int8_mixed_precision_training",
            "Int8WeightOnlyQuantizedTrainingConfig", "Int8WeightOnlyQuantizedLinear", "int8_weight_only_quantized_training",
            "Int4WeightOnlyConfig", "WeightOnlyInt4Linear", "Int4WeightOnlyQuantizedLinear", "Float8WeightOnlyConfig",
            "Float8WeightOnlyInferenceConfig", "Float8WeightOnlyInferenceLinear", "float8_weight_only", "float8_weight_only_inference",
