@@ -134,9 +134,11 @@ class ZeroRedundancyOptimizer(Optimizer, Joinable):
 
     # ------------------------------------------------------------------ step
     def _sync_hyperparameters(self) -> None:
-        live = [g for g in self._local_groups if g["params"]] or self._local_groups
-        src = [sg for sg, g in zip(self.param_groups, self._local_groups) if g in live]
-        for local, glob in zip(self.optim.param_groups, src):
+        # the local optimizer holds the groups that own parameters on this rank (all of them when none does), in
+        # order: pair them with the outer groups by position, never by comparing group dictionaries
+        keep = [i for i, g in enumerate(self._local_groups) if g["params"]] or list(range(len(self._local_groups)))
+        for local, i in zip(self.optim.param_groups, keep):
+            glob = self.param_groups[i]
             for k, v in glob.items():
                 if k != "params":
                     local[k] = v
