@@ -62,17 +62,12 @@ def set_timeout(timeout: timedelta, group=None) -> None:
 
 
 def register_device_backend(name: str, factory: Callable[[Any], Any]) -> None:
-    """Registers ``factory(process_group) -> provider`` as the collective provider of backend ``name`` and makes the
-    name known to ``Backend``; ``device_backend_factory(name)`` returns it."""
+    """Records ``factory(process_group) -> provider`` as the collective provider of the device backend ``name``;
+    ``device_backend_factory(name)`` returns it. (Making ``name`` a backend of ``init_process_group`` takes a creator
+    that builds a process group from a store: ``Backend.register_backend``.)"""
     if not callable(factory):
         raise TypeError("device backend factory must be callable")
-    key = str(name).lower()
-    _device_backends[key] = factory
-    if not hasattr(dist.Backend, key.upper()):
-        try:
-            dist.Backend.register_backend(key, lambda store, rank, size, timeout: factory((store, rank, size, timeout)))
-        except Exception:
-            pass
+    _device_backends[str(name).lower()] = factory
 
 
 def device_backend_factory(name: str) -> Optional[Callable[[Any], Any]]:
