@@ -51,7 +51,15 @@ def nms(boxes: Tensor, scores: Tensor, iou_threshold: float) -> Tensor:
     n = boxes.shape[0]
     if n == 0:
         return torch.empty(0, dtype=torch.long, device=boxes.device)
-    if not (boxes.is_cuda and use_native(boxes) and (n + 63) // 64 * 8 <= 200 * 1024):
+    if not (boxes.is_cuda and use_native(boxes)) or n > 32768:
+        # the kernel's overlap bit matrix takes n * n / 8 bytes (134 MB at 32 768 boxes) and the plain formulation an
+        # n x n float matrix: beyond that torchvision's operator, where it is installed
+        if n > 4096:
+            try:
+                import torchvision.ops as _tvo
+                return _tvo.nms(boxes.float(), scores.float(), iou_threshold)
+            except ImportError:
+                pass
         return nms_reference(boxes, scores, iou_threshold)
     b = boxes.detach().float().contiguous()
     order = torch.argsort(scores.detach(), descending=True, stable=True).contiguous()
