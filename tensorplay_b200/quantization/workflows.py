@@ -23,7 +23,8 @@ __all__ = ["Int8MixedPrecisionTrainingConfig", "Int8MixedPrecisionTrainingLinear
            "Float8WeightOnlyInferenceConfig", "Float8WeightOnlyInferenceLinear", "float8_weight_only", "float8_weight_only_inference",
            "Float8DynamicActivationFloat8WeightConfig", "Float8DynamicActivationFloat8WeightInferenceConfig",
            "Float8DynamicActivationInferenceLinear", "float8_dynamic_activation_float8_weight",
-           "float8_dynamic_activation_float8_weight_inference"]
+           "float8_dynamic_activation_float8_weight_inference", "Int2WeightOnlyConfig", "int2_weight_only", "WeightOnlyInt2Linear",
+           "pack_int2", "unpack_int2", "quantize_int2_weight_only", "BinaryWeightOnlyConfig", "BinaryWeightOnlyLinear"]
 
 
 def _rowwise_int8(x: Tensor):
@@ -191,6 +192,85 @@ class Float8DynamicActivationInferenceLinear(Float8WeightOnlyInferenceLinear):
         return super().forward(xq.to(x.dtype).reshape(x.shape))
 
 
+# ------------------------------------------------------------------------------------------- 2-bit and 1-bit weights
+def pack_int2(codes: Tensor) -> Tensor:
+    """``[N, K]`` codes in 0..3 -> ``uint8 [N, ceil(K / 4)]``, lowest bits first."""
+    N, K = codes.shape
+    c = torch.nn.functional.pad(codes.to(torch.uint8), (0, (-K) % 4)).view(N, -1, 4)
+    return (c[..., 0] | (c[..., 1] << 2) | (c[..., 2] << 4) | (c[..., 3] << 6)).contiguous()
+
+
+def unpack_int2(packed: Tensor, in_features: int) -> Tensor:
+    shifts = torch.tensor([0, 2, 4, 6], device=packed.device, dtype=torch.uint8)
+    return ((packed.unsqueeze(-1) >> shifts) & 3).reshape(packed.shape[0], -1)[:, :in_features]
+
+
+def quantize_int2_weight_only(w: Tensor, group_size: int = 64):
+    """Asymmetric 2-bit group quantisation: ``(packed, scale [N, K / g], zero [N, K / g])``, ``w ~ (code - zero) * scale``."""
+    N, K = w.shape
+    wf = w.float().reshape(N, K // group_size, group_size)
+    lo, hi = wf.amin(-1, keepdim=True), wf.amax(-1, keepdim=True)
+    scale = ((hi - lo) / 3.0).clamp_min(1e-8)
+    zero = torch.round(-lo / scale).clamp_(0, 3)
+    codes = torch.round(wf / scale + zero).clamp_(0, 3).to(torch.uint8).reshape(N, K)
+    return pack_int2(codes), scale.reshape(N, -1), zero.reshape(N, -1)
+
+
+@dataclass
+class Int2WeightOnlyConfig:
+    group_size: int = 64
+
+
+int2_weight_only = Int2WeightOnlyConfig
+
+
+class WeightOnlyInt2Linear(nn.Module):
+    """Two bits per weight with group-wise scale and zero point; dequantised on the fly."""
+
+    def __init__(self, lin: nn.Linear, group_size: int = 64):
+        super().__init__()
+        self.in_features, self.out_features, self.group_size = lin.in_features, lin.out_features, group_size
+        q, s, z = quantize_int2_weight_only(lin.weight.detach(), group_size)
+        self.register_buffer("qweight", q)
+        self.register_buffer("scale", s)
+        self.register_buffer("zero", z)
+        self.bias = None if lin.bias is None else nn.Parameter(lin.bias.detach().clone(), requires_grad=False)
+
+    def dequantize(self, dtype=torch.float32) -> Tensor:
+        codes = unpack_int2(self.qweight, self.in_features).float().view(self.out_features, -1, self.group_size)
+        return ((codes - self.zero.unsqueeze(-1)) * self.scale.unsqueeze(-1)).reshape(self.out_features, -1).to(dtype)
+
+    def forward(self, x: Tensor) -> Tensor:
+        return torch.nn.functional.linear(x, self.dequantize(x.dtype), self.bias)
+
+
+@dataclass
+class BinaryWeightOnlyConfig:
+    """One bit per weight: ``sign(w) * mean |w|`` per output row."""
+
+
+class BinaryWeightOnlyLinear(nn.Module):
+    def __init__(self, lin: nn.Linear):
+        super().__init__()
+        self.in_features, self.out_features = lin.in_features, lin.out_features
+        w = lin.weight.detach().float()
+        bits = (w >= 0).to(torch.uint8)
+        K = w.shape[1]
+        b = torch.nn.functional.pad(bits, (0, (-K) % 8)).view(w.shape[0], -1, 8)
+        weights = (1 << torch.arange(8, dtype=torch.int32, device=w.device)).to(torch.uint8)
+        self.register_buffer("qweight", (b * weights).sum(-1).to(torch.uint8))
+        self.register_buffer("scale", w.abs().mean(1, keepdim=True))
+        self.bias = None if lin.bias is None else nn.Parameter(lin.bias.detach().clone(), requires_grad=False)
+
+    def dequantize(self, dtype=torch.float32) -> Tensor:
+        shifts = torch.arange(8, device=self.qweight.device, dtype=torch.uint8)
+        bits = ((self.qweight.unsqueeze(-1) >> shifts) & 1).reshape(self.out_features, -1)[:, : self.in_features]
+        return ((bits.float() * 2 - 1) * self.scale).to(dtype)
+
+    def forward(self, x: Tensor) -> Tensor:
+        return torch.nn.functional.linear(x, self.dequantize(x.dtype), self.bias)
+
+
 def _swap(model: nn.Module, make: Callable[[nn.Linear], nn.Module], filter_fn) -> nn.Module:
     for name, child in list(model.named_children()):
         if isinstance(child, nn.Linear) and type(child) is nn.Linear and (filter_fn is None or filter_fn(child, name)):
@@ -219,6 +299,12 @@ def quantize_(model: nn.Module, config, filter_fn: Optional[Callable[[nn.Module,
     elif isinstance(cfg, Int4WeightOnlyConfig):
         def make(lin):
             return WeightOnlyInt4Linear(lin, cfg.group_size)
+    elif isinstance(cfg, Int2WeightOnlyConfig):
+        def make(lin):
+            return WeightOnlyInt2Linear(lin, cfg.group_size)
+    elif isinstance(cfg, BinaryWeightOnlyConfig):
+        def make(lin):
+            return BinaryWeightOnlyLinear(lin)
     elif isinstance(cfg, Float8DynamicActivationFloat8WeightConfig):
         def make(lin):
             return Float8DynamicActivationInferenceLinear(lin, cfg.activation_dtype, cfg.weight_dtype)

@@ -17,6 +17,8 @@ def _mlp(d=64, h=128):
     (W.Int4WeightOnlyConfig(group_size=32), W.WeightOnlyInt4Linear, 0.12),
     (W.Float8WeightOnlyConfig(), W.Float8WeightOnlyInferenceLinear, 0.06),
     (W.float8_dynamic_activation_float8_weight, W.Float8DynamicActivationInferenceLinear, 0.09),
+    (W.Int2WeightOnlyConfig(group_size=16), W.WeightOnlyInt2Linear, 0.45),
+    (W.BinaryWeightOnlyConfig(), W.BinaryWeightOnlyLinear, 0.85),
 ])
 def test_inference_configs_stay_close_to_the_float_model(config, layer, tol):
     ref, net = _mlp(), _mlp()
@@ -78,3 +80,18 @@ def test_int8_mixed_precision_on_the_tensor_core_gemm():
     r4 = w4[0](x[:4])
     W.quantize_(w4, W.Int4WeightOnlyConfig(group_size=128))
     assert (w4(x[:4]).float() - r4.float()).norm() / r4.float().norm() < 0.15     # decode-sized: the GEMV kernel
+
+
+def test_two_bit_packing_round_trip():
+    codes = torch.randint(0, 4, (5, 13))
+    assert torch.equal(W.unpack_int2(W.pack_int2(codes), 13), codes.to(torch.uint8))
+    w = torch.randn(6, 32)
+    q, s, z = W.quantize_int2_weight_only(w, 16)
+    lin = nn.Linear(32, 6, bias=False)
+    with torch.no_grad():
+        lin.weight.copy_(w)
+    m = W.WeightOnlyInt2Linear(lin, 16)
+    assert q.shape == (6, 8) and (m.dequantize() - w).abs().max() <= s.max() / 2 + 1e-6     # half a step at most
+    b = W.BinaryWeightOnlyLinear(lin)
+    assert torch.equal(torch.sign(b.dequantize()), torch.where(w >= 0, 1.0, -1.0)) and b.qweight.shape == (6, 4)
+
