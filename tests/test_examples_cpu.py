@@ -70,3 +70,10 @@ def test_decoder_lm_cache_equals_recompute():
     loss = m(t[:, :-1], t[:, 1:])
     loss.backward()
     assert m.embed.weight.grad is not None
+
+
+def test_uneven_inputs_example_ends_with_equal_parameters():
+    out = _run(["-m", "tensorplay_b200.distributed.run", "--nproc-per-node", "2", "examples/train_ddp_uneven.py",
+                "--device", "cpu", "--batches", "3"])
+    assert out.count("parameters equal to rank 0: True") == 2 and "rank 1: 4 batches" in out
+
