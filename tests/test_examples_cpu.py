@@ -77,3 +77,8 @@ def test_uneven_inputs_example_ends_with_equal_parameters():
                 "--device", "cpu", "--batches", "3"])
     assert out.count("parameters equal to rank 0: True") == 2 and "rank 1: 4 batches" in out
 
+
+def test_interpretability_example_runs():
+    out = _run(["examples/interpret_llm.py", "--steps", "60"])
+    assert "logit lens" in out and "attribution graph with" in out and "sparse autoencoder" in out
+
