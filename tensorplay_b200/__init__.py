@@ -47,9 +47,9 @@ from .serialization import inspect_checkpoint, load, save  # noqa: E402
 from .nn.generation import sample  # noqa: E402
 
 _LAZY_OWN = {"distributed", "utils", "models", "parallel", "cuda", "profiler", "autograd", "compat",
-             "multiprocessing", "testing", "quantization", "metrics", "snn", "library", "quantum", "lumen", "vision", "linalg", "sparse", "func", "audio", "config", "ao"}
+             "multiprocessing", "testing", "quantization", "metrics", "snn", "library", "quantum", "lumen", "vision", "linalg", "sparse", "func", "audio", "config", "ao", "backends"}
 _LAZY_TORCH = {"fft", "special", "distributions", "futures", "hub", "onnx", "mps",
-               "masked", "nested", "monitor", "backends", "accelerator", "export", "fx", "random",
+               "masked", "nested", "monitor", "accelerator", "export", "fx", "random",
                "signal", "overrides", "package", "storage", "types", "jit", "_numpy"}
 
 
@@ -62,7 +62,7 @@ class _TorchAliasFinder:
     ``profiler.profiler``, ``multiprocessing.reductions``), so module paths of the reference that only
     name PyTorch-equivalent code keep importing. Sits last on ``sys.meta_path``: own modules win."""
 
-    _PKGS = ("optim", "autograd", "profiler", "multiprocessing", "utils", "cuda", "amp", "testing", "nn", "distributed", "ao")
+    _PKGS = ("optim", "autograd", "profiler", "multiprocessing", "utils", "cuda", "amp", "testing", "nn", "distributed", "ao", "backends")
 
     def find_spec(self, fullname, path=None, target=None):
         parts = fullname.split(".")
