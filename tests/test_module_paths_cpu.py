@@ -106,3 +106,13 @@ def test_fallback_packages_show_pytorchs_names_and_the_references_extras():
     assert tp.accelerator.Graph is torch.cuda.CUDAGraph and tp.monitor.StatResult._fields[0] == "name"
     with pytest.raises(AttributeError):
         tp.export.no_such_name
+
+
+def test_backends_package():
+    import torch
+    import tensorplay_b200 as tp
+    assert tp.backends.cudnn is torch.backends.cudnn and tp.backends.cuda.matmul is torch.backends.cuda.matmul
+    assert tp.backends.cuda.is_available() == torch.cuda.is_available() and not tp.backends.cuda.is_ck_sdpa_available()
+    assert tp.backends.cuda.get_name() == (torch.cuda.get_device_name() if torch.cuda.is_available() else "cpu")
+    assert importlib.import_module("tensorplay_b200.backends.cudnn") is torch.backends.cudnn
+
